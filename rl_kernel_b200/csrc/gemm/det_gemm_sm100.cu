@@ -1,0 +1,396 @@
+// Batch-invariant bf16 GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma -> TMEM.
+//
+//   C[M,N] = A[M,K] * B[N,K]^T        (A and B may each be K-major or MN-major in memory)
+//
+// Numerical contract (what makes it deterministic, batch-invariant and TP-invariant):
+//   * every output element is one fp32 TMEM accumulator fed by UMMA K=16 steps in ascending k;
+//     no split-K, no atomics, one CTA owns a whole output tile;
+//   * the arithmetic of a row never depends on the other rows of its tile, so padding M to the
+//     128-row tile (TMA zero fill) makes every batch size run the same per-row program;
+//   * optional canonical K chunks (`nchunks` = 1,2,4,8, equal sizes): each chunk is accumulated
+//     in its own fp32 accumulator, rounded to bf16 once, and the chunks are combined by a
+//     balanced binary tree with a bf16 rounding at every node.  A rank that owns 8/TP canonical
+//     chunks therefore produces exactly the sub-tree that the fixed-order collective continues,
+//     and TP=1 reproduces the bits of TP=2/4/8.
+// The same tree is restated for the CPU in rl_kernel_b200/reference/gemm/det_gemm.py.
+//
+// Covers the reference's det_gemm_fwd / fwd_rhs_transposed / da / db entry points
+// (csrc/cuda/gemm/det_gemm_kernel.cu:527-602) with one kernel template.
+#include "rlk/host.h"
+#include "rlk/ptx.cuh"
+
+namespace rlk {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kGemmThreads = 192;  // warp0 TMA, warp1 MMA, warps2-5 epilogue
+
+struct GemmParams {
+  int M, N, K;
+  int nchunks;          // canonical K chunks (power of two)
+  int kb_per_chunk;     // 64-wide k blocks per chunk
+  int m_tiles, n_tiles;
+  void* C;              // bf16 or fp32, row-major
+  long long ldc;
+  int out_fp32;         // 1: C is fp32
+  int accumulate;       // 1: C += result (read-modify-write in fp32, rounded to C's dtype)
+  int* status;
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kStageA = BM * BK * 2;
+  static constexpr int kStageB = BN * BK * 2;
+  static constexpr int kStage = kStageA + kStageB;
+  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kBytes = kStages * kStage + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& mt, int& nt) {
+  constexpr int GROUP_M = 16;
+  const int per_group = GROUP_M * n_tiles;
+  const int g = t / per_group;
+  const int first_m = g * GROUP_M;
+  const int gsize = min(m_tiles - first_m, GROUP_M);
+  const int r = t - g * per_group;
+  mt = first_m + (r % gsize);
+  nt = r / gsize;
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const GemmParams p) {
+  using S = GemmSmem<BN>;
+  constexpr int kStages = S::kStages;
+  // TMEM columns: two accumulators (+ three packed-bf16 tree levels when chunked, BN==128 only)
+  constexpr uint32_t kTmemCols = (BN == 128) ? 512 : (2 * BN < 32 ? 32 : 2 * BN);
+  constexpr uint32_t kStackCol = 2 * BN;  // first column of the tree stack (BN == 128)
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * S::kStage);
+  // bars: full[kStages], empty[kStages], acc_full[2], acc_empty[2], then tmem ptr + abort flag
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t full0 = smem_u32(bars);
+  const uint32_t empty0 = smem_u32(bars + kStages);
+  const uint32_t accf0 = smem_u32(bars + 2 * kStages);
+  const uint32_t acce0 = smem_u32(bars + 2 * kStages + 2);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(accf0 + 8 * a, 1);
+      mbar_init(acce0 + 8 * a, 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_tiles = p.m_tiles * p.n_tiles;
+  const uint32_t smem_base = smem_u32(smem);
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
+        int mt, nt;
+        tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
+        const int m0 = mt * BM, n0 = nt * BN;
+        const int kbs = p.nchunks * p.kb_per_chunk;
+        for (int kb = 0; kb < kbs; ++kb, ++it) {
+          const uint32_t s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 101)) break;
+          const uint32_t fb = full0 + 8 * s;
+          mbar_expect_tx(fb, S::kStage);
+          const uint32_t sa = smem_base + s * S::kStage;
+          const uint32_t sb = sa + S::kStageA;
+          const int k0 = kb * BK;
+          if (!A_MN) {
+            tma_load_2d(sa, &tmA, k0, m0, fb);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, &tmA, m0 + 64 * i, k0, fb);
+          }
+          if (!B_MN) {
+            tma_load_2d(sb, &tmB, k0, n0, fb);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, &tmB, n0 + 64 * i, k0, fb);
+          }
+        }
+        if (*abort_flag) break;
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      uint32_t it = 0, u = 0;
+      for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+        for (int c = 0; c < p.nchunks; ++c, ++u) {
+          const uint32_t a = u & 1;
+          if (!mbar_wait(acce0 + 8 * a, ((u >> 1) & 1) ^ 1, abort_flag, p.status, 102)) break;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + a * BN;
+          for (int kb = 0; kb < p.kb_per_chunk; ++kb, ++it) {
+            const uint32_t s = it % kStages;
+            const uint32_t ph = (it / kStages) & 1;
+            if (!mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 103)) break;
+            tc_fence_after();
+            const uint32_t sa = smem_base + s * S::kStage;
+            const uint32_t sb = sa + S::kStageA;
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t da = A_MN ? umma_desc_sw128(sa + k * 2048, 8192, 1024)
+                                       : umma_desc_sw128(sa + k * 32, 16, 1024);
+              const uint64_t db = B_MN ? umma_desc_sw128(sb + k * 2048, 8192, 1024)
+                                       : umma_desc_sw128(sb + k * 32, 16, 1024);
+              umma_bf16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            umma_commit(empty0 + 8 * s);  // frees the smem stage when these MMAs retire
+          }
+          umma_commit(accf0 + 8 * a);  // accumulator of this chunk complete
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps)
+    const int quad = warp & 3;                  // TMEM lane quadrant this warp may access
+    const int row_in_tile = quad * 32 + lane;   // one thread owns one output row
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    uint32_t u = 0;
+    for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
+      int mt, nt;
+      tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
+      const int row = mt * BM + row_in_tile;
+      const int n0 = nt * BN;
+      for (int c = 0; c < p.nchunks; ++c, ++u) {
+        const uint32_t a = u & 1;
+        if (!mbar_wait(accf0 + 8 * a, (u >> 1) & 1, abort_flag, p.status, 104)) break;
+        tc_fence_after();
+        const bool last = (c == p.nchunks - 1);
+#pragma unroll 1
+        for (int col0 = 0; col0 < BN; col0 += 32) {
+          uint32_t r[32];
+          tmem_ld32(tmem_base + lane_off + a * BN + col0, r);
+          tmem_ld_wait();
+          if (p.nchunks == 1) {
+            if (row < p.M) {
+              if (p.out_fp32) {
+                float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + n0 + col0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                  if (n0 + col0 + j < p.N) {
+                    float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                           __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                    if (p.accumulate) {
+                      const float4 o = *reinterpret_cast<const float4*>(dst + j);
+                      v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                    }
+                    *reinterpret_cast<float4*>(dst + j) = v;
+                  }
+                }
+              } else {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) +
+                                     static_cast<long long>(row) * p.ldc + n0 + col0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                  if (n0 + col0 + j < p.N) {
+                    uint4 v;
+                    if (p.accumulate) {
+                      const uint4 o = *reinterpret_cast<const uint4*>(dst + j);
+                      v.x = pack_bf16x2(__uint_as_float(r[j]) + bf16_lo(o.x), __uint_as_float(r[j + 1]) + bf16_hi(o.x));
+                      v.y = pack_bf16x2(__uint_as_float(r[j + 2]) + bf16_lo(o.y), __uint_as_float(r[j + 3]) + bf16_hi(o.y));
+                      v.z = pack_bf16x2(__uint_as_float(r[j + 4]) + bf16_lo(o.z), __uint_as_float(r[j + 5]) + bf16_hi(o.z));
+                      v.w = pack_bf16x2(__uint_as_float(r[j + 6]) + bf16_lo(o.w), __uint_as_float(r[j + 7]) + bf16_hi(o.w));
+                    } else {
+                      v.x = pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                      v.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                      v.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                      v.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                    }
+                    *reinterpret_cast<uint4*>(dst + j) = v;
+                  }
+                }
+              }
+            }
+          } else if (BN == 128) {
+            // canonical chunk tree: leaf = bf16(fp32 accumulator); node = bf16(fp32(a)+fp32(b)).
+            uint32_t v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              v[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            int cc = c, level = 0;
+            while (cc & 1) {
+              uint32_t sv[16];
+              tmem_ld16(tmem_base + lane_off + kStackCol + level * 64 + (col0 >> 1), sv);
+              tmem_ld_wait();
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                v[j] = pack_bf16x2(__fadd_rn(bf16_lo(sv[j]), bf16_lo(v[j])),
+                                   __fadd_rn(bf16_hi(sv[j]), bf16_hi(v[j])));
+              cc >>= 1;
+              ++level;
+            }
+            if (!last) {
+              tmem_st16(tmem_base + lane_off + kStackCol + level * 64 + (col0 >> 1), v);
+            } else if (row < p.M) {
+              if (p.out_fp32) {
+                float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + n0 + col0;
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                  if (n0 + col0 + 2 * j < p.N) {
+                    float4 o = make_float4(bf16_lo(v[j]), bf16_hi(v[j]), bf16_lo(v[j + 1]), bf16_hi(v[j + 1]));
+                    if (p.accumulate) {
+                      const float4 q = *reinterpret_cast<const float4*>(dst + 2 * j);
+                      o.x += q.x; o.y += q.y; o.z += q.z; o.w += q.w;
+                    }
+                    *reinterpret_cast<float4*>(dst + 2 * j) = o;
+                  }
+                }
+              } else {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) +
+                                     static_cast<long long>(row) * p.ldc + n0 + col0;
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                  if (n0 + col0 + 2 * j < p.N) {
+                    uint4 o = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    if (p.accumulate) {
+                      const uint4 q = *reinterpret_cast<const uint4*>(dst + 2 * j);
+                      o.x = pack_bf16x2(bf16_lo(o.x) + bf16_lo(q.x), bf16_hi(o.x) + bf16_hi(q.x));
+                      o.y = pack_bf16x2(bf16_lo(o.y) + bf16_lo(q.y), bf16_hi(o.y) + bf16_hi(q.y));
+                      o.z = pack_bf16x2(bf16_lo(o.z) + bf16_lo(q.z), bf16_hi(o.z) + bf16_hi(q.z));
+                      o.w = pack_bf16x2(bf16_lo(o.w) + bf16_lo(q.w), bf16_hi(o.w) + bf16_hi(q.w));
+                    }
+                    *reinterpret_cast<uint4*>(dst + 2 * j) = o;
+                  }
+                }
+              }
+            }
+          }
+        }
+        if (p.nchunks > 1) tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(acce0 + 8 * a);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long long lda,
+                       long long ldb, cudaStream_t stream) {
+  GemmParams p = p0;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (!A_MN) rc = make_tmap_2d_sw128(&tmA, A, p.M, p.K, lda, BM, 64, 2);
+  else rc = make_tmap_2d_sw128(&tmA, A, p.K, p.M, lda, BK, 64, 2);
+  if (rc) return rc;
+  if (!B_MN) rc = make_tmap_2d_sw128(&tmB, B, p.N, p.K, ldb, BN, 64, 2);
+  else rc = make_tmap_2d_sw128(&tmB, B, p.K, p.N, ldb, BK, 64, 2);
+  if (rc) return rc;
+  p.m_tiles = (p.M + BM - 1) / BM;
+  p.n_tiles = (p.N + BN - 1) / BN;
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  auto kfn = det_gemm_kernel<BN, A_MN, B_MN>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  RLK_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev & 63]) {
+    RLK_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        GemmSmem<BN>::kBytes));
+    attr_set[dev & 63] = true;
+  }
+  kfn<<<grid, kGemmThreads, GemmSmem<BN>::kBytes, stream>>>(tmA, tmB, p);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+}  // namespace rlk
+
+// C[M,N] = A * B^T.
+//  a_mn = 0: A is [M,K] row-major (lda >= K);  a_mn = 1: A is stored [K,M] row-major (lda >= M).
+//  b_mn = 0: B is [N,K] row-major (ldb >= K);  b_mn = 1: B is stored [K,N] row-major (ldb >= N).
+//  nchunks: canonical K chunks (1,2,4,8); K/nchunks must be a multiple of 64 when nchunks > 1.
+//  tile_n: 0 = pick from the shape; else one of 32, 64, 128, 256 (chunked GEMMs use 128).
+//  out_fp32 / accumulate: C dtype and C += result.
+RLK_API int rlk_det_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
+                         long long ldb, long long ldc, int a_mn, int b_mn, int nchunks,
+                         int tile_n, int out_fp32, int accumulate, void* stream) {
+  using namespace rlk;
+  RLK_REQUIRE(M > 0 && N > 0 && K > 0, "det_gemm: empty shape");
+  RLK_REQUIRE(N % 8 == 0, "det_gemm: N must be a multiple of 8 (got %d)", N);
+  RLK_REQUIRE(K % 8 == 0, "det_gemm: K must be a multiple of 8 (got %d)", K);
+  RLK_REQUIRE(nchunks == 1 || nchunks == 2 || nchunks == 4 || nchunks == 8,
+              "det_gemm: nchunks must be 1, 2, 4 or 8");
+  RLK_REQUIRE(nchunks == 1 || (K % (nchunks * 64) == 0),
+              "det_gemm: K/nchunks must be a multiple of 64 (K=%d, nchunks=%d)", K, nchunks);
+  RLK_REQUIRE((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * (out_fp32 ? 4 : 2)) % 16 == 0,
+              "det_gemm: C must be 16-byte aligned with a 16-byte multiple pitch");
+  if (a_mn) RLK_REQUIRE(M % 8 == 0, "det_gemm: MN-major A needs M %% 8 == 0");
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.nchunks = nchunks;
+  p.kb_per_chunk = nchunks == 1 ? (K + 63) / 64 : K / nchunks / 64;
+  p.C = C; p.ldc = ldc; p.out_fp32 = out_fp32; p.accumulate = accumulate;
+  p.status = device_status_word();
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int bn = tile_n;
+  if (nchunks > 1) bn = 128;
+  if (bn == 0) {
+    const int m_tiles = (M + 127) / 128;
+    const int sms = sm_count();
+    bn = 256;
+    while (bn > 32 && (long long)m_tiles * ((N + bn - 1) / bn) < sms) bn >>= 1;
+    if (b_mn || a_mn) bn = bn < 128 ? 128 : bn;
+  }
+  if (nchunks > 1) RLK_REQUIRE(bn == 128, "det_gemm: chunked GEMM uses tile_n 128");
+#define RLK_GEMM_CASE(BN_, AM_, BM_)                                       \
+  if (bn == BN_ && a_mn == AM_ && b_mn == BM_)                             \
+    return launch_gemm<BN_, (AM_ != 0), (BM_ != 0)>(A, B, p, lda, ldb, s);
+  RLK_GEMM_CASE(256, 0, 0)
+  RLK_GEMM_CASE(128, 0, 0)
+  RLK_GEMM_CASE(64, 0, 0)
+  RLK_GEMM_CASE(32, 0, 0)
+  RLK_GEMM_CASE(256, 0, 1)
+  RLK_GEMM_CASE(128, 0, 1)
+  RLK_GEMM_CASE(256, 1, 1)
+  RLK_GEMM_CASE(128, 1, 1)
+  RLK_GEMM_CASE(256, 1, 0)
+  RLK_GEMM_CASE(128, 1, 0)
+#undef RLK_GEMM_CASE
+  return set_error(RLK_ERR_UNSUPPORTED, "det_gemm: no kernel for tile_n=%d a_mn=%d b_mn=%d", bn,
+                   a_mn, b_mn);
+}
