@@ -1,0 +1,367 @@
+// Deterministic causal GQA attention forward for sm_100a (head_dim 128, bf16).
+//
+// One CTA per work tile (see rlk/attn_common.cuh): 128 query rows x one KV head's keys.
+//   warp 0   : TMA producer  (Q once, then K and V blocks through 2-stage rings)
+//   warp 1   : UMMA issuer   (S = Q K^T into TMEM, O_blk = P V into TMEM)
+//   warps 2-5: softmax + accumulation, one thread per query row (no cross-thread reductions,
+//              so a row's arithmetic cannot depend on what else is in the tile)
+// Keys are consumed in canonical 128-key blocks in ascending order with an online softmax;
+// no split-KV, no atomics.  P is rounded to bf16 before P V (as every flash kernel does); the
+// row sum uses the unrounded fp32 probabilities, added in a fixed order.
+//
+// With NSRC > 1 the K/V blocks of a tile live on several GPUs (context parallel): block b is
+// read straight from its owner's memory with a plain (non-multicast) TMA load through that
+// peer's tensor map, so the KV exchange happens inside the kernel and the per-row arithmetic
+// is identical to the single-GPU run.
+//
+// Replaces the external FA4 call (rl_engine/backends/cuda/attention/flash_attn.py:343-353), the
+// materialising kernels in csrc/cuda/attention/deterministic_attention.cu and the AG -> full
+// attention -> scatter scheme of rl_engine/backends/cuda/attention/cp_comm.py:444-566.
+#include "rlk/attn_common.cuh"
+#include "rlk/host.h"
+#include "rlk/ptx.cuh"
+
+namespace rlk {
+
+constexpr int kAttnThreads = 192;
+constexpr int kTileBytes = 128 * 128 * 2;  // one 128x128 bf16 operand tile (two 64-wide boxes)
+constexpr int kHalfBytes = 128 * 64 * 2;
+
+template <int NSRC>
+struct KvMaps {
+  CUtensorMap k[NSRC];
+  CUtensorMap v[NSRC];
+};
+
+struct AttnFwdParams {
+  const AttnTile* tiles;
+  int n_tiles;
+  __nv_bfloat16* O;
+  long long ldo;      // elements between consecutive rows of O
+  float* lse;         // may be null
+  float scale_log2;   // softmax scale * log2(e)
+  float scale;        // softmax scale
+  int cp_blocks_per_chunk;  // NSRC > 1: 128-key blocks per contiguous chunk of the sequence
+  int cp_ranks;             // NSRC > 1: number of ranks holding the sequence
+  int cp_zigzag;            // NSRC > 1: 1 = rank c holds chunks c and 2*cp-1-c; 0 = chunk c on rank c
+  int* status;
+};
+
+struct AttnFwdSmem {
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQ + kTileBytes;
+  static constexpr int kV = kK + 2 * kTileBytes;
+  static constexpr int kP = kV + 2 * kTileBytes;
+  static constexpr int kBars = kP + kTileBytes;
+  static constexpr int kBytes = kBars + 256 + 1024;
+};
+
+// Which tensor map and which local row holds canonical block b of a sequence.
+__device__ __forceinline__ void cp_locate(const AttnFwdParams& p, const AttnTile& t, int b,
+                                          int& src, int& row) {
+  if (p.cp_ranks <= 1) {
+    src = t.kv_src;
+    row = t.kv_row0 + b * kAttnBlock;
+    return;
+  }
+  const int chunk = b / p.cp_blocks_per_chunk;
+  const int within = b - chunk * p.cp_blocks_per_chunk;
+  int local_chunk = 0;
+  if (p.cp_zigzag) {
+    if (chunk < p.cp_ranks) { src = chunk; local_chunk = 0; }
+    else { src = 2 * p.cp_ranks - 1 - chunk; local_chunk = 1; }
+  } else {
+    src = chunk;
+  }
+  row = t.kv_row0 + (local_chunk * p.cp_blocks_per_chunk + within) * kAttnBlock;
+}
+
+template <int NSRC>
+__global__ void __launch_bounds__(kAttnThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ KvMaps<NSRC> kv,
+                const AttnFwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttnFwdSmem::kBars);
+  // barrier indices
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11,
+         P_FULL = 13, O_FULL = 14, NBARS = 15 };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar0 = smem_u32(bars);
+  auto BAR = [&](int i) { return bar0 + 8u * i; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const AttnTile t = p.tiles[blockIdx.x];
+  if (t.n_rows <= 0) return;
+  int max_kv = t.pos0 + (t.n_rows - 1) * t.pos_step + 1;
+  if (max_kv > t.kv_cap) max_kv = t.kv_cap;
+  const int nblk = (max_kv + kAttnBlock - 1) / kAttnBlock;
+
+  if (threadIdx.x == 0) {
+    mbar_init(BAR(Q_FULL), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(BAR(K_FULL + s), 1);
+      mbar_init(BAR(K_EMPTY + s), 1);
+      mbar_init(BAR(V_FULL + s), 1);
+      mbar_init(BAR(V_EMPTY + s), 1);
+      mbar_init(BAR(S_FULL + s), 1);
+      mbar_init(BAR(S_EMPTY + s), 128);
+    }
+    mbar_init(BAR(P_FULL), 128);
+    mbar_init(BAR(O_FULL), 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t sQ = smem_u32(smem + AttnFwdSmem::kQ);
+  const uint32_t sK = smem_u32(smem + AttnFwdSmem::kK);
+  const uint32_t sV = smem_u32(smem + AttnFwdSmem::kV);
+  const uint32_t sP = smem_u32(smem + AttnFwdSmem::kP);
+  constexpr uint32_t TM_S = 0;     // two S buffers: columns [0,128) and [128,256)
+  constexpr uint32_t TM_O = 256;   // O_blk: columns [256,384)
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(BAR(Q_FULL), kTileBytes);
+      tma_load_2d(sQ, &tmQ, t.q_col0, t.q_row0, BAR(Q_FULL));
+      tma_load_2d(sQ + kHalfBytes, &tmQ, t.q_col0 + 64, t.q_row0, BAR(Q_FULL));
+      for (int b = 0; b < nblk; ++b) {
+        const int s = b & 1;
+        const uint32_t ph = (b >> 1) & 1;
+        int src, row;
+        cp_locate(p, t, b, src, row);
+        if (NSRC == 1) src = 0;
+        if (!mbar_wait(BAR(K_EMPTY + s), ph ^ 1, abort_flag, p.status, 201)) break;
+        mbar_expect_tx(BAR(K_FULL + s), kTileBytes);
+        tma_load_2d(sK + s * kTileBytes, &kv.k[src], t.kv_col0, row, BAR(K_FULL + s));
+        tma_load_2d(sK + s * kTileBytes + kHalfBytes, &kv.k[src], t.kv_col0 + 64, row, BAR(K_FULL + s));
+        if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1, abort_flag, p.status, 202)) break;
+        mbar_expect_tx(BAR(V_FULL + s), kTileBytes);
+        tma_load_2d(sV + s * kTileBytes, &kv.v[src], t.kv_col0, row, BAR(V_FULL + s));
+        tma_load_2d(sV + s * kTileBytes + kHalfBytes, &kv.v[src], t.kv_col0 + 64, row, BAR(V_FULL + s));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);  // Q (K-major) x K (K-major)
+      constexpr uint32_t idesc_o = umma_idesc_bf16(128, 128, 0, 1);  // P (K-major) x V (MN-major)
+      auto issue_s = [&](int b) -> bool {
+        const int s = b & 1;
+        const uint32_t ph = (b >> 1) & 1;
+        if (!mbar_wait(BAR(K_FULL + s), ph, abort_flag, p.status, 203)) return false;
+        if (!mbar_wait(BAR(S_EMPTY + s), ph ^ 1, abort_flag, p.status, 204)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_bf16_ss(tmem_base + TM_S + s * 128, umma_desc_sw128(sQ + off, 16, 1024),
+                       umma_desc_sw128(sK + s * kTileBytes + off, 16, 1024), idesc_s, k != 0);
+        }
+        umma_commit(BAR(S_FULL + s));
+        umma_commit(BAR(K_EMPTY + s));
+        return true;
+      };
+      bool ok = mbar_wait(BAR(Q_FULL), 0, abort_flag, p.status, 205);
+      if (ok && nblk > 0) ok = issue_s(0);
+      for (int b = 0; ok && b < nblk; ++b) {
+        if (b + 1 < nblk) ok = issue_s(b + 1);
+        if (!ok) break;
+        const int s = b & 1;
+        const uint32_t ph = (b >> 1) & 1;
+        if (!mbar_wait(BAR(V_FULL + s), ph, abort_flag, p.status, 206)) break;
+        if (!mbar_wait(BAR(P_FULL), b & 1, abort_flag, p.status, 207)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t aoff = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_bf16_ss(tmem_base + TM_O, umma_desc_sw128(sP + aoff, 16, 1024),
+                       umma_desc_sw128(sV + s * kTileBytes + k * 2048, kHalfBytes, 1024), idesc_o,
+                       k != 0);
+        }
+        umma_commit(BAR(O_FULL));
+        umma_commit(BAR(V_EMPTY + s));
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax / accumulate
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;  // this thread's query row within the tile
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    int kv_len = t.pos0 + r * t.pos_step + 1;
+    if (kv_len > t.kv_cap) kv_len = t.kv_cap;
+    if (r >= t.n_rows) kv_len = 0;
+    float m_run = -INFINITY, l_run = 0.f;
+    float o[128];
+#pragma unroll
+    for (int i = 0; i < 128; ++i) o[i] = 0.f;
+    uint8_t* p_row = smem + AttnFwdSmem::kP;
+
+    for (int b = 0; b < nblk; ++b) {
+      const int s = b & 1;
+      const uint32_t ph = (b >> 1) & 1;
+      if (!mbar_wait(BAR(S_FULL + s), ph, abort_flag, p.status, 208)) break;
+      tc_fence_after();
+      const int k0 = b * kAttnBlock;
+      const int nvis = kv_len - k0;  // visible keys of this block for this row (may be <= 0)
+      // pass 1: block max
+      float m_blk = -INFINITY;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t x[32];
+        tmem_ld32(tmem_base + lane_off + TM_S + s * 128 + c * 32, x);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (c * 32 + j < nvis) m_blk = fmaxf(m_blk, __uint_as_float(x[j]));
+      }
+      const float m_new = fmaxf(m_run, m_blk);
+      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+      const float alpha = exp2f((m_run - m_use) * p.scale_log2);  // m_run=-inf -> 0
+      const float neg_ms = -m_use * p.scale_log2;
+      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+      // pass 2: probabilities -> bf16 P tile in shared memory (K-major, 128B swizzle)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t x[32];
+        tmem_ld32(tmem_base + lane_off + TM_S + s * 128 + c * 32, x);
+        tmem_ld_wait();
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          float e0 = (c * 32 + j + 0 < nvis) ? exp2f(fmaf(__uint_as_float(x[j + 0]), p.scale_log2, neg_ms)) : 0.f;
+          float e1 = (c * 32 + j + 1 < nvis) ? exp2f(fmaf(__uint_as_float(x[j + 1]), p.scale_log2, neg_ms)) : 0.f;
+          float e2 = (c * 32 + j + 2 < nvis) ? exp2f(fmaf(__uint_as_float(x[j + 2]), p.scale_log2, neg_ms)) : 0.f;
+          float e3 = (c * 32 + j + 3 < nvis) ? exp2f(fmaf(__uint_as_float(x[j + 3]), p.scale_log2, neg_ms)) : 0.f;
+          sum0 += e0; sum1 += e1; sum2 += e2; sum3 += e3;
+          pk[j / 2] = pack_bf16x2(e0, e1);
+          pk[j / 2 + 1] = pack_bf16x2(e2, e3);
+        }
+        // 32 keys = 4 chunks of 16 bytes; keys [64h, 64h+64) live in half h of the P tile
+        const int half = c >> 1;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+          const uint32_t chunk16 = (c & 1) * 4 + q4;
+          *reinterpret_cast<uint4*>(p_row + half * kHalfBytes + sw128_offset(r, chunk16)) =
+              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+        }
+      }
+      fence_proxy_async_smem();  // make the generic-proxy P writes visible to the UMMA
+      tc_fence_before();
+      mbar_arrive(BAR(S_EMPTY + s));
+      mbar_arrive(BAR(P_FULL));
+      l_run = l_run * alpha + ((sum0 + sum1) + (sum2 + sum3));
+      m_run = m_new;
+      if (!mbar_wait(BAR(O_FULL), b & 1, abort_flag, p.status, 209)) break;
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t x[32];
+        tmem_ld32(tmem_base + lane_off + TM_O + c * 32, x);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[c * 32 + j] = fmaf(o[c * 32 + j], alpha, __uint_as_float(x[j]));
+      }
+    }
+    // ---------------------------------------------------------------- epilogue
+    if (r < t.n_rows && !*abort_flag) {
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* dst = p.O + static_cast<long long>(t.q_row0 + r) * p.ldo + t.q_col0;
+#pragma unroll
+      for (int j = 0; j < 128; j += 8) {
+        uint4 v;
+        v.x = pack_bf16x2(o[j] * inv_l, o[j + 1] * inv_l);
+        v.y = pack_bf16x2(o[j + 2] * inv_l, o[j + 3] * inv_l);
+        v.z = pack_bf16x2(o[j + 4] * inv_l, o[j + 5] * inv_l);
+        v.w = pack_bf16x2(o[j + 6] * inv_l, o[j + 7] * inv_l);
+        *reinterpret_cast<uint4*>(dst + j) = v;
+      }
+      if (p.lse) {
+        const float lse = (l_run > 0.f) ? fmaf(m_run, p.scale, logf(l_run)) : -INFINITY;
+        p.lse[t.lse_off + static_cast<long long>(r) * t.lse_stride] = lse;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int NSRC>
+static int launch_attn_fwd(const CUtensorMap& tmQ, const KvMaps<NSRC>& kv, const AttnFwdParams& p,
+                           cudaStream_t stream) {
+  auto kfn = attn_fwd_kernel<NSRC>;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  RLK_CHECK_CUDA(cudaGetDevice(&dev));
+  if (!attr_set[dev & 63]) {
+    RLK_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        AttnFwdSmem::kBytes));
+    attr_set[dev & 63] = true;
+  }
+  kfn<<<p.n_tiles, kAttnThreads, AttnFwdSmem::kBytes, stream>>>(tmQ, kv, p);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+}  // namespace rlk
+
+// Q: [q_rows, q_cols] bf16 row-major with pitch ldq; K and V: [kv_rows, kv_cols] with pitch ldkv.
+// `tiles` is a device array of n_tiles rlk::AttnTile.  O has Q's geometry with pitch ldo.
+// n_src == 1: k_ptrs/v_ptrs hold one pointer each.  n_src in 2..8 (context parallel): pointer s
+// is rank s's K / V buffer (same shape and pitch on every rank), mapped into this process.
+RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long long ldq,
+                         const void* const* k_ptrs, const void* const* v_ptrs, int n_src,
+                         long long kv_rows, long long kv_cols, long long ldkv, void* O,
+                         long long ldo, float* lse, const void* tiles, int n_tiles, float scale,
+                         int cp_blocks_per_chunk, int cp_zigzag, void* stream) {
+  using namespace rlk;
+  RLK_REQUIRE(n_tiles > 0, "attn_fwd: no tiles");
+  RLK_REQUIRE(n_src == 1 || (n_src >= 2 && n_src <= 8), "attn_fwd: n_src must be 1..8");
+  RLK_REQUIRE(q_cols % 128 == 0 && kv_cols % 128 == 0, "attn_fwd: head_dim must be 128");
+  RLK_REQUIRE((reinterpret_cast<uintptr_t>(O) & 15) == 0 && (ldo * 2) % 16 == 0,
+              "attn_fwd: O must be 16-byte aligned");
+  AttnFwdParams p{};
+  p.tiles = static_cast<const AttnTile*>(tiles);
+  p.n_tiles = n_tiles;
+  p.O = static_cast<__nv_bfloat16*>(O);
+  p.ldo = ldo;
+  p.lse = lse;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.cp_blocks_per_chunk = cp_blocks_per_chunk;
+  p.cp_ranks = n_src > 1 ? n_src : 1;
+  p.cp_zigzag = cp_zigzag;
+  p.status = device_status_word();
+  CUtensorMap tmQ;
+  int rc = make_tmap_2d_sw128(&tmQ, Q, q_rows, q_cols, ldq, 128, 64, 2);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (n_src == 1) {
+    KvMaps<1> kv;
+    if ((rc = make_tmap_2d_sw128(&kv.k[0], k_ptrs[0], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
+    if ((rc = make_tmap_2d_sw128(&kv.v[0], v_ptrs[0], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
+    return launch_attn_fwd<1>(tmQ, kv, p, s);
+  }
+  KvMaps<8> kv;
+  for (int i = 0; i < 8; ++i) {
+    const int j = i < n_src ? i : 0;
+    if ((rc = make_tmap_2d_sw128(&kv.k[i], k_ptrs[j], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
+    if ((rc = make_tmap_2d_sw128(&kv.v[i], v_ptrs[j], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
+  }
+  return launch_attn_fwd<8>(tmQ, kv, p, s);
+}
