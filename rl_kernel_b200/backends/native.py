@@ -1,0 +1,312 @@
+"""Typed Python entry points for every ``rlk_*`` function of librlk_b200.so.
+
+Each wrapper validates dtypes / contiguity that the C side cannot see, passes raw device
+pointers and the current CUDA stream, and raises on a non-zero return code.  No wrapper falls
+back to PyTorch: on a machine with a GPU a missing library is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_uint, c_ulonglong, c_void_p
+
+import torch
+
+from rl_kernel_b200.backends import extension as ext
+
+_ll = c_longlong
+LAUNCH_COUNT = 0  # number of native kernel-launching calls made by this process
+
+
+def _lib():
+    return ext.load()
+
+
+def _count(n: int = 1) -> None:
+    global LAUNCH_COUNT
+    LAUNCH_COUNT += n
+
+
+def _bf16(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != torch.bfloat16 or not t.is_cuda:
+        raise TypeError(f"{name} must be a CUDA bf16 tensor, got {t.dtype} on {t.device}")
+    return t
+
+
+def _rowmajor2d(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise ValueError(f"{name} must be 2-D with unit inner stride, got shape {tuple(t.shape)} "
+                         f"stride {t.stride()}")
+    return t
+
+
+# ------------------------------------------------------------------------------------- GEMM
+def det_gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int, K: int,
+             a_mn: bool = False, b_mn: bool = False, nchunks: int = 1, tile_n: int = 0,
+             accumulate: bool = False) -> torch.Tensor:
+    """out[M,N] (+)= A[M,K] @ B[N,K]^T; see csrc/gemm/det_gemm_sm100.cu for the contract."""
+    _bf16(a, "a"); _bf16(b, "b")
+    _rowmajor2d(a, "a"); _rowmajor2d(b, "b"); _rowmajor2d(out, "out")
+    out_fp32 = 1 if out.dtype == torch.float32 else 0
+    if not out_fp32:
+        _bf16(out, "out")
+    rc = _lib().rlk_det_gemm(ext.ptr(a), ext.ptr(b), ext.ptr(out), c_int(M), c_int(N), c_int(K),
+                             _ll(a.stride(0)), _ll(b.stride(0)), _ll(out.stride(0)),
+                             c_int(int(a_mn)), c_int(int(b_mn)), c_int(nchunks), c_int(tile_n),
+                             c_int(out_fp32), c_int(int(accumulate)), ext.stream_ptr(a.device))
+    ext.check(rc, "det_gemm")
+    _count()
+    return out
+
+
+def lmhead_logp_stats(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor | None,
+                      stats: torch.Tensor, tgt_logit: torch.Tensor, *, vocab_start: int,
+                      inv_temp: float, logits_out: torch.Tensor | None = None) -> None:
+    _bf16(h, "h"); _bf16(w, "w"); _rowmajor2d(h, "h"); _rowmajor2d(w, "w")
+    M, K = h.shape
+    N = w.shape[0]
+    assert stats.dtype == torch.float32 and stats.dim() == 3 and stats.shape[2] == 2 and stats.is_contiguous()
+    rc = _lib().rlk_lmhead_logp_stats(ext.ptr(h), ext.ptr(w), c_int(M), c_int(N), c_int(K),
+                                      _ll(h.stride(0)), _ll(w.stride(0)), ext.ptr(targets),
+                                      _ll(vocab_start), c_float(inv_temp), ext.ptr(stats),
+                                      _ll(stats.shape[1]), ext.ptr(tgt_logit), ext.ptr(logits_out),
+                                      _ll(logits_out.stride(0) if logits_out is not None else 0),
+                                      ext.stream_ptr(h.device))
+    ext.check(rc, "lmhead_logp_stats")
+    _count()
+
+
+# ------------------------------------------------------------------------------------- attention
+def attn_fwd(q2d: torch.Tensor, k_list: list[torch.Tensor], v_list: list[torch.Tensor],
+             o2d: torch.Tensor, lse: torch.Tensor | None, tiles: torch.Tensor, scale: float, *,
+             cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False) -> None:
+    """q2d/o2d: [rows, Hq*128]; k/v: [rows, Hkv*128] (one tensor per source rank)."""
+    _bf16(q2d, "q"); _rowmajor2d(q2d, "q"); _rowmajor2d(o2d, "o")
+    n_src = len(k_list)
+    k0 = k_list[0]
+    _rowmajor2d(k0, "k")
+    kp = (c_void_p * n_src)(*[t.data_ptr() for t in k_list])
+    vp = (c_void_p * n_src)(*[t.data_ptr() for t in v_list])
+    assert tiles.dtype == torch.int32 and tiles.is_contiguous() and tiles.shape[1] == 12
+    rc = _lib().rlk_attn_fwd(ext.ptr(q2d), _ll(q2d.shape[0]), _ll(q2d.shape[1]), _ll(q2d.stride(0)),
+                             kp, vp, c_int(n_src), _ll(k0.shape[0]), _ll(k0.shape[1]),
+                             _ll(k0.stride(0)), ext.ptr(o2d), _ll(o2d.stride(0)), ext.ptr(lse),
+                             ext.ptr(tiles), c_int(tiles.shape[0]), c_float(scale),
+                             c_int(cp_blocks_per_chunk), c_int(int(cp_zigzag)),
+                             ext.stream_ptr(q2d.device))
+    ext.check(rc, "attn_fwd")
+    _count()
+
+
+def attn_bwd_delta(o2d: torch.Tensor, do2d: torch.Tensor, delta: torch.Tensor, T: int, Hq: int) -> None:
+    rc = _lib().rlk_attn_bwd_delta(ext.ptr(o2d), _ll(o2d.stride(0)), ext.ptr(do2d),
+                                   _ll(do2d.stride(0)), ext.ptr(delta), c_int(T), c_int(Hq),
+                                   ext.stream_ptr(o2d.device))
+    ext.check(rc, "attn_bwd_delta")
+    _count()
+
+
+def attn_bwd_dq(q2d, do2d, k2d, v2d, lse, delta, dq2d, tiles, scale: float) -> None:
+    rc = _lib().rlk_attn_bwd_dq(ext.ptr(q2d), ext.ptr(do2d), _ll(q2d.shape[0]), _ll(q2d.shape[1]),
+                                _ll(q2d.stride(0)), _ll(do2d.stride(0)), ext.ptr(k2d), ext.ptr(v2d),
+                                _ll(k2d.shape[0]), _ll(k2d.shape[1]), _ll(k2d.stride(0)),
+                                ext.ptr(lse), ext.ptr(delta), ext.ptr(dq2d), _ll(dq2d.stride(0)),
+                                ext.ptr(tiles), c_int(tiles.shape[0]), c_float(scale),
+                                ext.stream_ptr(q2d.device))
+    ext.check(rc, "attn_bwd_dq")
+    _count()
+
+
+def attn_bwd_dkv(q2d, do2d, k2d, v2d, lse, delta, dk2d, dv2d, kv_tiles, scale: float) -> None:
+    assert dk2d.stride(0) == dv2d.stride(0)
+    rc = _lib().rlk_attn_bwd_dkv(ext.ptr(q2d), ext.ptr(do2d), _ll(q2d.shape[0]), _ll(q2d.shape[1]),
+                                 _ll(q2d.stride(0)), _ll(do2d.stride(0)), ext.ptr(k2d), ext.ptr(v2d),
+                                 _ll(k2d.shape[0]), _ll(k2d.shape[1]), _ll(k2d.stride(0)),
+                                 ext.ptr(lse), ext.ptr(delta), ext.ptr(dk2d), ext.ptr(dv2d),
+                                 _ll(dk2d.stride(0)), ext.ptr(kv_tiles), c_int(kv_tiles.shape[0]),
+                                 c_float(scale), ext.stream_ptr(q2d.device))
+    ext.check(rc, "attn_bwd_dkv")
+    _count()
+
+
+# ------------------------------------------------------------------------------------- norm / rope
+def rmsnorm_fwd(x, w, y, eps: float, *, res=None, res_out=None, rstd_out=None) -> None:
+    rows, H = x.shape
+    rc = _lib().rlk_rmsnorm_fwd(ext.ptr(x), ext.ptr(res), ext.ptr(w), ext.ptr(y), ext.ptr(res_out),
+                                ext.ptr(rstd_out), c_int(rows), c_int(H), c_float(eps),
+                                ext.stream_ptr(x.device))
+    ext.check(rc, "rmsnorm_fwd")
+    _count()
+
+
+def rmsnorm_bwd_scratch_elems(rows: int, H: int) -> int:
+    fn = _lib().rlk_rmsnorm_bwd_scratch_elems
+    fn.restype = c_longlong
+    return int(fn(c_int(rows), c_int(H)))
+
+
+def rmsnorm_bwd(x, w, dy, dx, scratch, eps: float, *, dres=None, dw_bf16=None, dw_f32=None,
+                accumulate_dw: bool = False) -> None:
+    rows, H = x.shape
+    rc = _lib().rlk_rmsnorm_bwd(ext.ptr(x), ext.ptr(w), ext.ptr(dy), ext.ptr(dres), ext.ptr(dx),
+                                ext.ptr(scratch), ext.ptr(dw_bf16), ext.ptr(dw_f32),
+                                c_int(int(accumulate_dw)), c_int(rows), c_int(H), c_float(eps),
+                                ext.stream_ptr(x.device))
+    ext.check(rc, "rmsnorm_bwd")
+    _count(2)
+
+
+def qk_norm_rope_fwd(qkv, q_w, k_w, cos_tab, sin_tab, pos, q_out, k_out, v_out, *, Hq: int, Hkv: int,
+                     eps: float, kv_slot=None) -> None:
+    T = qkv.shape[0]
+    assert pos.dtype == torch.int32 and cos_tab.dtype == torch.float32
+    rc = _lib().rlk_qk_norm_rope_fwd(ext.ptr(qkv), _ll(qkv.stride(0)), ext.ptr(q_w), ext.ptr(k_w),
+                                     ext.ptr(cos_tab), ext.ptr(sin_tab), ext.ptr(pos), ext.ptr(kv_slot),
+                                     ext.ptr(q_out), _ll(q_out.stride(0)), ext.ptr(k_out),
+                                     ext.ptr(v_out), _ll(k_out.stride(0)), c_int(T), c_int(Hq),
+                                     c_int(Hkv), c_float(eps), c_void_p(0), c_void_p(0),
+                                     ext.stream_ptr(qkv.device))
+    ext.check(rc, "qk_norm_rope_fwd")
+    _count()
+
+
+def qk_norm_rope_bwd_scratch_elems(T: int) -> int:
+    fn = _lib().rlk_qk_norm_rope_bwd_scratch_elems
+    fn.restype = c_longlong
+    return int(fn(c_int(T)))
+
+
+def qk_norm_rope_bwd(qkv, q_w, k_w, cos_tab, sin_tab, pos, dq, dk, dv, dqkv, scratch, dqw, dkw, *,
+                     Hq: int, Hkv: int, eps: float, accumulate_dw: bool) -> None:
+    T = qkv.shape[0]
+    rc = _lib().rlk_qk_norm_rope_bwd(ext.ptr(qkv), _ll(qkv.stride(0)), ext.ptr(q_w), ext.ptr(k_w),
+                                     ext.ptr(cos_tab), ext.ptr(sin_tab), ext.ptr(pos), ext.ptr(dq),
+                                     _ll(dq.stride(0)), ext.ptr(dk), ext.ptr(dv), _ll(dk.stride(0)),
+                                     ext.ptr(dqkv), _ll(dqkv.stride(0)), ext.ptr(scratch),
+                                     ext.ptr(dqw), ext.ptr(dkw), c_int(int(accumulate_dw)), c_int(T),
+                                     c_int(Hq), c_int(Hkv), c_float(eps), ext.stream_ptr(qkv.device))
+    ext.check(rc, "qk_norm_rope_bwd")
+    _count(4)
+
+
+# ------------------------------------------------------------------------------------- activation
+def swiglu_fwd(gu, out, I: int) -> None:
+    rc = _lib().rlk_swiglu_fwd(ext.ptr(gu), _ll(gu.stride(0)), ext.ptr(out), _ll(out.stride(0)),
+                               c_int(gu.shape[0]), c_int(I), ext.stream_ptr(gu.device))
+    ext.check(rc, "swiglu_fwd")
+    _count()
+
+
+def swiglu_bwd(gu, dout, dgu, I: int) -> None:
+    rc = _lib().rlk_swiglu_bwd(ext.ptr(gu), _ll(gu.stride(0)), ext.ptr(dout), _ll(dout.stride(0)),
+                               ext.ptr(dgu), _ll(dgu.stride(0)), c_int(gu.shape[0]), c_int(I),
+                               ext.stream_ptr(gu.device))
+    ext.check(rc, "swiglu_bwd")
+    _count()
+
+
+# ------------------------------------------------------------------------------------- embedding
+def embedding_fwd(ids, w, out, vocab_start: int = 0) -> None:
+    assert ids.dtype == torch.int64
+    rc = _lib().rlk_embedding_fwd(ext.ptr(ids), ext.ptr(w), ext.ptr(out), c_int(ids.numel()),
+                                  c_int(w.shape[1]), _ll(vocab_start), _ll(w.shape[0]),
+                                  ext.stream_ptr(w.device))
+    ext.check(rc, "embedding_fwd")
+    _count()
+
+
+def embedding_bwd(sorted_ids, order, dy, dw, vocab_start: int = 0) -> None:
+    rc = _lib().rlk_embedding_bwd(ext.ptr(sorted_ids), ext.ptr(order), ext.ptr(dy), ext.ptr(dw),
+                                  c_int(sorted_ids.numel()), c_int(dw.shape[1]), _ll(vocab_start),
+                                  _ll(dw.shape[0]), ext.stream_ptr(dw.device))
+    ext.check(rc, "embedding_bwd")
+    _count()
+
+
+# ------------------------------------------------------------------------------------- logp
+def logits_tile_stats(logits, targets, stats, tgt_logit, *, vocab_start: int, inv_temp: float) -> None:
+    rows, n_local = logits.shape
+    rc = _lib().rlk_logits_tile_stats(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(targets),
+                                      ext.ptr(stats), _ll(stats.shape[1]), ext.ptr(tgt_logit),
+                                      c_int(rows), c_int(n_local), _ll(vocab_start), c_float(inv_temp),
+                                      ext.stream_ptr(logits.device))
+    ext.check(rc, "logits_tile_stats")
+    _count()
+
+
+def logp_merge(stats, tgt_logit, logp, lse) -> None:
+    rows, n_tiles = stats.shape[0], stats.shape[1]
+    rc = _lib().rlk_logp_merge(ext.ptr(stats), _ll(n_tiles), c_int(n_tiles), ext.ptr(tgt_logit),
+                               ext.ptr(logp), ext.ptr(lse), c_int(rows), ext.stream_ptr(stats.device))
+    ext.check(rc, "logp_merge")
+    _count()
+
+
+def dlogits_(logits, targets, lse, g, *, vocab_start: int, inv_temp: float) -> None:
+    rows, n_local = logits.shape
+    rc = _lib().rlk_dlogits(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(targets), ext.ptr(lse),
+                            ext.ptr(g), c_int(rows), c_int(n_local), _ll(vocab_start),
+                            c_float(inv_temp), ext.stream_ptr(logits.device))
+    ext.check(rc, "dlogits")
+    _count()
+
+
+# ------------------------------------------------------------------------------------- loss
+def grpo_loss(logp, old_logp, ref_logp, adv, mask_u8, *, clip_lo: float, clip_hi: float, beta: float,
+              inv_norm: float, want_tokens: bool = True):
+    B, L = logp.shape
+    dev = logp.device
+    dlogp = torch.empty_like(logp)
+    loss_tok = torch.empty_like(logp) if want_tokens else None
+    kl_tok = torch.empty_like(logp) if want_tokens else None
+    ratio_tok = torch.empty_like(logp) if want_tokens else None
+    seq_sums = torch.empty(B, 4, device=dev, dtype=torch.float32)
+    totals = torch.empty(8, device=dev, dtype=torch.float32)
+    rc = _lib().rlk_grpo_loss(ext.ptr(logp), ext.ptr(old_logp), ext.ptr(ref_logp), ext.ptr(adv),
+                              ext.ptr(mask_u8), ext.ptr(loss_tok), ext.ptr(kl_tok), ext.ptr(ratio_tok),
+                              ext.ptr(dlogp), ext.ptr(seq_sums), ext.ptr(totals), c_int(B), c_int(L),
+                              c_float(clip_lo), c_float(clip_hi), c_float(beta), c_float(inv_norm),
+                              ext.stream_ptr(dev))
+    ext.check(rc, "grpo_loss")
+    _count(2)
+    return dict(dlogp=dlogp, loss_tok=loss_tok, kl_tok=kl_tok, ratio_tok=ratio_tok,
+                seq_sums=seq_sums, totals=totals)
+
+
+def group_advantages(rewards, groups: int, n: int, eps: float):
+    adv = torch.empty_like(rewards)
+    rc = _lib().rlk_group_advantages(ext.ptr(rewards), ext.ptr(adv), c_int(groups), c_int(n),
+                                     c_float(eps), ext.stream_ptr(rewards.device))
+    ext.check(rc, "group_advantages")
+    _count()
+    return adv
+
+
+# ------------------------------------------------------------------------------------- sampling
+def sample_gumbel(logits, out_ids, out_val, *, vocab_start: int, inv_temp: float, seed: int, step: int,
+                  greedy: bool = False, min_keep=None, row_keys=None) -> None:
+    rows, n_local = logits.shape
+    rc = _lib().rlk_sample_gumbel(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(min_keep),
+                                  ext.ptr(row_keys), ext.ptr(out_ids), ext.ptr(out_val), c_int(rows),
+                                  c_int(n_local), _ll(vocab_start), c_float(inv_temp),
+                                  c_ulonglong(seed), c_uint(step), c_int(int(greedy)),
+                                  ext.stream_ptr(logits.device))
+    ext.check(rc, "sample_gumbel")
+    _count()
+
+
+# ------------------------------------------------------------------------------------- optimizer
+def adamw(master, m, v, grad, param, *, lr: float, beta1: float, beta2: float, eps: float,
+          weight_decay: float, step: int, grad_scale=None) -> None:
+    rc = _lib().rlk_adamw(ext.ptr(master), ext.ptr(m), ext.ptr(v), ext.ptr(grad), ext.ptr(param),
+                          _ll(master.numel()), c_float(lr), c_float(beta1), c_float(beta2),
+                          c_float(eps), c_float(weight_decay), c_int(step), ext.ptr(grad_scale),
+                          ext.stream_ptr(master.device))
+    ext.check(rc, "adamw")
+    _count()
+
+
+def sumsq_bins(grad, bins) -> None:
+    assert bins.dtype == torch.int64 and bins.numel() == 256
+    rc = _lib().rlk_sumsq_bins(ext.ptr(grad), _ll(grad.numel()), ext.ptr(bins), ext.stream_ptr(grad.device))
+    ext.check(rc, "sumsq_bins")
+    _count()

@@ -17,6 +17,7 @@
 // Covers the reference's det_gemm_fwd / fwd_rhs_transposed / da / db entry points
 // (csrc/cuda/gemm/det_gemm_kernel.cu:527-602) with one kernel template.
 #include "rlk/host.h"
+#include "rlk/logp_contract.cuh"
 #include "rlk/ptx.cuh"
 
 namespace rlk {
@@ -36,6 +37,14 @@ struct GemmParams {
   int out_fp32;         // 1: C is fp32
   int accumulate;       // 1: C += result (read-modify-write in fp32, rounded to C's dtype)
   int* status;
+  // fused LM-head epilogue (tile_n == 128, nchunks == 1): per-(row, tile) softmax statistics
+  float2* stats;            // null = plain GEMM
+  long long stats_stride;   // float2 elements per row of `stats`
+  int stats_tile0;          // global tile index of this shard's first tile
+  const long long* targets; // [M] global target ids, may be null
+  long long vocab_start;    // global id of column 0
+  float* tgt_logit;         // [M]
+  float inv_temp;
 };
 
 template <int BN>
@@ -193,6 +202,57 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (!mbar_wait(accf0 + 8 * a, (u >> 1) & 1, abort_flag, p.status, 104)) break;
         tc_fence_after();
         const bool last = (c == p.nchunks - 1);
+        if (BN == 128 && p.stats != nullptr) {
+          // fused selected-logp statistics: logit = bf16(acc); z = logit * inv_temp
+          const long long tgt_col = (p.targets && row < p.M) ? p.targets[row] - p.vocab_start - n0 : -1;
+          float m = -INFINITY;
+#pragma unroll 1
+          for (int col0 = 0; col0 < BN; col0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + lane_off + a * BN + col0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + col0 + j < p.N)
+                m = fmaxf(m, logp_scale(round_bf16(__uint_as_float(r[j])), p.inv_temp));
+          }
+          TileSum ts;
+#pragma unroll 1
+          for (int col0 = 0; col0 < BN; col0 += 32) {
+            uint32_t r[32];
+            tmem_ld32(tmem_base + lane_off + a * BN + col0, r);
+            tmem_ld_wait();
+            float z[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              z[j] = (n0 + col0 + j < p.N) ? logp_scale(round_bf16(__uint_as_float(r[j])), p.inv_temp) : -INFINITY;
+            if (m > -INFINITY) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) ts.add4(z[j], z[j + 1], z[j + 2], z[j + 3], m);
+            }
+            if (tgt_col >= col0 && tgt_col < col0 + 32) {
+              float zt = 0.f;
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (tgt_col - col0 == j) zt = z[j];
+              if (n0 + tgt_col < p.N) p.tgt_logit[row] = zt;
+            }
+            if (p.C != nullptr && row < p.M) {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + n0 + col0;
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                if (n0 + col0 + j < p.N) {
+                  uint4 v;
+                  v.x = pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
+                  v.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                  v.z = pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]));
+                  v.w = pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+                  *reinterpret_cast<uint4*>(dst + j) = v;
+                }
+              }
+            }
+          }
+          if (row < p.M) p.stats[row * p.stats_stride + p.stats_tile0 + nt] = make_float2(m, ts.total());
+        } else
 #pragma unroll 1
         for (int col0 = 0; col0 < BN; col0 += 32) {
           uint32_t r[32];
@@ -393,4 +453,33 @@ RLK_API int rlk_det_gemm(const void* A, const void* B, void* C, int M, int N, in
 #undef RLK_GEMM_CASE
   return set_error(RLK_ERR_UNSUPPORTED, "det_gemm: no kernel for tile_n=%d a_mn=%d b_mn=%d", bn,
                    a_mn, b_mn);
+}
+
+// Fused vocab-(parallel) LM head: logits tile = H[M,K] * W[N,K]^T is reduced in the GEMM epilogue
+// to per-(row, 128-id tile) softmax statistics (see rlk/logp_contract.cuh) without writing the
+// [M,N] logits, unless `logits_out` is given.  W holds global vocab ids [vocab_start,
+// vocab_start+N); stats rows are float2[stats_stride] indexed by GLOBAL tile id.
+// Follow with rlk_logp_merge (after gathering the tiles of the other shards, if any).
+RLK_API int rlk_lmhead_logp_stats(const void* H, const void* W, int M, int N, int K, long long ldh,
+                                  long long ldw, const long long* targets, long long vocab_start,
+                                  float inv_temp, void* stats, long long stats_stride,
+                                  float* tgt_logit, void* logits_out, long long ld_logits,
+                                  void* stream) {
+  using namespace rlk;
+  RLK_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0, "lmhead_logp_stats: bad shape");
+  RLK_REQUIRE(vocab_start % kVocabTile == 0, "lmhead_logp_stats: vocab_start must be a multiple of 128");
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.nchunks = 1;
+  p.kb_per_chunk = (K + 63) / 64;
+  p.C = logits_out; p.ldc = ld_logits; p.out_fp32 = 0; p.accumulate = 0;
+  p.status = device_status_word();
+  p.stats = static_cast<float2*>(stats);
+  p.stats_stride = stats_stride;
+  p.stats_tile0 = static_cast<int>(vocab_start / kVocabTile);
+  p.targets = targets;
+  p.vocab_start = vocab_start;
+  p.tgt_logit = tgt_logit;
+  p.inv_temp = inv_temp;
+  return launch_gemm<128, false, false>(H, W, p, ldh, ldw, static_cast<cudaStream_t>(stream));
 }

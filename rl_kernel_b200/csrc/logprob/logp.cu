@@ -1,0 +1,131 @@
+// Selected-token log-prob from materialised bf16 logits, the ordered merge of per-tile
+// statistics, and the logits-gradient kernel.  See rlk/logp_contract.cuh for the contract.
+//
+// Kernels:
+//   logits_tile_stats : one thread per (row, 128-id tile) -> (max, sumexp), + target logit
+//   logp_merge        : one thread per row, tiles in ascending order -> logp, lse
+//   dlogits           : in place  logits <- g * (onehot(target) - softmax(z)) * inv_temp
+// Counterparts in the reference: csrc/cuda/logprob/deterministic_logp_kernel.cu:451-612
+// (tile_stats / backward) and csrc/cuda/logprob/fused_logp_kernel.cu:606-648 (ordered merge).
+#include "rlk/host.h"
+#include "rlk/logp_contract.cuh"
+#include "rlk/ptx.cuh"
+
+namespace rlk {
+
+__global__ void __launch_bounds__(128)
+logits_tile_stats_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
+                         float2* __restrict__ stats, long long stats_row_stride, float* __restrict__ tgt_logit,
+                         int rows, int n_local, long long vocab_start, int tile_start, int n_tiles_local,
+                         float inv_temp) {
+  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= static_cast<long long>(rows) * n_tiles_local) return;
+  const int row = static_cast<int>(gid / n_tiles_local);
+  const int lt = static_cast<int>(gid % n_tiles_local);
+  const int col0 = lt * kVocabTile;
+  const __nv_bfloat16* src = logits + row * ld + col0;
+  float z[128];
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    const bool in = col0 + c * 8 < n_local;  // n_local is a multiple of 8
+    if (in) v = *reinterpret_cast<const uint4*>(src + c * 8);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      z[c * 8 + 2 * k] = in ? logp_scale(bf16_lo(u[k]), inv_temp) : -INFINITY;
+      z[c * 8 + 2 * k + 1] = in ? logp_scale(bf16_hi(u[k]), inv_temp) : -INFINITY;
+    }
+  }
+  float m, s;
+  tile_stats_128(z, m, s);
+  stats[row * stats_row_stride + tile_start + lt] = make_float2(m, s);
+  if (targets) {
+    const long long tl = targets[row] - vocab_start - col0;
+    if (tl >= 0 && tl < kVocabTile && col0 + tl < n_local)
+      tgt_logit[row] = logp_scale(__bfloat162float(src[tl]), inv_temp);
+  }
+}
+
+__global__ void __launch_bounds__(128)
+logp_merge_kernel(const float2* __restrict__ stats, long long stats_row_stride, int n_tiles,
+                  const float* __restrict__ tgt_logit, float* __restrict__ logp, float* __restrict__ lse,
+                  int rows) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= rows) return;
+  const float2* st = stats + row * stats_row_stride;
+  float M = -INFINITY;
+  for (int t = 0; t < n_tiles; ++t) M = fmaxf(M, st[t].x);
+  float S = 0.f;
+  for (int t = 0; t < n_tiles; ++t) {
+    const float2 v = st[t];
+    if (v.x > -INFINITY) S = fmaf(v.y, logp_exp(__fsub_rn(v.x, M)), S);
+  }
+  const float l = __fadd_rn(M, logf(S));
+  if (lse) lse[row] = l;
+  if (logp) logp[row] = fminf(__fsub_rn(tgt_logit[row], l), 0.f);
+}
+
+// logits[row, j] <- (g[row] * inv_temp) * ( [j == target] - exp(z_j - lse[row]) )   (bf16, in place)
+__global__ void __launch_bounds__(256)
+dlogits_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
+               const float* __restrict__ lse, const float* __restrict__ g, int rows, int n_local,
+               long long vocab_start, float inv_temp) {
+  const int per_row = n_local / 8;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(rows) * per_row) return;
+  const int row = static_cast<int>(idx / per_row), c = static_cast<int>(idx % per_row) * 8;
+  const float gr = g[row] * inv_temp, l = lse[row];
+  const long long tl = targets[row] - vocab_start - c;
+  uint4* ptr = reinterpret_cast<uint4*>(logits + row * ld + c);
+  const uint4 v = *ptr;
+  const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float p0 = logp_exp(bf16_lo(u[k]) * inv_temp - l), p1 = logp_exp(bf16_hi(u[k]) * inv_temp - l);
+    const float d0 = gr * ((tl == 2 * k ? 1.f : 0.f) - p0), d1 = gr * ((tl == 2 * k + 1 ? 1.f : 0.f) - p1);
+    o[k] = pack_bf16x2(d0, d1);
+  }
+  *ptr = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+}  // namespace rlk
+using namespace rlk;
+
+// stats: float2 [rows][stats_row_stride]; this call fills tiles [tile_start, tile_start + n_tiles_local)
+// from a local logits shard [rows, n_local] whose first column is global vocab id `vocab_start`
+// (a multiple of 128). tgt_logit[row] is written only by the shard that owns the target.
+RLK_API int rlk_logits_tile_stats(const void* logits, long long ld, const long long* targets,
+                                  void* stats, long long stats_row_stride, float* tgt_logit, int rows,
+                                  int n_local, long long vocab_start, float inv_temp, void* stream) {
+  RLK_REQUIRE(rows > 0 && n_local > 0 && n_local % 8 == 0 && ld % 8 == 0, "tile_stats: bad shape");
+  RLK_REQUIRE(vocab_start % kVocabTile == 0, "tile_stats: vocab_start must be a multiple of 128");
+  const int n_tiles_local = (n_local + kVocabTile - 1) / kVocabTile;
+  const long long n = static_cast<long long>(rows) * n_tiles_local;
+  logits_tile_stats_kernel<<<static_cast<unsigned>((n + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)logits, ld, targets, (float2*)stats, stats_row_stride, tgt_logit, rows,
+      n_local, vocab_start, static_cast<int>(vocab_start / kVocabTile), n_tiles_local, inv_temp);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+RLK_API int rlk_logp_merge(const void* stats, long long stats_row_stride, int n_tiles,
+                           const float* tgt_logit, float* logp, float* lse, int rows, void* stream) {
+  RLK_REQUIRE(rows > 0 && n_tiles > 0, "logp_merge: bad shape");
+  logp_merge_kernel<<<(rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const float2*)stats, stats_row_stride, n_tiles, tgt_logit, logp, lse, rows);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+RLK_API int rlk_dlogits(void* logits, long long ld, const long long* targets, const float* lse,
+                        const float* g, int rows, int n_local, long long vocab_start, float inv_temp,
+                        void* stream) {
+  RLK_REQUIRE(rows > 0 && n_local % 8 == 0 && ld % 8 == 0, "dlogits: bad shape");
+  const long long n = static_cast<long long>(rows) * (n_local / 8);
+  dlogits_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (__nv_bfloat16*)logits, ld, targets, lse, g, rows, n_local, vocab_start, inv_temp);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}

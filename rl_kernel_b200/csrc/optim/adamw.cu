@@ -1,0 +1,114 @@
+// Fused AdamW over a flat parameter shard: bf16 gradient in, fp32 master / m / v state updated,
+// bf16 working copy written, all in one pass (16 bytes per element of state traffic is the floor).
+// Also the exact, partition-independent sum of squares used for gradient clipping (integer
+// per-exponent bins, the same idea as rl_engine/ops/norm/reproducible.py:17-57).
+#include "rlk/host.h"
+#include "rlk/ptx.cuh"
+
+namespace rlk {
+
+struct AdamParams {
+  float* master; float* m; float* v; const __nv_bfloat16* grad; __nv_bfloat16* param;
+  long long n;
+  float lr, beta1, beta2, eps, weight_decay, bc1, bc2;  // bc = 1 - beta^t
+  const float* grad_scale;  // device scalar multiplied into the gradient (clip factor), or null
+};
+
+__global__ void __launch_bounds__(256) adamw_kernel(const AdamParams p) {
+  const long long i0 = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * 8;
+  if (i0 >= p.n) return;
+  const float gs = p.grad_scale ? *p.grad_scale : 1.f;
+  if (i0 + 8 <= p.n) {
+    const uint4 g = *reinterpret_cast<const uint4*>(p.grad + i0);
+    const uint32_t gu[4] = {g.x, g.y, g.z, g.w};
+    float w[8], mm[8], vv[8];
+    *reinterpret_cast<float4*>(w) = *reinterpret_cast<const float4*>(p.master + i0);
+    *reinterpret_cast<float4*>(w + 4) = *reinterpret_cast<const float4*>(p.master + i0 + 4);
+    *reinterpret_cast<float4*>(mm) = *reinterpret_cast<const float4*>(p.m + i0);
+    *reinterpret_cast<float4*>(mm + 4) = *reinterpret_cast<const float4*>(p.m + i0 + 4);
+    *reinterpret_cast<float4*>(vv) = *reinterpret_cast<const float4*>(p.v + i0);
+    *reinterpret_cast<float4*>(vv + 4) = *reinterpret_cast<const float4*>(p.v + i0 + 4);
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gk = ((k & 1) ? bf16_hi(gu[k >> 1]) : bf16_lo(gu[k >> 1])) * gs;
+      mm[k] = p.beta1 * mm[k] + (1.f - p.beta1) * gk;
+      vv[k] = p.beta2 * vv[k] + (1.f - p.beta2) * gk * gk;
+      const float mh = mm[k] / p.bc1, vh = vv[k] / p.bc2;
+      w[k] = w[k] - p.lr * (mh / (sqrtf(vh) + p.eps) + p.weight_decay * w[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k) o[k] = pack_bf16x2(w[2 * k], w[2 * k + 1]);
+    *reinterpret_cast<float4*>(p.master + i0) = *reinterpret_cast<float4*>(w);
+    *reinterpret_cast<float4*>(p.master + i0 + 4) = *reinterpret_cast<float4*>(w + 4);
+    *reinterpret_cast<float4*>(p.m + i0) = *reinterpret_cast<float4*>(mm);
+    *reinterpret_cast<float4*>(p.m + i0 + 4) = *reinterpret_cast<float4*>(mm + 4);
+    *reinterpret_cast<float4*>(p.v + i0) = *reinterpret_cast<float4*>(vv);
+    *reinterpret_cast<float4*>(p.v + i0 + 4) = *reinterpret_cast<float4*>(vv + 4);
+    *reinterpret_cast<uint4*>(p.param + i0) = make_uint4(o[0], o[1], o[2], o[3]);
+  } else {
+    for (long long i = i0; i < p.n; ++i) {
+      const float gk = __bfloat162float(p.grad[i]) * gs;
+      const float m1 = p.beta1 * p.m[i] + (1.f - p.beta1) * gk;
+      const float v1 = p.beta2 * p.v[i] + (1.f - p.beta2) * gk * gk;
+      const float w1 = p.master[i] - p.lr * ((m1 / p.bc1) / (sqrtf(v1 / p.bc2) + p.eps) + p.weight_decay * p.master[i]);
+      p.m[i] = m1; p.v[i] = v1; p.master[i] = w1;
+      p.param[i] = __float2bfloat16_rn(w1);
+    }
+  }
+}
+
+// Exact sum of squares.  A finite bf16 value is mant * 2^ex with mant < 2^8, so its square is an
+// integer sq < 2^16 times 2^(2 ex).  Squares are summed as integers into one 64-bit bin per
+// biased exponent (256 bins); integer addition is associative, so the bins -- and the norm
+// computed from them in a fixed order -- do not depend on how the gradient is split over
+// threads, blocks or ranks.  bins[255] counts non-finite inputs.
+__global__ void __launch_bounds__(256)
+sumsq_bins_kernel(const __nv_bfloat16* __restrict__ g, long long n, unsigned long long* bins) {
+  __shared__ unsigned long long sb[256];
+  sb[threadIdx.x] = 0ull;
+  __syncthreads();
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint32_t h = *reinterpret_cast<const unsigned short*>(g + i);
+    const uint32_t e = (h >> 7) & 0xff;
+    uint32_t mant = h & 0x7f;
+    if (e == 0xff) { atomicAdd(&sb[255], 1ull); continue; }
+    if (e != 0) mant |= 0x80;
+    if (mant == 0) continue;
+    atomicAdd(&sb[e], static_cast<unsigned long long>(mant) * mant);
+  }
+  __syncthreads();
+  if (sb[threadIdx.x] != 0ull) atomicAdd(&bins[threadIdx.x], sb[threadIdx.x]);
+}
+
+}  // namespace rlk
+using namespace rlk;
+
+RLK_API int rlk_adamw(float* master, float* m, float* v, const void* grad, void* param, long long n,
+                      float lr, float beta1, float beta2, float eps, float weight_decay, int step,
+                      const float* grad_scale, void* stream) {
+  RLK_REQUIRE(n > 0 && step >= 1, "adamw: n > 0 and step >= 1 required");
+  RLK_REQUIRE(((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) |
+                reinterpret_cast<uintptr_t>(v) | reinterpret_cast<uintptr_t>(grad) |
+                reinterpret_cast<uintptr_t>(param)) & 15) == 0, "adamw: buffers must be 16-byte aligned");
+  AdamParams p{master, m, v, (const __nv_bfloat16*)grad, (__nv_bfloat16*)param, n, lr, beta1, beta2, eps,
+               weight_decay, 1.f - powf(beta1, (float)step), 1.f - powf(beta2, (float)step), grad_scale};
+  const long long threads = (n + 7) / 8;
+  adamw_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+// bins: 256 x uint64, zeroed by the caller.  bins[e] += sum of mant^2 over elements with biased
+// exponent e (e = 0 holds subnormals with exponent 1's scale); bins[255] += count of inf/nan.
+// sum of squares = sum_e bins[e] * 2^(2 * (max(e,1) - 127 - 7)).
+RLK_API int rlk_sumsq_bins(const void* grad, long long n, unsigned long long* bins, void* stream) {
+  RLK_REQUIRE(n > 0, "sumsq_bins: empty");
+  long long blocks = (n + 256 * 16 - 1) / (256 * 16);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  sumsq_bins_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)grad, n, bins);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}

@@ -1,0 +1,107 @@
+// Token sampling from bf16 logits: temperature + optional top-k / top-p support restriction,
+// drawn with the Gumbel-max trick and a counter-based Philox4x32-10 generator.
+//
+//   token = argmax_j ( z_j + G_j ),  z = logit / T,  G_j = -log(-log(u_j)),
+//   u_j = Philox(seed; counter = (row_key, step, global vocab id j))
+// Every vocabulary id owns its own random number, so the draw does not depend on how the
+// vocabulary is sharded over tensor-parallel ranks: each rank reduces its shard to (best value,
+// best id) and the global winner is the maximum over ranks (ties -> smaller id).
+// Top-k / top-p: a per-row logit threshold `min_keep[row]` (computed by the keep-mask op) removes
+// ids whose z is below it; ids at or beyond the real vocab are never sampled.
+// One CTA per row; threads stride the row with 16-byte loads, then a fixed shared-memory tree.
+// Replaces the torch sort/softmax/cumsum path of rl_engine/ops/sampling/policy.py:17-52 for the
+// draw itself (FlashInfer sampling in rl_engine/ops/sampling/api.py:42-79).
+#include "rlk/host.h"
+#include "rlk/ptx.cuh"
+
+namespace rlk {
+
+__device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint32_t k1) {
+  const uint32_t hi0 = __umulhi(0xD2511F53u, c[0]), lo0 = 0xD2511F53u * c[0];
+  const uint32_t hi1 = __umulhi(0xCD9E8D57u, c[2]), lo1 = 0xCD9E8D57u * c[2];
+  const uint32_t n0 = hi1 ^ c[1] ^ k0, n1 = lo1, n2 = hi0 ^ c[3] ^ k1, n3 = lo0;
+  c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
+}
+__device__ __forceinline__ uint32_t philox_u32(uint64_t seed, uint32_t c0, uint32_t c1, uint32_t c2) {
+  uint32_t c[4] = {c0, c1, c2, 0u};
+  uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    philox_round(c, k0, k1);
+    k0 += 0x9E3779B9u;
+    k1 += 0xBB67AE85u;
+  }
+  return c[0];
+}
+__device__ __forceinline__ float gumbel_from_u32(uint32_t r) {
+  const float u = (static_cast<float>(r >> 8) + 0.5f) * (1.0f / 16777216.0f);  // (0,1)
+  return -__logf(-__logf(u));
+}
+
+struct SampleParams {
+  const __nv_bfloat16* logits; long long ld;
+  const float* min_keep;       // [rows] or null
+  const long long* row_keys;   // [rows] stable per-sequence key for the RNG counter, or null (row index)
+  long long* out_ids; float* out_val;
+  int rows, n_local; long long vocab_start;
+  float inv_temp; uint64_t seed; uint32_t step; int greedy;
+};
+
+__global__ void __launch_bounds__(256) sample_gumbel_kernel(const SampleParams p) {
+  __shared__ float sval[256];
+  __shared__ long long sidx[256];
+  const int row = blockIdx.x;
+  const __nv_bfloat16* src = p.logits + row * p.ld;
+  const uint32_t key = static_cast<uint32_t>(p.row_keys ? p.row_keys[row] : row);
+  const float thr = p.min_keep ? p.min_keep[row] : -INFINITY;
+  float best = -INFINITY;
+  long long best_id = 0x7fffffffffffffffll;
+  for (int c = threadIdx.x; c < p.n_local / 8; c += blockDim.x) {
+    const uint4 v = *reinterpret_cast<const uint4*>(src + c * 8);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float z = ((k & 1) ? bf16_hi(u[k >> 1]) : bf16_lo(u[k >> 1])) * p.inv_temp;
+      if (z < thr) continue;
+      const long long id = p.vocab_start + c * 8 + k;
+      float s = z;
+      if (!p.greedy) s += gumbel_from_u32(philox_u32(p.seed, static_cast<uint32_t>(id), key, p.step));
+      if (s > best || (s == best && id < best_id)) { best = s; best_id = id; }
+    }
+  }
+  sval[threadIdx.x] = best;
+  sidx[threadIdx.x] = best_id;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) {
+      const float ov = sval[threadIdx.x + o];
+      const long long oi = sidx[threadIdx.x + o];
+      if (ov > sval[threadIdx.x] || (ov == sval[threadIdx.x] && oi < sidx[threadIdx.x])) {
+        sval[threadIdx.x] = ov;
+        sidx[threadIdx.x] = oi;
+      }
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    p.out_ids[row] = sidx[0];
+    if (p.out_val) p.out_val[row] = sval[0];
+  }
+}
+
+}  // namespace rlk
+using namespace rlk;
+
+// out_ids[row] = sampled GLOBAL vocab id from this shard's columns; out_val = its perturbed score
+// (the cross-rank winner is the shard with the largest out_val, ties to the smaller id).
+RLK_API int rlk_sample_gumbel(const void* logits, long long ld, const float* min_keep,
+                              const long long* row_keys, long long* out_ids, float* out_val, int rows,
+                              int n_local, long long vocab_start, float inv_temp,
+                              unsigned long long seed, unsigned int step, int greedy, void* stream) {
+  RLK_REQUIRE(rows > 0 && n_local > 0 && n_local % 8 == 0 && ld % 8 == 0, "sample: bad shape");
+  SampleParams p{(const __nv_bfloat16*)logits, ld, min_keep, row_keys, out_ids, out_val, rows, n_local,
+                 vocab_start, inv_temp, seed, step, greedy};
+  sample_gumbel_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
