@@ -189,17 +189,17 @@ def qk_norm_rope_bwd(qkv, q_w, k_w, cos_tab, sin_tab, pos, dq, dk, dv, dqkv, scr
 
 
 # ------------------------------------------------------------------------------------- activation
-def swiglu_fwd(gu, out, I: int) -> None:
+def swiglu_fwd(gu, out, I: int, blk: int | None = None) -> None:
     rc = _lib().rlk_swiglu_fwd(ext.ptr(gu), _ll(gu.stride(0)), ext.ptr(out), _ll(out.stride(0)),
-                               c_int(gu.shape[0]), c_int(I), ext.stream_ptr(gu.device))
+                               c_int(gu.shape[0]), c_int(I), c_int(blk or I), ext.stream_ptr(gu.device))
     ext.check(rc, "swiglu_fwd")
     _count()
 
 
-def swiglu_bwd(gu, dout, dgu, I: int) -> None:
+def swiglu_bwd(gu, dout, dgu, I: int, blk: int | None = None) -> None:
     rc = _lib().rlk_swiglu_bwd(ext.ptr(gu), _ll(gu.stride(0)), ext.ptr(dout), _ll(dout.stride(0)),
                                ext.ptr(dgu), _ll(dgu.stride(0)), c_int(gu.shape[0]), c_int(I),
-                               ext.stream_ptr(gu.device))
+                               c_int(blk or I), ext.stream_ptr(gu.device))
     ext.check(rc, "swiglu_bwd")
     _count()
 

@@ -1,5 +1,8 @@
-// Packed SwiGLU forward / backward: the column-parallel FFN GEMM writes gate and up side by
-// side ([rows, 2*I], gate = columns [0,I), up = [I,2I)); out = silu(gate) * up.
+// Packed SwiGLU forward / backward.  The column-parallel FFN GEMM writes gate and up interleaved
+// in blocks of `blk` columns: [g_0 | u_0 | g_1 | u_1 | ...] where g_c / u_c are columns
+// [c*blk, (c+1)*blk) of gate / up (blk = I gives the plain [gate | up] layout; the model uses
+// blk = I/8, one block per canonical tensor-parallel shard, so any TP degree sees the same
+// layout).  out[:, c*blk + j] = silu(g_c[j]) * u_c[j].
 // fp32 math, expf, one rounding at the store (same materialisation boundary as the reference's
 // csrc/cuda/activation/activation.cu:32-135).  Eight elements per thread, 16-byte accesses.
 #include "rlk/host.h"
@@ -11,13 +14,14 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g))
 
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_gu, __nv_bfloat16* __restrict__ out,
-                  long long ld_out, int rows, int I) {
+                  long long ld_out, int rows, int I, int blk) {
   const int per_row = I / 8;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(rows) * per_row) return;
   const int r = static_cast<int>(idx / per_row), c = static_cast<int>(idx % per_row) * 8;
-  const uint4 g = *reinterpret_cast<const uint4*>(gu + r * ld_gu + c);
-  const uint4 u = *reinterpret_cast<const uint4*>(gu + r * ld_gu + I + c);
+  const long long gc = static_cast<long long>(c / blk) * 2 * blk + (c % blk);  // column of gate[c]
+  const uint4 g = *reinterpret_cast<const uint4*>(gu + r * ld_gu + gc);
+  const uint4 u = *reinterpret_cast<const uint4*>(gu + r * ld_gu + gc + blk);
   const uint32_t gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {u.x, u.y, u.z, u.w};
   uint32_t o[4];
 #pragma unroll
@@ -29,13 +33,14 @@ swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_gu, __nv_bf
 // d(gate) = dout * up * silu'(gate), d(up) = dout * silu(gate); written packed like the input.
 __global__ void __launch_bounds__(256)
 swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_gu, const __nv_bfloat16* __restrict__ dout,
-                  long long ld_dout, __nv_bfloat16* __restrict__ dgu, long long ld_dgu, int rows, int I) {
+                  long long ld_dout, __nv_bfloat16* __restrict__ dgu, long long ld_dgu, int rows, int I, int blk) {
   const int per_row = I / 8;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(rows) * per_row) return;
   const int r = static_cast<int>(idx / per_row), c = static_cast<int>(idx % per_row) * 8;
-  const uint4 g = *reinterpret_cast<const uint4*>(gu + r * ld_gu + c);
-  const uint4 u = *reinterpret_cast<const uint4*>(gu + r * ld_gu + I + c);
+  const long long gc = static_cast<long long>(c / blk) * 2 * blk + (c % blk);  // column of gate[c]
+  const uint4 g = *reinterpret_cast<const uint4*>(gu + r * ld_gu + gc);
+  const uint4 u = *reinterpret_cast<const uint4*>(gu + r * ld_gu + gc + blk);
   const uint4 d = *reinterpret_cast<const uint4*>(dout + r * ld_dout + c);
   const uint32_t gv[4] = {g.x, g.y, g.z, g.w}, uv[4] = {u.x, u.y, u.z, u.w}, dv[4] = {d.x, d.y, d.z, d.w};
   uint32_t og[4], ou[4];
@@ -55,31 +60,33 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_gu, const _
     og[i] = pack_bf16x2(dgl[0], dgl[1]);
     ou[i] = pack_bf16x2(dul[0], dul[1]);
   }
-  *reinterpret_cast<uint4*>(dgu + r * ld_dgu + c) = make_uint4(og[0], og[1], og[2], og[3]);
-  *reinterpret_cast<uint4*>(dgu + r * ld_dgu + I + c) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
+  *reinterpret_cast<uint4*>(dgu + r * ld_dgu + gc) = make_uint4(og[0], og[1], og[2], og[3]);
+  *reinterpret_cast<uint4*>(dgu + r * ld_dgu + gc + blk) = make_uint4(ou[0], ou[1], ou[2], ou[3]);
 }
 
 }  // namespace rlk
 using namespace rlk;
 
 RLK_API int rlk_swiglu_fwd(const void* gu, long long ld_gu, void* out, long long ld_out, int rows,
-                           int I, void* stream) {
+                           int I, int blk, void* stream) {
   RLK_REQUIRE(rows > 0 && I > 0 && I % 8 == 0 && ld_gu % 8 == 0 && ld_out % 8 == 0,
               "swiglu: I and pitches must be multiples of 8");
+  RLK_REQUIRE(blk > 0 && blk % 8 == 0 && I % blk == 0, "swiglu: blk must divide I and be a multiple of 8");
   const long long n = static_cast<long long>(rows) * (I / 8);
   swiglu_fwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)out, ld_out, rows, I);
+      (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)out, ld_out, rows, I, blk);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
 
 RLK_API int rlk_swiglu_bwd(const void* gu, long long ld_gu, const void* dout, long long ld_dout,
-                           void* dgu, long long ld_dgu, int rows, int I, void* stream) {
+                           void* dgu, long long ld_dgu, int rows, int I, int blk, void* stream) {
   RLK_REQUIRE(rows > 0 && I > 0 && I % 8 == 0 && ld_gu % 8 == 0 && ld_dout % 8 == 0 && ld_dgu % 8 == 0,
               "swiglu_bwd: I and pitches must be multiples of 8");
+  RLK_REQUIRE(blk > 0 && blk % 8 == 0 && I % blk == 0, "swiglu_bwd: blk must divide I and be a multiple of 8");
   const long long n = static_cast<long long>(rows) * (I / 8);
   swiglu_bwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)gu, ld_gu, (const __nv_bfloat16*)dout, ld_dout, (__nv_bfloat16*)dgu, ld_dgu, rows, I);
+      (const __nv_bfloat16*)gu, ld_gu, (const __nv_bfloat16*)dout, ld_dout, (__nv_bfloat16*)dgu, ld_dgu, rows, I, blk);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

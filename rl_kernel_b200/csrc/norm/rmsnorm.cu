@@ -164,7 +164,9 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, int np
 
 // ------------------------------------------------------------------ QK-norm + RoPE (head_dim 128)
 // One warp per (token, head). Lane l owns elements 2l, 2l+1 and their rotate-half partners
-// 64+2l, 64+2l+1.  heads [0,Hq) are queries, [Hq,Hq+Hkv) keys, [Hq+Hkv,Hq+2Hkv) values (copied).
+// 64+2l, 64+2l+1.  The fused QKV activation is GQA-group-major: for every KV head g the columns
+// hold [G query heads of the group | key head g | value head g], G = Hq / Hkv.  A tensor-parallel
+// rank owns whole groups, so the layout (and every reduction over it) is the same for any TP.
 // Destination rows: q -> q_out[t], k/v -> k_out/v_out[kv_slot ? kv_slot[t] : t].
 struct QkRopeParams {
   const __nv_bfloat16* qkv; long long ld_qkv;
@@ -183,8 +185,12 @@ __global__ void __launch_bounds__(256) qk_norm_rope_fwd_kernel(const QkRopeParam
   const int gw = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int heads = p.Hq + 2 * p.Hkv;
   if (gw >= p.T * heads) return;
-  const int t = gw / heads, h = gw - t * heads;
-  const __nv_bfloat16* src = p.qkv + static_cast<long long>(t) * p.ld_qkv + h * 128;
+  const int t = gw / heads, hh = gw - t * heads;
+  const int G = p.Hq / p.Hkv;
+  const int grp = hh / (G + 2), jj = hh - grp * (G + 2);
+  // logical head index in the "all q | all k | all v" numbering used below
+  const int h = jj < G ? grp * G + jj : (jj == G ? p.Hq + grp : p.Hq + p.Hkv + grp);
+  const __nv_bfloat16* src = p.qkv + static_cast<long long>(t) * p.ld_qkv + hh * 128;
   const uint32_t lo = *reinterpret_cast<const uint32_t*>(src + 2 * lane);
   const uint32_t hi = *reinterpret_cast<const uint32_t*>(src + 64 + 2 * lane);
   if (h >= p.Hq + p.Hkv) {  // value head: plain copy into the cache / output
@@ -250,9 +256,12 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const QkRopeBwdPa
   const int t0 = blockIdx.x * p.tokens_per_cta;
   const int t1 = min(p.T, t0 + p.tokens_per_cta);
   const int items = (t1 - t0) * heads;
+  const int G = p.Hq / p.Hkv;
   for (int it = warp; it < items; it += 8) {
-    const int t = t0 + it / heads, h = it % heads;
-    __nv_bfloat16* dst = p.dqkv + static_cast<long long>(t) * p.ld_dqkv + h * 128;
+    const int t = t0 + it / heads, hh = it % heads;
+    const int grp = hh / (G + 2), jj = hh - grp * (G + 2);
+    const int h = jj < G ? grp * G + jj : (jj == G ? p.Hq + grp : p.Hq + p.Hkv + grp);
+    __nv_bfloat16* dst = p.dqkv + static_cast<long long>(t) * p.ld_dqkv + hh * 128;
     if (h >= p.Hq + p.Hkv) {
       const __nv_bfloat16* g = p.dv + static_cast<long long>(t) * p.ld_dkv + (h - p.Hq - p.Hkv) * 128;
       *reinterpret_cast<uint32_t*>(dst + 2 * lane) = *reinterpret_cast<const uint32_t*>(g + 2 * lane);
@@ -271,7 +280,7 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const QkRopeBwdPa
     const float ga0 = bf16_lo(glo), ga1 = bf16_hi(glo), gb0 = bf16_lo(ghi), gb1 = bf16_hi(ghi);
     const float dn_a0 = ga0 * c.x + gb0 * s.x, dn_a1 = ga1 * c.y + gb1 * s.y;
     const float dn_b0 = gb0 * c.x - ga0 * s.x, dn_b1 = gb1 * c.y - ga1 * s.y;
-    const __nv_bfloat16* src = p.qkv + static_cast<long long>(t) * p.ld_qkv + h * 128;
+    const __nv_bfloat16* src = p.qkv + static_cast<long long>(t) * p.ld_qkv + hh * 128;
     const uint32_t lo = *reinterpret_cast<const uint32_t*>(src + 2 * lane);
     const uint32_t hi = *reinterpret_cast<const uint32_t*>(src + 64 + 2 * lane);
     const float a0 = bf16_lo(lo), a1 = bf16_hi(lo), b0 = bf16_lo(hi), b1 = bf16_hi(hi);

@@ -1,0 +1,621 @@
+"""Qwen3 dense on the sm_100a kernels: packed parameters, training forward/backward with
+per-layer recomputation, prefill, and single-token decode against a KV cache.
+
+The SAME kernels with the SAME per-row programs serve rollout (decode, batch of sequences) and
+training (packed full sequences), which is what makes the selected-token log-probs of the two
+bitwise equal.  Every matrix product is ``det_gemm`` (csrc/gemm/det_gemm_sm100.cu); row-parallel
+projections use canonical K chunks so the tensor-parallel degree does not change a bit.
+
+Tensor parallelism follows the usual column/row split (rl_engine/backends/cuda/ffn/ffn.py:554-683,
+rl_engine/integrations/engines/train/megatron/runtime.py:491-636 in the reference); the partial
+sums of row-parallel GEMMs go through ``ParallelContext.tp_all_reduce`` (fixed balanced tree).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+
+from rl_kernel_b200.backends import native as nv
+from rl_kernel_b200.models.qwen3.spec import VOCAB_TILE, Qwen3DenseSpec
+from rl_kernel_b200.models.qwen3.weights import (Qwen3DenseWeights, pack_gate_up, pack_qkv, pad_vocab,
+                                                 unpack_gate_up, unpack_qkv)
+
+BF16 = torch.bfloat16
+
+
+# ------------------------------------------------------------------------------ parallel context
+class ParallelContext:
+    """Rank geometry plus the collectives the engine needs.  The default is a single GPU."""
+
+    def __init__(self, tp_rank: int = 0, tp_size: int = 1, cp_rank: int = 0, cp_size: int = 1,
+                 collective=None, cp_collective=None):
+        self.tp_rank, self.tp_size = tp_rank, tp_size
+        self.cp_rank, self.cp_size = cp_rank, cp_size
+        self.collective = collective        # fixed-order TP collective (all_reduce_, all_gather)
+        self.cp_collective = cp_collective
+
+    def tp_all_reduce_(self, x: torch.Tensor) -> torch.Tensor:
+        if self.tp_size > 1:
+            self.collective.all_reduce_(x)
+        return x
+
+    def tp_all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        """[..] -> [tp, ..] in rank order."""
+        if self.tp_size == 1:
+            return x.unsqueeze(0)
+        return self.collective.all_gather(x)
+
+
+# ------------------------------------------------------------------------------ parameters
+@dataclass
+class _Slot:
+    name: str
+    shape: tuple[int, ...]
+    offset: int = 0
+
+    @property
+    def numel(self) -> int:
+        return math.prod(self.shape)
+
+
+class PackedParams:
+    """All parameters of one rank in ONE flat bf16 buffer (plus a twin for gradients), so the
+    optimizer, gradient clipping, weight sync and gradient all-reduce are single launches."""
+
+    def __init__(self, spec: Qwen3DenseSpec, tp_rank: int, tp_size: int, device: torch.device,
+                 with_grad: bool = False):
+        if spec.canonical_tp % tp_size:
+            raise ValueError(f"tp_size {tp_size} must divide canonical_tp {spec.canonical_tp}")
+        self.spec, self.tp_rank, self.tp_size, self.device = spec, tp_rank, tp_size, device
+        h, d = spec.hidden_size, spec.head_dim
+        self.qkv_local = spec.qkv_dim // tp_size
+        self.q_local = spec.q_dim // tp_size
+        self.kv_local = spec.kv_dim // tp_size
+        self.i_local = spec.intermediate_size // tp_size
+        self.v_local = spec.padded_vocab_size // tp_size
+        self.vocab_start = tp_rank * self.v_local
+        self.v_real_local = max(0, min(self.v_local, spec.vocab_size - self.vocab_start))
+        slots: list[_Slot] = [_Slot("embed", (self.v_local, h))]
+        for l in range(spec.num_hidden_layers):
+            slots += [_Slot(f"l{l}.ln1", (h,)), _Slot(f"l{l}.wqkv", (self.qkv_local, h)),
+                      _Slot(f"l{l}.qn", (d,)), _Slot(f"l{l}.kn", (d,)),
+                      _Slot(f"l{l}.wo", (h, self.q_local)), _Slot(f"l{l}.ln2", (h,)),
+                      _Slot(f"l{l}.wgu", (2 * self.i_local, h)), _Slot(f"l{l}.wd", (h, self.i_local))]
+        slots += [_Slot("norm", (h,)), _Slot("lm_head", (self.v_local, h))]
+        off = 0
+        for s in slots:
+            s.offset = off
+            off += (s.numel + 7) // 8 * 8
+        self.slots = {s.name: s for s in slots}
+        self.numel = off
+        self.flat = torch.zeros(off, dtype=BF16, device=device)
+        self.grad = torch.zeros(off, dtype=BF16, device=device) if with_grad else None
+        self.w = {s.name: self.flat[s.offset:s.offset + s.numel].view(s.shape) for s in slots}
+        self.g = ({s.name: self.grad[s.offset:s.offset + s.numel].view(s.shape) for s in slots}
+                  if with_grad else {})
+
+    # replicated (not TP-sharded) parameters: their gradients are identical on every TP rank
+    def is_replicated(self, name: str) -> bool:
+        return name.endswith((".ln1", ".ln2", ".qn", ".kn")) or name == "norm"
+
+    def load(self, weights: Qwen3DenseWeights) -> "PackedParams":
+        spec, r, tp = self.spec, self.tp_rank, self.tp_size
+        dev = self.device
+
+        def put(name: str, t: torch.Tensor) -> None:
+            self.w[name].copy_(t.to(device=dev, dtype=BF16))
+
+        def rows(t: torch.Tensor) -> torch.Tensor:
+            n = t.shape[0] // tp
+            return t[r * n:(r + 1) * n]
+
+        def cols(t: torch.Tensor) -> torch.Tensor:
+            n = t.shape[1] // tp
+            return t[:, r * n:(r + 1) * n]
+
+        put("embed", rows(pad_vocab(spec, weights["embed_tokens.weight"])))
+        put("lm_head", rows(pad_vocab(spec, weights["lm_head.weight"])))
+        put("norm", weights["norm.weight"])
+        for l in range(spec.num_hidden_layers):
+            p = f"layers.{l}"
+            put(f"l{l}.ln1", weights[f"{p}.input_layernorm.weight"])
+            put(f"l{l}.ln2", weights[f"{p}.post_attention_layernorm.weight"])
+            put(f"l{l}.qn", weights[f"{p}.self_attn.q_norm.weight"])
+            put(f"l{l}.kn", weights[f"{p}.self_attn.k_norm.weight"])
+            put(f"l{l}.wqkv", rows(pack_qkv(spec, weights[f"{p}.self_attn.q_proj.weight"],
+                                            weights[f"{p}.self_attn.k_proj.weight"],
+                                            weights[f"{p}.self_attn.v_proj.weight"])))
+            put(f"l{l}.wo", cols(weights[f"{p}.self_attn.o_proj.weight"]))
+            put(f"l{l}.wgu", rows(pack_gate_up(spec, weights[f"{p}.mlp.gate_proj.weight"],
+                                               weights[f"{p}.mlp.up_proj.weight"])))
+            put(f"l{l}.wd", cols(weights[f"{p}.mlp.down_proj.weight"]))
+        return self
+
+    def init_synthetic_(self, seed: int = 0, std: float = 0.02) -> "PackedParams":
+        """Random-init directly on the device (used for the full-size benchmark where building
+        the HF-layout dictionary on the host first would take minutes)."""
+        gen = torch.Generator(device=self.device).manual_seed(seed * 1000 + self.tp_rank)
+        for name, s in self.slots.items():
+            if len(s.shape) == 1:
+                self.w[name].fill_(1.0)
+            else:
+                w = self.w[name]
+                step = max(1, (1 << 26) // max(1, w.shape[1]))
+                for r0 in range(0, w.shape[0], step):
+                    blk = w[r0:r0 + step]
+                    blk.copy_(torch.randn(blk.shape, generator=gen, device=self.device,
+                                          dtype=torch.float32).mul_(std))
+        for name in ("embed", "lm_head"):
+            w = self.w[name]
+            if self.v_real_local < self.v_local:
+                w[self.v_real_local:].zero_()
+        return self
+
+    def export_local(self) -> dict[str, torch.Tensor]:
+        """This rank's shard back in HF key names (TP=1: the full HF state)."""
+        spec = self.spec
+        if self.tp_size != 1:
+            raise NotImplementedError("export_local assembles full tensors only for tp_size == 1")
+        out = {"embed_tokens.weight": self.w["embed"][:spec.vocab_size],
+               "lm_head.weight": self.w["lm_head"][:spec.vocab_size], "norm.weight": self.w["norm"]}
+        for l in range(spec.num_hidden_layers):
+            p = f"layers.{l}"
+            q, k, v = unpack_qkv(spec, self.w[f"l{l}.wqkv"])
+            gte, up = unpack_gate_up(spec, self.w[f"l{l}.wgu"])
+            out.update({f"{p}.input_layernorm.weight": self.w[f"l{l}.ln1"],
+                        f"{p}.post_attention_layernorm.weight": self.w[f"l{l}.ln2"],
+                        f"{p}.self_attn.q_norm.weight": self.w[f"l{l}.qn"],
+                        f"{p}.self_attn.k_norm.weight": self.w[f"l{l}.kn"],
+                        f"{p}.self_attn.q_proj.weight": q, f"{p}.self_attn.k_proj.weight": k,
+                        f"{p}.self_attn.v_proj.weight": v,
+                        f"{p}.self_attn.o_proj.weight": self.w[f"l{l}.wo"],
+                        f"{p}.mlp.gate_proj.weight": gte, f"{p}.mlp.up_proj.weight": up,
+                        f"{p}.mlp.down_proj.weight": self.w[f"l{l}.wd"]})
+        return out
+
+
+# ------------------------------------------------------------------------------ attention tiles
+def rope_tables(spec: Qwen3DenseSpec, max_pos: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    d = spec.head_dim
+    inv_freq = 1.0 / (spec.rope_theta ** (torch.arange(0, d, 2, dtype=torch.float64) / d))
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv_freq[None]
+    return (ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous())
+
+
+def train_tiles(nseq: int, S: int, hq: int, hkv: int, d: int, device, *, q_pos0: int = 0
+                ) -> tuple[torch.Tensor, torch.Tensor]:
+    """Forward/dQ tiles and dK/dV tiles for ``nseq`` packed sequences of length ``S``."""
+    g = hq // hkv
+    nqt = (S + 127) // 128
+    b = torch.arange(nseq).view(-1, 1, 1)
+    qt = torch.arange(nqt - 1, -1, -1).view(1, -1, 1)  # longest tiles first
+    h = torch.arange(hq).view(1, 1, -1)
+    z = torch.zeros(nseq, nqt, hq, dtype=torch.long)
+    row0 = b * S + qt * 128 + z
+    fw = torch.stack([row0, h * d + z, torch.clamp(S - qt * 128, max=128) + z, b * S + z,
+                      (h // g) * d + z, qt * 128 + q_pos0 + z, z + 1, z + S + q_pos0,
+                      row0 * hq + h, z + hq, z, z], dim=-1).reshape(-1, 12)
+    hk = torch.arange(hkv).view(1, 1, -1)
+    kb = torch.arange(nqt).view(1, -1, 1)
+    zk = torch.zeros(nseq, nqt, hkv, dtype=torch.long)
+    kv = torch.stack([b * S + kb * 128 + zk, hk * d + zk, kb * 128 + zk,
+                      torch.clamp(S - kb * 128, max=128) + zk, b * S + zk, zk + q_pos0, zk + S,
+                      hk * g * d + zk, zk + g, (b * S) * hq + hk * g + zk, zk + hq, zk + 1],
+                     dim=-1).reshape(-1, 12)
+    return fw.to(torch.int32).to(device).contiguous(), kv.to(torch.int32).to(device).contiguous()
+
+
+# ------------------------------------------------------------------------------ workspace
+class Workspace:
+    """Named, shape-keyed scratch tensors that live for the lifetime of the engine."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: dict[tuple, torch.Tensor] = {}
+
+    def get(self, name: str, shape: tuple[int, ...], dtype=BF16, zero: bool = False) -> torch.Tensor:
+        key = (name, tuple(shape), dtype)
+        t = self._bufs.get(key)
+        if t is None:
+            t = (torch.zeros if zero else torch.empty)(shape, dtype=dtype, device=self.device)
+            self._bufs[key] = t
+        return t
+
+    def release(self, prefix: str = "") -> None:
+        for k in [k for k in self._bufs if k[0].startswith(prefix)]:
+            del self._bufs[k]
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self._bufs.values())
+
+
+@dataclass
+class KVCache:
+    k: list[torch.Tensor]   # per layer [nseq * max_len, kv_local]
+    v: list[torch.Tensor]
+    nseq: int
+    max_len: int
+
+
+@dataclass
+class TrainState:
+    nseq: int
+    S: int
+    ckpt: torch.Tensor                      # [L, T, H] residual-stream input of every layer
+    last_x: torch.Tensor | None = None      # output of the last MLP (pre residual add)
+    last_res: torch.Tensor | None = None
+    final_s: torch.Tensor | None = None
+    extra: dict = field(default_factory=dict)
+
+
+class Qwen3Engine:
+    """Forward / backward / decode of one model replica shard on one GPU."""
+
+    def __init__(self, spec: Qwen3DenseSpec, params: PackedParams, ctx: ParallelContext | None = None,
+                 max_positions: int = 4096):
+        self.spec, self.p = spec, params
+        self.ctx = ctx or ParallelContext()
+        self.dev = params.device
+        tp = self.ctx.tp_size
+        self.hq = spec.num_attention_heads // tp
+        self.hkv = spec.num_key_value_heads // tp
+        self.d = spec.head_dim
+        if self.d != 128:
+            raise ValueError("the sm_100a attention kernels are specialised for head_dim 128")
+        self.nchunks = spec.canonical_tp // tp      # canonical K chunks held by this rank
+        self.blk = spec.intermediate_size // spec.canonical_tp
+        self.scale = 1.0 / math.sqrt(self.d)
+        self.cos, self.sin = rope_tables(spec, max_positions, self.dev)
+        self.ws = Workspace(self.dev)
+        self._tiles: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
+        for K in (params.q_local, params.i_local):
+            if self.nchunks > 1 and (K // self.nchunks) % 64:
+                raise ValueError(f"canonical K chunk {K // self.nchunks} must be a multiple of 64")
+
+    # -------------------------------------------------------------------------- helpers
+    def _gemm(self, a, b, out, *, a_mn=False, b_mn=False, nchunks=1, accumulate=False, M=None, N=None, K=None):
+        if M is None:
+            M = a.shape[1] if a_mn else a.shape[0]
+            K = a.shape[0] if a_mn else a.shape[1]
+            N = b.shape[1] if b_mn else b.shape[0]
+        return nv.det_gemm(a, b, out, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, nchunks=nchunks,
+                           accumulate=accumulate)
+
+    def _tiles_for(self, nseq: int, S: int):
+        key = (nseq, S)
+        if key not in self._tiles:
+            self._tiles[key] = train_tiles(nseq, S, self.hq, self.hkv, self.d, self.dev)
+        return self._tiles[key]
+
+    # -------------------------------------------------------------------------- layer forward
+    def _layer_fwd(self, l: int, x, res, T: int, pos, *, tiles, kbuf, vbuf, kv_slot=None,
+                   q_view=None, lse=None, s_in_out=None, keep: dict | None = None, tag: str = "f"):
+        """One decoder layer.  ``x`` + ``res`` -> (mlp_out, s_mid).  When ``res`` is None, ``x`` is
+        already the residual stream.  ``keep`` receives the intermediates backward needs."""
+        w, ws, H = self.p.w, self.ws, self.spec.hidden_size
+        eps = self.spec.rms_norm_eps
+        h = ws.get(f"{tag}.h", (T, H))
+        if res is None:
+            s_in = x
+            nv.rmsnorm_fwd(s_in, w[f"l{l}.ln1"], h, eps)
+        else:
+            s_in = s_in_out if s_in_out is not None else ws.get(f"{tag}.s_in", (T, H))
+            nv.rmsnorm_fwd(x, w[f"l{l}.ln1"], h, eps, res=res, res_out=s_in)
+        qkv = ws.get(f"{tag}.qkv", (T, self.p.qkv_local))
+        self._gemm(h, w[f"l{l}.wqkv"], qkv)
+        q = ws.get(f"{tag}.q", (T, self.p.q_local))
+        nv.qk_norm_rope_fwd(qkv, w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos, q, kbuf, vbuf,
+                            Hq=self.hq, Hkv=self.hkv, eps=eps, kv_slot=kv_slot)
+        attn = ws.get(f"{tag}.attn", (T, self.p.q_local))
+        qv = q if q_view is None else q.view(*q_view)
+        ov = attn if q_view is None else attn.view(*q_view)
+        self._attention(qv, kbuf, vbuf, ov, lse, tiles)
+        o = ws.get(f"{tag}.o", (T, H))
+        self._gemm(attn, w[f"l{l}.wo"], o, nchunks=self.nchunks)
+        self.ctx.tp_all_reduce_(o)
+        s_mid = ws.get(f"{tag}.s_mid", (T, H))
+        h2 = ws.get(f"{tag}.h2", (T, H))
+        nv.rmsnorm_fwd(o, w[f"l{l}.ln2"], h2, eps, res=s_in, res_out=s_mid)
+        gu = ws.get(f"{tag}.gu", (T, 2 * self.p.i_local))
+        self._gemm(h2, w[f"l{l}.wgu"], gu)
+        act = ws.get(f"{tag}.act", (T, self.p.i_local))
+        nv.swiglu_fwd(gu, act, self.p.i_local, self.blk)
+        down = ws.get(f"{tag}.down", (T, H))
+        self._gemm(act, w[f"l{l}.wd"], down, nchunks=self.nchunks)
+        self.ctx.tp_all_reduce_(down)
+        if keep is not None:
+            keep.update(s_in=s_in, h=h, qkv=qkv, q=q, attn=attn, s_mid=s_mid, h2=h2, gu=gu, act=act)
+        return down, s_mid
+
+    def _attention(self, q2d, k2d, v2d, o2d, lse, tiles):
+        nv.attn_fwd(q2d, [k2d], [v2d], o2d, lse, tiles, self.scale)
+
+    # -------------------------------------------------------------------------- full forward
+    def forward_hidden(self, tokens: torch.Tensor, *, save: TrainState | None = None,
+                       kv: KVCache | None = None) -> torch.Tensor:
+        """tokens [nseq, S] -> final-norm hidden [nseq*S, H].  With ``kv`` the K/V of every layer are
+        written into the cache (prefill); with ``save`` layer inputs are checkpointed for backward."""
+        nseq, S = tokens.shape
+        T, H, L = nseq * S, self.spec.hidden_size, self.spec.num_hidden_layers
+        ws = self.ws
+        pos = ws.get("pos", (T,), torch.int32)
+        pos.copy_(torch.arange(S, device=self.dev, dtype=torch.int32).repeat(nseq))
+        tiles, _ = self._tiles_for(nseq, S)
+        x = ws.get("f.embed", (T, H))
+        nv.embedding_fwd(tokens.reshape(-1), self.p.w["embed"], x, self.p.vocab_start)
+        self.ctx.tp_all_reduce_(x)
+        if kv is not None:
+            slot = ws.get("pf.slot", (T,), torch.int32)
+            slot.copy_((torch.arange(nseq, device=self.dev, dtype=torch.int32) * kv.max_len)
+                       .repeat_interleave(S) + pos)
+        res = None
+        for l in range(L):
+            if kv is not None:
+                # prefill: K/V go to the cache; attention reads them back from there
+                ptiles = self._prefill_tiles(nseq, S, kv.max_len)
+                x, res = self._layer_fwd(l, x, res, T, pos, tiles=ptiles, kbuf=kv.k[l], vbuf=kv.v[l],
+                                         kv_slot=slot)
+            else:
+                kb = ws.get("f.k", (T, self.p.kv_local))
+                vb = ws.get("f.v", (T, self.p.kv_local))
+                s_out = save.ckpt[l] if save is not None else None
+                if save is not None and l == 0:
+                    save.ckpt[0].copy_(x)
+                    x = save.ckpt[0]
+                x, res = self._layer_fwd(l, x, res, T, pos, tiles=tiles, kbuf=kb, vbuf=vb,
+                                         s_in_out=s_out if l > 0 else None)
+        hf = ws.get("f.hf", (T, H))
+        s_fin = ws.get("f.s_fin", (T, H))
+        nv.rmsnorm_fwd(x, self.p.w["norm"], hf, self.spec.rms_norm_eps, res=res, res_out=s_fin)
+        if save is not None:
+            save.final_s = s_fin
+        return hf
+
+    def _prefill_tiles(self, nseq: int, S: int, max_len: int):
+        key = ("prefill", nseq, S, max_len)
+        if key not in self._tiles:
+            fw, _ = train_tiles(nseq, S, self.hq, self.hkv, self.d, self.dev)
+            fw = fw.clone()
+            b = torch.div(fw[:, 3], S, rounding_mode="floor")
+            fw[:, 3] = b * max_len          # kv_row0 inside the cache
+            self._tiles[key] = (fw.contiguous(), None)
+        return self._tiles[key][0]
+
+    # -------------------------------------------------------------------------- log-probs
+    def logp_from_hidden(self, hf: torch.Tensor, targets: torch.Tensor, *, temperature: float = 1.0,
+                         chunk: int = 8192, want_lse: bool = False):
+        """Selected-token log-prob of ``targets`` [R] from final hidden rows ``hf`` [R, H] through the
+        fused LM-head epilogue; the [R, V] logits are never written."""
+        R = hf.shape[0]
+        ntile = self.spec.num_vocab_tiles
+        logp = torch.empty(R, dtype=torch.float32, device=self.dev)
+        lse = torch.empty(R, dtype=torch.float32, device=self.dev) if want_lse else None
+        for r0 in range(0, R, chunk):
+            r1 = min(R, r0 + chunk)
+            stats, tl = self._lmhead_stats(hf[r0:r1], targets[r0:r1], temperature, None)
+            nv.logp_merge(stats, tl, logp[r0:r1], lse[r0:r1] if want_lse else None)
+        return (logp, lse) if want_lse else logp
+
+    def _lmhead_stats(self, hrows, targets, temperature, logits_out):
+        n = hrows.shape[0]
+        ntile = self.spec.num_vocab_tiles
+        tp = self.ctx.tp_size
+        stats = self.ws.get("lm.stats", (n, ntile, 2), torch.float32)
+        tl = self.ws.get("lm.tl", (n,), torch.float32)
+        if tp > 1:
+            stats.fill_(float("-inf"))
+            stats[..., 1] = 0
+            tl.zero_()
+        w = self.p.w["lm_head"][: self.p.v_real_local] if self.p.v_real_local < self.p.v_local else self.p.w["lm_head"]
+        if self.p.v_real_local < self.p.v_local:
+            # tiles that are entirely padding keep (-inf, 0)
+            stats[:, (self.p.vocab_start + self.p.v_real_local + VOCAB_TILE - 1) // VOCAB_TILE:] = \
+                torch.tensor([float("-inf"), 0.0], device=self.dev)
+        if self.p.v_real_local > 0:
+            nv.lmhead_logp_stats(hrows, w, targets, stats, tl, vocab_start=self.p.vocab_start,
+                                 inv_temp=1.0 / temperature, logits_out=logits_out)
+        if tp > 1:
+            # every rank filled only its own tiles / target: combine (exact: disjoint support)
+            per = ntile // tp
+            g = self.ctx.tp_all_gather(stats[:, self.ctx.tp_rank * per:(self.ctx.tp_rank + 1) * per].contiguous())
+            stats = g.permute(1, 0, 2, 3).reshape(n, ntile, 2).contiguous()
+            tl = self.ctx.tp_all_gather(tl).sum(0)
+        return stats, tl
+
+    # -------------------------------------------------------------------------- training step pieces
+    def new_train_state(self, nseq: int, S: int) -> TrainState:
+        T, H, L = nseq * S, self.spec.hidden_size, self.spec.num_hidden_layers
+        return TrainState(nseq, S, self.ws.get("ckpt", (L, T, H)))
+
+    def train_forward_backward(self, tokens: torch.Tensor, resp_start: int, dlogp_fn, *,
+                               temperature: float = 1.0, lm_chunk: int = 4096):
+        """One micro-batch: forward with checkpoints, LM head + log-probs on response positions,
+        ``dlogp_fn(logp [nseq, R]) -> dlogp [nseq, R]`` supplies d(loss)/d(logp), then the full
+        backward accumulates into ``params.grad``.  Returns logp [nseq, R] (fp32).
+
+        Position t predicts token t+1; response tokens are ``tokens[:, resp_start:]``, so rows
+        ``resp_start-1 .. S-2`` are scored.
+        """
+        nseq, S = tokens.shape
+        R = S - resp_start
+        H = self.spec.hidden_size
+        st = self.new_train_state(nseq, S)
+        hf = self.forward_hidden(tokens, save=st)
+        hf3 = hf.view(nseq, S, H)
+        rows = self.ws.get("lm.rows", (nseq * R, H))
+        rows.view(nseq, R, H).copy_(hf3[:, resp_start - 1:S - 1])
+        targets = tokens[:, resp_start:].reshape(-1).contiguous()
+        # ---- pass 1: log-probs (fused stats, logits not kept)
+        logp, lse = self.logp_from_hidden(rows, targets, temperature=temperature, want_lse=True)
+        dlogp = dlogp_fn(logp.view(nseq, R)).reshape(-1).contiguous()
+        # ---- pass 2: per chunk, logits -> dlogits -> dH, dW
+        drows = self.ws.get("lm.drows", (nseq * R, H))
+        vloc = self.p.v_real_local
+        wlm = self.p.w["lm_head"][:vloc]
+        glm = self.p.g["lm_head"][:vloc]
+        for r0 in range(0, nseq * R, lm_chunk):
+            r1 = min(nseq * R, r0 + lm_chunk)
+            n = r1 - r0
+            logits = self.ws.get("lm.logits", (lm_chunk, vloc))[:n]
+            if vloc > 0:
+                self._gemm(rows[r0:r1], wlm, logits)
+                nv.dlogits_(logits, targets[r0:r1], lse[r0:r1], dlogp[r0:r1],
+                            vocab_start=self.p.vocab_start, inv_temp=1.0 / temperature)
+                self._gemm(logits, wlm, drows[r0:r1], b_mn=True, M=n, N=H, K=vloc)
+                self._gemm(logits, rows[r0:r1], glm, a_mn=True, b_mn=True, accumulate=True,
+                           M=vloc, N=H, K=n)
+            else:
+                drows[r0:r1].zero_()
+        self.ctx.tp_all_reduce_(drows)
+        dhf = self.ws.get("b.dhf", (nseq * S, H))
+        dhf.zero_()
+        dhf.view(nseq, S, H)[:, resp_start - 1:S - 1].copy_(drows.view(nseq, R, H))
+        self._backward(st, tokens, dhf)
+        return logp.view(nseq, R)
+
+    def _backward(self, st: TrainState, tokens: torch.Tensor, dhf: torch.Tensor) -> None:
+        spec, w, g, ws = self.spec, self.p.w, self.p.g, self.ws
+        nseq, S = st.nseq, st.S
+        T, H, L = nseq * S, spec.hidden_size, spec.num_hidden_layers
+        eps = spec.rms_norm_eps
+        pos = ws.get("pos", (T,), torch.int32)
+        tiles, kvtiles = self._tiles_for(nseq, S)
+        scr = ws.get("b.scr", (max(nv.rmsnorm_bwd_scratch_elems(T, H), nv.qk_norm_rope_bwd_scratch_elems(T)),),
+                     torch.float32)
+        ds = ws.get("b.ds", (T, H))          # gradient of the residual stream
+        # final norm: s_fin -> hf
+        nv.rmsnorm_bwd(st.final_s, w["norm"], dhf, ds, scr, eps, dw_bf16=g["norm"], accumulate_dw=True)
+        lse = ws.get("b.lse", (T, self.hq), torch.float32)
+        delta = ws.get("b.delta", (T, self.hq), torch.float32)
+        for l in range(L - 1, -1, -1):
+            keep: dict = {}
+            kb = ws.get("f.k", (T, self.p.kv_local))
+            vb = ws.get("f.v", (T, self.p.kv_local))
+            # ---- recompute the layer from its checkpointed input
+            self._layer_fwd(l, st.ckpt[l], None, T, pos, tiles=tiles, kbuf=kb, vbuf=vb, lse=lse,
+                            keep=keep, tag="r")
+            # ---- MLP backward.  s_out = s_mid + down  =>  d(down) = ds, d(s_mid) += ds
+            dact = ws.get("b.dact", (T, self.p.i_local))
+            self._gemm(ds, w[f"l{l}.wd"], dact, b_mn=True, M=T, N=self.p.i_local, K=H)
+            self._gemm(ds, keep["act"], g[f"l{l}.wd"], a_mn=True, b_mn=True, accumulate=True,
+                       M=H, N=self.p.i_local, K=T)
+            dgu = ws.get("b.dgu", (T, 2 * self.p.i_local))
+            nv.swiglu_bwd(keep["gu"], dact, dgu, self.p.i_local, self.blk)
+            dh2 = ws.get("b.dh", (T, H))
+            self._gemm(dgu, w[f"l{l}.wgu"], dh2, b_mn=True, nchunks=self.nchunks, M=T, N=H,
+                       K=2 * self.p.i_local)
+            self.ctx.tp_all_reduce_(dh2)
+            self._gemm(dgu, keep["h2"], g[f"l{l}.wgu"], a_mn=True, b_mn=True, accumulate=True,
+                       M=2 * self.p.i_local, N=H, K=T)
+            ds2 = ws.get("b.ds2", (T, H))
+            nv.rmsnorm_bwd(keep["s_mid"], w[f"l{l}.ln2"], dh2, ds2, scr, eps, dres=ds,
+                           dw_bf16=g[f"l{l}.ln2"], accumulate_dw=True)
+            # ---- attention block backward.  s_mid = s_in + o  =>  d(o) = ds2
+            dattn = ws.get("b.dattn", (T, self.p.q_local))
+            self._gemm(ds2, w[f"l{l}.wo"], dattn, b_mn=True, M=T, N=self.p.q_local, K=H)
+            self._gemm(ds2, keep["attn"], g[f"l{l}.wo"], a_mn=True, b_mn=True, accumulate=True,
+                       M=H, N=self.p.q_local, K=T)
+            nv.attn_bwd_delta(keep["attn"], dattn, delta, T, self.hq)
+            dq = ws.get("b.dq", (T, self.p.q_local))
+            dk = ws.get("b.dk", (T, self.p.kv_local))
+            dv = ws.get("b.dv", (T, self.p.kv_local))
+            nv.attn_bwd_dq(keep["q"], dattn, kb, vb, lse, delta, dq, tiles, self.scale)
+            nv.attn_bwd_dkv(keep["q"], dattn, kb, vb, lse, delta, dk, dv, kvtiles, self.scale)
+            dqkv = ws.get("b.dqkv", (T, self.p.qkv_local))
+            nv.qk_norm_rope_bwd(keep["qkv"], w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos,
+                                dq, dk, dv, dqkv, scr, g[f"l{l}.qn"], g[f"l{l}.kn"], Hq=self.hq,
+                                Hkv=self.hkv, eps=eps, accumulate_dw=True)
+            dh = ws.get("b.dh", (T, H))
+            self._gemm(dqkv, w[f"l{l}.wqkv"], dh, b_mn=True, nchunks=self.nchunks, M=T, N=H,
+                       K=self.p.qkv_local)
+            self.ctx.tp_all_reduce_(dh)
+            self._gemm(dqkv, keep["h"], g[f"l{l}.wqkv"], a_mn=True, b_mn=True, accumulate=True,
+                       M=self.p.qkv_local, N=H, K=T)
+            nv.rmsnorm_bwd(st.ckpt[l], w[f"l{l}.ln1"], dh, ds, scr, eps, dres=ds2,
+                           dw_bf16=g[f"l{l}.ln1"], accumulate_dw=True)
+        # ---- embedding
+        sid, order = torch.sort(tokens.reshape(-1), stable=True)
+        nv.embedding_bwd(sid.contiguous(), order.contiguous(), ds, g["embed"], self.p.vocab_start)
+
+    # -------------------------------------------------------------------------- rollout
+    def new_kv_cache(self, nseq: int, max_len: int) -> KVCache:
+        L = self.spec.num_hidden_layers
+        k = [torch.zeros(nseq * max_len, self.p.kv_local, dtype=BF16, device=self.dev) for _ in range(L)]
+        v = [torch.zeros(nseq * max_len, self.p.kv_local, dtype=BF16, device=self.dev) for _ in range(L)]
+        return KVCache(k, v, nseq, max_len)
+
+    def decode_tiles(self, nseq: int, max_len: int) -> torch.Tensor:
+        """Static part of the decode tile table; columns 5 (pos0) and 7 (kv_cap) change per step."""
+        g = self.hq // self.hkv
+        b = torch.arange(nseq).view(-1, 1)
+        hk = torch.arange(self.hkv).view(1, -1)
+        z = torch.zeros(nseq, self.hkv, dtype=torch.long)
+        row0 = b * self.hq + hk * g + z
+        t = torch.stack([row0, z, z + g, b * max_len + z, hk * self.d + z, z, z, z + 1, row0, z + 1, z, z],
+                        dim=-1).reshape(-1, 12)
+        return t.to(torch.int32).to(self.dev).contiguous()
+
+    def decode_step(self, tokens: torch.Tensor, pos: torch.Tensor, kv: KVCache, tiles: torch.Tensor
+                    ) -> torch.Tensor:
+        """One token per sequence: tokens [B] at positions ``pos`` [B] (int32) -> final hidden [B, H].
+        ``tiles`` comes from ``decode_tiles``; this call refreshes its position columns on the
+        device, so the whole step can be captured in a CUDA graph."""
+        B, H, L = tokens.shape[0], self.spec.hidden_size, self.spec.num_hidden_layers
+        ws = self.ws
+        tiles[:, 5] = pos.repeat_interleave(self.hkv)
+        tiles[:, 7] = tiles[:, 5] + 1
+        slot = ws.get("d.slot", (B,), torch.int32)
+        torch.add(torch.arange(B, device=self.dev, dtype=torch.int32) * kv.max_len, pos, out=slot)
+        x = ws.get("d.embed", (B, H))
+        nv.embedding_fwd(tokens, self.p.w["embed"], x, self.p.vocab_start)
+        self.ctx.tp_all_reduce_(x)
+        res = None
+        for l in range(L):
+            x, res = self._layer_fwd(l, x, res, B, pos, tiles=tiles, kbuf=kv.k[l], vbuf=kv.v[l],
+                                     kv_slot=slot, q_view=(B * self.hq, self.d), tag="d")
+        hf = ws.get("d.hf", (B, H))
+        s_fin = ws.get("d.s_fin", (B, H))
+        nv.rmsnorm_fwd(x, self.p.w["norm"], hf, self.spec.rms_norm_eps, res=res, res_out=s_fin)
+        return hf
+
+    def logits(self, hf: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Local-vocab-shard logits [rows, v_real_local] (bf16)."""
+        n = hf.shape[0]
+        vloc = self.p.v_real_local
+        if out is None:
+            out = self.ws.get("d.logits", (n, vloc))
+        self._gemm(hf, self.p.w["lm_head"][:vloc], out)
+        return out
+
+    def sample(self, logits: torch.Tensor, row_keys: torch.Tensor, *, temperature: float, seed: int,
+               greedy: bool = False):
+        """Sample one id per row and return (ids, logp of the sampled id under the same temperature),
+        the log-prob computed with the tile contract shared with the training path."""
+        n = logits.shape[0]
+        ids = self.ws.get("s.ids", (n,), torch.int64)
+        val = self.ws.get("s.val", (n,), torch.float32)
+        nv.sample_gumbel(logits, ids, val, vocab_start=self.p.vocab_start, inv_temp=1.0 / temperature,
+                         seed=seed, step=0, greedy=greedy, row_keys=row_keys)
+        if self.ctx.tp_size > 1:
+            vals = self.ctx.tp_all_gather(val)           # [tp, n]
+            idss = self.ctx.tp_all_gather(ids)
+            best = vals.argmax(0, keepdim=True)          # ties: lowest rank = lowest ids
+            ids = idss.gather(0, best)[0].contiguous()
+        ntile = self.spec.num_vocab_tiles
+        stats = self.ws.get("s.stats", (n, ntile, 2), torch.float32)
+        tl = self.ws.get("s.tl", (n,), torch.float32)
+        stats[..., 0] = float("-inf")
+        stats[..., 1] = 0
+        tl.zero_()
+        nv.logits_tile_stats(logits, ids, stats, tl, vocab_start=self.p.vocab_start,
+                             inv_temp=1.0 / temperature)
+        if self.ctx.tp_size > 1:
+            per = ntile // self.ctx.tp_size
+            gs = self.ctx.tp_all_gather(stats[:, self.ctx.tp_rank * per:(self.ctx.tp_rank + 1) * per].contiguous())
+            stats = gs.permute(1, 0, 2, 3).reshape(n, ntile, 2).contiguous()
+            tl = self.ctx.tp_all_gather(tl).sum(0)
+        logp = self.ws.get("s.logp", (n,), torch.float32)
+        nv.logp_merge(stats, tl, logp, None)
+        return ids, logp

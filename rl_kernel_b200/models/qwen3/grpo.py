@@ -1,0 +1,275 @@
+"""A complete GRPO step on the sm_100a engine: weight publish -> rollout (prefill + CUDA-graph
+decode with sampling) -> rewards/advantages -> reference log-probs -> training forward/backward
+over micro-batches -> gradient clipping -> AdamW, plus the train-vs-rollout log-prob mismatch
+counter that is the product's acceptance metric
+(reports/archive/experiments/dense/convergence_s1234_g10_g11/README.md:16-24 in the reference).
+
+The rollout engine and the trainer share the kernels but not the call pattern: rollout runs one
+token per sequence against a KV cache, training runs packed full sequences; their selected-token
+log-probs must be bitwise equal.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from rl_kernel_b200.backends import native as nv
+from rl_kernel_b200.models.qwen3.engine import PackedParams, ParallelContext, Qwen3Engine
+from rl_kernel_b200.models.qwen3.spec import Qwen3DenseSpec
+from rl_kernel_b200.utils.bits import bit_mismatch_count
+
+
+@dataclass
+class GRPOConfig:
+    num_prompts: int = 8
+    group_size: int = 8
+    prompt_len: int = 512
+    response_len: int = 1024
+    temperature: float = 1.0
+    clip_eps: float = 0.2
+    kl_coef: float = 0.001
+    lr: float = 1e-6
+    beta1: float = 0.9
+    beta2: float = 0.95
+    adam_eps: float = 1e-8
+    weight_decay: float = 0.01
+    max_grad_norm: float = 1.0
+    micro_batch_seqs: int = 8
+    seed: int = 1234
+    use_cuda_graph: bool = True
+    use_reference_model: bool = True
+
+    @property
+    def num_seqs(self) -> int:
+        return self.num_prompts * self.group_size
+
+    @property
+    def seq_len(self) -> int:
+        return self.prompt_len + self.response_len
+
+
+class AdamW:
+    """Fused AdamW over the flat parameter shard with fp32 master weights and exact,
+    partition-independent gradient-norm clipping."""
+
+    def __init__(self, params: PackedParams, cfg: GRPOConfig, ctx: ParallelContext):
+        self.p, self.cfg, self.ctx = params, cfg, ctx
+        n, dev = params.numel, params.device
+        self.master = params.flat.float()
+        self.m = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.v = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.bins = torch.zeros(256, dtype=torch.int64, device=dev)
+        self.scale = torch.ones(1, dtype=torch.float32, device=dev)
+        self.step_count = 0
+        e = torch.arange(256, device=dev).clamp(min=1).double()
+        self._bin_w = torch.pow(2.0, 2.0 * (e - 134.0))
+        self._bin_w[255] = 0.0
+        self.last_grad_norm = torch.zeros(1, dtype=torch.float64, device=dev)
+
+    def grad_norm(self) -> torch.Tensor:
+        """Exact global L2 norm of the bf16 gradient: integer bins per shard, integer all-reduce,
+        one fixed-order fp64 combination.  Replicated parameters are counted once."""
+        self.bins.zero_()
+        if self.ctx.tp_size == 1:
+            nv.sumsq_bins(self.p.grad, self.bins)
+        else:
+            for name, s in self.p.slots.items():
+                if self.p.is_replicated(name) and self.ctx.tp_rank != 0:
+                    continue
+                nv.sumsq_bins(self.p.grad[s.offset:s.offset + s.numel], self.bins)
+            self.ctx.collective.all_reduce_int_(self.bins)
+        return (self.bins.double() * self._bin_w).sum().sqrt()
+
+    def step(self) -> None:
+        c = self.cfg
+        self.step_count += 1
+        gn = self.grad_norm()
+        self.last_grad_norm.copy_(gn.reshape(1))
+        if c.max_grad_norm > 0:
+            self.scale.copy_(torch.clamp(c.max_grad_norm / (gn + 1e-6), max=1.0).float().reshape(1))
+        nv.adamw(self.master, self.m, self.v, self.p.grad, self.p.flat, lr=c.lr, beta1=c.beta1,
+                 beta2=c.beta2, eps=c.adam_eps, weight_decay=c.weight_decay, step=self.step_count,
+                 grad_scale=self.scale)
+
+
+class GRPOTrainer:
+    """Owns the policy (with gradients and optimizer), the frozen reference policy and the rollout
+    state of one rank."""
+
+    def __init__(self, spec: Qwen3DenseSpec, cfg: GRPOConfig, device: torch.device,
+                 ctx: ParallelContext | None = None, weights=None):
+        self.spec, self.cfg, self.dev = spec, cfg, device
+        self.ctx = ctx or ParallelContext()
+        tp_r, tp = self.ctx.tp_rank, self.ctx.tp_size
+        self.policy = PackedParams(spec, tp_r, tp, device, with_grad=True)
+        if weights is not None:
+            self.policy.load(weights)
+        else:
+            self.policy.init_synthetic_(cfg.seed)
+        self.engine = Qwen3Engine(spec, self.policy, self.ctx, max_positions=cfg.seq_len + 8)
+        self.ref_params = None
+        if cfg.use_reference_model and cfg.kl_coef > 0:
+            self.ref_params = PackedParams(spec, tp_r, tp, device)
+            self.ref_params.flat.copy_(self.policy.flat)
+        # rollout weights: a separate buffer that receives every published version
+        self.rollout_params = PackedParams(spec, tp_r, tp, device)
+        self.rollout_engine = Qwen3Engine(spec, self.rollout_params, self.ctx, max_positions=cfg.seq_len + 8)
+        self.rollout_engine.ws = self.engine.ws      # rollout and training never overlap in time
+        self.rollout_engine.cos, self.rollout_engine.sin = self.engine.cos, self.engine.sin
+        self.weight_version = 0
+        self.opt = AdamW(self.policy, cfg, self.ctx)
+        self._graph = None
+        self._kv = None
+        self.metrics: dict[str, float] = {}
+
+    # ---------------------------------------------------------------- weight sync
+    def publish_weights(self) -> int:
+        """Train -> rollout weight sync: one device copy of the flat shard; monotonic version."""
+        self.rollout_params.flat.copy_(self.policy.flat)
+        self.weight_version += 1
+        return self.weight_version
+
+    # ---------------------------------------------------------------- rollout
+    def _ensure_rollout_state(self):
+        c = self.cfg
+        if self._kv is None:
+            B = c.num_seqs
+            eng = self.rollout_engine
+            self._kv = eng.new_kv_cache(B, c.seq_len)
+            self._pkv = eng.new_kv_cache(c.num_prompts, c.prompt_len)
+            self._dtiles = eng.decode_tiles(B, c.seq_len)
+            self._tok = torch.zeros(B, dtype=torch.int64, device=self.dev)
+            self._pos = torch.zeros(B, dtype=torch.int32, device=self.dev)
+            self._keys = torch.zeros(B, dtype=torch.int64, device=self.dev)
+            self._seq_key = torch.arange(B, dtype=torch.int64, device=self.dev) * 65536
+            self._out_tok = torch.zeros(B, c.response_len, dtype=torch.int64, device=self.dev)
+            self._out_lp = torch.zeros(B, c.response_len, dtype=torch.float32, device=self.dev)
+            self._col = torch.zeros(1, dtype=torch.int64, device=self.dev)
+
+    def _decode_once(self, seed: int):
+        """tok[B] at pos[B] -> next token + its logp, appended at column `col`; advances state."""
+        eng, c = self.rollout_engine, self.cfg
+        hf = eng.decode_step(self._tok, self._pos, self._kv, self._dtiles)
+        logits = eng.logits(hf)
+        torch.add(self._seq_key, self._pos, out=self._keys)
+        ids, lp = eng.sample(logits, self._keys, temperature=c.temperature, seed=seed)
+        col = self._col.expand(ids.shape[0]).unsqueeze(1)
+        self._out_tok.scatter_(1, col, ids.unsqueeze(1))
+        self._out_lp.scatter_(1, col, lp.unsqueeze(1))
+        self._tok.copy_(ids)
+        self._pos.add_(1)
+        self._col.add_(1)
+
+    @torch.no_grad()
+    def rollout(self, prompts: torch.Tensor, step_seed: int):
+        """prompts [num_prompts, prompt_len] -> (tokens [B, S], logp [B, R]); B = prompts x group."""
+        c, eng = self.cfg, self.rollout_engine
+        self._ensure_rollout_state()
+        B, P, R, G = c.num_seqs, c.prompt_len, c.response_len, c.group_size
+        # ---- prefill each distinct prompt once, then share its KV with the whole group
+        hf = eng.forward_hidden(prompts, kv=self._pkv)
+        H = self.spec.hidden_size
+        last = hf.view(c.num_prompts, P, H)[:, P - 1].repeat_interleave(G, dim=0).contiguous()
+        for l in range(self.spec.num_hidden_layers):
+            for src, dst in ((self._pkv.k[l], self._kv.k[l]), (self._pkv.v[l], self._kv.v[l])):
+                d3 = dst.view(c.num_prompts, G, c.seq_len, -1)
+                d3[:, :, :P].copy_(src.view(c.num_prompts, 1, P, -1).expand(-1, G, -1, -1))
+        # ---- first response token comes from the prefill logits
+        self._pos.fill_(P - 1)
+        self._col.zero_()
+        logits = eng.logits(last)
+        torch.add(self._seq_key, self._pos, out=self._keys)
+        ids, lp = eng.sample(logits, self._keys, temperature=c.temperature, seed=step_seed)
+        self._out_tok[:, 0].copy_(ids)
+        self._out_lp[:, 0].copy_(lp)
+        self._tok.copy_(ids)
+        self._pos.fill_(P)
+        self._col.fill_(1)
+        # ---- decode R-1 more tokens
+        if c.use_cuda_graph:
+            if self._graph is None:
+                # warm-up outside capture (allocations, attribute setting), then capture one step
+                snap = (self._tok.clone(), self._pos.clone(), self._col.clone())
+                s = torch.cuda.Stream(self.dev)
+                s.wait_stream(torch.cuda.current_stream(self.dev))
+                with torch.cuda.stream(s):
+                    self._decode_once(step_seed)
+                torch.cuda.current_stream(self.dev).wait_stream(s)
+                self._tok.copy_(snap[0]); self._pos.copy_(snap[1]); self._col.copy_(snap[2])
+                self._graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(self._graph):
+                    self._decode_once(step_seed)
+                self._tok.copy_(snap[0]); self._pos.copy_(snap[1]); self._col.copy_(snap[2])
+            for _ in range(R - 1):
+                self._graph.replay()
+        else:
+            for _ in range(R - 1):
+                self._decode_once(step_seed)
+        tokens = torch.cat([prompts.repeat_interleave(G, dim=0), self._out_tok], dim=1).contiguous()
+        return tokens, self._out_lp.clone()
+
+    # ---------------------------------------------------------------- scoring with frozen weights
+    @torch.no_grad()
+    def score(self, params: PackedParams, tokens: torch.Tensor) -> torch.Tensor:
+        """Selected-token log-probs of the response tokens under ``params`` (no gradients)."""
+        c = self.cfg
+        eng = self.engine
+        saved = eng.p
+        eng.p = params
+        try:
+            out = []
+            for b0 in range(0, tokens.shape[0], c.micro_batch_seqs):
+                tk = tokens[b0:b0 + c.micro_batch_seqs]
+                n, S = tk.shape
+                hf = eng.forward_hidden(tk).view(n, S, -1)
+                rows = hf[:, c.prompt_len - 1:S - 1].reshape(n * c.response_len, -1).contiguous()
+                lp = eng.logp_from_hidden(rows, tk[:, c.prompt_len:].reshape(-1).contiguous(),
+                                          temperature=c.temperature)
+                out.append(lp.view(n, c.response_len).clone())
+            return torch.cat(out)
+        finally:
+            eng.p = saved
+
+    # ---------------------------------------------------------------- one full step
+    def step(self, prompts: torch.Tensor, rewards_fn=None, step_index: int = 0) -> dict:
+        c = self.cfg
+        B, R = c.num_seqs, c.response_len
+        self.publish_weights()
+        tokens, old_logp = self.rollout(prompts, step_seed=c.seed + 7919 * step_index)
+        if rewards_fn is None:
+            gen = torch.Generator(device=self.dev).manual_seed(c.seed + step_index)
+            rewards = torch.bernoulli(torch.full((B,), 0.5, device=self.dev), generator=gen)
+        else:
+            rewards = rewards_fn(tokens).float()
+        adv = nv.group_advantages(rewards.contiguous(), c.num_prompts, c.group_size, 1e-6)
+        mask = torch.ones(B, R, dtype=torch.uint8, device=self.dev)
+        ref_logp = self.score(self.ref_params, tokens) if self.ref_params is not None else None
+        total_active = float(B * R)
+        self.policy.grad.zero_()
+        train_logp = torch.empty(B, R, dtype=torch.float32, device=self.dev)
+        loss_terms = []
+        for b0 in range(0, B, c.micro_batch_seqs):
+            b1 = min(B, b0 + c.micro_batch_seqs)
+
+            def dlogp_fn(lp, b0=b0, b1=b1):
+                r = nv.grpo_loss(lp.contiguous(), old_logp[b0:b1].contiguous(),
+                                 ref_logp[b0:b1].contiguous() if ref_logp is not None else None,
+                                 adv[b0:b1].contiguous(), mask[b0:b1].contiguous(), clip_lo=c.clip_eps,
+                                 clip_hi=c.clip_eps, beta=c.kl_coef, inv_norm=1.0 / total_active,
+                                 want_tokens=False)
+                loss_terms.append(r["totals"])
+                return r["dlogp"]
+
+            lp = self.engine.train_forward_backward(tokens[b0:b1], c.prompt_len, dlogp_fn,
+                                                    temperature=c.temperature)
+            train_logp[b0:b1].copy_(lp)
+        self.opt.step()
+        tot = torch.stack(loss_terms).sum(0)
+        return {"tokens": tokens, "old_logp": old_logp, "train_logp": train_logp, "rewards": rewards,
+                "loss_sums": tot, "grad_norm": self.opt.last_grad_norm, "total_active": total_active}
+
+    @staticmethod
+    def mismatch_count(train_logp: torch.Tensor, rollout_logp: torch.Tensor) -> int:
+        return bit_mismatch_count(train_logp, rollout_logp)

@@ -1,0 +1,35 @@
+"""Shared definitions: masked reductions, the plain selected-log-prob gold and drift summaries
+(parity: rl_engine/reference/definitions.py:15-142)."""
+from __future__ import annotations
+
+import torch
+
+
+def masked_mean(x: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    m = mask.to(x.dtype)
+    return (x * m).sum() / m.sum().clamp_min(1.0)
+
+
+def selected_logprobs_reference(logits: torch.Tensor, token_ids: torch.Tensor, mask: torch.Tensor | None = None,
+                                output_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    lp = torch.log_softmax(logits.float(), dim=-1).gather(-1, token_ids.unsqueeze(-1).long()).squeeze(-1)
+    if mask is not None:
+        lp = lp.masked_fill(~mask.bool(), 0.0)
+    return lp.to(output_dtype)
+
+
+def summarize_kernel_drift(candidate: torch.Tensor, gold: torch.Tensor, mask: torch.Tensor | None = None) -> dict:
+    c, g = candidate.float(), gold.float()
+    diff = (c - g).abs()
+    if mask is not None:
+        m = mask.bool()
+        diff = diff[m]
+        c, g = c[m], g[m]
+    n = diff.numel()
+    if n == 0:
+        return {"count": 0, "max_abs_error": 0.0, "mean_abs_error": 0.0, "mismatch_count": 0,
+                "approx_kl": 0.0}
+    mism = int((c.view(torch.int32) != g.view(torch.int32)).sum().item())
+    d = g - c
+    return {"count": n, "max_abs_error": float(diff.max()), "mean_abs_error": float(diff.mean()),
+            "mismatch_count": mism, "approx_kl": float((torch.exp(d) - d - 1).mean())}
