@@ -1,0 +1,221 @@
+"""Headline benchmark: Qwen3-8B-shape GRPO step (rollout + reference scoring + train fwd/bwd +
+optimizer) tokens/s, with the train-vs-rollout log-prob mismatch count.
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+    python bench.py --impl reference ...     # the unmodified reference from baseline/_ref
+
+Weak scaling: every GPU brings 8 prompts x group 8 x (512 + 1024) tokens; N GPUs run TP=min(N,4)
+and, at N=8, CP... see ``parallel_plan``.  Data is synthetic (uniform-random prompt ids,
+Bernoulli(0.5) rewards), weights are random-init N(0, 0.02) of the official architecture.
+One JSON line is printed by rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
+PROMPTS_PER_GPU, GROUP, PROMPT_LEN, RESPONSE_LEN = 8, 8, 512, 1024
+METRIC = "qwen3_8b_grpo_step_tokens_per_s"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.rows, self.proc = gpu_index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        busy = sorted(sm)[len(sm) // 4:] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def parallel_plan(n: int) -> dict:
+    """TP inside a replica; at 8 GPUs the training replica is TP4 x CP2 and rollout runs two TP4
+    engines (the reference's headline topology)."""
+    if n == 1:
+        return {"tp": 1, "cp": 1, "name": "tp1"}
+    if n in (2, 4):
+        return {"tp": n, "cp": 1, "name": f"tp{n}"}
+    if n == 8:
+        return {"tp": 4, "cp": 2, "name": "tp4xcp2"}
+    raise SystemExit(f"--gpus must be 1, 2, 4 or 8 (got {n})")
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    from rl_kernel_b200.backends import native as nv
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec
+    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
+    from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"WORLD_SIZE={world} but --gpus {args.gpus}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    plan = parallel_plan(args.gpus)
+    ctx = build_parallel_context(plan["tp"], plan["cp"], dev)
+
+    spec = Qwen3DenseSpec.official()
+    if args.layers:
+        spec = spec.with_layers(args.layers)
+    cfg = GRPOConfig(num_prompts=PROMPTS_PER_GPU * args.gpus // max(1, ctx.dp_size), group_size=GROUP,
+                     prompt_len=PROMPT_LEN, response_len=args.response_len, micro_batch_seqs=args.micro_batch,
+                     share_rollout_weights=True, seed=1234)
+    trainer = GRPOTrainer(spec, cfg, dev, ctx=ctx)
+    n_prompts_global = PROMPTS_PER_GPU * args.gpus
+    tokens_per_step = n_prompts_global * GROUP * (PROMPT_LEN + args.response_len)
+
+    # per-step prompts live in pinned host memory; each step copies its own batch to the device
+    gen = torch.Generator().manual_seed(99)
+    total = args.warmup + args.steps
+    host_prompts = torch.randint(0, spec.vocab_size, (total, n_prompts_global, PROMPT_LEN), generator=gen,
+                                 dtype=torch.int64).pin_memory()
+    dev_prompts = torch.empty(n_prompts_global, PROMPT_LEN, dtype=torch.int64, device=dev)
+    host_result = torch.empty(8, dtype=torch.float32).pin_memory()
+    mismatches = 0
+    mism_tokens = 0
+
+    def one_step(i: int):
+        nonlocal mismatches, mism_tokens
+        dev_prompts.copy_(host_prompts[i], non_blocking=True)                      # H2D
+        out = trainer.step(trainer.local_prompts(dev_prompts), step_index=i)
+        mm = (out["train_logp"].view(torch.int32) != out["old_logp"].view(torch.int32)).sum()
+        res = torch.cat([out["loss_sums"][:4].float(), out["grad_norm"].float(), mm.float().reshape(1),
+                         torch.zeros(2, device=dev)])
+        host_result.copy_(res, non_blocking=True)                                   # D2H
+        torch.cuda.current_stream().synchronize()
+        mismatches += int(host_result[5].item())
+        mism_tokens += out["old_logp"].numel()
+        return float(host_result[0].item())
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        one_step(i)
+    mismatches, mism_tokens = 0, 0
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    n0 = nv.LAUNCH_COUNT
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    ev0.record()
+    for i in range(args.warmup, total):
+        one_step(i)
+    ev1.record()
+    barrier()
+    wall = time.perf_counter() - t0
+    dev_ms = ev0.elapsed_time(ev1)
+    clocks = sampler.stop() if rank == 0 else {}
+    launches = nv.LAUNCH_COUNT - n0
+    t = torch.tensor([dev_ms, wall * 1e3, float(mismatches)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, wall_ms, mismatches = float(t[0]), float(t[1]), int(t[2])
+    ms_per_step = dev_ms / args.steps
+    value = tokens_per_step / (ms_per_step / 1e3)
+    result = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random prompt ids, Bernoulli rewards, random-init weights)",
+        "impl": "rl_kernel_b200",
+        "config": {"model": "Qwen3-8B" if not args.layers else f"Qwen3-8B-shape-{args.layers}L",
+                   "global_batch": n_prompts_global * GROUP, "seq_len": PROMPT_LEN + args.response_len,
+                   "prompt_len": PROMPT_LEN, "response_len": args.response_len, "group_size": GROUP,
+                   "parallelism": plan["name"], "micro_batch_seqs": args.micro_batch,
+                   "l2_policy": "inputs larger than L2 (16 GB of weights stream every pass)",
+                   "includes": "weight publish, prefill, CUDA-graph decode+sampling, reference-policy scoring, "
+                               "train fwd/bwd with recompute, exact grad-norm clip, AdamW"},
+        "logp_mismatch_count": mismatches, "logp_tokens_compared": mism_tokens * (1 if world == 1 else 1),
+        "clocks": clocks,
+        "e2e": {"value": tokens_per_step * args.steps / (wall_ms / 1e3), "unit": "tokens/s",
+                "h2d_bytes_per_step": int(dev_prompts.numel() * 8), "d2h_bytes_per_step": int(host_result.numel() * 4),
+                "timing": "host wall clock around the same steps incl. H2D of prompts and D2H of loss"},
+        "gpu_launches": int(launches),
+    }
+    if world > 1:
+        dist.destroy_process_group()
+    return result if rank == 0 else {}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", choices=("ours", "reference"), default="ours")
+    ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the config)")
+    ap.add_argument("--response-len", type=int, default=RESPONSE_LEN, help="debug only")
+    ap.add_argument("--micro-batch", type=int, default=8)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        from baseline.reference_arm import run_reference
+
+        out = run_reference(args)
+    else:
+        out = run_ours(args)
+    if out:
+        print(json.dumps(out), flush=True)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -35,6 +35,8 @@ class ParallelContext:
         self.cp_rank, self.cp_size = cp_rank, cp_size
         self.collective = collective        # fixed-order TP collective (all_reduce_, all_gather)
         self.cp_collective = cp_collective
+        self.dp_size = 1                    # independent rollout engines (training always uses all ranks)
+        self.tp_group = self.cp_group = None
 
     def tp_all_reduce_(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp_size > 1:
@@ -209,17 +211,33 @@ def train_tiles(nseq: int, S: int, hq: int, hkv: int, d: int, device, *, q_pos0:
 
 # ------------------------------------------------------------------------------ workspace
 class Workspace:
-    """Named, shape-keyed scratch tensors that live for the lifetime of the engine."""
+    """Named, shape-keyed scratch tensors that live for the lifetime of the engine.
 
-    def __init__(self, device):
+    With an ``arena`` (one big uint8 tensor) the buffers whose names start with one of
+    ``arena_prefixes`` are carved out of it by a bump allocator instead of being allocated one by
+    one.  The GRPO trainer hands the same arena to the KV cache: rollout and training never run at
+    the same time, so the training activations reuse the cache's memory (the cache is re-zeroed
+    before every rollout)."""
+
+    def __init__(self, device, arena: torch.Tensor | None = None,
+                 arena_prefixes: tuple[str, ...] = ("f.", "r.", "b.", "lm.", "ckpt", "pos")):
         self.device = device
         self._bufs: dict[tuple, torch.Tensor] = {}
+        self.arena, self.arena_prefixes, self._off = arena, arena_prefixes, 0
 
     def get(self, name: str, shape: tuple[int, ...], dtype=BF16, zero: bool = False) -> torch.Tensor:
         key = (name, tuple(shape), dtype)
         t = self._bufs.get(key)
         if t is None:
-            t = (torch.zeros if zero else torch.empty)(shape, dtype=dtype, device=self.device)
+            nbytes = math.prod(shape) * torch.empty((), dtype=dtype).element_size()
+            if (self.arena is not None and name.startswith(self.arena_prefixes)
+                    and self._off + nbytes <= self.arena.numel()):
+                t = self.arena[self._off:self._off + nbytes].view(dtype).view(shape)
+                self._off = (self._off + nbytes + 255) // 256 * 256
+                if zero:
+                    t.zero_()
+            else:
+                t = (torch.zeros if zero else torch.empty)(shape, dtype=dtype, device=self.device)
             self._bufs[key] = t
         return t
 
@@ -237,6 +255,7 @@ class KVCache:
     v: list[torch.Tensor]
     nseq: int
     max_len: int
+    flat: torch.Tensor | None = None   # the single buffer behind k and v (for one-shot zeroing)
 
 
 @dataclass
@@ -334,20 +353,20 @@ class Qwen3Engine:
 
     # -------------------------------------------------------------------------- full forward
     def forward_hidden(self, tokens: torch.Tensor, *, save: TrainState | None = None,
-                       kv: KVCache | None = None) -> torch.Tensor:
+                       kv: KVCache | None = None, tag: str = "f") -> torch.Tensor:
         """tokens [nseq, S] -> final-norm hidden [nseq*S, H].  With ``kv`` the K/V of every layer are
         written into the cache (prefill); with ``save`` layer inputs are checkpointed for backward."""
         nseq, S = tokens.shape
         T, H, L = nseq * S, self.spec.hidden_size, self.spec.num_hidden_layers
         ws = self.ws
-        pos = ws.get("pos", (T,), torch.int32)
+        pos = ws.get("pos" if tag == "f" else f"{tag}.pos", (T,), torch.int32)
         pos.copy_(torch.arange(S, device=self.dev, dtype=torch.int32).repeat(nseq))
         tiles, _ = self._tiles_for(nseq, S)
-        x = ws.get("f.embed", (T, H))
+        x = ws.get(f"{tag}.embed", (T, H))
         nv.embedding_fwd(tokens.reshape(-1), self.p.w["embed"], x, self.p.vocab_start)
         self.ctx.tp_all_reduce_(x)
         if kv is not None:
-            slot = ws.get("pf.slot", (T,), torch.int32)
+            slot = ws.get(f"{tag}.slot", (T,), torch.int32)
             slot.copy_((torch.arange(nseq, device=self.dev, dtype=torch.int32) * kv.max_len)
                        .repeat_interleave(S) + pos)
         res = None
@@ -356,18 +375,18 @@ class Qwen3Engine:
                 # prefill: K/V go to the cache; attention reads them back from there
                 ptiles = self._prefill_tiles(nseq, S, kv.max_len)
                 x, res = self._layer_fwd(l, x, res, T, pos, tiles=ptiles, kbuf=kv.k[l], vbuf=kv.v[l],
-                                         kv_slot=slot)
+                                         kv_slot=slot, tag=tag)
             else:
-                kb = ws.get("f.k", (T, self.p.kv_local))
-                vb = ws.get("f.v", (T, self.p.kv_local))
+                kb = ws.get(f"{tag}.k", (T, self.p.kv_local))
+                vb = ws.get(f"{tag}.v", (T, self.p.kv_local))
                 s_out = save.ckpt[l] if save is not None else None
                 if save is not None and l == 0:
                     save.ckpt[0].copy_(x)
                     x = save.ckpt[0]
                 x, res = self._layer_fwd(l, x, res, T, pos, tiles=tiles, kbuf=kb, vbuf=vb,
-                                         s_in_out=s_out if l > 0 else None)
-        hf = ws.get("f.hf", (T, H))
-        s_fin = ws.get("f.s_fin", (T, H))
+                                         s_in_out=s_out if l > 0 else None, tag=tag)
+        hf = ws.get(f"{tag}.hf", (T, H))
+        s_fin = ws.get(f"{tag}.s_fin", (T, H))
         nv.rmsnorm_fwd(x, self.p.w["norm"], hf, self.spec.rms_norm_eps, res=res, res_out=s_fin)
         if save is not None:
             save.final_s = s_fin
@@ -540,11 +559,21 @@ class Qwen3Engine:
         nv.embedding_bwd(sid.contiguous(), order.contiguous(), ds, g["embed"], self.p.vocab_start)
 
     # -------------------------------------------------------------------------- rollout
-    def new_kv_cache(self, nseq: int, max_len: int) -> KVCache:
+    def kv_cache_bytes(self, nseq: int, max_len: int) -> int:
+        return 2 * self.spec.num_hidden_layers * nseq * max_len * self.p.kv_local * 2
+
+    def new_kv_cache(self, nseq: int, max_len: int, storage: torch.Tensor | None = None) -> KVCache:
+        """K and V of every layer, zero-filled.  ``storage`` (uint8, at least ``kv_cache_bytes``)
+        lets the caller place the cache in memory it also uses for something else at other times."""
         L = self.spec.num_hidden_layers
-        k = [torch.zeros(nseq * max_len, self.p.kv_local, dtype=BF16, device=self.dev) for _ in range(L)]
-        v = [torch.zeros(nseq * max_len, self.p.kv_local, dtype=BF16, device=self.dev) for _ in range(L)]
-        return KVCache(k, v, nseq, max_len)
+        n = nseq * max_len * self.p.kv_local
+        if storage is None:
+            storage = torch.zeros(self.kv_cache_bytes(nseq, max_len), dtype=torch.uint8, device=self.dev)
+        flat = storage[: 2 * L * n * 2].view(BF16)
+        flat.zero_()
+        k = [flat[(2 * l) * n:(2 * l + 1) * n].view(nseq * max_len, self.p.kv_local) for l in range(L)]
+        v = [flat[(2 * l + 1) * n:(2 * l + 2) * n].view(nseq * max_len, self.p.kv_local) for l in range(L)]
+        return KVCache(k, v, nseq, max_len, flat)
 
     def decode_tiles(self, nseq: int, max_len: int) -> torch.Tensor:
         """Static part of the decode tile table; columns 5 (pos0) and 7 (kv_cap) change per step."""

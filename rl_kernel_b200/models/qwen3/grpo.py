@@ -40,6 +40,8 @@ class GRPOConfig:
     seed: int = 1234
     use_cuda_graph: bool = True
     use_reference_model: bool = True
+    share_rollout_weights: bool = False   # True: rollout reads the trainer's buffer (zero-copy publish)
+    share_kv_and_activation_memory: bool = True
 
     @property
     def num_seqs(self) -> int:
@@ -113,21 +115,33 @@ class GRPOTrainer:
         if cfg.use_reference_model and cfg.kl_coef > 0:
             self.ref_params = PackedParams(spec, tp_r, tp, device)
             self.ref_params.flat.copy_(self.policy.flat)
-        # rollout weights: a separate buffer that receives every published version
-        self.rollout_params = PackedParams(spec, tp_r, tp, device)
+        # rollout weights: a separate buffer that receives every published version, unless the
+        # engines are colocated and configured to alias the trainer's shard
+        self.rollout_params = self.policy if cfg.share_rollout_weights else PackedParams(spec, tp_r, tp, device)
         self.rollout_engine = Qwen3Engine(spec, self.rollout_params, self.ctx, max_positions=cfg.seq_len + 8)
+        kv_bytes = self.rollout_engine.kv_cache_bytes(cfg.num_seqs, cfg.seq_len)
+        self._arena = None
+        if cfg.share_kv_and_activation_memory:
+            self._arena = torch.zeros(kv_bytes, dtype=torch.uint8, device=device)
+            self.engine.ws.arena = self._arena
         self.rollout_engine.ws = self.engine.ws      # rollout and training never overlap in time
         self.rollout_engine.cos, self.rollout_engine.sin = self.engine.cos, self.engine.sin
         self.weight_version = 0
         self.opt = AdamW(self.policy, cfg, self.ctx)
         self._graph = None
+        self.graph_launches = 0
         self._kv = None
         self.metrics: dict[str, float] = {}
+
+    def local_prompts(self, prompts: torch.Tensor) -> torch.Tensor:
+        """The slice of the global prompt batch this rank's rollout engine generates for."""
+        return prompts
 
     # ---------------------------------------------------------------- weight sync
     def publish_weights(self) -> int:
         """Train -> rollout weight sync: one device copy of the flat shard; monotonic version."""
-        self.rollout_params.flat.copy_(self.policy.flat)
+        if self.rollout_params is not self.policy:
+            self.rollout_params.flat.copy_(self.policy.flat)
         self.weight_version += 1
         return self.weight_version
 
@@ -137,7 +151,7 @@ class GRPOTrainer:
         if self._kv is None:
             B = c.num_seqs
             eng = self.rollout_engine
-            self._kv = eng.new_kv_cache(B, c.seq_len)
+            self._kv = eng.new_kv_cache(B, c.seq_len, storage=self._arena)
             self._pkv = eng.new_kv_cache(c.num_prompts, c.prompt_len)
             self._dtiles = eng.decode_tiles(B, c.seq_len)
             self._tok = torch.zeros(B, dtype=torch.int64, device=self.dev)
@@ -168,8 +182,10 @@ class GRPOTrainer:
         c, eng = self.cfg, self.rollout_engine
         self._ensure_rollout_state()
         B, P, R, G = c.num_seqs, c.prompt_len, c.response_len, c.group_size
+        if self._arena is not None:
+            self._kv.flat.zero_()        # training activations lived here since the last rollout
         # ---- prefill each distinct prompt once, then share its KV with the whole group
-        hf = eng.forward_hidden(prompts, kv=self._pkv)
+        hf = eng.forward_hidden(prompts, kv=self._pkv, tag="p")
         H = self.spec.hidden_size
         last = hf.view(c.num_prompts, P, H)[:, P - 1].repeat_interleave(G, dim=0).contiguous()
         for l in range(self.spec.num_hidden_layers):
@@ -199,11 +215,14 @@ class GRPOTrainer:
                 torch.cuda.current_stream(self.dev).wait_stream(s)
                 self._tok.copy_(snap[0]); self._pos.copy_(snap[1]); self._col.copy_(snap[2])
                 self._graph = torch.cuda.CUDAGraph()
+                n0 = nv.LAUNCH_COUNT
                 with torch.cuda.graph(self._graph):
                     self._decode_once(step_seed)
+                self.graph_launches = nv.LAUNCH_COUNT - n0
                 self._tok.copy_(snap[0]); self._pos.copy_(snap[1]); self._col.copy_(snap[2])
             for _ in range(R - 1):
                 self._graph.replay()
+            nv.LAUNCH_COUNT += (R - 1) * self.graph_launches
         else:
             for _ in range(R - 1):
                 self._decode_once(step_seed)
