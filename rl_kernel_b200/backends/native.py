@@ -58,6 +58,25 @@ def det_gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: 
     return out
 
 
+def det_gemm_split(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor, *,
+                   nchunks: int, tile_n: int = 64) -> torch.Tensor:
+    """Chunked GEMM for few rows: one set of CTAs per canonical K chunk + a tree kernel.
+    Bitwise equal to ``det_gemm(..., nchunks=nchunks)``. ``scratch``: bf16, >= nchunks*M*ldc elements."""
+    _bf16(a, "a"); _bf16(b, "b"); _bf16(out, "out"); _bf16(scratch, "scratch")
+    _rowmajor2d(a, "a"); _rowmajor2d(b, "b"); _rowmajor2d(out, "out")
+    M, K = a.shape
+    N = b.shape[0]
+    if scratch.numel() < nchunks * M * out.stride(0):
+        raise ValueError("det_gemm_split: scratch too small")
+    rc = _lib().rlk_det_gemm_split(ext.ptr(a), ext.ptr(b), ext.ptr(out), ext.ptr(scratch), c_int(M),
+                                   c_int(N), c_int(K), _ll(a.stride(0)), _ll(b.stride(0)),
+                                   _ll(out.stride(0)), c_int(nchunks), c_int(tile_n),
+                                   ext.stream_ptr(a.device))
+    ext.check(rc, "det_gemm_split")
+    _count(2)
+    return out
+
+
 def lmhead_logp_stats(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor | None,
                       stats: torch.Tensor, tgt_logit: torch.Tensor, *, vocab_start: int,
                       inv_temp: float, logits_out: torch.Tensor | None = None) -> None:
@@ -78,7 +97,7 @@ def lmhead_logp_stats(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor | 
 # ------------------------------------------------------------------------------------- attention
 def attn_fwd(q2d: torch.Tensor, k_list: list[torch.Tensor], v_list: list[torch.Tensor],
              o2d: torch.Tensor, lse: torch.Tensor | None, tiles: torch.Tensor, scale: float, *,
-             cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False) -> None:
+             cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False, decode: bool = False) -> None:
     """q2d/o2d: [rows, Hq*128]; k/v: [rows, Hkv*128] (one tensor per source rank)."""
     _bf16(q2d, "q"); _rowmajor2d(q2d, "q"); _rowmajor2d(o2d, "o")
     n_src = len(k_list)
@@ -91,7 +110,7 @@ def attn_fwd(q2d: torch.Tensor, k_list: list[torch.Tensor], v_list: list[torch.T
                              kp, vp, c_int(n_src), _ll(k0.shape[0]), _ll(k0.shape[1]),
                              _ll(k0.stride(0)), ext.ptr(o2d), _ll(o2d.stride(0)), ext.ptr(lse),
                              ext.ptr(tiles), c_int(tiles.shape[0]), c_float(scale),
-                             c_int(cp_blocks_per_chunk), c_int(int(cp_zigzag)),
+                             c_int(cp_blocks_per_chunk), c_int(int(cp_zigzag)), c_int(int(decode)),
                              ext.stream_ptr(q2d.device))
     ext.check(rc, "attn_fwd")
     _count()
@@ -282,16 +301,30 @@ def group_advantages(rewards, groups: int, n: int, eps: float):
 
 
 # ------------------------------------------------------------------------------------- sampling
+_SAMPLE_SCRATCH: dict[tuple, torch.Tensor] = {}
+
+
+def _sample_scratch(rows: int, device) -> torch.Tensor:
+    key = (rows, str(device))
+    t = _SAMPLE_SCRATCH.get(key)
+    if t is None:
+        t = torch.empty(rows * 8 * 12 // 8 + 8, dtype=torch.int64, device=device)
+        _SAMPLE_SCRATCH[key] = t
+    return t
+
+
 def sample_gumbel(logits, out_ids, out_val, *, vocab_start: int, inv_temp: float, seed: int, step: int,
                   greedy: bool = False, min_keep=None, row_keys=None) -> None:
     rows, n_local = logits.shape
+    scratch = _sample_scratch(rows, logits.device)
     rc = _lib().rlk_sample_gumbel(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(min_keep),
-                                  ext.ptr(row_keys), ext.ptr(out_ids), ext.ptr(out_val), c_int(rows),
+                                  ext.ptr(row_keys), ext.ptr(out_ids), ext.ptr(out_val),
+                                  ext.ptr(scratch), c_int(rows),
                                   c_int(n_local), _ll(vocab_start), c_float(inv_temp),
                                   c_ulonglong(seed), c_uint(step), c_int(int(greedy)),
                                   ext.stream_ptr(logits.device))
     ext.check(rc, "sample_gumbel")
-    _count()
+    _count(2)
 
 
 # ------------------------------------------------------------------------------------- optimizer

@@ -44,15 +44,18 @@ struct AttnFwdParams {
   int cp_blocks_per_chunk;  // NSRC > 1: 128-key blocks per contiguous chunk of the sequence
   int cp_ranks;             // NSRC > 1: number of ranks holding the sequence
   int cp_zigzag;            // NSRC > 1: 1 = rank c holds chunks c and 2*cp-1-c; 0 = chunk c on rank c
+  int q_rows_box;           // 128 (training / prefill) or 8 (decode: at most 8 query rows per tile)
   int* status;
 };
 
+// Shared memory: [Q | P | K ring | V ring | barriers].  Full tiles: Q and P are 32 KB each and the
+// rings have 2 stages.  Decode tiles (<= 8 query rows): Q and P shrink to 2 KB each -- the UMMA
+// still reads 128 "rows" from those addresses, the ones past row 8 are whatever follows in shared
+// memory and only feed accumulator rows nobody reads -- and the freed space makes the rings 3
+// stages deep, which keeps enough K/V bytes in flight to stream the cache at memory speed.
 struct AttnFwdSmem {
-  static constexpr int kQ = 0;
-  static constexpr int kK = kQ + kTileBytes;
-  static constexpr int kV = kK + 2 * kTileBytes;
-  static constexpr int kP = kV + 2 * kTileBytes;
-  static constexpr int kBars = kP + kTileBytes;
+  static constexpr int kMaxStages = 3;
+  static constexpr int kBars = 6 * kTileBytes + 4096;  // decode layout: 4 KB of Q/P + two 3-stage rings
   static constexpr int kBytes = kBars + 256 + 1024;
 };
 
@@ -85,8 +88,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttnFwdSmem::kBars);
   // barrier indices
-  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 3, V_FULL = 5, V_EMPTY = 7, S_FULL = 9, S_EMPTY = 11,
-         P_FULL = 13, O_FULL = 14, NBARS = 15 };
+  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 10, S_FULL = 13, S_EMPTY = 15,
+         P_FULL = 17, O_FULL = 18, NBARS = 19 };
+  const bool decode = p.q_rows_box < 128;
+  const int nstage = decode ? 3 : 2;
+  const uint32_t q_half = static_cast<uint32_t>(p.q_rows_box) * 128u;  // bytes of one 64-column half of Q / P
+  const uint32_t off_p = 2 * q_half;
+  const uint32_t off_k = 4 * q_half;
+  const uint32_t off_v = off_k + nstage * kTileBytes;
+  const int n_active = decode ? 32 : 128;  // softmax threads that take part
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
@@ -103,15 +113,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(BAR(Q_FULL), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 3; ++s) {
       mbar_init(BAR(K_FULL + s), 1);
       mbar_init(BAR(K_EMPTY + s), 1);
       mbar_init(BAR(V_FULL + s), 1);
       mbar_init(BAR(V_EMPTY + s), 1);
-      mbar_init(BAR(S_FULL + s), 1);
-      mbar_init(BAR(S_EMPTY + s), 128);
     }
-    mbar_init(BAR(P_FULL), 128);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(BAR(S_FULL + s), 1);
+      mbar_init(BAR(S_EMPTY + s), n_active);
+    }
+    mbar_init(BAR(P_FULL), n_active);
     mbar_init(BAR(O_FULL), 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -124,21 +136,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t sQ = smem_u32(smem + AttnFwdSmem::kQ);
-  const uint32_t sK = smem_u32(smem + AttnFwdSmem::kK);
-  const uint32_t sV = smem_u32(smem + AttnFwdSmem::kV);
-  const uint32_t sP = smem_u32(smem + AttnFwdSmem::kP);
+  const uint32_t sQ = smem_u32(smem);
+  const uint32_t sP = sQ + off_p;
+  const uint32_t sK = sQ + off_k;
+  const uint32_t sV = sQ + off_v;
   constexpr uint32_t TM_S = 0;     // two S buffers: columns [0,128) and [128,256)
   constexpr uint32_t TM_O = 256;   // O_blk: columns [256,384)
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(BAR(Q_FULL), kTileBytes);
+      mbar_expect_tx(BAR(Q_FULL), 2 * q_half);
       tma_load_2d(sQ, &tmQ, t.q_col0, t.q_row0, BAR(Q_FULL));
-      tma_load_2d(sQ + kHalfBytes, &tmQ, t.q_col0 + 64, t.q_row0, BAR(Q_FULL));
+      tma_load_2d(sQ + q_half, &tmQ, t.q_col0 + 64, t.q_row0, BAR(Q_FULL));
       for (int b = 0; b < nblk; ++b) {
-        const int s = b & 1;
-        const uint32_t ph = (b >> 1) & 1;
+        const int s = b % nstage;
+        const uint32_t ph = (b / nstage) & 1;
         int src, row;
         cp_locate(p, t, b, src, row);
         if (NSRC == 1) src = 0;
@@ -157,18 +169,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);  // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, 128, 0, 1);  // P (K-major) x V (MN-major)
       auto issue_s = [&](int b) -> bool {
-        const int s = b & 1;
-        const uint32_t ph = (b >> 1) & 1;
+        const int s = b % nstage;               // K/V ring slot
+        const uint32_t ph = (b / nstage) & 1;
+        const int sb = b & 1;                   // S accumulator buffer
+        const uint32_t phs = (b >> 1) & 1;
         if (!mbar_wait(BAR(K_FULL + s), ph, abort_flag, p.status, 203)) return false;
-        if (!mbar_wait(BAR(S_EMPTY + s), ph ^ 1, abort_flag, p.status, 204)) return false;
+        if (!mbar_wait(BAR(S_EMPTY + sb), phs ^ 1, abort_flag, p.status, 204)) return false;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_bf16_ss(tmem_base + TM_S + s * 128, umma_desc_sw128(sQ + off, 16, 1024),
-                       umma_desc_sw128(sK + s * kTileBytes + off, 16, 1024), idesc_s, k != 0);
+          const uint32_t offq = (k >> 2) * q_half + (k & 3) * 32;
+          const uint32_t offk = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_bf16_ss(tmem_base + TM_S + sb * 128, umma_desc_sw128(sQ + offq, 16, 1024),
+                       umma_desc_sw128(sK + s * kTileBytes + offk, 16, 1024), idesc_s, k != 0);
         }
-        umma_commit(BAR(S_FULL + s));
+        umma_commit(BAR(S_FULL + sb));
         umma_commit(BAR(K_EMPTY + s));
         return true;
       };
@@ -177,14 +192,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       for (int b = 0; ok && b < nblk; ++b) {
         if (b + 1 < nblk) ok = issue_s(b + 1);
         if (!ok) break;
-        const int s = b & 1;
-        const uint32_t ph = (b >> 1) & 1;
+        const int s = b % nstage;
+        const uint32_t ph = (b / nstage) & 1;
         if (!mbar_wait(BAR(V_FULL + s), ph, abort_flag, p.status, 206)) break;
         if (!mbar_wait(BAR(P_FULL), b & 1, abort_flag, p.status, 207)) break;
         tc_fence_after();
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-          const uint32_t aoff = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          const uint32_t aoff = (k >> 2) * q_half + (k & 3) * 32;
           umma_bf16_ss(tmem_base + TM_O, umma_desc_sw128(sP + aoff, 16, 1024),
                        umma_desc_sw128(sV + s * kTileBytes + k * 2048, kHalfBytes, 1024), idesc_o,
                        k != 0);
@@ -193,8 +208,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         umma_commit(BAR(V_EMPTY + s));
       }
     }
-  } else {
+  } else if (!decode || (warp & 3) == 0) {
     // ---------------------------------------------------------------- softmax / accumulate
+    // (decode tiles have at most 8 rows: only the warp that owns TMEM lanes 0-31 takes part)
     const int quad = warp & 3;
     const int r = quad * 32 + lane;  // this thread's query row within the tile
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
@@ -205,7 +221,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float o[128];
 #pragma unroll
     for (int i = 0; i < 128; ++i) o[i] = 0.f;
-    uint8_t* p_row = smem + AttnFwdSmem::kP;
+    uint8_t* p_row = smem + off_p;
 
     for (int b = 0; b < nblk; ++b) {
       const int s = b & 1;
@@ -252,7 +268,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
         for (int q4 = 0; q4 < 4; ++q4) {
           const uint32_t chunk16 = (c & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(p_row + half * kHalfBytes + sw128_offset(r, chunk16)) =
+          if (r < p.q_rows_box)
+            *reinterpret_cast<uint4*>(p_row + half * q_half + sw128_offset(r, chunk16)) =
               make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
         }
       }
@@ -322,13 +339,15 @@ static int launch_attn_fwd(const CUtensorMap& tmQ, const KvMaps<NSRC>& kv, const
 
 // Q: [q_rows, q_cols] bf16 row-major with pitch ldq; K and V: [kv_rows, kv_cols] with pitch ldkv.
 // `tiles` is a device array of n_tiles rlk::AttnTile.  O has Q's geometry with pitch ldo.
+// decode_rows != 0 promises that every tile has n_rows <= 8 (single-token decode with GQA packing)
+// and selects the small-Q layout; the per-row arithmetic is unchanged.
 // n_src == 1: k_ptrs/v_ptrs hold one pointer each.  n_src in 2..8 (context parallel): pointer s
 // is rank s's K / V buffer (same shape and pitch on every rank), mapped into this process.
 RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long long ldq,
                          const void* const* k_ptrs, const void* const* v_ptrs, int n_src,
                          long long kv_rows, long long kv_cols, long long ldkv, void* O,
                          long long ldo, float* lse, const void* tiles, int n_tiles, float scale,
-                         int cp_blocks_per_chunk, int cp_zigzag, void* stream) {
+                         int cp_blocks_per_chunk, int cp_zigzag, int decode_rows, void* stream) {
   using namespace rlk;
   RLK_REQUIRE(n_tiles > 0, "attn_fwd: no tiles");
   RLK_REQUIRE(n_src == 1 || (n_src >= 2 && n_src <= 8), "attn_fwd: n_src must be 1..8");
@@ -347,8 +366,9 @@ RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long
   p.cp_ranks = n_src > 1 ? n_src : 1;
   p.cp_zigzag = cp_zigzag;
   p.status = device_status_word();
+  p.q_rows_box = decode_rows ? 8 : 128;
   CUtensorMap tmQ;
-  int rc = make_tmap_2d_sw128(&tmQ, Q, q_rows, q_cols, ldq, 128, 64, 2);
+  int rc = make_tmap_2d_sw128(&tmQ, Q, q_rows, q_cols, ldq, p.q_rows_box, 64, 2);
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (n_src == 1) {

@@ -37,6 +37,9 @@ struct GemmParams {
   int out_fp32;         // 1: C is fp32
   int accumulate;       // 1: C += result (read-modify-write in fp32, rounded to C's dtype)
   int* status;
+  int a_box_rows;           // rows of A that TMA brings per tile (128, or fewer when M < 128)
+  int split_chunks;         // > 1: every canonical chunk is its own tile and writes its bf16 leaf
+  long long split_stride;   //      to C + chunk * split_stride (elements); nchunks is 1 then
   // fused LM-head epilogue (tile_n == 128, nchunks == 1): per-(row, tile) softmax statistics
   float2* stats;            // null = plain GEMM
   long long stats_stride;   // float2 elements per row of `stats`
@@ -117,27 +120,30 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_tiles = p.m_tiles * p.n_tiles;
+  const int total_tiles = p.m_tiles * p.n_tiles * p.split_chunks;
   const uint32_t smem_base = smem_u32(smem);
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
+      const uint32_t stage_tx = (A_MN ? S::kStageA : static_cast<uint32_t>(p.a_box_rows) * BK * 2) + S::kStageB;
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
         int mt, nt;
-        tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
+        const int chunk = t % p.split_chunks;
+        tile_coords(t / p.split_chunks, p.m_tiles, p.n_tiles, mt, nt);
         const int m0 = mt * BM, n0 = nt * BN;
         const int kbs = p.nchunks * p.kb_per_chunk;
+        const int kb0 = chunk * p.kb_per_chunk;
         for (int kb = 0; kb < kbs; ++kb, ++it) {
           const uint32_t s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 101)) break;
           const uint32_t fb = full0 + 8 * s;
-          mbar_expect_tx(fb, S::kStage);
+          mbar_expect_tx(fb, stage_tx);
           const uint32_t sa = smem_base + s * S::kStage;
           const uint32_t sb = sa + S::kStageA;
-          const int k0 = kb * BK;
+          const int k0 = (kb0 + kb) * BK;
           if (!A_MN) {
             tma_load_2d(sa, &tmA, k0, m0, fb);
           } else {
@@ -194,9 +200,10 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     uint32_t u = 0;
     for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
       int mt, nt;
-      tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
+      tile_coords(t / p.split_chunks, p.m_tiles, p.n_tiles, mt, nt);
       const int row = mt * BM + row_in_tile;
       const int n0 = nt * BN;
+      const long long c_off = static_cast<long long>(t % p.split_chunks) * p.split_stride;
       for (int c = 0; c < p.nchunks; ++c, ++u) {
         const uint32_t a = u & 1;
         if (!mbar_wait(accf0 + 8 * a, (u >> 1) & 1, abort_flag, p.status, 104)) break;
@@ -261,7 +268,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (p.nchunks == 1) {
             if (row < p.M) {
               if (p.out_fp32) {
-                float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + n0 + col0;
+                float* dst = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + n0 + col0;
 #pragma unroll
                 for (int j = 0; j < 32; j += 4) {
                   if (n0 + col0 + j < p.N) {
@@ -275,7 +282,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                   }
                 }
               } else {
-                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) +
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off +
                                      static_cast<long long>(row) * p.ldc + n0 + col0;
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
@@ -374,7 +381,10 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   GemmParams p = p0;
   CUtensorMap tmA, tmB;
   int rc;
-  if (!A_MN) rc = make_tmap_2d_sw128(&tmA, A, p.M, p.K, lda, BM, 64, 2);
+  if (p.split_chunks < 1) p.split_chunks = 1;
+  p.a_box_rows = BM;
+  if (!A_MN && p.M < BM) p.a_box_rows = (p.M + 7) / 8 * 8;  // rows beyond are never stored: skip loading them
+  if (!A_MN) rc = make_tmap_2d_sw128(&tmA, A, p.M, p.K, lda, p.a_box_rows, 64, 2);
   else rc = make_tmap_2d_sw128(&tmA, A, p.K, p.M, lda, BK, 64, 2);
   if (rc) return rc;
   if (!B_MN) rc = make_tmap_2d_sw128(&tmB, B, p.N, p.K, ldb, BN, 64, 2);
@@ -382,7 +392,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   if (rc) return rc;
   p.m_tiles = (p.M + BM - 1) / BM;
   p.n_tiles = (p.N + BN - 1) / BN;
-  const int tiles = p.m_tiles * p.n_tiles;
+  const int tiles = p.m_tiles * p.n_tiles * p.split_chunks;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   auto kfn = det_gemm_kernel<BN, A_MN, B_MN>;
   static bool attr_set[64] = {false};
@@ -396,6 +406,28 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   kfn<<<grid, kGemmThreads, GemmSmem<BN>::kBytes, stream>>>(tmA, tmB, p);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
+}
+
+// out[i] = balanced tree over the nchunks bf16 leaves leaf[c][i], node = bf16(fp32(a) + fp32(b)).
+__global__ void __launch_bounds__(256)
+chunk_tree_kernel(const __nv_bfloat16* __restrict__ leaves, long long chunk_stride,
+                  __nv_bfloat16* __restrict__ out, int M, int N, long long ld, int nchunks) {
+  const int per_row = N / 8;
+  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= static_cast<long long>(M) * per_row) return;
+  const long long off = (idx / per_row) * ld + (idx % per_row) * 8;
+  uint4 v[8];
+  for (int c = 0; c < nchunks; ++c) v[c] = *reinterpret_cast<const uint4*>(leaves + c * chunk_stride + off);
+  for (int n = nchunks; n > 1; n >>= 1) {
+    for (int i = 0; i < n / 2; ++i) {
+      const uint4 a = v[2 * i], b = v[2 * i + 1];
+      v[i].x = pack_bf16x2(__fadd_rn(bf16_lo(a.x), bf16_lo(b.x)), __fadd_rn(bf16_hi(a.x), bf16_hi(b.x)));
+      v[i].y = pack_bf16x2(__fadd_rn(bf16_lo(a.y), bf16_lo(b.y)), __fadd_rn(bf16_hi(a.y), bf16_hi(b.y)));
+      v[i].z = pack_bf16x2(__fadd_rn(bf16_lo(a.z), bf16_lo(b.z)), __fadd_rn(bf16_hi(a.z), bf16_hi(b.z)));
+      v[i].w = pack_bf16x2(__fadd_rn(bf16_lo(a.w), bf16_lo(b.w)), __fadd_rn(bf16_hi(a.w), bf16_hi(b.w)));
+    }
+  }
+  *reinterpret_cast<uint4*>(out + off) = v[0];
 }
 
 }  // namespace rlk
@@ -453,6 +485,45 @@ RLK_API int rlk_det_gemm(const void* A, const void* B, void* C, int M, int N, in
 #undef RLK_GEMM_CASE
   return set_error(RLK_ERR_UNSUPPORTED, "det_gemm: no kernel for tile_n=%d a_mn=%d b_mn=%d", bn,
                    a_mn, b_mn);
+}
+
+// Small-M form of the chunked GEMM (decode): every canonical K chunk becomes its own set of CTAs
+// (nchunks times more parallelism), each writes its rounded bf16 leaf into `scratch`
+// ([nchunks][M][ldc] bf16), and a second kernel combines the leaves with the same balanced tree
+// the single-kernel form applies in its epilogue: identical bits, far better occupancy when
+// M <= a few hundred rows.  A and B are K-major.
+RLK_API long long rlk_det_gemm_split_scratch_elems(int M, long long ldc, int nchunks) {
+  return static_cast<long long>(nchunks) * M * ldc;
+}
+
+RLK_API int rlk_det_gemm_split(const void* A, const void* B, void* C, void* scratch, int M, int N,
+                               int K, long long lda, long long ldb, long long ldc, int nchunks,
+                               int tile_n, void* stream) {
+  using namespace rlk;
+  RLK_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0, "det_gemm_split: bad shape");
+  RLK_REQUIRE(nchunks == 2 || nchunks == 4 || nchunks == 8, "det_gemm_split: nchunks must be 2, 4 or 8");
+  RLK_REQUIRE(K % (nchunks * 64) == 0, "det_gemm_split: K/nchunks must be a multiple of 64");
+  RLK_REQUIRE((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 &&
+                  (ldc * 2) % 16 == 0, "det_gemm_split: C and scratch must be 16-byte aligned");
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.nchunks = 1;
+  p.kb_per_chunk = K / nchunks / 64;
+  p.C = scratch; p.ldc = ldc;
+  p.status = device_status_word();
+  p.split_chunks = nchunks;
+  p.split_stride = static_cast<long long>(M) * ldc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc;
+  if (tile_n == 32) rc = launch_gemm<32, false, false>(A, B, p, lda, ldb, s);
+  else if (tile_n == 128) rc = launch_gemm<128, false, false>(A, B, p, lda, ldb, s);
+  else rc = launch_gemm<64, false, false>(A, B, p, lda, ldb, s);
+  if (rc) return rc;
+  const long long n = static_cast<long long>(M) * (N / 8);
+  chunk_tree_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(
+      static_cast<const __nv_bfloat16*>(scratch), p.split_stride, static_cast<__nv_bfloat16*>(C), M, N, ldc, nchunks);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
 }
 
 // Fused vocab-(parallel) LM head: logits tile = H[M,K] * W[N,K]^T is reduced in the GEMM epilogue

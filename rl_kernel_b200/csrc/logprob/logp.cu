@@ -47,23 +47,40 @@ logits_tile_stats_kernel(const __nv_bfloat16* __restrict__ logits, long long ld,
   }
 }
 
+// One warp per row.  The maximum is order-free; the sum keeps the contract's order exactly: the 32
+// lanes compute exp(m_t - M) for 32 consecutive tiles in parallel, then lane 0 folds them into S
+// with S = fma(s_t, e_t, S) in ascending t (values handed over by shuffles).
 __global__ void __launch_bounds__(128)
 logp_merge_kernel(const float2* __restrict__ stats, long long stats_row_stride, int n_tiles,
                   const float* __restrict__ tgt_logit, float* __restrict__ logp, float* __restrict__ lse,
                   int rows) {
-  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   const float2* st = stats + row * stats_row_stride;
   float M = -INFINITY;
-  for (int t = 0; t < n_tiles; ++t) M = fmaxf(M, st[t].x);
+  for (int t = lane; t < n_tiles; t += 32) M = fmaxf(M, st[t].x);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
   float S = 0.f;
-  for (int t = 0; t < n_tiles; ++t) {
-    const float2 v = st[t];
-    if (v.x > -INFINITY) S = fmaf(v.y, logp_exp(__fsub_rn(v.x, M)), S);
+  for (int t0 = 0; t0 < n_tiles; t0 += 32) {
+    const int t = t0 + lane;
+    float y = 0.f, e = 0.f;
+    if (t < n_tiles) {
+      const float2 v = st[t];
+      if (v.x > -INFINITY) { y = v.y; e = logp_exp(__fsub_rn(v.x, M)); }
+    }
+    const int n = min(32, n_tiles - t0);
+    for (int j = 0; j < n; ++j) {
+      const float yj = __shfl_sync(0xffffffffu, y, j), ej = __shfl_sync(0xffffffffu, e, j);
+      if (ej != 0.f || yj != 0.f) S = fmaf(yj, ej, S);
+    }
   }
-  const float l = __fadd_rn(M, logf(S));
-  if (lse) lse[row] = l;
-  if (logp) logp[row] = fminf(__fsub_rn(tgt_logit[row], l), 0.f);
+  if (lane == 0) {
+    const float l = __fadd_rn(M, logf(S));
+    if (lse) lse[row] = l;
+    if (logp) logp[row] = fminf(__fsub_rn(tgt_logit[row], l), 0.f);
+  }
 }
 
 // logits[row, j] <- (g[row] * inv_temp) * ( [j == target] - exp(z_j - lse[row]) )   (bf16, in place)
@@ -113,7 +130,7 @@ RLK_API int rlk_logits_tile_stats(const void* logits, long long ld, const long l
 RLK_API int rlk_logp_merge(const void* stats, long long stats_row_stride, int n_tiles,
                            const float* tgt_logit, float* logp, float* lse, int rows, void* stream) {
   RLK_REQUIRE(rows > 0 && n_tiles > 0, "logp_merge: bad shape");
-  logp_merge_kernel<<<(rows + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+  logp_merge_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       (const float2*)stats, stats_row_stride, n_tiles, tgt_logit, logp, lse, rows);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;

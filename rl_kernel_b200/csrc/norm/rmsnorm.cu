@@ -2,10 +2,11 @@
 // per-head QK-RMSNorm + NeoX RoPE used on attention inputs.
 //
 // Reduction contract (depends on the row width only, never on the number of rows):
-//   one warp owns one row; lane l reads the 16-byte chunks l, l+32, l+64, ... of the row and
-//   adds their squares to a private fp32 sum in ascending element order; the 32 lane sums are
-//   combined by the xor butterfly 16,8,4,2,1.  y = bf16( x * rstd * w ) with all factors fp32
-//   ("multiply in fp32, round once").
+//   forward: 128 threads own one row; thread t reads the 16-byte chunks t, t+128, ... and adds their
+//   squares to a private fp32 sum in ascending element order; each warp folds its 32 sums with the
+//   xor butterfly 16,8,4,2,1 and the four warp sums are combined as (w0+w1)+(w2+w3).
+//   y = bf16( x * rstd * w ) with all factors fp32 ("multiply in fp32, round once").
+//   (backward and the 128-wide head norm use one warp per row with the same butterfly.)
 // Weight gradients are reduced in two fixed stages: each CTA sums its rows in ascending order
 // into a partial row of a scratch buffer, then a second kernel adds the partial rows in
 // ascending order.
@@ -26,21 +27,27 @@ __device__ __forceinline__ float warp_sum_xor(float v) {
 constexpr int kNormWarps = 8;
 
 // y = rmsnorm(x [+ res]) * w ; optionally writes the summed residual stream and rstd.
+// One CTA of 128 threads per row: thread t owns the 16-byte chunks t, t+128, ... (kept in
+// registers between the two passes when the row has at most 8 chunks per thread).
+constexpr int kRowThreads = 128;
+constexpr int kMaxChunks = 8;
+
 template <bool HAS_RES>
-__global__ void __launch_bounds__(kNormWarps * 32)
+__global__ void __launch_bounds__(kRowThreads)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int rows,
                    int H, float eps) {
-  const int row = blockIdx.x * kNormWarps + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= rows) return;
+  __shared__ float swarp[4];
+  const int row = blockIdx.x;
+  const int tid = threadIdx.x;
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * H);
   const uint4* rr = HAS_RES ? reinterpret_cast<const uint4*>(res + static_cast<long long>(row) * H) : nullptr;
   uint4* ro = HAS_RES ? reinterpret_cast<uint4*>(res_out + static_cast<long long>(row) * H) : nullptr;
   const int nchunk = H / 8;
+  uint4 keep[kMaxChunks];
   float ss = 0.f;
-  for (int c = lane; c < nchunk; c += 32) {
+  auto load_chunk = [&](int c) -> uint4 {
     uint4 v = xr[c];
     if (HAS_RES) {
       const uint4 q = rr[c];
@@ -57,15 +64,24 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
       ss = fmaf(a, a, ss);
       ss = fmaf(b, b, ss);
     }
+    return v;
+  };
+#pragma unroll
+  for (int i = 0; i < kMaxChunks; ++i) {
+    const int c = tid + i * kRowThreads;
+    if (c < nchunk) keep[i] = load_chunk(c);
   }
+  for (int c = tid + kMaxChunks * kRowThreads; c < nchunk; c += kRowThreads) load_chunk(c);
   ss = warp_sum_xor(ss);
+  if ((tid & 31) == 0) swarp[tid >> 5] = ss;
+  __syncthreads();
+  ss = (swarp[0] + swarp[1]) + (swarp[2] + swarp[3]);
   const float rstd = rsqrtf(ss / static_cast<float>(H) + eps);
-  if (rstd_out && lane == 0) rstd_out[row] = rstd;
+  if (rstd_out && tid == 0) rstd_out[row] = rstd;
   const uint4* wr = reinterpret_cast<const uint4*>(w);
   uint4* yr = reinterpret_cast<uint4*>(y + static_cast<long long>(row) * H);
   const uint4* src = HAS_RES ? reinterpret_cast<const uint4*>(ro) : xr;
-  for (int c = lane; c < nchunk; c += 32) {
-    const uint4 v = src[c];
+  auto store_chunk = [&](int c, const uint4 v) {
     const uint4 g = wr[c];
     uint4 o;
     o.x = pack_bf16x2(bf16_lo(v.x) * rstd * bf16_lo(g.x), bf16_hi(v.x) * rstd * bf16_hi(g.x));
@@ -73,7 +89,13 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
     o.z = pack_bf16x2(bf16_lo(v.z) * rstd * bf16_lo(g.z), bf16_hi(v.z) * rstd * bf16_hi(g.z));
     o.w = pack_bf16x2(bf16_lo(v.w) * rstd * bf16_lo(g.w), bf16_hi(v.w) * rstd * bf16_hi(g.w));
     yr[c] = o;
+  };
+#pragma unroll
+  for (int i = 0; i < kMaxChunks; ++i) {
+    const int c = tid + i * kRowThreads;
+    if (c < nchunk) store_chunk(c, keep[i]);
   }
+  for (int c = tid + kMaxChunks * kRowThreads; c < nchunk; c += kRowThreads) store_chunk(c, src[c]);
 }
 
 // dx = rstd * (w*dy - xhat * mean(w*dy*xhat)) [+ dres];  partial dw[cta] = sum_rows dy * xhat.
@@ -328,14 +350,14 @@ RLK_API int rlk_rmsnorm_fwd(const void* x, const void* res, const void* w, void*
                             float* rstd_out, int rows, int H, float eps, void* stream) {
   RLK_REQUIRE(rows > 0 && H > 0 && H % 8 == 0, "rmsnorm: H must be a positive multiple of 8");
   RLK_REQUIRE(!res || res_out, "rmsnorm: residual input needs res_out");
-  const int grid = (rows + kNormWarps - 1) / kNormWarps;
+  const int grid = rows;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (res)
-    rmsnorm_fwd_kernel<true><<<grid, kNormWarps * 32, 0, s>>>(
+    rmsnorm_fwd_kernel<true><<<grid, kRowThreads, 0, s>>>(
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
         (__nv_bfloat16*)y, (__nv_bfloat16*)res_out, rstd_out, rows, H, eps);
   else
-    rmsnorm_fwd_kernel<false><<<grid, kNormWarps * 32, 0, s>>>(
+    rmsnorm_fwd_kernel<false><<<grid, kRowThreads, 0, s>>>(
         (const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, nullptr,
         rstd_out, rows, H, eps);
   RLK_CHECK_CUDA(cudaGetLastError());

@@ -8,7 +8,9 @@
 // best id) and the global winner is the maximum over ranks (ties -> smaller id).
 // Top-k / top-p: a per-row logit threshold `min_keep[row]` (computed by the keep-mask op) removes
 // ids whose z is below it; ids at or beyond the real vocab are never sampled.
-// One CTA per row; threads stride the row with 16-byte loads, then a fixed shared-memory tree.
+// kSampleSegs CTAs per row, each reducing a contiguous slice of the row to (best score, best id)
+// in a small scratch array; a second kernel picks the winner (maximum, ties to the smaller id --
+// an order-free rule, so the split into segments does not change the result).
 // Replaces the torch sort/softmax/cumsum path of rl_engine/ops/sampling/policy.py:17-52 for the
 // draw itself (FlashInfer sampling in rl_engine/ops/sampling/api.py:42-79).
 #include "rlk/host.h"
@@ -38,11 +40,14 @@ __device__ __forceinline__ float gumbel_from_u32(uint32_t r) {
   return -__logf(-__logf(u));
 }
 
+constexpr int kSampleSegs = 8;
+
 struct SampleParams {
   const __nv_bfloat16* logits; long long ld;
   const float* min_keep;       // [rows] or null
   const long long* row_keys;   // [rows] stable per-sequence key for the RNG counter, or null (row index)
   long long* out_ids; float* out_val;
+  float* part_val; long long* part_id;   // [rows][kSampleSegs] scratch
   int rows, n_local; long long vocab_start;
   float inv_temp; uint64_t seed; uint32_t step; int greedy;
 };
@@ -50,13 +55,16 @@ struct SampleParams {
 __global__ void __launch_bounds__(256) sample_gumbel_kernel(const SampleParams p) {
   __shared__ float sval[256];
   __shared__ long long sidx[256];
-  const int row = blockIdx.x;
+  const int row = blockIdx.x / kSampleSegs, seg = blockIdx.x % kSampleSegs;
   const __nv_bfloat16* src = p.logits + row * p.ld;
+  const int nchunks = p.n_local / 8;
+  const int per_seg = (nchunks + kSampleSegs - 1) / kSampleSegs;
+  const int c_begin = seg * per_seg, c_end = min(nchunks, c_begin + per_seg);
   const uint32_t key = static_cast<uint32_t>(p.row_keys ? p.row_keys[row] : row);
   const float thr = p.min_keep ? p.min_keep[row] : -INFINITY;
   float best = -INFINITY;
   long long best_id = 0x7fffffffffffffffll;
-  for (int c = threadIdx.x; c < p.n_local / 8; c += blockDim.x) {
+  for (int c = c_begin + threadIdx.x; c < c_end; c += blockDim.x) {
     const uint4 v = *reinterpret_cast<const uint4*>(src + c * 8);
     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -84,9 +92,23 @@ __global__ void __launch_bounds__(256) sample_gumbel_kernel(const SampleParams p
     __syncthreads();
   }
   if (threadIdx.x == 0) {
-    p.out_ids[row] = sidx[0];
-    if (p.out_val) p.out_val[row] = sval[0];
+    p.part_val[row * kSampleSegs + seg] = sval[0];
+    p.part_id[row * kSampleSegs + seg] = sidx[0];
   }
+}
+
+__global__ void sample_pick_kernel(const SampleParams p) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= p.rows) return;
+  float best = p.part_val[row * kSampleSegs];
+  long long id = p.part_id[row * kSampleSegs];
+  for (int s = 1; s < kSampleSegs; ++s) {
+    const float v = p.part_val[row * kSampleSegs + s];
+    const long long i = p.part_id[row * kSampleSegs + s];
+    if (v > best || (v == best && i < id)) { best = v; id = i; }
+  }
+  p.out_ids[row] = id;
+  if (p.out_val) p.out_val[row] = best;
 }
 
 }  // namespace rlk
@@ -94,14 +116,24 @@ using namespace rlk;
 
 // out_ids[row] = sampled GLOBAL vocab id from this shard's columns; out_val = its perturbed score
 // (the cross-rank winner is the shard with the largest out_val, ties to the smaller id).
+// scratch: rows * 8 floats followed by rows * 8 int64 (see rlk_sample_scratch_bytes).
+RLK_API long long rlk_sample_scratch_bytes(int rows) { return static_cast<long long>(rows) * kSampleSegs * 12; }
+
 RLK_API int rlk_sample_gumbel(const void* logits, long long ld, const float* min_keep,
-                              const long long* row_keys, long long* out_ids, float* out_val, int rows,
+                              const long long* row_keys, long long* out_ids, float* out_val,
+                              void* scratch, int rows,
                               int n_local, long long vocab_start, float inv_temp,
                               unsigned long long seed, unsigned int step, int greedy, void* stream) {
   RLK_REQUIRE(rows > 0 && n_local > 0 && n_local % 8 == 0 && ld % 8 == 0, "sample: bad shape");
-  SampleParams p{(const __nv_bfloat16*)logits, ld, min_keep, row_keys, out_ids, out_val, rows, n_local,
-                 vocab_start, inv_temp, seed, step, greedy};
-  sample_gumbel_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  RLK_REQUIRE(scratch != nullptr && (reinterpret_cast<uintptr_t>(scratch) & 7) == 0, "sample: scratch required (8-byte aligned)");
+  long long* part_id = static_cast<long long*>(scratch);
+  float* part_val = reinterpret_cast<float*>(part_id + static_cast<long long>(rows) * kSampleSegs);
+  SampleParams p{(const __nv_bfloat16*)logits, ld, min_keep, row_keys, out_ids, out_val, part_val, part_id,
+                 rows, n_local, vocab_start, inv_temp, seed, step, greedy};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  sample_gumbel_kernel<<<rows * kSampleSegs, 256, 0, s>>>(p);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  sample_pick_kernel<<<(rows + 127) / 128, 128, 0, s>>>(p);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

@@ -299,6 +299,10 @@ class Qwen3Engine:
             M = a.shape[1] if a_mn else a.shape[0]
             K = a.shape[0] if a_mn else a.shape[1]
             N = b.shape[1] if b_mn else b.shape[0]
+        if nchunks > 1 and M <= 512 and not (a_mn or b_mn or accumulate):
+            # few rows (decode): one set of CTAs per canonical chunk, then the tree kernel
+            scratch = self.ws.get("d.split", (nchunks * M * out.stride(0),))
+            return nv.det_gemm_split(a, b, out, scratch, nchunks=nchunks, tile_n=64)
         return nv.det_gemm(a, b, out, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, nchunks=nchunks,
                            accumulate=accumulate)
 
@@ -330,7 +334,7 @@ class Qwen3Engine:
         attn = ws.get(f"{tag}.attn", (T, self.p.q_local))
         qv = q if q_view is None else q.view(*q_view)
         ov = attn if q_view is None else attn.view(*q_view)
-        self._attention(qv, kbuf, vbuf, ov, lse, tiles)
+        self._attention(qv, kbuf, vbuf, ov, lse, tiles, decode=q_view is not None)
         o = ws.get(f"{tag}.o", (T, H))
         self._gemm(attn, w[f"l{l}.wo"], o, nchunks=self.nchunks)
         self.ctx.tp_all_reduce_(o)
@@ -348,8 +352,9 @@ class Qwen3Engine:
             keep.update(s_in=s_in, h=h, qkv=qkv, q=q, attn=attn, s_mid=s_mid, h2=h2, gu=gu, act=act)
         return down, s_mid
 
-    def _attention(self, q2d, k2d, v2d, o2d, lse, tiles):
-        nv.attn_fwd(q2d, [k2d], [v2d], o2d, lse, tiles, self.scale)
+    def _attention(self, q2d, k2d, v2d, o2d, lse, tiles, decode: bool = False):
+        nv.attn_fwd(q2d, [k2d], [v2d], o2d, lse, tiles, self.scale,
+                    decode=decode and self.hq // self.hkv <= 8)
 
     # -------------------------------------------------------------------------- full forward
     def forward_hidden(self, tokens: torch.Tensor, *, save: TrainState | None = None,

@@ -255,8 +255,11 @@ class GRPOTrainer:
     def step(self, prompts: torch.Tensor, rewards_fn=None, step_index: int = 0) -> dict:
         c = self.cfg
         B, R = c.num_seqs, c.response_len
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        ev[0].record()
         self.publish_weights()
         tokens, old_logp = self.rollout(prompts, step_seed=c.seed + 7919 * step_index)
+        ev[1].record()
         if rewards_fn is None:
             gen = torch.Generator(device=self.dev).manual_seed(c.seed + step_index)
             rewards = torch.bernoulli(torch.full((B,), 0.5, device=self.dev), generator=gen)
@@ -265,6 +268,7 @@ class GRPOTrainer:
         adv = nv.group_advantages(rewards.contiguous(), c.num_prompts, c.group_size, 1e-6)
         mask = torch.ones(B, R, dtype=torch.uint8, device=self.dev)
         ref_logp = self.score(self.ref_params, tokens) if self.ref_params is not None else None
+        ev[2].record()
         total_active = float(B * R)
         self.policy.grad.zero_()
         train_logp = torch.empty(B, R, dtype=torch.float32, device=self.dev)
@@ -284,10 +288,19 @@ class GRPOTrainer:
             lp = self.engine.train_forward_backward(tokens[b0:b1], c.prompt_len, dlogp_fn,
                                                     temperature=c.temperature)
             train_logp[b0:b1].copy_(lp)
+        ev[3].record()
         self.opt.step()
+        ev[4].record()
+        self.phase_events = ev     # rollout, reference scoring, train fwd/bwd, optimizer
         tot = torch.stack(loss_terms).sum(0)
         return {"tokens": tokens, "old_logp": old_logp, "train_logp": train_logp, "rewards": rewards,
                 "loss_sums": tot, "grad_norm": self.opt.last_grad_norm, "total_active": total_active}
+
+    def phase_ms(self) -> dict[str, float]:
+        """Device time of the last step's phases (call after a synchronize)."""
+        e = self.phase_events
+        names = ("rollout", "ref_score", "train_fwd_bwd", "optimizer")
+        return {n: e[i].elapsed_time(e[i + 1]) for i, n in enumerate(names)}
 
     @staticmethod
     def mismatch_count(train_logp: torch.Tensor, rollout_logp: torch.Tensor) -> int:
