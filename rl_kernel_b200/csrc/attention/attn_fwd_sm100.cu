@@ -3,8 +3,10 @@
 // One CTA per work tile (see rlk/attn_common.cuh): 128 query rows x one KV head's keys.
 //   warp 0   : TMA producer  (Q once, then K and V blocks through 2-stage rings)
 //   warp 1   : UMMA issuer   (S = Q K^T into TMEM, O_blk = P V into TMEM)
-//   warps 2-5: softmax + accumulation, one thread per query row (no cross-thread reductions,
-//              so a row's arithmetic cannot depend on what else is in the tile)
+//   warps 2-17: softmax + accumulation, four threads per query row (each owns 32 of the 128 keys
+//              of a block and 32 of the 128 output dims; only the block maximum and the final row
+//              sum are exchanged, through shared memory).  A row's arithmetic never depends on
+//              what else is in the tile.
 // Keys are consumed in canonical 128-key blocks in ascending order with an online softmax;
 // no split-KV, no atomics.  P is rounded to bf16 before P V (as every flash kernel does); the
 // row sum uses the unrounded fp32 probabilities, added in a fixed order.
@@ -23,7 +25,8 @@
 
 namespace rlk {
 
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 576;  // TMA warp, UMMA warp, 16 softmax warps
+constexpr int kSplit = 4;           // threads (column slices) per query row
 constexpr int kTileBytes = 128 * 128 * 2;  // one 128x128 bf16 operand tile (two 64-wide boxes)
 constexpr int kHalfBytes = 128 * 64 * 2;
 
@@ -56,8 +59,15 @@ struct AttnFwdParams {
 struct AttnFwdSmem {
   static constexpr int kMaxStages = 3;
   static constexpr int kBars = 6 * kTileBytes + 4096;  // decode layout: 4 KB of Q/P + two 3-stage rings
-  static constexpr int kBytes = kBars + 256 + 1024;
+  static constexpr int kXch = kBars + 256;             // row-wise exchange of partial maxima / sums
+  static constexpr int kBytes = kXch + 6144 + 1024;
 };
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // Which tensor map and which local row holds canonical block b of a sequence.
 __device__ __forceinline__ void cp_locate(const AttnFwdParams& p, const AttnTile& t, int b,
@@ -89,14 +99,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttnFwdSmem::kBars);
   // barrier indices
   enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 10, S_FULL = 13, S_EMPTY = 15,
-         P_FULL = 17, O_FULL = 18, NBARS = 19 };
+         P_FULL = 17, O_FULL = 18, XCH = 19, NBARS = 23 };
   const bool decode = p.q_rows_box < 128;
   const int nstage = decode ? 3 : 2;
   const uint32_t q_half = static_cast<uint32_t>(p.q_rows_box) * 128u;  // bytes of one 64-column half of Q / P
   const uint32_t off_p = 2 * q_half;
   const uint32_t off_k = 4 * q_half;
   const uint32_t off_v = off_k + nstage * kTileBytes;
-  const int n_active = decode ? 32 : 128;  // softmax threads that take part
+  const int n_active = (decode ? 32 : 128) * kSplit;  // softmax threads that take part
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const uint32_t bar0 = smem_u32(bars);
@@ -124,6 +134,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(BAR(S_EMPTY + s), n_active);
     }
     mbar_init(BAR(P_FULL), n_active);
+    for (int q = 0; q < 4; ++q) mbar_init(BAR(XCH + q), 32 * kSplit);
     mbar_init(BAR(O_FULL), 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -210,92 +221,92 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else if (!decode || (warp & 3) == 0) {
     // ---------------------------------------------------------------- softmax / accumulate
-    // (decode tiles have at most 8 rows: only the warp that owns TMEM lanes 0-31 takes part)
+    // Sixteen warps: warp -> (quad, split).  quad = warp % 4 is the TMEM lane quadrant the hardware
+    // lets the warp touch, split = (warp - 2) / 4 selects which 32 of the 128 S columns (keys) and
+    // which 32 of the 128 O columns (head dims) the thread owns.  The four threads of a row
+    // exchange their partial maxima through shared memory; everything else is private.
+    // (decode tiles have at most 8 rows: only the quad-0 warps take part)
     const int quad = warp & 3;
+    const int split = (warp - 2) >> 2;
     const int r = quad * 32 + lane;  // this thread's query row within the tile
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     int kv_len = t.pos0 + r * t.pos_step + 1;
     if (kv_len > t.kv_cap) kv_len = t.kv_cap;
     if (r >= t.n_rows) kv_len = 0;
-    float m_run = -INFINITY, l_run = 0.f;
-    float o[128];
+    float m_run = -INFINITY, l_part = 0.f;
+    float o[32];
 #pragma unroll
-    for (int i = 0; i < 128; ++i) o[i] = 0.f;
+    for (int i = 0; i < 32; ++i) o[i] = 0.f;
     uint8_t* p_row = smem + off_p;
+    float* xch = reinterpret_cast<float*>(smem + AttnFwdSmem::kXch);  // [2][128][4] maxima, then [128][4] sums
+    bool alive = true;
 
     for (int b = 0; b < nblk; ++b) {
       const int s = b & 1;
       const uint32_t ph = (b >> 1) & 1;
-      if (!mbar_wait(BAR(S_FULL + s), ph, abort_flag, p.status, 208)) break;
+      if (!mbar_wait(BAR(S_FULL + s), ph, abort_flag, p.status, 208)) { alive = false; break; }
       tc_fence_after();
-      const int k0 = b * kAttnBlock;
-      const int nvis = kv_len - k0;  // visible keys of this block for this row (may be <= 0)
-      // pass 1: block max
-      float m_blk = -INFINITY;
+      const int nvis = kv_len - b * kAttnBlock - split * 32;  // visible keys among this thread's 32
+      uint32_t x[32];
+      tmem_ld32(tmem_base + lane_off + TM_S + s * 128 + split * 32, x);
+      tmem_ld_wait();
+      float m_part = -INFINITY;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t x[32];
-        tmem_ld32(tmem_base + lane_off + TM_S + s * 128 + c * 32, x);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (c * 32 + j < nvis) m_blk = fmaxf(m_blk, __uint_as_float(x[j]));
-      }
+      for (int j = 0; j < 32; ++j)
+        if (j < nvis) m_part = fmaxf(m_part, __uint_as_float(x[j]));
+      xch[(b & 1) * 512 + r * 4 + split] = m_part;
+      mbar_arrive(BAR(XCH + quad));
+      if (!mbar_wait(BAR(XCH + quad), b & 1, abort_flag, p.status, 210)) { alive = false; break; }
+      const float4 mm = *reinterpret_cast<const float4*>(xch + (b & 1) * 512 + r * 4);
+      const float m_blk = fmaxf(fmaxf(mm.x, mm.y), fmaxf(mm.z, mm.w));
       const float m_new = fmaxf(m_run, m_blk);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = exp2f((m_run - m_use) * p.scale_log2);  // m_run=-inf -> 0
+      const float alpha = fast_exp2((m_run - m_use) * p.scale_log2);  // m_run = -inf -> 0
       const float neg_ms = -m_use * p.scale_log2;
       float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-      // pass 2: probabilities -> bf16 P tile in shared memory (K-major, 128B swizzle)
+      uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t x[32];
-        tmem_ld32(tmem_base + lane_off + TM_S + s * 128 + c * 32, x);
-        tmem_ld_wait();
-        uint32_t pk[16];
+      for (int j = 0; j < 32; j += 4) {
+        const float e0 = (j + 0 < nvis) ? fast_exp2(fmaf(__uint_as_float(x[j + 0]), p.scale_log2, neg_ms)) : 0.f;
+        const float e1 = (j + 1 < nvis) ? fast_exp2(fmaf(__uint_as_float(x[j + 1]), p.scale_log2, neg_ms)) : 0.f;
+        const float e2 = (j + 2 < nvis) ? fast_exp2(fmaf(__uint_as_float(x[j + 2]), p.scale_log2, neg_ms)) : 0.f;
+        const float e3 = (j + 3 < nvis) ? fast_exp2(fmaf(__uint_as_float(x[j + 3]), p.scale_log2, neg_ms)) : 0.f;
+        sum0 += e0; sum1 += e1; sum2 += e2; sum3 += e3;
+        pk[j / 2] = pack_bf16x2(e0, e1);
+        pk[j / 2 + 1] = pack_bf16x2(e2, e3);
+      }
+      // this thread's 32 keys = 4 chunks of 16 bytes; keys [64h, 64h+64) live in half h of the P tile
+      if (r < p.q_rows_box) {
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          float e0 = (c * 32 + j + 0 < nvis) ? exp2f(fmaf(__uint_as_float(x[j + 0]), p.scale_log2, neg_ms)) : 0.f;
-          float e1 = (c * 32 + j + 1 < nvis) ? exp2f(fmaf(__uint_as_float(x[j + 1]), p.scale_log2, neg_ms)) : 0.f;
-          float e2 = (c * 32 + j + 2 < nvis) ? exp2f(fmaf(__uint_as_float(x[j + 2]), p.scale_log2, neg_ms)) : 0.f;
-          float e3 = (c * 32 + j + 3 < nvis) ? exp2f(fmaf(__uint_as_float(x[j + 3]), p.scale_log2, neg_ms)) : 0.f;
-          sum0 += e0; sum1 += e1; sum2 += e2; sum3 += e3;
-          pk[j / 2] = pack_bf16x2(e0, e1);
-          pk[j / 2 + 1] = pack_bf16x2(e2, e3);
-        }
-        // 32 keys = 4 chunks of 16 bytes; keys [64h, 64h+64) live in half h of the P tile
-        const int half = c >> 1;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const uint32_t chunk16 = (c & 1) * 4 + q4;
-          if (r < p.q_rows_box)
-            *reinterpret_cast<uint4*>(p_row + half * q_half + sw128_offset(r, chunk16)) =
+        for (int q4 = 0; q4 < 4; ++q4)
+          *reinterpret_cast<uint4*>(p_row + (split >> 1) * q_half + sw128_offset(r, (split & 1) * 4 + q4)) =
               make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-        }
       }
       fence_proxy_async_smem();  // make the generic-proxy P writes visible to the UMMA
       tc_fence_before();
       mbar_arrive(BAR(S_EMPTY + s));
       mbar_arrive(BAR(P_FULL));
-      l_run = l_run * alpha + ((sum0 + sum1) + (sum2 + sum3));
+      l_part = l_part * alpha + ((sum0 + sum1) + (sum2 + sum3));
       m_run = m_new;
-      if (!mbar_wait(BAR(O_FULL), b & 1, abort_flag, p.status, 209)) break;
+      if (!mbar_wait(BAR(O_FULL), b & 1, abort_flag, p.status, 209)) { alive = false; break; }
       tc_fence_after();
+      tmem_ld32(tmem_base + lane_off + TM_O + split * 32, x);
+      tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t x[32];
-        tmem_ld32(tmem_base + lane_off + TM_O + c * 32, x);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o[c * 32 + j] = fmaf(o[c * 32 + j], alpha, __uint_as_float(x[j]));
-      }
+      for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], alpha, __uint_as_float(x[j]));
     }
     // ---------------------------------------------------------------- epilogue
-    if (r < t.n_rows && !*abort_flag) {
+    // row sum = (l0 + l1) + (l2 + l3) over the four column slices
+    float* lx = xch + 1024;
+    lx[r * 4 + split] = l_part;
+    mbar_arrive(BAR(XCH + quad));
+    if (alive && mbar_wait(BAR(XCH + quad), nblk & 1, abort_flag, p.status, 211) && r < t.n_rows) {
+      const float4 ll = *reinterpret_cast<const float4*>(lx + r * 4);
+      const float l_run = (ll.x + ll.y) + (ll.z + ll.w);
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = p.O + static_cast<long long>(t.q_row0 + r) * p.ldo + t.q_col0;
+      __nv_bfloat16* dst = p.O + static_cast<long long>(t.q_row0 + r) * p.ldo + t.q_col0 + split * 32;
 #pragma unroll
-      for (int j = 0; j < 128; j += 8) {
+      for (int j = 0; j < 32; j += 8) {
         uint4 v;
         v.x = pack_bf16x2(o[j] * inv_l, o[j + 1] * inv_l);
         v.y = pack_bf16x2(o[j + 2] * inv_l, o[j + 3] * inv_l);
@@ -303,7 +314,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         v.w = pack_bf16x2(o[j + 6] * inv_l, o[j + 7] * inv_l);
         *reinterpret_cast<uint4*>(dst + j) = v;
       }
-      if (p.lse) {
+      if (p.lse && split == 0) {
         const float lse = (l_run > 0.f) ? fmaf(m_run, p.scale, logf(l_run)) : -INFINITY;
         p.lse[t.lse_off + static_cast<long long>(r) * t.lse_stride] = lse;
       }

@@ -1,0 +1,364 @@
+// Symmetric-memory runtime and fixed-order collectives over NVLink peer access (single node).
+//
+// Every rank allocates one "window" with cudaMalloc, exports it with a CUDA IPC handle and maps the
+// windows of its peers; a window is [flag area | frame 0 | frame 1].  Collectives are ONE kernel
+// per call, launched by every rank on its own stream:
+//   * the payload is processed in slices; CTA b of every rank owns slices b, b+grid, ... in the same
+//     order on every rank, so a CTA only ever waits for the same-numbered slice of its peers;
+//   * a CTA copies its slice into the local frame, publishes `seq` into flag[me][slice] of every
+//     peer (st.release.sys), waits until its own flag[peer][slice] words reach `seq`
+//     (ld.acquire.sys, BOUNDED: after the limit it records a status code and skips the slice),
+//     then reads the peers' slices with plain peer loads and combines them;
+//   * sums use the balanced tree ((r0+r1)+(r2+r3))+((r4+r5)+(r6+r7)) in fp32 with a rounding to the
+//     tensor dtype at every node -- the continuation of det_gemm's canonical K-chunk tree, so
+//     TP = 1, 2, 4, 8 give identical bits.  Nothing here uses multimem reductions for sums: the
+//     in-switch order and precision are not this contract.
+//   * two frames alternate between calls; stream order plus the per-slice handshake make a frame
+//     safe to reuse two calls later.
+// No NCCL, no multicast TMA; only ld/st to peer pointers.  The design replaces the reference's
+// CUDA-IPC collective (csrc/cuda/collectives/deterministic_collective.cu:109-1949), whose device
+// waits are unbounded.
+#include "rlk/host.h"
+#include "rlk/ptx.cuh"
+
+#include <cstring>
+
+namespace rlk {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxSlices = 2048;
+constexpr int kFlagBytes = kMaxRanks * kMaxSlices * 8;  // u64 flag[src_rank][slice]
+constexpr int kMinSliceBytes = 32768;                   // payload bytes per slice (grows with the payload)
+constexpr int kCollThreads = 256;
+
+struct SymmWorld {
+  unsigned char* win[kMaxRanks];  // window base of every rank (own entry = local pointer)
+  int world, rank;
+  long long frame_bytes;
+  // CUDA-graph support: a captured kernel's sequence number is base + epoch * stride, where epoch
+  // (device word 0) is bumped once per replay and stride (device word 1) is the EVEN number of
+  // collective calls in the graph, so the frame parity of every captured call is fixed.
+  const unsigned long long* epoch;
+  int use_epoch;
+};
+
+__device__ __forceinline__ unsigned long long effective_seq(const SymmWorld& w, unsigned long long base) {
+  return w.use_epoch ? base + w.epoch[0] * w.epoch[1] : base;
+}
+
+__device__ __forceinline__ void st_release_sys_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_acquire_sys_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_peer_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ unsigned long long* flag_ptr(unsigned char* win, int src, int slice) {
+  return reinterpret_cast<unsigned long long*>(win) + src * kMaxSlices + slice;
+}
+__device__ __forceinline__ unsigned char* frame_ptr(unsigned char* win, long long frame_bytes, int f) {
+  return win + kFlagBytes + f * frame_bytes;
+}
+
+// Publish "my slice is in my frame" to every peer and wait for theirs. Returns false on timeout.
+__device__ __forceinline__ bool slice_handshake(const SymmWorld& w, int slice, unsigned long long seq,
+                                                int* status, int code) {
+  __shared__ int ok_flag;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < w.world) {
+    const int peer = threadIdx.x;
+    if (peer != w.rank) st_release_sys_u64(flag_ptr(w.win[peer], w.rank, slice), seq);
+  }
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < w.world && threadIdx.x != w.rank) {
+    const unsigned long long* f = flag_ptr(w.win[w.rank], threadIdx.x, slice);
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t it = 0;
+    while (ld_acquire_sys_u64(f) < seq) {
+      if ((++it & 63) == 0 && globaltimer_ns() - t0 > RLK_WAIT_LIMIT_NS) {
+        ok_flag = 0;
+        if (status) atomicCAS(status, 0, code);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return ok_flag != 0;
+}
+
+template <int DT>  // 0 = bf16, 1 = fp32
+__device__ __forceinline__ uint4 tree_node(const uint4 a, const uint4 b) {
+  uint4 o;
+  if (DT == 0) {
+    o.x = pack_bf16x2(__fadd_rn(bf16_lo(a.x), bf16_lo(b.x)), __fadd_rn(bf16_hi(a.x), bf16_hi(b.x)));
+    o.y = pack_bf16x2(__fadd_rn(bf16_lo(a.y), bf16_lo(b.y)), __fadd_rn(bf16_hi(a.y), bf16_hi(b.y)));
+    o.z = pack_bf16x2(__fadd_rn(bf16_lo(a.z), bf16_lo(b.z)), __fadd_rn(bf16_hi(a.z), bf16_hi(b.z)));
+    o.w = pack_bf16x2(__fadd_rn(bf16_lo(a.w), bf16_lo(b.w)), __fadd_rn(bf16_hi(a.w), bf16_hi(b.w)));
+  } else {
+    o.x = __float_as_uint(__fadd_rn(__uint_as_float(a.x), __uint_as_float(b.x)));
+    o.y = __float_as_uint(__fadd_rn(__uint_as_float(a.y), __uint_as_float(b.y)));
+    o.z = __float_as_uint(__fadd_rn(__uint_as_float(a.z), __uint_as_float(b.z)));
+    o.w = __float_as_uint(__fadd_rn(__uint_as_float(a.w), __uint_as_float(b.w)));
+  }
+  return o;
+}
+
+// One-shot all-reduce: every rank reduces every slice itself (lowest latency; used for all sizes
+// the engine needs -- activations of a decode step or a training micro-batch).
+// staged != 0: the payload already sits in the local frame (a GEMM wrote it there).
+template <int DT>
+__global__ void __launch_bounds__(kCollThreads)
+all_reduce_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                  long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int staged, int* status) {
+  const unsigned long long seq = effective_seq(w, base_seq);
+  const int nslices = static_cast<int>((nbytes + slice_bytes - 1) / slice_bytes);
+  unsigned char* mine = frame_ptr(w.win[w.rank], w.frame_bytes, frame);
+  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+    const long long off = static_cast<long long>(s) * slice_bytes;
+    const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), nbytes - off) / 16);
+    if (!staged)
+      for (int i = threadIdx.x; i < n16; i += blockDim.x)
+        reinterpret_cast<uint4*>(mine + off)[i] = reinterpret_cast<const uint4*>(src + off)[i];
+    if (!slice_handshake(w, s, seq, status, 401)) continue;
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) {
+      uint4 v[kMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < w.world)
+          v[r] = (r == w.rank) ? reinterpret_cast<const uint4*>(mine + off)[i]
+                               : ld_peer_v4(frame_ptr(w.win[r], w.frame_bytes, frame) + off + 16ll * i);
+#pragma unroll
+      for (int n = kMaxRanks; n > 1; n >>= 1)
+        if (n <= w.world)
+#pragma unroll
+          for (int j = 0; j < n / 2; ++j) v[j] = tree_node<DT>(v[2 * j], v[2 * j + 1]);
+      reinterpret_cast<uint4*>(dst + off)[i] = v[0];
+    }
+  }
+}
+
+// All-gather: dst[r] = rank r's payload (rank order).
+__global__ void __launch_bounds__(kCollThreads)
+all_gather_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                  long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int* status) {
+  const unsigned long long seq = effective_seq(w, base_seq);
+  const int nslices = static_cast<int>((nbytes + slice_bytes - 1) / slice_bytes);
+  unsigned char* mine = frame_ptr(w.win[w.rank], w.frame_bytes, frame);
+  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+    const long long off = static_cast<long long>(s) * slice_bytes;
+    const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), nbytes - off) / 16);
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) {
+      const uint4 v = reinterpret_cast<const uint4*>(src + off)[i];
+      reinterpret_cast<uint4*>(mine + off)[i] = v;
+      reinterpret_cast<uint4*>(dst + w.rank * nbytes + off)[i] = v;
+    }
+    if (!slice_handshake(w, s, seq, status, 402)) continue;
+    for (int r = 0; r < w.world; ++r) {
+      if (r == w.rank) continue;
+      const unsigned char* pf = frame_ptr(w.win[r], w.frame_bytes, frame) + off;
+      for (int i = threadIdx.x; i < n16; i += blockDim.x)
+        reinterpret_cast<uint4*>(dst + r * nbytes + off)[i] = ld_peer_v4(pf + 16ll * i);
+    }
+  }
+}
+
+// Bounded barrier across ranks: everyone publishes seq in slice 0 of a dedicated flag row.
+__global__ void barrier_kernel(const SymmWorld w, unsigned long long base_seq, int* status) {
+  slice_handshake(w, kMaxSlices - 1, effective_seq(w, base_seq), status, 403);
+}
+
+__global__ void epoch_bump_kernel(unsigned long long* epoch) { epoch[0] += 1; }
+
+struct SymmState {
+  SymmWorld w;
+  unsigned char* local;
+  unsigned char* peers[kMaxRanks];
+  unsigned long long seq;
+  int device;
+  unsigned long long* dev_epoch;       // [epoch, stride]
+  int capturing;
+  unsigned long long capture_begin_seq;
+  unsigned long long graph_stride;
+};
+
+}  // namespace rlk
+using namespace rlk;
+
+RLK_API long long rlk_symm_window_bytes(long long frame_bytes) { return kFlagBytes + 2 * frame_bytes; }
+RLK_API int rlk_symm_ipc_handle_bytes() { return static_cast<int>(sizeof(cudaIpcMemHandle_t)); }
+
+// Allocates this rank's window (zeroed) and writes its IPC handle into handle_out.
+RLK_API int rlk_symm_alloc(long long frame_bytes, void** window_out, void* handle_out) {
+  RLK_REQUIRE(frame_bytes > 0 && frame_bytes % 256 == 0, "symm_alloc: frame_bytes must be a positive multiple of 256");
+  void* p = nullptr;
+  RLK_CHECK_CUDA(cudaMalloc(&p, rlk_symm_window_bytes(frame_bytes)));
+  RLK_CHECK_CUDA(cudaMemset(p, 0, rlk_symm_window_bytes(frame_bytes)));
+  RLK_CHECK_CUDA(cudaDeviceSynchronize());
+  cudaIpcMemHandle_t h;
+  RLK_CHECK_CUDA(cudaIpcGetMemHandle(&h, p));
+  memcpy(handle_out, &h, sizeof(h));
+  *window_out = p;
+  return RLK_OK;
+}
+
+// handles: world * handle_bytes, rank order. Returns an opaque state pointer in state_out.
+RLK_API int rlk_symm_create(void* local_window, const void* handles, int world, int rank,
+                            long long frame_bytes, void** state_out) {
+  RLK_REQUIRE(world >= 1 && world <= kMaxRanks && (world & (world - 1)) == 0, "symm_create: world must be 1, 2, 4 or 8");
+  RLK_REQUIRE(rank >= 0 && rank < world, "symm_create: bad rank");
+  SymmState* st = new SymmState();
+  memset(st, 0, sizeof(*st));
+  RLK_CHECK_CUDA(cudaGetDevice(&st->device));
+  st->local = static_cast<unsigned char*>(local_window);
+  st->w.world = world;
+  st->w.rank = rank;
+  st->w.frame_bytes = frame_bytes;
+  for (int r = 0; r < world; ++r) {
+    if (r == rank) {
+      st->peers[r] = st->local;
+    } else {
+      cudaIpcMemHandle_t h;
+      memcpy(&h, static_cast<const unsigned char*>(handles) + r * sizeof(h), sizeof(h));
+      void* p = nullptr;
+      cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) {
+        delete st;
+        return set_error(RLK_ERR_CUDA, "cudaIpcOpenMemHandle(rank %d) failed: %s", r, cudaGetErrorString(e));
+      }
+      st->peers[r] = static_cast<unsigned char*>(p);
+    }
+    st->w.win[r] = st->peers[r];
+  }
+  st->seq = 0;
+  RLK_CHECK_CUDA(cudaMalloc(&st->dev_epoch, 16));
+  RLK_CHECK_CUDA(cudaMemset(st->dev_epoch, 0, 16));
+  st->w.epoch = st->dev_epoch;
+  st->w.use_epoch = 0;
+  *state_out = st;
+  return RLK_OK;
+}
+
+RLK_API int rlk_symm_destroy(void* state, int free_local) {
+  SymmState* st = static_cast<SymmState*>(state);
+  if (!st) return RLK_OK;
+  for (int r = 0; r < st->w.world; ++r)
+    if (r != st->w.rank && st->peers[r]) cudaIpcCloseMemHandle(st->peers[r]);
+  if (free_local && st->local) cudaFree(st->local);
+  if (st->dev_epoch) cudaFree(st->dev_epoch);
+  delete st;
+  return RLK_OK;
+}
+
+// Device pointer of frame f of rank r's window as mapped in this process.
+RLK_API void* rlk_symm_frame_ptr(void* state, int r, int f) {
+  SymmState* st = static_cast<SymmState*>(state);
+  return st->peers[r] + kFlagBytes + f * st->w.frame_bytes;
+}
+RLK_API int rlk_symm_next_frame(void* state) {
+  return static_cast<int>((static_cast<SymmState*>(state)->seq + 1) & 1);
+}
+
+static int slice_bytes_for(long long nbytes) {
+  long long sb = kMinSliceBytes;
+  while ((nbytes + sb - 1) / sb > 1024) sb *= 2;
+  return static_cast<int>(sb);
+}
+static int coll_grid(long long nbytes) {
+  const long long s = (nbytes + slice_bytes_for(nbytes) - 1) / slice_bytes_for(nbytes);
+  const int cap = nbytes > (8 << 20) ? 128 : 64;  // small payloads: leave SMs to overlapping compute
+  return static_cast<int>(s < cap ? (s < 1 ? 1 : s) : cap);
+}
+
+// dtype: 0 = bf16, 1 = fp32. staged: src is ignored, the payload is already in the frame returned
+// by rlk_symm_next_frame() (written there by the producing kernel on the same stream).
+RLK_API int rlk_symm_all_reduce(void* state, const void* src, void* dst, long long nbytes, int dtype,
+                                int staged, void* stream) {
+  SymmState* st = static_cast<SymmState*>(state);
+  RLK_REQUIRE(nbytes > 0 && nbytes % 16 == 0, "all_reduce: byte count must be a positive multiple of 16");
+  RLK_REQUIRE(nbytes <= st->w.frame_bytes, "all_reduce: %lld bytes exceed the frame capacity %lld", nbytes, st->w.frame_bytes);
+  RLK_REQUIRE(dtype == 0 || dtype == 1, "all_reduce: dtype must be 0 (bf16) or 1 (fp32)");
+  st->seq += 1;
+  const int frame = static_cast<int>(st->seq & 1);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned char* sp = static_cast<const unsigned char*>(src);
+  unsigned char* dp = static_cast<unsigned char*>(dst);
+  if (dtype == 0)
+    all_reduce_kernel<0><<<coll_grid(nbytes), kCollThreads, 0, s>>>(st->w, sp, dp, nbytes, slice_bytes_for(nbytes), frame, st->seq, staged, device_status_word());
+  else
+    all_reduce_kernel<1><<<coll_grid(nbytes), kCollThreads, 0, s>>>(st->w, sp, dp, nbytes, slice_bytes_for(nbytes), frame, st->seq, staged, device_status_word());
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+RLK_API int rlk_symm_all_gather(void* state, const void* src, void* dst, long long nbytes, void* stream) {
+  SymmState* st = static_cast<SymmState*>(state);
+  RLK_REQUIRE(nbytes > 0 && nbytes % 16 == 0, "all_gather: byte count must be a positive multiple of 16");
+  RLK_REQUIRE(nbytes <= st->w.frame_bytes, "all_gather: %lld bytes exceed the frame capacity %lld", nbytes, st->w.frame_bytes);
+  st->seq += 1;
+  const int frame = static_cast<int>(st->seq & 1);
+  all_gather_kernel<<<coll_grid(nbytes), kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      st->w, static_cast<const unsigned char*>(src), static_cast<unsigned char*>(dst), nbytes,
+      slice_bytes_for(nbytes), frame, st->seq, device_status_word());
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+RLK_API int rlk_symm_barrier(void* state, void* stream) {
+  SymmState* st = static_cast<SymmState*>(state);
+  st->seq += 1;
+  barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(st->w, st->seq, device_status_word());
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+// ---- CUDA-graph protocol (all ranks must do the same):
+//   rlk_symm_graph_begin(state, capture_stream)      first thing inside the capture
+//   ... collectives on the capture stream ...
+//   n = rlk_symm_graph_end(state, capture_stream)    last thing inside the capture
+//   rlk_symm_graph_commit(state)                     after the capture has ended, before a replay
+//   rlk_symm_graph_replayed(state, k)                after k replays were enqueued
+RLK_API int rlk_symm_graph_begin(void* state, void* stream) {
+  SymmState* st = static_cast<SymmState*>(state);
+  RLK_REQUIRE(!st->capturing, "symm_graph_begin: a capture is already open");
+  st->capturing = 1;
+  st->w.use_epoch = 1;
+  st->capture_begin_seq = st->seq;
+  epoch_bump_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(st->dev_epoch);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+RLK_API long long rlk_symm_graph_end(void* state, void* stream) {
+  SymmState* st = static_cast<SymmState*>(state);
+  if (!st->capturing) return -1;
+  if ((st->seq - st->capture_begin_seq) & 1) rlk_symm_barrier(state, stream);  // keep the stride even
+  st->graph_stride = st->seq - st->capture_begin_seq;
+  st->capturing = 0;
+  st->w.use_epoch = 0;
+  return static_cast<long long>(st->graph_stride);
+}
+
+RLK_API int rlk_symm_graph_commit(void* state) {
+  SymmState* st = static_cast<SymmState*>(state);
+  const unsigned long long vals[2] = {0ull, st->graph_stride};
+  RLK_CHECK_CUDA(cudaMemcpy(st->dev_epoch, vals, 16, cudaMemcpyHostToDevice));
+  return RLK_OK;
+}
+
+RLK_API int rlk_symm_graph_replayed(void* state, long long times) {
+  SymmState* st = static_cast<SymmState*>(state);
+  st->seq += static_cast<unsigned long long>(times) * st->graph_stride;
+  return RLK_OK;
+}

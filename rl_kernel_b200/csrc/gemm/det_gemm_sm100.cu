@@ -38,6 +38,7 @@ struct GemmParams {
   int accumulate;       // 1: C += result (read-modify-write in fp32, rounded to C's dtype)
   int* status;
   int a_box_rows;           // rows of A that TMA brings per tile (128, or fewer when M < 128)
+  int stage_a_bytes;        // shared-memory bytes reserved for the A tile of one stage
   int split_chunks;         // > 1: every canonical chunk is its own tile and writes its bf16 leaf
   long long split_stride;   //      to C + chunk * split_stride (elements); nchunks is 1 then
   // fused LM-head epilogue (tile_n == 128, nchunks == 1): per-(row, tile) softmax statistics
@@ -83,7 +84,8 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * S::kStage);
+  const uint32_t stage_bytes = static_cast<uint32_t>(p.stage_a_bytes) + S::kStageB;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * stage_bytes);
   // bars: full[kStages], empty[kStages], acc_full[2], acc_empty[2], then tmem ptr + abort flag
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -141,8 +143,8 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 101)) break;
           const uint32_t fb = full0 + 8 * s;
           mbar_expect_tx(fb, stage_tx);
-          const uint32_t sa = smem_base + s * S::kStage;
-          const uint32_t sb = sa + S::kStageA;
+          const uint32_t sa = smem_base + s * stage_bytes;
+          const uint32_t sb = sa + p.stage_a_bytes;
           const int k0 = (kb0 + kb) * BK;
           if (!A_MN) {
             tma_load_2d(sa, &tmA, k0, m0, fb);
@@ -176,8 +178,8 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             const uint32_t ph = (it / kStages) & 1;
             if (!mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 103)) break;
             tc_fence_after();
-            const uint32_t sa = smem_base + s * S::kStage;
-            const uint32_t sb = sa + S::kStageA;
+            const uint32_t sa = smem_base + s * stage_bytes;
+            const uint32_t sb = sa + p.stage_a_bytes;
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
               const uint64_t da = A_MN ? umma_desc_sw128(sa + k * 2048, 8192, 1024)
@@ -384,6 +386,12 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   if (p.split_chunks < 1) p.split_chunks = 1;
   p.a_box_rows = BM;
   if (!A_MN && p.M < BM) p.a_box_rows = (p.M + 7) / 8 * 8;  // rows beyond are never stored: skip loading them
+  // The UMMA still addresses 128 A rows; with a short A box the rows past it alias the B tile /
+  // next stage (finite garbage feeding accumulator rows nobody stores), and the stage shrinks so
+  // two CTAs fit on an SM -- more loads in flight for the bandwidth-bound small-M case.
+  p.stage_a_bytes = A_MN ? GemmSmem<BN>::kStageA : (p.a_box_rows * BK * 2 + 1023) / 1024 * 1024;
+  const int smem_bytes = GemmSmem<BN>::kStages * (p.stage_a_bytes + GemmSmem<BN>::kStageB) + 1024 + 256 +
+                         (GemmSmem<BN>::kStageA - p.stage_a_bytes);  // slack: reads past the last stage stay in bounds
   if (!A_MN) rc = make_tmap_2d_sw128(&tmA, A, p.M, p.K, lda, p.a_box_rows, 64, 2);
   else rc = make_tmap_2d_sw128(&tmA, A, p.K, p.M, lda, BK, 64, 2);
   if (rc) return rc;
@@ -393,7 +401,8 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   p.m_tiles = (p.M + BM - 1) / BM;
   p.n_tiles = (p.N + BN - 1) / BN;
   const int tiles = p.m_tiles * p.n_tiles * p.split_chunks;
-  const int grid = tiles < sm_count() ? tiles : sm_count();
+  const int ctas_per_sm = smem_bytes <= 110 * 1024 ? 2 : 1;
+  const int grid = tiles < sm_count() * ctas_per_sm ? tiles : sm_count() * ctas_per_sm;
   auto kfn = det_gemm_kernel<BN, A_MN, B_MN>;
   static bool attr_set[64] = {false};
   int dev = 0;
@@ -403,7 +412,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
                                         GemmSmem<BN>::kBytes));
     attr_set[dev & 63] = true;
   }
-  kfn<<<grid, kGemmThreads, GemmSmem<BN>::kBytes, stream>>>(tmA, tmB, p);
+  kfn<<<grid, kGemmThreads, smem_bytes, stream>>>(tmA, tmB, p);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
