@@ -1,0 +1,96 @@
+"""Attention kernels on a B200: accuracy, decode == training bits, deterministic backward."""
+import math
+
+import pytest
+import torch
+
+from tests.gpu_util import dev, sync_and_check
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+HQ, HKV, D = 8, 2, 128
+G = HQ // HKV
+SCALE = 1.0 / math.sqrt(D)
+
+
+def _inputs(B, S, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    T = B * S
+    q = torch.randn(T, HQ * D, device=dev(), generator=g).to(BF)
+    k = torch.randn(T, HKV * D, device=dev(), generator=g).to(BF)
+    v = torch.randn(T, HKV * D, device=dev(), generator=g).to(BF)
+    return q, k, v
+
+
+def _gold(q, k, v, B, S):
+    qf = q.float().view(B, S, HQ, D).transpose(1, 2)
+    kf = k.float().view(B, S, HKV, D).transpose(1, 2).repeat_interleave(G, 1)
+    vf = v.float().view(B, S, HKV, D).transpose(1, 2).repeat_interleave(G, 1)
+    sc = (qf @ kf.transpose(-1, -2) * SCALE).masked_fill(
+        ~torch.ones(S, S, device=q.device, dtype=torch.bool).tril(), float("-inf"))
+    return sc, vf
+
+
+@pytest.mark.parametrize("S", [128, 320, 1000])
+def test_forward_and_decode_equivalence(S):
+    from rl_kernel_b200.backends import native as nv
+    from rl_kernel_b200.models.qwen3.engine import train_tiles
+
+    B, T = 2, 2 * S
+    q, k, v = _inputs(B, S)
+    o = torch.zeros_like(q)
+    lse = torch.zeros(T, HQ, device=dev())
+    tiles, _ = train_tiles(B, S, HQ, HKV, D, dev())
+    nv.attn_fwd(q, [k], [v], o, lse, tiles, SCALE)
+    sync_and_check()
+    sc, vf = _gold(q, k, v, B, S)
+    ref = (sc.softmax(-1) @ vf).transpose(1, 2).reshape(T, HQ * D)
+    assert (o.float() - ref).abs().max().item() < 0.03
+    assert (lse - sc.logsumexp(-1).transpose(1, 2).reshape(T, HQ)).abs().max().item() < 1e-3
+    # single-token decode of selected positions must reproduce the training rows bit for bit
+    pos = [p for p in (0, 1, 127, 128, 129, S // 2, S - 1) if p < S]
+    n = len(pos)
+    qd = torch.zeros(n * HQ + 128, D, device=dev(), dtype=BF)
+    qd[: n * HQ] = torch.stack([q.view(B, S, HQ, D)[1, p] for p in pos]).reshape(n * HQ, D)
+    t2 = [[i * HQ + hk * G, 0, G, S, hk * D, p, 0, S, i * HQ + hk * G, 1, 0, 0] for i, p in enumerate(pos) for hk in range(HKV)]
+    want_o = torch.stack([o.view(B, S, HQ, D)[1, p] for p in pos])
+    want_l = torch.stack([lse.view(B, S, HQ)[1, p] for p in pos])
+    for decode in (False, True):
+        od, ld = torch.zeros_like(qd), torch.zeros(n * HQ + 128, device=dev())
+        nv.attn_fwd(qd, [k], [v], od, ld, torch.tensor(t2, dtype=torch.int32, device=dev()), SCALE, decode=decode)
+        sync_and_check()
+        assert torch.equal(od[: n * HQ].view(n, HQ, D), want_o)
+        assert torch.equal(ld[: n * HQ].view(n, HQ), want_l)
+
+
+@pytest.mark.parametrize("S", [128, 320, 1000])
+def test_backward(S):
+    from rl_kernel_b200.backends import native as nv
+    from rl_kernel_b200.models.qwen3.engine import train_tiles
+
+    B, T = 2, 2 * S
+    q, k, v = _inputs(B, S, 1)
+    o, lse = torch.zeros_like(q), torch.zeros(T, HQ, device=dev())
+    tiles, kvt = train_tiles(B, S, HQ, HKV, D, dev())
+    nv.attn_fwd(q, [k], [v], o, lse, tiles, SCALE)
+    do = torch.randn(T, HQ * D, device=dev()).to(BF)
+    delta = torch.empty(T, HQ, device=dev())
+    grads = []
+    for _ in range(2):
+        dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+        nv.attn_bwd_delta(o, do, delta, T, HQ)
+        nv.attn_bwd_dq(q, do, k, v, lse, delta, dq, tiles, SCALE)
+        nv.attn_bwd_dkv(q, do, k, v, lse, delta, dk, dv, kvt, SCALE)
+        sync_and_check()
+        grads.append((dq, dk, dv))
+    for a, b in zip(*grads):
+        assert torch.equal(a, b), "backward is not run-to-run deterministic"
+    qf = q.float().view(B, S, HQ, D).transpose(1, 2).requires_grad_(True)
+    k0 = k.float().view(B, S, HKV, D).transpose(1, 2).requires_grad_(True)
+    v0 = v.float().view(B, S, HKV, D).transpose(1, 2).requires_grad_(True)
+    sc = (qf @ k0.repeat_interleave(G, 1).transpose(-1, -2) * SCALE).masked_fill(
+        ~torch.ones(S, S, device=dev(), dtype=torch.bool).tril(), float("-inf"))
+    (sc.softmax(-1) @ v0.repeat_interleave(G, 1)).backward(do.float().view(B, S, HQ, D).transpose(1, 2))
+    for got, want in zip(grads[0], (qf.grad, k0.grad, v0.grad)):
+        w = want.transpose(1, 2).reshape(got.shape)
+        assert (got.float() - w).abs().max().item() < 0.02 * w.abs().max().item() + 0.02

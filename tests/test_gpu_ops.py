@@ -1,0 +1,276 @@
+"""Row-wise and element-wise sm_100a kernels against fp32 PyTorch references."""
+import pytest
+import torch
+
+from tests.gpu_util import dev, sync_and_check
+
+pytestmark = pytest.mark.gpu
+BF = torch.bfloat16
+
+
+def _rms(x, w, eps=1e-6):
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
+
+
+def test_rmsnorm_forward_backward():
+    from rl_kernel_b200.backends import native as nv
+
+    rows, H = 300, 4096
+    x = torch.randn(rows, H, device=dev()).to(BF)
+    w = (1 + 0.1 * torch.randn(H, device=dev())).to(BF)
+    res = torch.randn(rows, H, device=dev()).to(BF)
+    y = torch.empty_like(x)
+    nv.rmsnorm_fwd(x, w, y, 1e-6)
+    sync_and_check()
+    assert (y.float() - _rms(x.float(), w.float())).abs().max().item() < 0.03
+    y1 = torch.empty(7, H, device=dev(), dtype=BF)
+    nv.rmsnorm_fwd(x[:7].contiguous(), w, y1, 1e-6)
+    assert torch.equal(y1, y[:7]), "rmsnorm must be batch-invariant"
+    y2, ro = torch.empty_like(x), torch.empty_like(x)
+    nv.rmsnorm_fwd(x, w, y2, 1e-6, res=res, res_out=ro)
+    s = (x.float() + res.float()).to(BF)
+    assert torch.equal(ro, s)
+    assert (y2.float() - _rms(s.float(), w.float())).abs().max().item() < 0.03
+    for Hh in (256, 1024, 16384):   # few and many chunks per thread
+        xx = torch.randn(5, Hh, device=dev()).to(BF)
+        ww = torch.ones(Hh, device=dev(), dtype=BF)
+        yy = torch.empty_like(xx)
+        nv.rmsnorm_fwd(xx, ww, yy, 1e-6)
+        assert (yy.float() - _rms(xx.float(), ww.float())).abs().max().item() < 0.03
+    dy = torch.randn(rows, H, device=dev()).to(BF)
+    dres = torch.randn(rows, H, device=dev()).to(BF)
+    dx, dw = torch.empty_like(x), torch.zeros(H, device=dev(), dtype=BF)
+    scratch = torch.empty(nv.rmsnorm_bwd_scratch_elems(rows, H), device=dev())
+    nv.rmsnorm_bwd(x, w, dy, dx, scratch, 1e-6, dres=dres, dw_bf16=dw)
+    sync_and_check()
+    xf, wf = x.float().requires_grad_(True), w.float().requires_grad_(True)
+    _rms(xf, wf).backward(dy.float())
+    assert (dx.float() - (xf.grad + dres.float())).abs().max().item() < 0.05
+    assert (dw.float() - wf.grad).abs().max().item() < 0.01 * wf.grad.abs().max().item() + 0.05
+
+
+def _tables(D=128, theta=1e6, n=4096):
+    inv = 1.0 / (theta ** (torch.arange(0, D, 2, device=dev()).double() / D))
+    ang = torch.arange(n, device=dev()).double()[:, None] * inv[None]
+    return ang.cos().float().contiguous(), ang.sin().float().contiguous()
+
+
+def test_qk_norm_rope_forward_backward():
+    from rl_kernel_b200.backends import native as nv
+
+    T, Hq, Hkv, D = 200, 8, 2, 128
+    G = Hq // Hkv
+    W = (Hq + 2 * Hkv) * D
+    qkv = torch.randn(T, W, device=dev()).to(BF)
+    qw = (1 + 0.1 * torch.randn(D, device=dev())).to(BF)
+    kw = (1 + 0.1 * torch.randn(D, device=dev())).to(BF)
+    pos = (torch.arange(T, device=dev(), dtype=torch.int32) * 3) % 77
+    cos, sin = _tables()
+    qo = torch.empty(T, Hq * D, device=dev(), dtype=BF)
+    ko = torch.empty(T, Hkv * D, device=dev(), dtype=BF)
+    vo = torch.empty(T, Hkv * D, device=dev(), dtype=BF)
+    nv.qk_norm_rope_fwd(qkv, qw, kw, cos, sin, pos, qo, ko, vo, Hq=Hq, Hkv=Hkv, eps=1e-6)
+    sync_and_check()
+    # the activation is GQA-group-major: [G q heads | k | v] per KV head
+    grp = qkv.view(T, Hkv, G + 2, D)
+    qf, kf, vf = grp[:, :, :G].reshape(T, Hq, D).float(), grp[:, :, G].float(), grp[:, :, G + 1]
+
+    def ref(x, w):
+        n = _rms(x, w)
+        c, s = cos[pos.long()][:, None], sin[pos.long()][:, None]
+        a, b = n[..., :64], n[..., 64:]
+        return torch.cat([a * c - b * s, b * c + a * s], -1)
+
+    assert (qo.float().view(T, Hq, D) - ref(qf, qw.float())).abs().max().item() < 0.03
+    assert (ko.float().view(T, Hkv, D) - ref(kf, kw.float())).abs().max().item() < 0.03
+    assert torch.equal(vo.view(T, Hkv, D), vf)
+    dq = torch.randn(T, Hq * D, device=dev()).to(BF)
+    dk = torch.randn(T, Hkv * D, device=dev()).to(BF)
+    dv = torch.randn(T, Hkv * D, device=dev()).to(BF)
+    dqkv = torch.empty_like(qkv)
+    dqw, dkw = torch.zeros(D, device=dev(), dtype=BF), torch.zeros(D, device=dev(), dtype=BF)
+    scr = torch.empty(nv.qk_norm_rope_bwd_scratch_elems(T), device=dev())
+    nv.qk_norm_rope_bwd(qkv, qw, kw, cos, sin, pos, dq, dk, dv, dqkv, scr, dqw, dkw, Hq=Hq, Hkv=Hkv, eps=1e-6,
+                        accumulate_dw=False)
+    sync_and_check()
+    q2, k2 = qf.clone().requires_grad_(True), kf.clone().requires_grad_(True)
+    qwf, kwf = qw.float().requires_grad_(True), kw.float().requires_grad_(True)
+    (ref(q2, qwf) * dq.float().view(T, Hq, D)).sum().backward()
+    (ref(k2, kwf) * dk.float().view(T, Hkv, D)).sum().backward()
+    dg = dqkv.view(T, Hkv, G + 2, D)
+    assert (dg[:, :, :G].reshape(T, Hq, D).float() - q2.grad).abs().max().item() < 0.05
+    assert (dg[:, :, G].float() - k2.grad).abs().max().item() < 0.05
+    assert torch.equal(dg[:, :, G + 1].reshape(T, Hkv * D), dv)
+    assert (dqw.float() - qwf.grad).abs().max().item() < 0.01 * qwf.grad.abs().max().item() + 0.05
+    assert (dkw.float() - kwf.grad).abs().max().item() < 0.01 * kwf.grad.abs().max().item() + 0.05
+
+
+@pytest.mark.parametrize("blk", [None, 192])
+def test_swiglu(blk):
+    from rl_kernel_b200.backends import native as nv
+    from rl_kernel_b200.reference.activation.swiglu import swiglu_packed_reference
+
+    rows, I = 100, 1536
+    gu = torch.randn(rows, 2 * I, device=dev()).to(BF)
+    out = torch.empty(rows, I, device=dev(), dtype=BF)
+    nv.swiglu_fwd(gu, out, I, blk)
+    sync_and_check()
+    assert (out.float() - swiglu_packed_reference(gu.float(), blk)).abs().max().item() < 0.05
+    dout = torch.randn(rows, I, device=dev()).to(BF)
+    dgu = torch.empty_like(gu)
+    nv.swiglu_bwd(gu, dout, dgu, I, blk)
+    sync_and_check()
+    g = gu.float().requires_grad_(True)
+    swiglu_packed_reference(g, blk).backward(dout.float())
+    assert (dgu.float() - g.grad).abs().max().item() < 0.05
+
+
+def test_embedding():
+    from rl_kernel_b200.backends import native as nv
+
+    V, H, T = 1000, 256, 500
+    ids = torch.randint(0, V, (T,), device=dev())
+    w = torch.randn(V, H, device=dev()).to(BF)
+    out = torch.empty(T, H, device=dev(), dtype=BF)
+    nv.embedding_fwd(ids, w, out)
+    assert torch.equal(out, w[ids])
+    half = torch.empty_like(out)
+    nv.embedding_fwd(ids, w[500:].contiguous(), half, vocab_start=500)   # vocab-parallel shard
+    assert torch.equal(half, w[ids] * (ids >= 500)[:, None])
+    dy = torch.randn(T, H, device=dev()).to(BF)
+    runs = []
+    for _ in range(2):
+        dw = torch.zeros(V, H, device=dev(), dtype=BF)
+        sid, order = torch.sort(ids, stable=True)
+        nv.embedding_bwd(sid, order, dy, dw)
+        sync_and_check()
+        runs.append(dw)
+    assert torch.equal(runs[0], runs[1])
+    ref = torch.zeros(V, H, device=dev()).index_add_(0, ids, dy.float())
+    assert (runs[0].float() - ref).abs().max().item() < 0.05
+
+
+@pytest.mark.parametrize("temp", [1.0, 0.7])
+def test_logp_fused_equals_from_logits_and_vocab_parallel(temp):
+    from rl_kernel_b200.backends import native as nv
+
+    T, H, V = 333, 512, 5000
+    h = torch.randn(T, H, device=dev()).to(BF)
+    w = (torch.randn(V, H, device=dev()) * 0.05).to(BF)
+    tg = torch.randint(0, V, (T,), device=dev())
+    nt = (V + 127) // 128
+
+    def fused(hh, tt, shards):
+        n = hh.shape[0]
+        stats = torch.zeros(n, nt, 2, device=dev())
+        tl = torch.zeros(n, device=dev())
+        for start, ws in shards:
+            nv.lmhead_logp_stats(hh, ws, tt, stats, tl, vocab_start=start, inv_temp=1 / temp)
+        lp, lse = torch.empty(n, device=dev()), torch.empty(n, device=dev())
+        nv.logp_merge(stats, tl, lp, lse)
+        sync_and_check()
+        return lp, lse
+
+    lp, lse = fused(h, tg, [(0, w)])
+    logits = torch.empty(T, V, device=dev(), dtype=BF)
+    nv.det_gemm(h, w, logits, M=T, N=V, K=H)
+    stats2, tl2 = torch.zeros(T, nt, 2, device=dev()), torch.zeros(T, device=dev())
+    nv.logits_tile_stats(logits, tg, stats2, tl2, vocab_start=0, inv_temp=1 / temp)
+    lp2, lse2 = torch.empty(T, device=dev()), torch.empty(T, device=dev())
+    nv.logp_merge(stats2, tl2, lp2, lse2)
+    sync_and_check()
+    assert torch.equal(lp, lp2) and torch.equal(lse, lse2), "fused LM head and from-logits paths differ"
+    ref = torch.log_softmax(logits.float() / temp, -1).gather(1, tg[:, None])[:, 0]
+    assert (lp - ref).abs().max().item() < 1e-4
+    assert torch.equal(fused(h[:3].contiguous(), tg[:3].contiguous(), [(0, w)])[0], lp[:3])
+    assert torch.equal(fused(h, tg, [(0, w[:2560].contiguous()), (2560, w[2560:].contiguous())])[0], lp)
+    # gradient of the logits
+    g = torch.randn(T, device=dev())
+    lc = logits.clone()
+    nv.dlogits_(lc, tg, lse2, g, vocab_start=0, inv_temp=1 / temp)
+    sync_and_check()
+    z = (logits.float() / temp).requires_grad_(True)
+    (torch.log_softmax(z, -1).gather(1, tg[:, None])[:, 0] * g).sum().backward()
+    assert (lc.float() - z.grad / temp).abs().max().item() < 0.02
+
+
+def test_grpo_loss_and_advantages():
+    from rl_kernel_b200.backends import native as nv
+    from rl_kernel_b200.reference.loss import grpo_loss_from_logps
+
+    B, L = 16, 100
+    lp = -torch.rand(B, L, device=dev())
+    old = lp + 0.3 * torch.randn(B, L, device=dev())
+    refl = lp + 0.1 * torch.randn(B, L, device=dev())
+    adv = torch.randn(B, device=dev())
+    mask = torch.rand(B, L, device=dev()) > 0.3
+    cnt = int(mask.sum())
+    r = nv.grpo_loss(lp, old, refl, adv, mask.to(torch.uint8), clip_lo=0.2, clip_hi=0.2, beta=0.01, inv_norm=1.0 / cnt)
+    sync_and_check()
+    lpr = lp.clone().requires_grad_(True)
+    loss, pol, kl = grpo_loss_from_logps(lpr, old, refl, adv, mask, clip_eps=0.2, beta=0.01)
+    loss.backward()
+    assert abs(r["totals"][4].item() - loss.item()) < 1e-5
+    assert (r["dlogp"] - lpr.grad).abs().max().item() < 1e-6
+    rw = torch.rand(4, 8, device=dev())
+    a = nv.group_advantages(rw.view(-1).contiguous(), 4, 8, 1e-6).view(4, 8)
+    assert (a - (rw - rw.mean(1, keepdim=True)) / rw.std(1, unbiased=False, keepdim=True)).abs().max().item() < 1e-5
+
+
+def test_sampling():
+    from rl_kernel_b200.backends import native as nv
+
+    rows, V = 64, 151936
+    lg = (torch.randn(rows, V, device=dev()) * 2).to(BF)
+    ids, val = torch.empty(rows, device=dev(), dtype=torch.int64), torch.empty(rows, device=dev())
+    nv.sample_gumbel(lg, ids, val, vocab_start=0, inv_temp=1.0, seed=1, step=0, greedy=True)
+    sync_and_check()
+    assert torch.equal(ids, lg.float().argmax(-1))
+    # the draw does not depend on how the vocabulary is sharded
+    ia, va = torch.empty_like(ids), torch.empty_like(val)
+    nv.sample_gumbel(lg, ia, va, vocab_start=0, inv_temp=1.0, seed=5, step=9)
+    hv = V // 2
+    i1, v1, i2, v2 = torch.empty_like(ids), torch.empty_like(val), torch.empty_like(ids), torch.empty_like(val)
+    nv.sample_gumbel(lg[:, :hv], i1, v1, vocab_start=0, inv_temp=1.0, seed=5, step=9)
+    nv.sample_gumbel(lg[:, hv:], i2, v2, vocab_start=hv, inv_temp=1.0, seed=5, step=9)
+    sync_and_check()
+    assert torch.equal(torch.where(v1 >= v2, i1, i2), ia)
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0, -2, -3, -4, -5]], device=dev()).to(BF).repeat(8192, 1).contiguous()
+    oi = torch.empty(8192, device=dev(), dtype=torch.int64)
+    nv.sample_gumbel(small, oi, None, vocab_start=0, inv_temp=1.0, seed=7, step=3)
+    sync_and_check()
+    freq = torch.bincount(oi, minlength=8).float() / 8192
+    assert (freq - torch.softmax(small[0].float(), -1)).abs().max().item() < 0.03
+
+
+def test_adamw_and_exact_sumsq():
+    from rl_kernel_b200.backends import native as nv
+
+    n = 100003
+    master = torch.randn(n, device=dev())
+    m, v = torch.zeros(n, device=dev()), torch.zeros(n, device=dev())
+    g = torch.randn(n, device=dev()).to(BF)
+    pb = master.to(BF)
+    pr = torch.nn.Parameter(master.clone())
+    opt = torch.optim.AdamW([pr], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for st in (1, 2):
+        nv.adamw(master, m, v, g, pb, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=st)
+        pr.grad = g.float()
+        opt.step()
+    sync_and_check()
+    assert (master - pr.data).abs().max().item() < 1e-5
+    assert torch.equal(pb, master.to(BF))
+    e = torch.arange(256, device=dev()).clamp(min=1).double()
+    wts = torch.pow(2.0, 2 * (e - 134))
+    wts[255] = 0
+
+    def ss(parts):
+        bins = torch.zeros(256, device=dev(), dtype=torch.int64)
+        for p in parts:
+            nv.sumsq_bins(p, bins)
+        sync_and_check()
+        return (bins.double() * wts).sum().item()
+
+    whole = ss([g])
+    assert whole == ss([g[:1000], g[1000:50000], g[50000:]]), "sum of squares must not depend on the partition"
+    assert abs(whole - g.double().pow(2).sum().item()) < 1e-6 * whole
