@@ -18,7 +18,10 @@
 // (csrc/cuda/gemm/det_gemm_kernel.cu:527-602) with one kernel template.
 #include "rlk/host.h"
 #include "rlk/logp_contract.cuh"
+#include "rlk/no_alloc.h"
 #include "rlk/ptx.cuh"
+
+#include <mutex>
 
 namespace rlk {
 
@@ -531,6 +534,62 @@ RLK_API int rlk_det_gemm_split(const void* A, const void* B, void* C, void* scra
   const long long n = static_cast<long long>(M) * (N / 8);
   chunk_tree_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(
       static_cast<const __nv_bfloat16*>(scratch), p.split_stride, static_cast<__nv_bfloat16*>(C), M, N, ldc, nchunks);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+// ---- the variant that allocates nothing (see rlk/no_alloc.h for the contract) ----------------
+// The partial results of the chunks live in this array, which is part of the library image.  Its
+// name is a host-side stand-in in host code, not a device address: the address the kernels get is
+// looked up once per device below.
+static __device__ __align__(256) unsigned char g_split_static_scratch[RLK_STATIC_SCRATCH_BYTES];
+
+RLK_API int rlk_det_gemm_split_static(const void* A, const void* B, void* C, int M, int N, int K,
+                                      long long lda, long long ldb, long long ldc, int nchunks,
+                                      int tile_n, void* stream) {
+  using namespace rlk;
+  RLK_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0, "det_gemm_split_static: bad shape");
+  RLK_REQUIRE(nchunks == 2 || nchunks == 4 || nchunks == 8, "det_gemm_split_static: nchunks must be 2, 4 or 8");
+  RLK_REQUIRE(K % (nchunks * 64) == 0, "det_gemm_split_static: K/nchunks must be a multiple of 64");
+  RLK_REQUIRE((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * 2) % 16 == 0,
+              "det_gemm_split_static: C must be 16-byte aligned with a 16-byte multiple pitch");
+  const long long need = 2ll * nchunks * M * ldc;
+  RLK_REQUIRE(need <= RLK_STATIC_SCRATCH_BYTES,
+              "det_gemm_split_static: nchunks*M*ldc*2 = %lld bytes exceeds the built-in scratch of %lld bytes; "
+              "use rlk_det_gemm_split with your own scratch", need, (long long)RLK_STATIC_SCRATCH_BYTES);
+  // once per device, with that device current: the device address of the built-in array
+  static unsigned char* dev_ptr[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  RLK_CHECK_CUDA(cudaGetDevice(&dev));
+  RLK_REQUIRE(dev >= 0 && dev < 64, "det_gemm_split_static: device index out of range");
+  unsigned char* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!dev_ptr[dev]) {
+      void* ptr = nullptr;
+      RLK_CHECK_CUDA(cudaGetSymbolAddress(&ptr, g_split_static_scratch));
+      dev_ptr[dev] = static_cast<unsigned char*>(ptr);
+    }
+    scratch = dev_ptr[dev];
+  }
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.nchunks = 1;
+  p.kb_per_chunk = K / nchunks / 64;
+  p.C = scratch; p.ldc = ldc;
+  p.status = nullptr;  // no status word: nothing may be allocated here
+  p.split_chunks = nchunks;
+  p.split_stride = static_cast<long long>(M) * ldc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc;
+  if (tile_n == 32) rc = launch_gemm<32, false, false>(A, B, p, lda, ldb, s);
+  else if (tile_n == 128) rc = launch_gemm<128, false, false>(A, B, p, lda, ldb, s);
+  else rc = launch_gemm<64, false, false>(A, B, p, lda, ldb, s);
+  if (rc) return rc;
+  const long long n = static_cast<long long>(M) * (N / 8);
+  chunk_tree_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(
+      reinterpret_cast<const __nv_bfloat16*>(scratch), p.split_stride, static_cast<__nv_bfloat16*>(C), M, N, ldc, nchunks);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
