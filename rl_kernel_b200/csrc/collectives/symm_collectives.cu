@@ -362,3 +362,11 @@ RLK_API int rlk_symm_graph_replayed(void* state, long long times) {
   st->seq += static_cast<unsigned long long>(times) * st->graph_stride;
   return RLK_OK;
 }
+
+// Sequence-number access for recovery after a timed-out collective: the ranks agree on the
+// maximum over the host (torch.distributed) and continue from there.
+RLK_API long long rlk_symm_get_seq(void* state) { return static_cast<long long>(static_cast<SymmState*>(state)->seq); }
+RLK_API int rlk_symm_set_seq(void* state, long long seq) {
+  static_cast<SymmState*>(state)->seq = static_cast<unsigned long long>(seq);
+  return RLK_OK;
+}

@@ -192,6 +192,19 @@ class SymmetricMemoryCollective:
         if self.world > 1:
             self._lib.rlk_symm_graph_replayed(self._state, c_longlong(times))
 
+    def resync(self) -> int:
+        """After a ``CollectiveTimeout``: agree (on the host) on the highest sequence number any
+        rank reached, rounded up to an even value so every rank also agrees on the frame parity."""
+        if self.world == 1:
+            return 0
+        self._lib.rlk_symm_get_seq.restype = c_longlong
+        torch.cuda.synchronize(self.device)
+        t = torch.tensor([int(self._lib.rlk_symm_get_seq(self._state))], dtype=torch.int64, device=self.device)
+        self._dist.all_reduce(t, op=self._dist.ReduceOp.MAX, group=self.group)
+        seq = (int(t.item()) + 2) // 2 * 2
+        self._lib.rlk_symm_set_seq(self._state, c_longlong(seq))
+        return seq
+
     def close(self) -> None:
         if not self._closed and self.world > 1 and self._state:
             torch.cuda.synchronize(self.device)

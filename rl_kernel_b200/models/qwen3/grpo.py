@@ -84,9 +84,24 @@ class AdamW:
             self.ctx.collective.all_reduce_int_(self.bins)
         return (self.bins.double() * self._bin_w).sum().sqrt()
 
+    def _sync_partial_replicated_grads(self) -> None:
+        """q_norm / k_norm gains are replicated but each TP rank only saw its own heads: sum the
+        partial gradients over TP (fixed tree) so every rank holds the same full gradient."""
+        if self.ctx.tp_size == 1:
+            return
+        names = [n for n in self.p.slots if n.endswith((".qn", ".kn"))]
+        buf = torch.cat([self.p.g[n].reshape(-1) for n in names]).contiguous()
+        self.ctx.collective.all_reduce_(buf)
+        off = 0
+        for n in names:
+            k = self.p.g[n].numel()
+            self.p.g[n].copy_(buf[off:off + k].view_as(self.p.g[n]))
+            off += k
+
     def step(self) -> None:
         c = self.cfg
         self.step_count += 1
+        self._sync_partial_replicated_grads()
         gn = self.grad_norm()
         self.last_grad_norm.copy_(gn.reshape(1))
         if c.max_grad_norm > 0:
@@ -216,12 +231,21 @@ class GRPOTrainer:
                 self._tok.copy_(snap[0]); self._pos.copy_(snap[1]); self._col.copy_(snap[2])
                 self._graph = torch.cuda.CUDAGraph()
                 n0 = nv.LAUNCH_COUNT
+                coll = self.ctx.collective
                 with torch.cuda.graph(self._graph):
-                    self._decode_once(step_seed)
+                    if coll is not None:
+                        with coll.graph_capture():
+                            self._decode_once(step_seed)
+                    else:
+                        self._decode_once(step_seed)
+                if coll is not None:
+                    coll.graph_commit()
                 self.graph_launches = nv.LAUNCH_COUNT - n0
                 self._tok.copy_(snap[0]); self._pos.copy_(snap[1]); self._col.copy_(snap[2])
             for _ in range(R - 1):
                 self._graph.replay()
+            if self.ctx.collective is not None:
+                self.ctx.collective.graph_replayed(R - 1)
             nv.LAUNCH_COUNT += (R - 1) * self.graph_launches
         else:
             for _ in range(R - 1):

@@ -1,0 +1,159 @@
+"""Two-GPU tests: fixed-order collectives on symmetric memory, tensor-parallel bit invariance,
+and a bounded wait that runs out without hanging the GPU.  Each test owns its worker processes
+(NCCL bootstrap on 127.0.0.1); NVLS is off and the kernels use plain peer loads."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _init(rank, world, port):
+    import torch.distributed as dist
+
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", rank))
+    return dist
+
+
+def _collective_worker(rank, world, port, out):
+    dist = _init(rank, world, port)
+    from rl_kernel_b200.backends import extension as ext
+    from rl_kernel_b200.distributed import balanced_tree_sum
+    from rl_kernel_b200.distributed.transports.symm import SymmetricMemoryCollective
+
+    dev = torch.device("cuda", rank)
+    coll = SymmetricMemoryCollective(None, dev, frame_bytes=64 << 20)
+    ok = True
+    for it, (n, dtype) in enumerate([(8, torch.bfloat16), (4096 * 64, torch.bfloat16), (1 << 22, torch.float32),
+                                     (12288 * 1024, torch.bfloat16), (1000 * 8, torch.bfloat16)] * 4):
+        g = torch.Generator(device="cuda").manual_seed(100 + it)
+        parts = [torch.randn(n, device=dev, generator=g).to(dtype) for _ in range(world)]   # same on all ranks
+        want = balanced_tree_sum(parts, dtype)
+        got = coll.all_reduce(parts[rank])
+        ok &= torch.equal(got, want)
+        ag = coll.all_gather(parts[rank])
+        ok &= all(torch.equal(ag[r], parts[r]) for r in range(world))
+    # staged all-reduce: the producer writes straight into the symmetric frame
+    x = torch.full((256, 128), float(rank + 1), device=dev, dtype=torch.bfloat16)
+    st = coll.staging_view(x.shape, x.dtype)
+    st.copy_(x)
+    res = coll.all_reduce_staged(st, torch.empty_like(x))
+    ok &= bool((res == float(sum(range(1, world + 1)))).all())
+    # CUDA graph replay keeps the sequence numbers moving
+    buf = torch.ones(4096, device=dev, dtype=torch.float32)
+    s = torch.cuda.Stream(dev)
+    s.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(s):
+        coll.all_reduce_(buf)
+    torch.cuda.current_stream(dev).wait_stream(s)
+    buf.fill_(1.0)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph), coll.graph_capture():
+        coll.all_reduce_(buf)
+    coll.graph_commit()
+    for _ in range(5):
+        graph.replay()
+    coll.graph_replayed(5)
+    torch.cuda.synchronize(dev)
+    ok &= bool((buf == float(world) ** 5).all())
+    ok &= bool(torch.equal(coll.all_reduce(torch.ones(8, device=dev)), torch.full((8,), float(world), device=dev)))
+    ok &= ext.poll_status(dev) == 0
+    coll.close()
+    if rank == 0:
+        torch.save(ok, out)
+    dist.destroy_process_group()
+
+
+def test_symmetric_collectives(tmp_path):
+    out = str(tmp_path / "ok.pt")
+    mp.spawn(_collective_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    assert torch.load(out)
+
+
+def _timeout_worker(rank, world, port, out):
+    dist = _init(rank, world, port)
+    from rl_kernel_b200.distributed import CollectiveTimeout
+    from rl_kernel_b200.distributed.transports.symm import SymmetricMemoryCollective
+
+    dev = torch.device("cuda", rank)
+    coll = SymmetricMemoryCollective(None, dev, frame_bytes=1 << 20)
+    x = torch.ones(1024, device=dev)
+    coll.all_reduce_(x)
+    raised = False
+    if rank == 0:
+        coll.all_reduce_(x)          # rank 1 never joins this one: the device wait must give up
+        try:
+            coll.raise_on_timeout()
+        except CollectiveTimeout:
+            raised = True
+    dist.barrier()                   # rank 1 learns on the host that the step is over
+    coll.resync()
+    y = torch.ones(1024, device=dev)
+    coll.all_reduce_(y)              # the context is still usable on both ranks
+    torch.cuda.synchronize(dev)
+    fine = bool((y == float(world)).all())
+    coll.close()
+    if rank == 0:
+        torch.save((raised, fine), out)
+    dist.destroy_process_group()
+
+
+def test_bounded_wait_reports_instead_of_hanging(tmp_path):
+    out = str(tmp_path / "t.pt")
+    mp.spawn(_timeout_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    raised, fine = torch.load(out)
+    assert raised, "a missing peer must surface as CollectiveTimeout"
+    assert fine, "collectives must work again after resync"
+
+
+def _tp_worker(rank, world, port, out):
+    dist = _init(rank, world, port)
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
+    from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context
+
+    dev = torch.device("cuda", rank)
+    spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+    w = Qwen3DenseWeights.synthetic(spec, seed=3)
+    ctx = build_parallel_context(world, 1, dev)
+    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=48, micro_batch_seqs=4, lr=1e-4)
+    tr = GRPOTrainer(spec, cfg, dev, ctx=ctx, weights=w)
+    prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5)).to(dev)
+    res = tr.step(prompts, step_index=0)
+    torch.cuda.synchronize(dev)
+    if rank == 0:
+        torch.save({k: res[k].cpu() for k in ("tokens", "old_logp", "train_logp", "grad_norm")}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp2_matches_tp1_bitwise(tmp_path):
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
+
+    out = str(tmp_path / "tp2.pt")
+    mp.spawn(_tp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    tp2 = torch.load(out)
+    dev = torch.device("cuda:0")
+    spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+    w = Qwen3DenseWeights.synthetic(spec, seed=3)
+    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=48, micro_batch_seqs=4, lr=1e-4)
+    tr = GRPOTrainer(spec, cfg, dev, weights=w)
+    prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5)).to(dev)
+    tp1 = tr.step(prompts, step_index=0)
+    assert torch.equal(tp2["tokens"], tp1["tokens"].cpu())
+    assert torch.equal(tp2["old_logp"], tp1["old_logp"].cpu())
+    assert torch.equal(tp2["train_logp"], tp1["train_logp"].cpu())
+    assert torch.equal(tp2["train_logp"], tp2["old_logp"])
