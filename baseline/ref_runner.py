@@ -1,0 +1,153 @@
+"""Child process of the reference arm: a GRPO step built ONLY from the reference's public API.
+
+    rollout : Qwen3DenseBIModel.forward (prefill) + .decode_step with its StatefulKVCache,
+              support restriction by rl_engine.ops.sampling.policy.sampling_keep_mask
+    scoring : Qwen3DenseBIModel.forward(target_ids=...) -> selected_logp   (reference policy + train pass)
+    loss    : compute_policy_ratio / compute_reference_kl / masked_mean (rl_engine.validation.common)
+    update  : torch autograd through the reference's operator profile + torch.optim.AdamW
+Same synthetic data shape as the main arm: 8 prompts x group 8, prompt 512 + response 1024.
+Prints one JSON line; any failure is reported as {"impl": "reference", "unavailable": ...}.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import signal
+import sys
+import time
+
+PROMPTS, GROUP, PROMPT_LEN = 8, 8, 512
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--steps", type=int, default=1)
+    ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--response-len", type=int, default=1024)
+    ap.add_argument("--layers", type=int, default=0)
+    ap.add_argument("--micro-batch", type=int, default=2)
+    ap.add_argument("--step-timeout", type=int, default=2400)
+    a = ap.parse_args()
+    try:
+        out = run(a)
+    except BaseException as exc:  # noqa: BLE001 - reported to the parent
+        out = {"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
+    print(json.dumps(out), flush=True)
+    return 0
+
+
+def run(a) -> dict:
+    import torch
+
+    import rl_engine  # noqa: F401  (must be the reference: the parent set PYTHONPATH)
+    from rl_engine.models.qwen3.reference import Qwen3DenseBIModel, Qwen3DenseWeights, load_profile_ops
+    from rl_engine.models.qwen3.spec import Qwen3DenseSpec
+    from rl_engine.ops.sampling.policy import sampling_keep_mask
+    from rl_engine.validation.common import compute_policy_ratio, compute_reference_kl, masked_mean
+
+    if "baseline/_ref" not in rl_engine.__file__.replace("\\", "/"):
+        raise RuntimeError(f"imported {rl_engine.__file__}, not the reference install")
+    dev = torch.device("cuda:0")
+    spec = Qwen3DenseSpec.from_manifest()
+    if a.layers:
+        import dataclasses
+
+        spec = dataclasses.replace(spec, num_hidden_layers=a.layers)
+    ops = load_profile_ops("triton_cuda_bf16")
+    weights = Qwen3DenseWeights.synthetic(spec, device=dev, dtype=torch.bfloat16, seed=1234)
+    for k, t in weights.tensors.items():
+        if t.dim() == 2:
+            t.mul_(0.02)
+    ref_weights = Qwen3DenseWeights({k: v.clone() for k, v in weights.tensors.items()}, "synthetic", "synthetic")
+    params = [t.requires_grad_(True) for t in weights.tensors.values()]
+    model = Qwen3DenseBIModel(spec, weights, ops)
+    ref_model = Qwen3DenseBIModel(spec, ref_weights, ops)
+    opt = torch.optim.AdamW(params, lr=1e-6, betas=(0.9, 0.95), weight_decay=0.01)
+    B, P, R = PROMPTS * GROUP, PROMPT_LEN, a.response_len
+    S = P + R
+    total = a.warmup + a.steps
+    host_prompts = torch.randint(0, spec.vocab_size, (total, PROMPTS, P),
+                                 generator=torch.Generator().manual_seed(99)).pin_memory()
+    host_loss = torch.empty(1).pin_memory()
+
+    def alarm(_sig, _frm):
+        raise TimeoutError(f"one reference step exceeded {a.step_timeout} s")
+
+    signal.signal(signal.SIGALRM, alarm)
+
+    def one_step(i: int) -> None:
+        signal.alarm(a.step_timeout)
+        prompts = host_prompts[i].to(dev, non_blocking=True).repeat_interleave(GROUP, 0)
+        # ---- rollout
+        with torch.no_grad():
+            cache = model.allocate_cache(B, S, dev)
+            out = model.forward(prompts, kv_cache=cache)
+            logits = out["logits"][:, -1].float()
+            toks, lps = [], []
+            pos = torch.full((B, 1), P, device=dev, dtype=torch.long)
+            for t in range(R):
+                keep = sampling_keep_mask(logits, temperature=1.0, top_k=-1, top_p=1.0)
+                z = logits.masked_fill(~keep, float("-inf")) if keep is not None else logits
+                probs = torch.softmax(z, -1)
+                tok = torch.multinomial(probs, 1)
+                toks.append(tok)
+                lps.append(torch.log_softmax(z, -1).gather(1, tok))
+                if t + 1 < R:
+                    out = model.decode_step(tok, cache, position_ids=pos)
+                    logits = out["logits"][:, -1].float()
+                    pos = pos + 1
+            resp = torch.cat(toks, 1)
+            old_logp = torch.cat(lps, 1)
+            tokens = torch.cat([prompts, resp], 1)
+            del cache
+        rewards = torch.bernoulli(torch.full((B,), 0.5, device=dev))
+        g = rewards.view(PROMPTS, GROUP)
+        adv = ((g - g.mean(1, keepdim=True)) / g.std(1, unbiased=False, keepdim=True).clamp_min(1e-6)).reshape(B)
+        mask = torch.ones(B, R, dtype=torch.bool, device=dev)
+        opt.zero_grad(set_to_none=True)
+        loss_total = torch.zeros((), device=dev)
+        for b0 in range(0, B, a.micro_batch):
+            tk = tokens[b0:b0 + a.micro_batch]
+            with torch.no_grad():
+                ref_lp = ref_model.forward(tk, target_ids=tk)["selected_logp"][:, P - 1:]
+            lp = model.forward(tk, target_ids=tk)["selected_logp"][:, P - 1:]
+            m = mask[b0:b0 + a.micro_batch]
+            ratio = compute_policy_ratio(lp, old_logp[b0:b0 + a.micro_batch], m)
+            av = adv[b0:b0 + a.micro_batch, None].expand_as(lp)
+            pol = -torch.minimum(ratio * av, torch.clamp(ratio, 0.8, 1.2) * av)
+            kl = compute_reference_kl(lp, ref_lp, m)
+            loss = (masked_mean(pol, m) + 0.001 * masked_mean(kl, m)) * (tk.shape[0] / B)
+            loss.backward()
+            loss_total += loss.detach()
+        torch.nn.utils.clip_grad_norm_(params, 1.0)
+        opt.step()
+        host_loss.copy_(loss_total.reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        signal.alarm(0)
+
+    for i in range(a.warmup):
+        one_step(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record()
+    for i in range(a.warmup, total):
+        one_step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    ms = e0.elapsed_time(e1) / a.steps
+    tokens_per_step = B * S
+    return {"metric": "qwen3_8b_grpo_step_tokens_per_s", "value": tokens_per_step / (ms / 1e3), "unit": "tokens/s",
+            "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "reference",
+            "data": "synthetic (uniform-random prompt ids, Bernoulli rewards, random-init weights)",
+            "config": {"model": "Qwen3-8B" if not a.layers else f"Qwen3-8B-shape-{a.layers}L", "global_batch": B,
+                       "seq_len": S, "parallelism": "single GPU", "operator_profile": "triton_cuda_bf16",
+                       "micro_batch_seqs": a.micro_batch},
+            "e2e": {"value": tokens_per_step * a.steps / wall, "unit": "tokens/s",
+                    "h2d_bytes_per_step": PROMPTS * P * 8, "d2h_bytes_per_step": 4}}
+
+
+if __name__ == "__main__":
+    sys.exit(main())
