@@ -1,0 +1,129 @@
+"""Selected-token log-prob operators: from logits (batch-invariant, tile contract) and fused
+linear->logp (hidden @ W^T never materialised), both differentiable with native backward."""
+from __future__ import annotations
+
+import torch
+
+from rl_kernel_b200.ops._dispatch import use_native
+from rl_kernel_b200.reference.logprob.tile_logp import (NativeBatchInvariantLogpOp, NativeLinearLogpOp, TILE)
+
+
+def _ntiles(vocab: int) -> int:
+    return (vocab + TILE - 1) // TILE
+
+
+class _LogpFromLogitsFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, inv_temp):
+        from rl_kernel_b200.backends import native as nv
+
+        rows, V = logits.shape
+        stats = torch.empty(rows, _ntiles(V), 2, device=logits.device, dtype=torch.float32)
+        tl = torch.zeros(rows, device=logits.device, dtype=torch.float32)
+        nv.logits_tile_stats(logits, targets, stats, tl, vocab_start=0, inv_temp=inv_temp)
+        logp = torch.empty(rows, device=logits.device, dtype=torch.float32)
+        lse = torch.empty(rows, device=logits.device, dtype=torch.float32)
+        nv.logp_merge(stats, tl, logp, lse)
+        ctx.save_for_backward(logits, targets, lse)
+        ctx.inv_temp = inv_temp
+        return logp
+
+    @staticmethod
+    def backward(ctx, g):
+        from rl_kernel_b200.backends import native as nv
+
+        logits, targets, lse = ctx.saved_tensors
+        d = logits.clone()
+        nv.dlogits_(d, targets, lse, g.float().contiguous(), vocab_start=0, inv_temp=ctx.inv_temp)
+        return d, None, None
+
+
+def logp_from_logits(logits: torch.Tensor, targets: torch.Tensor, temperature: float = 1.0) -> torch.Tensor:
+    """logits [..., V] bf16, targets [...] -> fp32 selected log-prob (batch-invariant, differentiable)."""
+    shp = targets.shape
+    lg = logits.reshape(-1, logits.shape[-1])
+    if not use_native(lg):
+        return NativeBatchInvariantLogpOp(temperature).apply_fp32(lg, targets.reshape(-1)).view(shp)
+    return _LogpFromLogitsFn.apply(lg.contiguous(), targets.reshape(-1).contiguous(), 1.0 / temperature).view(shp)
+
+
+class _LinearLogpFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, weight, targets, inv_temp, chunk):
+        from rl_kernel_b200.backends import native as nv
+
+        rows, V = hidden.shape[0], weight.shape[0]
+        logp = torch.empty(rows, device=hidden.device, dtype=torch.float32)
+        lse = torch.empty(rows, device=hidden.device, dtype=torch.float32)
+        for r0 in range(0, rows, chunk):
+            r1 = min(rows, r0 + chunk)
+            stats = torch.empty(r1 - r0, _ntiles(V), 2, device=hidden.device, dtype=torch.float32)
+            tl = torch.zeros(r1 - r0, device=hidden.device, dtype=torch.float32)
+            nv.lmhead_logp_stats(hidden[r0:r1], weight, targets[r0:r1], stats, tl, vocab_start=0, inv_temp=inv_temp)
+            nv.logp_merge(stats, tl, logp[r0:r1], lse[r0:r1])
+        ctx.save_for_backward(hidden, weight, targets, lse)
+        ctx.meta = (inv_temp, chunk)
+        return logp
+
+    @staticmethod
+    def backward(ctx, g):
+        from rl_kernel_b200.backends import native as nv
+
+        hidden, weight, targets, lse = ctx.saved_tensors
+        inv_temp, chunk = ctx.meta
+        rows, H = hidden.shape
+        V = weight.shape[0]
+        g = g.float().contiguous()
+        dh = torch.empty_like(hidden)
+        dw = torch.zeros_like(weight)
+        for r0 in range(0, rows, chunk):
+            r1 = min(rows, r0 + chunk)
+            n = r1 - r0
+            logits = torch.empty(n, V, device=hidden.device, dtype=hidden.dtype)
+            nv.det_gemm(hidden[r0:r1], weight, logits, M=n, N=V, K=H)
+            nv.dlogits_(logits, targets[r0:r1], lse[r0:r1], g[r0:r1], vocab_start=0, inv_temp=inv_temp)
+            nv.det_gemm(logits, weight, dh[r0:r1], M=n, N=H, K=V, b_mn=True)
+            nv.det_gemm(logits, hidden[r0:r1], dw, M=V, N=H, K=n, a_mn=True, b_mn=True, accumulate=True)
+        return dh, dw, None, None, None
+
+
+def linear_logp(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tensor, temperature: float = 1.0,
+                chunk: int = 4096) -> torch.Tensor:
+    """logp[n] = log_softmax(hidden[n] @ weight^T / T)[targets[n]] without keeping [N, V] logits
+    (parity: FusedLinearLogpSM90Op, rl_engine/backends/cuda/logprob/linear_logp.py:802)."""
+    shp = targets.shape
+    h = hidden.reshape(-1, hidden.shape[-1])
+    if not use_native(h, weight):
+        return NativeLinearLogpOp(temperature)(h, weight, targets.reshape(-1)).view(shp)
+    if weight.shape[0] % 8:
+        raise ValueError("vocab size must be a multiple of 8 for the fused LM head")
+    return _LinearLogpFn.apply(h.contiguous(), weight.contiguous(), targets.reshape(-1).contiguous(),
+                               1.0 / temperature, chunk).view(shp)
+
+
+class BatchInvariantLogpOp:
+    backend_id = "b200"
+    is_fused_logp = True
+    backward_impl = "native"
+
+    def __init__(self, temperature: float = 1.0):
+        self.temperature = temperature
+
+    def __call__(self, logits, token_ids):
+        return logp_from_logits(logits, token_ids, self.temperature)
+
+    forward = apply_fp32 = __call__
+
+
+class LinearLogpOp:
+    backend_id = "b200-tcgen05"
+    is_fused_logp = True
+    backward_impl = "native"
+
+    def __init__(self, temperature: float = 1.0):
+        self.temperature = temperature
+
+    def __call__(self, hidden, weight, targets):
+        return linear_logp(hidden, weight, targets, self.temperature)
+
+    forward = __call__
