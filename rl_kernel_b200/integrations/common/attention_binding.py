@@ -1,0 +1,40 @@
+"""Binds an AttentionContract to a framework's attention layer in three tiers: explicit contract >
+contract derived from the layer's config > refusal in strict mode (parity: bind_attention_contracts,
+rl_engine/integrations/common/attention_binding.py:597)."""
+from __future__ import annotations
+
+from rl_kernel_b200.contracts.operators.attention import AttentionContract, CPLayout, ShardingSpec
+from rl_kernel_b200.runtime.policy import strict_contract_enabled
+
+
+def contract_from_layer(layer, tp_size: int = 1, cp_size: int = 1, cp_layout: str = "zigzag") -> AttentionContract:
+    def pick(*names):
+        for n in names:
+            if hasattr(layer, n):
+                return getattr(layer, n)
+        raise AttributeError(f"attention layer {type(layer).__name__} exposes none of {names}")
+
+    hq = int(pick("num_heads", "num_attention_heads", "total_num_heads"))
+    hkv = int(pick("num_kv_heads", "num_key_value_heads", "total_num_kv_heads", "num_query_groups"))
+    d = int(pick("head_dim", "head_size", "hidden_size_per_attention_head"))
+    layout = CPLayout(cp_layout) if cp_size > 1 else CPLayout.NONE
+    return AttentionContract(hq, hkv, d, sharding=ShardingSpec(tp_size, cp_size, layout))
+
+
+def bind_attention_contracts(layers, *, explicit: AttentionContract | None = None, tp_size: int = 1, cp_size: int = 1,
+                             cp_layout: str = "zigzag") -> list[AttentionContract]:
+    out = []
+    for layer in layers:
+        if explicit is not None:
+            c = explicit
+        else:
+            try:
+                c = contract_from_layer(layer, tp_size, cp_size, cp_layout)
+            except (AttributeError, ValueError) as exc:
+                if strict_contract_enabled():
+                    raise RuntimeError(f"strict mode: cannot bind an attention contract to {type(layer).__name__}: {exc}")
+                c = None
+        if c is not None:
+            setattr(layer, "rl_kernel_attention_contract", c)
+        out.append(c)
+    return out
