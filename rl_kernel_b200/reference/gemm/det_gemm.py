@@ -50,12 +50,19 @@ def det_gemm_reference(x: torch.Tensor, w: torch.Tensor, *, nchunks: int = 1,
 
 
 class NativeGemmOp:
-    """Callable reference op (registry name ``det_gemm``)."""
+    """Callable reference op (registry name ``det_gemm``): ``op(a, b)`` = a [M,K] @ b [K,N]."""
+    backend_id = "reference"
 
-    def __call__(self, x, w, nchunks: int = 1):
-        return det_gemm_reference(x, w, nchunks=nchunks)
+    def __call__(self, a, b, nchunks: int = 1):
+        return det_gemm_reference(a, b.t(), nchunks=nchunks)
 
     forward = __call__
 
-    def forward_fp32(self, x, w, nchunks: int = 1):
-        return det_gemm_reference(x, w, nchunks=nchunks, out_dtype=torch.float32)
+    def forward_rhs_transposed(self, a, b_t, nchunks: int = 1):
+        return det_gemm_reference(a, b_t, nchunks=nchunks)
+
+    def forward_fp32(self, a, b, nchunks: int = 1):
+        return det_gemm_reference(a, b.t(), nchunks=nchunks, out_dtype=torch.float32)
+
+    def linear(self, x, w, nchunks: int = 1):
+        return det_gemm_reference(x.reshape(-1, x.shape[-1]), w, nchunks=nchunks).reshape(*x.shape[:-1], w.shape[0])

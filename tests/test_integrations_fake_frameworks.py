@@ -1,0 +1,155 @@
+"""Framework bindings exercised with stand-in classes (no vLLM / Megatron / DeepSpeed / Ray needed)."""
+import types
+
+import pytest
+import torch
+
+from rl_engine.integrations.common.ray_actor_manager import RayActorManager
+from rl_engine.integrations.common.runtime import FrameworkOperatorIntegration
+from rl_engine.integrations.common.weights import LocalTensorCopyBridge, WeightPublisher
+from rl_engine.integrations.engines.rollout.vllm.runtime import install_vllm_integration
+from rl_engine.integrations.engines.train.contract import RolloutStageResult
+from rl_engine.integrations.engines.train.deepspeed.adapter import DeepSpeedTrainingWorker
+from rl_engine.integrations.engines.train.megatron.runtime import (CanonicalColumnProjection,
+                                                                   DeterministicTPOutputProjection,
+                                                                   install_megatron_integration)
+from rl_engine.runtime.plan import IntegrationPlan
+
+
+class FakeAttention:
+    num_heads, num_kv_heads, head_dim = 4, 2, 64
+
+    def forward(self, q, k, v, **kw):
+        raise AssertionError("original attention must not run")
+
+
+class FakeModel:
+    def __init__(self):
+        self.lm_head = types.SimpleNamespace(weight=torch.randn(64, 16))
+
+    def compute_logits(self, hidden_states):
+        return hidden_states @ self.lm_head.weight.t()
+
+
+class FakeSampler:
+    def forward(self, logits, sampling_metadata=None):
+        return types.SimpleNamespace(sampled_token_ids=logits.argmax(-1))
+
+
+def test_vllm_binding_routes_attention_and_logp():
+    integ = install_vllm_integration(attention_cls=FakeAttention, model_cls=FakeModel, sampler_cls=FakeSampler,
+                                     plan=IntegrationPlan.uniform("R/R"))
+    T = 24
+    q, k, v = torch.randn(T, 4 * 64), torch.randn(T, 2 * 64), torch.randn(T, 2 * 64)
+    out = FakeAttention().forward(q, k, v, cu_seqlens=[0, 10, 24])
+    assert out.shape == (T, 256)
+    model, sampler = FakeModel(), FakeSampler()
+    hidden = torch.randn(5, 16)
+    res = sampler.forward(model.compute_logits(hidden))
+    want = torch.log_softmax(hidden @ model.lm_head.weight.t(), -1).gather(1, res.sampled_token_ids[:, None])[:, 0]
+    assert torch.allclose(res.rl_kernel_logprobs, want, atol=1e-4)
+    rb = integ.readback()
+    assert rb["modules"]["attention"]["calls"] == 1 and rb["modules"]["logp"]["calls"] == 1
+    with pytest.raises(RuntimeError):
+        integ.assert_strict_ready()          # the plan also wants an ffn operator, none was installed
+
+
+def test_plan_gates_installation(tmp_path, monkeypatch):
+    integ = FrameworkOperatorIntegration("vllm", "rollout", IntegrationPlan.uniform("P/R"))
+    with pytest.raises(RuntimeError):
+        integ.install("attention", object())
+    monkeypatch.setenv("RL_KERNEL_READBACK_DIR", str(tmp_path))
+    assert integ.persist_readback().exists()
+
+
+def test_megatron_projections_tp_simulated():
+    torch.manual_seed(0)
+    H, I = 64, 128
+    x = torch.randn(6, H)
+    w1, w2 = torch.randn(I, H), torch.randn(H, I)
+    full = DeterministicTPOutputProjection(w2.clone(), canonical_tp=8, tp_size=1)(CanonicalColumnProjection(w1.clone())(x))
+    from rl_engine.distributed import balanced_tree_sum
+
+    parts = []
+    for r in range(2):
+        col = CanonicalColumnProjection(w1[r * 64:(r + 1) * 64].clone())
+        row = DeterministicTPOutputProjection(w2[:, r * 64:(r + 1) * 64].clone(), canonical_tp=8, tp_size=2)
+        parts.append(row(col(x)))
+    assert torch.equal(balanced_tree_sum(parts), full)
+
+
+class FakeEngine:
+    def __init__(self):
+        self.module = torch.nn.ModuleDict({"emb": torch.nn.Embedding(32, 16), "lm_head": torch.nn.Linear(16, 32, bias=False)})
+        self.opt = torch.optim.SGD(self.module.parameters(), lr=0.1)
+
+    def backward(self, loss):
+        loss.backward()
+
+    def step(self):
+        self.opt.step()
+        self.opt.zero_grad()
+
+
+def test_deepspeed_worker_trains_and_publishes():
+    eng = FakeEngine()
+    bridge = LocalTensorCopyBridge()
+    w = DeepSpeedTrainingWorker(eng, WeightPublisher(bridge), hidden_fn=lambda m, ids: m["emb"](ids),
+                                lm_head_name="lm_head.weight", kl_coef=0.0)
+    B, P, R = 4, 3, 5
+    tokens = torch.randint(0, 32, (B, P + R))
+    with torch.no_grad():
+        h = eng.module["emb"](tokens)[:, P - 1:P - 1 + R]
+        old = torch.log_softmax(h @ eng.module["lm_head"].weight.t(), -1).gather(-1, tokens[:, P:, None])[..., 0]
+    ro = RolloutStageResult(tokens, torch.ones(B, R, dtype=torch.bool), old, torch.tensor([1.0, 0.0, 1.0, 1.0]), P, 2)
+    before = eng.module["lm_head"].weight.detach().clone()
+    res = w.train(ro)
+    assert res.tokens_compared == B * R and not torch.equal(before, eng.module["lm_head"].weight)
+    m = w.publish_weights(1)
+    assert "lm_head.weight" in m.tensors and m.metadata["layout"] == "full-state"
+
+
+class FakeRay:
+    class _Ref:
+        def __init__(self, v):
+            self.v = v
+
+    def remote(self, **kw):
+        ray = self
+
+        def deco(cls):
+            class Handle:
+                def __init__(self, obj):
+                    for name in ("call", "health"):
+                        fn = getattr(obj, name)
+                        setattr(self, name, types.SimpleNamespace(remote=lambda *a, _f=fn, **k: ray._Ref(_f(*a, **k))))
+
+            return types.SimpleNamespace(remote=lambda *a, **k: Handle(cls(*a, **k)))
+
+        return deco
+
+    def get(self, ref):
+        return ref.v
+
+    def kill(self, actor):
+        pass
+
+
+def test_ray_actor_manager_with_fake_ray():
+    mgr = RayActorManager(ray_module=FakeRay())
+
+    class W:
+        def __init__(self, k):
+            self.k = k
+
+        def ping(self, x):
+            return x * self.k
+
+    mgr.spawn("a", "rollout", W, 2)
+    mgr.spawn("b", "rollout", W, 3)
+    assert mgr.call("a", "ping", 5) == 10 and mgr.broadcast("rollout", "ping", 1) == {"a": 2, "b": 3}
+    assert mgr.health_check() == {"a": True, "b": True}
+    with pytest.raises(ValueError):
+        mgr.spawn("a", "rollout", W, 1)
+    mgr.shutdown()
+    assert not mgr.workers
