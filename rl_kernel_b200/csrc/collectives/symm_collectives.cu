@@ -20,27 +20,14 @@
 // waits are unbounded.
 #include "rlk/host.h"
 #include "rlk/ptx.cuh"
+#include "rlk/symm.h"
 
 #include <cstring>
 
 namespace rlk {
 
-constexpr int kMaxRanks = 8;
-constexpr int kMaxSlices = 2048;
-constexpr int kFlagBytes = kMaxRanks * kMaxSlices * 8;  // u64 flag[src_rank][slice]
 constexpr int kMinSliceBytes = 32768;                   // payload bytes per slice (grows with the payload)
 constexpr int kCollThreads = 256;
-
-struct SymmWorld {
-  unsigned char* win[kMaxRanks];  // window base of every rank (own entry = local pointer)
-  int world, rank;
-  long long frame_bytes;
-  // CUDA-graph support: a captured kernel's sequence number is base + epoch * stride, where epoch
-  // (device word 0) is bumped once per replay and stride (device word 1) is the EVEN number of
-  // collective calls in the graph, so the frame parity of every captured call is fixed.
-  const unsigned long long* epoch;
-  int use_epoch;
-};
 
 __device__ __forceinline__ unsigned long long effective_seq(const SymmWorld& w, unsigned long long base) {
   return w.use_epoch ? base + w.epoch[0] * w.epoch[1] : base;
@@ -180,18 +167,6 @@ __global__ void barrier_kernel(const SymmWorld w, unsigned long long base_seq, i
 }
 
 __global__ void epoch_bump_kernel(unsigned long long* epoch) { epoch[0] += 1; }
-
-struct SymmState {
-  SymmWorld w;
-  unsigned char* local;
-  unsigned char* peers[kMaxRanks];
-  unsigned long long seq;
-  int device;
-  unsigned long long* dev_epoch;       // [epoch, stride]
-  int capturing;
-  unsigned long long capture_begin_seq;
-  unsigned long long graph_stride;
-};
 
 }  // namespace rlk
 using namespace rlk;

@@ -20,6 +20,7 @@
 #include "rlk/logp_contract.cuh"
 #include "rlk/no_alloc.h"
 #include "rlk/ptx.cuh"
+#include "rlk/symm.h"
 
 #include <mutex>
 
@@ -52,7 +53,33 @@ struct GemmParams {
   long long vocab_start;    // global id of column 0
   float* tgt_logit;         // [M]
   float inv_temp;
+  // fused all-reduce epilogue (ar_world > 1): C points into this rank's symmetric frame; after a
+  // tile's partial is stored there the epilogue warps shake hands with the same tile on every
+  // peer, pull the peers' partials over NVLink, finish the balanced tree and write ar_out.
+  int ar_world, ar_rank;
+  unsigned char* ar_frame[8];
+  unsigned long long* ar_flags[8];
+  unsigned long long ar_seq;
+  const unsigned long long* ar_epoch;
+  int ar_use_epoch;
+  __nv_bfloat16* ar_out;
+  long long ar_ld_out;
 };
+
+__device__ __forceinline__ uint4 ar_ld_peer_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ar_tree_node(const uint4 a, const uint4 b) {
+  uint4 o;
+  o.x = pack_bf16x2(__fadd_rn(bf16_lo(a.x), bf16_lo(b.x)), __fadd_rn(bf16_hi(a.x), bf16_hi(b.x)));
+  o.y = pack_bf16x2(__fadd_rn(bf16_lo(a.y), bf16_lo(b.y)), __fadd_rn(bf16_hi(a.y), bf16_hi(b.y)));
+  o.z = pack_bf16x2(__fadd_rn(bf16_lo(a.z), bf16_lo(b.z)), __fadd_rn(bf16_hi(a.z), bf16_hi(b.z)));
+  o.w = pack_bf16x2(__fadd_rn(bf16_lo(a.w), bf16_lo(b.w)), __fadd_rn(bf16_hi(a.w), bf16_hi(b.w)));
+  return o;
+}
 
 template <int BN>
 struct GemmSmem {
@@ -369,6 +396,52 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tc_fence_before();
         mbar_arrive(acce0 + 8 * a);
       }
+      if (p.ar_world > 1) {
+        // ---- fused all-reduce of this tile (the MMA warp is already working on the next tile)
+        const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+        const unsigned long long seq = p.ar_use_epoch ? p.ar_seq + p.ar_epoch[0] * p.ar_epoch[1] : p.ar_seq;
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et < p.ar_world && et != p.ar_rank)
+          asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p.ar_flags[et] + p.ar_rank * kMaxSlices + t), "l"(seq) : "memory");
+        if (et < p.ar_world && et != p.ar_rank) {
+          const unsigned long long* f = p.ar_flags[p.ar_rank] + et * kMaxSlices + t;
+          const uint64_t t0 = globaltimer_ns();
+          uint32_t it = 0;
+          unsigned long long v;
+          while (true) {
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(f) : "memory");
+            if (v >= seq) break;
+            if ((++it & 63) == 0 && (*abort_flag || globaltimer_ns() - t0 > RLK_WAIT_LIMIT_NS)) {
+              *abort_flag = 1;
+              if (p.status) atomicCAS(p.status, 0, 105);
+              break;
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*abort_flag) break;
+        constexpr int kPerRow = BN / 8;                         // 16-byte pieces per tile row
+        const int m0 = mt * BM;
+        for (int idx = et; idx < BM * kPerRow; idx += 128) {
+          const int rr = idx / kPerRow, cc = (idx % kPerRow) * 8;
+          if (m0 + rr < p.M && n0 + cc < p.N) {
+            const long long off = (static_cast<long long>(m0 + rr) * p.ldc + n0 + cc) * 2;
+            uint4 v[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r)
+              if (r < p.ar_world)
+                v[r] = (r == p.ar_rank) ? *reinterpret_cast<const uint4*>(p.ar_frame[r] + off)
+                                        : ar_ld_peer_v4(p.ar_frame[r] + off);
+#pragma unroll
+            for (int n = 8; n > 1; n >>= 1)
+              if (n <= p.ar_world)
+#pragma unroll
+                for (int j = 0; j < n / 2; ++j) v[j] = ar_tree_node(v[2 * j], v[2 * j + 1]);
+            *reinterpret_cast<uint4*>(p.ar_out + static_cast<long long>(m0 + rr) * p.ar_ld_out + n0 + cc) = v[0];
+          }
+        }
+      }
     }
   }
 
@@ -536,6 +609,48 @@ RLK_API int rlk_det_gemm_split(const void* A, const void* B, void* C, void* scra
       static_cast<const __nv_bfloat16*>(scratch), p.split_stride, static_cast<__nv_bfloat16*>(C), M, N, ldc, nchunks);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
+}
+
+// GEMM + fixed-order all-reduce in ONE kernel (row-parallel projections: o_proj, FFN down):
+// out = all_reduce_tree_over_ranks( A_local @ B_local^T with nchunks canonical K chunks ).
+// `state` is the rlk_symm_create handle of the tensor-parallel group; every rank calls this with
+// the same shapes on its own stream.  The partial result lives only in the symmetric frame; the
+// transfer of a tile overlaps the MMA of the following tiles.  M * ld_out * 2 bytes must fit the
+// frame and the number of 128 x tile_n tiles must not exceed the flag slots.
+RLK_API int rlk_det_gemm_ar(void* state, const void* A, const void* B, void* out, int M, int N, int K,
+                            long long lda, long long ldb, long long ld_out, int nchunks, void* stream) {
+  using namespace rlk;
+  SymmState* st = static_cast<SymmState*>(state);
+  RLK_REQUIRE(st != nullptr && st->w.world > 1, "det_gemm_ar: needs a symmetric-memory group of 2+ ranks");
+  RLK_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0, "det_gemm_ar: bad shape");
+  RLK_REQUIRE(nchunks == 1 || nchunks == 2 || nchunks == 4 || nchunks == 8, "det_gemm_ar: nchunks must be 1, 2, 4 or 8");
+  RLK_REQUIRE(nchunks == 1 || K % (nchunks * 64) == 0, "det_gemm_ar: K/nchunks must be a multiple of 64");
+  RLK_REQUIRE(2ll * M * ld_out <= st->w.frame_bytes, "det_gemm_ar: %lld bytes exceed the frame capacity %lld",
+              2ll * M * ld_out, st->w.frame_bytes);
+  const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
+  RLK_REQUIRE(tiles < kMaxSlices - 1, "det_gemm_ar: %lld tiles exceed the flag slots", tiles);
+  RLK_REQUIRE((reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ld_out * 2) % 16 == 0, "det_gemm_ar: out must be 16-byte aligned");
+  st->seq += 1;
+  const int frame = static_cast<int>(st->seq & 1);
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.nchunks = nchunks;
+  p.kb_per_chunk = nchunks == 1 ? (K + 63) / 64 : K / nchunks / 64;
+  p.C = st->peers[st->w.rank] + kFlagBytes + frame * st->w.frame_bytes;
+  p.ldc = ld_out;
+  p.status = device_status_word();
+  p.ar_world = st->w.world;
+  p.ar_rank = st->w.rank;
+  for (int r = 0; r < st->w.world; ++r) {
+    p.ar_frame[r] = st->peers[r] + kFlagBytes + frame * st->w.frame_bytes;
+    p.ar_flags[r] = reinterpret_cast<unsigned long long*>(st->peers[r]);
+  }
+  p.ar_seq = st->seq;
+  p.ar_epoch = st->dev_epoch;
+  p.ar_use_epoch = st->w.use_epoch;
+  p.ar_out = static_cast<__nv_bfloat16*>(out);
+  p.ar_ld_out = ld_out;
+  return launch_gemm<128, false, false>(A, B, p, lda, ldb, static_cast<cudaStream_t>(stream));
 }
 
 // ---- the variant that allocates nothing (see rlk/no_alloc.h for the contract) ----------------

@@ -120,6 +120,20 @@ class SymmetricMemoryCollective:
         nv._count()
         return out
 
+    def gemm_all_reduce(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, nchunks: int = 1) -> torch.Tensor:
+        """out = tree-all-reduce over the group of (a_local @ b_local^T with canonical K chunks), as
+        ONE kernel: tiles are exchanged over NVLink from inside the GEMM epilogue while later tiles
+        are still being multiplied (csrc/gemm/det_gemm_sm100.cu, rlk_det_gemm_ar)."""
+        self._check_open()
+        M, K = a.shape
+        N = b.shape[0]
+        ext.check(self._lib.rlk_det_gemm_ar(self._state, ext.ptr(a), ext.ptr(b), ext.ptr(out), c_int(M), c_int(N),
+                                            c_int(K), c_longlong(a.stride(0)), c_longlong(b.stride(0)),
+                                            c_longlong(out.stride(0)), c_int(nchunks), ext.stream_ptr(self.device)),
+                  "det_gemm_ar")
+        nv._count()
+        return out
+
     def all_reduce_int_(self, t: torch.Tensor) -> torch.Tensor:
         """Integer sums are associative: gather and add (exact in any order)."""
         if self.world == 1:

@@ -288,6 +288,7 @@ class Qwen3Engine:
         self.scale = 1.0 / math.sqrt(self.d)
         self.cos, self.sin = rope_tables(spec, max_positions, self.dev)
         self.ws = Workspace(self.dev)
+        self.fuse_gemm_allreduce = True
         self._tiles: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
         for K in (params.q_local, params.i_local):
             if self.nchunks > 1 and (K // self.nchunks) % 64:
@@ -305,6 +306,24 @@ class Qwen3Engine:
             return nv.det_gemm_split(a, b, out, scratch, nchunks=nchunks, tile_n=64)
         return nv.det_gemm(a, b, out, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, nchunks=nchunks,
                            accumulate=accumulate)
+
+    def _row_parallel(self, a, w, out, nchunks: int):
+        """Row-parallel projection: local GEMM with canonical chunks, then the fixed-tree sum over TP.
+        Many rows: one fused GEMM+all-reduce kernel.  Few rows (decode): the split GEMM writes into
+        the symmetric frame and the all-reduce kernel skips its copy-in."""
+        coll = self.ctx.collective
+        if self.ctx.tp_size == 1:
+            return self._gemm(a, w, out, nchunks=nchunks)
+        M = a.shape[0]
+        if M > 512 and hasattr(coll, "gemm_all_reduce") and self.fuse_gemm_allreduce:
+            return coll.gemm_all_reduce(a, w, out, nchunks)
+        if hasattr(coll, "staging_view"):
+            staged = coll.staging_view(tuple(out.shape), out.dtype)
+            self._gemm(a, w, staged, nchunks=nchunks)
+            return coll.all_reduce_staged(staged, out)
+        self._gemm(a, w, out, nchunks=nchunks)
+        coll.all_reduce_(out)
+        return out
 
     def _tiles_for(self, nseq: int, S: int):
         key = (nseq, S)
@@ -336,8 +355,7 @@ class Qwen3Engine:
         ov = attn if q_view is None else attn.view(*q_view)
         self._attention(qv, kbuf, vbuf, ov, lse, tiles, decode=q_view is not None)
         o = ws.get(f"{tag}.o", (T, H))
-        self._gemm(attn, w[f"l{l}.wo"], o, nchunks=self.nchunks)
-        self.ctx.tp_all_reduce_(o)
+        self._row_parallel(attn, w[f"l{l}.wo"], o, self.nchunks)
         s_mid = ws.get(f"{tag}.s_mid", (T, H))
         h2 = ws.get(f"{tag}.h2", (T, H))
         nv.rmsnorm_fwd(o, w[f"l{l}.ln2"], h2, eps, res=s_in, res_out=s_mid)
@@ -346,8 +364,7 @@ class Qwen3Engine:
         act = ws.get(f"{tag}.act", (T, self.p.i_local))
         nv.swiglu_fwd(gu, act, self.p.i_local, self.blk)
         down = ws.get(f"{tag}.down", (T, H))
-        self._gemm(act, w[f"l{l}.wd"], down, nchunks=self.nchunks)
-        self.ctx.tp_all_reduce_(down)
+        self._row_parallel(act, w[f"l{l}.wd"], down, self.nchunks)
         if keep is not None:
             keep.update(s_in=s_in, h=h, qkv=qkv, q=q, attn=attn, s_mid=s_mid, h2=h2, gu=gu, act=act)
         return down, s_mid

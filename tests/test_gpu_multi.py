@@ -51,6 +51,18 @@ def _collective_worker(rank, world, port, out):
     st.copy_(x)
     res = coll.all_reduce_staged(st, torch.empty_like(x))
     ok &= bool((res == float(sum(range(1, world + 1)))).all())
+    # fused GEMM + all-reduce == local GEMM followed by the tree all-reduce, bit for bit
+    from rl_kernel_b200.backends import native as nv
+
+    for (M, N, K, nch) in [(700, 512, 1024, 4), (1536, 1024, 512, 1), (128, 256, 512, 8)]:
+        g = torch.Generator(device="cuda").manual_seed(7 + rank)
+        a = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        b = torch.randn(N, K, device=dev, generator=g).to(torch.bfloat16)
+        part = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        nv.det_gemm(a, b, part, M=M, N=N, K=K, nchunks=nch, tile_n=128)
+        want = coll.all_reduce(part)
+        got = coll.gemm_all_reduce(a, b, torch.empty_like(part), nch)
+        ok &= torch.equal(got, want)
     # CUDA graph replay keeps the sequence numbers moving
     buf = torch.ones(4096, device=dev, dtype=torch.float32)
     s = torch.cuda.Stream(dev)
