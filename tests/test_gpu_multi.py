@@ -169,3 +169,104 @@ def test_tp2_matches_tp1_bitwise(tmp_path):
     assert torch.equal(tp2["old_logp"], tp1["old_logp"].cpu())
     assert torch.equal(tp2["train_logp"], tp1["train_logp"].cpu())
     assert torch.equal(tp2["train_logp"], tp2["old_logp"])
+
+
+def _cp_worker(rank, world, port, out):
+    dist = _init(rank, world, port)
+    import math
+
+    from rl_kernel_b200.backends import native as nv
+    from rl_kernel_b200.distributed.cp_attention import CPAttention, cp_positions
+    from rl_kernel_b200.distributed.transports.symm import SymmetricMemoryCollective
+    from rl_kernel_b200.models.qwen3.engine import train_tiles
+
+    dev = torch.device("cuda", rank)
+    coll = SymmetricMemoryCollective(None, dev, frame_bytes=1 << 20)
+    HQ, HKV, D, B, S = 8, 2, 128, 2, 1024
+    g = torch.Generator(device="cuda").manual_seed(3)            # same full tensors on every rank
+    q = torch.randn(B, S, HQ * D, device=dev, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, HKV * D, device=dev, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, HKV * D, device=dev, generator=g).to(torch.bfloat16)
+    # single-GPU result
+    o1 = torch.empty(B * S, HQ * D, device=dev, dtype=torch.bfloat16)
+    l1 = torch.empty(B * S, HQ, device=dev)
+    tiles, _ = train_tiles(B, S, HQ, HKV, D, dev)
+    nv.attn_fwd(q.view(B * S, -1), [k.view(B * S, -1)], [v.view(B * S, -1)], o1, l1, tiles, 1 / math.sqrt(D))
+    ok = True
+    for layout in ("contiguous", "zigzag"):
+        pos = cp_positions(S, world, rank, layout).to(dev)
+        cp = CPAttention(coll, dev, num_q_heads=HQ, num_kv_heads=HKV, max_local_tokens=B * S // world, layout=layout)
+        sel = lambda t: t[:, pos].reshape(B * pos.numel(), -1).contiguous()
+        o, l = cp.forward(sel(q), sel(k), sel(v), B, S)
+        ok &= torch.equal(o, sel(o1.view(B, S, -1)))
+        ok &= torch.equal(l, sel(l1.view(B, S, -1)))
+    torch.cuda.synchronize(dev)
+    from rl_kernel_b200.backends import extension as ext
+    ok &= ext.poll_status(dev) == 0
+    if rank == 0:
+        torch.save(ok, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_cp_attention_equals_single_gpu_bitwise(tmp_path):
+    out = str(tmp_path / "cp.pt")
+    mp.spawn(_cp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    assert torch.load(out)
+
+
+def _push_worker(rank, world, port, out):
+    dist = _init(rank, world, port)
+    import ctypes
+
+    from rl_kernel_b200.backends import extension as ext
+    from rl_kernel_b200.distributed.transports.symm import _DevicePtrView
+    from rl_kernel_b200.integrations.common.weights import NVLinkPushBridge
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.engine import PackedParams
+
+    dev = torch.device("cuda", rank)
+    lib = ext.load()
+    spec = Qwen3DenseSpec.scaled(layers=2, hidden=256, ffn=512, q_heads=4, kv_heads=2, head_dim=128, vocab=1024)
+    w = Qwen3DenseWeights.synthetic(spec, seed=9)
+    # destination: a TP2 rollout shard on every rank, living in exportable memory
+    dst_layout = PackedParams(spec, rank, 2, dev)
+    nbytes = dst_layout.numel * 2 + 256
+    h = ctypes.create_string_buffer(lib.rlk_symm_ipc_handle_bytes())
+    p = ctypes.c_void_p(0)
+    ext.check(lib.rlk_ipc_alloc(ctypes.c_longlong(nbytes), ctypes.byref(p), h), "ipc_alloc")
+    handles = [None] * world
+    dist.all_gather_object(handles, bytes(h.raw))
+    mine = torch.as_tensor(_DevicePtrView(p.value, nbytes), device=dev)
+    ok = True
+    if rank == 0:
+        # source: the TP1 trainer shard on rank 0 pushes to both rollout shards (rank 0 local, rank 1 peer)
+        src = PackedParams(spec, 0, 1, dev).load(w)
+        bridge = NVLinkPushBridge(src, dev)
+        peer = ctypes.c_void_p(0)
+        ext.check(lib.rlk_ipc_open(handles[1], ctypes.byref(peer)), "ipc_open")
+        bases = [p.value, peer.value]
+        for r in range(2):
+            bridge.add_target(PackedParams(spec, r, 2, torch.device("cpu")), base_ptr=bases[r],
+                              version_flag_ptr=bases[r] + dst_layout.numel * 2)
+        m = bridge.publish(7)
+        ok &= m.metadata["targets"] == 2
+    flag = mine[dst_layout.numel * 2: dst_layout.numel * 2 + 8].view(torch.int64)
+    okd = torch.zeros(1, dtype=torch.int32, device=dev)
+    ext.check(lib.rlk_version_wait(ext.ptr(flag), ctypes.c_ulonglong(7), ext.ptr(okd), ext.stream_ptr(dev)), "wait")
+    torch.cuda.synchronize(dev)
+    ok &= int(okd.item()) == 1
+    want = PackedParams(spec, rank, 2, dev).load(w)
+    ok &= torch.equal(mine[: dst_layout.numel * 2].view(torch.bfloat16), want.flat)
+    res = [None] * world
+    dist.all_gather_object(res, bool(ok))
+    if rank == 0:
+        torch.save(all(res), out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_weight_push_reshards_over_nvlink(tmp_path):
+    out = str(tmp_path / "push.pt")
+    mp.spawn(_push_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    assert torch.load(out)
