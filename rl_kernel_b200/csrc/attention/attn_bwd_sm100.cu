@@ -17,10 +17,16 @@
 
 namespace rlk {
 
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 576;  // TMA warp, UMMA warp, 16 compute warps (4 threads per row)
 constexpr int kTile = 128 * 128 * 2;
 constexpr int kHalf = 128 * 64 * 2;
 constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float bwd_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // ------------------------------------------------------------------------------------ delta
 __global__ void __launch_bounds__(256)
@@ -95,7 +101,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(BAR(V_EMPTY + s), 1);
     }
     mbar_init(BAR(SDP_FULL), 1);
-    mbar_init(BAR(DS_FULL), 128);
+    mbar_init(BAR(DS_FULL), 512);
     mbar_init(BAR(DS_EMPTY), 1);
     mbar_init(BAR(ACC_FULL), 1);
     *abort_flag = 0;
@@ -175,7 +181,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       umma_commit(BAR(ACC_FULL));
     }
   } else {
+    // warp -> (quad, split): quad = TMEM lane quadrant, split = which 32 of the 128 columns
     const int quad = warp & 3;
+    const int split = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     int kv_len = t.pos0 + r * t.pos_step + 1;
@@ -193,62 +201,53 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       // the previous block's dQ MMA must have finished reading the dS tile
       if (b > 0 && !mbar_wait(BAR(DS_EMPTY), (b - 1) & 1, abort_flag, p.status, 308)) break;
       tc_fence_after();
-      const int nvis = kv_len - b * kAttnBlock;
+      const int nvis = kv_len - b * kAttnBlock - split * 32;
+      uint32_t sx[32], dx[32];
+      tmem_ld32(tmem_base + lane_off + TM_S + split * 32, sx);
+      tmem_ld32(tmem_base + lane_off + TM_DP + split * 32, dx);
+      tmem_ld_wait();
+      uint32_t pk[16];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sx[32], dx[32];
-        tmem_ld32(tmem_base + lane_off + TM_S + c * 32, sx);
-        tmem_ld32(tmem_base + lane_off + TM_DP + c * 32, dx);
-        tmem_ld_wait();
-        uint32_t pk[16];
-#pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float d0 = 0.f, d1 = 0.f;
-          if (c * 32 + j < nvis) {
-            const float pr = exp2f(fmaf(__uint_as_float(sx[j]), p.scale_log2, -lse2));
-            d0 = pr * (__uint_as_float(dx[j]) - dlt) * p.scale;
-          }
-          if (c * 32 + j + 1 < nvis) {
-            const float pr = exp2f(fmaf(__uint_as_float(sx[j + 1]), p.scale_log2, -lse2));
-            d1 = pr * (__uint_as_float(dx[j + 1]) - dlt) * p.scale;
-          }
-          pk[j >> 1] = pack_bf16x2(d0, d1);
+      for (int j = 0; j < 32; j += 2) {
+        float d0 = 0.f, d1 = 0.f;
+        if (j < nvis) {
+          const float pr = bwd_exp2(fmaf(__uint_as_float(sx[j]), p.scale_log2, -lse2));
+          d0 = pr * (__uint_as_float(dx[j]) - dlt) * p.scale;
         }
-        const int half = c >> 1;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const uint32_t chunk16 = (c & 1) * 4 + q4;
-          *reinterpret_cast<uint4*>(ds_base + half * kHalf + sw128_offset(r, chunk16)) =
-              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+        if (j + 1 < nvis) {
+          const float pr = bwd_exp2(fmaf(__uint_as_float(sx[j + 1]), p.scale_log2, -lse2));
+          d1 = pr * (__uint_as_float(dx[j + 1]) - dlt) * p.scale;
         }
+        pk[j >> 1] = pack_bf16x2(d0, d1);
       }
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4)
+        *reinterpret_cast<uint4*>(ds_base + (split >> 1) * kHalf + sw128_offset(r, (split & 1) * 4 + q4)) =
+            make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(BAR(DS_FULL));
     }
     if (mbar_wait(BAR(ACC_FULL), 0, abort_flag, p.status, 309)) {
       tc_fence_after();
-      __nv_bfloat16* dst = p.dQ + static_cast<long long>(t.q_row0 + r) * p.lddq + t.q_col0;
+      __nv_bfloat16* dst = p.dQ + static_cast<long long>(t.q_row0 + r) * p.lddq + t.q_col0 + split * 32;
+      uint32_t x[32];
+      if (nblk > 0) {
+        tmem_ld32(tmem_base + lane_off + TM_DQ + split * 32, x);
+        tmem_ld_wait();
+      } else {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t x[32];
-        if (nblk > 0) {
-          tmem_ld32(tmem_base + lane_off + TM_DQ + c * 32, x);
-          tmem_ld_wait();
-        } else {
+        for (int j = 0; j < 32; ++j) x[j] = 0u;
+      }
+      if (r < t.n_rows) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) x[j] = 0u;
-        }
-        if (r < t.n_rows) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(x[j]), __uint_as_float(x[j + 1]));
-            v.y = pack_bf16x2(__uint_as_float(x[j + 2]), __uint_as_float(x[j + 3]));
-            v.z = pack_bf16x2(__uint_as_float(x[j + 4]), __uint_as_float(x[j + 5]));
-            v.w = pack_bf16x2(__uint_as_float(x[j + 6]), __uint_as_float(x[j + 7]));
-            *reinterpret_cast<uint4*>(dst + c * 32 + j) = v;
-          }
+        for (int j = 0; j < 32; j += 8) {
+          uint4 v;
+          v.x = pack_bf16x2(__uint_as_float(x[j]), __uint_as_float(x[j + 1]));
+          v.y = pack_bf16x2(__uint_as_float(x[j + 2]), __uint_as_float(x[j + 3]));
+          v.z = pack_bf16x2(__uint_as_float(x[j + 4]), __uint_as_float(x[j + 5]));
+          v.w = pack_bf16x2(__uint_as_float(x[j + 6]), __uint_as_float(x[j + 7]));
+          *reinterpret_cast<uint4*>(dst + j) = v;
         }
       }
     }
@@ -330,7 +329,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(BAR(Q_FULL), 1);
     mbar_init(BAR(Q_EMPTY), 1);
     mbar_init(BAR(SDP_FULL), 1);
-    mbar_init(BAR(PDS_FULL), 128);
+    mbar_init(BAR(PDS_FULL), 512);
     mbar_init(BAR(ACC_FULL), 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -405,6 +404,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else {
     const int quad = warp & 3;
+    const int split = (warp - 2) >> 2;
     const int r = quad * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     uint8_t* p_base = smem + DkvSmem::kP;
@@ -422,38 +422,35 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         nvis = t.q_pos0 + qi + 1 - t.key0;
         if (nvis > t.n_keys) nvis = t.n_keys;
       }
+      nvis -= split * 32;           // among this thread's 32 keys
       if (!mbar_wait(BAR(SDP_FULL), it & 1, abort_flag, p.status, 315)) break;
       // P / dS tiles of the previous iteration must have been consumed (Q_EMPTY commit covers them)
       if (it > 0 && !mbar_wait(BAR(Q_EMPTY), (it - 1) & 1, abort_flag, p.status, 316)) break;
       tc_fence_after();
+      uint32_t sx[32], dx[32];
+      tmem_ld32(tmem_base + lane_off + TM_S + split * 32, sx);
+      tmem_ld32(tmem_base + lane_off + TM_DP + split * 32, dx);
+      tmem_ld_wait();
+      uint32_t pp[16], pd[16];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t sx[32], dx[32];
-        tmem_ld32(tmem_base + lane_off + TM_S + c * 32, sx);
-        tmem_ld32(tmem_base + lane_off + TM_DP + c * 32, dx);
-        tmem_ld_wait();
-        uint32_t pp[16], pd[16];
-#pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
-          if (c * 32 + j < nvis) {
-            p0 = exp2f(fmaf(__uint_as_float(sx[j]), p.scale_log2, -lse2));
-            d0 = p0 * (__uint_as_float(dx[j]) - dlt) * p.scale;
-          }
-          if (c * 32 + j + 1 < nvis) {
-            p1 = exp2f(fmaf(__uint_as_float(sx[j + 1]), p.scale_log2, -lse2));
-            d1 = p1 * (__uint_as_float(dx[j + 1]) - dlt) * p.scale;
-          }
-          pp[j >> 1] = pack_bf16x2(p0, p1);
-          pd[j >> 1] = pack_bf16x2(d0, d1);
+      for (int j = 0; j < 32; j += 2) {
+        float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
+        if (j < nvis) {
+          p0 = bwd_exp2(fmaf(__uint_as_float(sx[j]), p.scale_log2, -lse2));
+          d0 = p0 * (__uint_as_float(dx[j]) - dlt) * p.scale;
         }
-        const int half = c >> 1;
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {
-          const uint32_t off = half * kHalf + sw128_offset(r, (c & 1) * 4 + q4);
-          *reinterpret_cast<uint4*>(p_base + off) = make_uint4(pp[4 * q4], pp[4 * q4 + 1], pp[4 * q4 + 2], pp[4 * q4 + 3]);
-          *reinterpret_cast<uint4*>(ds_base + off) = make_uint4(pd[4 * q4], pd[4 * q4 + 1], pd[4 * q4 + 2], pd[4 * q4 + 3]);
+        if (j + 1 < nvis) {
+          p1 = bwd_exp2(fmaf(__uint_as_float(sx[j + 1]), p.scale_log2, -lse2));
+          d1 = p1 * (__uint_as_float(dx[j + 1]) - dlt) * p.scale;
         }
+        pp[j >> 1] = pack_bf16x2(p0, p1);
+        pd[j >> 1] = pack_bf16x2(d0, d1);
+      }
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const uint32_t off = (split >> 1) * kHalf + sw128_offset(r, (split & 1) * 4 + q4);
+        *reinterpret_cast<uint4*>(p_base + off) = make_uint4(pp[4 * q4], pp[4 * q4 + 1], pp[4 * q4 + 2], pp[4 * q4 + 3]);
+        *reinterpret_cast<uint4*>(ds_base + off) = make_uint4(pd[4 * q4], pd[4 * q4 + 1], pd[4 * q4 + 2], pd[4 * q4 + 3]);
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -461,35 +458,32 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
     if (mbar_wait(BAR(ACC_FULL), 0, abort_flag, p.status, 317)) {
       tc_fence_after();
-      // thread r owns key r of the block
-      __nv_bfloat16* dk = p.dK + static_cast<long long>(t.kv_row + r) * p.lddkv + t.kv_col0;
-      __nv_bfloat16* dv = p.dV + static_cast<long long>(t.kv_row + r) * p.lddkv + t.kv_col0;
+      // thread (r, split) owns key r of the block and head dims [32 split, 32 split + 32)
+      __nv_bfloat16* dk = p.dK + static_cast<long long>(t.kv_row + r) * p.lddkv + t.kv_col0 + split * 32;
+      __nv_bfloat16* dv = p.dV + static_cast<long long>(t.kv_row + r) * p.lddkv + t.kv_col0 + split * 32;
+      uint32_t xk[32], xv[32];
+      if (n_iter > 0) {
+        tmem_ld32(tmem_base + lane_off + TM_DK + split * 32, xk);
+        tmem_ld32(tmem_base + lane_off + TM_DV + split * 32, xv);
+        tmem_ld_wait();
+      } else {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t xk[32], xv[32];
-        if (n_iter > 0) {
-          tmem_ld32(tmem_base + lane_off + TM_DK + c * 32, xk);
-          tmem_ld32(tmem_base + lane_off + TM_DV + c * 32, xv);
-          tmem_ld_wait();
-        } else {
+        for (int j = 0; j < 32; ++j) { xk[j] = 0u; xv[j] = 0u; }
+      }
+      if (r < t.n_keys) {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) { xk[j] = 0u; xv[j] = 0u; }
-        }
-        if (r < t.n_keys) {
-#pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 a, b;
-            a.x = pack_bf16x2(__uint_as_float(xk[j]), __uint_as_float(xk[j + 1]));
-            a.y = pack_bf16x2(__uint_as_float(xk[j + 2]), __uint_as_float(xk[j + 3]));
-            a.z = pack_bf16x2(__uint_as_float(xk[j + 4]), __uint_as_float(xk[j + 5]));
-            a.w = pack_bf16x2(__uint_as_float(xk[j + 6]), __uint_as_float(xk[j + 7]));
-            b.x = pack_bf16x2(__uint_as_float(xv[j]), __uint_as_float(xv[j + 1]));
-            b.y = pack_bf16x2(__uint_as_float(xv[j + 2]), __uint_as_float(xv[j + 3]));
-            b.z = pack_bf16x2(__uint_as_float(xv[j + 4]), __uint_as_float(xv[j + 5]));
-            b.w = pack_bf16x2(__uint_as_float(xv[j + 6]), __uint_as_float(xv[j + 7]));
-            *reinterpret_cast<uint4*>(dk + c * 32 + j) = a;
-            *reinterpret_cast<uint4*>(dv + c * 32 + j) = b;
-          }
+        for (int j = 0; j < 32; j += 8) {
+          uint4 a, b;
+          a.x = pack_bf16x2(__uint_as_float(xk[j]), __uint_as_float(xk[j + 1]));
+          a.y = pack_bf16x2(__uint_as_float(xk[j + 2]), __uint_as_float(xk[j + 3]));
+          a.z = pack_bf16x2(__uint_as_float(xk[j + 4]), __uint_as_float(xk[j + 5]));
+          a.w = pack_bf16x2(__uint_as_float(xk[j + 6]), __uint_as_float(xk[j + 7]));
+          b.x = pack_bf16x2(__uint_as_float(xv[j]), __uint_as_float(xv[j + 1]));
+          b.y = pack_bf16x2(__uint_as_float(xv[j + 2]), __uint_as_float(xv[j + 3]));
+          b.z = pack_bf16x2(__uint_as_float(xv[j + 4]), __uint_as_float(xv[j + 5]));
+          b.w = pack_bf16x2(__uint_as_float(xv[j + 6]), __uint_as_float(xv[j + 7]));
+          *reinterpret_cast<uint4*>(dk + j) = a;
+          *reinterpret_cast<uint4*>(dv + j) = b;
         }
       }
     }

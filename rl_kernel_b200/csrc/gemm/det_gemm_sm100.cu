@@ -41,6 +41,7 @@ struct GemmParams {
   int out_fp32;         // 1: C is fp32
   int accumulate;       // 1: C += result (read-modify-write in fp32, rounded to C's dtype)
   int* status;
+  uint4* tree_scratch;      // tile_n 256 with chunks: per-CTA tree stack [grid][3][128][32] uint4 (L2 resident)
   int a_box_rows;           // rows of A that TMA brings per tile (128, or fewer when M < 128)
   int stage_a_bytes;        // shared-memory bytes reserved for the A tile of one stage
   int split_chunks;         // > 1: every canonical chunk is its own tile and writes its bf16 leaf
@@ -291,6 +292,93 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
           }
           if (row < p.M) p.stats[row * p.stats_stride + p.stats_tile0 + nt] = make_float2(m, ts.total());
+        } else if (BN == 256 && p.nchunks > 1) {
+          // chunk tree with 128x256 tiles: both accumulators fill TMEM, so the tree stack lives in a
+          // per-CTA global buffer (L2 resident; a row's entries are only ever touched by its own
+          // thread).  Stack reads are issued two 32-column slices ahead of their use.
+          int nmerge = 0;
+          while ((c >> nmerge) & 1) ++nmerge;                       // levels to fold into this chunk
+          uint4* sbase = p.tree_scratch + (static_cast<size_t>(blockIdx.x) * 3 * BM + row_in_tile) * 32;
+          constexpr size_t kLevel = static_cast<size_t>(BM) * 32;   // uint4 per level
+          uint4 pre[2][3][4];
+#pragma unroll
+          for (int ahead = 0; ahead < 2; ++ahead)
+#pragma unroll
+            for (int lv = 0; lv < 3; ++lv)
+              if (lv < nmerge)
+#pragma unroll
+                for (int q = 0; q < 4; ++q) pre[ahead][lv][q] = sbase[lv * kLevel + ahead * 4 + q];
+#pragma unroll
+          for (int sl = 0; sl < 8; ++sl) {
+            uint4 cur[3][4];
+#pragma unroll
+            for (int lv = 0; lv < 3; ++lv)
+#pragma unroll
+              for (int q = 0; q < 4; ++q) cur[lv][q] = pre[sl & 1][lv][q];
+            if (sl + 2 < 8) {
+#pragma unroll
+              for (int lv = 0; lv < 3; ++lv)
+                if (lv < nmerge)
+#pragma unroll
+                  for (int q = 0; q < 4; ++q) pre[sl & 1][lv][q] = sbase[lv * kLevel + (sl + 2) * 4 + q];
+            }
+            uint32_t r[32];
+            tmem_ld32(tmem_base + lane_off + a * BN + sl * 32, r);
+            tmem_ld_wait();
+            uint32_t v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              v[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+#pragma unroll
+            for (int lv = 0; lv < 3; ++lv) {
+              if (lv < nmerge) {
+                const uint32_t sv[16] = {cur[lv][0].x, cur[lv][0].y, cur[lv][0].z, cur[lv][0].w,
+                                         cur[lv][1].x, cur[lv][1].y, cur[lv][1].z, cur[lv][1].w,
+                                         cur[lv][2].x, cur[lv][2].y, cur[lv][2].z, cur[lv][2].w,
+                                         cur[lv][3].x, cur[lv][3].y, cur[lv][3].z, cur[lv][3].w};
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  v[j] = pack_bf16x2(__fadd_rn(bf16_lo(sv[j]), bf16_lo(v[j])), __fadd_rn(bf16_hi(sv[j]), bf16_hi(v[j])));
+              }
+            }
+            const int col0 = sl * 32;
+            if (!last) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                sbase[nmerge * kLevel + sl * 4 + q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else if (row < p.M) {
+              if (p.out_fp32) {
+                float* dst = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + n0 + col0;
+#pragma unroll
+                for (int j = 0; j < 16; j += 2) {
+                  if (n0 + col0 + 2 * j < p.N) {
+                    float4 o = make_float4(bf16_lo(v[j]), bf16_hi(v[j]), bf16_lo(v[j + 1]), bf16_hi(v[j + 1]));
+                    if (p.accumulate) {
+                      const float4 q4 = *reinterpret_cast<const float4*>(dst + 2 * j);
+                      o.x += q4.x; o.y += q4.y; o.z += q4.z; o.w += q4.w;
+                    }
+                    *reinterpret_cast<float4*>(dst + 2 * j) = o;
+                  }
+                }
+              } else {
+                __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + n0 + col0;
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                  if (n0 + col0 + 2 * j < p.N) {
+                    uint4 o = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    if (p.accumulate) {
+                      const uint4 q4 = *reinterpret_cast<const uint4*>(dst + 2 * j);
+                      o.x = pack_bf16x2(bf16_lo(o.x) + bf16_lo(q4.x), bf16_hi(o.x) + bf16_hi(q4.x));
+                      o.y = pack_bf16x2(bf16_lo(o.y) + bf16_lo(q4.y), bf16_hi(o.y) + bf16_hi(q4.y));
+                      o.z = pack_bf16x2(bf16_lo(o.z) + bf16_lo(q4.z), bf16_hi(o.z) + bf16_hi(q4.z));
+                      o.w = pack_bf16x2(bf16_lo(o.w) + bf16_lo(q4.w), bf16_hi(o.w) + bf16_hi(q4.w));
+                    }
+                    *reinterpret_cast<uint4*>(dst + 2 * j) = o;
+                  }
+                }
+              }
+            }
+          }
         } else
 #pragma unroll 1
         for (int col0 = 0; col0 < BN; col0 += 32) {
@@ -346,8 +434,19 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             int cc = c, level = 0;
             while (cc & 1) {
               uint32_t sv[16];
-              tmem_ld16(tmem_base + lane_off + kStackCol + level * 64 + (col0 >> 1), sv);
-              tmem_ld_wait();
+              if (BN == 128) {
+                tmem_ld16(tmem_base + lane_off + kStackCol + level * 64 + (col0 >> 1), sv);
+                tmem_ld_wait();
+              } else {
+                // tile_n 256: both accumulators fill TMEM, the stack lives in a per-CTA global buffer
+                // that only this thread ever touches for its row (and that stays in L2)
+                const uint4* sp = p.tree_scratch + ((static_cast<size_t>(blockIdx.x) * 3 + level) * BM + row_in_tile) * (BN / 8) + (col0 >> 3);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const uint4 t4 = sp[q];
+                  sv[4 * q] = t4.x; sv[4 * q + 1] = t4.y; sv[4 * q + 2] = t4.z; sv[4 * q + 3] = t4.w;
+                }
+              }
 #pragma unroll
               for (int j = 0; j < 16; ++j)
                 v[j] = pack_bf16x2(__fadd_rn(bf16_lo(sv[j]), bf16_lo(v[j])),
@@ -356,7 +455,13 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               ++level;
             }
             if (!last) {
-              tmem_st16(tmem_base + lane_off + kStackCol + level * 64 + (col0 >> 1), v);
+              if (BN == 128) {
+                tmem_st16(tmem_base + lane_off + kStackCol + level * 64 + (col0 >> 1), v);
+              } else {
+                uint4* sp = p.tree_scratch + ((static_cast<size_t>(blockIdx.x) * 3 + level) * BM + row_in_tile) * (BN / 8) + (col0 >> 3);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) sp[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+              }
             } else if (row < p.M) {
               if (p.out_fp32) {
                 float* dst = reinterpret_cast<float*>(p.C) + static_cast<long long>(row) * p.ldc + n0 + col0;
@@ -392,7 +497,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
           }
         }
-        if (p.nchunks > 1) tmem_st_wait();
+        if (p.nchunks > 1 && BN == 128) tmem_st_wait();
         tc_fence_before();
         mbar_arrive(acce0 + 8 * a);
       }
@@ -517,11 +622,27 @@ chunk_tree_kernel(const __nv_bfloat16* __restrict__ leaves, long long chunk_stri
 
 }  // namespace rlk
 
+// Per-device scratch of the tile_n 256 chunk tree: one stack of 3 levels per CTA of a full grid.
+static uint4* tree_scratch_for_device() {
+  static uint4* ptr[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!ptr[dev]) {
+    void* p = nullptr;
+    const size_t bytes = static_cast<size_t>(2 * rlk::sm_count()) * 3 * 128 * 32 * sizeof(uint4);
+    if (cudaMalloc(&p, bytes) != cudaSuccess) return nullptr;
+    ptr[dev] = static_cast<uint4*>(p);
+  }
+  return ptr[dev];
+}
+
 // C[M,N] = A * B^T.
 //  a_mn = 0: A is [M,K] row-major (lda >= K);  a_mn = 1: A is stored [K,M] row-major (lda >= M).
 //  b_mn = 0: B is [N,K] row-major (ldb >= K);  b_mn = 1: B is stored [K,N] row-major (ldb >= N).
 //  nchunks: canonical K chunks (1,2,4,8); K/nchunks must be a multiple of 64 when nchunks > 1.
-//  tile_n: 0 = pick from the shape; else one of 32, 64, 128, 256 (chunked GEMMs use 128).
+//  tile_n: 0 = pick from the shape; else one of 32, 64, 128, 256 (chunked GEMMs: 128 or 256).
 //  out_fp32 / accumulate: C dtype and C += result.
 RLK_API int rlk_det_gemm(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                          long long ldb, long long ldc, int a_mn, int b_mn, int nchunks,
@@ -545,7 +666,18 @@ RLK_API int rlk_det_gemm(const void* A, const void* B, void* C, int M, int N, in
   p.status = device_status_word();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int bn = tile_n;
-  if (nchunks > 1) bn = 128;
+  if (nchunks > 1) {
+    // many tiles: 128x256 tiles (full tensor-core rate) with the tree stack in an L2-resident
+    // scratch; few tiles: 128x128 tiles with the stack in TMEM
+    const long long tiles256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
+    // (the scratch-stack epilogue only keeps up with the MMA when a chunk has >= 1536 k)
+    bn = (tile_n == 256 || (tile_n == 0 && tiles256 >= sm_count() && K / nchunks >= 1536)) ? 256 : 128;
+    if (a_mn) bn = 128;
+    if (bn == 256) {
+      p.tree_scratch = tree_scratch_for_device();
+      if (!p.tree_scratch) return set_error(RLK_ERR_CUDA, "det_gemm: cannot allocate the tree scratch");
+    }
+  }
   if (bn == 0) {
     const int m_tiles = (M + 127) / 128;
     const int sms = sm_count();
@@ -553,7 +685,6 @@ RLK_API int rlk_det_gemm(const void* A, const void* B, void* C, int M, int N, in
     while (bn > 32 && (long long)m_tiles * ((N + bn - 1) / bn) < sms) bn >>= 1;
     if (b_mn || a_mn) bn = bn < 128 ? 128 : bn;
   }
-  if (nchunks > 1) RLK_REQUIRE(bn == 128, "det_gemm: chunked GEMM uses tile_n 128");
 #define RLK_GEMM_CASE(BN_, AM_, BM_)                                       \
   if (bn == BN_ && a_mn == AM_ && b_mn == BM_)                             \
     return launch_gemm<BN_, (AM_ != 0), (BM_ != 0)>(A, B, p, lda, ldb, s);

@@ -7,9 +7,9 @@
 //   xor butterfly 16,8,4,2,1 and the four warp sums are combined as (w0+w1)+(w2+w3).
 //   y = bf16( x * rstd * w ) with all factors fp32 ("multiply in fp32, round once").
 //   (backward and the 128-wide head norm use one warp per row with the same butterfly.)
-// Weight gradients are reduced in two fixed stages: each CTA sums its rows in ascending order
-// into a partial row of a scratch buffer, then a second kernel adds the partial rows in
-// ascending order.
+// Weight gradients are reduced in two fixed stages: each CTA sums its 32 rows in ascending order
+// (in registers) into a partial row of a scratch buffer, then a second kernel adds the partial
+// rows in ascending order.
 //
 // Covers csrc/cuda/norm/rmsnorm.cu:81-244 and csrc/cuda/rope/rope_sm90.cu:24-102 of the
 // reference, plus the QK-norm preprocessing of rl_engine/ops/attention/preprocess.py:180-345.
@@ -99,77 +99,102 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
 }
 
 // dx = rstd * (w*dy - xhat * mean(w*dy*xhat)) [+ dres];  partial dw[cta] = sum_rows dy * xhat.
-// Each CTA handles `rows_per_cta` consecutive rows, its 8 warps take rows round-robin, and the
-// 8 per-warp partial dw rows are added in warp order through shared memory.
-__global__ void __launch_bounds__(kNormWarps * 32)
+// One CTA of 128 threads walks `rows_per_cta` consecutive rows; thread t owns the 16-byte chunks
+// t, t+128, ... of every row, so its slice of the weight gradient accumulates in registers in
+// ascending row order -- no shared-memory traffic, fixed order.
+constexpr int kBwdRowsPerCta = 32;
+
+__global__ void __launch_bounds__(kRowThreads)
 rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
                    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ dres,
                    __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int rows, int H,
-                   float eps, int rows_per_cta) {
-  extern __shared__ float sdw[];  // [kNormWarps][H]
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+                   float eps) {
+  __shared__ float red[2][4];
+  const int tid = threadIdx.x;
   const int nchunk = H / 8;
-  float* my = sdw + warp * H;
-  for (int i = lane; i < H; i += 32) my[i] = 0.f;
-  __syncwarp();
-  const int r0 = blockIdx.x * rows_per_cta;
-  const int r1 = min(rows, r0 + rows_per_cta);
+  const int r0 = blockIdx.x * kBwdRowsPerCta;
+  const int r1 = min(rows, r0 + kBwdRowsPerCta);
   const uint4* wr = reinterpret_cast<const uint4*>(w);
-  for (int row = r0 + warp; row < r1; row += kNormWarps) {
+  float dwacc[kMaxChunks][8];
+#pragma unroll
+  for (int i = 0; i < kMaxChunks; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+  for (int row = r0; row < r1; ++row) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<long long>(row) * H);
     const uint4* gr = reinterpret_cast<const uint4*>(dy + static_cast<long long>(row) * H);
+    uint4 xv[kMaxChunks], gv[kMaxChunks], wv[kMaxChunks];
     float ss = 0.f;
-    for (int c = lane; c < nchunk; c += 32) {
-      const uint4 v = xr[c];
-      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float a = bf16_lo(u[i]), b = bf16_hi(u[i]);
-        ss = fmaf(a, a, ss);
-        ss = fmaf(b, b, ss);
+    for (int i = 0; i < kMaxChunks; ++i) {
+      const int c = tid + i * kRowThreads;
+      if (c < nchunk) {
+        xv[i] = xr[c]; gv[i] = gr[c]; wv[i] = wr[c];
+        const uint32_t u[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float a = bf16_lo(u[k]), b = bf16_hi(u[k]);
+          ss = fmaf(a, a, ss);
+          ss = fmaf(b, b, ss);
+        }
       }
     }
     ss = warp_sum_xor(ss);
+    if ((tid & 31) == 0) red[0][tid >> 5] = ss;
+    __syncthreads();
+    ss = (red[0][0] + red[0][1]) + (red[0][2] + red[0][3]);
     const float rstd = rsqrtf(ss / static_cast<float>(H) + eps);
     float dot = 0.f;
-    for (int c = lane; c < nchunk; c += 32) {
-      const uint4 v = xr[c], g = gr[c], ww = wr[c];
-      const uint32_t xv[4] = {v.x, v.y, v.z, v.w}, gv[4] = {g.x, g.y, g.z, g.w}, wv[4] = {ww.x, ww.y, ww.z, ww.w};
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        dot = fmaf(bf16_lo(wv[i]) * bf16_lo(gv[i]), bf16_lo(xv[i]) * rstd, dot);
-        dot = fmaf(bf16_hi(wv[i]) * bf16_hi(gv[i]), bf16_hi(xv[i]) * rstd, dot);
+    for (int i = 0; i < kMaxChunks; ++i) {
+      const int c = tid + i * kRowThreads;
+      if (c < nchunk) {
+        const uint32_t xu[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w}, gu[4] = {gv[i].x, gv[i].y, gv[i].z, gv[i].w},
+                       wu[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          dot = fmaf(bf16_lo(wu[k]) * bf16_lo(gu[k]), bf16_lo(xu[k]) * rstd, dot);
+          dot = fmaf(bf16_hi(wu[k]) * bf16_hi(gu[k]), bf16_hi(xu[k]) * rstd, dot);
+        }
       }
     }
-    dot = warp_sum_xor(dot) / static_cast<float>(H);
+    dot = warp_sum_xor(dot);
+    if ((tid & 31) == 0) red[1][tid >> 5] = dot;
+    __syncthreads();
+    dot = ((red[1][0] + red[1][1]) + (red[1][2] + red[1][3])) / static_cast<float>(H);
     uint4* dxr = reinterpret_cast<uint4*>(dx + static_cast<long long>(row) * H);
     const uint4* drr = dres ? reinterpret_cast<const uint4*>(dres + static_cast<long long>(row) * H) : nullptr;
-    for (int c = lane; c < nchunk; c += 32) {
-      const uint4 v = xr[c], g = gr[c], ww = wr[c];
-      uint4 dr = make_uint4(0, 0, 0, 0);
-      if (drr) dr = drr[c];
-      const uint32_t xv[4] = {v.x, v.y, v.z, v.w}, gv[4] = {g.x, g.y, g.z, g.w}, wv[4] = {ww.x, ww.y, ww.z, ww.w};
-      const uint32_t dv[4] = {dr.x, dr.y, dr.z, dr.w};
-      uint32_t ov[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float xh0 = bf16_lo(xv[i]) * rstd, xh1 = bf16_hi(xv[i]) * rstd;
-        const float g0 = bf16_lo(gv[i]), g1 = bf16_hi(gv[i]);
-        float d0 = rstd * (bf16_lo(wv[i]) * g0 - xh0 * dot) + bf16_lo(dv[i]);
-        float d1 = rstd * (bf16_hi(wv[i]) * g1 - xh1 * dot) + bf16_hi(dv[i]);
-        ov[i] = pack_bf16x2(d0, d1);
-        my[c * 8 + 2 * i] += g0 * xh0;
-        my[c * 8 + 2 * i + 1] += g1 * xh1;
+    for (int i = 0; i < kMaxChunks; ++i) {
+      const int c = tid + i * kRowThreads;
+      if (c < nchunk) {
+        uint4 dr = make_uint4(0, 0, 0, 0);
+        if (drr) dr = drr[c];
+        const uint32_t xu[4] = {xv[i].x, xv[i].y, xv[i].z, xv[i].w}, gu[4] = {gv[i].x, gv[i].y, gv[i].z, gv[i].w},
+                       wu[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w}, du[4] = {dr.x, dr.y, dr.z, dr.w};
+        uint32_t ov[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float xh0 = bf16_lo(xu[k]) * rstd, xh1 = bf16_hi(xu[k]) * rstd;
+          const float g0 = bf16_lo(gu[k]), g1 = bf16_hi(gu[k]);
+          ov[k] = pack_bf16x2(rstd * (bf16_lo(wu[k]) * g0 - xh0 * dot) + bf16_lo(du[k]),
+                              rstd * (bf16_hi(wu[k]) * g1 - xh1 * dot) + bf16_hi(du[k]));
+          dwacc[i][2 * k] += g0 * xh0;
+          dwacc[i][2 * k + 1] += g1 * xh1;
+        }
+        dxr[c] = make_uint4(ov[0], ov[1], ov[2], ov[3]);
       }
-      dxr[c] = make_uint4(ov[0], ov[1], ov[2], ov[3]);
     }
+    __syncthreads();   // red[] is reused by the next row
   }
-  __syncthreads();
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    float s = 0.f;
+  float* out = dw_partial + static_cast<long long>(blockIdx.x) * H;
 #pragma unroll
-    for (int k = 0; k < kNormWarps; ++k) s += sdw[k * H + i];
-    dw_partial[static_cast<long long>(blockIdx.x) * H + i] = s;
+  for (int i = 0; i < kMaxChunks; ++i) {
+    const int c = tid + i * kRowThreads;
+    if (c < nchunk) {
+      *reinterpret_cast<float4*>(out + c * 8) = make_float4(dwacc[i][0], dwacc[i][1], dwacc[i][2], dwacc[i][3]);
+      *reinterpret_cast<float4*>(out + c * 8 + 4) = make_float4(dwacc[i][4], dwacc[i][5], dwacc[i][6], dwacc[i][7]);
+    }
   }
 }
 
@@ -366,23 +391,20 @@ RLK_API int rlk_rmsnorm_fwd(const void* x, const void* res, const void* w, void*
 
 // Number of fp32 elements of scratch that rlk_rmsnorm_bwd needs for `rows` x `H`.
 RLK_API long long rlk_rmsnorm_bwd_scratch_elems(int rows, int H) {
-  const int rows_per_cta = 64;
-  return static_cast<long long>((rows + rows_per_cta - 1) / rows_per_cta) * H;
+  return static_cast<long long>((rows + kBwdRowsPerCta - 1) / kBwdRowsPerCta) * H;
 }
 
 // dx = d/dx [ rmsnorm(x) * w ] (+ dres); dw (bf16 or fp32, optionally accumulated) in fixed order.
 RLK_API int rlk_rmsnorm_bwd(const void* x, const void* w, const void* dy, const void* dres,
                             void* dx, float* scratch, void* dw_bf16, float* dw_f32,
                             int accumulate_dw, int rows, int H, float eps, void* stream) {
-  RLK_REQUIRE(rows > 0 && H > 0 && H % 8 == 0 && H <= 6144, "rmsnorm_bwd: H must be a multiple of 8, <= 6144");
-  const int rows_per_cta = 64;
-  const int grid = (rows + rows_per_cta - 1) / rows_per_cta;
-  const int smem = kNormWarps * H * 4;
+  RLK_REQUIRE(rows > 0 && H > 0 && H % 8 == 0 && H <= kRowThreads * kMaxChunks * 8,
+              "rmsnorm_bwd: H must be a multiple of 8, <= 8192");
+  const int grid = (rows + kBwdRowsPerCta - 1) / kBwdRowsPerCta;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  RLK_CHECK_CUDA(cudaFuncSetAttribute(rmsnorm_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  rmsnorm_bwd_kernel<<<grid, kNormWarps * 32, smem, s>>>(
+  rmsnorm_bwd_kernel<<<grid, kRowThreads, 0, s>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dy,
-      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, rows, H, eps, rows_per_cta);
+      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, rows, H, eps);
   RLK_CHECK_CUDA(cudaGetLastError());
   reduce_partials_kernel<<<(H + 255) / 256, 256, 0, s>>>(scratch, grid, H, (__nv_bfloat16*)dw_bf16,
                                                          dw_f32, accumulate_dw);

@@ -69,6 +69,10 @@ def test_canonical_chunk_tree(nchunks):
     while len(leaves) > 1:
         leaves = [(leaves[i].float() + leaves[i + 1].float()).to(BF) for i in range(0, len(leaves), 2)]
     assert torch.equal(got, leaves[0])
+    # 128x256 tiles with the tree stack in the L2-resident scratch give the same bits
+    assert torch.equal(_gemm(a, b, M, N, K, nchunks=nchunks, tile_n=256), got)
+    bt = b.t().contiguous()
+    assert torch.equal(_gemm(a, bt, M, N, K, nchunks=nchunks, tile_n=256, b_mn=True), got)
     # the split (small-M) form gives the same bits
     out = torch.empty(M, N, device=dev(), dtype=BF)
     scratch = torch.empty(nchunks * M * N, device=dev(), dtype=BF)
