@@ -6,8 +6,8 @@ optimizer) tokens/s, with the train-vs-rollout log-prob mismatch count.
         --master-port P bench.py --gpus N --steps K --warmup W
     python bench.py --impl reference ...     # the unmodified reference from baseline/_ref
 
-Weak scaling: every GPU brings 8 prompts x group 8 x (512 + 1024) tokens; N GPUs run TP=min(N,4)
-and, at N=8, CP... see ``parallel_plan``.  Data is synthetic (uniform-random prompt ids,
+Weak scaling: every GPU brings 8 prompts x group 8 x (512 + 1024) tokens; N = 2 and 4 run one
+TP-N replica, N = 8 trains TP4 x CP2 and rolls out on two TP4 engines (``parallel_plan``).  Data is synthetic (uniform-random prompt ids,
 Bernoulli(0.5) rewards), weights are random-init N(0, 0.02) of the official architecture.
 One JSON line is printed by rank 0.
 """
@@ -76,9 +76,15 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def parallel_plan(n: int) -> dict:
+def parallel_plan(n: int, override: str = "") -> dict:
     """TP inside a replica; at 8 GPUs the training replica is TP4 x CP2 and rollout runs two TP4
-    engines (the reference's headline topology)."""
+    engines (the reference's headline topology).  ``override`` ("tp2xcp2") is a debugging aid."""
+    if override:
+        tp, _, cp = override.lower().removeprefix("tp").partition("xcp")
+        tp, cp = int(tp), int(cp or 1)
+        if tp * cp != n:
+            raise SystemExit(f"--plan {override} does not use {n} GPUs")
+        return {"tp": tp, "cp": cp, "name": f"tp{tp}" + (f"xcp{cp}" if cp > 1 else "")}
     if n == 1:
         return {"tp": 1, "cp": 1, "name": "tp1"}
     if n in (2, 4):
@@ -106,15 +112,16 @@ def run_ours(args) -> dict:
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    plan = parallel_plan(args.gpus)
+    plan = parallel_plan(args.gpus, args.plan)
     ctx = build_parallel_context(plan["tp"], plan["cp"], dev)
 
     spec = Qwen3DenseSpec.official()
     if args.layers:
         spec = spec.with_layers(args.layers)
-    cfg = GRPOConfig(num_prompts=PROMPTS_PER_GPU * args.gpus // max(1, ctx.dp_size), group_size=GROUP,
-                     prompt_len=PROMPT_LEN, response_len=args.response_len, micro_batch_seqs=args.micro_batch,
-                     share_rollout_weights=True, seed=1234)
+    # one training replica spans all GPUs; a micro-batch keeps micro_batch x seq_len tokens per rank
+    cfg = GRPOConfig(num_prompts=PROMPTS_PER_GPU * args.gpus, group_size=GROUP,
+                     prompt_len=PROMPT_LEN, response_len=args.response_len,
+                     micro_batch_seqs=args.micro_batch * plan["cp"], share_rollout_weights=True, seed=1234)
     trainer = GRPOTrainer(spec, cfg, dev, ctx=ctx)
     n_prompts_global = PROMPTS_PER_GPU * args.gpus
     tokens_per_step = n_prompts_global * GROUP * (PROMPT_LEN + args.response_len)
@@ -206,6 +213,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the config)")
     ap.add_argument("--response-len", type=int, default=RESPONSE_LEN, help="debug only")
     ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--plan", default="", help="debug only: e.g. tp1xcp2 instead of the default plan for --gpus")
     args = ap.parse_args()
     if args.impl == "reference":
         from baseline.reference_arm import run_reference

@@ -124,25 +124,44 @@ def attn_bwd_delta(o2d: torch.Tensor, do2d: torch.Tensor, delta: torch.Tensor, T
     _count()
 
 
-def attn_bwd_dq(q2d, do2d, k2d, v2d, lse, delta, dq2d, tiles, scale: float) -> None:
+def _as_list(x):
+    return list(x) if isinstance(x, (list, tuple)) else [x]
+
+
+def attn_bwd_dq(q2d, do2d, k2d, v2d, lse, delta, dq2d, tiles, scale: float, *,
+                cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False) -> None:
+    """``k2d`` / ``v2d``: one tensor, or one per context-parallel rank (peers' buffers mapped here)."""
+    ks, vs = _as_list(k2d), _as_list(v2d)
+    n_src, k0 = len(ks), ks[0]
+    kp = (c_void_p * n_src)(*[t.data_ptr() for t in ks])
+    vp = (c_void_p * n_src)(*[t.data_ptr() for t in vs])
     rc = _lib().rlk_attn_bwd_dq(ext.ptr(q2d), ext.ptr(do2d), _ll(q2d.shape[0]), _ll(q2d.shape[1]),
-                                _ll(q2d.stride(0)), _ll(do2d.stride(0)), ext.ptr(k2d), ext.ptr(v2d),
-                                _ll(k2d.shape[0]), _ll(k2d.shape[1]), _ll(k2d.stride(0)),
+                                _ll(q2d.stride(0)), _ll(do2d.stride(0)), kp, vp, c_int(n_src),
+                                _ll(k0.shape[0]), _ll(k0.shape[1]), _ll(k0.stride(0)),
                                 ext.ptr(lse), ext.ptr(delta), ext.ptr(dq2d), _ll(dq2d.stride(0)),
                                 ext.ptr(tiles), c_int(tiles.shape[0]), c_float(scale),
-                                ext.stream_ptr(q2d.device))
+                                c_int(cp_blocks_per_chunk), c_int(int(cp_zigzag)),
+                                ext.stream_ptr(dq2d.device))
     ext.check(rc, "attn_bwd_dq")
     _count()
 
 
-def attn_bwd_dkv(q2d, do2d, k2d, v2d, lse, delta, dk2d, dv2d, kv_tiles, scale: float) -> None:
-    assert dk2d.stride(0) == dv2d.stride(0)
-    rc = _lib().rlk_attn_bwd_dkv(ext.ptr(q2d), ext.ptr(do2d), _ll(q2d.shape[0]), _ll(q2d.shape[1]),
-                                 _ll(q2d.stride(0)), _ll(do2d.stride(0)), ext.ptr(k2d), ext.ptr(v2d),
-                                 _ll(k2d.shape[0]), _ll(k2d.shape[1]), _ll(k2d.stride(0)),
-                                 ext.ptr(lse), ext.ptr(delta), ext.ptr(dk2d), ext.ptr(dv2d),
-                                 _ll(dk2d.stride(0)), ext.ptr(kv_tiles), c_int(kv_tiles.shape[0]),
-                                 c_float(scale), ext.stream_ptr(q2d.device))
+def attn_bwd_dkv(q2d, do2d, k2d, v2d, lse, delta, dk2d, dv2d, kv_tiles, scale: float, *,
+                 cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False) -> None:
+    """``q2d`` / ``do2d`` / ``lse`` / ``delta``: one tensor each, or one per context-parallel rank."""
+    qs, dos, ls, ds = _as_list(q2d), _as_list(do2d), _as_list(lse), _as_list(delta)
+    n_src, q0, do0 = len(qs), qs[0], dos[0]
+    assert len(dos) == len(ls) == len(ds) == n_src
+    qp = (c_void_p * n_src)(*[t.data_ptr() for t in qs])
+    dop = (c_void_p * n_src)(*[t.data_ptr() for t in dos])
+    lp = (c_void_p * n_src)(*[t.data_ptr() for t in ls])
+    dp = (c_void_p * n_src)(*[t.data_ptr() for t in ds])
+    rc = _lib().rlk_attn_bwd_dkv(qp, dop, c_int(n_src), _ll(q0.shape[0]), _ll(q0.shape[1]),
+                                 _ll(q0.stride(0)), _ll(do0.stride(0)), ext.ptr(k2d), ext.ptr(v2d),
+                                 _ll(k2d.shape[0]), _ll(k2d.shape[1]), _ll(k2d.stride(0)), lp, dp,
+                                 ext.ptr(dk2d), ext.ptr(dv2d), _ll(dk2d.stride(0)), ext.ptr(kv_tiles),
+                                 c_int(kv_tiles.shape[0]), c_float(scale), c_int(cp_blocks_per_chunk),
+                                 c_int(int(cp_zigzag)), ext.stream_ptr(dk2d.device))
     ext.check(rc, "attn_bwd_dkv")
     _count()
 

@@ -57,6 +57,7 @@ struct AttnDqParams {
   __nv_bfloat16* dQ;
   long long lddq;
   float scale, scale_log2;
+  CpLayout cp;         // context parallel: which rank's K/V holds canonical block b
   int* status;
 };
 
@@ -70,10 +71,10 @@ struct DqSmem {
   static constexpr int kBytes = kBars + 256 + 1024;
 };
 
+template <int NSRC>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
-                   const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                   const AttnDqParams p) {
+                   const __grid_constant__ KvMaps<NSRC> kv, const AttnDqParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -130,15 +131,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       for (int b = 0; b < nblk; ++b) {
         const int s = b & 1;
         const uint32_t ph = (b >> 1) & 1;
-        const int row = t.kv_row0 + b * kAttnBlock;
+        int src, lb;
+        cp_locate_block(p.cp, b, src, lb);   // plain TMA loads, possibly from a peer's memory
+        if (NSRC == 1) src = 0;
+        const int row = t.kv_row0 + lb * kAttnBlock;
         if (!mbar_wait(BAR(K_EMPTY + s), ph ^ 1, abort_flag, p.status, 301)) break;
         mbar_expect_tx(BAR(K_FULL + s), kTile);
-        tma_load_2d(sK + s * kTile, &tmK, t.kv_col0, row, BAR(K_FULL + s));
-        tma_load_2d(sK + s * kTile + kHalf, &tmK, t.kv_col0 + 64, row, BAR(K_FULL + s));
+        tma_load_2d(sK + s * kTile, &kv.k[src], t.kv_col0, row, BAR(K_FULL + s));
+        tma_load_2d(sK + s * kTile + kHalf, &kv.k[src], t.kv_col0 + 64, row, BAR(K_FULL + s));
         if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1, abort_flag, p.status, 302)) break;
         mbar_expect_tx(BAR(V_FULL + s), kTile);
-        tma_load_2d(sV + s * kTile, &tmV, t.kv_col0, row, BAR(V_FULL + s));
-        tma_load_2d(sV + s * kTile + kHalf, &tmV, t.kv_col0 + 64, row, BAR(V_FULL + s));
+        tma_load_2d(sV + s * kTile, &kv.v[src], t.kv_col0, row, BAR(V_FULL + s));
+        tma_load_2d(sV + s * kTile + kHalf, &kv.v[src], t.kv_col0 + 64, row, BAR(V_FULL + s));
       }
     }
   } else if (warp == 1) {
@@ -279,8 +283,9 @@ struct AttnKvTile {
 struct AttnDkvParams {
   const AttnKvTile* tiles;
   int n_tiles;
-  const float* lse;
-  const float* delta;
+  const float* lse[8];    // per context-parallel rank (index 0 only when not context parallel)
+  const float* delta[8];
+  CpLayout cp;            // which rank holds query tile qt of a sequence, and where
   __nv_bfloat16* dK;
   __nv_bfloat16* dV;
   long long lddkv;
@@ -299,10 +304,13 @@ struct DkvSmem {
   static constexpr int kBytes = kBars + 256 + 1024;
 };
 
+// Context parallel (NSRC > 1): the key block is local; the query tiles that see it are spread over
+// the ranks.  Q and dO tiles arrive through the owning rank's tensor maps (qdo.k = Q, qdo.v = dO)
+// and lse / delta through plain peer loads, in the same ascending query-tile order as on one GPU.
+template <int NSRC>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
-                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                    const AttnDkvParams p) {
+attn_bwd_dkv_kernel(const __grid_constant__ KvMaps<NSRC> qdo, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const AttnDkvParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -358,11 +366,14 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int g = it / n_qt, qt = qt0 + it % n_qt;
         if (!mbar_wait(BAR(Q_EMPTY), (it & 1) ^ 1, abort_flag, p.status, 311)) break;
         mbar_expect_tx(BAR(Q_FULL), 2 * kTile);
-        const int row = t.q_row0 + qt * 128, col = t.q_col0 + g * 128;
-        tma_load_2d(sQ, &tmQ, col, row, BAR(Q_FULL));
-        tma_load_2d(sQ + kHalf, &tmQ, col + 64, row, BAR(Q_FULL));
-        tma_load_2d(sDO, &tmDO, col, row, BAR(Q_FULL));
-        tma_load_2d(sDO + kHalf, &tmDO, col + 64, row, BAR(Q_FULL));
+        int src, lb;
+        cp_locate_block(p.cp, qt, src, lb);
+        if (NSRC == 1) src = 0;
+        const int row = t.q_row0 + lb * 128, col = t.q_col0 + g * 128;
+        tma_load_2d(sQ, &qdo.k[src], col, row, BAR(Q_FULL));
+        tma_load_2d(sQ + kHalf, &qdo.k[src], col + 64, row, BAR(Q_FULL));
+        tma_load_2d(sDO, &qdo.v[src], col, row, BAR(Q_FULL));
+        tma_load_2d(sDO + kHalf, &qdo.v[src], col + 64, row, BAR(Q_FULL));
       }
     }
   } else if (warp == 1) {
@@ -415,10 +426,13 @@ attn_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       float lse2 = 0.f, dlt = 0.f;
       int nvis = 0;  // keys of this block visible to this query row
       if (qi < t.n_q) {
-        const long long li = t.lse_off + static_cast<long long>(qi) * t.lse_stride +
+        int src, lb;
+        cp_locate_block(p.cp, qt, src, lb);
+        if (NSRC == 1) src = 0;
+        const long long li = t.lse_off + static_cast<long long>(lb * 128 + r) * t.lse_stride +
                              static_cast<long long>(g) * t.lse_head_stride;
-        lse2 = p.lse[li] * kLog2e;
-        dlt = p.delta[li];
+        lse2 = p.lse[src][li] * kLog2e;
+        dlt = p.delta[src][li];
         nvis = t.q_pos0 + qi + 1 - t.key0;
         if (nvis > t.n_keys) nvis = t.n_keys;
       }
@@ -521,49 +535,100 @@ RLK_API int rlk_attn_bwd_delta(const void* O, long long ldo, const void* dO, lon
   return RLK_OK;
 }
 
-// Geometry as in rlk_attn_fwd; lse and delta use the forward's lse indexing.
+// Geometry as in rlk_attn_fwd; lse and delta use the forward's lse indexing.  n_src in 2..8
+// (context parallel): k_ptrs[s] / v_ptrs[s] is rank s's K / V buffer mapped into this process,
+// cp_blocks_per_chunk / cp_zigzag describe the layout (rlk::CpLayout).
 RLK_API int rlk_attn_bwd_dq(const void* Q, const void* dO, long long q_rows, long long q_cols,
-                            long long ldq, long long lddo, const void* K, const void* V,
-                            long long kv_rows, long long kv_cols, long long ldkv, const float* lse,
-                            const float* delta, void* dQ, long long lddq, const void* tiles,
-                            int n_tiles, float scale, void* stream) {
+                            long long ldq, long long lddo, const void* const* k_ptrs,
+                            const void* const* v_ptrs, int n_src, long long kv_rows, long long kv_cols,
+                            long long ldkv, const float* lse, const float* delta, void* dQ,
+                            long long lddq, const void* tiles, int n_tiles, float scale,
+                            int cp_blocks_per_chunk, int cp_zigzag, void* stream) {
   RLK_REQUIRE(n_tiles > 0, "attn_bwd_dq: no tiles");
-  CUtensorMap tmQ, tmDO, tmK, tmV;
+  RLK_REQUIRE(n_src == 1 || (n_src >= 2 && n_src <= 8), "attn_bwd_dq: n_src must be 1..8");
+  RLK_REQUIRE(n_src == 1 || cp_blocks_per_chunk > 0, "attn_bwd_dq: cp_blocks_per_chunk must be positive");
+  CUtensorMap tmQ, tmDO;
   int rc;
   if ((rc = make_tmap_2d_sw128(&tmQ, Q, q_rows, q_cols, ldq, 128, 64, 2))) return rc;
   if ((rc = make_tmap_2d_sw128(&tmDO, dO, q_rows, q_cols, lddo, 128, 64, 2))) return rc;
-  if ((rc = make_tmap_2d_sw128(&tmK, K, kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
-  if ((rc = make_tmap_2d_sw128(&tmV, V, kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
   AttnDqParams p{static_cast<const AttnTile*>(tiles), n_tiles, lse, delta,
-                 static_cast<__nv_bfloat16*>(dQ), lddq, scale, scale * kLog2e, device_status_word()};
-  static bool flags[64] = {false};
-  if ((rc = set_smem_attr(attn_bwd_dq_kernel, DqSmem::kBytes, flags))) return rc;
-  attn_bwd_dq_kernel<<<n_tiles, kBwdThreads, DqSmem::kBytes, static_cast<cudaStream_t>(stream)>>>(
-      tmQ, tmDO, tmK, tmV, p);
+                 static_cast<__nv_bfloat16*>(dQ), lddq, scale, scale * kLog2e,
+                 CpLayout{n_src > 1 ? n_src : 1, cp_blocks_per_chunk, cp_zigzag}, device_status_word()};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_src == 1) {
+    KvMaps<1> kv;
+    if ((rc = make_tmap_2d_sw128(&kv.k[0], k_ptrs[0], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
+    if ((rc = make_tmap_2d_sw128(&kv.v[0], v_ptrs[0], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
+    static bool flags[64] = {false};
+    if ((rc = set_smem_attr(attn_bwd_dq_kernel<1>, DqSmem::kBytes, flags))) return rc;
+    attn_bwd_dq_kernel<1><<<n_tiles, kBwdThreads, DqSmem::kBytes, st>>>(tmQ, tmDO, kv, p);
+  } else {
+    KvMaps<8> kv;
+    for (int i = 0; i < 8; ++i) {
+      const int j = i < n_src ? i : 0;
+      if ((rc = make_tmap_2d_sw128(&kv.k[i], k_ptrs[j], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
+      if ((rc = make_tmap_2d_sw128(&kv.v[i], v_ptrs[j], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
+    }
+    static bool flags[64] = {false};
+    if ((rc = set_smem_attr(attn_bwd_dq_kernel<8>, DqSmem::kBytes, flags))) return rc;
+    attn_bwd_dq_kernel<8><<<n_tiles, kBwdThreads, DqSmem::kBytes, st>>>(tmQ, tmDO, kv, p);
+  }
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
 
-// `tiles` is a device array of rlk::AttnKvTile (12 ints each).
-RLK_API int rlk_attn_bwd_dkv(const void* Q, const void* dO, long long q_rows, long long q_cols,
-                             long long ldq, long long lddo, const void* K, const void* V,
-                             long long kv_rows, long long kv_cols, long long ldkv, const float* lse,
-                             const float* delta, void* dK, void* dV, long long lddkv,
-                             const void* tiles, int n_tiles, float scale, void* stream) {
+// `tiles` is a device array of rlk::AttnKvTile (12 ints each).  n_src in 2..8 (context parallel):
+// q_ptrs / do_ptrs / lse_ptrs / delta_ptrs hold one pointer per rank (this rank's own at its own
+// index), all with the same shape and pitch; the tiles give key positions in the whole sequence
+// (key0), n_q = the whole sequence length and q_row0 / lse_off for the sequence's first LOCAL row.
+RLK_API int rlk_attn_bwd_dkv(const void* const* q_ptrs, const void* const* do_ptrs, int n_src,
+                             long long q_rows, long long q_cols, long long ldq, long long lddo,
+                             const void* K, const void* V, long long kv_rows, long long kv_cols,
+                             long long ldkv, const float* const* lse_ptrs,
+                             const float* const* delta_ptrs, void* dK, void* dV, long long lddkv,
+                             const void* tiles, int n_tiles, float scale, int cp_blocks_per_chunk,
+                             int cp_zigzag, void* stream) {
   RLK_REQUIRE(n_tiles > 0, "attn_bwd_dkv: no tiles");
-  CUtensorMap tmQ, tmDO, tmK, tmV;
+  RLK_REQUIRE(n_src == 1 || (n_src >= 2 && n_src <= 8), "attn_bwd_dkv: n_src must be 1..8");
+  RLK_REQUIRE(n_src == 1 || cp_blocks_per_chunk > 0, "attn_bwd_dkv: cp_blocks_per_chunk must be positive");
+  CUtensorMap tmK, tmV;
   int rc;
-  if ((rc = make_tmap_2d_sw128(&tmQ, Q, q_rows, q_cols, ldq, 128, 64, 2))) return rc;
-  if ((rc = make_tmap_2d_sw128(&tmDO, dO, q_rows, q_cols, lddo, 128, 64, 2))) return rc;
   if ((rc = make_tmap_2d_sw128(&tmK, K, kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
   if ((rc = make_tmap_2d_sw128(&tmV, V, kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
-  AttnDkvParams p{static_cast<const AttnKvTile*>(tiles), n_tiles, lse, delta,
-                  static_cast<__nv_bfloat16*>(dK), static_cast<__nv_bfloat16*>(dV), lddkv, scale,
-                  scale * kLog2e, device_status_word()};
-  static bool flags[64] = {false};
-  if ((rc = set_smem_attr(attn_bwd_dkv_kernel, DkvSmem::kBytes, flags))) return rc;
-  attn_bwd_dkv_kernel<<<n_tiles, kBwdThreads, DkvSmem::kBytes, static_cast<cudaStream_t>(stream)>>>(
-      tmQ, tmDO, tmK, tmV, p);
+  AttnDkvParams p{};
+  p.tiles = static_cast<const AttnKvTile*>(tiles);
+  p.n_tiles = n_tiles;
+  for (int i = 0; i < 8; ++i) {
+    const int j = i < n_src ? i : 0;
+    p.lse[i] = lse_ptrs[j];
+    p.delta[i] = delta_ptrs[j];
+  }
+  p.cp = CpLayout{n_src > 1 ? n_src : 1, cp_blocks_per_chunk, cp_zigzag};
+  p.dK = static_cast<__nv_bfloat16*>(dK);
+  p.dV = static_cast<__nv_bfloat16*>(dV);
+  p.lddkv = lddkv;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  p.status = device_status_word();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (n_src == 1) {
+    KvMaps<1> qdo;
+    if ((rc = make_tmap_2d_sw128(&qdo.k[0], q_ptrs[0], q_rows, q_cols, ldq, 128, 64, 2))) return rc;
+    if ((rc = make_tmap_2d_sw128(&qdo.v[0], do_ptrs[0], q_rows, q_cols, lddo, 128, 64, 2))) return rc;
+    static bool flags[64] = {false};
+    if ((rc = set_smem_attr(attn_bwd_dkv_kernel<1>, DkvSmem::kBytes, flags))) return rc;
+    attn_bwd_dkv_kernel<1><<<n_tiles, kBwdThreads, DkvSmem::kBytes, st>>>(qdo, tmK, tmV, p);
+  } else {
+    KvMaps<8> qdo;
+    for (int i = 0; i < 8; ++i) {
+      const int j = i < n_src ? i : 0;
+      if ((rc = make_tmap_2d_sw128(&qdo.k[i], q_ptrs[j], q_rows, q_cols, ldq, 128, 64, 2))) return rc;
+      if ((rc = make_tmap_2d_sw128(&qdo.v[i], do_ptrs[j], q_rows, q_cols, lddo, 128, 64, 2))) return rc;
+    }
+    static bool flags[64] = {false};
+    if ((rc = set_smem_attr(attn_bwd_dkv_kernel<8>, DkvSmem::kBytes, flags))) return rc;
+    attn_bwd_dkv_kernel<8><<<n_tiles, kBwdThreads, DkvSmem::kBytes, st>>>(qdo, tmK, tmV, p);
+  }
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

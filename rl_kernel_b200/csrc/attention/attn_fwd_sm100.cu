@@ -30,12 +30,6 @@ constexpr int kSplit = 4;           // threads (column slices) per query row
 constexpr int kTileBytes = 128 * 128 * 2;  // one 128x128 bf16 operand tile (two 64-wide boxes)
 constexpr int kHalfBytes = 128 * 64 * 2;
 
-template <int NSRC>
-struct KvMaps {
-  CUtensorMap k[NSRC];
-  CUtensorMap v[NSRC];
-};
-
 struct AttnFwdParams {
   const AttnTile* tiles;
   int n_tiles;
@@ -77,16 +71,9 @@ __device__ __forceinline__ void cp_locate(const AttnFwdParams& p, const AttnTile
     row = t.kv_row0 + b * kAttnBlock;
     return;
   }
-  const int chunk = b / p.cp_blocks_per_chunk;
-  const int within = b - chunk * p.cp_blocks_per_chunk;
-  int local_chunk = 0;
-  if (p.cp_zigzag) {
-    if (chunk < p.cp_ranks) { src = chunk; local_chunk = 0; }
-    else { src = 2 * p.cp_ranks - 1 - chunk; local_chunk = 1; }
-  } else {
-    src = chunk;
-  }
-  row = t.kv_row0 + (local_chunk * p.cp_blocks_per_chunk + within) * kAttnBlock;
+  int lb;
+  cp_locate_block(CpLayout{p.cp_ranks, p.cp_blocks_per_chunk, p.cp_zigzag}, b, src, lb);
+  row = t.kv_row0 + lb * kAttnBlock;
 }
 
 template <int NSRC>

@@ -12,6 +12,7 @@
 // That is what makes selected-token log-probs of rollout (decode) and training (full sequence)
 // bitwise equal, for every batch size and query tiling.
 #pragma once
+#include <cuda.h>
 #include <stdint.h>
 
 namespace rlk {
@@ -33,5 +34,46 @@ struct AttnTile {
 
 constexpr int kAttnBlock = 128;  // canonical KV block and query tile
 constexpr int kHeadDim = 128;
+
+// One tensor map per context-parallel rank for a pair of operands that are fetched together
+// (K and V in the forward and dQ kernels, Q and dO in the dK/dV kernel).
+template <int NSRC>
+struct KvMaps {
+  CUtensorMap k[NSRC];
+  CUtensorMap v[NSRC];
+};
+
+// How the 128-token blocks of one sequence are spread over context-parallel ranks.  Every rank
+// stores its blocks of a sequence back to back, so "local block i" is row 128*i after the
+// sequence's first local row.  contiguous: the sequence is cut into `ranks` chunks of
+// `blocks_per_chunk` blocks, chunk c on rank c.  zigzag: 2*ranks chunks, rank c holds chunks c and
+// 2*ranks-1-c (in that order), which balances causal work.
+struct CpLayout {
+  int ranks;             // <= 1: not context parallel
+  int blocks_per_chunk;
+  int zigzag;
+};
+
+__host__ __device__ __forceinline__ void cp_locate_block(const CpLayout& c, int b, int& src, int& local_block) {
+  if (c.ranks <= 1) {
+    src = 0;
+    local_block = b;
+    return;
+  }
+  const int chunk = b / c.blocks_per_chunk;
+  const int within = b - chunk * c.blocks_per_chunk;
+  int local_chunk = 0;
+  if (c.zigzag) {
+    if (chunk < c.ranks) {
+      src = chunk;
+    } else {
+      src = 2 * c.ranks - 1 - chunk;
+      local_chunk = 1;
+    }
+  } else {
+    src = chunk;
+  }
+  local_block = local_chunk * c.blocks_per_chunk + within;
+}
 
 }  // namespace rlk

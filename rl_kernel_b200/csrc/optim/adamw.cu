@@ -63,23 +63,71 @@ __global__ void __launch_bounds__(256) adamw_kernel(const AdamParams p) {
 // biased exponent (256 bins); integer addition is associative, so the bins -- and the norm
 // computed from them in a fixed order -- do not depend on how the gradient is split over
 // threads, blocks or ranks.  bins[255] counts non-finite inputs.
+//
+// Each warp keeps a private 256 x uint32 histogram in shared memory (native 32-bit shared atomics;
+// lanes that hit the same bin are serialised by the hardware, nothing spins) and spills it to the
+// 64-bit global bins before any bin could overflow: at most 64 iterations x 8 values x 32 lanes
+// squares of < 2^16 each lie between two spills.
+__device__ __forceinline__ void sumsq_add(uint32_t* hist, uint32_t h) {
+  const uint32_t e = (h >> 7) & 0xff;
+  uint32_t mant = h & 0x7f;
+  if (e == 0xff) { atomicAdd(&hist[255], 1u); return; }
+  if (e != 0) mant |= 0x80;
+  if (mant != 0) atomicAdd(&hist[e], mant * mant);
+}
+
 __global__ void __launch_bounds__(256)
 sumsq_bins_kernel(const __nv_bfloat16* __restrict__ g, long long n, unsigned long long* bins) {
-  __shared__ unsigned long long sb[256];
-  sb[threadIdx.x] = 0ull;
-  __syncthreads();
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const uint32_t h = *reinterpret_cast<const unsigned short*>(g + i);
-    const uint32_t e = (h >> 7) & 0xff;
-    uint32_t mant = h & 0x7f;
-    if (e == 0xff) { atomicAdd(&sb[255], 1ull); continue; }
-    if (e != 0) mant |= 0x80;
-    if (mant == 0) continue;
-    atomicAdd(&sb[e], static_cast<unsigned long long>(mant) * mant);
+  __shared__ uint32_t sh[8][256];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t* hist = sh[warp];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) hist[lane + 32 * k] = 0u;
+  __syncwarp();
+  auto spill = [&]() {
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const uint32_t v = hist[lane + 32 * k];
+      if (v) {
+        atomicAdd(&bins[lane + 32 * k], static_cast<unsigned long long>(v));
+        hist[lane + 32 * k] = 0u;
+      }
+    }
+    __syncwarp();
+  };
+  // elements before the first 16-byte boundary and after the last full vector: one thread
+  const uintptr_t addr = reinterpret_cast<uintptr_t>(g);
+  long long head = ((16 - (addr & 15)) & 15) / 2;
+  if (head > n) head = n;
+  const long long nvec = (n - head) / 8;
+  const long long tail0 = head + nvec * 8;
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    const unsigned short* u = reinterpret_cast<const unsigned short*>(g);
+    for (long long i = 0; i < head; ++i) sumsq_add(hist, u[i]);
+    for (long long i = tail0; i < n; ++i) sumsq_add(hist, u[i]);
   }
-  __syncthreads();
-  if (sb[threadIdx.x] != 0ull) atomicAdd(&bins[threadIdx.x], sb[threadIdx.x]);
+  const uint4* v4 = reinterpret_cast<const uint4*>(g + head);
+  int since = 0;
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  // the loop bounds are warp-uniform, so the whole warp reaches every spill together
+  for (long long base = static_cast<long long>(blockIdx.x) * blockDim.x + warp * 32; base < nvec; base += stride) {
+    const long long i = base + lane;
+    if (i < nvec) {
+      const uint4 x = v4[i];
+      const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        sumsq_add(hist, w[k] & 0xffffu);
+        sumsq_add(hist, w[k] >> 16);
+      }
+    }
+    if (++since == 64) {
+      since = 0;
+      spill();
+    }
+  }
+  spill();
 }
 
 }  // namespace rlk
@@ -105,7 +153,7 @@ RLK_API int rlk_adamw(float* master, float* m, float* v, const void* grad, void*
 // sum of squares = sum_e bins[e] * 2^(2 * (max(e,1) - 127 - 7)).
 RLK_API int rlk_sumsq_bins(const void* grad, long long n, unsigned long long* bins, void* stream) {
   RLK_REQUIRE(n > 0, "sumsq_bins: empty");
-  long long blocks = (n + 256 * 16 - 1) / (256 * 16);
+  long long blocks = (n + 256 * 64 - 1) / (256 * 64);
   if (blocks > 148 * 8) blocks = 148 * 8;
   sumsq_bins_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)grad, n, bins);

@@ -102,10 +102,13 @@ class SymmetricMemoryCollective:
         nbytes = t.numel() * t.element_size()
         if nbytes % 16:
             raise ValueError("all_reduce_: byte size must be a multiple of 16")
-        ext.check(self._lib.rlk_symm_all_reduce(self._state, ext.ptr(t), ext.ptr(t), c_longlong(nbytes),
-                                                c_int(_DT[t.dtype]), c_int(0), ext.stream_ptr(self.device)),
-                  "symm_all_reduce")
-        nv._count()
+        base = t.data_ptr()
+        for off in range(0, nbytes, self.frame_bytes):       # larger than a frame: frame-sized pieces
+            n = min(self.frame_bytes, nbytes - off)
+            ext.check(self._lib.rlk_symm_all_reduce(self._state, c_void_p(base + off), c_void_p(base + off),
+                                                    c_longlong(n), c_int(_DT[t.dtype]), c_int(0),
+                                                    ext.stream_ptr(self.device)), "symm_all_reduce")
+            nv._count()
         return t
 
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:

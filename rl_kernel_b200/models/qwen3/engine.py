@@ -289,10 +289,21 @@ class Qwen3Engine:
         self.cos, self.sin = rope_tables(spec, max_positions, self.dev)
         self.ws = Workspace(self.dev)
         self.fuse_gemm_allreduce = True
+        self.cp = None                               # CPAttention once enable_context_parallel ran
         self._tiles: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
         for K in (params.q_local, params.i_local):
             if self.nchunks > 1 and (K // self.nchunks) % 64:
                 raise ValueError(f"canonical K chunk {K // self.nchunks} must be a multiple of 64")
+
+    def enable_context_parallel(self, max_local_tokens: int, layout: str = "zigzag") -> None:
+        """Training over ``ctx.cp_size`` ranks that each hold 1/cp of every sequence: K/V (and Q, dO,
+        lse, delta for backward) live in peer-mapped buffers and the attention kernels fetch remote
+        blocks themselves (distributed/cp_attention.py)."""
+        from rl_kernel_b200.distributed.cp_attention import CPAttention
+
+        if self.ctx.cp_size > 1 and self.cp is None:
+            self.cp = CPAttention(self.ctx.cp_collective, self.dev, num_q_heads=self.hq, num_kv_heads=self.hkv,
+                                  max_local_tokens=max_local_tokens, layout=layout)
 
     # -------------------------------------------------------------------------- helpers
     def _gemm(self, a, b, out, *, a_mn=False, b_mn=False, nchunks=1, accumulate=False, M=None, N=None, K=None):
@@ -333,7 +344,8 @@ class Qwen3Engine:
 
     # -------------------------------------------------------------------------- layer forward
     def _layer_fwd(self, l: int, x, res, T: int, pos, *, tiles, kbuf, vbuf, kv_slot=None,
-                   q_view=None, lse=None, s_in_out=None, keep: dict | None = None, tag: str = "f"):
+                   q_view=None, lse=None, s_in_out=None, keep: dict | None = None, tag: str = "f",
+                   cp_geom: tuple[int, int] | None = None):
         """One decoder layer.  ``x`` + ``res`` -> (mlp_out, s_mid).  When ``res`` is None, ``x`` is
         already the residual stream.  ``keep`` receives the intermediates backward needs."""
         w, ws, H = self.p.w, self.ws, self.spec.hidden_size
@@ -347,13 +359,19 @@ class Qwen3Engine:
             nv.rmsnorm_fwd(x, w[f"l{l}.ln1"], h, eps, res=res, res_out=s_in)
         qkv = ws.get(f"{tag}.qkv", (T, self.p.qkv_local))
         self._gemm(h, w[f"l{l}.wqkv"], qkv)
-        q = ws.get(f"{tag}.q", (T, self.p.q_local))
+        if cp_geom is not None and keep is not None:
+            q = self.cp.bufs.local("q")[:T]          # the dK/dV kernels of the peers read it
+        else:
+            q = ws.get(f"{tag}.q", (T, self.p.q_local))
         nv.qk_norm_rope_fwd(qkv, w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos, q, kbuf, vbuf,
                             Hq=self.hq, Hkv=self.hkv, eps=eps, kv_slot=kv_slot)
         attn = ws.get(f"{tag}.attn", (T, self.p.q_local))
         qv = q if q_view is None else q.view(*q_view)
         ov = attn if q_view is None else attn.view(*q_view)
-        self._attention(qv, kbuf, vbuf, ov, lse, tiles, decode=q_view is not None)
+        if cp_geom is not None:
+            self.cp.forward_inplace(q, attn, lse, *cp_geom)
+        else:
+            self._attention(qv, kbuf, vbuf, ov, lse, tiles, decode=q_view is not None)
         o = ws.get(f"{tag}.o", (T, H))
         self._row_parallel(attn, w[f"l{l}.wo"], o, self.nchunks)
         s_mid = ws.get(f"{tag}.s_mid", (T, H))
@@ -375,15 +393,27 @@ class Qwen3Engine:
 
     # -------------------------------------------------------------------------- full forward
     def forward_hidden(self, tokens: torch.Tensor, *, save: TrainState | None = None,
-                       kv: KVCache | None = None, tag: str = "f") -> torch.Tensor:
+                       kv: KVCache | None = None, tag: str = "f", cp_seq_len: int | None = None) -> torch.Tensor:
         """tokens [nseq, S] -> final-norm hidden [nseq*S, H].  With ``kv`` the K/V of every layer are
-        written into the cache (prefill); with ``save`` layer inputs are checkpointed for backward."""
+        written into the cache (prefill); with ``save`` layer inputs are checkpointed for backward.
+        ``cp_seq_len``: context parallel -- ``tokens`` holds this rank's S = cp_seq_len / cp positions
+        of every sequence (``cp.local_positions`` order)."""
         nseq, S = tokens.shape
         T, H, L = nseq * S, self.spec.hidden_size, self.spec.num_hidden_layers
         ws = self.ws
         pos = ws.get("pos" if tag == "f" else f"{tag}.pos", (T,), torch.int32)
-        pos.copy_(torch.arange(S, device=self.dev, dtype=torch.int32).repeat(nseq))
-        tiles, _ = self._tiles_for(nseq, S)
+        cp_geom = None
+        if cp_seq_len is not None:
+            if self.cp is None or kv is not None:
+                raise RuntimeError("context parallel forward needs enable_context_parallel and no KV cache")
+            if T > self.cp.max_tokens:
+                raise ValueError(f"{T} local tokens exceed the context-parallel buffers ({self.cp.max_tokens})")
+            cp_geom = (nseq, cp_seq_len)
+            pos.copy_(self.cp.local_positions(cp_seq_len).to(device=self.dev, dtype=torch.int32).repeat(nseq))
+            tiles = None
+        else:
+            pos.copy_(torch.arange(S, device=self.dev, dtype=torch.int32).repeat(nseq))
+            tiles, _ = self._tiles_for(nseq, S)
         x = ws.get(f"{tag}.embed", (T, H))
         nv.embedding_fwd(tokens.reshape(-1), self.p.w["embed"], x, self.p.vocab_start)
         self.ctx.tp_all_reduce_(x)
@@ -399,14 +429,17 @@ class Qwen3Engine:
                 x, res = self._layer_fwd(l, x, res, T, pos, tiles=ptiles, kbuf=kv.k[l], vbuf=kv.v[l],
                                          kv_slot=slot, tag=tag)
             else:
-                kb = ws.get(f"{tag}.k", (T, self.p.kv_local))
-                vb = ws.get(f"{tag}.v", (T, self.p.kv_local))
+                if cp_geom is not None:
+                    kb, vb = self.cp.bufs.local("k")[:T], self.cp.bufs.local("v")[:T]
+                else:
+                    kb = ws.get(f"{tag}.k", (T, self.p.kv_local))
+                    vb = ws.get(f"{tag}.v", (T, self.p.kv_local))
                 s_out = save.ckpt[l] if save is not None else None
                 if save is not None and l == 0:
                     save.ckpt[0].copy_(x)
                     x = save.ckpt[0]
                 x, res = self._layer_fwd(l, x, res, T, pos, tiles=tiles, kbuf=kb, vbuf=vb,
-                                         s_in_out=s_out if l > 0 else None, tag=tag)
+                                         s_in_out=s_out if l > 0 else None, tag=tag, cp_geom=cp_geom)
         hf = ws.get(f"{tag}.hf", (T, H))
         s_fin = ws.get(f"{tag}.s_fin", (T, H))
         nv.rmsnorm_fwd(x, self.p.w["norm"], hf, self.spec.rms_norm_eps, res=res, res_out=s_fin)
@@ -470,24 +503,52 @@ class Qwen3Engine:
         T, H, L = nseq * S, self.spec.hidden_size, self.spec.num_hidden_layers
         return TrainState(nseq, S, self.ws.get("ckpt", (L, T, H)))
 
+    def response_index(self, S: int, resp_start: int) -> tuple[torch.Tensor, torch.Tensor]:
+        """(local row of every scored position this rank holds, its response index).  Position t
+        scores token t+1, so the scored positions are resp_start-1 .. S-2; without context
+        parallelism every rank holds all of them."""
+        if self.cp is None:
+            sel = torch.arange(resp_start - 1, S - 1, device=self.dev)
+            return sel, sel + 1 - resp_start
+        lpos = self.cp.local_positions(S).to(self.dev)
+        sel = torch.nonzero((lpos >= resp_start - 1) & (lpos <= S - 2)).reshape(-1)
+        return sel, lpos[sel] + 1 - resp_start
+
+    def local_tokens(self, tokens: torch.Tensor) -> torch.Tensor:
+        """The columns of ``tokens`` [nseq, S] this context-parallel rank holds (all without CP)."""
+        if self.cp is None:
+            return tokens
+        return tokens[:, self.cp.local_positions(tokens.shape[1]).to(self.dev)].contiguous()
+
     def train_forward_backward(self, tokens: torch.Tensor, resp_start: int, dlogp_fn, *,
                                temperature: float = 1.0, lm_chunk: int = 4096):
         """One micro-batch: forward with checkpoints, LM head + log-probs on response positions,
-        ``dlogp_fn(logp [nseq, R]) -> dlogp [nseq, R]`` supplies d(loss)/d(logp), then the full
-        backward accumulates into ``params.grad``.  Returns logp [nseq, R] (fp32).
+        ``dlogp_fn(logp [nseq, Rl]) -> dlogp [nseq, Rl]`` supplies d(loss)/d(logp), then the full
+        backward accumulates into ``params.grad``.  Returns logp [nseq, Rl] (fp32).
 
-        Position t predicts token t+1; response tokens are ``tokens[:, resp_start:]``, so rows
-        ``resp_start-1 .. S-2`` are scored.
+        Position t predicts token t+1; response tokens are ``tokens[:, resp_start:]``, so positions
+        ``resp_start-1 .. S-2`` are scored.  ``tokens`` is always the full [nseq, S] matrix; with
+        context parallelism this rank embeds and scores only its own positions and the Rl columns
+        of logp are the response indices ``response_index(S, resp_start)[1]``.
         """
         nseq, S = tokens.shape
-        R = S - resp_start
         H = self.spec.hidden_size
-        st = self.new_train_state(nseq, S)
-        hf = self.forward_hidden(tokens, save=st)
-        hf3 = hf.view(nseq, S, H)
+        cp = self.cp is not None
+        tok_local = self.local_tokens(tokens)
+        Sl = tok_local.shape[1]
+        sel, ridx = self.response_index(S, resp_start)
+        R = sel.numel()
+        st = self.new_train_state(nseq, Sl)
+        st.extra["S_global"] = S
+        hf = self.forward_hidden(tok_local, save=st, cp_seq_len=S if cp else None)
+        hf3 = hf.view(nseq, Sl, H)
         rows = self.ws.get("lm.rows", (nseq * R, H))
-        rows.view(nseq, R, H).copy_(hf3[:, resp_start - 1:S - 1])
-        targets = tokens[:, resp_start:].reshape(-1).contiguous()
+        if cp:
+            torch.index_select(hf3, 1, sel, out=rows.view(nseq, R, H))
+        else:
+            rows.view(nseq, R, H).copy_(hf3[:, resp_start - 1:S - 1])
+        targets = tokens[:, resp_start:][:, ridx].reshape(-1).contiguous() if cp else \
+            tokens[:, resp_start:].reshape(-1).contiguous()
         # ---- pass 1: log-probs (fused stats, logits not kept)
         logp, lse = self.logp_from_hidden(rows, targets, temperature=temperature, want_lse=True)
         dlogp = dlogp_fn(logp.view(nseq, R)).reshape(-1).contiguous()
@@ -510,10 +571,13 @@ class Qwen3Engine:
             else:
                 drows[r0:r1].zero_()
         self.ctx.tp_all_reduce_(drows)
-        dhf = self.ws.get("b.dhf", (nseq * S, H))
+        dhf = self.ws.get("b.dhf", (nseq * Sl, H))
         dhf.zero_()
-        dhf.view(nseq, S, H)[:, resp_start - 1:S - 1].copy_(drows.view(nseq, R, H))
-        self._backward(st, tokens, dhf)
+        if cp:
+            dhf.view(nseq, Sl, H).index_copy_(1, sel, drows.view(nseq, R, H))
+        else:
+            dhf.view(nseq, Sl, H)[:, resp_start - 1:S - 1].copy_(drows.view(nseq, R, H))
+        self._backward(st, tok_local, dhf)
         return logp.view(nseq, R)
 
     def _backward(self, st: TrainState, tokens: torch.Tensor, dhf: torch.Tensor) -> None:
@@ -522,21 +586,30 @@ class Qwen3Engine:
         T, H, L = nseq * S, spec.hidden_size, spec.num_hidden_layers
         eps = spec.rms_norm_eps
         pos = ws.get("pos", (T,), torch.int32)
-        tiles, kvtiles = self._tiles_for(nseq, S)
+        cp = self.cp is not None
+        cp_geom = (nseq, st.extra["S_global"]) if cp else None
+        tiles, kvtiles = (None, None) if cp else self._tiles_for(nseq, S)
         scr = ws.get("b.scr", (max(nv.rmsnorm_bwd_scratch_elems(T, H), nv.qk_norm_rope_bwd_scratch_elems(T)),),
                      torch.float32)
         ds = ws.get("b.ds", (T, H))          # gradient of the residual stream
         # final norm: s_fin -> hf
         nv.rmsnorm_bwd(st.final_s, w["norm"], dhf, ds, scr, eps, dw_bf16=g["norm"], accumulate_dw=True)
-        lse = ws.get("b.lse", (T, self.hq), torch.float32)
-        delta = ws.get("b.delta", (T, self.hq), torch.float32)
+        if cp:
+            # peers read these while computing their dK / dV
+            lse, delta = self.cp.bufs.local("lse"), self.cp.bufs.local("delta")
+        else:
+            lse = ws.get("b.lse", (T, self.hq), torch.float32)
+            delta = ws.get("b.delta", (T, self.hq), torch.float32)
         for l in range(L - 1, -1, -1):
             keep: dict = {}
-            kb = ws.get("f.k", (T, self.p.kv_local))
-            vb = ws.get("f.v", (T, self.p.kv_local))
+            if cp:
+                kb, vb = self.cp.bufs.local("k")[:T], self.cp.bufs.local("v")[:T]
+            else:
+                kb = ws.get("f.k", (T, self.p.kv_local))
+                vb = ws.get("f.v", (T, self.p.kv_local))
             # ---- recompute the layer from its checkpointed input
             self._layer_fwd(l, st.ckpt[l], None, T, pos, tiles=tiles, kbuf=kb, vbuf=vb, lse=lse,
-                            keep=keep, tag="r")
+                            keep=keep, tag="r", cp_geom=cp_geom)
             # ---- MLP backward.  s_out = s_mid + down  =>  d(down) = ds, d(s_mid) += ds
             dact = ws.get("b.dact", (T, self.p.i_local))
             self._gemm(ds, w[f"l{l}.wd"], dact, b_mn=True, M=T, N=self.p.i_local, K=H)
@@ -554,7 +627,7 @@ class Qwen3Engine:
             nv.rmsnorm_bwd(keep["s_mid"], w[f"l{l}.ln2"], dh2, ds2, scr, eps, dres=ds,
                            dw_bf16=g[f"l{l}.ln2"], accumulate_dw=True)
             # ---- attention block backward.  s_mid = s_in + o  =>  d(o) = ds2
-            dattn = ws.get("b.dattn", (T, self.p.q_local))
+            dattn = self.cp.bufs.local("do")[:T] if cp else ws.get("b.dattn", (T, self.p.q_local))
             self._gemm(ds2, w[f"l{l}.wo"], dattn, b_mn=True, M=T, N=self.p.q_local, K=H)
             self._gemm(ds2, keep["attn"], g[f"l{l}.wo"], a_mn=True, b_mn=True, accumulate=True,
                        M=H, N=self.p.q_local, K=T)
@@ -562,8 +635,11 @@ class Qwen3Engine:
             dq = ws.get("b.dq", (T, self.p.q_local))
             dk = ws.get("b.dk", (T, self.p.kv_local))
             dv = ws.get("b.dv", (T, self.p.kv_local))
-            nv.attn_bwd_dq(keep["q"], dattn, kb, vb, lse, delta, dq, tiles, self.scale)
-            nv.attn_bwd_dkv(keep["q"], dattn, kb, vb, lse, delta, dk, dv, kvtiles, self.scale)
+            if cp:
+                self.cp.backward_inplace(dq, dk, dv, *cp_geom)
+            else:
+                nv.attn_bwd_dq(keep["q"], dattn, kb, vb, lse, delta, dq, tiles, self.scale)
+                nv.attn_bwd_dkv(keep["q"], dattn, kb, vb, lse, delta, dk, dv, kvtiles, self.scale)
             dqkv = ws.get("b.dqkv", (T, self.p.qkv_local))
             nv.qk_norm_rope_bwd(keep["qkv"], w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos,
                                 dq, dk, dv, dqkv, scr, g[f"l{l}.qn"], g[f"l{l}.kn"], Hq=self.hq,

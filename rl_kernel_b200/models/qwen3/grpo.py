@@ -120,12 +120,22 @@ class GRPOTrainer:
         self.spec, self.cfg, self.dev = spec, cfg, device
         self.ctx = ctx or ParallelContext()
         tp_r, tp = self.ctx.tp_rank, self.ctx.tp_size
+        # Context parallelism applies to training only.  For rollout the cp TP groups act as cp
+        # independent engines, each generating for its share of the prompts.
+        self.cp = self.ctx.cp_size
+        if cfg.num_prompts % self.cp or cfg.micro_batch_seqs < 1:
+            raise ValueError(f"num_prompts {cfg.num_prompts} must be a multiple of the context-parallel size {self.cp}")
+        self.roll_prompts = cfg.num_prompts // self.cp
+        self.roll_seqs = self.roll_prompts * cfg.group_size
+        self.rollout_ctx = self.ctx if self.cp == 1 else ParallelContext(tp_r, tp, collective=self.ctx.collective)
         self.policy = PackedParams(spec, tp_r, tp, device, with_grad=True)
         if weights is not None:
             self.policy.load(weights)
         else:
             self.policy.init_synthetic_(cfg.seed)
         self.engine = Qwen3Engine(spec, self.policy, self.ctx, max_positions=cfg.seq_len + 8)
+        if self.cp > 1:
+            self.engine.enable_context_parallel(cfg.micro_batch_seqs * cfg.seq_len // self.cp)
         self.ref_params = None
         if cfg.use_reference_model and cfg.kl_coef > 0:
             self.ref_params = PackedParams(spec, tp_r, tp, device)
@@ -133,8 +143,8 @@ class GRPOTrainer:
         # rollout weights: a separate buffer that receives every published version, unless the
         # engines are colocated and configured to alias the trainer's shard
         self.rollout_params = self.policy if cfg.share_rollout_weights else PackedParams(spec, tp_r, tp, device)
-        self.rollout_engine = Qwen3Engine(spec, self.rollout_params, self.ctx, max_positions=cfg.seq_len + 8)
-        kv_bytes = self.rollout_engine.kv_cache_bytes(cfg.num_seqs, cfg.seq_len)
+        self.rollout_engine = Qwen3Engine(spec, self.rollout_params, self.rollout_ctx, max_positions=cfg.seq_len + 8)
+        kv_bytes = self.rollout_engine.kv_cache_bytes(self.roll_seqs, cfg.seq_len)
         self._arena = None
         if cfg.share_kv_and_activation_memory:
             self._arena = torch.zeros(kv_bytes, dtype=torch.uint8, device=device)
@@ -150,7 +160,8 @@ class GRPOTrainer:
 
     def local_prompts(self, prompts: torch.Tensor) -> torch.Tensor:
         """The slice of the global prompt batch this rank's rollout engine generates for."""
-        return prompts
+        n = self.roll_prompts
+        return prompts[self.ctx.cp_rank * n:(self.ctx.cp_rank + 1) * n]
 
     # ---------------------------------------------------------------- weight sync
     def publish_weights(self) -> int:
@@ -164,15 +175,18 @@ class GRPOTrainer:
     def _ensure_rollout_state(self):
         c = self.cfg
         if self._kv is None:
-            B = c.num_seqs
+            B = self.roll_seqs
             eng = self.rollout_engine
             self._kv = eng.new_kv_cache(B, c.seq_len, storage=self._arena)
-            self._pkv = eng.new_kv_cache(c.num_prompts, c.prompt_len)
+            self._pkv = eng.new_kv_cache(self.roll_prompts, c.prompt_len)
             self._dtiles = eng.decode_tiles(B, c.seq_len)
             self._tok = torch.zeros(B, dtype=torch.int64, device=self.dev)
             self._pos = torch.zeros(B, dtype=torch.int32, device=self.dev)
             self._keys = torch.zeros(B, dtype=torch.int64, device=self.dev)
-            self._seq_key = torch.arange(B, dtype=torch.int64, device=self.dev) * 65536
+            # sampling keys are global sequence numbers: the draw of a sequence does not depend on
+            # which rollout engine generated it
+            self._seq_key = (torch.arange(B, dtype=torch.int64, device=self.dev)
+                             + self.ctx.cp_rank * B) * 65536
             self._out_tok = torch.zeros(B, c.response_len, dtype=torch.int64, device=self.dev)
             self._out_lp = torch.zeros(B, c.response_len, dtype=torch.float32, device=self.dev)
             self._col = torch.zeros(1, dtype=torch.int64, device=self.dev)
@@ -193,20 +207,21 @@ class GRPOTrainer:
 
     @torch.no_grad()
     def rollout(self, prompts: torch.Tensor, step_seed: int):
-        """prompts [num_prompts, prompt_len] -> (tokens [B, S], logp [B, R]); B = prompts x group."""
+        """prompts [n, prompt_len] (this engine's share) -> (tokens [B, S], logp [B, R]); B = n x group."""
         c, eng = self.cfg, self.rollout_engine
         self._ensure_rollout_state()
-        B, P, R, G = c.num_seqs, c.prompt_len, c.response_len, c.group_size
+        B, P, R, G = self.roll_seqs, c.prompt_len, c.response_len, c.group_size
+        NP = self.roll_prompts
         if self._arena is not None:
             self._kv.flat.zero_()        # training activations lived here since the last rollout
         # ---- prefill each distinct prompt once, then share its KV with the whole group
         hf = eng.forward_hidden(prompts, kv=self._pkv, tag="p")
         H = self.spec.hidden_size
-        last = hf.view(c.num_prompts, P, H)[:, P - 1].repeat_interleave(G, dim=0).contiguous()
+        last = hf.view(NP, P, H)[:, P - 1].repeat_interleave(G, dim=0).contiguous()
         for l in range(self.spec.num_hidden_layers):
             for src, dst in ((self._pkv.k[l], self._kv.k[l]), (self._pkv.v[l], self._kv.v[l])):
-                d3 = dst.view(c.num_prompts, G, c.seq_len, -1)
-                d3[:, :, :P].copy_(src.view(c.num_prompts, 1, P, -1).expand(-1, G, -1, -1))
+                d3 = dst.view(NP, G, c.seq_len, -1)
+                d3[:, :, :P].copy_(src.view(NP, 1, P, -1).expand(-1, G, -1, -1))
         # ---- first response token comes from the prefill logits
         self._pos.fill_(P - 1)
         self._col.zero_()
@@ -231,7 +246,7 @@ class GRPOTrainer:
                 self._tok.copy_(snap[0]); self._pos.copy_(snap[1]); self._col.copy_(snap[2])
                 self._graph = torch.cuda.CUDAGraph()
                 n0 = nv.LAUNCH_COUNT
-                coll = self.ctx.collective
+                coll = self.rollout_ctx.collective
                 with torch.cuda.graph(self._graph):
                     if coll is not None:
                         with coll.graph_capture():
@@ -244,8 +259,8 @@ class GRPOTrainer:
                 self._tok.copy_(snap[0]); self._pos.copy_(snap[1]); self._col.copy_(snap[2])
             for _ in range(R - 1):
                 self._graph.replay()
-            if self.ctx.collective is not None:
-                self.ctx.collective.graph_replayed(R - 1)
+            if self.rollout_ctx.collective is not None:
+                self.rollout_ctx.collective.graph_replayed(R - 1)
             nv.LAUNCH_COUNT += (R - 1) * self.graph_launches
         else:
             for _ in range(R - 1):
@@ -256,24 +271,40 @@ class GRPOTrainer:
     # ---------------------------------------------------------------- scoring with frozen weights
     @torch.no_grad()
     def score(self, params: PackedParams, tokens: torch.Tensor) -> torch.Tensor:
-        """Selected-token log-probs of the response tokens under ``params`` (no gradients)."""
+        """Selected-token log-probs of the response tokens under ``params`` (no gradients):
+        [n, Rl], the columns being this rank's response indices (all of them without CP)."""
         c = self.cfg
         eng = self.engine
         saved = eng.p
         eng.p = params
+        S = c.seq_len
+        sel, ridx = eng.response_index(S, c.prompt_len)
         try:
             out = []
             for b0 in range(0, tokens.shape[0], c.micro_batch_seqs):
                 tk = tokens[b0:b0 + c.micro_batch_seqs]
-                n, S = tk.shape
-                hf = eng.forward_hidden(tk).view(n, S, -1)
-                rows = hf[:, c.prompt_len - 1:S - 1].reshape(n * c.response_len, -1).contiguous()
-                lp = eng.logp_from_hidden(rows, tk[:, c.prompt_len:].reshape(-1).contiguous(),
+                n = tk.shape[0]
+                tl = eng.local_tokens(tk)
+                hf = eng.forward_hidden(tl, cp_seq_len=S if self.cp > 1 else None).view(n, tl.shape[1], -1)
+                rows = hf[:, sel].reshape(n * sel.numel(), -1).contiguous()
+                lp = eng.logp_from_hidden(rows, tk[:, c.prompt_len:][:, ridx].reshape(-1).contiguous(),
                                           temperature=c.temperature)
-                out.append(lp.view(n, c.response_len).clone())
+                out.append(lp.view(n, sel.numel()).clone())
             return torch.cat(out)
         finally:
             eng.p = saved
+
+    def _gather_rollouts(self, tokens: torch.Tensor, logp: torch.Tensor):
+        """Every rollout engine's sequences, in global sequence order, on every rank."""
+        if self.cp == 1:
+            return tokens, logp
+        import torch.distributed as dist
+
+        tk = torch.empty((self.cp,) + tuple(tokens.shape), dtype=tokens.dtype, device=self.dev)
+        lp = torch.empty((self.cp,) + tuple(logp.shape), dtype=logp.dtype, device=self.dev)
+        dist.all_gather_into_tensor(tk, tokens.contiguous(), group=self.ctx.cp_group)
+        dist.all_gather_into_tensor(lp, logp.contiguous(), group=self.ctx.cp_group)
+        return tk.flatten(0, 1), lp.flatten(0, 1)
 
     # ---------------------------------------------------------------- one full step
     def step(self, prompts: torch.Tensor, rewards_fn=None, step_index: int = 0) -> dict:
@@ -283,6 +314,7 @@ class GRPOTrainer:
         ev[0].record()
         self.publish_weights()
         tokens, old_logp = self.rollout(prompts, step_seed=c.seed + 7919 * step_index)
+        tokens, old_logp = self._gather_rollouts(tokens, old_logp)
         ev[1].record()
         if rewards_fn is None:
             gen = torch.Generator(device=self.dev).manual_seed(c.seed + step_index)
@@ -290,18 +322,21 @@ class GRPOTrainer:
         else:
             rewards = rewards_fn(tokens).float()
         adv = nv.group_advantages(rewards.contiguous(), c.num_prompts, c.group_size, 1e-6)
-        mask = torch.ones(B, R, dtype=torch.uint8, device=self.dev)
+        _, ridx = self.engine.response_index(c.seq_len, c.prompt_len)   # response columns of this rank
+        Rl = ridx.numel()
+        mask = torch.ones(B, Rl, dtype=torch.uint8, device=self.dev)
+        old_local = old_logp if self.cp == 1 else old_logp[:, ridx].contiguous()
         ref_logp = self.score(self.ref_params, tokens) if self.ref_params is not None else None
         ev[2].record()
         total_active = float(B * R)
         self.policy.grad.zero_()
-        train_logp = torch.empty(B, R, dtype=torch.float32, device=self.dev)
+        train_logp = torch.empty(B, Rl, dtype=torch.float32, device=self.dev)
         loss_terms = []
         for b0 in range(0, B, c.micro_batch_seqs):
             b1 = min(B, b0 + c.micro_batch_seqs)
 
             def dlogp_fn(lp, b0=b0, b1=b1):
-                r = nv.grpo_loss(lp.contiguous(), old_logp[b0:b1].contiguous(),
+                r = nv.grpo_loss(lp.contiguous(), old_local[b0:b1].contiguous(),
                                  ref_logp[b0:b1].contiguous() if ref_logp is not None else None,
                                  adv[b0:b1].contiguous(), mask[b0:b1].contiguous(), clip_lo=c.clip_eps,
                                  clip_hi=c.clip_eps, beta=c.kl_coef, inv_norm=1.0 / total_active,
@@ -312,11 +347,24 @@ class GRPOTrainer:
             lp = self.engine.train_forward_backward(tokens[b0:b1], c.prompt_len, dlogp_fn,
                                                     temperature=c.temperature)
             train_logp[b0:b1].copy_(lp)
+        tot = torch.stack(loss_terms).sum(0)
+        if self.cp > 1:
+            # weights are replicated over CP: sum the gradients of the token shards (fixed tree)
+            self.ctx.cp_collective.all_reduce_(self.policy.grad)
+            pad = torch.zeros(B, R, dtype=torch.float32, device=self.dev)
+            pad[:, :Rl] = train_logp
+            idx = torch.full((R,), -1, dtype=torch.int64, device=self.dev)
+            idx[:Rl] = ridx
+            gp, gi = self.ctx.cp_collective.all_gather(pad), self.ctx.cp_collective.all_gather(idx)
+            train_logp = torch.empty(B, R, dtype=torch.float32, device=self.dev)
+            for r in range(self.cp):                      # every response column has exactly one owner
+                m = gi[r] >= 0
+                train_logp[:, gi[r][m]] = gp[r][:, m]
+            tot = self.ctx.cp_collective.all_gather(tot.contiguous()).sum(0)
         ev[3].record()
         self.opt.step()
         ev[4].record()
         self.phase_events = ev     # rollout, reference scoring, train fwd/bwd, optimizer
-        tot = torch.stack(loss_terms).sum(0)
         return {"tokens": tokens, "old_logp": old_logp, "train_logp": train_logp, "rewards": rewards,
                 "loss_sums": tot, "grad_norm": self.opt.last_grad_norm, "total_active": total_active}
 

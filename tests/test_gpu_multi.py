@@ -171,6 +171,51 @@ def test_tp2_matches_tp1_bitwise(tmp_path):
     assert torch.equal(tp2["train_logp"], tp2["old_logp"])
 
 
+def _cp_train_worker(rank, world, port, out):
+    dist = _init(rank, world, port)
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
+    from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context
+
+    dev = torch.device("cuda", rank)
+    spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+    w = Qwen3DenseWeights.synthetic(spec, seed=3)
+    ctx = build_parallel_context(1, world, dev)
+    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=384, micro_batch_seqs=4, lr=1e-4)
+    tr = GRPOTrainer(spec, cfg, dev, ctx=ctx, weights=w)
+    prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5)).to(dev)
+    res = tr.step(tr.local_prompts(prompts), step_index=0)
+    torch.cuda.synchronize(dev)
+    if rank == 0:
+        torch.save({k: res[k].cpu() for k in ("tokens", "old_logp", "train_logp", "grad_norm")}, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_cp2_training_matches_single_gpu(tmp_path):
+    """Rollout on two independent engines + training with every sequence split over two GPUs gives
+    the tokens and log-probs of one GPU bit for bit; the gradient norm agrees to rounding (weight
+    gradients sum over tokens in a different order)."""
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
+
+    out = str(tmp_path / "cp2.pt")
+    mp.spawn(_cp_train_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    cp2 = torch.load(out)
+    dev = torch.device("cuda:0")
+    spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+    w = Qwen3DenseWeights.synthetic(spec, seed=3)
+    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=384, micro_batch_seqs=4, lr=1e-4)
+    tr = GRPOTrainer(spec, cfg, dev, weights=w)
+    prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5)).to(dev)
+    one = tr.step(prompts, step_index=0)
+    assert torch.equal(cp2["tokens"], one["tokens"].cpu())
+    assert torch.equal(cp2["old_logp"], one["old_logp"].cpu())
+    assert torch.equal(cp2["train_logp"], one["train_logp"].cpu())
+    assert torch.equal(cp2["train_logp"], cp2["old_logp"])
+    assert abs(float(cp2["grad_norm"]) - float(one["grad_norm"])) <= 2e-2 * float(one["grad_norm"])
+
+
 def _cp_worker(rank, world, port, out):
     dist = _init(rank, world, port)
     import math
@@ -190,8 +235,17 @@ def _cp_worker(rank, world, port, out):
     # single-GPU result
     o1 = torch.empty(B * S, HQ * D, device=dev, dtype=torch.bfloat16)
     l1 = torch.empty(B * S, HQ, device=dev)
-    tiles, _ = train_tiles(B, S, HQ, HKV, D, dev)
-    nv.attn_fwd(q.view(B * S, -1), [k.view(B * S, -1)], [v.view(B * S, -1)], o1, l1, tiles, 1 / math.sqrt(D))
+    tiles, kvtiles = train_tiles(B, S, HQ, HKV, D, dev)
+    sc = 1 / math.sqrt(D)
+    q2, k2, v2 = q.view(B * S, -1), k.view(B * S, -1), v.view(B * S, -1)
+    nv.attn_fwd(q2, [k2], [v2], o1, l1, tiles, sc)
+    do = torch.randn(B, S, HQ * D, device=dev, generator=g).to(torch.bfloat16)
+    do2 = do.view(B * S, -1)
+    dl1 = torch.empty(B * S, HQ, device=dev)
+    nv.attn_bwd_delta(o1, do2, dl1, B * S, HQ)
+    dq1, dk1, dv1 = torch.empty_like(q2), torch.empty_like(k2), torch.empty_like(v2)
+    nv.attn_bwd_dq(q2, do2, k2, v2, l1, dl1, dq1, tiles, sc)
+    nv.attn_bwd_dkv(q2, do2, k2, v2, l1, dl1, dk1, dv1, kvtiles, sc)
     ok = True
     for layout in ("contiguous", "zigzag"):
         pos = cp_positions(S, world, rank, layout).to(dev)
@@ -200,6 +254,10 @@ def _cp_worker(rank, world, port, out):
         o, l = cp.forward(sel(q), sel(k), sel(v), B, S)
         ok &= torch.equal(o, sel(o1.view(B, S, -1)))
         ok &= torch.equal(l, sel(l1.view(B, S, -1)))
+        dq, dk, dv = cp.backward(sel(q), sel(k), sel(v), o, l, sel(do), B, S)
+        ok &= torch.equal(dq, sel(dq1.view(B, S, -1)))
+        ok &= torch.equal(dk, sel(dk1.view(B, S, -1)))
+        ok &= torch.equal(dv, sel(dv1.view(B, S, -1)))
     torch.cuda.synchronize(dev)
     from rl_kernel_b200.backends import extension as ext
     ok &= ext.poll_status(dev) == 0
@@ -209,7 +267,7 @@ def _cp_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_cp_attention_equals_single_gpu_bitwise(tmp_path):
+def test_cp_attention_fwd_bwd_equals_single_gpu_bitwise(tmp_path):
     out = str(tmp_path / "cp.pt")
     mp.spawn(_cp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
     assert torch.load(out)

@@ -273,4 +273,5 @@ def test_adamw_and_exact_sumsq():
 
     whole = ss([g])
     assert whole == ss([g[:1000], g[1000:50000], g[50000:]]), "sum of squares must not depend on the partition"
+    assert whole == ss([g[:1001], g[1001:50003], g[50003:]]), "nor on the alignment of the pieces"
     assert abs(whole - g.double().pow(2).sum().item()) < 1e-6 * whole
