@@ -227,17 +227,19 @@ def qk_norm_rope_bwd(qkv, q_w, k_w, cos_tab, sin_tab, pos, dq, dk, dv, dqkv, scr
 
 
 # ------------------------------------------------------------------------------------- activation
-def swiglu_fwd(gu, out, I: int, blk: int | None = None) -> None:
-    rc = _lib().rlk_swiglu_fwd(ext.ptr(gu), _ll(gu.stride(0)), ext.ptr(out), _ll(out.stride(0)),
-                               c_int(gu.shape[0]), c_int(I), c_int(blk or I), ext.stream_ptr(gu.device))
+def swiglu_fwd(gu, out, I: int, blk: int | None = None, rows_limit=None) -> None:
+    """``rows_limit``: int32 device scalar; rows at or beyond it are skipped."""
+    rc = _lib().rlk_swiglu_fwd_dyn(ext.ptr(gu), _ll(gu.stride(0)), ext.ptr(out), _ll(out.stride(0)),
+                                   c_int(gu.shape[0]), c_int(I), c_int(blk or I), ext.ptr(rows_limit),
+                                   ext.stream_ptr(gu.device))
     ext.check(rc, "swiglu_fwd")
     _count()
 
 
-def swiglu_bwd(gu, dout, dgu, I: int, blk: int | None = None) -> None:
-    rc = _lib().rlk_swiglu_bwd(ext.ptr(gu), _ll(gu.stride(0)), ext.ptr(dout), _ll(dout.stride(0)),
-                               ext.ptr(dgu), _ll(dgu.stride(0)), c_int(gu.shape[0]), c_int(I),
-                               c_int(blk or I), ext.stream_ptr(gu.device))
+def swiglu_bwd(gu, dout, dgu, I: int, blk: int | None = None, rows_limit=None) -> None:
+    rc = _lib().rlk_swiglu_bwd_dyn(ext.ptr(gu), _ll(gu.stride(0)), ext.ptr(dout), _ll(dout.stride(0)),
+                                   ext.ptr(dgu), _ll(dgu.stride(0)), c_int(gu.shape[0]), c_int(I),
+                                   c_int(blk or I), ext.ptr(rows_limit), ext.stream_ptr(gu.device))
     ext.check(rc, "swiglu_bwd")
     _count()
 
@@ -361,4 +363,105 @@ def sumsq_bins(grad, bins) -> None:
     assert bins.dtype == torch.int64 and bins.numel() == 256
     rc = _lib().rlk_sumsq_bins(ext.ptr(grad), _ll(grad.numel()), ext.ptr(bins), ext.stream_ptr(grad.device))
     ext.check(rc, "sumsq_bins")
+    _count()
+
+
+# ------------------------------------------------------------------------------------- MoE
+def _ptr_array(tensors):
+    ts = _as_list(tensors)
+    return (c_void_p * len(ts))(*[t.data_ptr() for t in ts]), len(ts)
+
+
+def grouped_gemm(a, b, c, tiles, n_tiles, *, a_mn: bool = False, b_mn: bool = False,
+                 accumulate: bool = False) -> None:
+    """Tile-list driven expert GEMM (csrc/moe/grouped_gemm_sm100.cu).  ``tiles`` int32 [max, 8] and
+    ``n_tiles`` int32 [1] live on the device and come from ``moe_tiles``."""
+    _bf16(a, "a"); _bf16(b, "b"); _bf16(c, "c")
+    _rowmajor2d(a, "a"); _rowmajor2d(b, "b"); _rowmajor2d(c, "c")
+    rc = _lib().rlk_grouped_gemm(ext.ptr(a), _ll(a.shape[0]), _ll(a.shape[1]), _ll(a.stride(0)),
+                                 ext.ptr(b), _ll(b.shape[0]), _ll(b.shape[1]), _ll(b.stride(0)),
+                                 ext.ptr(c), _ll(c.stride(0)), ext.ptr(tiles), ext.ptr(n_tiles),
+                                 c_int(tiles.shape[0]), c_int(int(a_mn)), c_int(int(b_mn)),
+                                 c_int(int(accumulate)), ext.stream_ptr(a.device))
+    ext.check(rc, "grouped_gemm")
+    _count()
+
+
+def moe_router_topk(logits, idx, w, probs=None, counts=None) -> None:
+    """logits fp32 [T, E] -> idx int32 [T, K] (ascending expert ids), w fp32 [T, K]."""
+    T, E = logits.shape
+    assert logits.dtype == torch.float32 and logits.is_contiguous() and idx.dtype == torch.int32
+    rc = _lib().rlk_moe_router_topk(ext.ptr(logits), c_int(T), c_int(E), c_int(idx.shape[1]), ext.ptr(idx),
+                                    ext.ptr(w), ext.ptr(probs), ext.ptr(counts), ext.stream_ptr(logits.device))
+    ext.check(rc, "moe_router_topk")
+    _count()
+
+
+def moe_router_bwd(idx, w, dw, dlogits) -> None:
+    T, K = idx.shape
+    rc = _lib().rlk_moe_router_bwd(ext.ptr(idx), ext.ptr(w), ext.ptr(dw), c_int(T), c_int(K),
+                                   c_int(dlogits.shape[1]), ext.ptr(dlogits), ext.stream_ptr(idx.device))
+    ext.check(rc, "moe_router_bwd")
+    _count()
+
+
+def moe_plan(counts_all, rank: int, send_row0, loc, rows_used) -> None:
+    W, E = counts_all.shape
+    rc = _lib().rlk_moe_plan(ext.ptr(counts_all), c_int(W), c_int(rank), c_int(E), ext.ptr(send_row0),
+                             ext.ptr(loc), ext.ptr(rows_used), ext.stream_ptr(counts_all.device))
+    ext.check(rc, "moe_plan")
+    _count()
+
+
+def moe_tiles(loc, kind: int, n_cols: int, k_dim: int, b_mn: bool, m_out: int, tiles, n_tiles) -> None:
+    rc = _lib().rlk_moe_tiles(ext.ptr(loc), c_int(loc.shape[0]), c_int(kind), c_int(n_cols), c_int(k_dim),
+                              c_int(int(b_mn)), c_int(m_out), ext.ptr(tiles), ext.ptr(n_tiles),
+                              c_int(tiles.shape[0]), ext.stream_ptr(loc.device))
+    ext.check(rc, "moe_tiles")
+    _count()
+
+
+def moe_slots(idx, E: int, send_row0, slot_row) -> None:
+    rc = _lib().rlk_moe_slots(ext.ptr(idx), c_int(idx.numel()), c_int(E), ext.ptr(send_row0),
+                              ext.ptr(slot_row), ext.stream_ptr(idx.device))
+    ext.check(rc, "moe_slots")
+    _count()
+
+
+def moe_dispatch(x, scale, idx, slot_row, E_loc: int, dst_bufs) -> None:
+    """Row t of ``x`` goes to row slot_row[t, k] of ``dst_bufs[owner of idx[t, k]]`` for every k."""
+    pa, n = _ptr_array(dst_bufs)
+    d0 = _as_list(dst_bufs)[0]
+    rc = _lib().rlk_moe_dispatch(ext.ptr(x), _ll(x.stride(0)), ext.ptr(scale), ext.ptr(idx), ext.ptr(slot_row),
+                                 c_int(idx.numel()), c_int(idx.shape[1]), c_int(E_loc), c_int(x.shape[1]), pa,
+                                 c_int(n), _ll(d0.stride(0)), ext.stream_ptr(x.device))
+    ext.check(rc, "moe_dispatch")
+    _count()
+
+
+def moe_combine(base, w, idx, slot_row, E_loc: int, src_bufs, out) -> None:
+    pa, n = _ptr_array(src_bufs)
+    s0 = _as_list(src_bufs)[0]
+    rc = _lib().rlk_moe_combine(ext.ptr(base), _ll(base.stride(0) if base is not None else 0), ext.ptr(w),
+                                ext.ptr(idx), ext.ptr(slot_row), c_int(idx.shape[0]), c_int(idx.shape[1]),
+                                c_int(E_loc), c_int(out.shape[1]), pa, c_int(n), _ll(s0.stride(0)), ext.ptr(out),
+                                _ll(out.stride(0)), ext.stream_ptr(out.device))
+    ext.check(rc, "moe_combine")
+    _count()
+
+
+def moe_combine_dw(dout, idx, slot_row, E_loc: int, src_bufs, dw) -> None:
+    pa, n = _ptr_array(src_bufs)
+    s0 = _as_list(src_bufs)[0]
+    rc = _lib().rlk_moe_combine_dw(ext.ptr(dout), _ll(dout.stride(0)), ext.ptr(idx), ext.ptr(slot_row),
+                                   c_int(idx.numel()), c_int(idx.shape[1]), c_int(E_loc), c_int(dout.shape[1]),
+                                   pa, c_int(n), _ll(s0.stride(0)), ext.ptr(dw), ext.stream_ptr(dout.device))
+    ext.check(rc, "moe_combine_dw")
+    _count()
+
+
+def moe_zero_pad(loc, buf) -> None:
+    rc = _lib().rlk_moe_zero_pad(ext.ptr(loc), c_int(loc.shape[0]), ext.ptr(buf), _ll(buf.stride(0)),
+                                 c_int(buf.shape[1]), ext.stream_ptr(buf.device))
+    ext.check(rc, "moe_zero_pad")
     _count()

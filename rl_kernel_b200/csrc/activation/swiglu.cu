@@ -14,11 +14,12 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g))
 
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_gu, __nv_bfloat16* __restrict__ out,
-                  long long ld_out, int rows, int I, int blk) {
+                  long long ld_out, int rows, int I, int blk, const int* __restrict__ rows_limit) {
   const int per_row = I / 8;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(rows) * per_row) return;
   const int r = static_cast<int>(idx / per_row), c = static_cast<int>(idx % per_row) * 8;
+  if (rows_limit && r >= *rows_limit) return;  // row count known only on the device (MoE)
   const long long gc = static_cast<long long>(c / blk) * 2 * blk + (c % blk);  // column of gate[c]
   const uint4 g = *reinterpret_cast<const uint4*>(gu + r * ld_gu + gc);
   const uint4 u = *reinterpret_cast<const uint4*>(gu + r * ld_gu + gc + blk);
@@ -33,11 +34,13 @@ swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_gu, __nv_bf
 // d(gate) = dout * up * silu'(gate), d(up) = dout * silu(gate); written packed like the input.
 __global__ void __launch_bounds__(256)
 swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_gu, const __nv_bfloat16* __restrict__ dout,
-                  long long ld_dout, __nv_bfloat16* __restrict__ dgu, long long ld_dgu, int rows, int I, int blk) {
+                  long long ld_dout, __nv_bfloat16* __restrict__ dgu, long long ld_dgu, int rows, int I, int blk,
+                  const int* __restrict__ rows_limit) {
   const int per_row = I / 8;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(rows) * per_row) return;
   const int r = static_cast<int>(idx / per_row), c = static_cast<int>(idx % per_row) * 8;
+  if (rows_limit && r >= *rows_limit) return;
   const long long gc = static_cast<long long>(c / blk) * 2 * blk + (c % blk);  // column of gate[c]
   const uint4 g = *reinterpret_cast<const uint4*>(gu + r * ld_gu + gc);
   const uint4 u = *reinterpret_cast<const uint4*>(gu + r * ld_gu + gc + blk);
@@ -67,26 +70,38 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_gu, const _
 }  // namespace rlk
 using namespace rlk;
 
-RLK_API int rlk_swiglu_fwd(const void* gu, long long ld_gu, void* out, long long ld_out, int rows,
-                           int I, int blk, void* stream) {
+// rows_limit (device int, may be null): rows at or beyond *rows_limit are skipped.
+RLK_API int rlk_swiglu_fwd_dyn(const void* gu, long long ld_gu, void* out, long long ld_out, int rows,
+                               int I, int blk, const int* rows_limit, void* stream) {
   RLK_REQUIRE(rows > 0 && I > 0 && I % 8 == 0 && ld_gu % 8 == 0 && ld_out % 8 == 0,
               "swiglu: I and pitches must be multiples of 8");
   RLK_REQUIRE(blk > 0 && blk % 8 == 0 && I % blk == 0, "swiglu: blk must divide I and be a multiple of 8");
   const long long n = static_cast<long long>(rows) * (I / 8);
   swiglu_fwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)out, ld_out, rows, I, blk);
+      (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)out, ld_out, rows, I, blk, rows_limit);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+RLK_API int rlk_swiglu_fwd(const void* gu, long long ld_gu, void* out, long long ld_out, int rows,
+                           int I, int blk, void* stream) {
+  return rlk_swiglu_fwd_dyn(gu, ld_gu, out, ld_out, rows, I, blk, nullptr, stream);
+}
+
+RLK_API int rlk_swiglu_bwd_dyn(const void* gu, long long ld_gu, const void* dout, long long ld_dout,
+                               void* dgu, long long ld_dgu, int rows, int I, int blk, const int* rows_limit,
+                               void* stream) {
+  RLK_REQUIRE(rows > 0 && I > 0 && I % 8 == 0 && ld_gu % 8 == 0 && ld_dout % 8 == 0 && ld_dgu % 8 == 0,
+              "swiglu_bwd: I and pitches must be multiples of 8");
+  RLK_REQUIRE(blk > 0 && blk % 8 == 0 && I % blk == 0, "swiglu_bwd: blk must divide I and be a multiple of 8");
+  const long long n = static_cast<long long>(rows) * (I / 8);
+  swiglu_bwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)gu, ld_gu, (const __nv_bfloat16*)dout, ld_dout, (__nv_bfloat16*)dgu, ld_dgu, rows, I, blk, rows_limit);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
 
 RLK_API int rlk_swiglu_bwd(const void* gu, long long ld_gu, const void* dout, long long ld_dout,
                            void* dgu, long long ld_dgu, int rows, int I, int blk, void* stream) {
-  RLK_REQUIRE(rows > 0 && I > 0 && I % 8 == 0 && ld_gu % 8 == 0 && ld_dout % 8 == 0 && ld_dgu % 8 == 0,
-              "swiglu_bwd: I and pitches must be multiples of 8");
-  RLK_REQUIRE(blk > 0 && blk % 8 == 0 && I % blk == 0, "swiglu_bwd: blk must divide I and be a multiple of 8");
-  const long long n = static_cast<long long>(rows) * (I / 8);
-  swiglu_bwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)gu, ld_gu, (const __nv_bfloat16*)dout, ld_dout, (__nv_bfloat16*)dgu, ld_dgu, rows, I, blk);
-  RLK_CHECK_CUDA(cudaGetLastError());
-  return RLK_OK;
+  return rlk_swiglu_bwd_dyn(gu, ld_gu, dout, ld_dout, dgu, ld_dgu, rows, I, blk, nullptr, stream);
 }
