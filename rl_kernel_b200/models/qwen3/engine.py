@@ -83,9 +83,10 @@ class PackedParams:
         for l in range(spec.num_hidden_layers):
             slots += [_Slot(f"l{l}.ln1", (h,)), _Slot(f"l{l}.wqkv", (self.qkv_local, h)),
                       _Slot(f"l{l}.qn", (d,)), _Slot(f"l{l}.kn", (d,)),
-                      _Slot(f"l{l}.wo", (h, self.q_local)), _Slot(f"l{l}.ln2", (h,)),
-                      _Slot(f"l{l}.wgu", (2 * self.i_local, h)), _Slot(f"l{l}.wd", (h, self.i_local))]
+                      _Slot(f"l{l}.wo", (h, self.q_local)), _Slot(f"l{l}.ln2", (h,))]
+            slots += self._mlp_slots(l)
         slots += [_Slot("norm", (h,)), _Slot("lm_head", (self.v_local, h))]
+        slots += self._trailing_slots()
         off = 0
         for s in slots:
             s.offset = off
@@ -97,6 +98,15 @@ class PackedParams:
         self.w = {s.name: self.flat[s.offset:s.offset + s.numel].view(s.shape) for s in slots}
         self.g = ({s.name: self.grad[s.offset:s.offset + s.numel].view(s.shape) for s in slots}
                   if with_grad else {})
+
+    def _mlp_slots(self, l: int) -> list[_Slot]:
+        h = self.spec.hidden_size
+        return [_Slot(f"l{l}.wgu", (2 * self.i_local, h)), _Slot(f"l{l}.wd", (h, self.i_local))]
+
+    def _trailing_slots(self) -> list[_Slot]:
+        """Slots placed after everything else (subclasses: parameters that are not replicated over
+        the data-parallel group, so that the replicated ones form one contiguous prefix)."""
+        return []
 
     # replicated (not TP-sharded) parameters: their gradients are identical on every TP rank
     def is_replicated(self, name: str) -> bool:
@@ -377,6 +387,14 @@ class Qwen3Engine:
         s_mid = ws.get(f"{tag}.s_mid", (T, H))
         h2 = ws.get(f"{tag}.h2", (T, H))
         nv.rmsnorm_fwd(o, w[f"l{l}.ln2"], h2, eps, res=s_in, res_out=s_mid)
+        if keep is not None:
+            keep.update(s_in=s_in, h=h, qkv=qkv, q=q, attn=attn, s_mid=s_mid, h2=h2)
+        down = self._mlp_fwd(l, h2, T, tag, keep)
+        return down, s_mid
+
+    def _mlp_fwd(self, l: int, h2: torch.Tensor, T: int, tag: str, keep: dict | None) -> torch.Tensor:
+        """Feed-forward block on the normalised stream ``h2`` [T, H] -> [T, H] (before the residual)."""
+        w, ws, H = self.p.w, self.ws, self.spec.hidden_size
         gu = ws.get(f"{tag}.gu", (T, 2 * self.p.i_local))
         self._gemm(h2, w[f"l{l}.wgu"], gu)
         act = ws.get(f"{tag}.act", (T, self.p.i_local))
@@ -384,8 +402,26 @@ class Qwen3Engine:
         down = ws.get(f"{tag}.down", (T, H))
         self._row_parallel(act, w[f"l{l}.wd"], down, self.nchunks)
         if keep is not None:
-            keep.update(s_in=s_in, h=h, qkv=qkv, q=q, attn=attn, s_mid=s_mid, h2=h2, gu=gu, act=act)
-        return down, s_mid
+            keep.update(gu=gu, act=act)
+        return down
+
+    def _mlp_bwd(self, l: int, ds: torch.Tensor, keep: dict, T: int) -> torch.Tensor:
+        """Backward of ``_mlp_fwd``: ``ds`` = d(loss)/d(output) -> d(loss)/d(h2), summed over TP;
+        weight gradients are accumulated."""
+        w, g, ws, H = self.p.w, self.p.g, self.ws, self.spec.hidden_size
+        dact = ws.get("b.dact", (T, self.p.i_local))
+        self._gemm(ds, w[f"l{l}.wd"], dact, b_mn=True, M=T, N=self.p.i_local, K=H)
+        self._gemm(ds, keep["act"], g[f"l{l}.wd"], a_mn=True, b_mn=True, accumulate=True,
+                   M=H, N=self.p.i_local, K=T)
+        dgu = ws.get("b.dgu", (T, 2 * self.p.i_local))
+        nv.swiglu_bwd(keep["gu"], dact, dgu, self.p.i_local, self.blk)
+        dh2 = ws.get("b.dh", (T, H))
+        self._gemm(dgu, w[f"l{l}.wgu"], dh2, b_mn=True, nchunks=self.nchunks, M=T, N=H,
+                   K=2 * self.p.i_local)
+        self.ctx.tp_all_reduce_(dh2)
+        self._gemm(dgu, keep["h2"], g[f"l{l}.wgu"], a_mn=True, b_mn=True, accumulate=True,
+                   M=2 * self.p.i_local, N=H, K=T)
+        return dh2
 
     def _attention(self, q2d, k2d, v2d, o2d, lse, tiles, decode: bool = False):
         nv.attn_fwd(q2d, [k2d], [v2d], o2d, lse, tiles, self.scale,
@@ -611,18 +647,7 @@ class Qwen3Engine:
             self._layer_fwd(l, st.ckpt[l], None, T, pos, tiles=tiles, kbuf=kb, vbuf=vb, lse=lse,
                             keep=keep, tag="r", cp_geom=cp_geom)
             # ---- MLP backward.  s_out = s_mid + down  =>  d(down) = ds, d(s_mid) += ds
-            dact = ws.get("b.dact", (T, self.p.i_local))
-            self._gemm(ds, w[f"l{l}.wd"], dact, b_mn=True, M=T, N=self.p.i_local, K=H)
-            self._gemm(ds, keep["act"], g[f"l{l}.wd"], a_mn=True, b_mn=True, accumulate=True,
-                       M=H, N=self.p.i_local, K=T)
-            dgu = ws.get("b.dgu", (T, 2 * self.p.i_local))
-            nv.swiglu_bwd(keep["gu"], dact, dgu, self.p.i_local, self.blk)
-            dh2 = ws.get("b.dh", (T, H))
-            self._gemm(dgu, w[f"l{l}.wgu"], dh2, b_mn=True, nchunks=self.nchunks, M=T, N=H,
-                       K=2 * self.p.i_local)
-            self.ctx.tp_all_reduce_(dh2)
-            self._gemm(dgu, keep["h2"], g[f"l{l}.wgu"], a_mn=True, b_mn=True, accumulate=True,
-                       M=2 * self.p.i_local, N=H, K=T)
+            dh2 = self._mlp_bwd(l, ds, keep, T)
             ds2 = ws.get("b.ds2", (T, H))
             nv.rmsnorm_bwd(keep["s_mid"], w[f"l{l}.ln2"], dh2, ds2, scr, eps, dres=ds,
                            dw_bf16=g[f"l{l}.ln2"], accumulate_dw=True)

@@ -101,18 +101,27 @@ class MoEExperts:
     def __init__(self, bufs: MoEBuffers):
         self.b = bufs
 
+    def _view(self, T: int) -> None:
+        """The first T rows of the per-token state (the buffers are sized for the largest call)."""
+        b = self.b
+        self.idx, self.w, self.logits = b.idx[:T], b.w[:T], b.logits[:T]
+        self.slot_row = b.slot_row[: T * b.K]
+        if hasattr(b, "dw"):
+            self.dw, self.dlogits = b.dw[:T], b.dlogits[:T]
+
     # ------------------------------------------------------------------ routing
     def route(self, x: torch.Tensor, wts: MoEWeights) -> None:
         b = self.b
         T = x.shape[0]
-        if T != b.T:
+        if T > b.T:
             raise ValueError(f"the buffers were sized for {b.T} tokens per rank, got {T}")
-        nv.det_gemm(x, wts.router, b.logits, M=T, N=b.E, K=b.H)
+        self._view(T)
+        nv.det_gemm(x, wts.router, self.logits, M=T, N=b.E, K=b.H)
         b.counts.zero_()
-        nv.moe_router_topk(b.logits, b.idx, b.w, None, b.counts)
+        nv.moe_router_topk(self.logits, self.idx, self.w, None, b.counts)
         counts_all = b.coll.all_gather(b.counts) if b.coll else b.counts.unsqueeze(0)
         nv.moe_plan(counts_all.contiguous(), b.rank, b.send_row0, b.loc, b.rows_used)
-        nv.moe_slots(b.idx, b.E, b.send_row0, b.slot_row)
+        nv.moe_slots(self.idx, b.E, b.send_row0, self.slot_row)
         for name, (kind, n_cols, k_dim, b_mn, m_out) in b._tile_cfg.items():
             nv.moe_tiles(b.loc, kind, n_cols, k_dim, b_mn, m_out, b.tiles[name], b.n_tiles[name])
 
@@ -124,14 +133,14 @@ class MoEExperts:
         b = self.b
         if not routed:
             self.route(x, wts)
-        nv.moe_dispatch(x, None, b.idx, b.slot_row, b.E_loc, b.peer["xr"])
+        nv.moe_dispatch(x, None, self.idx, self.slot_row, b.E_loc, b.peer["xr"])
         b.barrier()                                   # every rank's rows have landed
         nv.moe_zero_pad(b.loc, b.local("xr"))
         nv.grouped_gemm(b.local("xr"), wts.w1, b.gu, b.tiles["gu"], b.n_tiles["gu"])
         nv.swiglu_fwd(b.gu, b.act, b.I, b.I, rows_limit=b.rows_used)
         nv.grouped_gemm(b.act, wts.w2, b.local("y"), b.tiles["dn"], b.n_tiles["dn"])
         b.barrier()                                   # every rank's expert outputs are complete
-        nv.moe_combine(base, b.w, b.idx, b.slot_row, b.E_loc, b.peer["y"], out)
+        nv.moe_combine(base, self.w, self.idx, self.slot_row, b.E_loc, b.peer["y"], out)
         return out
 
     # ------------------------------------------------------------------ backward
@@ -143,8 +152,8 @@ class MoEExperts:
         b = self.b
         T = x.shape[0]
         # routing-weight gradient and the scaled copies of dOut for the experts
-        nv.moe_combine_dw(dout, b.idx, b.slot_row, b.E_loc, b.peer["y"], b.dw)
-        nv.moe_dispatch(dout, b.w, b.idx, b.slot_row, b.E_loc, b.peer["dy"])
+        nv.moe_combine_dw(dout, self.idx, self.slot_row, b.E_loc, b.peer["y"], self.dw)
+        nv.moe_dispatch(dout, self.w, self.idx, self.slot_row, b.E_loc, b.peer["dy"])
         b.barrier()
         dy = b.local("dy")
         nv.moe_zero_pad(b.loc, dy)
@@ -156,12 +165,12 @@ class MoEExperts:
         nv.grouped_gemm(b.dgu, b.local("xr"), wts.g_w1, b.tiles["dw1"], b.n_tiles["dw1"], a_mn=True, b_mn=True,
                         accumulate=True)
         # router: dlogits -> dx (through the router weights) and the router weight gradient
-        nv.moe_router_bwd(b.idx, b.w, b.dw, b.dlogits)
+        nv.moe_router_bwd(self.idx, self.w, self.dw, self.dlogits)
         dxr_router = dx                                # reuse the output as the fma chain's start
-        nv.det_gemm(b.dlogits, wts.router, dxr_router, M=T, N=b.H, K=b.E, b_mn=True)
-        nv.det_gemm(b.dlogits, x, wts.g_router, M=b.E, N=b.H, K=T, a_mn=True, b_mn=True, accumulate=True)
+        nv.det_gemm(self.dlogits, wts.router, dxr_router, M=T, N=b.H, K=b.E, b_mn=True)
+        nv.det_gemm(self.dlogits, x, wts.g_router, M=b.E, N=b.H, K=T, a_mn=True, b_mn=True, accumulate=True)
         if dx_base is not None:
             dx.add_(dx_base)
         b.barrier()                                   # every rank's dXr is complete
-        nv.moe_combine(dx, None, b.idx, b.slot_row, b.E_loc, b.peer["dxr"], dx)
+        nv.moe_combine(dx, None, self.idx, self.slot_row, b.E_loc, b.peer["dxr"], dx)
         return dx

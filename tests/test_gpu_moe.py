@@ -58,9 +58,9 @@ def test_moe_forward_matches_cpu_contract_and_is_batch_invariant():
     sync_and_check()
     ref, ridx, rw = moe_ffn_reference(x.cpu(), wts.router.cpu(), wts.w1.cpu().view(E, 2 * I, H),
                                       wts.w2.cpu().view(E, H, I), K, base.cpu())
-    assert torch.equal(moe.b.idx.cpu().long(), ridx)
+    assert torch.equal(moe.idx.cpu().long(), ridx)
     rows, _, total, padded = moe_dispatch_plan_reference([ridx], E)
-    assert torch.equal(moe.b.slot_row.cpu().long().view(T, K), rows[0])
+    assert torch.equal(moe.slot_row.cpu().long().view(T, K), rows[0])
     assert int(moe.b.rows_used.item()) == int(padded.sum())
     err = (out.float().cpu() - ref.float()).abs().max().item()
     assert err < 0.03, err
@@ -86,7 +86,7 @@ def test_moe_backward_matches_fp64_autograd():
     moe.backward(x, dout, wts, dx)
     sync_and_check()
     # fp64 reference with the routing decisions of the kernel
-    idx = moe.b.idx.long()
+    idx = moe.idx.long()
     xd = x.double().requires_grad_(True)
     wr = wts.router.double().requires_grad_(True)
     w1 = wts.w1.double().view(E, 2 * I, H).requires_grad_(True)
@@ -112,3 +112,36 @@ def test_moe_backward_matches_fp64_autograd():
     close(wts.g_w1.view(E, 2 * I, H), w1.grad, "dW1")
     close(wts.g_w2.view(E, H, I), w2.grad, "dW2")
     close(wts.g_router, wr.grad, "dWrouter")
+
+
+def test_moe_engine_rollout_and_training_logp_agree_bitwise():
+    """Decode (one token per sequence against the KV cache) and training (full sequences) route
+    every token to the same experts and produce the same selected-token log-prob bits."""
+    from rl_kernel_b200.models.qwen3_moe import MoEPackedParams, Qwen3MoeEngine, Qwen3MoeSpec
+
+    spec = Qwen3MoeSpec.tiny()
+    B, P, R = 4, 128, 24
+    S = P + R
+    params = MoEPackedParams(spec, 0, 1, dev(), with_grad=True).init_synthetic_(3, std=0.05)
+    eng = Qwen3MoeEngine(spec, params, max_tokens=B * S, max_positions=S + 8)
+    prompts = torch.randint(0, spec.vocab_size, (B, P), device=dev())
+    kv = eng.new_kv_cache(B, S)
+    hf = eng.forward_hidden(prompts, kv=kv, tag="p")
+    last = hf.view(B, P, -1)[:, P - 1].contiguous()
+    keys = torch.arange(B, device=dev(), dtype=torch.int64) * 65536
+    dtiles = eng.decode_tiles(B, S)
+    toks, lps = [], []
+    ids, lp = eng.sample(eng.logits(last), keys + P - 1, temperature=1.0, seed=11)
+    for i in range(R):
+        toks.append(ids.clone()); lps.append(lp.clone())
+        if i == R - 1:
+            break
+        pos = torch.full((B,), P + i, dtype=torch.int32, device=dev())
+        hf = eng.decode_step(ids.clone(), pos, kv, dtiles)
+        ids, lp = eng.sample(eng.logits(hf), keys + P + i, temperature=1.0, seed=11)
+    tokens = torch.cat([prompts, torch.stack(toks, 1)], 1).contiguous()
+    old = torch.stack(lps, 1)
+    new = eng.train_forward_backward(tokens, P, lambda x: torch.full_like(x, -1.0 / x.numel()))
+    sync_and_check()
+    assert torch.equal(new, old), (new - old).abs().max().item()
+    assert params.g["l0.w1"].float().abs().sum().item() > 0 and params.g["l1.router"].float().abs().sum().item() > 0
