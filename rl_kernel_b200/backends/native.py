@@ -94,6 +94,24 @@ def lmhead_logp_stats(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor | 
     _count()
 
 
+def lmhead_logp_stats_vp(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, stats_bufs, tgt_bufs, rank: int,
+                         *, vocab_start: int, inv_temp: float) -> None:
+    """Vocab-parallel fused LM head: this shard's per-tile statistics (and the target logit, if this
+    shard owns the target) are stored into every rank's buffers from the GEMM epilogue.
+    ``stats_bufs[r]`` [M, ntile, 2] fp32 and ``tgt_bufs[r]`` [M] fp32 are rank r's buffers mapped here."""
+    _bf16(h, "h"); _bf16(w, "w"); _rowmajor2d(h, "h"); _rowmajor2d(w, "w")
+    M, K = h.shape
+    world = len(stats_bufs)
+    sp = (c_void_p * world)(*[t.data_ptr() for t in stats_bufs])
+    tp = (c_void_p * world)(*[t.data_ptr() for t in tgt_bufs])
+    rc = _lib().rlk_lmhead_logp_stats_vp(ext.ptr(h), ext.ptr(w), c_int(M), c_int(w.shape[0]), c_int(K),
+                                         _ll(h.stride(0)), _ll(w.stride(0)), ext.ptr(targets), _ll(vocab_start),
+                                         c_float(inv_temp), sp, _ll(stats_bufs[0].shape[1]), tp, c_int(world),
+                                         c_int(rank), ext.stream_ptr(h.device))
+    ext.check(rc, "lmhead_logp_stats_vp")
+    _count()
+
+
 # ------------------------------------------------------------------------------------- attention
 def attn_fwd(q2d: torch.Tensor, k_list: list[torch.Tensor], v_list: list[torch.Tensor],
              o2d: torch.Tensor, lse: torch.Tensor | None, tiles: torch.Tensor, scale: float, *,

@@ -54,6 +54,12 @@ struct GemmParams {
   long long vocab_start;    // global id of column 0
   float* tgt_logit;         // [M]
   float inv_temp;
+  // vocab-parallel exchange fused into the same epilogue (stats_world > 1): every statistic and
+  // the owner's target logit are also stored into the other tensor-parallel ranks' buffers
+  // (peer stores over NVLink), so after one barrier every rank holds all tiles of every row.
+  int stats_world, stats_rank;
+  float2* stats_peer[8];
+  float* tgt_peer[8];
   // fused all-reduce epilogue (ar_world > 1): C points into this rank's symmetric frame; after a
   // tile's partial is stored there the epilogue warps shake hands with the same tile on every
   // peer, pull the peers' partials over NVLink, finish the balanced tree and write ar_out.
@@ -274,7 +280,11 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               float zt = 0.f;
 #pragma unroll
               for (int j = 0; j < 32; ++j) if (tgt_col - col0 == j) zt = z[j];
-              if (n0 + tgt_col < p.N) p.tgt_logit[row] = zt;
+              if (n0 + tgt_col < p.N) {
+                p.tgt_logit[row] = zt;
+                for (int pr = 0; pr < p.stats_world; ++pr)
+                  if (pr != p.stats_rank) p.tgt_peer[pr][row] = zt;
+              }
             }
             if (p.C != nullptr && row < p.M) {
               __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + n0 + col0;
@@ -291,7 +301,13 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               }
             }
           }
-          if (row < p.M) p.stats[row * p.stats_stride + p.stats_tile0 + nt] = make_float2(m, ts.total());
+          if (row < p.M) {
+            const float2 st2 = make_float2(m, ts.total());
+            const long long si = row * p.stats_stride + p.stats_tile0 + nt;
+            p.stats[si] = st2;
+            for (int pr = 0; pr < p.stats_world; ++pr)
+              if (pr != p.stats_rank) p.stats_peer[pr][si] = st2;
+          }
         } else if (BN == 256 && p.nchunks > 1) {
           // chunk tree with 128x256 tiles: both accumulators fill TMEM, so the tree stack lives in a
           // per-CTA global buffer (L2 resident; a row's entries are only ever touched by its own
@@ -845,11 +861,11 @@ RLK_API int rlk_det_gemm_split_static(const void* A, const void* B, void* C, int
 // [M,N] logits, unless `logits_out` is given.  W holds global vocab ids [vocab_start,
 // vocab_start+N); stats rows are float2[stats_stride] indexed by GLOBAL tile id.
 // Follow with rlk_logp_merge (after gathering the tiles of the other shards, if any).
-RLK_API int rlk_lmhead_logp_stats(const void* H, const void* W, int M, int N, int K, long long ldh,
-                                  long long ldw, const long long* targets, long long vocab_start,
-                                  float inv_temp, void* stats, long long stats_stride,
-                                  float* tgt_logit, void* logits_out, long long ld_logits,
-                                  void* stream) {
+static int lmhead_stats_impl(const void* H, const void* W, int M, int N, int K, long long ldh,
+                             long long ldw, const long long* targets, long long vocab_start,
+                             float inv_temp, void* stats, long long stats_stride, float* tgt_logit,
+                             void* logits_out, long long ld_logits, void* const* stats_ptrs,
+                             void* const* tgt_ptrs, int world, int rank, void* stream) {
   using namespace rlk;
   RLK_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0, "lmhead_logp_stats: bad shape");
   RLK_REQUIRE(vocab_start % kVocabTile == 0, "lmhead_logp_stats: vocab_start must be a multiple of 128");
@@ -866,5 +882,35 @@ RLK_API int rlk_lmhead_logp_stats(const void* H, const void* W, int M, int N, in
   p.vocab_start = vocab_start;
   p.tgt_logit = tgt_logit;
   p.inv_temp = inv_temp;
+  p.stats_world = world > 1 ? world : 0;
+  p.stats_rank = rank;
+  for (int i = 0; i < 8; ++i) {
+    p.stats_peer[i] = world > 1 ? static_cast<float2*>(stats_ptrs[i < world ? i : 0]) : nullptr;
+    p.tgt_peer[i] = world > 1 ? static_cast<float*>(tgt_ptrs[i < world ? i : 0]) : nullptr;
+  }
   return launch_gemm<128, false, false>(H, W, p, ldh, ldw, static_cast<cudaStream_t>(stream));
+}
+
+RLK_API int rlk_lmhead_logp_stats(const void* H, const void* W, int M, int N, int K, long long ldh,
+                                  long long ldw, const long long* targets, long long vocab_start,
+                                  float inv_temp, void* stats, long long stats_stride,
+                                  float* tgt_logit, void* logits_out, long long ld_logits,
+                                  void* stream) {
+  return lmhead_stats_impl(H, W, M, N, K, ldh, ldw, targets, vocab_start, inv_temp, stats, stats_stride,
+                           tgt_logit, logits_out, ld_logits, nullptr, nullptr, 1, 0, stream);
+}
+
+// Vocab-parallel form: stats_ptrs[r] / tgt_ptrs[r] are rank r's stats and target-logit buffers as
+// mapped in this process (this rank's own at index `rank`), all with the same geometry.  The
+// epilogue stores every statistic of this shard into all `world` buffers; after a barrier of the
+// group each rank can run rlk_logp_merge on complete rows.  Tiles no shard owns (vocab padding)
+// must hold (-inf, 0) beforehand.
+RLK_API int rlk_lmhead_logp_stats_vp(const void* H, const void* W, int M, int N, int K, long long ldh,
+                                     long long ldw, const long long* targets, long long vocab_start,
+                                     float inv_temp, void* const* stats_ptrs, long long stats_stride,
+                                     void* const* tgt_ptrs, int world, int rank, void* stream) {
+  RLK_REQUIRE(world >= 2 && world <= 8 && rank >= 0 && rank < world, "lmhead_logp_stats_vp: world must be 2..8");
+  return lmhead_stats_impl(H, W, M, N, K, ldh, ldw, targets, vocab_start, inv_temp, stats_ptrs[rank],
+                           stats_stride, static_cast<float*>(tgt_ptrs[rank]), nullptr, 0, stats_ptrs, tgt_ptrs,
+                           world, rank, stream);
 }

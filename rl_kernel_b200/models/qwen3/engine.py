@@ -512,6 +512,8 @@ class Qwen3Engine:
         n = hrows.shape[0]
         ntile = self.spec.num_vocab_tiles
         tp = self.ctx.tp_size
+        if tp > 1 and logits_out is None and hasattr(self.ctx.collective, "frame_tensor"):
+            return self._lmhead_stats_fused_exchange(hrows, targets, temperature)
         stats = self.ws.get("lm.stats", (n, ntile, 2), torch.float32)
         tl = self.ws.get("lm.tl", (n,), torch.float32)
         if tp > 1:
@@ -533,6 +535,44 @@ class Qwen3Engine:
             stats = g.permute(1, 0, 2, 3).reshape(n, ntile, 2).contiguous()
             tl = self.ctx.tp_all_gather(tl).sum(0)
         return stats, tl
+
+    LM_EXCHANGE_ROWS = 8192
+
+    def _lmhead_stats_fused_exchange(self, hrows, targets, temperature):
+        """Vocab-parallel LM head with the statistics exchange inside the GEMM: every rank's epilogue
+        stores its tiles' (max, sum-exp) and, for the rows whose target it owns, the target logit
+        straight into all ranks' buffers over NVLink; one barrier later every rank merges complete
+        rows locally.  Two buffer sets alternate so that a rank may start the next chunk while a
+        peer still merges the previous one."""
+        n = hrows.shape[0]
+        ntile = self.spec.num_vocab_tiles
+        if n > self.LM_EXCHANGE_ROWS:
+            raise ValueError(f"at most {self.LM_EXCHANGE_ROWS} rows per LM-head call")
+        if getattr(self, "_lm_peer", None) is None:
+            from rl_kernel_b200.distributed.cp_attention import PeerMappedBuffers
+
+            R = self.LM_EXCHANGE_ROWS
+            specs = {}
+            for q in (0, 1):
+                specs[f"stats{q}"] = ((R, ntile, 2), torch.float32)
+                specs[f"tl{q}"] = ((R,), torch.float32)
+            self._lm_peer = PeerMappedBuffers(self.ctx.collective.group, self.dev, specs)
+            for q in (0, 1):                             # tiles nobody owns (vocab padding) stay (-inf, 0)
+                st = self._lm_peer.local(f"stats{q}")
+                st[..., 0] = float("-inf")
+                st[..., 1] = 0
+            self._lm_parity = 0
+            torch.cuda.synchronize(self.dev)
+            self.ctx.collective.barrier()
+        q = self._lm_parity
+        self._lm_parity ^= 1
+        pm = self._lm_peer
+        w = self.p.w["lm_head"][: self.p.v_real_local]
+        if self.p.v_real_local > 0:
+            nv.lmhead_logp_stats_vp(hrows, w, targets, pm[f"stats{q}"], pm[f"tl{q}"], self.ctx.tp_rank,
+                                    vocab_start=self.p.vocab_start, inv_temp=1.0 / temperature)
+        self.ctx.collective.barrier()
+        return pm.local(f"stats{q}")[:n], pm.local(f"tl{q}")[:n]
 
     # -------------------------------------------------------------------------- training step pieces
     def new_train_state(self, nseq: int, S: int) -> TrainState:

@@ -328,3 +328,55 @@ def test_weight_push_reshards_over_nvlink(tmp_path):
     out = str(tmp_path / "push.pt")
     mp.spawn(_push_worker, args=(2, _free_port(), out), nprocs=2, join=True)
     assert torch.load(out)
+
+
+def _moe_case(dev, ep_rank, ep_size, coll):
+    from rl_kernel_b200.models.qwen3_moe import MoEPackedParams, Qwen3MoeEngine, Qwen3MoeSpec
+
+    spec = Qwen3MoeSpec.tiny()
+    B, S, P = 4, 256, 64
+    tokens = torch.randint(0, spec.vocab_size, (B, S), generator=torch.Generator().manual_seed(9)).to(dev)
+    per = B // ep_size
+    mine = tokens[ep_rank * per:(ep_rank + 1) * per].contiguous()
+    params = MoEPackedParams(spec, ep_rank, ep_size, dev, with_grad=True).init_synthetic_(3, std=0.05)
+    eng = Qwen3MoeEngine(spec, params, ep_collective=coll, max_tokens=per * S, max_positions=S + 8)
+    logp = eng.train_forward_backward(mine, P, lambda x: torch.full_like(x, -1.0 / (B * (S - P))))
+    eng.sync_replicated_grads()
+    torch.cuda.synchronize(dev)
+    return spec, params, logp
+
+
+def _moe_ep_worker(rank, world, port, out):
+    dist = _init(rank, world, port)
+    from rl_kernel_b200.backends import extension as ext
+    from rl_kernel_b200.distributed.transports.symm import SymmetricMemoryCollective
+
+    dev = torch.device("cuda", rank)
+    coll = SymmetricMemoryCollective(None, dev, frame_bytes=64 << 20)
+    spec, params, logp = _moe_case(dev, rank, world, coll)
+    res = {"logp": logp.cpu(), "w1": params.g["l0.w1"].cpu(), "w2": params.g["l1.w2"].cpu(),
+           "router": params.g["l0.router"].cpu(), "wqkv": params.g["l1.wqkv"].cpu(), "status": ext.poll_status(dev)}
+    gathered = [None] * world
+    dist.all_gather_object(gathered, res)
+    if rank == 0:
+        torch.save(gathered, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_moe_expert_parallel_matches_single_gpu(tmp_path):
+    """Two expert-parallel ranks (tokens and experts both split, dispatch / combine over NVLink)
+    reproduce one GPU: log-probs and expert weight gradients bit for bit, replicated-parameter
+    gradients to rounding (they are summed over the ranks instead of over one long token axis)."""
+    out = str(tmp_path / "moe.pt")
+    mp.spawn(_moe_ep_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    ep = torch.load(out)
+    spec, params, logp = _moe_case(torch.device("cuda:0"), 0, 1, None)
+    assert all(r["status"] == 0 for r in ep)
+    assert torch.equal(torch.cat([r["logp"] for r in ep]), logp.cpu())
+    assert torch.equal(torch.cat([r["w1"] for r in ep]), params.g["l0.w1"].cpu())
+    assert torch.equal(torch.cat([r["w2"] for r in ep]), params.g["l1.w2"].cpu())
+    for name, key in (("router", "l0.router"), ("wqkv", "l1.wqkv")):
+        a, b = ep[0][name].float(), params.g[key].float().cpu()
+        assert torch.equal(ep[0][name], ep[1][name]), "replicated gradients must agree across ranks"
+        assert (a - b).abs().max().item() <= 0.05 * b.abs().max().item() + 1e-6, name
