@@ -380,3 +380,43 @@ def test_moe_expert_parallel_matches_single_gpu(tmp_path):
         a, b = ep[0][name].float(), params.g[key].float().cpu()
         assert torch.equal(ep[0][name], ep[1][name]), "replicated gradients must agree across ranks"
         assert (a - b).abs().max().item() <= 0.05 * b.abs().max().item() + 1e-6, name
+
+
+def _ag_gemm_worker(rank, world, port, out):
+    dist = _init(rank, world, port)
+    from rl_kernel_b200.backends import extension as ext
+    from rl_kernel_b200.backends import native as nv
+    from rl_kernel_b200.distributed.ag_gemm import AllGatherGemm
+    from rl_kernel_b200.distributed.transports.symm import SymmetricMemoryCollective
+
+    dev = torch.device("cuda", rank)
+    coll = SymmetricMemoryCollective(None, dev, frame_bytes=1 << 20)
+    M, K, N = 1024, 1024, 640
+    g = torch.Generator(device="cuda").manual_seed(7)             # same full matrices on every rank
+    a = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+    w = torch.randn(N, K, device=dev, generator=g).to(torch.bfloat16)
+    ag = AllGatherGemm(coll, dev, M, K)
+    rows = M // world
+    ok = True
+    for rep in range(3):                                          # buffers and counters are reusable
+        a2 = (a.float() * (rep + 1)).to(torch.bfloat16)
+        ag.local_shard.copy_(a2[rank * rows:(rank + 1) * rows])
+        c = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        ag(w, c)
+        ref = torch.empty_like(c)
+        nv.det_gemm(a2, w, ref, M=M, N=N, K=K)
+        torch.cuda.synchronize(dev)
+        ok &= torch.equal(c, ref) and torch.equal(ag.gathered, a2)
+    ok &= ext.poll_status(dev) == 0
+    res = [None] * world
+    dist.all_gather_object(res, bool(ok))
+    if rank == 0:
+        torch.save(all(res), out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_all_gather_gemm_equals_gemm_of_gathered_matrix(tmp_path):
+    out = str(tmp_path / "ag.pt")
+    mp.spawn(_ag_gemm_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    assert torch.load(out)
