@@ -115,8 +115,10 @@ def lmhead_logp_stats_vp(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor
 # ------------------------------------------------------------------------------------- attention
 def attn_fwd(q2d: torch.Tensor, k_list: list[torch.Tensor], v_list: list[torch.Tensor],
              o2d: torch.Tensor, lse: torch.Tensor | None, tiles: torch.Tensor, scale: float, *,
-             cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False, decode: bool = False) -> None:
-    """q2d/o2d: [rows, Hq*128]; k/v: [rows, Hkv*128] (one tensor per source rank)."""
+             cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False, decode: bool = False,
+             page_table: torch.Tensor | None = None) -> None:
+    """q2d/o2d: [rows, Hq*128]; k/v: [rows, Hkv*128] (one tensor per source rank).  ``page_table``
+    int32: tiles whose last column is > 0 read KV block b from page ``table[col - 1 + b]``."""
     _bf16(q2d, "q"); _rowmajor2d(q2d, "q"); _rowmajor2d(o2d, "o")
     n_src = len(k_list)
     k0 = k_list[0]
@@ -129,7 +131,7 @@ def attn_fwd(q2d: torch.Tensor, k_list: list[torch.Tensor], v_list: list[torch.T
                              _ll(k0.stride(0)), ext.ptr(o2d), _ll(o2d.stride(0)), ext.ptr(lse),
                              ext.ptr(tiles), c_int(tiles.shape[0]), c_float(scale),
                              c_int(cp_blocks_per_chunk), c_int(int(cp_zigzag)), c_int(int(decode)),
-                             ext.stream_ptr(q2d.device))
+                             ext.ptr(page_table), ext.stream_ptr(q2d.device))
     ext.check(rc, "attn_fwd")
     _count()
 

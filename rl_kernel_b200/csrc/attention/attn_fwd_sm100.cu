@@ -42,6 +42,7 @@ struct AttnFwdParams {
   int cp_ranks;             // NSRC > 1: number of ranks holding the sequence
   int cp_zigzag;            // NSRC > 1: 1 = rank c holds chunks c and 2*cp-1-c; 0 = chunk c on rank c
   int q_rows_box;           // 128 (training / prefill) or 8 (decode: at most 8 query rows per tile)
+  const int* page_table;    // paged KV cache: see cp_locate; null = contiguous KV
   int* status;
 };
 
@@ -64,8 +65,18 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 // Which tensor map and which local row holds canonical block b of a sequence.
+// Paged KV (tile.reserved = 1 + index of the sequence's first entry in page_table): canonical block
+// b of the sequence lives in page (entry & 0xffffff) -- 128 rows starting at row 128 * page -- of
+// the K/V buffer of rank (entry >> 24), so a sequence's pages may sit anywhere and, with several
+// source maps, on other GPUs (prefill / decode context parallelism over a distributed page pool).
 __device__ __forceinline__ void cp_locate(const AttnFwdParams& p, const AttnTile& t, int b,
                                           int& src, int& row) {
+  if (p.page_table != nullptr && t.reserved > 0) {
+    const int e = p.page_table[t.reserved - 1 + b];
+    src = e >> 24;
+    row = (e & 0xffffff) * kAttnBlock;
+    return;
+  }
   if (p.cp_ranks <= 1) {
     src = t.kv_src;
     row = t.kv_row0 + b * kAttnBlock;
@@ -339,13 +350,16 @@ static int launch_attn_fwd(const CUtensorMap& tmQ, const KvMaps<NSRC>& kv, const
 // `tiles` is a device array of n_tiles rlk::AttnTile.  O has Q's geometry with pitch ldo.
 // decode_rows != 0 promises that every tile has n_rows <= 8 (single-token decode with GQA packing)
 // and selects the small-Q layout; the per-row arithmetic is unchanged.
+// page_table (device int32, may be null): tiles with reserved > 0 read their KV blocks through it
+// (see cp_locate); entries must name source ranks < n_src.
 // n_src == 1: k_ptrs/v_ptrs hold one pointer each.  n_src in 2..8 (context parallel): pointer s
 // is rank s's K / V buffer (same shape and pitch on every rank), mapped into this process.
 RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long long ldq,
                          const void* const* k_ptrs, const void* const* v_ptrs, int n_src,
                          long long kv_rows, long long kv_cols, long long ldkv, void* O,
                          long long ldo, float* lse, const void* tiles, int n_tiles, float scale,
-                         int cp_blocks_per_chunk, int cp_zigzag, int decode_rows, void* stream) {
+                         int cp_blocks_per_chunk, int cp_zigzag, int decode_rows,
+                         const int* page_table, void* stream) {
   using namespace rlk;
   RLK_REQUIRE(n_tiles > 0, "attn_fwd: no tiles");
   RLK_REQUIRE(n_src == 1 || (n_src >= 2 && n_src <= 8), "attn_fwd: n_src must be 1..8");
@@ -364,6 +378,7 @@ RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long
   p.cp_ranks = n_src > 1 ? n_src : 1;
   p.cp_zigzag = cp_zigzag;
   p.status = device_status_word();
+  p.page_table = page_table;
   p.q_rows_box = decode_rows ? 8 : 128;
   CUtensorMap tmQ;
   int rc = make_tmap_2d_sw128(&tmQ, Q, q_rows, q_cols, ldq, p.q_rows_box, 64, 2);

@@ -2,3 +2,4 @@ from rl_kernel_b200.ops.attention.attention import (AttentionOp, causal_attentio
                                                     varlen_tiles)
 from rl_kernel_b200.ops.attention.preprocess import AttentionPreprocessor  # noqa: F401
 from rl_kernel_b200.ops.attention.projection import AttentionProjectionOp  # noqa: F401
+from rl_kernel_b200.ops.attention.paged import PagedKVCache, paged_attention  # noqa: F401

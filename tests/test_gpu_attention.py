@@ -94,3 +94,48 @@ def test_backward(S):
     for got, want in zip(grads[0], (qf.grad, k0.grad, v0.grad)):
         w = want.transpose(1, 2).reshape(got.shape)
         assert (got.float() - w).abs().max().item() < 0.02 * w.abs().max().item() + 0.02
+
+
+def test_paged_attention_equals_contiguous_bitwise():
+    """Decode and chunked prefill through a fragmented page pool give the bits of contiguous KV."""
+    from rl_kernel_b200.ops.attention import PagedKVCache, causal_attention, paged_attention
+
+    hq, hkv, d = 8, 2, 128
+    lens = [300, 129, 517]
+    cache = PagedKVCache(16, hkv, d, dev())
+    ks, vs, qs = [], [], []
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for s, n in enumerate(lens):
+        ks.append(torch.randn(n, hkv, d, device=dev(), generator=g).to(BF))
+        vs.append(torch.randn(n, hkv, d, device=dev(), generator=g).to(BF))
+        qs.append(torch.randn(n, hq, d, device=dev(), generator=g).to(BF))
+    # interleave the allocations so that every sequence's pages are scattered over the pool
+    for upto in (100, 260, 600):
+        for s, n in enumerate(lens):
+            m = min(n, upto)
+            old = cache.lengths.get(s, 0)
+            if m > old:
+                cache.reserve(s, m)
+                cache.write(s, torch.arange(old, m), ks[s][old:m].reshape(m - old, -1), vs[s][old:m].reshape(m - old, -1))
+    assert cache.tables[0] != sorted(cache.tables[0]) or cache.tables[2] != sorted(cache.tables[2])
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    ref, ref_lse = causal_attention(torch.cat(qs), torch.cat(ks), torch.cat(vs), cu, return_lse=True)
+    # decode: the last token of every sequence
+    q_last = torch.stack([q[-1] for q in qs])
+    out = paged_attention(q_last, cache, [0, 1, 2], [torch.tensor([n - 1]) for n in lens])
+    sync_and_check()
+    for s in range(3):
+        assert torch.equal(out[s], ref[cu[s + 1] - 1])
+    # chunked prefill: the second half of every sequence as one query chunk each
+    halves = [n // 2 for n in lens]
+    q_chunk = torch.cat([q[h:] for q, h in zip(qs, halves)])
+    out2, lse2 = paged_attention(q_chunk, cache, [0, 1, 2], [torch.arange(h, n) for h, n in zip(halves, lens)],
+                                 return_lse=True)
+    sync_and_check()
+    t0 = 0
+    for s, (h, n) in enumerate(zip(halves, lens)):
+        assert torch.equal(out2[t0:t0 + n - h], ref[cu[s] + h:cu[s + 1]])
+        assert torch.equal(lse2[t0:t0 + n - h], ref_lse[cu[s] + h:cu[s + 1]])
+        t0 += n - h

@@ -420,3 +420,53 @@ def test_all_gather_gemm_equals_gemm_of_gathered_matrix(tmp_path):
     out = str(tmp_path / "ag.pt")
     mp.spawn(_ag_gemm_worker, args=(2, _free_port(), out), nprocs=2, join=True)
     assert torch.load(out)
+
+
+def _pcp_worker(rank, world, port, out):
+    """Page pool spread over two GPUs (block b of every sequence lives on rank b % 2); each rank
+    computes a disjoint slice of the query rows and reads the other rank's pages over NVLink."""
+    dist = _init(rank, world, port)
+    from rl_kernel_b200.backends import extension as ext
+    from rl_kernel_b200.distributed.cp_attention import PeerMappedBuffers
+    from rl_kernel_b200.ops.attention import PagedKVCache, causal_attention, paged_attention
+
+    dev = torch.device("cuda", rank)
+    hq, hkv, d, n, pages = 8, 2, 128, 700, 8
+    g = torch.Generator(device="cuda").manual_seed(2)
+    q = torch.randn(n, hq, d, device=dev, generator=g).to(torch.bfloat16)
+    k = torch.randn(n, hkv, d, device=dev, generator=g).to(torch.bfloat16)
+    v = torch.randn(n, hkv, d, device=dev, generator=g).to(torch.bfloat16)
+    pm = PeerMappedBuffers(None, dev, {"k": ((pages * 128, hkv * d), torch.bfloat16),
+                                       "v": ((pages * 128, hkv * d), torch.bfloat16)})
+    cache = PagedKVCache(pages, hkv, d, dev, rank=rank, k_pool=pm.local("k"), v_pool=pm.local("v"))
+    cache.reserve(0, n, owner_of_block=lambda b: b % world)
+    mine = [b for b in range((n + 127) // 128) if b % world == rank]
+    for b in mine:                                       # fill the blocks this rank owns
+        lo, hi = b * 128, min(n, b * 128 + 128)
+        cache.write(0, torch.arange(lo, hi), k[lo:hi].reshape(hi - lo, -1), v[lo:hi].reshape(hi - lo, -1))
+    tables = [None] * world
+    dist.all_gather_object(tables, cache.tables[0])
+    for b in range(len(cache.tables[0])):                # learn where the other ranks put their blocks
+        owner = b % world
+        if owner != rank:
+            cache.set_remote_page(0, b, owner, tables[owner][b] & 0xFFFFFF)
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    lo, hi = (0, 384) if rank == 0 else (384, n)         # disjoint query slices
+    o = paged_attention(q[lo:hi].contiguous(), cache, [0], [torch.arange(lo, hi)], peer_pools=(pm["k"], pm["v"]))
+    ref = causal_attention(q, k, v, [0, n])
+    torch.cuda.synchronize(dev)
+    ok = torch.equal(o, ref[lo:hi]) and ext.poll_status(dev) == 0
+    dist.barrier()                                       # nobody frees pages a peer still reads
+    res = [None] * world
+    dist.all_gather_object(res, bool(ok))
+    if rank == 0:
+        torch.save(all(res), out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_paged_context_parallel_reads_remote_pages(tmp_path):
+    out = str(tmp_path / "pcp.pt")
+    mp.spawn(_pcp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    assert torch.load(out)

@@ -86,3 +86,24 @@ def test_gloo_tp2_matches_tp1(tmp_path):
     torch.set_num_threads(1)
     lp1 = Qwen3DenseBIModel(SPEC, w)(ids[:2], target_ids=ids[:2], return_logits=False)["selected_logp"]
     assert bit_equal(torch.load(out), lp1)
+
+
+def test_paged_kv_reference_equals_contiguous_scoring():
+    from rl_kernel_b200.reference.attention import PagedKVReference, blockwise_attention_reference
+
+    g = torch.Generator().manual_seed(4)
+    hq, hkv, d, n = 4, 2, 16, 300
+    k = torch.randn(n, hkv, d, generator=g).to(torch.bfloat16)
+    v = torch.randn(n, hkv, d, generator=g).to(torch.bfloat16)
+    q = torch.randn(n, hq, d, generator=g).to(torch.bfloat16)
+    cache = PagedKVReference(8, hkv, d)
+    cache.append(7, k[:5], v[:5])          # another sequence takes pages first: tables interleave
+    cache.append(3, k[:200], v[:200])
+    cache.append(7, k[5:140], v[5:140])
+    cache.append(3, k[200:], v[200:])
+    pos = torch.arange(n)
+    o_p, l_p = cache.score(3, q, pos)
+    o_c, l_c = blockwise_attention_reference(q, k, v, pos, strict=False)
+    assert torch.equal(o_p, o_c) and torch.equal(l_p, l_c)
+    cache.release(7)
+    assert len(cache.free) == 8 - 3
