@@ -369,6 +369,16 @@ def sample_gumbel(logits, out_ids, out_val, *, vocab_start: int, inv_temp: float
 
 
 # ------------------------------------------------------------------------------------- optimizer
+def sample_keep_threshold(logits, out_thr, *, inv_temp: float, top_k: int = 0, top_p: float = 1.0) -> None:
+    """out_thr[row] = smallest scaled logit kept under top-k / top-p (no sort; csrc/sampling/sampling.cu)."""
+    _bf16(logits, "logits"); _rowmajor2d(logits, "logits")
+    rc = _lib().rlk_sample_keep_threshold(ext.ptr(logits), _ll(logits.stride(0)), c_int(logits.shape[0]),
+                                          c_int(logits.shape[1]), c_float(inv_temp), c_int(int(top_k)),
+                                          c_float(float(top_p)), ext.ptr(out_thr), ext.stream_ptr(logits.device))
+    ext.check(rc, "sample_keep_threshold")
+    _count()
+
+
 def adamw(master, m, v, grad, param, *, lr: float, beta1: float, beta2: float, eps: float,
           weight_decay: float, step: int, grad_scale=None) -> None:
     rc = _lib().rlk_adamw(ext.ptr(master), ext.ptr(m), ext.ptr(v), ext.ptr(grad), ext.ptr(param),

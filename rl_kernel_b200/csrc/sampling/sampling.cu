@@ -111,6 +111,127 @@ __global__ void sample_pick_kernel(const SampleParams p) {
   if (p.out_val) p.out_val[row] = best;
 }
 
+// ------------------------------------------------------------------------------------ top-k / top-p
+// Per-row support threshold without sorting.  bf16 logits take at most 65536 distinct values, so
+// two 256-bin histogram passes over an order-preserving 16-bit key (high byte, then low byte inside
+// the crossing bin) locate the cut exactly:
+//   top-k: the k-th largest value (ties with it are all kept, like `z >= kth` in the torch policy);
+//   top-p: the smallest value v whose strictly-greater mass is still below top_p * total mass.
+// Masses are exp(z - zmax) in 32.32 fixed point summed with integer atomics, so the result does not
+// depend on the order in which threads arrive.  (The torch policy walks a stable sort and may cut
+// inside a group of equal values; a threshold keeps or drops the whole group -- it keeps it.)
+__device__ __forceinline__ uint32_t bf16_order_key(uint32_t h) {  // larger value -> larger key
+  return (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u);
+}
+__device__ __forceinline__ uint32_t bf16_from_order_key(uint32_t k) {
+  return (k & 0x8000u) ? (k & 0x7fffu) : (~k & 0xffffu);
+}
+
+struct KeepParams {
+  const __nv_bfloat16* logits; long long ld;
+  int rows, n;
+  float inv_temp; int top_k; float top_p;
+  float* out_thr;
+};
+
+__global__ void __launch_bounds__(512) sample_keep_threshold_kernel(const KeepParams p) {
+  __shared__ unsigned int cnt[256];
+  __shared__ unsigned long long mass[256];
+  __shared__ unsigned int cnt2[256];
+  __shared__ unsigned long long mass2[256];
+  __shared__ unsigned int red[16];
+  __shared__ int s_bk, s_bp;
+  __shared__ unsigned int s_cnt_above;
+  __shared__ unsigned long long s_mass_above, s_target;
+  const int row = blockIdx.x, tid = threadIdx.x;
+  const unsigned short* src = reinterpret_cast<const unsigned short*>(p.logits + row * p.ld);
+  const bool want_k = p.top_k > 0 && p.top_k < p.n, want_p = p.top_p < 1.f;
+  // ---- pass 0: maximum key (NaN never enters: its key compares like a huge value only for +NaN;
+  //      logits are finite by contract)
+  unsigned int kmax = 0;
+  for (int i = tid; i < p.n; i += blockDim.x) kmax = max(kmax, bf16_order_key(src[i]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) kmax = max(kmax, __shfl_xor_sync(0xffffffffu, kmax, o));
+  if ((tid & 31) == 0) red[tid >> 5] = kmax;
+  if (tid < 256) { cnt[tid] = 0u; mass[tid] = 0ull; cnt2[tid] = 0u; mass2[tid] = 0ull; }
+  __syncthreads();
+  kmax = 0;
+  for (int w = 0; w < 16; ++w) kmax = max(kmax, red[w]);
+  const float zmax = __uint_as_float(bf16_from_order_key(kmax) << 16) * p.inv_temp;
+  auto weight = [&](uint32_t h) -> unsigned long long {
+    const float z = __uint_as_float(h << 16) * p.inv_temp;
+    return static_cast<unsigned long long>(__expf(z - zmax) * 4294967296.0f);
+  };
+  // ---- pass 1: histogram over the high byte of the key
+  for (int i = tid; i < p.n; i += blockDim.x) {
+    const uint32_t h = src[i], k = bf16_order_key(h);
+    atomicAdd(&cnt[k >> 8], 1u);
+    if (want_p) atomicAdd(&mass[k >> 8], weight(h));
+  }
+  __syncthreads();
+  if (tid == 0) {
+    unsigned int c = 0;
+    int bk = 0;
+    if (want_k) {
+      for (int b = 255; b >= 0; --b) {
+        if (c + cnt[b] >= static_cast<unsigned int>(p.top_k)) { bk = b; break; }
+        c += cnt[b];
+      }
+    }
+    s_bk = bk;
+    s_cnt_above = c;
+    unsigned long long total = 0ull, m = 0ull;
+    int bp = 0;
+    if (want_p) {
+      for (int b = 0; b < 256; ++b) total += mass[b];
+      const unsigned long long target = static_cast<unsigned long long>(static_cast<double>(p.top_p) * static_cast<double>(total));
+      for (int b = 255; b >= 0; --b) {
+        // the cut lies in the first non-empty bin (from the top) whose end reaches the target
+        if (mass[b] != 0ull && m + mass[b] >= target) { bp = b; break; }
+        m += mass[b];
+      }
+      s_target = target;
+    }
+    s_bp = bp;
+    s_mass_above = m;
+  }
+  __syncthreads();
+  // ---- pass 2: histograms over the low byte inside the crossing bins
+  const uint32_t bk = s_bk, bp = s_bp;
+  for (int i = tid; i < p.n; i += blockDim.x) {
+    const uint32_t h = src[i], k = bf16_order_key(h);
+    if (want_k && (k >> 8) == bk) atomicAdd(&cnt2[k & 255u], 1u);
+    if (want_p && (k >> 8) == bp) atomicAdd(&mass2[k & 255u], weight(h));
+  }
+  __syncthreads();
+  if (tid == 0) {
+    float thr = -INFINITY;
+    if (want_k) {
+      unsigned int c = s_cnt_above;
+      uint32_t key = bk << 8;
+      for (int b = 255; b >= 0; --b) {
+        c += cnt2[b];
+        if (c >= static_cast<unsigned int>(p.top_k)) { key = (bk << 8) | b; break; }
+      }
+      thr = fmaxf(thr, __uint_as_float(bf16_from_order_key(key) << 16) * p.inv_temp);
+    }
+    if (want_p) {
+      unsigned long long m = s_mass_above;
+      uint32_t key = bp << 8;
+      // descending: a value is kept while the mass strictly above it is below the target; the
+      // row maximum (nothing above it) is always kept
+      for (int b = 255; b >= 0; --b) {
+        if (mass2[b] == 0ull) continue;
+        if (m >= s_target && m != 0ull) break;
+        key = (bp << 8) | b;
+        m += mass2[b];
+      }
+      thr = fmaxf(thr, __uint_as_float(bf16_from_order_key(key) << 16) * p.inv_temp);
+    }
+    p.out_thr[row] = thr;
+  }
+}
+
 }  // namespace rlk
 using namespace rlk;
 
@@ -134,6 +255,19 @@ RLK_API int rlk_sample_gumbel(const void* logits, long long ld, const float* min
   sample_gumbel_kernel<<<rows * kSampleSegs, 256, 0, s>>>(p);
   RLK_CHECK_CUDA(cudaGetLastError());
   sample_pick_kernel<<<(rows + 127) / 128, 128, 0, s>>>(p);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+// out_thr[row] = smallest scaled logit (logit * inv_temp) that stays in the sampling support under
+// top-k (0 = off) and top-p (1 = off); -inf when neither cuts.  Feed it to rlk_sample_gumbel as
+// `min_keep`.  One CTA per row, three passes over the row (L2 resident).
+RLK_API int rlk_sample_keep_threshold(const void* logits, long long ld, int rows, int n, float inv_temp,
+                                      int top_k, float top_p, float* out_thr, void* stream) {
+  RLK_REQUIRE(rows > 0 && n > 0, "sample_keep_threshold: empty");
+  RLK_REQUIRE(top_p > 0.f, "sample_keep_threshold: top_p must be positive");
+  KeepParams p{(const __nv_bfloat16*)logits, ld, rows, n, inv_temp, top_k, top_p, out_thr};
+  sample_keep_threshold_kernel<<<rows, 512, 0, static_cast<cudaStream_t>(stream)>>>(p);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

@@ -13,6 +13,14 @@ def keep_threshold(logits: torch.Tensor, *, temperature: float = 1.0, top_k: int
     The sm_100a sampler takes this threshold instead of a [rows, V] mask."""
     if (not top_k or top_k >= logits.shape[1]) and top_p >= 1.0:
         return None
+    if logits.is_cuda and logits.dtype == torch.bfloat16 and logits.stride(-1) == 1:
+        # native: two histogram passes over the 65536 possible bf16 values, no sort
+        from rl_kernel_b200.backends import native as nv
+
+        lg = logits if real_vocab is None else logits[:, :real_vocab]
+        thr = torch.empty(lg.shape[0], dtype=torch.float32, device=lg.device)
+        nv.sample_keep_threshold(lg, thr, inv_temp=1.0 / max(temperature, 1e-6), top_k=top_k, top_p=top_p)
+        return thr
     keep = sampling_keep_mask(logits, temperature=temperature, top_k=top_k, top_p=top_p, real_vocab=real_vocab)
     z = logits.float() / max(temperature, 1e-6)
     return z.masked_fill(~keep, float("inf")).min(dim=-1).values

@@ -275,3 +275,26 @@ def test_adamw_and_exact_sumsq():
     assert whole == ss([g[:1000], g[1000:50000], g[50000:]]), "sum of squares must not depend on the partition"
     assert whole == ss([g[:1001], g[1001:50003], g[50003:]]), "nor on the alignment of the pieces"
     assert abs(whole - g.double().pow(2).sum().item()) < 1e-6 * whole
+
+
+def test_top_k_top_p_threshold_matches_sorted_policy():
+    """The histogram threshold keeps exactly the ids of the sort-based policy whenever the cut does
+    not fall inside a group of equal logits (then it keeps the whole group)."""
+    from rl_kernel_b200.backends import native as nv
+    from rl_kernel_b200.reference.sampling.policy import sampling_keep_mask
+
+    rows, V = 12, 20000
+    logits = (torch.randn(rows, V, device=dev()) * 3).to(BF)
+    for temperature, top_k, top_p in ((1.0, 50, 1.0), (0.7, 0, 0.9), (1.3, 200, 0.95), (1.0, 1, 0.5)):
+        thr = torch.empty(rows, device=dev())
+        nv.sample_keep_threshold(logits, thr, inv_temp=1.0 / temperature, top_k=top_k, top_p=top_p)
+        sync_and_check()
+        z = logits.float() * (1.0 / temperature)
+        mine = z >= thr[:, None]
+        ref = sampling_keep_mask(logits.cpu(), temperature=temperature, top_k=top_k, top_p=top_p).to(dev())
+        assert torch.all(mine | ~ref), "every id of the sorted policy must be kept"
+        extra = mine & ~ref
+        # anything extra ties with the smallest kept logit of the reference
+        low = z.masked_fill(~ref, float("inf")).min(dim=-1, keepdim=True).values
+        assert torch.all(~extra | (z == low)), (temperature, top_k, top_p)
+        assert mine.sum().item() <= ref.sum().item() + rows * 8
