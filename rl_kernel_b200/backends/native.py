@@ -283,12 +283,15 @@ def embedding_bwd(sorted_ids, order, dy, dw, vocab_start: int = 0) -> None:
 
 
 # ------------------------------------------------------------------------------------- logp
-def logits_tile_stats(logits, targets, stats, tgt_logit, *, vocab_start: int, inv_temp: float) -> None:
-    rows, n_local = logits.shape
-    rc = _lib().rlk_logits_tile_stats(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(targets),
-                                      ext.ptr(stats), _ll(stats.shape[1]), ext.ptr(tgt_logit),
-                                      c_int(rows), c_int(n_local), _ll(vocab_start), c_float(inv_temp),
-                                      ext.stream_ptr(logits.device))
+def logits_tile_stats(logits, targets, stats, tgt_logit, *, vocab_start: int, inv_temp: float,
+                      row_indices=None) -> None:
+    """``row_indices`` int64 [rows]: output row r scores logits row ``row_indices[r]``."""
+    n_local = logits.shape[1]
+    rows = logits.shape[0] if row_indices is None else row_indices.numel()
+    rc = _lib().rlk_logits_tile_stats_indexed(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(targets),
+                                              ext.ptr(stats), _ll(stats.shape[1]), ext.ptr(tgt_logit),
+                                              c_int(rows), c_int(n_local), _ll(vocab_start), c_float(inv_temp),
+                                              ext.ptr(row_indices), ext.stream_ptr(logits.device))
     ext.check(rc, "logits_tile_stats")
     _count()
 
@@ -301,11 +304,11 @@ def logp_merge(stats, tgt_logit, logp, lse) -> None:
     _count()
 
 
-def dlogits_(logits, targets, lse, g, *, vocab_start: int, inv_temp: float) -> None:
+def dlogits_(logits, targets, lse, g, *, vocab_start: int, inv_temp: float, g_lse=None) -> None:
     rows, n_local = logits.shape
-    rc = _lib().rlk_dlogits(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(targets), ext.ptr(lse),
-                            ext.ptr(g), c_int(rows), c_int(n_local), _ll(vocab_start),
-                            c_float(inv_temp), ext.stream_ptr(logits.device))
+    rc = _lib().rlk_dlogits_lse(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(targets), ext.ptr(lse),
+                                ext.ptr(g), ext.ptr(g_lse), c_int(rows), c_int(n_local), _ll(vocab_start),
+                                c_float(inv_temp), ext.stream_ptr(logits.device))
     ext.check(rc, "dlogits")
     _count()
 

@@ -1,9 +1,9 @@
 """Fused all-gather + GEMM against NCCL all-gather followed by det_gemm, per tensor-parallel rank.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 \
-        --master-port 29544 -m rl_kernel_b200.benchmarks.ag_gemm --m 12288 --n 6144 --k 4096
+        --master-port 29544 -m rl_kernel_b200.benchmarks.ag_gemm --rows 12288 --out-features 6144 --in-features 4096
 
-``--n`` is the full output width; each rank multiplies its N / W columns.  CUDA events, max over
+``--out-features`` is the full output width; each rank multiplies its N / W columns.  CUDA events, max over
 ranks, L2 flushed between iterations.  Roofline: max(2 M N_loc K / measured bf16 peak,
 (W-1)/W * M * K * 2 bytes / 770 GB/s).
 """
@@ -19,9 +19,9 @@ import torch.distributed as dist
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--m", type=int, default=12288)
-    ap.add_argument("--n", type=int, default=6144)
-    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--rows", dest="m", type=int, default=12288)
+    ap.add_argument("--out-features", dest="n", type=int, default=6144)
+    ap.add_argument("--in-features", dest="k", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
     from rl_kernel_b200.backends import extension as ext

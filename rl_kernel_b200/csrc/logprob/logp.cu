@@ -17,13 +17,16 @@ __global__ void __launch_bounds__(128)
 logits_tile_stats_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
                          float2* __restrict__ stats, long long stats_row_stride, float* __restrict__ tgt_logit,
                          int rows, int n_local, long long vocab_start, int tile_start, int n_tiles_local,
-                         float inv_temp) {
+                         float inv_temp, const long long* __restrict__ row_indices) {
   const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (gid >= static_cast<long long>(rows) * n_tiles_local) return;
   const int row = static_cast<int>(gid / n_tiles_local);
   const int lt = static_cast<int>(gid % n_tiles_local);
   const int col0 = lt * kVocabTile;
-  const __nv_bfloat16* src = logits + row * ld + col0;
+  // indexed form: output row `row` scores logits row row_indices[row] (the launch geometry
+  // depends only on the number of scored rows and the vocabulary, never on the index values)
+  const long long src_row = row_indices ? row_indices[row] : row;
+  const __nv_bfloat16* src = logits + src_row * ld + col0;
   float z[128];
 #pragma unroll
   for (int c = 0; c < 16; ++c) {
@@ -87,12 +90,13 @@ logp_merge_kernel(const float2* __restrict__ stats, long long stats_row_stride, 
 __global__ void __launch_bounds__(256)
 dlogits_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
                const float* __restrict__ lse, const float* __restrict__ g, int rows, int n_local,
-               long long vocab_start, float inv_temp) {
+               long long vocab_start, float inv_temp, const float* __restrict__ g_lse) {
   const int per_row = n_local / 8;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(rows) * per_row) return;
   const int row = static_cast<int>(idx / per_row), c = static_cast<int>(idx % per_row) * 8;
   const float gr = g[row] * inv_temp, l = lse[row];
+  const float gl = g_lse ? g_lse[row] * inv_temp : 0.f;   // d(loss)/d(lse): adds g_lse * p
   const long long tl = targets[row] - vocab_start - c;
   uint4* ptr = reinterpret_cast<uint4*>(logits + row * ld + c);
   const uint4 v = *ptr;
@@ -101,7 +105,8 @@ dlogits_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const long long
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
     const float p0 = logp_exp(bf16_lo(u[k]) * inv_temp - l), p1 = logp_exp(bf16_hi(u[k]) * inv_temp - l);
-    const float d0 = gr * ((tl == 2 * k ? 1.f : 0.f) - p0), d1 = gr * ((tl == 2 * k + 1 ? 1.f : 0.f) - p1);
+    float d0 = gr * ((tl == 2 * k ? 1.f : 0.f) - p0), d1 = gr * ((tl == 2 * k + 1 ? 1.f : 0.f) - p1);
+    if (g_lse) { d0 = fmaf(gl, p0, d0); d1 = fmaf(gl, p1, d1); }
     o[k] = pack_bf16x2(d0, d1);
   }
   *ptr = make_uint4(o[0], o[1], o[2], o[3]);
@@ -113,18 +118,26 @@ using namespace rlk;
 // stats: float2 [rows][stats_row_stride]; this call fills tiles [tile_start, tile_start + n_tiles_local)
 // from a local logits shard [rows, n_local] whose first column is global vocab id `vocab_start`
 // (a multiple of 128). tgt_logit[row] is written only by the shard that owns the target.
-RLK_API int rlk_logits_tile_stats(const void* logits, long long ld, const long long* targets,
-                                  void* stats, long long stats_row_stride, float* tgt_logit, int rows,
-                                  int n_local, long long vocab_start, float inv_temp, void* stream) {
+RLK_API int rlk_logits_tile_stats_indexed(const void* logits, long long ld, const long long* targets,
+                                          void* stats, long long stats_row_stride, float* tgt_logit, int rows,
+                                          int n_local, long long vocab_start, float inv_temp,
+                                          const long long* row_indices, void* stream) {
   RLK_REQUIRE(rows > 0 && n_local > 0 && n_local % 8 == 0 && ld % 8 == 0, "tile_stats: bad shape");
   RLK_REQUIRE(vocab_start % kVocabTile == 0, "tile_stats: vocab_start must be a multiple of 128");
   const int n_tiles_local = (n_local + kVocabTile - 1) / kVocabTile;
   const long long n = static_cast<long long>(rows) * n_tiles_local;
   logits_tile_stats_kernel<<<static_cast<unsigned>((n + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)logits, ld, targets, (float2*)stats, stats_row_stride, tgt_logit, rows,
-      n_local, vocab_start, static_cast<int>(vocab_start / kVocabTile), n_tiles_local, inv_temp);
+      n_local, vocab_start, static_cast<int>(vocab_start / kVocabTile), n_tiles_local, inv_temp, row_indices);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
+}
+
+RLK_API int rlk_logits_tile_stats(const void* logits, long long ld, const long long* targets,
+                                  void* stats, long long stats_row_stride, float* tgt_logit, int rows,
+                                  int n_local, long long vocab_start, float inv_temp, void* stream) {
+  return rlk_logits_tile_stats_indexed(logits, ld, targets, stats, stats_row_stride, tgt_logit, rows, n_local,
+                                       vocab_start, inv_temp, nullptr, stream);
 }
 
 RLK_API int rlk_logp_merge(const void* stats, long long stats_row_stride, int n_tiles,
@@ -136,13 +149,21 @@ RLK_API int rlk_logp_merge(const void* stats, long long stats_row_stride, int n_
   return RLK_OK;
 }
 
-RLK_API int rlk_dlogits(void* logits, long long ld, const long long* targets, const float* lse,
-                        const float* g, int rows, int n_local, long long vocab_start, float inv_temp,
-                        void* stream) {
+// In place: logits <- g_logp * (onehot(target) - p) + g_lse * p, p = softmax(logits * inv_temp),
+// both scaled by inv_temp (g_lse may be null: the log-sum-exp does not enter the loss).
+RLK_API int rlk_dlogits_lse(void* logits, long long ld, const long long* targets, const float* lse,
+                            const float* g, const float* g_lse, int rows, int n_local, long long vocab_start,
+                            float inv_temp, void* stream) {
   RLK_REQUIRE(rows > 0 && n_local % 8 == 0 && ld % 8 == 0, "dlogits: bad shape");
   const long long n = static_cast<long long>(rows) * (n_local / 8);
   dlogits_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      (__nv_bfloat16*)logits, ld, targets, lse, g, rows, n_local, vocab_start, inv_temp);
+      (__nv_bfloat16*)logits, ld, targets, lse, g, rows, n_local, vocab_start, inv_temp, g_lse);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
+}
+
+RLK_API int rlk_dlogits(void* logits, long long ld, const long long* targets, const float* lse,
+                        const float* g, int rows, int n_local, long long vocab_start, float inv_temp,
+                        void* stream) {
+  return rlk_dlogits_lse(logits, ld, targets, lse, g, nullptr, rows, n_local, vocab_start, inv_temp, stream);
 }

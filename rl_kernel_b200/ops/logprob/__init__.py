@@ -47,6 +47,55 @@ def logp_from_logits(logits: torch.Tensor, targets: torch.Tensor, temperature: f
     return _LogpFromLogitsFn.apply(lg.contiguous(), targets.reshape(-1).contiguous(), 1.0 / temperature).view(shp)
 
 
+class _IndexedLogpLseFn(torch.autograd.Function):
+    """(logp, lse) of the rows listed in ``row_indices``; both outputs are differentiable."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, row_indices, inv_temp):
+        from rl_kernel_b200.backends import native as nv
+
+        V = logits.shape[1]
+        rows = row_indices.numel()
+        stats = torch.empty(rows, _ntiles(V), 2, device=logits.device, dtype=torch.float32)
+        tl = torch.zeros(rows, device=logits.device, dtype=torch.float32)
+        nv.logits_tile_stats(logits, targets, stats, tl, vocab_start=0, inv_temp=inv_temp, row_indices=row_indices)
+        logp = torch.empty(rows, device=logits.device, dtype=torch.float32)
+        lse = torch.empty(rows, device=logits.device, dtype=torch.float32)
+        nv.logp_merge(stats, tl, logp, lse)
+        ctx.save_for_backward(logits, targets, row_indices, lse)
+        ctx.inv_temp = inv_temp
+        return logp, lse
+
+    @staticmethod
+    def backward(ctx, g_logp, g_lse):
+        from rl_kernel_b200.backends import native as nv
+
+        logits, targets, row_indices, lse = ctx.saved_tensors
+        sel = logits.index_select(0, row_indices).contiguous()
+        nv.dlogits_(sel, targets, lse, g_logp.float().contiguous(), vocab_start=0, inv_temp=ctx.inv_temp,
+                    g_lse=g_lse.float().contiguous())
+        d = torch.zeros_like(logits)
+        d.index_add_(0, row_indices, sel)        # an index may repeat: its gradients add up
+        return d, None, None, None
+
+
+def logp_from_logits_indexed(logits: torch.Tensor, targets: torch.Tensor, row_indices: torch.Tensor,
+                             temperature: float = 1.0, return_lse: bool = False):
+    """Selected log-prob of ``targets[i]`` under row ``row_indices[i]`` of ``logits`` [R, V] (scoring
+    a subset of positions without gathering the logits first; parity: the row_indices variants of
+    csrc/cuda/logprob/fused_logp_kernel.cu:125-220).  With ``return_lse`` also the log-sum-exp,
+    whose gradient is g_lse * softmax."""
+    if not use_native(logits):
+        lg = logits.index_select(0, row_indices)
+        lp = NativeBatchInvariantLogpOp(temperature).apply_fp32(lg, targets)
+        if not return_lse:
+            return lp
+        return lp, torch.logsumexp(lg.float() / temperature, -1)
+    lp, lse = _IndexedLogpLseFn.apply(logits.contiguous(), targets.contiguous(), row_indices.contiguous().long(),
+                                      1.0 / temperature)
+    return (lp, lse) if return_lse else lp
+
+
 class _LinearLogpFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, hidden, weight, targets, inv_temp, chunk):
