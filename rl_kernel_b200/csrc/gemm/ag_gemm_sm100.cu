@@ -48,6 +48,20 @@ __device__ __forceinline__ int ag_mtile(const AgGemmParams& p, int ord) {
   return shard * per + ord % per;
 }
 
+// Tile t -> (position of its m-tile in processing order, n-tile).  Groups of kAgGroupM m-tiles
+// sweep all n-tiles with the m-tile varying fastest, so the CTAs that run at the same time share a
+// few B tiles and the group's A rows stay in L2 while B streams through once per group.
+constexpr int kAgGroupM = 8;
+__device__ __forceinline__ void ag_tile_coords(const AgGemmParams& p, int t, int& ord, int& nt) {
+  const int per_group = kAgGroupM * p.n_tiles;
+  const int g = t / per_group;
+  const int first = g * kAgGroupM;
+  const int gsize = min(p.m_tiles - first, kAgGroupM);
+  const int r = t - g * per_group;
+  ord = first + r % gsize;
+  nt = r / gsize;
+}
+
 __global__ void __launch_bounds__(kAgThreads, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const AgGemmParams p) {
@@ -91,7 +105,8 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       uint32_t it = 0;
       for (int t = blockIdx.x; t < total; t += gridDim.x) {
-        const int ord = t / p.n_tiles, nt = t % p.n_tiles;
+        int ord, nt;
+        ag_tile_coords(p, t, ord, nt);
         const int mt = ag_mtile(p, ord);
         if (ord >= own_tiles) {
           // remote rows: wait until all of the m-tile's gather items have landed
@@ -150,7 +165,8 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     uint32_t u = 0;
     for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x, ++u) {
-      const int ord = t / p.n_tiles, nt = t % p.n_tiles;
+      int ord, nt;
+      ag_tile_coords(p, t, ord, nt);
       const int row = ag_mtile(p, ord) * ABM + r;
       const uint32_t a = u & 1;
       if (!mbar_wait(accf0 + 8 * a, (u >> 1) & 1, abort_flag, p.status, 505)) break;

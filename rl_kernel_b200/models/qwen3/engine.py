@@ -67,10 +67,15 @@ class PackedParams:
     optimizer, gradient clipping, weight sync and gradient all-reduce are single launches."""
 
     def __init__(self, spec: Qwen3DenseSpec, tp_rank: int, tp_size: int, device: torch.device,
-                 with_grad: bool = False):
+                 with_grad: bool = False, *, layers: tuple[int, int] | None = None,
+                 has_embed: bool = True, has_head: bool = True):
+        """``layers`` = (first, end) and ``has_embed`` / ``has_head`` select what a pipeline stage owns
+        (default: the whole model)."""
         if spec.canonical_tp % tp_size:
             raise ValueError(f"tp_size {tp_size} must divide canonical_tp {spec.canonical_tp}")
         self.spec, self.tp_rank, self.tp_size, self.device = spec, tp_rank, tp_size, device
+        self.layer_range = layers if layers is not None else (0, spec.num_hidden_layers)
+        self.has_embed, self.has_head = has_embed, has_head
         h, d = spec.hidden_size, spec.head_dim
         self.qkv_local = spec.qkv_dim // tp_size
         self.q_local = spec.q_dim // tp_size
@@ -79,13 +84,14 @@ class PackedParams:
         self.v_local = spec.padded_vocab_size // tp_size
         self.vocab_start = tp_rank * self.v_local
         self.v_real_local = max(0, min(self.v_local, spec.vocab_size - self.vocab_start))
-        slots: list[_Slot] = [_Slot("embed", (self.v_local, h))]
-        for l in range(spec.num_hidden_layers):
+        slots: list[_Slot] = [_Slot("embed", (self.v_local, h))] if has_embed else []
+        for l in range(*self.layer_range):
             slots += [_Slot(f"l{l}.ln1", (h,)), _Slot(f"l{l}.wqkv", (self.qkv_local, h)),
                       _Slot(f"l{l}.qn", (d,)), _Slot(f"l{l}.kn", (d,)),
                       _Slot(f"l{l}.wo", (h, self.q_local)), _Slot(f"l{l}.ln2", (h,))]
             slots += self._mlp_slots(l)
-        slots += [_Slot("norm", (h,)), _Slot("lm_head", (self.v_local, h))]
+        if has_head:
+            slots += [_Slot("norm", (h,)), _Slot("lm_head", (self.v_local, h))]
         slots += self._trailing_slots()
         off = 0
         for s in slots:
@@ -127,10 +133,12 @@ class PackedParams:
             n = t.shape[1] // tp
             return t[:, r * n:(r + 1) * n]
 
-        put("embed", rows(pad_vocab(spec, weights["embed_tokens.weight"])))
-        put("lm_head", rows(pad_vocab(spec, weights["lm_head.weight"])))
-        put("norm", weights["norm.weight"])
-        for l in range(spec.num_hidden_layers):
+        if self.has_embed:
+            put("embed", rows(pad_vocab(spec, weights["embed_tokens.weight"])))
+        if self.has_head:
+            put("lm_head", rows(pad_vocab(spec, weights["lm_head.weight"])))
+            put("norm", weights["norm.weight"])
+        for l in range(*self.layer_range):
             p = f"layers.{l}"
             put(f"l{l}.ln1", weights[f"{p}.input_layernorm.weight"])
             put(f"l{l}.ln2", weights[f"{p}.post_attention_layernorm.weight"])
@@ -160,9 +168,8 @@ class PackedParams:
                     blk.copy_(torch.randn(blk.shape, generator=gen, device=self.device,
                                           dtype=torch.float32).mul_(std))
         for name in ("embed", "lm_head"):
-            w = self.w[name]
-            if self.v_real_local < self.v_local:
-                w[self.v_real_local:].zero_()
+            if name in self.w and self.v_real_local < self.v_local:
+                self.w[name][self.v_real_local:].zero_()
         return self
 
     def export_local(self) -> dict[str, torch.Tensor]:
@@ -293,6 +300,8 @@ class Qwen3Engine:
         self.d = spec.head_dim
         if self.d != 128:
             raise ValueError("the sm_100a attention kernels are specialised for head_dim 128")
+        self.l0, self.l1 = params.layer_range        # decoder layers of this pipeline stage
+        self.first_stage, self.last_stage = params.has_embed, params.has_head
         self.nchunks = spec.canonical_tp // tp      # canonical K chunks held by this rank
         self.blk = spec.intermediate_size // spec.canonical_tp
         self.scale = 1.0 / math.sqrt(self.d)
@@ -429,13 +438,20 @@ class Qwen3Engine:
 
     # -------------------------------------------------------------------------- full forward
     def forward_hidden(self, tokens: torch.Tensor, *, save: TrainState | None = None,
-                       kv: KVCache | None = None, tag: str = "f", cp_seq_len: int | None = None) -> torch.Tensor:
+                       kv: KVCache | None = None, tag: str = "f", cp_seq_len: int | None = None,
+                       stage_in: tuple[torch.Tensor, torch.Tensor] | None = None):
         """tokens [nseq, S] -> final-norm hidden [nseq*S, H].  With ``kv`` the K/V of every layer are
         written into the cache (prefill); with ``save`` layer inputs are checkpointed for backward.
         ``cp_seq_len``: context parallel -- ``tokens`` holds this rank's S = cp_seq_len / cp positions
-        of every sequence (``cp.local_positions`` order)."""
+        of every sequence (``cp.local_positions`` order).
+        Pipeline stages: a stage without the embedding takes ``stage_in`` = (block output, residual)
+        of the previous stage's last layer; a stage without the head returns that pair for its own
+        last layer instead of the final-norm hidden (the pair, not its sum, crosses the boundary so
+        that the next layer's fused add + norm sees exactly the single-GPU operands)."""
         nseq, S = tokens.shape
-        T, H, L = nseq * S, self.spec.hidden_size, self.spec.num_hidden_layers
+        T, H = nseq * S, self.spec.hidden_size
+        if (kv is not None or cp_seq_len is not None) and not (self.first_stage and self.last_stage):
+            raise NotImplementedError("KV-cache and context-parallel paths run on a whole-model engine")
         ws = self.ws
         pos = ws.get("pos" if tag == "f" else f"{tag}.pos", (T,), torch.int32)
         cp_geom = None
@@ -450,15 +466,18 @@ class Qwen3Engine:
         else:
             pos.copy_(torch.arange(S, device=self.dev, dtype=torch.int32).repeat(nseq))
             tiles, _ = self._tiles_for(nseq, S)
-        x = ws.get(f"{tag}.embed", (T, H))
-        nv.embedding_fwd(tokens.reshape(-1), self.p.w["embed"], x, self.p.vocab_start)
-        self.ctx.tp_all_reduce_(x)
+        res = None
+        if self.first_stage:
+            x = ws.get(f"{tag}.embed", (T, H))
+            nv.embedding_fwd(tokens.reshape(-1), self.p.w["embed"], x, self.p.vocab_start)
+            self.ctx.tp_all_reduce_(x)
+        else:
+            x, res = stage_in
         if kv is not None:
             slot = ws.get(f"{tag}.slot", (T,), torch.int32)
             slot.copy_((torch.arange(nseq, device=self.dev, dtype=torch.int32) * kv.max_len)
                        .repeat_interleave(S) + pos)
-        res = None
-        for l in range(L):
+        for l in range(self.l0, self.l1):
             if kv is not None:
                 # prefill: K/V go to the cache; attention reads them back from there
                 ptiles = self._prefill_tiles(nseq, S, kv.max_len)
@@ -470,12 +489,14 @@ class Qwen3Engine:
                 else:
                     kb = ws.get(f"{tag}.k", (T, self.p.kv_local))
                     vb = ws.get(f"{tag}.v", (T, self.p.kv_local))
-                s_out = save.ckpt[l] if save is not None else None
-                if save is not None and l == 0:
-                    save.ckpt[0].copy_(x)
+                s_out = save.ckpt[l - self.l0] if save is not None else None
+                if save is not None and res is None:
+                    save.ckpt[0].copy_(x)          # the embedding output is layer 0's residual stream
                     x = save.ckpt[0]
                 x, res = self._layer_fwd(l, x, res, T, pos, tiles=tiles, kbuf=kb, vbuf=vb,
-                                         s_in_out=s_out if l > 0 else None, tag=tag, cp_geom=cp_geom)
+                                         s_in_out=s_out if res is not None else None, tag=tag, cp_geom=cp_geom)
+        if not self.last_stage:
+            return x, res
         hf = ws.get(f"{tag}.hf", (T, H))
         s_fin = ws.get(f"{tag}.s_fin", (T, H))
         nv.rmsnorm_fwd(x, self.p.w["norm"], hf, self.spec.rms_norm_eps, res=res, res_out=s_fin)
@@ -575,9 +596,11 @@ class Qwen3Engine:
         return pm.local(f"stats{q}")[:n], pm.local(f"tl{q}")[:n]
 
     # -------------------------------------------------------------------------- training step pieces
-    def new_train_state(self, nseq: int, S: int) -> TrainState:
-        T, H, L = nseq * S, self.spec.hidden_size, self.spec.num_hidden_layers
-        return TrainState(nseq, S, self.ws.get("ckpt", (L, T, H)))
+    def new_train_state(self, nseq: int, S: int, slot: int = 0) -> TrainState:
+        """``slot`` separates the checkpoints of micro-batches that are in flight at the same time
+        (pipeline schedules)."""
+        T, H, L = nseq * S, self.spec.hidden_size, self.l1 - self.l0
+        return TrainState(nseq, S, self.ws.get("ckpt" if slot == 0 else f"ckpt{slot}", (L, T, H)))
 
     def response_index(self, S: int, resp_start: int) -> tuple[torch.Tensor, torch.Tensor]:
         """(local row of every scored position this rank holds, its response index).  Position t
@@ -597,7 +620,7 @@ class Qwen3Engine:
         return tokens[:, self.cp.local_positions(tokens.shape[1]).to(self.dev)].contiguous()
 
     def train_forward_backward(self, tokens: torch.Tensor, resp_start: int, dlogp_fn, *,
-                               temperature: float = 1.0, lm_chunk: int = 4096):
+                               temperature: float = 1.0, lm_chunk: int = 4096, stage_in=None):
         """One micro-batch: forward with checkpoints, LM head + log-probs on response positions,
         ``dlogp_fn(logp [nseq, Rl]) -> dlogp [nseq, Rl]`` supplies d(loss)/d(logp), then the full
         backward accumulates into ``params.grad``.  Returns logp [nseq, Rl] (fp32).
@@ -616,7 +639,7 @@ class Qwen3Engine:
         R = sel.numel()
         st = self.new_train_state(nseq, Sl)
         st.extra["S_global"] = S
-        hf = self.forward_hidden(tok_local, save=st, cp_seq_len=S if cp else None)
+        hf = self.forward_hidden(tok_local, save=st, cp_seq_len=S if cp else None, stage_in=stage_in)
         hf3 = hf.view(nseq, Sl, H)
         rows = self.ws.get("lm.rows", (nseq * R, H))
         if cp:
@@ -653,13 +676,18 @@ class Qwen3Engine:
             dhf.view(nseq, Sl, H).index_copy_(1, sel, drows.view(nseq, R, H))
         else:
             dhf.view(nseq, Sl, H)[:, resp_start - 1:S - 1].copy_(drows.view(nseq, R, H))
-        self._backward(st, tok_local, dhf)
+        self.stage_input_grad = self._backward(st, tok_local, dhf)   # None unless a pipeline stage
         return logp.view(nseq, R)
 
-    def _backward(self, st: TrainState, tokens: torch.Tensor, dhf: torch.Tensor) -> None:
+    def _backward(self, st: TrainState, tokens: torch.Tensor, dhf: torch.Tensor | None,
+                  ds_in: torch.Tensor | None = None) -> torch.Tensor | None:
+        """Backward of this stage's layers.  Last stage: ``dhf`` is the gradient of the final-norm
+        output.  Other stages: ``ds_in`` is the gradient of the residual stream after the stage's last
+        layer (what the next stage returned).  Returns the gradient of the stage input's residual
+        stream for the previous stage (None on the first stage, which ends in the embedding)."""
         spec, w, g, ws = self.spec, self.p.w, self.p.g, self.ws
         nseq, S = st.nseq, st.S
-        T, H, L = nseq * S, spec.hidden_size, spec.num_hidden_layers
+        T, H = nseq * S, spec.hidden_size
         eps = spec.rms_norm_eps
         pos = ws.get("pos", (T,), torch.int32)
         cp = self.cp is not None
@@ -668,23 +696,27 @@ class Qwen3Engine:
         scr = ws.get("b.scr", (max(nv.rmsnorm_bwd_scratch_elems(T, H), nv.qk_norm_rope_bwd_scratch_elems(T)),),
                      torch.float32)
         ds = ws.get("b.ds", (T, H))          # gradient of the residual stream
-        # final norm: s_fin -> hf
-        nv.rmsnorm_bwd(st.final_s, w["norm"], dhf, ds, scr, eps, dw_bf16=g["norm"], accumulate_dw=True)
+        if self.last_stage:
+            # final norm: s_fin -> hf
+            nv.rmsnorm_bwd(st.final_s, w["norm"], dhf, ds, scr, eps, dw_bf16=g["norm"], accumulate_dw=True)
+        else:
+            ds.copy_(ds_in)
         if cp:
             # peers read these while computing their dK / dV
             lse, delta = self.cp.bufs.local("lse"), self.cp.bufs.local("delta")
         else:
             lse = ws.get("b.lse", (T, self.hq), torch.float32)
             delta = ws.get("b.delta", (T, self.hq), torch.float32)
-        for l in range(L - 1, -1, -1):
+        for l in range(self.l1 - 1, self.l0 - 1, -1):
             keep: dict = {}
+            ck = st.ckpt[l - self.l0]
             if cp:
                 kb, vb = self.cp.bufs.local("k")[:T], self.cp.bufs.local("v")[:T]
             else:
                 kb = ws.get("f.k", (T, self.p.kv_local))
                 vb = ws.get("f.v", (T, self.p.kv_local))
             # ---- recompute the layer from its checkpointed input
-            self._layer_fwd(l, st.ckpt[l], None, T, pos, tiles=tiles, kbuf=kb, vbuf=vb, lse=lse,
+            self._layer_fwd(l, ck, None, T, pos, tiles=tiles, kbuf=kb, vbuf=vb, lse=lse,
                             keep=keep, tag="r", cp_geom=cp_geom)
             # ---- MLP backward.  s_out = s_mid + down  =>  d(down) = ds, d(s_mid) += ds
             dh2 = self._mlp_bwd(l, ds, keep, T)
@@ -715,11 +747,30 @@ class Qwen3Engine:
             self.ctx.tp_all_reduce_(dh)
             self._gemm(dqkv, keep["h"], g[f"l{l}.wqkv"], a_mn=True, b_mn=True, accumulate=True,
                        M=self.p.qkv_local, N=H, K=T)
-            nv.rmsnorm_bwd(st.ckpt[l], w[f"l{l}.ln1"], dh, ds, scr, eps, dres=ds2,
+            nv.rmsnorm_bwd(ck, w[f"l{l}.ln1"], dh, ds, scr, eps, dres=ds2,
                            dw_bf16=g[f"l{l}.ln1"], accumulate_dw=True)
+        if not self.first_stage:
+            return ds
         # ---- embedding
         sid, order = torch.sort(tokens.reshape(-1), stable=True)
         nv.embedding_bwd(sid.contiguous(), order.contiguous(), ds, g["embed"], self.p.vocab_start)
+        return None
+
+    # -------------------------------------------------------------------------- pipeline stages
+    def stage_forward(self, tokens: torch.Tensor, stage_in, slot: int = 0):
+        """Forward of a stage that does not own the head: returns (TrainState, (x, res))."""
+        nseq, S = tokens.shape
+        st = self.new_train_state(nseq, S, slot)
+        out = self.forward_hidden(tokens, save=st, stage_in=stage_in)
+        return st, out
+
+    def stage_backward(self, st: TrainState, tokens: torch.Tensor, ds_in: torch.Tensor):
+        """Backward of a stage that does not own the head; returns the gradient for the previous
+        stage (None on the first stage)."""
+        # recompute needs this micro-batch's positions again (another one may have run in between)
+        pos = self.ws.get("pos", (st.nseq * st.S,), torch.int32)
+        pos.copy_(torch.arange(st.S, device=self.dev, dtype=torch.int32).repeat(st.nseq))
+        return self._backward(st, tokens, None, ds_in)
 
     # -------------------------------------------------------------------------- rollout
     def kv_cache_bytes(self, nseq: int, max_len: int) -> int:

@@ -470,3 +470,56 @@ def test_paged_context_parallel_reads_remote_pages(tmp_path):
     out = str(tmp_path / "pcp.pt")
     mp.spawn(_pcp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
     assert torch.load(out)
+
+
+def _pp_setup(dev, layers, has_embed, has_head):
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.engine import PackedParams, Qwen3Engine
+
+    spec = Qwen3DenseSpec.scaled(layers=4, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+    w = Qwen3DenseWeights.synthetic(spec, seed=3)
+    params = PackedParams(spec, 0, 1, dev, with_grad=True, layers=layers, has_embed=has_embed, has_head=has_head).load(w)
+    eng = Qwen3Engine(spec, params, max_positions=512)
+    micro = [torch.randint(0, spec.vocab_size, (2, 256), generator=torch.Generator().manual_seed(20 + i)).to(dev)
+             for i in range(4)]
+    return spec, params, eng, micro
+
+
+def _pp_worker(rank, world, port, out):
+    dist = _init(rank, world, port)
+    from rl_kernel_b200.parallel.pipeline import PipelineTrainer, StageLink, split_layers
+
+    dev = torch.device("cuda", rank)
+    ranges = split_layers(4, world)
+    spec, params, eng, micro = _pp_setup(dev, ranges[rank], rank == 0, rank == world - 1)
+    trainer = PipelineTrainer(eng, StageLink(rank, world, dev))
+    logps = trainer.run(micro, 64, lambda lp, i: torch.full_like(lp, -1.0 / lp.numel()))
+    torch.cuda.synchronize(dev)
+    res = {"logp": [l.cpu() for l in logps], "grads": {k: v.cpu() for k, v in params.g.items()}}
+    gathered = [None] * world
+    dist.all_gather_object(gathered, res)
+    if rank == 0:
+        torch.save(gathered, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_pipeline_two_stages_match_single_gpu_bitwise(tmp_path):
+    """1F1B over two stages (NCCL p2p between them) gives the log-probs and every gradient of the
+    unsplit model bit for bit."""
+    out = str(tmp_path / "pp.pt")
+    mp.spawn(_pp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    pp = torch.load(out)
+    dev = torch.device("cuda:0")
+    spec, params, eng, micro = _pp_setup(dev, None, True, True)
+    ref = [eng.train_forward_backward(t, 64, lambda lp: torch.full_like(lp, -1.0 / lp.numel())).clone() for t in micro]
+    torch.cuda.synchronize(dev)
+    assert len(pp[1]["logp"]) == 4 and pp[0]["logp"] == []
+    for a, b in zip(pp[1]["logp"], ref):
+        assert torch.equal(a, b.cpu())
+    seen = set()
+    for stage in pp:
+        for name, g in stage["grads"].items():
+            assert torch.equal(g, params.g[name].cpu()), name
+            seen.add(name)
+    assert seen == set(params.g)
