@@ -276,6 +276,20 @@ class KVCache:
 
 
 @dataclass
+class SharedPrefixKV:
+    """KV pool in which the sequences of a GRPO group share their prompt's pages: per layer
+    [num_prompts * P + nseq * R_pad, kv_local] rows = prompt region then one response region per
+    sequence, addressed through a page table (page = 128 rows)."""
+    kv: KVCache                 # the whole pool (nseq = 1, max_len = rows)
+    prompt_kv: KVCache          # view of the prompt region, [num_prompts, P] (prefill writes here)
+    page_table: torch.Tensor    # int32 [nseq, blocks_per_seq]
+    slot_base: torch.Tensor     # int32 [nseq]: pool row of a sequence's first response token
+    prompt_len: int
+    blocks_per_seq: int
+    seq_of_tile: torch.Tensor | None = None
+
+
+@dataclass
 class TrainState:
     nseq: int
     S: int
@@ -309,6 +323,7 @@ class Qwen3Engine:
         self.ws = Workspace(self.dev)
         self.fuse_gemm_allreduce = True
         self.cp = None                               # CPAttention once enable_context_parallel ran
+        self._decode_page_table = None               # set while a paged decode step runs
         self._tiles: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
         for K in (params.q_local, params.i_local):
             if self.nchunks > 1 and (K // self.nchunks) % 64:
@@ -434,7 +449,8 @@ class Qwen3Engine:
 
     def _attention(self, q2d, k2d, v2d, o2d, lse, tiles, decode: bool = False):
         nv.attn_fwd(q2d, [k2d], [v2d], o2d, lse, tiles, self.scale,
-                    decode=decode and self.hq // self.hkv <= 8)
+                    decode=decode and self.hq // self.hkv <= 8,
+                    page_table=self._decode_page_table if decode else None)
 
     # -------------------------------------------------------------------------- full forward
     def forward_hidden(self, tokens: torch.Tensor, *, save: TrainState | None = None,
@@ -789,6 +805,46 @@ class Qwen3Engine:
         v = [flat[(2 * l + 1) * n:(2 * l + 2) * n].view(nseq * max_len, self.p.kv_local) for l in range(L)]
         return KVCache(k, v, nseq, max_len, flat)
 
+    def new_shared_prefix_cache(self, num_prompts: int, group: int, prompt_len: int, resp_len: int,
+                                storage: torch.Tensor | None = None) -> SharedPrefixKV:
+        """Pool for ``num_prompts * group`` sequences whose first ``prompt_len`` keys (a multiple of
+        128) are the group's shared prompt.  Nothing is copied per sample: a sequence's page table
+        names the prompt's pages for its first blocks and its own pages after them."""
+        if prompt_len % 128:
+            raise ValueError("shared-prefix pages need a prompt length that is a multiple of 128")
+        L, P = self.spec.num_hidden_layers, prompt_len
+        rp = (resp_len + 127) // 128 * 128
+        nseq = num_prompts * group
+        rows = num_prompts * P + nseq * rp
+        n = rows * self.p.kv_local
+        if storage is None:
+            storage = torch.zeros(2 * L * n * 2, dtype=torch.uint8, device=self.dev)
+        flat = storage[: 2 * L * n * 2].view(BF16)
+        flat.zero_()
+        k = [flat[(2 * l) * n:(2 * l + 1) * n].view(rows, self.p.kv_local) for l in range(L)]
+        v = [flat[(2 * l + 1) * n:(2 * l + 2) * n].view(rows, self.p.kv_local) for l in range(L)]
+        kv = KVCache(k, v, 1, rows, flat)
+        pkv = KVCache([t[: num_prompts * P] for t in k], [t[: num_prompts * P] for t in v], num_prompts, P, None)
+        b = torch.arange(nseq)
+        pb, rb = P // 128, rp // 128
+        prompt_pages = (b // group).view(-1, 1) * pb + torch.arange(pb).view(1, -1)
+        own_pages = (num_prompts * P) // 128 + b.view(-1, 1) * rb + torch.arange(rb).view(1, -1)
+        table = torch.cat([prompt_pages, own_pages], dim=1).to(torch.int32).to(self.dev).contiguous()
+        slot_base = (num_prompts * P + b * rp).to(torch.int32).to(self.dev)
+        return SharedPrefixKV(kv, pkv, table, slot_base, P, pb + rb)
+
+    def decode_tiles_shared_prefix(self, sp: SharedPrefixKV, group: int) -> torch.Tensor:
+        """Decode tiles for a shared-prefix pool, ordered (prompt, KV head, sample) so that the tiles
+        that read the same prompt pages run next to each other and share them through L2."""
+        nseq = sp.page_table.shape[0]
+        t = self.decode_tiles(nseq, 0)
+        b = torch.arange(nseq).view(-1, 1).expand(nseq, self.hkv).reshape(-1)
+        t[:, 3] = 0
+        t[:, 11] = (b * sp.blocks_per_seq + 1).to(torch.int32).to(self.dev)
+        hk = torch.arange(self.hkv).view(1, -1).expand(nseq, self.hkv).reshape(-1)
+        order = torch.argsort((b // group) * (self.hkv * group) + hk * group + b % group, stable=True)
+        return t[order.to(self.dev)].contiguous()
+
     def decode_tiles(self, nseq: int, max_len: int) -> torch.Tensor:
         """Static part of the decode tile table; columns 5 (pos0) and 7 (kv_cap) change per step."""
         g = self.hq // self.hkv
@@ -800,17 +856,26 @@ class Qwen3Engine:
                         dim=-1).reshape(-1, 12)
         return t.to(torch.int32).to(self.dev).contiguous()
 
-    def decode_step(self, tokens: torch.Tensor, pos: torch.Tensor, kv: KVCache, tiles: torch.Tensor
-                    ) -> torch.Tensor:
+    def decode_step(self, tokens: torch.Tensor, pos: torch.Tensor, kv: KVCache, tiles: torch.Tensor,
+                    shared: SharedPrefixKV | None = None) -> torch.Tensor:
         """One token per sequence: tokens [B] at positions ``pos`` [B] (int32) -> final hidden [B, H].
         ``tiles`` comes from ``decode_tiles``; this call refreshes its position columns on the
-        device, so the whole step can be captured in a CUDA graph."""
+        device, so the whole step can be captured in a CUDA graph.  ``shared``: the KV lives in a
+        shared-prefix pool (``kv`` is ``shared.kv``, tiles from ``decode_tiles_shared_prefix``)."""
         B, H, L = tokens.shape[0], self.spec.hidden_size, self.spec.num_hidden_layers
         ws = self.ws
-        tiles[:, 5] = pos.repeat_interleave(self.hkv)
-        tiles[:, 7] = tiles[:, 5] + 1
         slot = ws.get("d.slot", (B,), torch.int32)
-        torch.add(torch.arange(B, device=self.dev, dtype=torch.int32) * kv.max_len, pos, out=slot)
+        if shared is None:
+            tiles[:, 5] = pos.repeat_interleave(self.hkv)
+            torch.add(torch.arange(B, device=self.dev, dtype=torch.int32) * kv.max_len, pos, out=slot)
+        else:
+            # tiles are not in sequence order: column 0 (first query row) identifies the sequence
+            if shared.seq_of_tile is None:
+                shared.seq_of_tile = torch.div(tiles[:, 0], self.hq, rounding_mode="floor").long()
+            tiles[:, 5] = pos[shared.seq_of_tile]
+            torch.add(shared.slot_base, pos - shared.prompt_len, out=slot)
+        tiles[:, 7] = tiles[:, 5] + 1
+        self._decode_page_table = shared.page_table if shared is not None else None
         x = ws.get("d.embed", (B, H))
         nv.embedding_fwd(tokens, self.p.w["embed"], x, self.p.vocab_start)
         self.ctx.tp_all_reduce_(x)
@@ -818,6 +883,7 @@ class Qwen3Engine:
         for l in range(L):
             x, res = self._layer_fwd(l, x, res, B, pos, tiles=tiles, kbuf=kv.k[l], vbuf=kv.v[l],
                                      kv_slot=slot, q_view=(B * self.hq, self.d), tag="d")
+        self._decode_page_table = None
         hf = ws.get("d.hf", (B, H))
         s_fin = ws.get("d.s_fin", (B, H))
         nv.rmsnorm_fwd(x, self.p.w["norm"], hf, self.spec.rms_norm_eps, res=res, res_out=s_fin)

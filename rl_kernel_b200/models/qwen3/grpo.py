@@ -42,6 +42,7 @@ class GRPOConfig:
     use_reference_model: bool = True
     share_rollout_weights: bool = False   # True: rollout reads the trainer's buffer (zero-copy publish)
     share_kv_and_activation_memory: bool = True
+    share_prompt_pages: bool = True       # group members read their prompt's K/V pages in place
 
     @property
     def num_seqs(self) -> int:
@@ -177,9 +178,16 @@ class GRPOTrainer:
         if self._kv is None:
             B = self.roll_seqs
             eng = self.rollout_engine
-            self._kv = eng.new_kv_cache(B, c.seq_len, storage=self._arena)
-            self._pkv = eng.new_kv_cache(self.roll_prompts, c.prompt_len)
-            self._dtiles = eng.decode_tiles(B, c.seq_len)
+            self._shared = None
+            if c.share_prompt_pages and c.prompt_len % 128 == 0:
+                self._shared = eng.new_shared_prefix_cache(self.roll_prompts, c.group_size, c.prompt_len,
+                                                           c.response_len, storage=self._arena)
+                self._kv, self._pkv = self._shared.kv, self._shared.prompt_kv
+                self._dtiles = eng.decode_tiles_shared_prefix(self._shared, c.group_size)
+            else:
+                self._kv = eng.new_kv_cache(B, c.seq_len, storage=self._arena)
+                self._pkv = eng.new_kv_cache(self.roll_prompts, c.prompt_len)
+                self._dtiles = eng.decode_tiles(B, c.seq_len)
             self._tok = torch.zeros(B, dtype=torch.int64, device=self.dev)
             self._pos = torch.zeros(B, dtype=torch.int32, device=self.dev)
             self._keys = torch.zeros(B, dtype=torch.int64, device=self.dev)
@@ -194,7 +202,7 @@ class GRPOTrainer:
     def _decode_once(self, seed: int):
         """tok[B] at pos[B] -> next token + its logp, appended at column `col`; advances state."""
         eng, c = self.rollout_engine, self.cfg
-        hf = eng.decode_step(self._tok, self._pos, self._kv, self._dtiles)
+        hf = eng.decode_step(self._tok, self._pos, self._kv, self._dtiles, shared=self._shared)
         logits = eng.logits(hf)
         torch.add(self._seq_key, self._pos, out=self._keys)
         ids, lp = eng.sample(logits, self._keys, temperature=c.temperature, seed=seed)
@@ -218,10 +226,11 @@ class GRPOTrainer:
         hf = eng.forward_hidden(prompts, kv=self._pkv, tag="p")
         H = self.spec.hidden_size
         last = hf.view(NP, P, H)[:, P - 1].repeat_interleave(G, dim=0).contiguous()
-        for l in range(self.spec.num_hidden_layers):
-            for src, dst in ((self._pkv.k[l], self._kv.k[l]), (self._pkv.v[l], self._kv.v[l])):
-                d3 = dst.view(NP, G, c.seq_len, -1)
-                d3[:, :, :P].copy_(src.view(NP, 1, P, -1).expand(-1, G, -1, -1))
+        if self._shared is None:
+            for l in range(self.spec.num_hidden_layers):
+                for src, dst in ((self._pkv.k[l], self._kv.k[l]), (self._pkv.v[l], self._kv.v[l])):
+                    d3 = dst.view(NP, G, c.seq_len, -1)
+                    d3[:, :, :P].copy_(src.view(NP, 1, P, -1).expand(-1, G, -1, -1))
         # ---- first response token comes from the prefill logits
         self._pos.fill_(P - 1)
         self._col.zero_()

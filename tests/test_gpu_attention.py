@@ -140,3 +140,22 @@ def test_paged_attention_equals_contiguous_bitwise():
         assert torch.equal(out2[t0:t0 + n - h], ref[cu[s] + h:cu[s + 1]])
         assert torch.equal(lse2[t0:t0 + n - h], ref_lse[cu[s] + h:cu[s + 1]])
         t0 += n - h
+
+
+def test_prefix_shared_attention_matches_per_sample_attention():
+    from rl_kernel_b200.ops.attention import prefix_shared_attention
+
+    bs, G, Lq, hq, hkv, d, Lkv = 2, 8, 24, 8, 2, 128, 300
+    g = torch.Generator(device="cuda").manual_seed(8)
+    q = torch.randn(bs, G, Lq, hq, d, device=dev(), generator=g).to(BF)
+    k = torch.randn(bs, Lkv, hkv, d, device=dev(), generator=g).to(BF)
+    v = torch.randn(bs, Lkv, hkv, d, device=dev(), generator=g).to(BF)
+    out, lse = prefix_shared_attention(q, k, v, return_lse=True)
+    sync_and_check()
+    ref, rl = prefix_shared_attention(q.cpu(), k.cpu(), v.cpu(), return_lse=True)
+    assert (out.float().cpu() - ref.float()).abs().max().item() < 0.02
+    assert (lse.cpu() - rl).abs().max().item() < 1e-2
+    # packing the samples into shared tiles does not change a row: one sample alone gives the same bits
+    one = prefix_shared_attention(q[:, 3:4].contiguous(), k, v)
+    sync_and_check()
+    assert torch.equal(one[:, 0], out[:, 3])
