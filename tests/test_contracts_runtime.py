@@ -86,3 +86,21 @@ def test_semantic_session_fails_closed():
     with pytest.raises(KeyError):
         s.observe("attention", "unknown-backend")
     assert s.readback()["records"]
+
+
+def test_profiler_reports_blocked_without_a_gpu_and_serialises(tmp_path):
+    import json
+
+    import torch
+
+    from rl_kernel_b200.benchmarks.common import PerformanceProfiler, WORKLOAD_REGISTRY
+
+    assert {"det_gemm_4096x12288x4096", "attention_fwd_8x1536", "linear_logp_fwd_4096x151936"} <= set(WORKLOAD_REGISTRY)
+    if torch.cuda.is_available():
+        return
+    prof = PerformanceProfiler(device=torch.device("cpu"), iters=1)
+    r = prof.run("rmsnorm_fwd_12288x4096")
+    assert r.status == "blocked" and "CUDA" in r.reason
+    out = json.loads(prof.to_json(str(tmp_path / "p.json")))
+    assert out[0]["name"] == "rmsnorm_fwd_12288x4096" and out[0]["ms"] is None
+    prof.to_csv(str(tmp_path / "p.csv"))
