@@ -498,3 +498,11 @@ def moe_zero_pad(loc, buf) -> None:
                                  c_int(buf.shape[1]), ext.stream_ptr(buf.device))
     ext.check(rc, "moe_zero_pad")
     _count()
+
+
+def sumsq_bins_f32(grad, bins) -> None:
+    """Exact fp32 sum of squares: ``bins`` int64 [768] (three 16-bit limbs per exponent)."""
+    assert grad.dtype == torch.float32 and bins.dtype == torch.int64 and bins.numel() == 768
+    rc = _lib().rlk_sumsq_bins_f32(ext.ptr(grad), _ll(grad.numel()), ext.ptr(bins), ext.stream_ptr(grad.device))
+    ext.check(rc, "sumsq_bins_f32")
+    _count()

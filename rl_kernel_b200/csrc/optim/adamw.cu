@@ -130,6 +130,54 @@ sumsq_bins_kernel(const __nv_bfloat16* __restrict__ g, long long n, unsigned lon
   spill();
 }
 
+// fp32 inputs: a finite value is m * 2^(e - 150) with an integer m < 2^24, so m^2 < 2^48 is split
+// into three 16-bit limbs and every (exponent, limb) pair gets its own integer bin (768 bins):
+// bins[3 e + l] += limb_l(m^2).  Still exact and order-free; the caller folds the limbs back with
+// weights 2^(16 l) * 2^(2 (max(e, 1) - 150)).  bins[3 * 255] counts non-finite inputs.
+__global__ void __launch_bounds__(256)
+sumsq_bins_f32_kernel(const float* __restrict__ g, long long n, unsigned long long* bins) {
+  __shared__ uint32_t sh[4][768];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t* hist = sh[warp >> 1];   // two warps share one histogram (shared atomics make that safe)
+  for (int k = threadIdx.x; k < 4 * 768; k += 256) (&sh[0][0])[k] = 0u;
+  __syncthreads();
+  auto add = [&](uint32_t u) {
+    const uint32_t e = (u >> 23) & 0xff;
+    if (e == 0xff) { atomicAdd(&hist[3 * 255], 1u); return; }
+    unsigned long long m = u & 0x7fffffu;
+    if (e != 0) m |= 0x800000u;
+    if (m == 0) return;
+    const unsigned long long sq = m * m;
+    atomicAdd(&hist[3 * e], static_cast<uint32_t>(sq & 0xffffu));
+    atomicAdd(&hist[3 * e + 1], static_cast<uint32_t>((sq >> 16) & 0xffffu));
+    atomicAdd(&hist[3 * e + 2], static_cast<uint32_t>(sq >> 32));
+  };
+  auto spill = [&]() {
+    __syncthreads();
+    for (int k = threadIdx.x; k < 4 * 768; k += 256) {
+      const uint32_t v = (&sh[0][0])[k];
+      if (v) {
+        atomicAdd(&bins[k % 768], static_cast<unsigned long long>(v));
+        (&sh[0][0])[k] = 0u;
+      }
+    }
+    __syncthreads();
+  };
+  const uint32_t* u = reinterpret_cast<const uint32_t*>(g);
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  int since = 0;
+  // block-uniform trip count: every thread of the block reaches every spill
+  for (long long base = static_cast<long long>(blockIdx.x) * blockDim.x; base < n; base += stride) {
+    const long long i = base + threadIdx.x;
+    if (i < n) add(u[i]);
+    if (++since == 512) {    // 512 iterations x 64 lanes x limbs < 2^16 stays below 2^31 per bin
+      since = 0;
+      spill();
+    }
+  }
+  spill();
+}
+
 }  // namespace rlk
 using namespace rlk;
 
@@ -157,6 +205,18 @@ RLK_API int rlk_sumsq_bins(const void* grad, long long n, unsigned long long* bi
   if (blocks > 148 * 8) blocks = 148 * 8;
   sumsq_bins_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)grad, n, bins);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+// fp32 form: bins is 768 x uint64 (zeroed by the caller), bins[3 e + l] += limb l (16 bits) of the
+// squared 24-bit significand of every element with biased exponent e; bins[765] counts inf / nan.
+// sum of squares = sum_{e,l} bins[3 e + l] * 2^(16 l) * 2^(2 * (max(e,1) - 150)).
+RLK_API int rlk_sumsq_bins_f32(const float* grad, long long n, unsigned long long* bins, void* stream) {
+  RLK_REQUIRE(n > 0, "sumsq_bins_f32: empty");
+  long long blocks = (n + 256 * 32 - 1) / (256 * 32);
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  sumsq_bins_f32_kernel<<<static_cast<unsigned>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(grad, n, bins);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

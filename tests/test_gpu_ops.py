@@ -333,3 +333,16 @@ def test_indexed_logp_and_lse_gradient():
     sync_and_check()
     assert (lse.detach() - torch.logsumexp(z, -1).detach()).abs().max().item() < 1e-3
     assert (logits.grad.float() - ref.grad).abs().max().item() < 0.02
+
+
+def test_exact_fp32_sum_of_squares_matches_cpu_bins():
+    from rl_kernel_b200.ops.norm.reproducible import norm_from_bins_f32, sumsq_bins_f32
+
+    x = torch.randn(300001, device=dev()) * 5
+    x[7], x[8] = 1e-41, 0.0
+    gpu = sumsq_bins_f32([x[:1000], x[1000:170001], x[170001:]])
+    sync_and_check()
+    cpu = sumsq_bins_f32([x.cpu()])
+    assert torch.equal(gpu.cpu(), cpu), "integer bins must be exact and independent of the partition"
+    ref = x.double().pow(2).sum().sqrt().item()
+    assert abs(norm_from_bins_f32(gpu).item() - ref) <= 1e-12 * ref
