@@ -6,8 +6,9 @@ optimizer) tokens/s, with the train-vs-rollout log-prob mismatch count.
         --master-port P bench.py --gpus N --steps K --warmup W
     python bench.py --impl reference ...     # the unmodified reference from baseline/_ref
 
-Weak scaling: every GPU brings 8 prompts x group 8 x (512 + 1024) tokens; N = 2 and 4 run one
-TP-N replica, N = 8 trains TP4 x CP2 and rolls out on two TP4 engines (``parallel_plan``).  Data is synthetic (uniform-random prompt ids,
+Weak scaling: every GPU brings 8 prompts x group 8 x (512 + 1024) tokens.  Default layout: data
+parallel (one whole-model replica per GPU); ``--plan tp4xcp2`` etc. select tensor / context
+parallel layouts (``parallel_plan``).  Data is synthetic (uniform-random prompt ids,
 Bernoulli(0.5) rewards), weights are random-init N(0, 0.02) of the official architecture.
 One JSON line is printed by rank 0.
 """
@@ -76,22 +77,30 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def parse_plan(text: str) -> dict:
+    """"tp4xcp2", "dp8", "tp2xdp4" ... -> {"tp": .., "cp": .., "dp": ..}."""
+    plan = {"tp": 1, "cp": 1, "dp": 1}
+    for part in text.lower().split("x"):
+        for key in plan:
+            if part.startswith(key):
+                plan[key] = int(part[len(key):])
+                break
+        else:
+            raise SystemExit(f"cannot parse plan component {part!r}")
+    plan["name"] = "x".join(f"{k}{plan[k]}" for k in ("tp", "cp", "dp") if plan[k] > 1) or "tp1"
+    return plan
+
+
 def parallel_plan(n: int, override: str = "") -> dict:
-    """TP inside a replica; at 8 GPUs the training replica is TP4 x CP2 and rollout runs two TP4
-    engines (the reference's headline topology).  ``override`` ("tp2xcp2") is a debugging aid."""
-    if override:
-        tp, _, cp = override.lower().removeprefix("tp").partition("xcp")
-        tp, cp = int(tp), int(cp or 1)
-        if tp * cp != n:
-            raise SystemExit(f"--plan {override} does not use {n} GPUs")
-        return {"tp": tp, "cp": cp, "name": f"tp{tp}" + (f"xcp{cp}" if cp > 1 else "")}
-    if n == 1:
-        return {"tp": 1, "cp": 1, "name": "tp1"}
-    if n in (2, 4):
-        return {"tp": n, "cp": 1, "name": f"tp{n}"}
-    if n == 8:
-        return {"tp": 4, "cp": 2, "name": "tp4xcp2"}
-    raise SystemExit(f"--gpus must be 1, 2, 4 or 8 (got {n})")
+    """Default: data parallel.  A B200 holds the whole 8B model with its optimizer state (about
+    150 GB), so every GPU rolls out and trains its own 8 prompts x 8 samples and the only
+    collective of a step is the gradient all-reduce -- the layout that keeps per-GPU work and
+    per-GPU efficiency constant as N grows.  ``--plan tp4xcp2`` runs the layout the reference
+    needs on 80 GB parts (tensor parallel 4 x context parallel 2, two TP4 rollout engines)."""
+    plan = parse_plan(override) if override else {"tp": 1, "cp": 1, "dp": n, "name": f"dp{n}" if n > 1 else "tp1"}
+    if plan["tp"] * plan["cp"] * plan["dp"] != n:
+        raise SystemExit(f"plan {plan['name']} does not use {n} GPUs")
+    return plan
 
 
 def run_ours(args) -> dict:
@@ -113,7 +122,7 @@ def run_ours(args) -> dict:
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     plan = parallel_plan(args.gpus, args.plan)
-    ctx = build_parallel_context(plan["tp"], plan["cp"], dev)
+    ctx = build_parallel_context(plan["tp"], plan["cp"], dev, dp=plan["dp"])
 
     spec = Qwen3DenseSpec.official()
     if args.layers:
@@ -140,6 +149,7 @@ def run_ours(args) -> dict:
         nonlocal mismatches, mism_tokens
         dev_prompts.copy_(host_prompts[i], non_blocking=True)                      # H2D
         out = trainer.step(trainer.local_prompts(dev_prompts), step_index=i)
+        # raw-bit comparison of this replica's sequences (every rank of a replica holds the same values)
         mm = (out["train_logp"].view(torch.int32) != out["old_logp"].view(torch.int32)).sum()
         res = torch.cat([out["loss_sums"][:4].float(), out["grad_norm"].float(), mm.float().reshape(1),
                          torch.zeros(2, device=dev)])
@@ -173,10 +183,14 @@ def run_ours(args) -> dict:
     dev_ms = ev0.elapsed_time(ev1)
     clocks = sampler.stop() if rank == 0 else {}
     launches = nv.LAUNCH_COUNT - n0
-    t = torch.tensor([dev_ms, wall * 1e3, float(mismatches)], dtype=torch.float64, device=dev)
+    t = torch.tensor([dev_ms, wall * 1e3], dtype=torch.float64, device=dev)
+    cnt = torch.tensor([float(mismatches), float(mism_tokens)], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    dev_ms, wall_ms, mismatches = float(t[0]), float(t[1]), int(t[2])
+        dist.all_reduce(cnt, op=dist.ReduceOp.SUM)      # summed over replicas ...
+    per_replica = plan["tp"] * plan["cp"]               # ... every rank of a replica counted the same tokens
+    dev_ms, wall_ms = float(t[0]), float(t[1])
+    mismatches, mism_tokens = int(cnt[0]) // per_replica, int(cnt[1]) // per_replica
     ms_per_step = dev_ms / args.steps
     value = tokens_per_step / (ms_per_step / 1e3)
     result = {
@@ -191,7 +205,7 @@ def run_ours(args) -> dict:
                    "l2_policy": "inputs larger than L2 (16 GB of weights stream every pass)",
                    "includes": "weight publish, prefill, CUDA-graph decode+sampling, reference-policy scoring, "
                                "train fwd/bwd with recompute, exact grad-norm clip, AdamW"},
-        "logp_mismatch_count": mismatches, "logp_tokens_compared": mism_tokens * (1 if world == 1 else 1),
+        "logp_mismatch_count": mismatches, "logp_tokens_compared": mism_tokens,
         "clocks": clocks,
         "e2e": {"value": tokens_per_step * args.steps / (wall_ms / 1e3), "unit": "tokens/s",
                 "h2d_bytes_per_step": int(dev_prompts.numel() * 8), "d2h_bytes_per_step": int(host_result.numel() * 4),

@@ -35,8 +35,9 @@ class ParallelContext:
         self.cp_rank, self.cp_size = cp_rank, cp_size
         self.collective = collective        # fixed-order TP collective (all_reduce_, all_gather)
         self.cp_collective = cp_collective
-        self.dp_size = 1                    # independent rollout engines (training always uses all ranks)
-        self.tp_group = self.cp_group = None
+        # data parallel replicas (each trains its own sequences; gradients are summed over them)
+        self.dp_rank, self.dp_size, self.dp_collective = 0, 1, None
+        self.tp_group = self.cp_group = self.dp_group = None
 
     def tp_all_reduce_(self, x: torch.Tensor) -> torch.Tensor:
         if self.tp_size > 1:
@@ -805,6 +806,10 @@ class Qwen3Engine:
         v = [flat[(2 * l + 1) * n:(2 * l + 2) * n].view(nseq * max_len, self.p.kv_local) for l in range(L)]
         return KVCache(k, v, nseq, max_len, flat)
 
+    def shared_prefix_cache_bytes(self, num_prompts: int, group: int, prompt_len: int, resp_len: int) -> int:
+        rows = num_prompts * prompt_len + num_prompts * group * ((resp_len + 127) // 128 * 128)
+        return 2 * self.spec.num_hidden_layers * rows * self.p.kv_local * 2
+
     def new_shared_prefix_cache(self, num_prompts: int, group: int, prompt_len: int, resp_len: int,
                                 storage: torch.Tensor | None = None) -> SharedPrefixKV:
         """Pool for ``num_prompts * group`` sequences whose first ``prompt_len`` keys (a multiple of
@@ -819,6 +824,8 @@ class Qwen3Engine:
         n = rows * self.p.kv_local
         if storage is None:
             storage = torch.zeros(2 * L * n * 2, dtype=torch.uint8, device=self.dev)
+        if storage.numel() < 2 * L * n * 2:
+            raise ValueError(f"storage holds {storage.numel()} bytes, the pool needs {2 * L * n * 2}")
         flat = storage[: 2 * L * n * 2].view(BF16)
         flat.zero_()
         k = [flat[(2 * l) * n:(2 * l + 1) * n].view(rows, self.p.kv_local) for l in range(L)]

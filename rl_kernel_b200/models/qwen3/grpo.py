@@ -123,11 +123,16 @@ class GRPOTrainer:
         tp_r, tp = self.ctx.tp_rank, self.ctx.tp_size
         # Context parallelism applies to training only.  For rollout the cp TP groups act as cp
         # independent engines, each generating for its share of the prompts.
-        self.cp = self.ctx.cp_size
-        if cfg.num_prompts % self.cp or cfg.micro_batch_seqs < 1:
-            raise ValueError(f"num_prompts {cfg.num_prompts} must be a multiple of the context-parallel size {self.cp}")
-        self.roll_prompts = cfg.num_prompts // self.cp
+        # Data parallelism: ``cfg.num_prompts`` counts the whole job; a replica (one TP x CP group)
+        # rolls out and trains num_prompts / dp of them and the gradients are summed over replicas.
+        self.cp, self.dp = self.ctx.cp_size, self.ctx.dp_size
+        if cfg.num_prompts % (self.cp * self.dp) or cfg.micro_batch_seqs < 1:
+            raise ValueError(f"num_prompts {cfg.num_prompts} must be a multiple of cp x dp = {self.cp * self.dp}")
+        self.rep_prompts = cfg.num_prompts // self.dp          # prompts of this replica
+        self.rep_seqs = self.rep_prompts * cfg.group_size
+        self.roll_prompts = self.rep_prompts // self.cp        # prompts of this rollout engine
         self.roll_seqs = self.roll_prompts * cfg.group_size
+        self.engine_index = self.ctx.dp_rank * self.cp + self.ctx.cp_rank   # which rollout engine this is
         self.rollout_ctx = self.ctx if self.cp == 1 else ParallelContext(tp_r, tp, collective=self.ctx.collective)
         self.policy = PackedParams(spec, tp_r, tp, device, with_grad=True)
         if weights is not None:
@@ -146,6 +151,9 @@ class GRPOTrainer:
         self.rollout_params = self.policy if cfg.share_rollout_weights else PackedParams(spec, tp_r, tp, device)
         self.rollout_engine = Qwen3Engine(spec, self.rollout_params, self.rollout_ctx, max_positions=cfg.seq_len + 8)
         kv_bytes = self.rollout_engine.kv_cache_bytes(self.roll_seqs, cfg.seq_len)
+        if cfg.share_prompt_pages and cfg.prompt_len % 128 == 0:
+            kv_bytes = max(kv_bytes, self.rollout_engine.shared_prefix_cache_bytes(
+                self.roll_prompts, cfg.group_size, cfg.prompt_len, cfg.response_len))
         self._arena = None
         if cfg.share_kv_and_activation_memory:
             self._arena = torch.zeros(kv_bytes, dtype=torch.uint8, device=device)
@@ -162,7 +170,7 @@ class GRPOTrainer:
     def local_prompts(self, prompts: torch.Tensor) -> torch.Tensor:
         """The slice of the global prompt batch this rank's rollout engine generates for."""
         n = self.roll_prompts
-        return prompts[self.ctx.cp_rank * n:(self.ctx.cp_rank + 1) * n]
+        return prompts[self.engine_index * n:(self.engine_index + 1) * n]
 
     # ---------------------------------------------------------------- weight sync
     def publish_weights(self) -> int:
@@ -194,7 +202,7 @@ class GRPOTrainer:
             # sampling keys are global sequence numbers: the draw of a sequence does not depend on
             # which rollout engine generated it
             self._seq_key = (torch.arange(B, dtype=torch.int64, device=self.dev)
-                             + self.ctx.cp_rank * B) * 65536
+                             + self.engine_index * B) * 65536
             self._out_tok = torch.zeros(B, c.response_len, dtype=torch.int64, device=self.dev)
             self._out_lp = torch.zeros(B, c.response_len, dtype=torch.float32, device=self.dev)
             self._col = torch.zeros(1, dtype=torch.int64, device=self.dev)
@@ -318,7 +326,7 @@ class GRPOTrainer:
     # ---------------------------------------------------------------- one full step
     def step(self, prompts: torch.Tensor, rewards_fn=None, step_index: int = 0) -> dict:
         c = self.cfg
-        B, R = c.num_seqs, c.response_len
+        B, R = self.rep_seqs, c.response_len          # sequences this replica trains on
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
         ev[0].record()
         self.publish_weights()
@@ -327,17 +335,19 @@ class GRPOTrainer:
         ev[1].record()
         if rewards_fn is None:
             gen = torch.Generator(device=self.dev).manual_seed(c.seed + step_index)
-            rewards = torch.bernoulli(torch.full((B,), 0.5, device=self.dev), generator=gen)
+            # drawn for the whole job, then cut: a sequence's reward does not depend on the layout
+            rewards = torch.bernoulli(torch.full((c.num_seqs,), 0.5, device=self.dev), generator=gen)
+            rewards = rewards[self.ctx.dp_rank * B:(self.ctx.dp_rank + 1) * B]
         else:
             rewards = rewards_fn(tokens).float()
-        adv = nv.group_advantages(rewards.contiguous(), c.num_prompts, c.group_size, 1e-6)
+        adv = nv.group_advantages(rewards.contiguous(), self.rep_prompts, c.group_size, 1e-6)
         _, ridx = self.engine.response_index(c.seq_len, c.prompt_len)   # response columns of this rank
         Rl = ridx.numel()
         mask = torch.ones(B, Rl, dtype=torch.uint8, device=self.dev)
         old_local = old_logp if self.cp == 1 else old_logp[:, ridx].contiguous()
         ref_logp = self.score(self.ref_params, tokens) if self.ref_params is not None else None
         ev[2].record()
-        total_active = float(B * R)
+        total_active = float(c.num_seqs * R)          # the loss is normalised over the whole job
         self.policy.grad.zero_()
         train_logp = torch.empty(B, Rl, dtype=torch.float32, device=self.dev)
         loss_terms = []
@@ -370,6 +380,10 @@ class GRPOTrainer:
                 m = gi[r] >= 0
                 train_logp[:, gi[r][m]] = gp[r][:, m]
             tot = self.ctx.cp_collective.all_gather(tot.contiguous()).sum(0)
+        if self.dp > 1:
+            # replicas saw different sequences: sum their gradients in the collective's fixed tree
+            self.ctx.dp_collective.all_reduce_(self.policy.grad)
+            tot = self.ctx.dp_collective.all_gather(tot.contiguous()).sum(0)
         ev[3].record()
         self.opt.step()
         ev[4].record()

@@ -1,5 +1,6 @@
 """Builds the ParallelContext of this process from the torch.distributed world: ranks are laid out
-TP-fastest ([cp][tp]), so TP peers are adjacent GPUs and CP peers are ``tp`` apart."""
+TP-fastest ([dp][cp][tp]), so TP peers are adjacent GPUs, CP peers are ``tp`` apart and data
+parallel replicas ``tp * cp`` apart."""
 from __future__ import annotations
 
 import torch
@@ -7,28 +8,39 @@ import torch
 from rl_kernel_b200.models.qwen3.engine import ParallelContext
 
 
-def build_parallel_context(tp: int, cp: int, device: torch.device) -> ParallelContext:
+def build_parallel_context(tp: int, cp: int, device: torch.device, dp: int = 1) -> ParallelContext:
     import torch.distributed as dist
 
-    if tp * cp == 1 or not dist.is_initialized():
+    if tp * cp * dp == 1 or not dist.is_initialized():
         return ParallelContext()
     world, rank = dist.get_world_size(), dist.get_rank()
-    if world != tp * cp:
-        raise ValueError(f"world {world} != tp {tp} x cp {cp}")
+    if world != tp * cp * dp:
+        raise ValueError(f"world {world} != tp {tp} x cp {cp} x dp {dp}")
     from rl_kernel_b200.distributed import create_deterministic_collective
 
-    tp_rank, cp_rank = rank % tp, rank // tp
-    tp_group = cp_group = None
+    tp_rank, cp_rank, dp_rank = rank % tp, (rank // tp) % cp, rank // (tp * cp)
+    tp_group = cp_group = dp_group = None
+    # every rank must create every group, in the same order
+    for d in range(dp):
+        for c in range(cp):
+            g = dist.new_group([d * tp * cp + c * tp + t for t in range(tp)]) if tp > 1 else None
+            if d == dp_rank and c == cp_rank:
+                tp_group = g
+    for d in range(dp):
+        for t in range(tp):
+            g = dist.new_group([d * tp * cp + c * tp + t for c in range(cp)]) if cp > 1 else None
+            if d == dp_rank and t == tp_rank:
+                cp_group = g
     for c in range(cp):
-        g = dist.new_group(list(range(c * tp, (c + 1) * tp)))
-        if c == cp_rank:
-            tp_group = g
-    for t in range(tp):
-        g = dist.new_group([t + c * tp for c in range(cp)])
-        if t == tp_rank:
-            cp_group = g
+        for t in range(tp):
+            g = dist.new_group([d * tp * cp + c * tp + t for d in range(dp)]) if dp > 1 else None
+            if c == cp_rank and t == tp_rank:
+                dp_group = g
     coll = create_deterministic_collective(tp_group, device) if tp > 1 else None
     cp_coll = create_deterministic_collective(cp_group, device) if cp > 1 else None
     ctx = ParallelContext(tp_rank, tp, cp_rank, cp, coll, cp_coll)
-    ctx.tp_group, ctx.cp_group = tp_group, cp_group
+    ctx.tp_group, ctx.cp_group, ctx.dp_group = tp_group, cp_group, dp_group
+    if dp > 1:
+        ctx.dp_rank, ctx.dp_size = dp_rank, dp
+        ctx.dp_collective = create_deterministic_collective(dp_group, device)
     return ctx

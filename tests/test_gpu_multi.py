@@ -523,3 +523,53 @@ def test_pipeline_two_stages_match_single_gpu_bitwise(tmp_path):
             assert torch.equal(g, params.g[name].cpu()), name
             seen.add(name)
     assert seen == set(params.g)
+
+
+def _dp_worker(rank, world, port, out):
+    dist = _init(rank, world, port)
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
+    from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context
+
+    dev = torch.device("cuda", rank)
+    spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+    w = Qwen3DenseWeights.synthetic(spec, seed=3)
+    ctx = build_parallel_context(1, 1, dev, dp=world)
+    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=48, micro_batch_seqs=2, lr=1e-4)
+    tr = GRPOTrainer(spec, cfg, dev, ctx=ctx, weights=w)
+    prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5)).to(dev)
+    res = tr.step(tr.local_prompts(prompts), step_index=0)
+    torch.cuda.synchronize(dev)
+    mine = {k: res[k].cpu() for k in ("tokens", "old_logp", "train_logp", "grad_norm", "rewards")}
+    mine["w"] = tr.policy.w["l1.wqkv"].cpu()
+    gathered = [None] * world
+    dist.all_gather_object(gathered, mine)
+    if rank == 0:
+        torch.save(gathered, out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_data_parallel_replicas_match_single_gpu(tmp_path):
+    """Two whole-model replicas, each rolling out and training its own prompts: sequences and
+    log-probs equal the single-GPU run bit for bit, the summed gradient agrees to rounding and both
+    replicas end the step with identical weights."""
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
+
+    out = str(tmp_path / "dp.pt")
+    mp.spawn(_dp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    dp = torch.load(out)
+    dev = torch.device("cuda:0")
+    spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+    w = Qwen3DenseWeights.synthetic(spec, seed=3)
+    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=48, micro_batch_seqs=2, lr=1e-4)
+    tr = GRPOTrainer(spec, cfg, dev, weights=w)
+    prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5)).to(dev)
+    one = tr.step(prompts, step_index=0)
+    for key in ("tokens", "old_logp", "train_logp", "rewards"):
+        assert torch.equal(torch.cat([r[key] for r in dp]), one[key].cpu()), key
+    assert torch.equal(dp[0]["train_logp"], dp[0]["old_logp"])
+    assert torch.equal(dp[0]["w"], dp[1]["w"])
+    assert torch.equal(dp[0]["grad_norm"], dp[1]["grad_norm"])
+    assert abs(float(dp[0]["grad_norm"]) - float(one["grad_norm"])) <= 2e-2 * float(one["grad_norm"])
