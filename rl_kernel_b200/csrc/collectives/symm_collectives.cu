@@ -136,6 +136,117 @@ all_reduce_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsi
   }
 }
 
+// Publish / wait for a single flag word of one slice (thread 0 of the CTA does the memory ops).
+__device__ __forceinline__ void slice_publish(const SymmWorld& w, int slice, unsigned long long seq) {
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < w.world && threadIdx.x != w.rank)
+    st_release_sys_u64(flag_ptr(w.win[threadIdx.x], w.rank, slice), seq);
+}
+// Wait until flag[src][slice] of this rank's window reaches seq, for every src with bit set in mask.
+__device__ __forceinline__ bool slice_wait(const SymmWorld& w, int slice, unsigned long long seq, unsigned mask,
+                                           int* status, int code) {
+  __shared__ int ok2;
+  if (threadIdx.x == 0) ok2 = 1;
+  __syncthreads();
+  if (threadIdx.x < w.world && ((mask >> threadIdx.x) & 1u)) {
+    const unsigned long long* f = flag_ptr(w.win[w.rank], threadIdx.x, slice);
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t it = 0;
+    while (ld_acquire_sys_u64(f) < seq) {
+      if ((++it & 63) == 0 && globaltimer_ns() - t0 > RLK_WAIT_LIMIT_NS) {
+        ok2 = 0;
+        if (status) atomicCAS(status, 0, code);
+        break;
+      }
+    }
+  }
+  __syncthreads();
+  return ok2 != 0;
+}
+
+// Two-shot all-reduce for large payloads: slice s is reduced by its owner (rank s % world) alone --
+// it reads the other ranks' partials of that slice, runs the same balanced tree as the one-shot
+// kernel, keeps the result in its own frame -- and the other ranks then copy the finished slice.
+// Every rank moves 2 (W-1)/W of the payload over NVLink instead of (W-1) times the payload, and
+// every element still sees exactly the tree ((r0+r1)+(r2+r3))+..., so the bits equal the one-shot
+// kernel's.  Uses two flag values: seq_a = "my partial of this slice is in my frame",
+// seq_b = "the reduced slice is in the owner's frame".
+template <int DT, int W>
+__global__ void __launch_bounds__(kCollThreads)
+all_reduce_2shot_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                        long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int* status) {
+  const unsigned long long seq_a = effective_seq(w, base_seq), seq_b = seq_a + 1;
+  const int nslices = static_cast<int>((nbytes + slice_bytes - 1) / slice_bytes);
+  unsigned char* mine = frame_ptr(w.win[w.rank], w.frame_bytes, frame);
+  constexpr int U = 16 / W;   // independent 16-byte loads in flight per thread and rank
+  // ---- phase 1: stage my partial of every slice this CTA handles
+  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+    const long long off = static_cast<long long>(s) * slice_bytes;
+    const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), nbytes - off) / 16);
+    if (s % W != w.rank)   // the owner reads its own partial straight from src
+      for (int i = threadIdx.x; i < n16; i += blockDim.x)
+        reinterpret_cast<uint4*>(mine + off)[i] = reinterpret_cast<const uint4*>(src + off)[i];
+    slice_publish(w, s, seq_a);
+  }
+  // ---- phase 2: reduce the slices I own
+  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+    if (s % W != w.rank) continue;
+    const long long off = static_cast<long long>(s) * slice_bytes;
+    const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), nbytes - off) / 16);
+    if (slice_wait(w, s, seq_a, ((1u << W) - 1u) & ~(1u << w.rank), status, 404)) {
+      for (int i0 = threadIdx.x; i0 < n16; i0 += blockDim.x * U) {
+        uint4 v[U][W];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int i = i0 + u * blockDim.x;
+          if (i < n16) {
+#pragma unroll
+            for (int r = 0; r < W; ++r)
+              v[u][r] = (r == w.rank) ? reinterpret_cast<const uint4*>(src + off)[i]
+                                      : ld_peer_v4(frame_ptr(w.win[r], w.frame_bytes, frame) + off + 16ll * i);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int i = i0 + u * blockDim.x;
+          if (i < n16) {
+#pragma unroll
+            for (int n = W; n > 1; n >>= 1)
+#pragma unroll
+              for (int j = 0; j < n / 2; ++j) v[u][j] = tree_node<DT>(v[u][2 * j], v[u][2 * j + 1]);
+            reinterpret_cast<uint4*>(mine + off)[i] = v[u][0];
+            reinterpret_cast<uint4*>(dst + off)[i] = v[u][0];
+          }
+        }
+      }
+    }
+    slice_publish(w, s, seq_b);
+  }
+  // ---- phase 3: fetch the slices the others reduced
+  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+    const int owner = s % W;
+    if (owner == w.rank) continue;
+    const long long off = static_cast<long long>(s) * slice_bytes;
+    const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), nbytes - off) / 16);
+    if (!slice_wait(w, s, seq_b, 1u << owner, status, 405)) continue;
+    const unsigned char* pf = frame_ptr(w.win[owner], w.frame_bytes, frame) + off;
+    for (int i0 = threadIdx.x; i0 < n16; i0 += blockDim.x * 8) {
+      uint4 q[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < n16) q[u] = ld_peer_v4(pf + 16ll * i);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int i = i0 + u * blockDim.x;
+        if (i < n16) reinterpret_cast<uint4*>(dst + off)[i] = q[u];
+      }
+    }
+  }
+}
+
 // All-gather: dst[r] = rank r's payload (rank order).
 __global__ void __launch_bounds__(kCollThreads)
 all_gather_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
@@ -250,6 +361,12 @@ static int slice_bytes_for(long long nbytes) {
   while ((nbytes + sb - 1) / sb > 1024) sb *= 2;
   return static_cast<int>(sb);
 }
+constexpr long long kTwoShotMinBytes = 4ll << 20;
+static int coll_grid_large(long long nbytes) {
+  const long long sl = (nbytes + slice_bytes_for(nbytes) - 1) / slice_bytes_for(nbytes);
+  const int cap = 2 * sm_count();      // two CTAs per SM keep enough peer loads in flight
+  return static_cast<int>(sl < cap ? sl : cap);
+}
 static int coll_grid(long long nbytes) {
   const long long s = (nbytes + slice_bytes_for(nbytes) - 1) / slice_bytes_for(nbytes);
   const int cap = nbytes > (8 << 20) ? 128 : 64;  // small payloads: leave SMs to overlapping compute
@@ -264,11 +381,31 @@ RLK_API int rlk_symm_all_reduce(void* state, const void* src, void* dst, long lo
   RLK_REQUIRE(nbytes > 0 && nbytes % 16 == 0, "all_reduce: byte count must be a positive multiple of 16");
   RLK_REQUIRE(nbytes <= st->w.frame_bytes, "all_reduce: %lld bytes exceed the frame capacity %lld", nbytes, st->w.frame_bytes);
   RLK_REQUIRE(dtype == 0 || dtype == 1, "all_reduce: dtype must be 0 (bf16) or 1 (fp32)");
-  st->seq += 1;
-  const int frame = static_cast<int>(st->seq & 1);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const unsigned char* sp = static_cast<const unsigned char*>(src);
   unsigned char* dp = static_cast<unsigned char*>(dst);
+  if (!staged && nbytes >= kTwoShotMinBytes && st->w.world > 1) {
+    // large payload: reduce-scatter + all-gather over the same tree.  Three sequence numbers are
+    // consumed (two are used as flag values) so that consecutive calls keep alternating frames.
+    st->seq += 1;
+    const int frame2 = static_cast<int>(st->seq & 1);
+    const unsigned long long base = st->seq;
+    st->seq += 2;
+    const int sb = slice_bytes_for(nbytes);
+    const int grid = coll_grid_large(nbytes);
+    int* stw = device_status_word();
+#define RLK_LAUNCH_2SHOT(DT, WW) all_reduce_2shot_kernel<DT, WW><<<grid, kCollThreads, 0, s>>>(st->w, sp, dp, nbytes, sb, frame2, base, stw)
+    if (dtype == 0) {
+      if (st->w.world == 2) RLK_LAUNCH_2SHOT(0, 2); else if (st->w.world == 4) RLK_LAUNCH_2SHOT(0, 4); else RLK_LAUNCH_2SHOT(0, 8);
+    } else {
+      if (st->w.world == 2) RLK_LAUNCH_2SHOT(1, 2); else if (st->w.world == 4) RLK_LAUNCH_2SHOT(1, 4); else RLK_LAUNCH_2SHOT(1, 8);
+    }
+#undef RLK_LAUNCH_2SHOT
+    RLK_CHECK_CUDA(cudaGetLastError());
+    return RLK_OK;
+  }
+  st->seq += 1;
+  const int frame = static_cast<int>(st->seq & 1);
   if (dtype == 0)
     all_reduce_kernel<0><<<coll_grid(nbytes), kCollThreads, 0, s>>>(st->w, sp, dp, nbytes, slice_bytes_for(nbytes), frame, st->seq, staged, device_status_word());
   else
