@@ -24,21 +24,30 @@ def main() -> None:
     ap.add_argument("--max-len", type=int, default=1536)
     ap.add_argument("--iters", type=int, default=5)
     ap.add_argument("--graph", action="store_true")
+    ap.add_argument("--shared-prefix", type=int, default=0, metavar="P",
+                    help="the first P positions of every group of --group sequences are shared prompt pages")
+    ap.add_argument("--group", type=int, default=8)
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     spec = Qwen3DenseSpec.official().with_layers(a.layers)
     params = PackedParams(spec, 0, 1, dev).init_synthetic_(1)
     eng = Qwen3Engine(spec, params, max_positions=a.max_len + 8)
-    kv = eng.new_kv_cache(a.batch, a.max_len)
+    shared = None
+    if a.shared_prefix:
+        shared = eng.new_shared_prefix_cache(a.batch // a.group, a.group, a.shared_prefix, a.max_len - a.shared_prefix)
+        kv = shared.kv
+        tiles = eng.decode_tiles_shared_prefix(shared, a.group)
+    else:
+        kv = eng.new_kv_cache(a.batch, a.max_len)
+        tiles = eng.decode_tiles(a.batch, a.max_len)
     for t in kv.k + kv.v:
         t.normal_(0, 1)
-    tiles = eng.decode_tiles(a.batch, a.max_len)
     tok = torch.randint(0, spec.vocab_size, (a.batch,), device=dev)
     pos = torch.full((a.batch,), a.pos, dtype=torch.int32, device=dev)
     keys = torch.arange(a.batch, device=dev)
 
     def step():
-        hf = eng.decode_step(tok, pos, kv, tiles)
+        hf = eng.decode_step(tok, pos, kv, tiles, shared=shared)
         logits = eng.logits(hf)
         return eng.sample(logits, keys, temperature=1.0, seed=1)
 
@@ -51,7 +60,8 @@ def main() -> None:
         step()
     e.record()
     torch.cuda.synchronize()
-    out = {"layers": a.layers, "batch": a.batch, "pos": a.pos, "eager_ms_per_step": s.elapsed_time(e) / a.iters}
+    out = {"layers": a.layers, "batch": a.batch, "pos": a.pos, "shared_prefix": a.shared_prefix,
+           "eager_ms_per_step": s.elapsed_time(e) / a.iters}
     if a.graph:
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
