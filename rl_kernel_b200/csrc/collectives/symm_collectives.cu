@@ -247,7 +247,9 @@ all_reduce_2shot_kernel(const SymmWorld w, const unsigned char* __restrict__ src
   }
 }
 
-// All-gather: dst[r] = rank r's payload (rank order).
+// All-gather: dst[r] = rank r's payload (rank order).  Every CTA first stages and publishes all of
+// its slices, then pulls the peers' copies with eight 16-byte loads in flight per thread, so the
+// NVLink round trip is paid once per batch of loads instead of once per load.
 __global__ void __launch_bounds__(kCollThreads)
 all_gather_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
                   long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int* status) {
@@ -262,12 +264,30 @@ all_gather_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsi
       reinterpret_cast<uint4*>(mine + off)[i] = v;
       reinterpret_cast<uint4*>(dst + w.rank * nbytes + off)[i] = v;
     }
-    if (!slice_handshake(w, s, seq, status, 402)) continue;
+    slice_publish(w, s, seq);
+  }
+  const unsigned others = ((1u << w.world) - 1u) & ~(1u << w.rank);
+  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+    const long long off = static_cast<long long>(s) * slice_bytes;
+    const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), nbytes - off) / 16);
+    if (!slice_wait(w, s, seq, others, status, 402)) continue;
     for (int r = 0; r < w.world; ++r) {
       if (r == w.rank) continue;
       const unsigned char* pf = frame_ptr(w.win[r], w.frame_bytes, frame) + off;
-      for (int i = threadIdx.x; i < n16; i += blockDim.x)
-        reinterpret_cast<uint4*>(dst + r * nbytes + off)[i] = ld_peer_v4(pf + 16ll * i);
+      unsigned char* out = dst + r * nbytes + off;
+      for (int i0 = threadIdx.x; i0 < n16; i0 += blockDim.x * 8) {
+        uint4 q[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * blockDim.x;
+          if (i < n16) q[u] = ld_peer_v4(pf + 16ll * i);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int i = i0 + u * blockDim.x;
+          if (i < n16) reinterpret_cast<uint4*>(out)[i] = q[u];
+        }
+      }
     }
   }
 }
@@ -420,7 +440,7 @@ RLK_API int rlk_symm_all_gather(void* state, const void* src, void* dst, long lo
   RLK_REQUIRE(nbytes <= st->w.frame_bytes, "all_gather: %lld bytes exceed the frame capacity %lld", nbytes, st->w.frame_bytes);
   st->seq += 1;
   const int frame = static_cast<int>(st->seq & 1);
-  all_gather_kernel<<<coll_grid(nbytes), kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  all_gather_kernel<<<nbytes >= kTwoShotMinBytes ? coll_grid_large(nbytes) : coll_grid(nbytes), kCollThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       st->w, static_cast<const unsigned char*>(src), static_cast<unsigned char*>(dst), nbytes,
       slice_bytes_for(nbytes), frame, st->seq, device_status_word());
   RLK_CHECK_CUDA(cudaGetLastError());
