@@ -61,6 +61,8 @@ def load(required: bool = True) -> ctypes.CDLL | None:
                     f"{_LIB_PATH} has ABI {lib.rlk_abi_version()}, expected {ABI_VERSION}; rebuild "
                     "with `python -m rl_kernel_b200.csrc.build --force`"
                 )
+            if os.environ.get("RLK_PDL", "1") == "0":
+                lib.rlk_set_pdl(ctypes.c_int(0))     # programmatic dependent launch off
             _lib = lib
         except Exception as exc:  # noqa: BLE001 - reported below
             _load_error = f"{type(exc).__name__}: {exc}"

@@ -26,6 +26,12 @@ def _count(n: int = 1) -> None:
     LAUNCH_COUNT += n
 
 
+def set_pdl(on: bool) -> bool:
+    """Programmatic dependent launch for the library's kernel chains (on by default; the environment
+    variable RLK_PDL=0 turns it off at load).  Returns the previous setting."""
+    return bool(_lib().rlk_set_pdl(c_int(int(on))))
+
+
 def _bf16(t: torch.Tensor, name: str) -> torch.Tensor:
     if t.dtype != torch.bfloat16 or not t.is_cuda:
         raise TypeError(f"{name} must be a CUDA bf16 tensor, got {t.dtype} on {t.device}")

@@ -15,6 +15,7 @@ __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g))
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_gu, __nv_bfloat16* __restrict__ out,
                   long long ld_out, int rows, int I, int blk, const int* __restrict__ rows_limit) {
+  griddep_sync();
   const int per_row = I / 8;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(rows) * per_row) return;
@@ -77,8 +78,9 @@ RLK_API int rlk_swiglu_fwd_dyn(const void* gu, long long ld_gu, void* out, long 
               "swiglu: I and pitches must be multiples of 8");
   RLK_REQUIRE(blk > 0 && blk % 8 == 0 && I % blk == 0, "swiglu: blk must divide I and be a multiple of 8");
   const long long n = static_cast<long long>(rows) * (I / 8);
-  swiglu_fwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)out, ld_out, rows, I, blk, rows_limit);
+  RLK_CHECK_CUDA(launch_pdl(swiglu_fwd_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0,
+                            static_cast<cudaStream_t>(stream), (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)out,
+                            ld_out, rows, I, blk, rows_limit));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

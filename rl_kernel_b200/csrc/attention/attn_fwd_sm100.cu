@@ -91,6 +91,7 @@ template <int NSRC>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ KvMaps<NSRC> kv,
                 const AttnFwdParams p) {
+  griddep_sync();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -339,7 +340,7 @@ static int launch_attn_fwd(const CUtensorMap& tmQ, const KvMaps<NSRC>& kv, const
                                         AttnFwdSmem::kBytes));
     attr_set[dev & 63] = true;
   }
-  kfn<<<p.n_tiles, kAttnThreads, AttnFwdSmem::kBytes, stream>>>(tmQ, kv, p);
+  RLK_CHECK_CUDA(launch_pdl(kfn, dim3(p.n_tiles), dim3(kAttnThreads), AttnFwdSmem::kBytes, stream, tmQ, kv, p));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

@@ -15,6 +15,7 @@ __global__ void __launch_bounds__(128)
 embedding_fwd_kernel(const long long* __restrict__ ids, const __nv_bfloat16* __restrict__ w,
                      __nv_bfloat16* __restrict__ out, int T, int H, long long vocab_start,
                      long long vocab_rows) {
+  griddep_sync();
   const int t = blockIdx.x;
   const long long id = ids[t] - vocab_start;
   const bool mine = id >= 0 && id < vocab_rows;
@@ -62,8 +63,8 @@ using namespace rlk;
 RLK_API int rlk_embedding_fwd(const long long* ids, const void* w, void* out, int T, int H,
                               long long vocab_start, long long vocab_rows, void* stream) {
   RLK_REQUIRE(T > 0 && H % 8 == 0, "embedding: H must be a multiple of 8");
-  embedding_fwd_kernel<<<T, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      ids, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, T, H, vocab_start, vocab_rows);
+  RLK_CHECK_CUDA(launch_pdl(embedding_fwd_kernel, dim3(T), dim3(128), 0, static_cast<cudaStream_t>(stream), ids,
+                            (const __nv_bfloat16*)w, (__nv_bfloat16*)out, T, H, vocab_start, vocab_rows));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

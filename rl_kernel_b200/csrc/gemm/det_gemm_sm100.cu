@@ -112,6 +112,7 @@ template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const GemmParams p) {
+  griddep_sync();
   using S = GemmSmem<BN>;
   constexpr int kStages = S::kStages;
   // TMEM columns: two accumulators (+ three packed-bf16 tree levels when chunked, BN==128 only)
@@ -609,7 +610,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
                                         GemmSmem<BN>::kBytes));
     attr_set[dev & 63] = true;
   }
-  kfn<<<grid, kGemmThreads, smem_bytes, stream>>>(tmA, tmB, p);
+  RLK_CHECK_CUDA(launch_pdl(kfn, dim3(grid), dim3(kGemmThreads), smem_bytes, stream, tmA, tmB, p));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
@@ -618,6 +619,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
 __global__ void __launch_bounds__(256)
 chunk_tree_kernel(const __nv_bfloat16* __restrict__ leaves, long long chunk_stride,
                   __nv_bfloat16* __restrict__ out, int M, int N, long long ld, int nchunks) {
+  griddep_sync();
   const int per_row = N / 8;
   const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<long long>(M) * per_row) return;
@@ -752,8 +754,8 @@ RLK_API int rlk_det_gemm_split(const void* A, const void* B, void* C, void* scra
   else rc = launch_gemm<64, false, false>(A, B, p, lda, ldb, s);
   if (rc) return rc;
   const long long n = static_cast<long long>(M) * (N / 8);
-  chunk_tree_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(
-      static_cast<const __nv_bfloat16*>(scratch), p.split_stride, static_cast<__nv_bfloat16*>(C), M, N, ldc, nchunks);
+  RLK_CHECK_CUDA(launch_pdl(chunk_tree_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s,
+                            static_cast<const __nv_bfloat16*>(scratch), p.split_stride, static_cast<__nv_bfloat16*>(C), M, N, ldc, nchunks));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
@@ -850,8 +852,8 @@ RLK_API int rlk_det_gemm_split_static(const void* A, const void* B, void* C, int
   else rc = launch_gemm<64, false, false>(A, B, p, lda, ldb, s);
   if (rc) return rc;
   const long long n = static_cast<long long>(M) * (N / 8);
-  chunk_tree_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(
-      reinterpret_cast<const __nv_bfloat16*>(scratch), p.split_stride, static_cast<__nv_bfloat16*>(C), M, N, ldc, nchunks);
+  RLK_CHECK_CUDA(launch_pdl(chunk_tree_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s,
+                            reinterpret_cast<const __nv_bfloat16*>(scratch), p.split_stride, static_cast<__nv_bfloat16*>(C), M, N, ldc, nchunks));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

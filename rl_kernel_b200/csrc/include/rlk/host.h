@@ -50,4 +50,27 @@ int make_tmap_3d_sw128(CUtensorMap* out, const void* base, uint64_t batch, uint6
 
 int sm_count();
 
+// 1 when kernels that start with griddep_sync() are launched with programmatic stream
+// serialization (rlk_set_pdl); their launch latency then overlaps the previous kernel's execution.
+int pdl_enabled();
+
+#ifdef __CUDACC__
+// Launch for kernels whose first statement is griddep_sync() (rlk/ptx.cuh).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 }  // namespace rlk

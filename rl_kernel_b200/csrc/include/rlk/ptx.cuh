@@ -21,6 +21,16 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// Programmatic dependent launch.  A kernel launched with rlk::launch_pdl may be placed on the SMs
+// while the previous kernel of the stream is still running; griddep_sync() -- the first statement
+// of every such kernel -- blocks until that kernel has completed and its writes are visible, and
+// lets the NEXT kernel of the stream be placed in turn.  Without the launch attribute both
+// instructions do nothing.
+__device__ __forceinline__ void griddep_sync() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));

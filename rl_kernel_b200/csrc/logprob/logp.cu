@@ -18,6 +18,7 @@ logits_tile_stats_kernel(const __nv_bfloat16* __restrict__ logits, long long ld,
                          float2* __restrict__ stats, long long stats_row_stride, float* __restrict__ tgt_logit,
                          int rows, int n_local, long long vocab_start, int tile_start, int n_tiles_local,
                          float inv_temp, const long long* __restrict__ row_indices) {
+  griddep_sync();
   const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (gid >= static_cast<long long>(rows) * n_tiles_local) return;
   const int row = static_cast<int>(gid / n_tiles_local);
@@ -57,6 +58,7 @@ __global__ void __launch_bounds__(128)
 logp_merge_kernel(const float2* __restrict__ stats, long long stats_row_stride, int n_tiles,
                   const float* __restrict__ tgt_logit, float* __restrict__ logp, float* __restrict__ lse,
                   int rows) {
+  griddep_sync();
   const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
@@ -126,9 +128,10 @@ RLK_API int rlk_logits_tile_stats_indexed(const void* logits, long long ld, cons
   RLK_REQUIRE(vocab_start % kVocabTile == 0, "tile_stats: vocab_start must be a multiple of 128");
   const int n_tiles_local = (n_local + kVocabTile - 1) / kVocabTile;
   const long long n = static_cast<long long>(rows) * n_tiles_local;
-  logits_tile_stats_kernel<<<static_cast<unsigned>((n + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)logits, ld, targets, (float2*)stats, stats_row_stride, tgt_logit, rows,
-      n_local, vocab_start, static_cast<int>(vocab_start / kVocabTile), n_tiles_local, inv_temp, row_indices);
+  RLK_CHECK_CUDA(launch_pdl(logits_tile_stats_kernel, dim3(static_cast<unsigned>((n + 127) / 128)), dim3(128), 0,
+                            static_cast<cudaStream_t>(stream), (const __nv_bfloat16*)logits, ld, targets,
+                            (float2*)stats, stats_row_stride, tgt_logit, rows, n_local, vocab_start,
+                            static_cast<int>(vocab_start / kVocabTile), n_tiles_local, inv_temp, row_indices));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
@@ -143,8 +146,8 @@ RLK_API int rlk_logits_tile_stats(const void* logits, long long ld, const long l
 RLK_API int rlk_logp_merge(const void* stats, long long stats_row_stride, int n_tiles,
                            const float* tgt_logit, float* logp, float* lse, int rows, void* stream) {
   RLK_REQUIRE(rows > 0 && n_tiles > 0, "logp_merge: bad shape");
-  logp_merge_kernel<<<(rows + 3) / 4, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      (const float2*)stats, stats_row_stride, n_tiles, tgt_logit, logp, lse, rows);
+  RLK_CHECK_CUDA(launch_pdl(logp_merge_kernel, dim3((rows + 3) / 4), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                            (const float2*)stats, stats_row_stride, n_tiles, tgt_logit, logp, lse, rows));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

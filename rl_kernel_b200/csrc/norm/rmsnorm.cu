@@ -38,6 +38,7 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int rows,
                    int H, float eps) {
+  griddep_sync();
   __shared__ float swarp[4];
   const int row = blockIdx.x;
   const int tid = threadIdx.x;
@@ -228,6 +229,7 @@ struct QkRopeParams {
 };
 
 __global__ void __launch_bounds__(256) qk_norm_rope_fwd_kernel(const QkRopeParams p) {
+  griddep_sync();
   const int lane = threadIdx.x & 31;
   const int gw = blockIdx.x * 8 + (threadIdx.x >> 5);
   const int heads = p.Hq + 2 * p.Hkv;
@@ -378,13 +380,13 @@ RLK_API int rlk_rmsnorm_fwd(const void* x, const void* res, const void* w, void*
   const int grid = rows;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (res)
-    rmsnorm_fwd_kernel<true><<<grid, kRowThreads, 0, s>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
-        (__nv_bfloat16*)y, (__nv_bfloat16*)res_out, rstd_out, rows, H, eps);
+    RLK_CHECK_CUDA(launch_pdl(rmsnorm_fwd_kernel<true>, dim3(grid), dim3(kRowThreads), 0, s,
+                              (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
+                              (__nv_bfloat16*)y, (__nv_bfloat16*)res_out, rstd_out, rows, H, eps));
   else
-    rmsnorm_fwd_kernel<false><<<grid, kRowThreads, 0, s>>>(
-        (const __nv_bfloat16*)x, nullptr, (const __nv_bfloat16*)w, (__nv_bfloat16*)y, nullptr,
-        rstd_out, rows, H, eps);
+    RLK_CHECK_CUDA(launch_pdl(rmsnorm_fwd_kernel<false>, dim3(grid), dim3(kRowThreads), 0, s,
+                              (const __nv_bfloat16*)x, (const __nv_bfloat16*)nullptr, (const __nv_bfloat16*)w,
+                              (__nv_bfloat16*)y, (__nv_bfloat16*)nullptr, rstd_out, rows, H, eps));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
@@ -423,7 +425,8 @@ RLK_API int rlk_qk_norm_rope_fwd(const void* qkv, long long ld_qkv, const void* 
                  (__nv_bfloat16*)q_out, ld_q, (__nv_bfloat16*)k_out, (__nv_bfloat16*)v_out, ld_kv,
                  T, Hq, Hkv, eps, q_rstd, k_rstd};
   const long long warps = static_cast<long long>(T) * (Hq + 2 * Hkv);
-  qk_norm_rope_fwd_kernel<<<static_cast<int>((warps + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  RLK_CHECK_CUDA(launch_pdl(qk_norm_rope_fwd_kernel, dim3(static_cast<unsigned>((warps + 7) / 8)), dim3(256), 0,
+                            static_cast<cudaStream_t>(stream), p));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

@@ -117,7 +117,17 @@ int make_tmap_3d_sw128(CUtensorMap* out, const void* base, uint64_t batch, uint6
   return RLK_OK;
 }
 
+static int g_pdl = 1;
+int pdl_enabled() { return g_pdl; }
+
 }  // namespace rlk
+
+// Programmatic dependent launch for the library's kernel chains: 1 = on (default), 0 = off.
+RLK_API int rlk_set_pdl(int on) {
+  const int old = rlk::g_pdl;
+  rlk::g_pdl = on ? 1 : 0;
+  return old;
+}
 
 RLK_API const char* rlk_last_error() { return rlk::g_err; }
 

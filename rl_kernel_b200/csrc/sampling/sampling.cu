@@ -53,6 +53,7 @@ struct SampleParams {
 };
 
 __global__ void __launch_bounds__(256) sample_gumbel_kernel(const SampleParams p) {
+  griddep_sync();
   __shared__ float sval[256];
   __shared__ long long sidx[256];
   const int row = blockIdx.x / kSampleSegs, seg = blockIdx.x % kSampleSegs;
@@ -98,6 +99,7 @@ __global__ void __launch_bounds__(256) sample_gumbel_kernel(const SampleParams p
 }
 
 __global__ void sample_pick_kernel(const SampleParams p) {
+  griddep_sync();
   const int row = blockIdx.x * blockDim.x + threadIdx.x;
   if (row >= p.rows) return;
   float best = p.part_val[row * kSampleSegs];
@@ -252,9 +254,8 @@ RLK_API int rlk_sample_gumbel(const void* logits, long long ld, const float* min
   SampleParams p{(const __nv_bfloat16*)logits, ld, min_keep, row_keys, out_ids, out_val, part_val, part_id,
                  rows, n_local, vocab_start, inv_temp, seed, step, greedy};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  sample_gumbel_kernel<<<rows * kSampleSegs, 256, 0, s>>>(p);
-  RLK_CHECK_CUDA(cudaGetLastError());
-  sample_pick_kernel<<<(rows + 127) / 128, 128, 0, s>>>(p);
+  RLK_CHECK_CUDA(launch_pdl(sample_gumbel_kernel, dim3(rows * kSampleSegs), dim3(256), 0, s, p));
+  RLK_CHECK_CUDA(launch_pdl(sample_pick_kernel, dim3((rows + 127) / 128), dim3(128), 0, s, p));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
