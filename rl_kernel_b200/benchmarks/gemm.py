@@ -43,6 +43,7 @@ def main() -> None:
     ap.add_argument("--nchunks", type=int, default=1)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-cublas", action="store_true")
+    ap.add_argument("--tile-n", type=int, default=0, help="force the output tile width (0 = the kernel's own choice)")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     peaks = Path("MEASURED_PEAKS.json")
@@ -56,9 +57,9 @@ def main() -> None:
             scratch = torch.empty(a.nchunks * M * N, device=dev, dtype=torch.bfloat16)
             fn = lambda: nv.det_gemm_split(x, w, out, scratch, nchunks=a.nchunks)  # noqa: E731
         else:
-            fn = lambda: nv.det_gemm(x, w, out, M=M, N=N, K=K, nchunks=a.nchunks)  # noqa: E731
+            fn = lambda: nv.det_gemm(x, w, out, M=M, N=N, K=K, nchunks=a.nchunks, tile_n=a.tile_n)  # noqa: E731
         ms = bench(fn, a.iters, flush)
-        rec = {"M": M, "N": N, "K": K, "nchunks": a.nchunks, "det_gemm_ms": ms, "det_gemm_tflops": 2 * M * N * K / ms / 1e9,
+        rec = {"M": M, "N": N, "K": K, "nchunks": a.nchunks, "tile_n": a.tile_n, "det_gemm_ms": ms, "det_gemm_tflops": 2 * M * N * K / ms / 1e9,
                "frac_of_measured_cublas_peak": 2 * M * N * K / ms / 1e9 / peak, "weight_gbs": N * K * 2 / ms / 1e6}
         if not a.no_cublas:
             cms = bench(lambda: torch.matmul(x, w.t(), out=out), a.iters, flush)
