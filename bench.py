@@ -130,7 +130,9 @@ def run_ours(args) -> dict:
     # one training replica spans all GPUs; a micro-batch keeps micro_batch x seq_len tokens per rank
     cfg = GRPOConfig(num_prompts=PROMPTS_PER_GPU * args.gpus, group_size=GROUP,
                      prompt_len=PROMPT_LEN, response_len=args.response_len,
-                     micro_batch_seqs=args.micro_batch * plan["cp"], share_rollout_weights=True, seed=1234)
+                     micro_batch_seqs=args.micro_batch * plan["cp"], share_rollout_weights=True, seed=1234,
+                     store_activations=plan["cp"] == 1 and args.train_micro_batch > 0,
+                     train_micro_batch_seqs=args.train_micro_batch if plan["cp"] == 1 else 0)
     trainer = GRPOTrainer(spec, cfg, dev, ctx=ctx)
     n_prompts_global = PROMPTS_PER_GPU * args.gpus
     tokens_per_step = n_prompts_global * GROUP * (PROMPT_LEN + args.response_len)
@@ -202,6 +204,8 @@ def run_ours(args) -> dict:
                    "global_batch": n_prompts_global * GROUP, "seq_len": PROMPT_LEN + args.response_len,
                    "prompt_len": PROMPT_LEN, "response_len": args.response_len, "group_size": GROUP,
                    "parallelism": plan["name"], "micro_batch_seqs": args.micro_batch,
+                   "train_micro_batch_seqs": cfg.train_micro_batch_seqs or cfg.micro_batch_seqs,
+                   "activations": "stored" if cfg.store_activations else "per-layer recompute",
                    "l2_policy": "inputs larger than L2 (16 GB of weights stream every pass)",
                    "includes": "weight publish, prefill, CUDA-graph decode+sampling, reference-policy scoring, "
                                "train fwd/bwd with recompute, exact grad-norm clip, AdamW"},
@@ -227,6 +231,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the config)")
     ap.add_argument("--response-len", type=int, default=RESPONSE_LEN, help="debug only")
     ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--train-micro-batch", type=int, default=2,
+                    help="sequences per training micro-batch with stored activations (0 = recompute, --micro-batch)")
     ap.add_argument("--plan", default="", help="debug only: e.g. tp1xcp2 instead of the default plan for --gpus")
     args = ap.parse_args()
     if args.impl == "reference":

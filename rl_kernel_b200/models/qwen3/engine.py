@@ -238,7 +238,7 @@ class Workspace:
     before every rollout)."""
 
     def __init__(self, device, arena: torch.Tensor | None = None,
-                 arena_prefixes: tuple[str, ...] = ("f.", "r.", "b.", "lm.", "ckpt", "pos")):
+                 arena_prefixes: tuple[str, ...] = ("f.", "r.", "b.", "lm.", "ckpt", "pos", "act")):
         self.device = device
         self._bufs: dict[tuple, torch.Tensor] = {}
         self.arena, self.arena_prefixes, self._off = arena, arena_prefixes, 0
@@ -380,11 +380,15 @@ class Qwen3Engine:
     # -------------------------------------------------------------------------- layer forward
     def _layer_fwd(self, l: int, x, res, T: int, pos, *, tiles, kbuf, vbuf, kv_slot=None,
                    q_view=None, lse=None, s_in_out=None, keep: dict | None = None, tag: str = "f",
-                   cp_geom: tuple[int, int] | None = None):
+                   cp_geom: tuple[int, int] | None = None, store_tag: str | None = None):
         """One decoder layer.  ``x`` + ``res`` -> (mlp_out, s_mid).  When ``res`` is None, ``x`` is
-        already the residual stream.  ``keep`` receives the intermediates backward needs."""
+        already the residual stream.  ``keep`` receives the intermediates backward needs.
+        ``store_tag``: the tensors backward cannot cheaply rebuild (qkv, q, attention output, s_mid,
+        gate/up) go to buffers of their own under this tag instead of the shared scratch, so they
+        survive until this layer's backward."""
         w, ws, H = self.p.w, self.ws, self.spec.hidden_size
         eps = self.spec.rms_norm_eps
+        stag = store_tag or tag
         h = ws.get(f"{tag}.h", (T, H))
         if res is None:
             s_in = x
@@ -392,15 +396,15 @@ class Qwen3Engine:
         else:
             s_in = s_in_out if s_in_out is not None else ws.get(f"{tag}.s_in", (T, H))
             nv.rmsnorm_fwd(x, w[f"l{l}.ln1"], h, eps, res=res, res_out=s_in)
-        qkv = ws.get(f"{tag}.qkv", (T, self.p.qkv_local))
+        qkv = ws.get(f"{stag}.qkv", (T, self.p.qkv_local))
         self._gemm(h, w[f"l{l}.wqkv"], qkv)
         if cp_geom is not None and keep is not None:
             q = self.cp.bufs.local("q")[:T]          # the dK/dV kernels of the peers read it
         else:
-            q = ws.get(f"{tag}.q", (T, self.p.q_local))
+            q = ws.get(f"{stag}.q", (T, self.p.q_local))
         nv.qk_norm_rope_fwd(qkv, w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos, q, kbuf, vbuf,
                             Hq=self.hq, Hkv=self.hkv, eps=eps, kv_slot=kv_slot)
-        attn = ws.get(f"{tag}.attn", (T, self.p.q_local))
+        attn = ws.get(f"{stag}.attn", (T, self.p.q_local))
         qv = q if q_view is None else q.view(*q_view)
         ov = attn if q_view is None else attn.view(*q_view)
         if cp_geom is not None:
@@ -409,18 +413,21 @@ class Qwen3Engine:
             self._attention(qv, kbuf, vbuf, ov, lse, tiles, decode=q_view is not None)
         o = ws.get(f"{tag}.o", (T, H))
         self._row_parallel(attn, w[f"l{l}.wo"], o, self.nchunks)
-        s_mid = ws.get(f"{tag}.s_mid", (T, H))
+        s_mid = ws.get(f"{stag}.s_mid", (T, H))
         h2 = ws.get(f"{tag}.h2", (T, H))
         nv.rmsnorm_fwd(o, w[f"l{l}.ln2"], h2, eps, res=s_in, res_out=s_mid)
         if keep is not None:
             keep.update(s_in=s_in, h=h, qkv=qkv, q=q, attn=attn, s_mid=s_mid, h2=h2)
-        down = self._mlp_fwd(l, h2, T, tag, keep)
+        down = self._mlp_fwd(l, h2, T, tag, keep, store_tag)
         return down, s_mid
 
-    def _mlp_fwd(self, l: int, h2: torch.Tensor, T: int, tag: str, keep: dict | None) -> torch.Tensor:
+    supports_stored_activations = True
+
+    def _mlp_fwd(self, l: int, h2: torch.Tensor, T: int, tag: str, keep: dict | None,
+                 store_tag: str | None = None) -> torch.Tensor:
         """Feed-forward block on the normalised stream ``h2`` [T, H] -> [T, H] (before the residual)."""
         w, ws, H = self.p.w, self.ws, self.spec.hidden_size
-        gu = ws.get(f"{tag}.gu", (T, 2 * self.p.i_local))
+        gu = ws.get(f"{store_tag or tag}.gu", (T, 2 * self.p.i_local))
         self._gemm(h2, w[f"l{l}.wgu"], gu)
         act = ws.get(f"{tag}.act", (T, self.p.i_local))
         nv.swiglu_fwd(gu, act, self.p.i_local, self.blk)
@@ -429,6 +436,11 @@ class Qwen3Engine:
         if keep is not None:
             keep.update(gu=gu, act=act)
         return down
+
+    def _rebuild_mlp_activation(self, keep: dict, T: int) -> None:
+        """Stored-activation backward: SwiGLU output from the kept gate/up tensor."""
+        keep["act"] = self.ws.get("r.act", (T, self.p.i_local))
+        nv.swiglu_fwd(keep["gu"], keep["act"], self.p.i_local, self.blk)
 
     def _mlp_bwd(self, l: int, ds: torch.Tensor, keep: dict, T: int) -> torch.Tensor:
         """Backward of ``_mlp_fwd``: ``ds`` = d(loss)/d(output) -> d(loss)/d(h2), summed over TP;
@@ -510,8 +522,18 @@ class Qwen3Engine:
                 if save is not None and res is None:
                     save.ckpt[0].copy_(x)          # the embedding output is layer 0's residual stream
                     x = save.ckpt[0]
-                x, res = self._layer_fwd(l, x, res, T, pos, tiles=tiles, kbuf=kb, vbuf=vb,
-                                         s_in_out=s_out if res is not None else None, tag=tag, cp_geom=cp_geom)
+                keep, stag, lse_l = None, None, None
+                if save is not None and save.extra.get("stored"):
+                    # keep this layer's expensive intermediates for its backward (no recompute)
+                    stag = f"act{l - self.l0}"
+                    kb = ws.get(f"{stag}.k", (T, self.p.kv_local))
+                    vb = ws.get(f"{stag}.v", (T, self.p.kv_local))
+                    lse_l = ws.get(f"{stag}.lse", (T, self.hq), torch.float32)
+                    keep = {"k": kb, "v": vb, "lse": lse_l}
+                    save.extra["keeps"].append(keep)
+                x, res = self._layer_fwd(l, x, res, T, pos, tiles=tiles, kbuf=kb, vbuf=vb, lse=lse_l, keep=keep,
+                                         s_in_out=s_out if res is not None else None, tag=tag, cp_geom=cp_geom,
+                                         store_tag=stag)
         if not self.last_stage:
             return x, res
         hf = ws.get(f"{tag}.hf", (T, H))
@@ -637,7 +659,8 @@ class Qwen3Engine:
         return tokens[:, self.cp.local_positions(tokens.shape[1]).to(self.dev)].contiguous()
 
     def train_forward_backward(self, tokens: torch.Tensor, resp_start: int, dlogp_fn, *,
-                               temperature: float = 1.0, lm_chunk: int = 4096, stage_in=None):
+                               temperature: float = 1.0, lm_chunk: int = 4096, stage_in=None,
+                               store_activations: bool = False):
         """One micro-batch: forward with checkpoints, LM head + log-probs on response positions,
         ``dlogp_fn(logp [nseq, Rl]) -> dlogp [nseq, Rl]`` supplies d(loss)/d(logp), then the full
         backward accumulates into ``params.grad``.  Returns logp [nseq, Rl] (fp32).
@@ -656,6 +679,10 @@ class Qwen3Engine:
         R = sel.numel()
         st = self.new_train_state(nseq, Sl)
         st.extra["S_global"] = S
+        if store_activations and not cp and self.supports_stored_activations:
+            # trade memory for time: backward reuses the forward's tensors instead of recomputing
+            # every layer (about 100 KB per token and layer at Qwen3-8B width)
+            st.extra["stored"], st.extra["keeps"] = True, []
         hf = self.forward_hidden(tok_local, save=st, cp_seq_len=S if cp else None, stage_in=stage_in)
         hf3 = hf.view(nseq, Sl, H)
         rows = self.ws.get("lm.rows", (nseq * R, H))
@@ -665,12 +692,21 @@ class Qwen3Engine:
             rows.view(nseq, R, H).copy_(hf3[:, resp_start - 1:S - 1])
         targets = tokens[:, resp_start:][:, ridx].reshape(-1).contiguous() if cp else \
             tokens[:, resp_start:].reshape(-1).contiguous()
-        # ---- pass 1: log-probs (fused stats, logits not kept)
-        logp, lse = self.logp_from_hidden(rows, targets, temperature=temperature, want_lse=True)
+        # ---- pass 1: log-probs (fused stats).  A single-chunk, single-shard head keeps the bf16
+        # logits the same kernel can write, so pass 2 does not have to multiply again.
+        vloc = self.p.v_real_local
+        kept_logits = None
+        if self.ctx.tp_size == 1 and nseq * R <= lm_chunk and vloc > 0:
+            kept_logits = self.ws.get("lm.logits", (lm_chunk, vloc))[: nseq * R]
+            stats, tl = self._lmhead_stats(rows, targets, temperature, kept_logits)
+            logp = torch.empty(nseq * R, dtype=torch.float32, device=self.dev)
+            lse = torch.empty(nseq * R, dtype=torch.float32, device=self.dev)
+            nv.logp_merge(stats, tl, logp, lse)
+        else:
+            logp, lse = self.logp_from_hidden(rows, targets, temperature=temperature, want_lse=True)
         dlogp = dlogp_fn(logp.view(nseq, R)).reshape(-1).contiguous()
         # ---- pass 2: per chunk, logits -> dlogits -> dH, dW
         drows = self.ws.get("lm.drows", (nseq * R, H))
-        vloc = self.p.v_real_local
         wlm = self.p.w["lm_head"][:vloc]
         glm = self.p.g["lm_head"][:vloc]
         for r0 in range(0, nseq * R, lm_chunk):
@@ -678,7 +714,8 @@ class Qwen3Engine:
             n = r1 - r0
             logits = self.ws.get("lm.logits", (lm_chunk, vloc))[:n]
             if vloc > 0:
-                self._gemm(rows[r0:r1], wlm, logits)
+                if kept_logits is None:
+                    self._gemm(rows[r0:r1], wlm, logits)
                 nv.dlogits_(logits, targets[r0:r1], lse[r0:r1], dlogp[r0:r1],
                             vocab_start=self.p.vocab_start, inv_temp=1.0 / temperature)
                 self._gemm(logits, wlm, drows[r0:r1], b_mn=True, M=n, N=H, K=vloc)
@@ -732,9 +769,20 @@ class Qwen3Engine:
             else:
                 kb = ws.get("f.k", (T, self.p.kv_local))
                 vb = ws.get("f.v", (T, self.p.kv_local))
-            # ---- recompute the layer from its checkpointed input
-            self._layer_fwd(l, ck, None, T, pos, tiles=tiles, kbuf=kb, vbuf=vb, lse=lse,
-                            keep=keep, tag="r", cp_geom=cp_geom)
+            if st.extra.get("stored"):
+                # the forward kept qkv, q, k, v, attention output, s_mid, gate/up and lse of this layer;
+                # the two norms and the activation are rebuilt (bitwise the forward's values)
+                keep = dict(st.extra["keeps"][l - self.l0])
+                kb, vb, lse = keep["k"], keep["v"], keep["lse"]
+                keep["h"] = ws.get("r.h", (T, H))
+                nv.rmsnorm_fwd(ck, w[f"l{l}.ln1"], keep["h"], eps)
+                keep["h2"] = ws.get("r.h2", (T, H))
+                nv.rmsnorm_fwd(keep["s_mid"], w[f"l{l}.ln2"], keep["h2"], eps)
+                self._rebuild_mlp_activation(keep, T)
+            else:
+                # ---- recompute the layer from its checkpointed input
+                self._layer_fwd(l, ck, None, T, pos, tiles=tiles, kbuf=kb, vbuf=vb, lse=lse,
+                                keep=keep, tag="r", cp_geom=cp_geom)
             # ---- MLP backward.  s_out = s_mid + down  =>  d(down) = ds, d(s_mid) += ds
             dh2 = self._mlp_bwd(l, ds, keep, T)
             ds2 = ws.get("b.ds2", (T, H))

@@ -43,6 +43,8 @@ class GRPOConfig:
     share_rollout_weights: bool = False   # True: rollout reads the trainer's buffer (zero-copy publish)
     share_kv_and_activation_memory: bool = True
     share_prompt_pages: bool = True       # group members read their prompt's K/V pages in place
+    store_activations: bool = False       # training keeps layer intermediates instead of recomputing them
+    train_micro_batch_seqs: int = 0       # sequences per training micro-batch (0 = micro_batch_seqs)
 
     @property
     def num_seqs(self) -> int:
@@ -351,8 +353,9 @@ class GRPOTrainer:
         self.policy.grad.zero_()
         train_logp = torch.empty(B, Rl, dtype=torch.float32, device=self.dev)
         loss_terms = []
-        for b0 in range(0, B, c.micro_batch_seqs):
-            b1 = min(B, b0 + c.micro_batch_seqs)
+        tmb = c.train_micro_batch_seqs or c.micro_batch_seqs
+        for b0 in range(0, B, tmb):
+            b1 = min(B, b0 + tmb)
 
             def dlogp_fn(lp, b0=b0, b1=b1):
                 r = nv.grpo_loss(lp.contiguous(), old_local[b0:b1].contiguous(),
@@ -364,7 +367,8 @@ class GRPOTrainer:
                 return r["dlogp"]
 
             lp = self.engine.train_forward_backward(tokens[b0:b1], c.prompt_len, dlogp_fn,
-                                                    temperature=c.temperature)
+                                                    temperature=c.temperature,
+                                                    store_activations=c.store_activations)
             train_logp[b0:b1].copy_(lp)
         tot = torch.stack(loss_terms).sum(0)
         if self.cp > 1:

@@ -93,7 +93,9 @@ class Qwen3MoeEngine(Qwen3Engine):
         return MoEWeights(w[f"l{l}.router"], w[f"l{l}.w1"], w[f"l{l}.w2"], g.get(f"l{l}.router"),
                           g.get(f"l{l}.w1"), g.get(f"l{l}.w2"))
 
-    def _mlp_fwd(self, l, h2, T, tag, keep):
+    supports_stored_activations = False     # the expert buffers are shared by all layers: recompute
+
+    def _mlp_fwd(self, l, h2, T, tag, keep, store_tag=None):
         shared = super()._mlp_fwd(l, h2, T, tag, keep)
         out = self.ws.get(f"{tag}.moe_out", (T, self.spec.hidden_size))
         self.moe.forward(h2, self._moe_weights(l), out, base=shared)

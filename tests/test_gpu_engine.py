@@ -133,3 +133,26 @@ def test_gradients_against_autograd():
         want = W[name].grad
         err = (got.float() - want).abs().max().item()
         assert err < 0.04 * want.abs().max().item() + 1e-5, f"{name}: err {err} vs max {want.abs().max().item()}"
+
+
+def test_stored_activation_backward_equals_recompute_bitwise():
+    """Keeping a layer's intermediates for its backward gives the gradients of the recomputing path
+    bit for bit (the tensors that are rebuilt -- both norms and the activation -- repeat the
+    forward's arithmetic)."""
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.engine import PackedParams, Qwen3Engine
+
+    spec = _spec()
+    w = Qwen3DenseWeights.synthetic(spec, seed=4)
+    tok = torch.randint(0, spec.vocab_size, (3, 320), device=dev())
+    out = []
+    for stored in (False, True):
+        params = PackedParams(spec, 0, 1, dev(), with_grad=True).load(w)
+        eng = Qwen3Engine(spec, params, max_positions=512)
+        lp = eng.train_forward_backward(tok, 64, lambda x: torch.full_like(x, -1.0 / x.numel()),
+                                        store_activations=stored)
+        sync_and_check()
+        out.append((lp.clone(), params.grad.clone()))
+    assert torch.equal(out[0][0], out[1][0])
+    assert torch.equal(out[0][1], out[1][1])
+    assert out[0][1].float().abs().sum().item() > 0
