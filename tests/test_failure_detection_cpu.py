@@ -33,10 +33,11 @@ def _raising_worker(rank, world, port, store_port, out):
     try:
         for step in range(4):
             with mon.step(step):
-                if rank == 1 and step == 2:
-                    raise RuntimeError("injected host failure")
                 x = torch.full((4,), float(rank + step))
                 coll.all_reduce_(x)
+                if rank == 1 and step == 2:
+                    # the step's collective is done, nothing is in flight: fail on the host
+                    raise RuntimeError("injected host failure")
     except PeerFailure as e:
         seen = ("peer", e.rank, e.reason)
     except RuntimeError as e:
