@@ -239,6 +239,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     uint8_t* p_row = smem + off_p;
     float* xch = reinterpret_cast<float*>(smem + AttnFwdSmem::kXch);  // [2][128][4] maxima, then [128][4] sums
     bool alive = true;
+    float alpha_prev = 0.f;
 
     for (int b = 0; b < nblk; ++b) {
       const int s = b & 1;
@@ -274,6 +275,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         pk[j / 2] = pack_bf16x2(e0, e1);
         pk[j / 2 + 1] = pack_bf16x2(e2, e3);
       }
+      // The previous block's P*V product is collected only now, after this block's exponentials
+      // are already in registers: the MMA of block b-1 runs while block b's scores are reduced.
+      // (It must be collected before P is overwritten and before the next P*V reuses the O columns.)
+      if (b > 0) {
+        if (!mbar_wait(BAR(O_FULL), (b - 1) & 1, abort_flag, p.status, 209)) { alive = false; break; }
+        tc_fence_after();
+        uint32_t xo[32];
+        tmem_ld32(tmem_base + lane_off + TM_O + split * 32, xo);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], alpha_prev, __uint_as_float(xo[j]));
+      }
       // this thread's 32 keys = 4 chunks of 16 bytes; keys [64h, 64h+64) live in half h of the P tile
       if (r < p.q_rows_box) {
 #pragma unroll
@@ -287,12 +300,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_arrive(BAR(P_FULL));
       l_part = l_part * alpha + ((sum0 + sum1) + (sum2 + sum3));
       m_run = m_new;
-      if (!mbar_wait(BAR(O_FULL), b & 1, abort_flag, p.status, 209)) { alive = false; break; }
-      tc_fence_after();
-      tmem_ld32(tmem_base + lane_off + TM_O + split * 32, x);
-      tmem_ld_wait();
+      alpha_prev = alpha;
+    }
+    if (alive && nblk > 0) {
+      if (mbar_wait(BAR(O_FULL), (nblk - 1) & 1, abort_flag, p.status, 209)) {
+        tc_fence_after();
+        uint32_t xo[32];
+        tmem_ld32(tmem_base + lane_off + TM_O + split * 32, xo);
+        tmem_ld_wait();
 #pragma unroll
-      for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], alpha, __uint_as_float(x[j]));
+        for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], alpha_prev, __uint_as_float(xo[j]));
+      } else {
+        alive = false;
+      }
     }
     // ---------------------------------------------------------------- epilogue
     // row sum = (l0 + l1) + (l2 + l3) over the four column slices
