@@ -247,6 +247,62 @@ all_reduce_2shot_kernel(const SymmWorld w, const unsigned char* __restrict__ src
   }
 }
 
+// Reduce-scatter: the payload is `world` equal ranges; rank r ends with the balanced-tree sum of
+// range r (dst holds per_rank bytes).  Every rank stages the ranges it does not own in its frame,
+// the owner of a range pulls the peers' copies slice by slice -- half of the two-shot all-reduce.
+template <int DT, int W>
+__global__ void __launch_bounds__(kCollThreads)
+reduce_scatter_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                      long long per_rank, int slice_bytes, int frame, unsigned long long base_seq, int* status) {
+  const unsigned long long seq = effective_seq(w, base_seq);
+  const int spr = static_cast<int>((per_rank + slice_bytes - 1) / slice_bytes);   // slices per range
+  const int nslices = spr * W;
+  unsigned char* mine = frame_ptr(w.win[w.rank], w.frame_bytes, frame);
+  constexpr int U = 16 / W;
+  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+    const int owner = s / spr;
+    const long long in_range = static_cast<long long>(s % spr) * slice_bytes;
+    const long long off = owner * per_rank + in_range;
+    const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), per_rank - in_range) / 16);
+    if (owner != w.rank)
+      for (int i = threadIdx.x; i < n16; i += blockDim.x)
+        reinterpret_cast<uint4*>(mine + off)[i] = reinterpret_cast<const uint4*>(src + off)[i];
+    slice_publish(w, s, seq);
+  }
+  for (int i = 0; i < spr; ++i) {
+    const int s = w.rank * spr + i;
+    if (s % gridDim.x != blockIdx.x) continue;
+    const long long in_range = static_cast<long long>(i) * slice_bytes;
+    const long long off = w.rank * per_rank + in_range;
+    const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), per_rank - in_range) / 16);
+    if (!slice_wait(w, s, seq, ((1u << W) - 1u) & ~(1u << w.rank), status, 406)) continue;
+    for (int i0 = threadIdx.x; i0 < n16; i0 += blockDim.x * U) {
+      uint4 v[U][W];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int k = i0 + u * blockDim.x;
+        if (k < n16) {
+#pragma unroll
+          for (int r = 0; r < W; ++r)
+            v[u][r] = (r == w.rank) ? reinterpret_cast<const uint4*>(src + off)[k]
+                                    : ld_peer_v4(frame_ptr(w.win[r], w.frame_bytes, frame) + off + 16ll * k);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int k = i0 + u * blockDim.x;
+        if (k < n16) {
+#pragma unroll
+          for (int n = W; n > 1; n >>= 1)
+#pragma unroll
+            for (int j = 0; j < n / 2; ++j) v[u][j] = tree_node<DT>(v[u][2 * j], v[u][2 * j + 1]);
+          reinterpret_cast<uint4*>(dst + in_range)[k] = v[u][0];
+        }
+      }
+    }
+  }
+}
+
 // All-gather: dst[r] = rank r's payload (rank order).  Every CTA first stages and publishes all of
 // its slices, then pulls the peers' copies with eight 16-byte loads in flight per thread, so the
 // NVLink round trip is paid once per batch of loads instead of once per load.
@@ -430,6 +486,38 @@ RLK_API int rlk_symm_all_reduce(void* state, const void* src, void* dst, long lo
     all_reduce_kernel<0><<<coll_grid(nbytes), kCollThreads, 0, s>>>(st->w, sp, dp, nbytes, slice_bytes_for(nbytes), frame, st->seq, staged, device_status_word());
   else
     all_reduce_kernel<1><<<coll_grid(nbytes), kCollThreads, 0, s>>>(st->w, sp, dp, nbytes, slice_bytes_for(nbytes), frame, st->seq, staged, device_status_word());
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+// src: world * per_rank bytes (range r belongs to rank r); dst: per_rank bytes.
+RLK_API int rlk_symm_reduce_scatter(void* state, const void* src, void* dst, long long per_rank, int dtype,
+                                    void* stream) {
+  SymmState* st = static_cast<SymmState*>(state);
+  const int W = st->w.world;
+  RLK_REQUIRE(per_rank > 0 && per_rank % 16 == 0, "reduce_scatter: bytes per rank must be a positive multiple of 16");
+  RLK_REQUIRE(per_rank * W <= st->w.frame_bytes, "reduce_scatter: %lld bytes exceed the frame capacity %lld", per_rank * W, st->w.frame_bytes);
+  RLK_REQUIRE(dtype == 0 || dtype == 1, "reduce_scatter: dtype must be 0 (bf16) or 1 (fp32)");
+  RLK_REQUIRE(W == 2 || W == 4 || W == 8, "reduce_scatter: world must be 2, 4 or 8");
+  st->seq += 1;
+  const int frame = static_cast<int>(st->seq & 1);
+  const unsigned long long base = st->seq;
+  long long sb = kMinSliceBytes;
+  while (((per_rank + sb - 1) / sb) * W > kMaxSlices - 1) sb *= 2;
+  const long long nsl = ((per_rank + sb - 1) / sb) * W;
+  const int cap = per_rank * W >= kTwoShotMinBytes ? 2 * sm_count() : 64;
+  const int grid = static_cast<int>(nsl < cap ? nsl : cap);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const unsigned char* sp = static_cast<const unsigned char*>(src);
+  unsigned char* dp = static_cast<unsigned char*>(dst);
+  int* stw = device_status_word();
+#define RLK_LAUNCH_RS(DT, WW) reduce_scatter_kernel<DT, WW><<<grid, kCollThreads, 0, s>>>(st->w, sp, dp, per_rank, static_cast<int>(sb), frame, base, stw)
+  if (dtype == 0) {
+    if (W == 2) RLK_LAUNCH_RS(0, 2); else if (W == 4) RLK_LAUNCH_RS(0, 4); else RLK_LAUNCH_RS(0, 8);
+  } else {
+    if (W == 2) RLK_LAUNCH_RS(1, 2); else if (W == 4) RLK_LAUNCH_RS(1, 4); else RLK_LAUNCH_RS(1, 8);
+  }
+#undef RLK_LAUNCH_RS
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

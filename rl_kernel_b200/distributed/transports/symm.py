@@ -169,8 +169,22 @@ class SymmetricMemoryCollective:
         return [self.all_gather(t) for t in tensors]
 
     def reduce_scatter(self, t: torch.Tensor) -> torch.Tensor:
+        """t [world * n, ...] -> the fixed-tree sum of this rank's [n, ...] slice (one kernel: every
+        rank stages the slices it does not own, the owner pulls and reduces them)."""
+        if self.world == 1:
+            return t
+        self._check_open()
         n = t.shape[0] // self.world
-        return self.all_reduce(t)[self.rank * n:(self.rank + 1) * n].contiguous()
+        t = t.contiguous()
+        per = t.numel() // self.world * t.element_size()
+        if t.dtype not in _DT or t.shape[0] % self.world or per % 16 or per * self.world > self.frame_bytes:
+            return self.all_reduce(t)[self.rank * n:(self.rank + 1) * n].contiguous()
+        out = torch.empty((n,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        ext.check(self._lib.rlk_symm_reduce_scatter(self._state, ext.ptr(t), ext.ptr(out), c_longlong(per),
+                                                    c_int(_DT[t.dtype]), ext.stream_ptr(self.device)),
+                  "symm_reduce_scatter")
+        nv._count()
+        return out
 
     def broadcast_(self, t: torch.Tensor, src: int = 0) -> torch.Tensor:
         if self.world > 1:

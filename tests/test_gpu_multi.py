@@ -45,6 +45,9 @@ def _collective_worker(rank, world, port, out):
         ok &= torch.equal(got, want)
         ag = coll.all_gather(parts[rank])
         ok &= all(torch.equal(ag[r], parts[r]) for r in range(world))
+        if n % (8 * world) == 0:
+            rs = coll.reduce_scatter(parts[rank])
+            ok &= torch.equal(rs, want[rank * (n // world):(rank + 1) * (n // world)])
     # staged all-reduce: the producer writes straight into the symmetric frame
     x = torch.full((256, 128), float(rank + 1), device=dev, dtype=torch.bfloat16)
     st = coll.staging_view(x.shape, x.dtype)
