@@ -21,13 +21,15 @@ def main() -> None:
     ap.add_argument("--seq-len", type=int, default=1536)
     ap.add_argument("--prompt-len", type=int, default=512)
     ap.add_argument("--iters", type=int, default=2)
+    ap.add_argument("--store", action="store_true", help="keep layer intermediates instead of recomputing them")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     spec = Qwen3DenseSpec.official().with_layers(a.layers)
     params = PackedParams(spec, 0, 1, dev, with_grad=True).init_synthetic_(1)
     eng = Qwen3Engine(spec, params, max_positions=a.seq_len + 8)
     tok = torch.randint(0, spec.vocab_size, (a.seqs, a.seq_len), device=dev)
-    fn = lambda: eng.train_forward_backward(tok, a.prompt_len, lambda lp: torch.full_like(lp, -1.0 / lp.numel()))  # noqa: E731
+    fn = lambda: eng.train_forward_backward(tok, a.prompt_len, lambda lp: torch.full_like(lp, -1.0 / lp.numel()),  # noqa: E731
+                                            store_activations=a.store)
     fn()
     torch.cuda.synchronize()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -38,7 +40,7 @@ def main() -> None:
     torch.cuda.synchronize()
     ms = s.elapsed_time(e) / a.iters
     T = a.seqs * a.seq_len
-    print(json.dumps({"layers": a.layers, "tokens": T, "ms_per_microbatch": ms, "tokens_per_s": T / ms * 1e3}))
+    print(json.dumps({"layers": a.layers, "tokens": T, "stored_activations": a.store, "ms_per_microbatch": ms, "tokens_per_s": T / ms * 1e3}))
 
 
 if __name__ == "__main__":
