@@ -122,7 +122,7 @@ def lmhead_logp_stats_vp(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor
 def attn_fwd(q2d: torch.Tensor, k_list: list[torch.Tensor], v_list: list[torch.Tensor],
              o2d: torch.Tensor, lse: torch.Tensor | None, tiles: torch.Tensor, scale: float, *,
              cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False, decode: bool = False,
-             page_table: torch.Tensor | None = None) -> None:
+             page_table: torch.Tensor | None = None, stage: tuple | None = None) -> None:
     """q2d/o2d: [rows, Hq*128]; k/v: [rows, Hkv*128] (one tensor per source rank).  ``page_table``
     int32: tiles whose last column is > 0 read KV block b from page ``table[col - 1 + b]``."""
     _bf16(q2d, "q"); _rowmajor2d(q2d, "q"); _rowmajor2d(o2d, "o")
@@ -137,9 +137,18 @@ def attn_fwd(q2d: torch.Tensor, k_list: list[torch.Tensor], v_list: list[torch.T
                              _ll(k0.stride(0)), ext.ptr(o2d), _ll(o2d.stride(0)), ext.ptr(lse),
                              ext.ptr(tiles), c_int(tiles.shape[0]), c_float(scale),
                              c_int(cp_blocks_per_chunk), c_int(int(cp_zigzag)), c_int(int(decode)),
-                             ext.ptr(page_table), ext.stream_ptr(q2d.device))
+                             ext.ptr(page_table), *_stage_args(stage), ext.stream_ptr(q2d.device))
     ext.check(rc, "attn_fwd")
     _count()
+
+
+def _stage_args(stage):
+    """``stage`` = (buffer a, buffer b, int32 flags, rows per rank, this rank) for context-parallel
+    staging of remote blocks, or None."""
+    if stage is None:
+        return c_void_p(0), c_void_p(0), c_void_p(0), c_int(0), c_int(0)
+    a, b, flags, rows, rank = stage
+    return ext.ptr(a), ext.ptr(b), ext.ptr(flags), c_int(int(rows)), c_int(int(rank))
 
 
 def attn_bwd_delta(o2d: torch.Tensor, do2d: torch.Tensor, delta: torch.Tensor, T: int, Hq: int) -> None:
@@ -155,7 +164,7 @@ def _as_list(x):
 
 
 def attn_bwd_dq(q2d, do2d, k2d, v2d, lse, delta, dq2d, tiles, scale: float, *,
-                cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False) -> None:
+                cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False, stage: tuple | None = None) -> None:
     """``k2d`` / ``v2d``: one tensor, or one per context-parallel rank (peers' buffers mapped here)."""
     ks, vs = _as_list(k2d), _as_list(v2d)
     n_src, k0 = len(ks), ks[0]
@@ -166,14 +175,14 @@ def attn_bwd_dq(q2d, do2d, k2d, v2d, lse, delta, dq2d, tiles, scale: float, *,
                                 _ll(k0.shape[0]), _ll(k0.shape[1]), _ll(k0.stride(0)),
                                 ext.ptr(lse), ext.ptr(delta), ext.ptr(dq2d), _ll(dq2d.stride(0)),
                                 ext.ptr(tiles), c_int(tiles.shape[0]), c_float(scale),
-                                c_int(cp_blocks_per_chunk), c_int(int(cp_zigzag)),
+                                c_int(cp_blocks_per_chunk), c_int(int(cp_zigzag)), *_stage_args(stage),
                                 ext.stream_ptr(dq2d.device))
     ext.check(rc, "attn_bwd_dq")
     _count()
 
 
 def attn_bwd_dkv(q2d, do2d, k2d, v2d, lse, delta, dk2d, dv2d, kv_tiles, scale: float, *,
-                 cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False) -> None:
+                 cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False, stage: tuple | None = None) -> None:
     """``q2d`` / ``do2d`` / ``lse`` / ``delta``: one tensor each, or one per context-parallel rank."""
     qs, dos, ls, ds = _as_list(q2d), _as_list(do2d), _as_list(lse), _as_list(delta)
     n_src, q0, do0 = len(qs), qs[0], dos[0]
@@ -187,7 +196,7 @@ def attn_bwd_dkv(q2d, do2d, k2d, v2d, lse, delta, dk2d, dv2d, kv_tiles, scale: f
                                  _ll(k2d.shape[0]), _ll(k2d.shape[1]), _ll(k2d.stride(0)), lp, dp,
                                  ext.ptr(dk2d), ext.ptr(dv2d), _ll(dk2d.stride(0)), ext.ptr(kv_tiles),
                                  c_int(kv_tiles.shape[0]), c_float(scale), c_int(cp_blocks_per_chunk),
-                                 c_int(int(cp_zigzag)), ext.stream_ptr(dk2d.device))
+                                 c_int(int(cp_zigzag)), *_stage_args(stage), ext.stream_ptr(dk2d.device))
     ext.check(rc, "attn_bwd_dkv")
     _count()
 

@@ -58,6 +58,7 @@ struct AttnDqParams {
   long long lddq;
   float scale, scale_log2;
   CpLayout cp;         // context parallel: which rank's K/V holds canonical block b
+  CpStage stage;       // remote K/V blocks are copied once into local memory (rows = 0: off)
   int* status;
 };
 
@@ -74,7 +75,8 @@ struct DqSmem {
 template <int NSRC>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmDO,
-                   const __grid_constant__ KvMaps<NSRC> kv, const AttnDqParams p) {
+                   const __grid_constant__ KvMaps<NSRC> kv, const __grid_constant__ KvMaps<1> staged,
+                   const AttnDqParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -88,7 +90,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const AttnTile t = p.tiles[blockIdx.x];
-  if (t.n_rows <= 0) return;
+  const bool use_stage = NSRC > 1 && p.stage.rows > 0;
+  volatile int* stage_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  if (t.n_rows <= 0) {
+    if (use_stage && warp >= 2) cp_stage_gather(p.stage, threadIdx.x - 64, kBwdThreads - 64, 3, stage_slot);
+    return;
+  }
   int max_kv = t.pos0 + (t.n_rows - 1) * t.pos_step + 1;
   if (max_kv > t.kv_cap) max_kv = t.kv_cap;
   const int nblk = (max_kv + kAttnBlock - 1) / kAttnBlock;
@@ -134,15 +141,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         int src, lb;
         cp_locate_block(p.cp, b, src, lb);   // plain TMA loads, possibly from a peer's memory
         if (NSRC == 1) src = 0;
-        const int row = t.kv_row0 + lb * kAttnBlock;
+        int row = t.kv_row0 + lb * kAttnBlock;
+        const CUtensorMap* mk = &kv.k[src];
+        const CUtensorMap* mv = &kv.v[src];
+        if (use_stage && src != p.stage.rank) {
+          if (!cp_stage_wait(p.stage, src, row / kAttnBlock, abort_flag, p.status, 320)) break;
+          row += src * p.stage.rows;
+          mk = &staged.k[0];
+          mv = &staged.v[0];
+        }
         if (!mbar_wait(BAR(K_EMPTY + s), ph ^ 1, abort_flag, p.status, 301)) break;
         mbar_expect_tx(BAR(K_FULL + s), kTile);
-        tma_load_2d(sK + s * kTile, &kv.k[src], t.kv_col0, row, BAR(K_FULL + s));
-        tma_load_2d(sK + s * kTile + kHalf, &kv.k[src], t.kv_col0 + 64, row, BAR(K_FULL + s));
+        tma_load_2d(sK + s * kTile, mk, t.kv_col0, row, BAR(K_FULL + s));
+        tma_load_2d(sK + s * kTile + kHalf, mk, t.kv_col0 + 64, row, BAR(K_FULL + s));
         if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1, abort_flag, p.status, 302)) break;
         mbar_expect_tx(BAR(V_FULL + s), kTile);
-        tma_load_2d(sV + s * kTile, &kv.v[src], t.kv_col0, row, BAR(V_FULL + s));
-        tma_load_2d(sV + s * kTile + kHalf, &kv.v[src], t.kv_col0 + 64, row, BAR(V_FULL + s));
+        tma_load_2d(sV + s * kTile, mv, t.kv_col0, row, BAR(V_FULL + s));
+        tma_load_2d(sV + s * kTile + kHalf, mv, t.kv_col0 + 64, row, BAR(V_FULL + s));
       }
     }
   } else if (warp == 1) {
@@ -200,6 +215,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       dlt = p.delta[li];
     }
     uint8_t* ds_base = smem + DqSmem::kDS;
+    if (use_stage) cp_stage_gather(p.stage, threadIdx.x - 64, kBwdThreads - 64, 3, stage_slot);
     for (int b = 0; b < nblk; ++b) {
       if (!mbar_wait(BAR(SDP_FULL), b & 1, abort_flag, p.status, 307)) break;
       // the previous block's dQ MMA must have finished reading the dS tile
@@ -286,6 +302,7 @@ struct AttnDkvParams {
   const float* lse[8];    // per context-parallel rank (index 0 only when not context parallel)
   const float* delta[8];
   CpLayout cp;            // which rank holds query tile qt of a sequence, and where
+  CpStage stage;          // remote Q / dO tiles are copied once into local memory (rows = 0: off)
   __nv_bfloat16* dK;
   __nv_bfloat16* dV;
   long long lddkv;
@@ -309,8 +326,9 @@ struct DkvSmem {
 // and lse / delta through plain peer loads, in the same ascending query-tile order as on one GPU.
 template <int NSRC>
 __global__ void __launch_bounds__(kBwdThreads, 1)
-attn_bwd_dkv_kernel(const __grid_constant__ KvMaps<NSRC> qdo, const __grid_constant__ CUtensorMap tmK,
-                    const __grid_constant__ CUtensorMap tmV, const AttnDkvParams p) {
+attn_bwd_dkv_kernel(const __grid_constant__ KvMaps<NSRC> qdo, const __grid_constant__ KvMaps<1> staged,
+                    const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                    const AttnDkvParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -323,7 +341,12 @@ attn_bwd_dkv_kernel(const __grid_constant__ KvMaps<NSRC> qdo, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const AttnKvTile t = p.tiles[blockIdx.x];
-  if (t.n_keys <= 0) return;
+  const bool use_stage = NSRC > 1 && p.stage.rows > 0;
+  volatile int* stage_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
+  if (t.n_keys <= 0) {
+    if (use_stage && warp >= 2) cp_stage_gather(p.stage, threadIdx.x - 64, kBwdThreads - 64, 3, stage_slot);
+    return;
+  }
   // first query row that can see key0, rounded down to the sequence's 128-row tile grid
   int i0 = t.key0 - t.q_pos0;
   if (i0 < 0) i0 = 0;
@@ -369,11 +392,20 @@ attn_bwd_dkv_kernel(const __grid_constant__ KvMaps<NSRC> qdo, const __grid_const
         int src, lb;
         cp_locate_block(p.cp, qt, src, lb);
         if (NSRC == 1) src = 0;
-        const int row = t.q_row0 + lb * 128, col = t.q_col0 + g * 128;
-        tma_load_2d(sQ, &qdo.k[src], col, row, BAR(Q_FULL));
-        tma_load_2d(sQ + kHalf, &qdo.k[src], col + 64, row, BAR(Q_FULL));
-        tma_load_2d(sDO, &qdo.v[src], col, row, BAR(Q_FULL));
-        tma_load_2d(sDO + kHalf, &qdo.v[src], col + 64, row, BAR(Q_FULL));
+        int row = t.q_row0 + lb * 128;
+        const int col = t.q_col0 + g * 128;
+        const CUtensorMap* mq = &qdo.k[src];
+        const CUtensorMap* md = &qdo.v[src];
+        if (use_stage && src != p.stage.rank) {
+          if (!cp_stage_wait(p.stage, src, row / 128, abort_flag, p.status, 321)) break;
+          row += src * p.stage.rows;
+          mq = &staged.k[0];
+          md = &staged.v[0];
+        }
+        tma_load_2d(sQ, mq, col, row, BAR(Q_FULL));
+        tma_load_2d(sQ + kHalf, mq, col + 64, row, BAR(Q_FULL));
+        tma_load_2d(sDO, md, col, row, BAR(Q_FULL));
+        tma_load_2d(sDO + kHalf, md, col + 64, row, BAR(Q_FULL));
       }
     }
   } else if (warp == 1) {
@@ -420,6 +452,7 @@ attn_bwd_dkv_kernel(const __grid_constant__ KvMaps<NSRC> qdo, const __grid_const
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     uint8_t* p_base = smem + DkvSmem::kP;
     uint8_t* ds_base = smem + DkvSmem::kDS;
+    if (use_stage) cp_stage_gather(p.stage, threadIdx.x - 64, kBwdThreads - 64, 3, stage_slot);
     for (int it = 0; it < n_iter; ++it) {
       const int g = it / n_qt, qt = qt0 + it % n_qt;
       const int qi = qt * 128 + r;  // query row index within the sequence
@@ -543,7 +576,8 @@ RLK_API int rlk_attn_bwd_dq(const void* Q, const void* dO, long long q_rows, lon
                             const void* const* v_ptrs, int n_src, long long kv_rows, long long kv_cols,
                             long long ldkv, const float* lse, const float* delta, void* dQ,
                             long long lddq, const void* tiles, int n_tiles, float scale,
-                            int cp_blocks_per_chunk, int cp_zigzag, void* stream) {
+                            int cp_blocks_per_chunk, int cp_zigzag, void* stage_k, void* stage_v,
+                            int* stage_flags, int stage_rows, int cp_rank, void* stream) {
   RLK_REQUIRE(n_tiles > 0, "attn_bwd_dq: no tiles");
   RLK_REQUIRE(n_src == 1 || (n_src >= 2 && n_src <= 8), "attn_bwd_dq: n_src must be 1..8");
   RLK_REQUIRE(n_src == 1 || cp_blocks_per_chunk > 0, "attn_bwd_dq: cp_blocks_per_chunk must be positive");
@@ -551,9 +585,17 @@ RLK_API int rlk_attn_bwd_dq(const void* Q, const void* dO, long long q_rows, lon
   int rc;
   if ((rc = make_tmap_2d_sw128(&tmQ, Q, q_rows, q_cols, ldq, 128, 64, 2))) return rc;
   if ((rc = make_tmap_2d_sw128(&tmDO, dO, q_rows, q_cols, lddo, 128, 64, 2))) return rc;
-  AttnDqParams p{static_cast<const AttnTile*>(tiles), n_tiles, lse, delta,
-                 static_cast<__nv_bfloat16*>(dQ), lddq, scale, scale * kLog2e,
-                 CpLayout{n_src > 1 ? n_src : 1, cp_blocks_per_chunk, cp_zigzag}, device_status_word()};
+  AttnDqParams p{};
+  p.tiles = static_cast<const AttnTile*>(tiles);
+  p.n_tiles = n_tiles;
+  p.lse = lse;
+  p.delta = delta;
+  p.dQ = static_cast<__nv_bfloat16*>(dQ);
+  p.lddq = lddq;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  p.cp = CpLayout{n_src > 1 ? n_src : 1, cp_blocks_per_chunk, cp_zigzag};
+  p.status = device_status_word();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (n_src == 1) {
     KvMaps<1> kv;
@@ -561,7 +603,7 @@ RLK_API int rlk_attn_bwd_dq(const void* Q, const void* dO, long long q_rows, lon
     if ((rc = make_tmap_2d_sw128(&kv.v[0], v_ptrs[0], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
     static bool flags[64] = {false};
     if ((rc = set_smem_attr(attn_bwd_dq_kernel<1>, DqSmem::kBytes, flags))) return rc;
-    attn_bwd_dq_kernel<1><<<n_tiles, kBwdThreads, DqSmem::kBytes, st>>>(tmQ, tmDO, kv, p);
+    attn_bwd_dq_kernel<1><<<n_tiles, kBwdThreads, DqSmem::kBytes, st>>>(tmQ, tmDO, kv, kv, p);
   } else {
     KvMaps<8> kv;
     for (int i = 0; i < 8; ++i) {
@@ -569,9 +611,32 @@ RLK_API int rlk_attn_bwd_dq(const void* Q, const void* dO, long long q_rows, lon
       if ((rc = make_tmap_2d_sw128(&kv.k[i], k_ptrs[j], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
       if ((rc = make_tmap_2d_sw128(&kv.v[i], v_ptrs[j], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
     }
+    KvMaps<1> staged;
+    staged.k[0] = kv.k[0];
+    staged.v[0] = kv.v[0];
+    if (stage_rows > 0) {
+      RLK_REQUIRE(stage_k && stage_v && stage_flags && stage_rows % 128 == 0 && stage_rows <= kv_rows &&
+                  ldkv == kv_cols && cp_rank >= 0 && cp_rank < n_src, "attn_bwd_dq: bad staging arguments");
+      CpStage& sg = p.stage;
+      for (int i = 0; i < 8; ++i) {
+        sg.src_a[i] = static_cast<const unsigned char*>(k_ptrs[i < n_src ? i : 0]);
+        sg.src_b[i] = static_cast<const unsigned char*>(v_ptrs[i < n_src ? i : 0]);
+      }
+      sg.dst_a = static_cast<unsigned char*>(stage_k);
+      sg.dst_b = static_cast<unsigned char*>(stage_v);
+      sg.flags = stage_flags;
+      sg.rows = stage_rows;
+      sg.row_bytes_a = sg.row_bytes_b = static_cast<int>(kv_cols * 2);
+      sg.ranks = n_src;
+      sg.rank = cp_rank;
+      const long long total = static_cast<long long>(n_src) * stage_rows;
+      if ((rc = make_tmap_2d_sw128(&staged.k[0], stage_k, total, kv_cols, kv_cols, 128, 64, 2))) return rc;
+      if ((rc = make_tmap_2d_sw128(&staged.v[0], stage_v, total, kv_cols, kv_cols, 128, 64, 2))) return rc;
+      RLK_CHECK_CUDA(cudaMemsetAsync(stage_flags, 0, sizeof(int) * (n_src * (stage_rows / 128) * 2 + 1), st));
+    }
     static bool flags[64] = {false};
     if ((rc = set_smem_attr(attn_bwd_dq_kernel<8>, DqSmem::kBytes, flags))) return rc;
-    attn_bwd_dq_kernel<8><<<n_tiles, kBwdThreads, DqSmem::kBytes, st>>>(tmQ, tmDO, kv, p);
+    attn_bwd_dq_kernel<8><<<n_tiles, kBwdThreads, DqSmem::kBytes, st>>>(tmQ, tmDO, kv, staged, p);
   }
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
@@ -587,7 +652,8 @@ RLK_API int rlk_attn_bwd_dkv(const void* const* q_ptrs, const void* const* do_pt
                              long long ldkv, const float* const* lse_ptrs,
                              const float* const* delta_ptrs, void* dK, void* dV, long long lddkv,
                              const void* tiles, int n_tiles, float scale, int cp_blocks_per_chunk,
-                             int cp_zigzag, void* stream) {
+                             int cp_zigzag, void* stage_q, void* stage_do, int* stage_flags,
+                             int stage_rows, int cp_rank, void* stream) {
   RLK_REQUIRE(n_tiles > 0, "attn_bwd_dkv: no tiles");
   RLK_REQUIRE(n_src == 1 || (n_src >= 2 && n_src <= 8), "attn_bwd_dkv: n_src must be 1..8");
   RLK_REQUIRE(n_src == 1 || cp_blocks_per_chunk > 0, "attn_bwd_dkv: cp_blocks_per_chunk must be positive");
@@ -617,7 +683,7 @@ RLK_API int rlk_attn_bwd_dkv(const void* const* q_ptrs, const void* const* do_pt
     if ((rc = make_tmap_2d_sw128(&qdo.v[0], do_ptrs[0], q_rows, q_cols, lddo, 128, 64, 2))) return rc;
     static bool flags[64] = {false};
     if ((rc = set_smem_attr(attn_bwd_dkv_kernel<1>, DkvSmem::kBytes, flags))) return rc;
-    attn_bwd_dkv_kernel<1><<<n_tiles, kBwdThreads, DkvSmem::kBytes, st>>>(qdo, tmK, tmV, p);
+    attn_bwd_dkv_kernel<1><<<n_tiles, kBwdThreads, DkvSmem::kBytes, st>>>(qdo, qdo, tmK, tmV, p);
   } else {
     KvMaps<8> qdo;
     for (int i = 0; i < 8; ++i) {
@@ -625,9 +691,33 @@ RLK_API int rlk_attn_bwd_dkv(const void* const* q_ptrs, const void* const* do_pt
       if ((rc = make_tmap_2d_sw128(&qdo.k[i], q_ptrs[j], q_rows, q_cols, ldq, 128, 64, 2))) return rc;
       if ((rc = make_tmap_2d_sw128(&qdo.v[i], do_ptrs[j], q_rows, q_cols, lddo, 128, 64, 2))) return rc;
     }
+    KvMaps<1> staged;
+    staged.k[0] = qdo.k[0];
+    staged.v[0] = qdo.v[0];
+    if (stage_rows > 0) {
+      RLK_REQUIRE(stage_q && stage_do && stage_flags && stage_rows % 128 == 0 && stage_rows <= q_rows &&
+                  ldq == q_cols && lddo == q_cols && cp_rank >= 0 && cp_rank < n_src,
+                  "attn_bwd_dkv: bad staging arguments");
+      CpStage& sg = p.stage;
+      for (int i = 0; i < 8; ++i) {
+        sg.src_a[i] = static_cast<const unsigned char*>(q_ptrs[i < n_src ? i : 0]);
+        sg.src_b[i] = static_cast<const unsigned char*>(do_ptrs[i < n_src ? i : 0]);
+      }
+      sg.dst_a = static_cast<unsigned char*>(stage_q);
+      sg.dst_b = static_cast<unsigned char*>(stage_do);
+      sg.flags = stage_flags;
+      sg.rows = stage_rows;
+      sg.row_bytes_a = sg.row_bytes_b = static_cast<int>(q_cols * 2);
+      sg.ranks = n_src;
+      sg.rank = cp_rank;
+      const long long total = static_cast<long long>(n_src) * stage_rows;
+      if ((rc = make_tmap_2d_sw128(&staged.k[0], stage_q, total, q_cols, q_cols, 128, 64, 2))) return rc;
+      if ((rc = make_tmap_2d_sw128(&staged.v[0], stage_do, total, q_cols, q_cols, 128, 64, 2))) return rc;
+      RLK_CHECK_CUDA(cudaMemsetAsync(stage_flags, 0, sizeof(int) * (n_src * (stage_rows / 128) * 2 + 1), st));
+    }
     static bool flags[64] = {false};
     if ((rc = set_smem_attr(attn_bwd_dkv_kernel<8>, DkvSmem::kBytes, flags))) return rc;
-    attn_bwd_dkv_kernel<8><<<n_tiles, kBwdThreads, DkvSmem::kBytes, st>>>(qdo, tmK, tmV, p);
+    attn_bwd_dkv_kernel<8><<<n_tiles, kBwdThreads, DkvSmem::kBytes, st>>>(qdo, staged, tmK, tmV, p);
   }
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;

@@ -43,6 +43,7 @@ struct AttnFwdParams {
   int cp_zigzag;            // NSRC > 1: 1 = rank c holds chunks c and 2*cp-1-c; 0 = chunk c on rank c
   int q_rows_box;           // 128 (training / prefill) or 8 (decode: at most 8 query rows per tile)
   const int* page_table;    // paged KV cache: see cp_locate; null = contiguous KV
+  CpStage stage;            // context parallel: remote K/V blocks are copied here once (rows = 0: off)
   int* status;
 };
 
@@ -90,7 +91,7 @@ __device__ __forceinline__ void cp_locate(const AttnFwdParams& p, const AttnTile
 template <int NSRC>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ KvMaps<NSRC> kv,
-                const AttnFwdParams p) {
+                const __grid_constant__ KvMaps<1> staged, const AttnFwdParams p) {
   griddep_sync();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -108,6 +109,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int n_active = (decode ? 32 : 128) * kSplit;  // softmax threads that take part
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* stage_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
   const uint32_t bar0 = smem_u32(bars);
   auto BAR = [&](int i) { return bar0 + 8u * i; };
 
@@ -115,7 +117,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int lane = threadIdx.x & 31;
 
   const AttnTile t = p.tiles[blockIdx.x];
-  if (t.n_rows <= 0) return;
+  const bool use_stage = NSRC > 1 && p.stage.rows > 0;
+  if (t.n_rows <= 0) {
+    // an empty tile still helps with the staging copies (its threads do nothing else)
+    if (use_stage && warp >= 2) cp_stage_gather(p.stage, threadIdx.x - 64, kAttnThreads - 64, 3, stage_slot);
+    return;
+  }
   int max_kv = t.pos0 + (t.n_rows - 1) * t.pos_step + 1;
   if (max_kv > t.kv_cap) max_kv = t.kv_cap;
   const int nblk = (max_kv + kAttnBlock - 1) / kAttnBlock;
@@ -164,14 +171,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         int src, row;
         cp_locate(p, t, b, src, row);
         if (NSRC == 1) src = 0;
+        const CUtensorMap* mk = &kv.k[src];
+        const CUtensorMap* mv = &kv.v[src];
+        if (use_stage && src != p.stage.rank) {
+          // remote block: read the local copy once it has landed
+          if (!cp_stage_wait(p.stage, src, row / kAttnBlock, abort_flag, p.status, 212)) break;
+          row += src * p.stage.rows;
+          mk = &staged.k[0];
+          mv = &staged.v[0];
+        }
         if (!mbar_wait(BAR(K_EMPTY + s), ph ^ 1, abort_flag, p.status, 201)) break;
         mbar_expect_tx(BAR(K_FULL + s), kTileBytes);
-        tma_load_2d(sK + s * kTileBytes, &kv.k[src], t.kv_col0, row, BAR(K_FULL + s));
-        tma_load_2d(sK + s * kTileBytes + kHalfBytes, &kv.k[src], t.kv_col0 + 64, row, BAR(K_FULL + s));
+        tma_load_2d(sK + s * kTileBytes, mk, t.kv_col0, row, BAR(K_FULL + s));
+        tma_load_2d(sK + s * kTileBytes + kHalfBytes, mk, t.kv_col0 + 64, row, BAR(K_FULL + s));
         if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1, abort_flag, p.status, 202)) break;
         mbar_expect_tx(BAR(V_FULL + s), kTileBytes);
-        tma_load_2d(sV + s * kTileBytes, &kv.v[src], t.kv_col0, row, BAR(V_FULL + s));
-        tma_load_2d(sV + s * kTileBytes + kHalfBytes, &kv.v[src], t.kv_col0 + 64, row, BAR(V_FULL + s));
+        tma_load_2d(sV + s * kTileBytes, mv, t.kv_col0, row, BAR(V_FULL + s));
+        tma_load_2d(sV + s * kTileBytes + kHalfBytes, mv, t.kv_col0 + 64, row, BAR(V_FULL + s));
       }
     }
   } else if (warp == 1) {
@@ -232,6 +248,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     int kv_len = t.pos0 + r * t.pos_step + 1;
     if (kv_len > t.kv_cap) kv_len = t.kv_cap;
     if (r >= t.n_rows) kv_len = 0;
+    // context parallel with staging: the compute warps first help copy the remote K/V blocks
+    // (the CTAs that start first do all of it; later ones find the work counter exhausted)
+    if (use_stage && !decode) cp_stage_gather(p.stage, threadIdx.x - 64, kAttnThreads - 64, 3, stage_slot);
     float m_run = -INFINITY, l_part = 0.f;
     float o[32];
 #pragma unroll
@@ -349,8 +368,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 }
 
 template <int NSRC>
-static int launch_attn_fwd(const CUtensorMap& tmQ, const KvMaps<NSRC>& kv, const AttnFwdParams& p,
-                           cudaStream_t stream) {
+static int launch_attn_fwd(const CUtensorMap& tmQ, const KvMaps<NSRC>& kv, const KvMaps<1>& staged,
+                           const AttnFwdParams& p, cudaStream_t stream) {
   auto kfn = attn_fwd_kernel<NSRC>;
   static bool attr_set[64] = {false};
   int dev = 0;
@@ -360,7 +379,7 @@ static int launch_attn_fwd(const CUtensorMap& tmQ, const KvMaps<NSRC>& kv, const
                                         AttnFwdSmem::kBytes));
     attr_set[dev & 63] = true;
   }
-  RLK_CHECK_CUDA(launch_pdl(kfn, dim3(p.n_tiles), dim3(kAttnThreads), AttnFwdSmem::kBytes, stream, tmQ, kv, p));
+  RLK_CHECK_CUDA(launch_pdl(kfn, dim3(p.n_tiles), dim3(kAttnThreads), AttnFwdSmem::kBytes, stream, tmQ, kv, staged, p));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
@@ -373,6 +392,9 @@ static int launch_attn_fwd(const CUtensorMap& tmQ, const KvMaps<NSRC>& kv, const
 // and selects the small-Q layout; the per-row arithmetic is unchanged.
 // page_table (device int32, may be null): tiles with reserved > 0 read their KV blocks through it
 // (see cp_locate); entries must name source ranks < n_src.
+// stage_rows > 0 (context parallel only): the first stage_rows rows of every peer's K / V are
+// copied once into stage_k / stage_v ([n_src * stage_rows, kv_cols]) by the kernel itself and
+// remote blocks are read from there; stage_flags holds n_src * stage_rows / 128 * 2 + 1 ints.
 // n_src == 1: k_ptrs/v_ptrs hold one pointer each.  n_src in 2..8 (context parallel): pointer s
 // is rank s's K / V buffer (same shape and pitch on every rank), mapped into this process.
 RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long long ldq,
@@ -380,7 +402,8 @@ RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long
                          long long kv_rows, long long kv_cols, long long ldkv, void* O,
                          long long ldo, float* lse, const void* tiles, int n_tiles, float scale,
                          int cp_blocks_per_chunk, int cp_zigzag, int decode_rows,
-                         const int* page_table, void* stream) {
+                         const int* page_table, void* stage_k, void* stage_v, int* stage_flags,
+                         int stage_rows, int cp_rank, void* stream) {
   using namespace rlk;
   RLK_REQUIRE(n_tiles > 0, "attn_fwd: no tiles");
   RLK_REQUIRE(n_src == 1 || (n_src >= 2 && n_src <= 8), "attn_fwd: n_src must be 1..8");
@@ -409,7 +432,7 @@ RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long
     KvMaps<1> kv;
     if ((rc = make_tmap_2d_sw128(&kv.k[0], k_ptrs[0], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
     if ((rc = make_tmap_2d_sw128(&kv.v[0], v_ptrs[0], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
-    return launch_attn_fwd<1>(tmQ, kv, p, s);
+    return launch_attn_fwd<1>(tmQ, kv, kv, p, s);
   }
   KvMaps<8> kv;
   for (int i = 0; i < 8; ++i) {
@@ -417,5 +440,31 @@ RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long
     if ((rc = make_tmap_2d_sw128(&kv.k[i], k_ptrs[j], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
     if ((rc = make_tmap_2d_sw128(&kv.v[i], v_ptrs[j], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
   }
-  return launch_attn_fwd<8>(tmQ, kv, p, s);
+  KvMaps<1> staged;
+  staged.k[0] = kv.k[0];
+  staged.v[0] = kv.v[0];
+  if (stage_rows > 0) {
+    // remote K/V blocks are copied once into [n_src * stage_rows, kv_cols] buffers of this GPU
+    RLK_REQUIRE(stage_k && stage_v && stage_flags, "attn_fwd: staging buffers missing");
+    RLK_REQUIRE(stage_rows % 128 == 0 && stage_rows <= kv_rows && ldkv == kv_cols && page_table == nullptr,
+                "attn_fwd: staging needs 128-row multiples, contiguous K/V rows and no page table");
+    RLK_REQUIRE(cp_rank >= 0 && cp_rank < n_src, "attn_fwd: bad cp_rank");
+    CpStage& st = p.stage;
+    for (int i = 0; i < 8; ++i) {
+      st.src_a[i] = static_cast<const unsigned char*>(k_ptrs[i < n_src ? i : 0]);
+      st.src_b[i] = static_cast<const unsigned char*>(v_ptrs[i < n_src ? i : 0]);
+    }
+    st.dst_a = static_cast<unsigned char*>(stage_k);
+    st.dst_b = static_cast<unsigned char*>(stage_v);
+    st.flags = stage_flags;
+    st.rows = stage_rows;
+    st.row_bytes_a = st.row_bytes_b = static_cast<int>(kv_cols * 2);
+    st.ranks = n_src;
+    st.rank = cp_rank;
+    const long long total = static_cast<long long>(n_src) * stage_rows;
+    if ((rc = make_tmap_2d_sw128(&staged.k[0], stage_k, total, kv_cols, kv_cols, 128, 64, 2))) return rc;
+    if ((rc = make_tmap_2d_sw128(&staged.v[0], stage_v, total, kv_cols, kv_cols, 128, 64, 2))) return rc;
+    RLK_CHECK_CUDA(cudaMemsetAsync(stage_flags, 0, sizeof(int) * (n_src * (stage_rows / 128) * 2 + 1), s));
+  }
+  return launch_attn_fwd<8>(tmQ, kv, staged, p, s);
 }

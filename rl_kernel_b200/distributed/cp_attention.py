@@ -2,10 +2,14 @@
 
 Every CP rank keeps the tensors its peers need (K, V for the forward and the dQ kernel; Q, dO, lse
 and delta for the dK/dV kernel) in buffers that the peers have mapped (CUDA IPC over NVLink).  A
-kernel walks the canonical 128-token blocks of its work item in ascending order and loads each one
-straight from the rank that owns it with a plain (non-multicast) TMA load through that peer's tensor
-map (csrc/attention/attn_fwd_sm100.cu and attn_bwd_sm100.cu, NSRC = 8).  Nothing is gathered
-beforehand and nothing is merged or reduce-scattered afterwards: every query row (forward, dQ) and
+kernel walks the canonical 128-token blocks of its work item in ascending order.  Remote blocks
+reach it in one of two ways, both inside the same kernel launch (csrc/attention/attn_fwd_sm100.cu,
+attn_bwd_sm100.cu, NSRC = 8): with ``stage_remote`` (default) the compute warps of the CTAs that
+start first copy every remote block once into a local staging buffer (16-byte peer loads, work
+items from an atomic counter, a ready flag per block) and the TMA producers read the local copy
+after a bounded wait on the flag -- a block crosses NVLink once however many tiles use it; without
+it every tile loads the block straight from its owner with a plain (non-multicast) TMA load through
+that peer's tensor map.  Nothing is merged or reduce-scattered afterwards: every query row (forward, dQ) and
 every key row (dK, dV) executes exactly the single-GPU program, so outputs and gradients are bitwise
 equal to CP = 1 for every CP degree and layout.  (The reference all-gathers Q/K/V, lets every rank
 compute the whole sequence and scatters rank 0's result, and reduce-scatters dK/dV:
@@ -83,7 +87,8 @@ class PeerMappedBuffers:
 
 class CPAttention:
     def __init__(self, collective, device: torch.device, *, num_q_heads: int, num_kv_heads: int, head_dim: int = 128,
-                 max_local_tokens: int, layout: str = "zigzag", with_backward: bool = True):
+                 max_local_tokens: int, layout: str = "zigzag", with_backward: bool = True,
+                 stage_remote: bool = True):
         if layout not in ("zigzag", "contiguous"):
             raise ValueError(layout)
         if head_dim != 128:
@@ -101,6 +106,17 @@ class CPAttention:
         self.bufs = PeerMappedBuffers(collective.group, device, specs)
         self.k_bufs, self.v_bufs = self.bufs["k"], self.bufs["v"]
         self._tiles: dict = {}
+        # Local copies of the peers' blocks: the kernels fill them themselves, once per call, so a
+        # remote block crosses NVLink once instead of once per tile that needs it.
+        self.stage_remote = stage_remote
+        if stage_remote:
+            R = (T + 127) // 128 * 128
+            z = lambda cols: torch.zeros(self.cp * R, cols, dtype=bf16, device=device)  # noqa: E731
+            self._st_k, self._st_v = z(num_kv_heads * head_dim), z(num_kv_heads * head_dim)
+            self._st_flags = torch.zeros(self.cp * (R // 128) * 2 + 1, dtype=torch.int32, device=device)
+            if with_backward:
+                self._st_q, self._st_do = z(num_q_heads * head_dim), z(num_q_heads * head_dim)
+                self._st_flags2 = torch.zeros_like(self._st_flags)
 
     # ------------------------------------------------------------------ geometry
     def local_positions(self, seq_len: int) -> torch.Tensor:
@@ -143,6 +159,11 @@ class CPAttention:
         self._tiles[key] = out
         return out
 
+    def _stage_kv(self, T: int):
+        if not self.stage_remote:
+            return None
+        return (self._st_k, self._st_v, self._st_flags, (T + 127) // 128 * 128, self.rank)
+
     # ------------------------------------------------------------------ in-place API (engine)
     def forward_inplace(self, q_local: torch.Tensor, out: torch.Tensor, lse: torch.Tensor | None, nseq: int,
                         seq_len: int) -> None:
@@ -150,7 +171,7 @@ class CPAttention:
         tiles, _, bpc = self.tiles_for(nseq, seq_len)
         self.coll.barrier()                                  # every rank's K/V is in place and visible
         nv.attn_fwd(q_local, self.k_bufs, self.v_bufs, out, lse, tiles, self.scale, cp_blocks_per_chunk=bpc,
-                    cp_zigzag=self.layout == "zigzag")
+                    cp_zigzag=self.layout == "zigzag", stage=self._stage_kv(q_local.shape[0]))
         self.coll.barrier()                                  # nobody overwrites K/V while a peer still reads
 
     def backward_inplace(self, dq: torch.Tensor, dk: torch.Tensor, dv: torch.Tensor, nseq: int, seq_len: int) -> None:
@@ -161,9 +182,13 @@ class CPAttention:
         zz = self.layout == "zigzag"
         self.coll.barrier()
         nv.attn_bwd_dq(b.local("q")[:T], b.local("do")[:T], self.k_bufs, self.v_bufs, b.local("lse"),
-                       b.local("delta"), dq, tiles, self.scale, cp_blocks_per_chunk=bpc, cp_zigzag=zz)
+                       b.local("delta"), dq, tiles, self.scale, cp_blocks_per_chunk=bpc, cp_zigzag=zz,
+                       stage=self._stage_kv(T))
+        st_q = None
+        if self.stage_remote:
+            st_q = (self._st_q, self._st_do, self._st_flags2, (T + 127) // 128 * 128, self.rank)
         nv.attn_bwd_dkv(b["q"], b["do"], b.local("k"), b.local("v"), b["lse"], b["delta"], dk, dv, kvtiles,
-                        self.scale, cp_blocks_per_chunk=bpc, cp_zigzag=zz)
+                        self.scale, cp_blocks_per_chunk=bpc, cp_zigzag=zz, stage=st_q)
         self.coll.barrier()
 
     # ------------------------------------------------------------------ copying API
