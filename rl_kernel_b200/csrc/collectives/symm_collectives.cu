@@ -106,13 +106,12 @@ __device__ __forceinline__ uint4 tree_node(const uint4 a, const uint4 b) {
 // the engine needs -- activations of a decode step or a training micro-batch).
 // staged != 0: the payload already sits in the local frame (a GEMM wrote it there).
 template <int DT>
-__global__ void __launch_bounds__(kCollThreads)
-all_reduce_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
-                  long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int staged, int* status) {
+__device__ __forceinline__ void all_reduce_kernel_body(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                  long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int staged, int* status, int bx, int gx) {
   const unsigned long long seq = effective_seq(w, base_seq);
   const int nslices = static_cast<int>((nbytes + slice_bytes - 1) / slice_bytes);
   unsigned char* mine = frame_ptr(w.win[w.rank], w.frame_bytes, frame);
-  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+  for (int s = bx; s < nslices; s += gx) {
     const long long off = static_cast<long long>(s) * slice_bytes;
     const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), nbytes - off) / 16);
     if (!staged)
@@ -134,6 +133,13 @@ all_reduce_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsi
       reinterpret_cast<uint4*>(dst + off)[i] = v[0];
     }
   }
+}
+
+template <int DT>
+__global__ void __launch_bounds__(kCollThreads)
+all_reduce_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                  long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int staged, int* status) {
+  all_reduce_kernel_body<DT>(w, src, dst, nbytes, slice_bytes, frame, base_seq, staged, status, blockIdx.x, gridDim.x);
 }
 
 // Publish / wait for a single flag word of one slice (thread 0 of the CTA does the memory ops).
@@ -173,15 +179,14 @@ __device__ __forceinline__ bool slice_wait(const SymmWorld& w, int slice, unsign
 // kernel's.  Uses two flag values: seq_a = "my partial of this slice is in my frame",
 // seq_b = "the reduced slice is in the owner's frame".
 template <int DT, int W>
-__global__ void __launch_bounds__(kCollThreads)
-all_reduce_2shot_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
-                        long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int* status) {
+__device__ __forceinline__ void all_reduce_2shot_kernel_body(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                        long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int* status, int bx, int gx) {
   const unsigned long long seq_a = effective_seq(w, base_seq), seq_b = seq_a + 1;
   const int nslices = static_cast<int>((nbytes + slice_bytes - 1) / slice_bytes);
   unsigned char* mine = frame_ptr(w.win[w.rank], w.frame_bytes, frame);
   constexpr int U = 16 / W;   // independent 16-byte loads in flight per thread and rank
   // ---- phase 1: stage my partial of every slice this CTA handles
-  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+  for (int s = bx; s < nslices; s += gx) {
     const long long off = static_cast<long long>(s) * slice_bytes;
     const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), nbytes - off) / 16);
     if (s % W != w.rank)   // the owner reads its own partial straight from src
@@ -190,7 +195,7 @@ all_reduce_2shot_kernel(const SymmWorld w, const unsigned char* __restrict__ src
     slice_publish(w, s, seq_a);
   }
   // ---- phase 2: reduce the slices I own
-  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+  for (int s = bx; s < nslices; s += gx) {
     if (s % W != w.rank) continue;
     const long long off = static_cast<long long>(s) * slice_bytes;
     const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), nbytes - off) / 16);
@@ -224,7 +229,7 @@ all_reduce_2shot_kernel(const SymmWorld w, const unsigned char* __restrict__ src
     slice_publish(w, s, seq_b);
   }
   // ---- phase 3: fetch the slices the others reduced
-  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+  for (int s = bx; s < nslices; s += gx) {
     const int owner = s % W;
     if (owner == w.rank) continue;
     const long long off = static_cast<long long>(s) * slice_bytes;
@@ -247,19 +252,25 @@ all_reduce_2shot_kernel(const SymmWorld w, const unsigned char* __restrict__ src
   }
 }
 
+template <int DT, int W>
+__global__ void __launch_bounds__(kCollThreads)
+all_reduce_2shot_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                        long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int* status) {
+  all_reduce_2shot_kernel_body<DT, W>(w, src, dst, nbytes, slice_bytes, frame, base_seq, status, blockIdx.x, gridDim.x);
+}
+
 // Reduce-scatter: the payload is `world` equal ranges; rank r ends with the balanced-tree sum of
 // range r (dst holds per_rank bytes).  Every rank stages the ranges it does not own in its frame,
 // the owner of a range pulls the peers' copies slice by slice -- half of the two-shot all-reduce.
 template <int DT, int W>
-__global__ void __launch_bounds__(kCollThreads)
-reduce_scatter_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
-                      long long per_rank, int slice_bytes, int frame, unsigned long long base_seq, int* status) {
+__device__ __forceinline__ void reduce_scatter_kernel_body(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                      long long per_rank, int slice_bytes, int frame, unsigned long long base_seq, int* status, int bx, int gx) {
   const unsigned long long seq = effective_seq(w, base_seq);
   const int spr = static_cast<int>((per_rank + slice_bytes - 1) / slice_bytes);   // slices per range
   const int nslices = spr * W;
   unsigned char* mine = frame_ptr(w.win[w.rank], w.frame_bytes, frame);
   constexpr int U = 16 / W;
-  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+  for (int s = bx; s < nslices; s += gx) {
     const int owner = s / spr;
     const long long in_range = static_cast<long long>(s % spr) * slice_bytes;
     const long long off = owner * per_rank + in_range;
@@ -271,7 +282,7 @@ reduce_scatter_kernel(const SymmWorld w, const unsigned char* __restrict__ src, 
   }
   for (int i = 0; i < spr; ++i) {
     const int s = w.rank * spr + i;
-    if (s % gridDim.x != blockIdx.x) continue;
+    if (s % gx != bx) continue;
     const long long in_range = static_cast<long long>(i) * slice_bytes;
     const long long off = w.rank * per_rank + in_range;
     const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), per_rank - in_range) / 16);
@@ -303,16 +314,22 @@ reduce_scatter_kernel(const SymmWorld w, const unsigned char* __restrict__ src, 
   }
 }
 
+template <int DT, int W>
+__global__ void __launch_bounds__(kCollThreads)
+reduce_scatter_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                      long long per_rank, int slice_bytes, int frame, unsigned long long base_seq, int* status) {
+  reduce_scatter_kernel_body<DT, W>(w, src, dst, per_rank, slice_bytes, frame, base_seq, status, blockIdx.x, gridDim.x);
+}
+
 // All-gather: dst[r] = rank r's payload (rank order).  Every CTA first stages and publishes all of
 // its slices, then pulls the peers' copies with eight 16-byte loads in flight per thread, so the
 // NVLink round trip is paid once per batch of loads instead of once per load.
-__global__ void __launch_bounds__(kCollThreads)
-all_gather_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
-                  long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int* status) {
+__device__ __forceinline__ void all_gather_kernel_body(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                  long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int* status, int bx, int gx) {
   const unsigned long long seq = effective_seq(w, base_seq);
   const int nslices = static_cast<int>((nbytes + slice_bytes - 1) / slice_bytes);
   unsigned char* mine = frame_ptr(w.win[w.rank], w.frame_bytes, frame);
-  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+  for (int s = bx; s < nslices; s += gx) {
     const long long off = static_cast<long long>(s) * slice_bytes;
     const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), nbytes - off) / 16);
     for (int i = threadIdx.x; i < n16; i += blockDim.x) {
@@ -323,7 +340,7 @@ all_gather_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsi
     slice_publish(w, s, seq);
   }
   const unsigned others = ((1u << w.world) - 1u) & ~(1u << w.rank);
-  for (int s = blockIdx.x; s < nslices; s += gridDim.x) {
+  for (int s = bx; s < nslices; s += gx) {
     const long long off = static_cast<long long>(s) * slice_bytes;
     const int n16 = static_cast<int>(min(static_cast<long long>(slice_bytes), nbytes - off) / 16);
     if (!slice_wait(w, s, seq, others, status, 402)) continue;
@@ -346,6 +363,32 @@ all_gather_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsi
       }
     }
   }
+}
+
+__global__ void __launch_bounds__(kCollThreads)
+all_gather_kernel(const SymmWorld w, const unsigned char* __restrict__ src, unsigned char* __restrict__ dst,
+                  long long nbytes, int slice_bytes, int frame, unsigned long long base_seq, int* status) {
+  all_gather_kernel_body(w, src, dst, nbytes, slice_bytes, frame, base_seq, status, blockIdx.x, gridDim.x);
+}
+
+// Single-GPU emulation of a W-rank group for testing the W = 4 and W = 8 code paths without W
+// GPUs: all ranks' windows live on this device and ONE cooperative kernel runs every rank's CTAs
+// (blockIdx.y = rank), so the CTAs that wait on one another are guaranteed to be resident together.
+// mode: 0 one-shot all-reduce, 1 two-shot all-reduce, 2 reduce-scatter, 3 all-gather.
+struct EmulArgs {
+  SymmWorld w[kMaxRanks];
+  const unsigned char* src[kMaxRanks];
+  unsigned char* dst[kMaxRanks];
+};
+
+template <int DT, int W>
+__global__ void __launch_bounds__(kCollThreads)
+emulate_kernel(const EmulArgs a, int mode, long long nbytes, int slice_bytes, int* status) {
+  const int r = blockIdx.y;
+  if (mode == 0) all_reduce_kernel_body<DT>(a.w[r], a.src[r], a.dst[r], nbytes, slice_bytes, 1, 1ull, 0, status, blockIdx.x, gridDim.x);
+  else if (mode == 1) all_reduce_2shot_kernel_body<DT, W>(a.w[r], a.src[r], a.dst[r], nbytes, slice_bytes, 1, 1ull, status, blockIdx.x, gridDim.x);
+  else if (mode == 2) reduce_scatter_kernel_body<DT, W>(a.w[r], a.src[r], a.dst[r], nbytes / W, slice_bytes, 1, 1ull, status, blockIdx.x, gridDim.x);
+  else all_gather_kernel_body(a.w[r], a.src[r], a.dst[r], nbytes, slice_bytes, 1, 1ull, status, blockIdx.x, gridDim.x);
 }
 
 // Bounded barrier across ranks: everyone publishes seq in slice 0 of a dedicated flag row.
@@ -588,5 +631,53 @@ RLK_API int rlk_symm_graph_replayed(void* state, long long times) {
 RLK_API long long rlk_symm_get_seq(void* state) { return static_cast<long long>(static_cast<SymmState*>(state)->seq); }
 RLK_API int rlk_symm_set_seq(void* state, long long seq) {
   static_cast<SymmState*>(state)->seq = static_cast<unsigned long long>(seq);
+  return RLK_OK;
+}
+
+// Test entry: runs `mode` for a group of `world` emulated ranks on the current device.  srcs / dsts
+// hold one device pointer per rank (all-reduce: nbytes each; reduce-scatter: dst nbytes / world;
+// all-gather: dst world * nbytes).  Allocates and frees its own windows; synchronises the stream.
+RLK_API int rlk_symm_emulate(int world, int mode, long long nbytes, int dtype, void* const* srcs,
+                             void* const* dsts, void* stream) {
+  RLK_REQUIRE(world == 2 || world == 4 || world == 8, "symm_emulate: world must be 2, 4 or 8");
+  RLK_REQUIRE(mode >= 0 && mode <= 3 && nbytes > 0 && nbytes % (16 * world) == 0, "symm_emulate: bad arguments");
+  RLK_REQUIRE(dtype == 0 || dtype == 1, "symm_emulate: dtype must be 0 (bf16) or 1 (fp32)");
+  const long long frame_bytes = (nbytes + 255) / 256 * 256;
+  EmulArgs a{};
+  unsigned char* wins[kMaxRanks] = {nullptr};
+  for (int r = 0; r < world; ++r) {
+    RLK_CHECK_CUDA(cudaMalloc(&wins[r], rlk_symm_window_bytes(frame_bytes)));
+    RLK_CHECK_CUDA(cudaMemset(wins[r], 0, kFlagBytes));
+  }
+  for (int r = 0; r < world; ++r) {
+    for (int q = 0; q < kMaxRanks; ++q) a.w[r].win[q] = wins[q < world ? q : 0];
+    a.w[r].world = world;
+    a.w[r].rank = r;
+    a.w[r].frame_bytes = frame_bytes;
+    a.w[r].epoch = nullptr;
+    a.w[r].use_epoch = 0;
+    a.src[r] = static_cast<const unsigned char*>(srcs[r]);
+    a.dst[r] = static_cast<unsigned char*>(dsts[r]);
+  }
+  long long payload = mode == 2 ? nbytes / world : nbytes;
+  long long sb = kMinSliceBytes;
+  while (((payload + sb - 1) / sb) * (mode == 2 ? world : 1) > 1024) sb *= 2;
+  const long long nsl = ((payload + sb - 1) / sb) * (mode == 2 ? world : 1);
+  // every CTA of every rank must be resident at once: a small grid per rank
+  int gx = static_cast<int>(nsl < 8 ? nsl : 8);
+  int slice = static_cast<int>(sb);
+  int* stw = device_status_word();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  void* args[] = {&a, &mode, &nbytes, &slice, &stw};
+  const void* fn = nullptr;
+#define RLK_EMUL(DT, WW) fn = reinterpret_cast<const void*>(&emulate_kernel<DT, WW>)
+  if (dtype == 0) { if (world == 2) RLK_EMUL(0, 2); else if (world == 4) RLK_EMUL(0, 4); else RLK_EMUL(0, 8); }
+  else { if (world == 2) RLK_EMUL(1, 2); else if (world == 4) RLK_EMUL(1, 4); else RLK_EMUL(1, 8); }
+#undef RLK_EMUL
+  cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(gx, world), dim3(kCollThreads), args, 0, st);
+  cudaError_t e2 = cudaStreamSynchronize(st);
+  for (int r = 0; r < world; ++r) cudaFree(wins[r]);
+  RLK_CHECK_CUDA(e);
+  RLK_CHECK_CUDA(e2);
   return RLK_OK;
 }

@@ -346,3 +346,35 @@ def test_exact_fp32_sum_of_squares_matches_cpu_bins():
     assert torch.equal(gpu.cpu(), cpu), "integer bins must be exact and independent of the partition"
     ref = x.double().pow(2).sum().sqrt().item()
     assert abs(norm_from_bins_f32(gpu).item() - ref) <= 1e-12 * ref
+
+
+@pytest.mark.parametrize("world", [4, 8])
+def test_collective_kernels_for_4_and_8_ranks_emulated_on_one_gpu(world):
+    """The 4- and 8-rank instantiations of the collective kernels, run as one cooperative kernel over
+    all ranks' windows on a single GPU, against the balanced tree computed with torch."""
+    import ctypes
+
+    from rl_kernel_b200.backends import extension as ext
+    from rl_kernel_b200.distributed import balanced_tree_sum
+
+    lib = ext.load()
+    n = 8 * world * 1031 * 4                       # elements: multiple of 8 * world, not of the slice size
+    for dtype, code in ((torch.bfloat16, 0), (torch.float32, 1)):
+        parts = [torch.randn(n, device=dev()).to(dtype) for _ in range(world)]
+        want = balanced_tree_sum(parts, dtype)
+        nbytes = n * parts[0].element_size()
+        for mode in (0, 1, 2, 3):
+            size = {0: n, 1: n, 2: n // world, 3: n * world}[mode]
+            outs = [torch.zeros(size, device=dev(), dtype=dtype) for _ in range(world)]
+            srcs = (ctypes.c_void_p * world)(*[t.data_ptr() for t in parts])
+            dsts = (ctypes.c_void_p * world)(*[t.data_ptr() for t in outs])
+            ext.check(lib.rlk_symm_emulate(ctypes.c_int(world), ctypes.c_int(mode), ctypes.c_longlong(nbytes),
+                                           ctypes.c_int(code), srcs, dsts, ext.stream_ptr(dev())), "symm_emulate")
+            sync_and_check()
+            for r in range(world):
+                if mode in (0, 1):
+                    assert torch.equal(outs[r], want), (world, dtype, mode, r)
+                elif mode == 2:
+                    assert torch.equal(outs[r], want[r * size:(r + 1) * size]), (world, dtype, mode, r)
+                else:
+                    assert torch.equal(outs[r], torch.cat(parts)), (world, dtype, mode, r)
