@@ -46,6 +46,24 @@ def _rowmajor2d(t: torch.Tensor, name: str) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------------------------- GEMM
+def det_gemm_split_leaves(a: torch.Tensor, b: torch.Tensor, scratch: torch.Tensor, *, nchunks: int,
+                          tile_n: int = 64) -> int:
+    """The chunked few-row GEMM without its tree pass: ``scratch`` [nchunks, M, N] receives one bf16
+    partial result per canonical K chunk; returns the element stride between chunks.  The consumer
+    (``rmsnorm_fwd_leaves``) evaluates the tree while it loads."""
+    _bf16(a, "a"); _bf16(b, "b"); _bf16(scratch, "scratch")
+    M, K = a.shape
+    N = b.shape[0]
+    if scratch.numel() < nchunks * M * N:
+        raise ValueError("det_gemm_split_leaves: scratch too small")
+    rc = _lib().rlk_det_gemm_split(ext.ptr(a), ext.ptr(b), c_void_p(0), ext.ptr(scratch), c_int(M), c_int(N),
+                                   c_int(K), _ll(a.stride(0)), _ll(b.stride(0)), _ll(N), c_int(nchunks),
+                                   c_int(tile_n), ext.stream_ptr(a.device))
+    ext.check(rc, "det_gemm_split_leaves")
+    _count()
+    return M * N
+
+
 def det_gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, M: int, N: int, K: int,
              a_mn: bool = False, b_mn: bool = False, nchunks: int = 1, tile_n: int = 0,
              accumulate: bool = False) -> torch.Tensor:
@@ -208,6 +226,16 @@ def rmsnorm_fwd(x, w, y, eps: float, *, res=None, res_out=None, rstd_out=None) -
                                 ext.ptr(rstd_out), c_int(rows), c_int(H), c_float(eps),
                                 ext.stream_ptr(x.device))
     ext.check(rc, "rmsnorm_fwd")
+    _count()
+
+
+def rmsnorm_fwd_leaves(leaves, chunk_stride: int, nchunks: int, res, w, y, res_out, eps: float) -> None:
+    """y = rmsnorm(tree(leaves) + res) * w; res_out = tree(leaves) + res (see det_gemm_split_leaves)."""
+    rows, H = y.shape
+    rc = _lib().rlk_rmsnorm_fwd_leaves(ext.ptr(leaves), _ll(chunk_stride), c_int(nchunks), ext.ptr(res), ext.ptr(w),
+                                       ext.ptr(y), ext.ptr(res_out), c_int(rows), c_int(H), c_float(eps),
+                                       ext.stream_ptr(y.device))
+    ext.check(rc, "rmsnorm_fwd_leaves")
     _count()
 
 

@@ -733,6 +733,8 @@ RLK_API long long rlk_det_gemm_split_scratch_elems(int M, long long ldc, int nch
   return static_cast<long long>(nchunks) * M * ldc;
 }
 
+// C == nullptr: only the leaves are produced (scratch [nchunks][M][ldc]); the caller folds the tree
+// into its next kernel (rlk_rmsnorm_fwd_leaves).
 RLK_API int rlk_det_gemm_split(const void* A, const void* B, void* C, void* scratch, int M, int N,
                                int K, long long lda, long long ldb, long long ldc, int nchunks,
                                int tile_n, void* stream) {
@@ -741,7 +743,7 @@ RLK_API int rlk_det_gemm_split(const void* A, const void* B, void* C, void* scra
   RLK_REQUIRE(nchunks == 2 || nchunks == 4 || nchunks == 8, "det_gemm_split: nchunks must be 2, 4 or 8");
   RLK_REQUIRE(K % (nchunks * 64) == 0, "det_gemm_split: K/nchunks must be a multiple of 64");
   RLK_REQUIRE((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 &&
-                  (ldc * 2) % 16 == 0, "det_gemm_split: C and scratch must be 16-byte aligned");
+                  scratch != nullptr && (ldc * 2) % 16 == 0, "det_gemm_split: C and scratch must be 16-byte aligned");
   GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.nchunks = 1;
@@ -756,6 +758,7 @@ RLK_API int rlk_det_gemm_split(const void* A, const void* B, void* C, void* scra
   else if (tile_n == 128) rc = launch_gemm<128, false, false>(A, B, p, lda, ldb, s);
   else rc = launch_gemm<64, false, false>(A, B, p, lda, ldb, s);
   if (rc) return rc;
+  if (C == nullptr) return RLK_OK;
   const long long n = static_cast<long long>(M) * (N / 8);
   RLK_CHECK_CUDA(launch_pdl(chunk_tree_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s,
                             static_cast<const __nv_bfloat16*>(scratch), p.split_stride, static_cast<__nv_bfloat16*>(C), M, N, ldc, nchunks));

@@ -32,12 +32,16 @@ constexpr int kNormWarps = 8;
 constexpr int kRowThreads = 128;
 constexpr int kMaxChunks = 8;
 
-template <bool HAS_RES>
+// NCH > 1: `x` holds NCH canonical K-chunk partial results (leaves) of a row-parallel GEMM,
+// chunk_stride elements apart; the balanced bf16 tree over them (the GEMM's own chunk tree:
+// node = bf16(fp32 a + fp32 b)) is evaluated while loading, so the separate tree pass and its
+// round trip through memory disappear.
+template <bool HAS_RES, int NCH>
 __global__ void __launch_bounds__(kRowThreads)
 rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
                    const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                    __nv_bfloat16* __restrict__ res_out, float* __restrict__ rstd_out, int rows,
-                   int H, float eps) {
+                   int H, float eps, long long chunk_stride) {
   griddep_sync();
   __shared__ float swarp[4];
   const int row = blockIdx.x;
@@ -50,6 +54,24 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   float ss = 0.f;
   auto load_chunk = [&](int c) -> uint4 {
     uint4 v = xr[c];
+    if (NCH > 1) {
+      uint4 leaf[NCH > 1 ? NCH : 1];
+      leaf[0] = v;
+#pragma unroll
+      for (int k = 1; k < NCH; ++k)
+        leaf[k] = *reinterpret_cast<const uint4*>(x + k * chunk_stride + static_cast<long long>(row) * H + c * 8);
+#pragma unroll
+      for (int n = NCH; n > 1; n >>= 1)
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+          const uint4 a = leaf[2 * i], b = leaf[2 * i + 1];
+          leaf[i].x = pack_bf16x2(__fadd_rn(bf16_lo(a.x), bf16_lo(b.x)), __fadd_rn(bf16_hi(a.x), bf16_hi(b.x)));
+          leaf[i].y = pack_bf16x2(__fadd_rn(bf16_lo(a.y), bf16_lo(b.y)), __fadd_rn(bf16_hi(a.y), bf16_hi(b.y)));
+          leaf[i].z = pack_bf16x2(__fadd_rn(bf16_lo(a.z), bf16_lo(b.z)), __fadd_rn(bf16_hi(a.z), bf16_hi(b.z)));
+          leaf[i].w = pack_bf16x2(__fadd_rn(bf16_lo(a.w), bf16_lo(b.w)), __fadd_rn(bf16_hi(a.w), bf16_hi(b.w)));
+        }
+      v = leaf[0];
+    }
     if (HAS_RES) {
       const uint4 q = rr[c];
       v.x = pack_bf16x2(bf16_lo(v.x) + bf16_lo(q.x), bf16_hi(v.x) + bf16_hi(q.x));
@@ -380,13 +402,36 @@ RLK_API int rlk_rmsnorm_fwd(const void* x, const void* res, const void* w, void*
   const int grid = rows;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (res)
-    RLK_CHECK_CUDA(launch_pdl(rmsnorm_fwd_kernel<true>, dim3(grid), dim3(kRowThreads), 0, s,
+    RLK_CHECK_CUDA(launch_pdl(rmsnorm_fwd_kernel<true, 1>, dim3(grid), dim3(kRowThreads), 0, s,
                               (const __nv_bfloat16*)x, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w,
-                              (__nv_bfloat16*)y, (__nv_bfloat16*)res_out, rstd_out, rows, H, eps));
+                              (__nv_bfloat16*)y, (__nv_bfloat16*)res_out, rstd_out, rows, H, eps, 0ll));
   else
-    RLK_CHECK_CUDA(launch_pdl(rmsnorm_fwd_kernel<false>, dim3(grid), dim3(kRowThreads), 0, s,
+    RLK_CHECK_CUDA(launch_pdl(rmsnorm_fwd_kernel<false, 1>, dim3(grid), dim3(kRowThreads), 0, s,
                               (const __nv_bfloat16*)x, (const __nv_bfloat16*)nullptr, (const __nv_bfloat16*)w,
-                              (__nv_bfloat16*)y, (__nv_bfloat16*)nullptr, rstd_out, rows, H, eps));
+                              (__nv_bfloat16*)y, (__nv_bfloat16*)nullptr, rstd_out, rows, H, eps, 0ll));
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
+}
+
+// y = rmsnorm(tree(leaves) + res) * w where `leaves` holds nchunks (2, 4 or 8) partial results of a
+// row-parallel GEMM, each [rows, H] and chunk_stride elements apart (rlk_det_gemm_split_leaves);
+// res_out receives tree(leaves) + res.  Bitwise the result of the tree pass followed by
+// rlk_rmsnorm_fwd.
+RLK_API int rlk_rmsnorm_fwd_leaves(const void* leaves, long long chunk_stride, int nchunks, const void* res,
+                                   const void* w, void* y, void* res_out, int rows, int H, float eps,
+                                   void* stream) {
+  RLK_REQUIRE(rows > 0 && H > 0 && H % 8 == 0, "rmsnorm_fwd_leaves: H must be a positive multiple of 8");
+  RLK_REQUIRE(res && res_out, "rmsnorm_fwd_leaves: residual input and output are required");
+  RLK_REQUIRE(nchunks == 2 || nchunks == 4 || nchunks == 8, "rmsnorm_fwd_leaves: nchunks must be 2, 4 or 8");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define RLK_RMS_LEAVES(N_)                                                                                    \
+  RLK_CHECK_CUDA(launch_pdl(rmsnorm_fwd_kernel<true, N_>, dim3(rows), dim3(kRowThreads), 0, s,               \
+                            (const __nv_bfloat16*)leaves, (const __nv_bfloat16*)res, (const __nv_bfloat16*)w, \
+                            (__nv_bfloat16*)y, (__nv_bfloat16*)res_out, (float*)nullptr, rows, H, eps, chunk_stride))
+  if (nchunks == 2) RLK_RMS_LEAVES(2);
+  else if (nchunks == 4) RLK_RMS_LEAVES(4);
+  else RLK_RMS_LEAVES(8);
+#undef RLK_RMS_LEAVES
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }

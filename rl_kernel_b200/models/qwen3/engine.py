@@ -277,6 +277,14 @@ class KVCache:
 
 
 @dataclass
+class _Leaves:
+    """Per-chunk partial results of a few-row row-parallel GEMM whose tree the next norm evaluates."""
+    buf: torch.Tensor
+    stride: int
+    nchunks: int
+
+
+@dataclass
 class SharedPrefixKV:
     """KV pool in which the sequences of a GRPO group share their prompt's pages: per layer
     [num_prompts * P + nseq * R_pad, kv_local] rows = prompt region then one response region per
@@ -353,6 +361,22 @@ class Qwen3Engine:
         return nv.det_gemm(a, b, out, M=M, N=N, K=K, a_mn=a_mn, b_mn=b_mn, nchunks=nchunks,
                            accumulate=accumulate)
 
+    fold_tree_into_norm = True     # decode: the chunk tree of o_proj / down is evaluated by the next norm
+
+    def _row_parallel_leaves(self, a, w, name: str, nchunks: int) -> _Leaves:
+        M, N = a.shape[0], w.shape[0]
+        buf = self.ws.get(name, (nchunks * M * N,))
+        stride = nv.det_gemm_split_leaves(a, w, buf, nchunks=nchunks, tile_n=64)
+        return _Leaves(buf, stride, nchunks)
+
+    def _norm_after(self, x, weight, y, res, res_out):
+        """rmsnorm(x + res) where ``x`` may still be in per-chunk form."""
+        eps = self.spec.rms_norm_eps
+        if isinstance(x, _Leaves):
+            nv.rmsnorm_fwd_leaves(x.buf, x.stride, x.nchunks, res, weight, y, res_out, eps)
+        else:
+            nv.rmsnorm_fwd(x, weight, y, eps, res=res, res_out=res_out)
+
     def _row_parallel(self, a, w, out, nchunks: int):
         """Row-parallel projection: local GEMM with canonical chunks, then the fixed-tree sum over TP.
         Many rows: one fused GEMM+all-reduce kernel.  Few rows (decode): the split GEMM writes into
@@ -395,7 +419,7 @@ class Qwen3Engine:
             nv.rmsnorm_fwd(s_in, w[f"l{l}.ln1"], h, eps)
         else:
             s_in = s_in_out if s_in_out is not None else ws.get(f"{tag}.s_in", (T, H))
-            nv.rmsnorm_fwd(x, w[f"l{l}.ln1"], h, eps, res=res, res_out=s_in)
+            self._norm_after(x, w[f"l{l}.ln1"], h, res, s_in)
         qkv = ws.get(f"{stag}.qkv", (T, self.p.qkv_local))
         self._gemm(h, w[f"l{l}.wqkv"], qkv)
         if cp_geom is not None and keep is not None:
@@ -411,11 +435,15 @@ class Qwen3Engine:
             self.cp.forward_inplace(q, attn, lse, *cp_geom)
         else:
             self._attention(qv, kbuf, vbuf, ov, lse, tiles, decode=q_view is not None)
-        o = ws.get(f"{tag}.o", (T, H))
-        self._row_parallel(attn, w[f"l{l}.wo"], o, self.nchunks)
+        fold = (self.fold_tree_into_norm and tag == "d" and self.ctx.tp_size == 1 and self.nchunks > 1 and T <= 512)
+        if fold:
+            o = self._row_parallel_leaves(attn, w[f"l{l}.wo"], "d.leaf_o", self.nchunks)
+        else:
+            o = ws.get(f"{tag}.o", (T, H))
+            self._row_parallel(attn, w[f"l{l}.wo"], o, self.nchunks)
         s_mid = ws.get(f"{stag}.s_mid", (T, H))
         h2 = ws.get(f"{tag}.h2", (T, H))
-        nv.rmsnorm_fwd(o, w[f"l{l}.ln2"], h2, eps, res=s_in, res_out=s_mid)
+        self._norm_after(o, w[f"l{l}.ln2"], h2, s_in, s_mid)
         if keep is not None:
             keep.update(s_in=s_in, h=h, qkv=qkv, q=q, attn=attn, s_mid=s_mid, h2=h2)
         down = self._mlp_fwd(l, h2, T, tag, keep, store_tag)
@@ -431,6 +459,8 @@ class Qwen3Engine:
         self._gemm(h2, w[f"l{l}.wgu"], gu)
         act = ws.get(f"{tag}.act", (T, self.p.i_local))
         nv.swiglu_fwd(gu, act, self.p.i_local, self.blk)
+        if self.fold_tree_into_norm and tag == "d" and self.ctx.tp_size == 1 and self.nchunks > 1 and T <= 512:
+            return self._row_parallel_leaves(act, w[f"l{l}.wd"], "d.leaf_down", self.nchunks)
         down = ws.get(f"{tag}.down", (T, H))
         self._row_parallel(act, w[f"l{l}.wd"], down, self.nchunks)
         if keep is not None:
@@ -941,7 +971,7 @@ class Qwen3Engine:
         self._decode_page_table = None
         hf = ws.get("d.hf", (B, H))
         s_fin = ws.get("d.s_fin", (B, H))
-        nv.rmsnorm_fwd(x, self.p.w["norm"], hf, self.spec.rms_norm_eps, res=res, res_out=s_fin)
+        self._norm_after(x, self.p.w["norm"], hf, res, s_fin)
         return hf
 
     def logits(self, hf: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

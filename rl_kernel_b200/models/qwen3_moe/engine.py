@@ -94,6 +94,7 @@ class Qwen3MoeEngine(Qwen3Engine):
                           g.get(f"l{l}.w1"), g.get(f"l{l}.w2"))
 
     supports_stored_activations = False     # the expert buffers are shared by all layers: recompute
+    fold_tree_into_norm = False             # the shared expert's output feeds the combine, not a norm
 
     def _mlp_fwd(self, l, h2, T, tag, keep, store_tag=None):
         shared = super()._mlp_fwd(l, h2, T, tag, keep)
