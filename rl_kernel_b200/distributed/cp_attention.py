@@ -41,6 +41,36 @@ def cp_positions(seq_len: int, cp: int, rank: int, layout: str) -> torch.Tensor:
     return torch.cat([torch.arange(rank * c, (rank + 1) * c), torch.arange((2 * cp - 1 - rank) * c, (2 * cp - rank) * c)])
 
 
+def cp_tiles(cp: int, rank: int, layout: str, nseq: int, seq_len: int, hq: int, hkv: int, d: int, device):
+    """Work items of one context-parallel rank: (forward/dQ tiles, dK/dV tiles, blocks per chunk) for
+    ``nseq`` sequences of global length ``seq_len`` whose local tokens are stored sequence after
+    sequence.  Positions are global, rows are local."""
+    g = hq // hkv
+    nchunks = cp if layout == "contiguous" else 2 * cp
+    chunk = seq_len // nchunks
+    if seq_len % nchunks or chunk % 128:
+        raise ValueError(f"sequence length {seq_len} must split into {nchunks} chunks of a multiple of 128")
+    my_chunks = [rank] if layout == "contiguous" else [rank, 2 * cp - 1 - rank]
+    s_local = seq_len // cp
+    bpc = chunk // 128
+    fw, kv = [], []
+    for b in range(nseq):
+        for li, ch in enumerate(my_chunks):
+            for t in range(bpc):
+                row0 = b * s_local + li * chunk + t * 128
+                gpos = ch * chunk + t * 128
+                for h in range(hq):
+                    fw.append([row0, h * d, 128, b * s_local, (h // g) * d, gpos, 1,
+                               seq_len, row0 * hq + h, hq, 0, 0])
+                for hk in range(hkv):
+                    kv.append([row0, hk * d, gpos, 128, b * s_local, 0, seq_len, hk * g * d, g,
+                               (b * s_local) * hq + hk * g, hq, 1])
+    fw.sort(key=lambda r: -r[5])                      # most keys first
+    kv.sort(key=lambda r: r[2])                       # most query tiles first
+    return (torch.tensor(fw, dtype=torch.int32, device=device).contiguous(),
+            torch.tensor(kv, dtype=torch.int32, device=device).contiguous(), bpc)
+
+
 class PeerMappedBuffers:
     """Named device buffers of identical shape on every rank of a group, each rank's copy mapped
     into every other rank's address space.  ``self[name][r]`` is rank r's tensor as seen from here."""
@@ -122,42 +152,14 @@ class CPAttention:
     def local_positions(self, seq_len: int) -> torch.Tensor:
         return cp_positions(seq_len, self.cp, self.rank, self.layout)
 
-    def _chunking(self, seq_len: int):
-        nchunks = self.cp if self.layout == "contiguous" else 2 * self.cp
-        chunk = seq_len // nchunks
-        if seq_len % nchunks or chunk % 128:
-            raise ValueError(f"sequence length {seq_len} must split into {nchunks} chunks of a multiple of 128")
-        my_chunks = [self.rank] if self.layout == "contiguous" else [self.rank, 2 * self.cp - 1 - self.rank]
-        return chunk, my_chunks
-
     def tiles_for(self, nseq: int, seq_len: int):
         """(forward/dQ tiles, dK/dV tiles, blocks per chunk) for ``nseq`` sequences of global length
         ``seq_len`` whose local tokens are stored sequence after sequence."""
         key = (nseq, seq_len)
-        if key in self._tiles:
-            return self._tiles[key]
-        g = self.hq // self.hkv
-        chunk, my_chunks = self._chunking(seq_len)
-        s_local = seq_len // self.cp
-        bpc = chunk // 128
-        fw, kv = [], []
-        for b in range(nseq):
-            for li, ch in enumerate(my_chunks):
-                for t in range(bpc):
-                    row0 = b * s_local + li * chunk + t * 128
-                    gpos = ch * chunk + t * 128
-                    for h in range(self.hq):
-                        fw.append([row0, h * self.d, 128, b * s_local, (h // g) * self.d, gpos, 1,
-                                   seq_len, row0 * self.hq + h, self.hq, 0, 0])
-                    for hk in range(self.hkv):
-                        kv.append([row0, hk * self.d, gpos, 128, b * s_local, 0, seq_len, hk * g * self.d, g,
-                                   (b * s_local) * self.hq + hk * g, self.hq, 1])
-        fw.sort(key=lambda r: -r[5])                      # most keys first
-        kv.sort(key=lambda r: r[2])                       # most query tiles first
-        out = (torch.tensor(fw, dtype=torch.int32, device=self.device).contiguous(),
-               torch.tensor(kv, dtype=torch.int32, device=self.device).contiguous(), bpc)
-        self._tiles[key] = out
-        return out
+        if key not in self._tiles:
+            self._tiles[key] = cp_tiles(self.cp, self.rank, self.layout, nseq, seq_len, self.hq, self.hkv, self.d,
+                                        self.device)
+        return self._tiles[key]
 
     def _stage_kv(self, T: int):
         if not self.stage_remote:

@@ -159,3 +159,62 @@ def test_prefix_shared_attention_matches_per_sample_attention():
     one = prefix_shared_attention(q[:, 3:4].contiguous(), k, v)
     sync_and_check()
     assert torch.equal(one[:, 0], out[:, 3])
+
+
+@pytest.mark.parametrize("cp,layout", [(4, "zigzag"), (8, "zigzag"), (4, "contiguous")])
+def test_context_parallel_kernels_with_emulated_ranks(cp, layout):
+    """The CP kernels never wait on a peer inside a launch, so the ranks of a CP group can be run one
+    after the other on a single GPU with every rank's buffers resident: forward, dQ and dK/dV of all
+    4 or 8 ranks -- with the remote blocks staged by the kernels -- must reproduce the single-GPU
+    tensors bit for bit."""
+    import math
+
+    from rl_kernel_b200.backends import native as nv
+    from rl_kernel_b200.distributed.cp_attention import cp_positions, cp_tiles
+    from rl_kernel_b200.models.qwen3.engine import train_tiles
+
+    hq, hkv, d, B, S = 8, 2, 128, 2, 2048
+    g = torch.Generator(device="cuda").manual_seed(13)
+    mk = lambda h: torch.randn(B, S, h * d, device=dev(), generator=g).to(BF)  # noqa: E731
+    q, k, v, do = mk(hq), mk(hkv), mk(hkv), mk(hq)
+    sc = 1 / math.sqrt(d)
+    T = B * S
+    o1, l1, dl1 = torch.empty(T, hq * d, device=dev(), dtype=BF), torch.empty(T, hq, device=dev()), torch.empty(T, hq, device=dev())
+    tiles, kvt = train_tiles(B, S, hq, hkv, d, dev())
+    q2, k2, v2, do2 = (t.view(T, -1) for t in (q, k, v, do))
+    nv.attn_fwd(q2, [k2], [v2], o1, l1, tiles, sc)
+    nv.attn_bwd_delta(o1, do2, dl1, T, hq)
+    dq1, dk1, dv1 = torch.empty_like(q2), torch.empty_like(k2), torch.empty_like(v2)
+    nv.attn_bwd_dq(q2, do2, k2, v2, l1, dl1, dq1, tiles, sc)
+    nv.attn_bwd_dkv(q2, do2, k2, v2, l1, dl1, dk1, dv1, kvt, sc)
+    # every rank's local tensors (what its peers would have mapped)
+    pos = [cp_positions(S, cp, r, layout).to(dev()) for r in range(cp)]
+    sel = lambda t, r: t[:, pos[r]].reshape(B * pos[r].numel(), -1).contiguous()  # noqa: E731
+    ql, kl, vl, dol = ([sel(t, r) for r in range(cp)] for t in (q, k, v, do))
+    Tl = ql[0].shape[0]
+    zz = layout == "zigzag"
+    outs, lses, deltas = [], [], []
+    st = lambda cols: torch.zeros(cp * Tl, cols, device=dev(), dtype=BF)  # noqa: E731
+    for r in range(cp):
+        fw, _, bpc = cp_tiles(cp, r, layout, B, S, hq, hkv, d, dev())
+        o, l = torch.empty_like(ql[r]), torch.empty(Tl, hq, device=dev())
+        flags = torch.zeros(cp * (Tl // 128) * 2 + 1, dtype=torch.int32, device=dev())
+        nv.attn_fwd(ql[r], kl, vl, o, l, fw, sc, cp_blocks_per_chunk=bpc, cp_zigzag=zz,
+                    stage=(st(hkv * d), st(hkv * d), flags, Tl, r))
+        dl = torch.empty(Tl, hq, device=dev())
+        nv.attn_bwd_delta(o, dol[r], dl, Tl, hq)
+        outs.append(o); lses.append(l); deltas.append(dl)
+        assert torch.equal(o, sel(o1.view(B, S, -1), r)) and torch.equal(l, sel(l1.view(B, S, -1), r))
+    for r in range(cp):
+        fw, kvl, bpc = cp_tiles(cp, r, layout, B, S, hq, hkv, d, dev())
+        dq, dk, dv = torch.empty_like(ql[r]), torch.empty_like(kl[r]), torch.empty_like(vl[r])
+        f1 = torch.zeros(cp * (Tl // 128) * 2 + 1, dtype=torch.int32, device=dev())
+        f2 = torch.zeros_like(f1)
+        nv.attn_bwd_dq(ql[r], dol[r], kl, vl, lses[r], deltas[r], dq, fw, sc, cp_blocks_per_chunk=bpc, cp_zigzag=zz,
+                       stage=(st(hkv * d), st(hkv * d), f1, Tl, r))
+        nv.attn_bwd_dkv(ql, dol, kl[r], vl[r], lses, deltas, dk, dv, kvl, sc, cp_blocks_per_chunk=bpc, cp_zigzag=zz,
+                        stage=(st(hq * d), st(hq * d), f2, Tl, r))
+        sync_and_check()
+        assert torch.equal(dq, sel(dq1.view(B, S, -1), r)), ("dq", r)
+        assert torch.equal(dk, sel(dk1.view(B, S, -1), r)), ("dk", r)
+        assert torch.equal(dv, sel(dv1.view(B, S, -1), r)), ("dv", r)
