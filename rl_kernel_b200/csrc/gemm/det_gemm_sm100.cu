@@ -30,6 +30,11 @@ constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
 constexpr int kGemmThreads = 192;  // warp0 TMA, warp1 MMA, warps2-5 epilogue
+// Tiles of 128 columns and more get a second set of epilogue warps (warps 6-9): two warps share a
+// TMEM lane quadrant and each drains half of the tile's columns, which keeps the epilogue of the
+// chunk-tree variants (one accumulator drain per canonical K chunk) off the critical path.
+constexpr int kGemmThreadsWide = 320;
+template <int BN> constexpr int gemm_threads() { return BN >= 128 ? kGemmThreadsWide : kGemmThreads; }
 
 struct GemmParams {
   int M, N, K;
@@ -109,7 +114,7 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
 }
 
 template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(gemm_threads<BN>(), 1)
 det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const GemmParams p) {
   griddep_sync();
@@ -142,7 +147,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(accf0 + 8 * a, 1);
-      mbar_init(acce0 + 8 * a, 128);
+      mbar_init(acce0 + 8 * a, gemm_threads<BN>() - 64);   // every epilogue thread arrives
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -233,8 +238,10 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
       }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps)
+    // ------------------------------------------------------------------ epilogue (4 or 8 warps)
     const int quad = warp & 3;                  // TMEM lane quadrant this warp may access
+    const int half = (warp - 2) >> 2;           // 0: warps 2-5; 1: warps 6-9 (tiles of >= 128 columns only)
+    constexpr int kColsPerWarp = BN >= 128 ? BN / 2 : BN;
     const int row_in_tile = quad * 32 + lane;   // one thread owns one output row
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     uint32_t u = 0;
@@ -250,7 +257,9 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tc_fence_after();
         const bool last = (c == p.nchunks - 1);
         if (BN == 128 && p.stats != nullptr) {
+          if (half == 0) {
           // fused selected-logp statistics: logit = bf16(acc); z = logit * inv_temp
+          // (one thread walks all 128 columns of its row: the statistics have a fixed order)
           const long long tgt_col = (p.targets && row < p.M) ? p.targets[row] - p.vocab_start - n0 : -1;
           float m = -INFINITY;
 #pragma unroll 1
@@ -309,36 +318,26 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int pr = 0; pr < p.stats_world; ++pr)
               if (pr != p.stats_rank) p.stats_peer[pr][si] = st2;
           }
+          }
         } else if (BN == 256 && p.nchunks > 1) {
           // chunk tree with 128x256 tiles: both accumulators fill TMEM, so the tree stack lives in a
-          // per-CTA global buffer (L2 resident; a row's entries are only ever touched by its own
-          // thread).  Stack reads are issued two 32-column slices ahead of their use.
+          // per-CTA global buffer (L2 resident; a row's entries of a slice are only ever touched by
+          // the one thread that owns that row and slice).
           int nmerge = 0;
           while ((c >> nmerge) & 1) ++nmerge;                       // levels to fold into this chunk
           uint4* sbase = p.tree_scratch + (static_cast<size_t>(blockIdx.x) * 3 * BM + row_in_tile) * 32;
           constexpr size_t kLevel = static_cast<size_t>(BM) * 32;   // uint4 per level
-          uint4 pre[2][3][4];
+          const int sl0 = half * 4;   // this warp's four 32-column slices
 #pragma unroll
-          for (int ahead = 0; ahead < 2; ++ahead)
+          for (int si = 0; si < 4; ++si) {
+            const int sl = sl0 + si;
+            // stack entries of this slice: issued before the TMEM load so that both are in flight
+            uint4 cur[3][4];
 #pragma unroll
             for (int lv = 0; lv < 3; ++lv)
               if (lv < nmerge)
 #pragma unroll
-                for (int q = 0; q < 4; ++q) pre[ahead][lv][q] = sbase[lv * kLevel + ahead * 4 + q];
-#pragma unroll
-          for (int sl = 0; sl < 8; ++sl) {
-            uint4 cur[3][4];
-#pragma unroll
-            for (int lv = 0; lv < 3; ++lv)
-#pragma unroll
-              for (int q = 0; q < 4; ++q) cur[lv][q] = pre[sl & 1][lv][q];
-            if (sl + 2 < 8) {
-#pragma unroll
-              for (int lv = 0; lv < 3; ++lv)
-                if (lv < nmerge)
-#pragma unroll
-                  for (int q = 0; q < 4; ++q) pre[sl & 1][lv][q] = sbase[lv * kLevel + (sl + 2) * 4 + q];
-            }
+                for (int q = 0; q < 4; ++q) cur[lv][q] = sbase[lv * kLevel + sl * 4 + q];
             uint32_t r[32];
             tmem_ld32(tmem_base + lane_off + a * BN + sl * 32, r);
             tmem_ld_wait();
@@ -398,7 +397,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
         } else
 #pragma unroll 1
-        for (int col0 = 0; col0 < BN; col0 += 32) {
+        for (int col0 = half * kColsPerWarp; col0 < (half + 1) * kColsPerWarp; col0 += 32) {
           uint32_t r[32];
           tmem_ld32(tmem_base + lane_off + a * BN + col0, r);
           tmem_ld_wait();
@@ -518,9 +517,16 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tc_fence_before();
         mbar_arrive(acce0 + 8 * a);
       }
-      if (p.ar_world > 1) {
+      if (p.ar_world > 1 && half == 1) {
+        // the second set of epilogue warps only drains accumulators; its partial-tile stores must
+        // be visible before the first set signals the peers
+        __threadfence_system();
+        asm volatile("bar.arrive 2, 256;" ::: "memory");
+      }
+      if (p.ar_world > 1 && half == 0) {
         // ---- fused all-reduce of this tile (the MMA warp is already working on the next tile)
-        const int et = threadIdx.x - 64;  // 0..127 among the epilogue threads
+        const int et = threadIdx.x - 64;  // 0..127 among the first set of epilogue threads
+        if (BN >= 128) asm volatile("bar.sync 2, 256;" ::: "memory");   // wait for the other half's stores
         const unsigned long long seq = p.ar_use_epoch ? p.ar_seq + p.ar_epoch[0] * p.ar_epoch[1] : p.ar_seq;
         __threadfence_system();
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -610,7 +616,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
                                         GemmSmem<BN>::kBytes));
     attr_set[dev & 63] = true;
   }
-  RLK_CHECK_CUDA(launch_pdl(kfn, dim3(grid), dim3(kGemmThreads), smem_bytes, stream, tmA, tmB, p));
+  RLK_CHECK_CUDA(launch_pdl(kfn, dim3(grid), dim3(gemm_threads<BN>()), smem_bytes, stream, tmA, tmB, p));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
