@@ -215,6 +215,7 @@ def run_ours(args) -> dict:
                 "h2d_bytes_per_step": int(dev_prompts.numel() * 8), "d2h_bytes_per_step": int(host_result.numel() * 4),
                 "timing": "host wall clock around the same steps incl. H2D of prompts and D2H of loss"},
         "gpu_launches": int(launches),
+        "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
         "phase_ms_last_step": trainer.phase_ms(),
     }
     if world > 1:
