@@ -245,6 +245,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int row_in_tile = quad * 32 + lane;   // one thread owns one output row
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     uint32_t u = 0;
+    uint32_t tree_l0[4][16];   // 128x256 chunk tree: level 0 of this thread's four slices (packed bf16)
     for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
       int mt, nt;
       tile_coords(t / p.split_chunks, p.m_tiles, p.n_tiles, mt, nt);
@@ -320,9 +321,10 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
           }
         } else if (BN == 256 && p.nchunks > 1) {
-          // chunk tree with 128x256 tiles: both accumulators fill TMEM, so the tree stack lives in a
-          // per-CTA global buffer (L2 resident; a row's entries of a slice are only ever touched by
-          // the one thread that owns that row and slice).
+          // chunk tree with 128x256 tiles: both accumulators fill TMEM, so the tree stack cannot live
+          // there.  Level 0 (written by every even chunk, read by the next odd one) stays in this
+          // thread's registers; levels 1 and 2 go to a per-CTA global buffer (L2 resident; a row's
+          // entries of a slice are only ever touched by the one thread that owns that row and slice).
           int nmerge = 0;
           while ((c >> nmerge) & 1) ++nmerge;                       // levels to fold into this chunk
           uint4* sbase = p.tree_scratch + (static_cast<size_t>(blockIdx.x) * 3 * BM + row_in_tile) * 32;
@@ -334,7 +336,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             // stack entries of this slice: issued before the TMEM load so that both are in flight
             uint4 cur[3][4];
 #pragma unroll
-            for (int lv = 0; lv < 3; ++lv)
+            for (int lv = 1; lv < 3; ++lv)   // level 0 lives in registers (tree_l0)
               if (lv < nmerge)
 #pragma unroll
                 for (int q = 0; q < 4; ++q) cur[lv][q] = sbase[lv * kLevel + sl * 4 + q];
@@ -345,8 +347,14 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
             for (int j = 0; j < 16; ++j)
               v[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
+            if (nmerge > 0) {
 #pragma unroll
-            for (int lv = 0; lv < 3; ++lv) {
+              for (int j = 0; j < 16; ++j)
+                v[j] = pack_bf16x2(__fadd_rn(bf16_lo(tree_l0[si][j]), bf16_lo(v[j])),
+                                   __fadd_rn(bf16_hi(tree_l0[si][j]), bf16_hi(v[j])));
+            }
+#pragma unroll
+            for (int lv = 1; lv < 3; ++lv) {
               if (lv < nmerge) {
                 const uint32_t sv[16] = {cur[lv][0].x, cur[lv][0].y, cur[lv][0].z, cur[lv][0].w,
                                          cur[lv][1].x, cur[lv][1].y, cur[lv][1].z, cur[lv][1].w,
@@ -359,9 +367,15 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
             const int col0 = sl * 32;
             if (!last) {
+              if (nmerge == 0) {
+                // an even chunk's leaf waits in registers for the next (odd) chunk
 #pragma unroll
-              for (int q = 0; q < 4; ++q)
-                sbase[nmerge * kLevel + sl * 4 + q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                for (int j = 0; j < 16; ++j) tree_l0[si][j] = v[j];
+              } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  sbase[nmerge * kLevel + sl * 4 + q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+              }
             } else if (row < p.M) {
               if (p.out_fp32) {
                 float* dst = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + n0 + col0;
