@@ -32,6 +32,20 @@ def set_pdl(on: bool) -> bool:
     return bool(_lib().rlk_set_pdl(c_int(int(on))))
 
 
+class static_weights:
+    """Context: the B operands (weights) of the GEMMs launched inside were complete before the
+    kernel preceding each GEMM was launched, so the kernels may start streaming them while that
+    kernel still runs.  Never wrap a GEMM whose B is produced by the kernel right before it."""
+
+    def __enter__(self):
+        self._old = _lib().rlk_set_static_b(c_int(1))
+        return self
+
+    def __exit__(self, *exc):
+        _lib().rlk_set_static_b(c_int(self._old))
+        return False
+
+
 def _bf16(t: torch.Tensor, name: str) -> torch.Tensor:
     if t.dtype != torch.bfloat16 or not t.is_cuda:
         raise TypeError(f"{name} must be a CUDA bf16 tensor, got {t.dtype} on {t.device}")

@@ -92,7 +92,6 @@ template <int NSRC>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ KvMaps<NSRC> kv,
                 const __grid_constant__ KvMaps<1> staged, const AttnFwdParams p) {
-  griddep_sync();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -116,17 +115,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  const AttnTile t = p.tiles[blockIdx.x];
-  const bool use_stage = NSRC > 1 && p.stage.rows > 0;
-  if (t.n_rows <= 0) {
-    // an empty tile still helps with the staging copies (its threads do nothing else)
-    if (use_stage && warp >= 2) cp_stage_gather(p.stage, threadIdx.x - 64, kAttnThreads - 64, 3, stage_slot);
-    return;
-  }
-  int max_kv = t.pos0 + (t.n_rows - 1) * t.pos_step + 1;
-  if (max_kv > t.kv_cap) max_kv = t.kv_cap;
-  const int nblk = (max_kv + kAttnBlock - 1) / kAttnBlock;
-
+  // Barriers and tensor memory are set up before the dependency wait, so this part overlaps the
+  // tail of the previous kernel of the stream; nothing before the wait touches global memory.
   if (threadIdx.x == 0) {
     mbar_init(BAR(Q_FULL), 1);
     for (int s = 0; s < 3; ++s) {
@@ -153,6 +143,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  griddep_sync();
+
+  const AttnTile t = p.tiles[blockIdx.x];
+  const bool use_stage = NSRC > 1 && p.stage.rows > 0;
+  if (t.n_rows <= 0) {
+    // an empty tile still helps with the staging copies (its threads do nothing else)
+    if (use_stage && warp >= 2) cp_stage_gather(p.stage, threadIdx.x - 64, kAttnThreads - 64, 3, stage_slot);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+      tc_fence_after();
+      tmem_dealloc(tmem_base, 512);
+    }
+    return;
+  }
+  int max_kv = t.pos0 + (t.n_rows - 1) * t.pos_step + 1;
+  if (max_kv > t.kv_cap) max_kv = t.kv_cap;
+  const int nblk = (max_kv + kAttnBlock - 1) / kAttnBlock;
+
   const uint32_t sQ = smem_u32(smem);
   const uint32_t sP = sQ + off_p;
   const uint32_t sK = sQ + off_k;

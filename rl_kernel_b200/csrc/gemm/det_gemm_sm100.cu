@@ -49,6 +49,9 @@ struct GemmParams {
   uint4* tree_scratch;      // tile_n 256 with chunks: per-CTA tree stack [grid][3][128][32] uint4 (L2 resident)
   int a_box_rows;           // rows of A that TMA brings per tile (128, or fewer when M < 128)
   int stage_a_bytes;        // shared-memory bytes reserved for the A tile of one stage
+  int stages;               // depth of the shared-memory ring
+  int b_static;             // 1: B was complete before the previous kernel of the stream started (a
+                            //    weight): its first tiles are fetched before the dependency wait
   int split_chunks;         // > 1: every canonical chunk is its own tile and writes its bf16 leaf
   long long split_stride;   //      to C + chunk * split_stride (elements); nchunks is 1 then
   // fused LM-head epilogue (tile_n == 128, nchunks == 1): per-(row, tile) softmax statistics
@@ -93,13 +96,16 @@ __device__ __forceinline__ uint4 ar_tree_node(const uint4 a, const uint4 b) {
   return o;
 }
 
+constexpr int kMaxStages = 16;
+
 template <int BN>
 struct GemmSmem {
   static constexpr int kStageA = BM * BK * 2;
   static constexpr int kStageB = BN * BK * 2;
   static constexpr int kStage = kStageA + kStageB;
   static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
-  static constexpr int kBytes = kStages * kStage + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kBarBytes = 512;           // room for the barriers of kMaxStages stages
+  static constexpr int kBytes = 227 * 1024;       // the launch may use up to all of an SM's shared memory
 };
 
 __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int& mt, int& nt) {
@@ -117,9 +123,8 @@ template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(gemm_threads<BN>(), 1)
 det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                 const GemmParams p) {
-  griddep_sync();
   using S = GemmSmem<BN>;
-  constexpr int kStages = S::kStages;
+  const uint32_t kStages = static_cast<uint32_t>(p.stages);   // ring depth chosen by the host (<= kMaxStages)
   // TMEM columns: two accumulators (+ three packed-bf16 tree levels when chunked, BN==128 only)
   constexpr uint32_t kTmemCols = (BN == 128) ? 512 : (2 * BN < 32 ? 32 : 2 * BN);
   constexpr uint32_t kStackCol = 2 * BN;  // first column of the tree stack (BN == 128)
@@ -127,7 +132,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  const uint32_t stage_bytes = static_cast<uint32_t>(p.stage_a_bytes) + S::kStageB;
+  const uint32_t stage_bytes = static_cast<uint32_t>(p.stage_a_bytes) + S::kStageB;   // one k block: A tile, B tile
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * stage_bytes);
   // bars: full[kStages], empty[kStages], acc_full[2], acc_empty[2], then tmem ptr + abort flag
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
@@ -141,7 +146,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   const uint32_t acce0 = smem_u32(bars + 2 * kStages + 2);
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (uint32_t s = 0; s < kStages; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
@@ -171,8 +176,31 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t it = 0, pre = 0;
+      uint32_t ps = 0, pph = 0, psa = smem_base;   // ring slot, its phase, its shared-memory address
       const uint32_t stage_tx = (A_MN ? S::kStageA : static_cast<uint32_t>(p.a_box_rows) * BK * 2) + S::kStageB;
+      if (p.b_static && static_cast<int>(blockIdx.x) < total_tiles) {
+        // weights do not depend on the previous kernel: start streaming the first tile's B blocks
+        // while that kernel is still running
+        int mt, nt;
+        tile_coords(blockIdx.x / p.split_chunks, p.m_tiles, p.n_tiles, mt, nt);
+        const uint32_t kbs = static_cast<uint32_t>(p.nchunks * p.kb_per_chunk);
+        const int kb0 = (blockIdx.x % p.split_chunks) * p.kb_per_chunk;
+        pre = kbs < kStages ? kbs : kStages;
+        for (uint32_t kb = 0; kb < pre; ++kb) {
+          const uint32_t fb = full0 + 8 * kb;
+          mbar_expect_tx(fb, stage_tx);
+          const uint32_t sb = smem_base + kb * stage_bytes + p.stage_a_bytes;
+          const int k0 = (kb0 + static_cast<int>(kb)) * BK;
+          if (!B_MN) {
+            tma_load_2d(sb, &tmB, k0, nt * BN, fb);
+          } else {
+#pragma unroll
+            for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, &tmB, nt * BN + 64 * i, k0, fb);
+          }
+        }
+      }
+      griddep_sync();
       for (int t = blockIdx.x; t < total_tiles; t += gridDim.x) {
         int mt, nt;
         const int chunk = t % p.split_chunks;
@@ -180,21 +208,25 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int m0 = mt * BM, n0 = nt * BN;
         const int kbs = p.nchunks * p.kb_per_chunk;
         const int kb0 = chunk * p.kb_per_chunk;
-        for (int kb = 0; kb < kbs; ++kb, ++it) {
-          const uint32_t s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
-          if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 101)) break;
-          const uint32_t fb = full0 + 8 * s;
-          mbar_expect_tx(fb, stage_tx);
-          const uint32_t sa = smem_base + s * stage_bytes;
+        int k0 = kb0 * BK;
+        for (int kb = 0; kb < kbs; ++kb, ++it, k0 += BK) {
+          const uint32_t fb = full0 + 8 * ps;
+          const bool fresh = it >= pre;   // else: armed, and B requested, before the dependency wait
+          if (fresh) {
+            if (!mbar_wait(empty0 + 8 * ps, pph ^ 1, abort_flag, p.status, 101)) break;
+            mbar_expect_tx(fb, stage_tx);
+          }
+          const uint32_t sa = psa;
           const uint32_t sb = sa + p.stage_a_bytes;
-          const int k0 = (kb0 + kb) * BK;
+          // ring position of the next k block (a single thread runs this loop: no divisions)
+          if (++ps == kStages) { ps = 0; pph ^= 1; psa = smem_base; } else { psa += stage_bytes; }
           if (!A_MN) {
             tma_load_2d(sa, &tmA, k0, m0, fb);
           } else {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, &tmA, m0 + 64 * i, k0, fb);
           }
+          if (!fresh) continue;
           if (!B_MN) {
             tma_load_2d(sb, &tmB, k0, n0, fb);
           } else {
@@ -209,29 +241,35 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
-      uint32_t it = 0, u = 0;
+      // One thread issues every MMA, so each instruction of this loop is on the critical path of a
+      // small tile.  The shared-memory descriptors differ only in their 14-bit start-address field
+      // (address / 16, bits 0-13; shared memory ends below 2^18, so adding never carries out of
+      // it): build them once and step the low word per k step and per ring slot.
+      const uint64_t da_base = A_MN ? umma_desc_sw128(smem_base, 8192, 1024) : umma_desc_sw128(smem_base, 16, 1024);
+      const uint64_t db_base = B_MN ? umma_desc_sw128(smem_base + p.stage_a_bytes, 8192, 1024)
+                                    : umma_desc_sw128(smem_base + p.stage_a_bytes, 16, 1024);
+      const uint32_t da_hi = static_cast<uint32_t>(da_base >> 32), db_hi = static_cast<uint32_t>(db_base >> 32);
+      const uint32_t da_lo0 = static_cast<uint32_t>(da_base), db_lo0 = static_cast<uint32_t>(db_base);
+      constexpr uint32_t ka_step = (A_MN ? 2048u : 32u) >> 4, kb_step = (B_MN ? 2048u : 32u) >> 4;
+      const uint32_t slot_step = stage_bytes >> 4;
+      uint32_t s = 0, ph = 0, da_lo = da_lo0, db_lo = db_lo0, u = 0;
+      auto desc64 = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
       for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
         for (int c = 0; c < p.nchunks; ++c, ++u) {
           const uint32_t a = u & 1;
           if (!mbar_wait(acce0 + 8 * a, ((u >> 1) & 1) ^ 1, abort_flag, p.status, 102)) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + a * BN;
-          for (int kb = 0; kb < p.kb_per_chunk; ++kb, ++it) {
-            const uint32_t s = it % kStages;
-            const uint32_t ph = (it / kStages) & 1;
+          for (int kb = 0; kb < p.kb_per_chunk; ++kb) {
             if (!mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 103)) break;
             tc_fence_after();
-            const uint32_t sa = smem_base + s * stage_bytes;
-            const uint32_t sb = sa + p.stage_a_bytes;
+            umma_bf16_ss(d_tmem, desc64(da_lo, da_hi), desc64(db_lo, db_hi), idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint64_t da = A_MN ? umma_desc_sw128(sa + k * 2048, 8192, 1024)
-                                       : umma_desc_sw128(sa + k * 32, 16, 1024);
-              const uint64_t db = B_MN ? umma_desc_sw128(sb + k * 2048, 8192, 1024)
-                                       : umma_desc_sw128(sb + k * 32, 16, 1024);
-              umma_bf16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
-            }
+            for (uint32_t k = 1; k < BK / UMMA_K; ++k)
+              umma_bf16_ss(d_tmem, desc64(da_lo + k * ka_step, da_hi), desc64(db_lo + k * kb_step, db_hi), idesc, 1u);
             umma_commit(empty0 + 8 * s);  // frees the smem stage when these MMAs retire
+            if (++s == kStages) { s = 0; ph ^= 1; da_lo = da_lo0; db_lo = db_lo0; }
+            else { da_lo += slot_step; db_lo += slot_step; }
           }
           umma_commit(accf0 + 8 * a);  // accumulator of this chunk complete
         }
@@ -245,7 +283,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int row_in_tile = quad * 32 + lane;   // one thread owns one output row
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     uint32_t u = 0;
-    uint32_t tree_l0[4][16];   // 128x256 chunk tree: level 0 of this thread's four slices (packed bf16)
+    griddep_sync();            // C, the statistics and the tree scratch may still be in use by the previous kernel
     for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
       int mt, nt;
       tile_coords(t / p.split_chunks, p.m_tiles, p.n_tiles, mt, nt);
@@ -321,10 +359,10 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
           }
         } else if (BN == 256 && p.nchunks > 1) {
-          // chunk tree with 128x256 tiles: both accumulators fill TMEM, so the tree stack cannot live
-          // there.  Level 0 (written by every even chunk, read by the next odd one) stays in this
-          // thread's registers; levels 1 and 2 go to a per-CTA global buffer (L2 resident; a row's
-          // entries of a slice are only ever touched by the one thread that owns that row and slice).
+          // chunk tree with 128x256 tiles: both accumulators fill TMEM, so the tree stack lives in a
+          // per-CTA global buffer (L2 resident; a row's entries of a slice are only ever touched by
+          // the one thread that owns that row and slice).  Keeping level 0 in registers instead was
+          // tried: 64 more live registers spill under the 168-register cap and nothing is gained.
           int nmerge = 0;
           while ((c >> nmerge) & 1) ++nmerge;                       // levels to fold into this chunk
           uint4* sbase = p.tree_scratch + (static_cast<size_t>(blockIdx.x) * 3 * BM + row_in_tile) * 32;
@@ -336,7 +374,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             // stack entries of this slice: issued before the TMEM load so that both are in flight
             uint4 cur[3][4];
 #pragma unroll
-            for (int lv = 1; lv < 3; ++lv)   // level 0 lives in registers (tree_l0)
+            for (int lv = 0; lv < 3; ++lv)
               if (lv < nmerge)
 #pragma unroll
                 for (int q = 0; q < 4; ++q) cur[lv][q] = sbase[lv * kLevel + sl * 4 + q];
@@ -347,14 +385,8 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
             for (int j = 0; j < 16; ++j)
               v[j] = pack_bf16x2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1]));
-            if (nmerge > 0) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j)
-                v[j] = pack_bf16x2(__fadd_rn(bf16_lo(tree_l0[si][j]), bf16_lo(v[j])),
-                                   __fadd_rn(bf16_hi(tree_l0[si][j]), bf16_hi(v[j])));
-            }
-#pragma unroll
-            for (int lv = 1; lv < 3; ++lv) {
+            for (int lv = 0; lv < 3; ++lv) {
               if (lv < nmerge) {
                 const uint32_t sv[16] = {cur[lv][0].x, cur[lv][0].y, cur[lv][0].z, cur[lv][0].w,
                                          cur[lv][1].x, cur[lv][1].y, cur[lv][1].z, cur[lv][1].w,
@@ -367,15 +399,9 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
             const int col0 = sl * 32;
             if (!last) {
-              if (nmerge == 0) {
-                // an even chunk's leaf waits in registers for the next (odd) chunk
 #pragma unroll
-                for (int j = 0; j < 16; ++j) tree_l0[si][j] = v[j];
-              } else {
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  sbase[nmerge * kLevel + sl * 4 + q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-              }
+              for (int q = 0; q < 4; ++q)
+                sbase[nmerge * kLevel + sl * 4 + q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
             } else if (row < p.M) {
               if (p.out_fp32) {
                 float* dst = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + n0 + col0;
@@ -602,14 +628,28 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   CUtensorMap tmA, tmB;
   int rc;
   if (p.split_chunks < 1) p.split_chunks = 1;
+  p.b_static = static_b_operand();
   p.a_box_rows = BM;
   if (!A_MN && p.M < BM) p.a_box_rows = (p.M + 7) / 8 * 8;  // rows beyond are never stored: skip loading them
   // The UMMA still addresses 128 A rows; with a short A box the rows past it alias the B tile /
   // next stage (finite garbage feeding accumulator rows nobody stores), and the stage shrinks so
   // two CTAs fit on an SM -- more loads in flight for the bandwidth-bound small-M case.
   p.stage_a_bytes = A_MN ? GemmSmem<BN>::kStageA : (p.a_box_rows * BK * 2 + 1023) / 1024 * 1024;
-  const int smem_bytes = GemmSmem<BN>::kStages * (p.stage_a_bytes + GemmSmem<BN>::kStageB) + 1024 + 256 +
-                         (GemmSmem<BN>::kStageA - p.stage_a_bytes);  // slack: reads past the last stage stay in bounds
+  // Ring depth: the default for full tiles; with a short A box (small M: the kernel is bound by
+  // how many weight bytes each SM keeps in flight) as deep as shared memory allows.
+  const int stage_bytes = p.stage_a_bytes + GemmSmem<BN>::kStageB;
+  const int slack = GemmSmem<BN>::kStageA - p.stage_a_bytes;   // reads past the last stage stay in bounds
+  // Ring depth.  Small M (short A box): measured on a 64-row decode step inside a CUDA graph, two
+  // CTAs per SM with four stages each beat one CTA with 8 to 16 stages (1.066 against 1.10 ms for
+  // four layers), and so did they beat three CTAs, or stages of several k blocks per barrier pair:
+  // the second CTA streams while the first is between tiles.
+  p.stages = GemmSmem<BN>::kStages;
+  if (!A_MN && p.M < BM) {
+    p.stages = 4;
+    const int fit = (GemmSmem<BN>::kBytes - 1024 - GemmSmem<BN>::kBarBytes - slack) / stage_bytes;
+    if (p.stages > fit) p.stages = fit;
+  }
+  const int smem_bytes = p.stages * stage_bytes + 1024 + GemmSmem<BN>::kBarBytes + slack;
   if (!A_MN) rc = make_tmap_2d_sw128(&tmA, A, p.M, p.K, lda, p.a_box_rows, 64, 2);
   else rc = make_tmap_2d_sw128(&tmA, A, p.K, p.M, lda, BK, 64, 2);
   if (rc) return rc;
@@ -619,7 +659,11 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   p.m_tiles = (p.M + BM - 1) / BM;
   p.n_tiles = (p.N + BN - 1) / BN;
   const int tiles = p.m_tiles * p.n_tiles * p.split_chunks;
-  const int ctas_per_sm = smem_bytes <= 110 * 1024 ? 2 : 1;
+  int ctas_per_sm = (GemmSmem<BN>::kBytes + 1024) / (smem_bytes + 1024);   // shared memory
+  const int tmem_fit = 512 / ((BN == 128) ? 512 : (2 * BN < 32 ? 32 : 2 * BN));          // tensor memory columns
+  if (ctas_per_sm > tmem_fit) ctas_per_sm = tmem_fit;
+  if (ctas_per_sm > 2) ctas_per_sm = 2;
+  if (ctas_per_sm < 1) ctas_per_sm = 1;
   const int grid = tiles < sm_count() * ctas_per_sm ? tiles : sm_count() * ctas_per_sm;
   auto kfn = det_gemm_kernel<BN, A_MN, B_MN>;
   static bool attr_set[64] = {false};

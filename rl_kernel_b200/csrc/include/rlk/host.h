@@ -53,6 +53,8 @@ int sm_count();
 // 1 when kernels that start with griddep_sync() are launched with programmatic stream
 // serialization (rlk_set_pdl); their launch latency then overlaps the previous kernel's execution.
 int pdl_enabled();
+// 1 while the calling thread has declared the B operands of its GEMMs static (rlk_set_static_b).
+int static_b_operand();
 
 #ifdef __CUDACC__
 // Launch for kernels whose first statement is griddep_sync() (rlk/ptx.cuh).

@@ -119,6 +119,8 @@ int make_tmap_3d_sw128(CUtensorMap* out, const void* base, uint64_t batch, uint6
 
 static int g_pdl = 1;
 int pdl_enabled() { return g_pdl; }
+static thread_local int g_static_b = 0;
+int static_b_operand() { return g_static_b && g_pdl; }
 
 }  // namespace rlk
 
@@ -126,6 +128,15 @@ int pdl_enabled() { return g_pdl; }
 RLK_API int rlk_set_pdl(int on) {
   const int old = rlk::g_pdl;
   rlk::g_pdl = on ? 1 : 0;
+  return old;
+}
+
+// While on (per host thread), det_gemm launches may fetch their B operand before the previous
+// kernel of the stream has finished.  The caller promises that B (a weight) was complete before
+// that previous kernel was launched; A and C keep the full dependency.  Returns the old setting.
+RLK_API int rlk_set_static_b(int on) {
+  const int old = rlk::g_static_b;
+  rlk::g_static_b = on ? 1 : 0;
   return old;
 }
 

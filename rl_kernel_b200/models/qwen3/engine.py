@@ -402,9 +402,16 @@ class Qwen3Engine:
         return self._tiles[key]
 
     # -------------------------------------------------------------------------- layer forward
-    def _layer_fwd(self, l: int, x, res, T: int, pos, *, tiles, kbuf, vbuf, kv_slot=None,
-                   q_view=None, lse=None, s_in_out=None, keep: dict | None = None, tag: str = "f",
-                   cp_geom: tuple[int, int] | None = None, store_tag: str | None = None):
+    def _layer_fwd(self, *args, **kwargs):
+        """One decoder layer (see ``_layer_fwd_body``).  Every GEMM of the layer multiplies by a
+        weight and follows a norm / rope / attention / activation kernel, none of which writes
+        weights, so the GEMMs may stream their weights ahead of the dependency wait."""
+        with nv.static_weights():
+            return self._layer_fwd_body(*args, **kwargs)
+
+    def _layer_fwd_body(self, l: int, x, res, T: int, pos, *, tiles, kbuf, vbuf, kv_slot=None,
+                        q_view=None, lse=None, s_in_out=None, keep: dict | None = None, tag: str = "f",
+                        cp_geom: tuple[int, int] | None = None, store_tag: str | None = None):
         """One decoder layer.  ``x`` + ``res`` -> (mlp_out, s_mid).  When ``res`` is None, ``x`` is
         already the residual stream.  ``keep`` receives the intermediates backward needs.
         ``store_tag``: the tensors backward cannot cheaply rebuild (qkv, q, attention output, s_mid,
@@ -980,7 +987,8 @@ class Qwen3Engine:
         vloc = self.p.v_real_local
         if out is None:
             out = self.ws.get("d.logits", (n, vloc))
-        self._gemm(hf, self.p.w["lm_head"][:vloc], out)
+        with nv.static_weights():       # follows the final norm; the LM head is a weight
+            self._gemm(hf, self.p.w["lm_head"][:vloc], out)
         return out
 
     def sample(self, logits: torch.Tensor, row_keys: torch.Tensor, *, temperature: float, seed: int,
