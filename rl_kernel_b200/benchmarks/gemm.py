@@ -44,6 +44,9 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--no-cublas", action="store_true")
     ap.add_argument("--tile-n", type=int, default=0, help="force the output tile width (0 = the kernel's own choice)")
+    ap.add_argument("--rotate", action="store_true",
+                    help="instead of flushing L2 with writes (which leaves it full of dirty lines whose write-back "
+                         "competes with a weight-streaming kernel), cycle through enough weight copies to exceed L2")
     a = ap.parse_args()
     dev = torch.device("cuda:0")
     peaks = Path("MEASURED_PEAKS.json")
@@ -51,18 +54,26 @@ def main() -> None:
     flush = L2Flusher(dev)
     for (M, N, K) in ([tuple(a.shape)] if a.shape else SHAPES):
         x = torch.randn(M, K, device=dev).bfloat16()
-        w = torch.randn(N, K, device=dev).bfloat16()
+        copies = max(1, -(-400_000_000 // (N * K * 2))) if a.rotate else 1
+        ws = [torch.randn(N, K, device=dev).bfloat16() for _ in range(copies)]
+        w = ws[0]
         out = torch.empty(M, N, device=dev, dtype=torch.bfloat16)
+        turn = [0]
+
+        def next_w():
+            turn[0] = (turn[0] + 1) % copies
+            return ws[turn[0]]
+
         if a.nchunks > 1 and M <= 512:
             scratch = torch.empty(a.nchunks * M * N, device=dev, dtype=torch.bfloat16)
-            fn = lambda: nv.det_gemm_split(x, w, out, scratch, nchunks=a.nchunks)  # noqa: E731
+            fn = lambda: nv.det_gemm_split(x, next_w(), out, scratch, nchunks=a.nchunks)  # noqa: E731
         else:
-            fn = lambda: nv.det_gemm(x, w, out, M=M, N=N, K=K, nchunks=a.nchunks, tile_n=a.tile_n)  # noqa: E731
-        ms = bench(fn, a.iters, flush)
+            fn = lambda: nv.det_gemm(x, next_w(), out, M=M, N=N, K=K, nchunks=a.nchunks, tile_n=a.tile_n)  # noqa: E731
+        ms = bench(fn, a.iters, (lambda: None) if a.rotate else flush)
         rec = {"M": M, "N": N, "K": K, "nchunks": a.nchunks, "tile_n": a.tile_n, "det_gemm_ms": ms, "det_gemm_tflops": 2 * M * N * K / ms / 1e9,
                "frac_of_measured_cublas_peak": 2 * M * N * K / ms / 1e9 / peak, "weight_gbs": N * K * 2 / ms / 1e6}
         if not a.no_cublas:
-            cms = bench(lambda: torch.matmul(x, w.t(), out=out), a.iters, flush)
+            cms = bench(lambda: torch.matmul(x, next_w().t(), out=out), a.iters, (lambda: None) if a.rotate else flush)
             rec.update(cublas_ms=cms, cublas_tflops=2 * M * N * K / cms / 1e9, det_over_cublas=ms / cms)
         print(json.dumps(rec))
 
