@@ -154,9 +154,13 @@ def lmhead_logp_stats_vp(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor
 def attn_fwd(q2d: torch.Tensor, k_list: list[torch.Tensor], v_list: list[torch.Tensor],
              o2d: torch.Tensor, lse: torch.Tensor | None, tiles: torch.Tensor, scale: float, *,
              cp_blocks_per_chunk: int = 0, cp_zigzag: bool = False, decode: bool = False,
-             page_table: torch.Tensor | None = None, stage: tuple | None = None) -> None:
+             page_table: torch.Tensor | None = None, stage: tuple | None = None,
+             resume: tuple | None = None) -> None:
     """q2d/o2d: [rows, Hq*128]; k/v: [rows, Hkv*128] (one tensor per source rank).  ``page_table``
-    int32: tiles whose last column is > 0 read KV block b from page ``table[col - 1 + b]``."""
+    int32: tiles whose last column is > 0 read KV block b from page ``table[col - 1 + b]``.
+    ``resume`` = (tile_ext int32 [tiles, 4], state fp32, rows per sequence in a tile, rows between
+    sequences in q2d, sequences per tile or 0): rows whose block loop is cut in two launches
+    (see ``AttnFwdParams::tile_ext``)."""
     _bf16(q2d, "q"); _rowmajor2d(q2d, "q"); _rowmajor2d(o2d, "o")
     n_src = len(k_list)
     k0 = k_list[0]
@@ -169,9 +173,19 @@ def attn_fwd(q2d: torch.Tensor, k_list: list[torch.Tensor], v_list: list[torch.T
                              _ll(k0.stride(0)), ext.ptr(o2d), _ll(o2d.stride(0)), ext.ptr(lse),
                              ext.ptr(tiles), c_int(tiles.shape[0]), c_float(scale),
                              c_int(cp_blocks_per_chunk), c_int(int(cp_zigzag)), c_int(int(decode)),
-                             ext.ptr(page_table), *_stage_args(stage), ext.stream_ptr(q2d.device))
+                             ext.ptr(page_table), *_stage_args(stage), *_resume_args(resume, tiles),
+                             ext.stream_ptr(q2d.device))
     ext.check(rc, "attn_fwd")
     _count()
+
+
+def _resume_args(resume, tiles):
+    if resume is None:
+        return c_void_p(0), c_void_p(0), c_int(0), c_int(0), c_int(0)
+    ext_t, state, rps, seq_rows, group = resume
+    assert ext_t.dtype == torch.int32 and ext_t.is_contiguous() and ext_t.shape == (tiles.shape[0], 4)
+    assert state.dtype == torch.float32 and state.is_contiguous()
+    return ext.ptr(ext_t), ext.ptr(state), c_int(int(rps)), c_int(int(seq_rows)), c_int(int(group))
 
 
 def _stage_args(stage):

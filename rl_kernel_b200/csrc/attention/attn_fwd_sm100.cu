@@ -44,8 +44,22 @@ struct AttnFwdParams {
   int q_rows_box;           // 128 (training / prefill) or 8 (decode: at most 8 query rows per tile)
   const int* page_table;    // paged KV cache: see cp_locate; null = contiguous KV
   CpStage stage;            // context parallel: remote K/V blocks are copied here once (rows = 0: off)
+  // Resumable rows (shared-prefix decode).  tile_ext[4 * tile] = {first block, mode, state row, 0}:
+  // mode 1 tiles stop after their last block and write every row's running (max, partial sums,
+  // unnormalised output) to `state` instead of O; mode 2 tiles start at `first block` from that
+  // state.  A row's program is the same sequence of block updates either way, so the bits equal
+  // an uninterrupted run.  State row of tile row r: state_row + (r / q_rows_per_seq) * q_seq_rows
+  // + r % q_rows_per_seq, kAttnStateFloats floats each.
+  const int* tile_ext;
+  float* state;
+  int q_rows_per_seq;       // rows of one sequence inside a tile (the GQA group size)
+  int q_seq_rows;           // rows between consecutive sequences in Q (query heads per sequence)
+  int q3d;                  // 1: Q comes through a 3-D map {128, q_seq_rows, sequences}: a tile's rows are
+                            //    q_rows_per_seq rows of each of q_rows_box / q_rows_per_seq consecutive sequences
   int* status;
 };
+
+constexpr int kAttnStateFloats = 136;   // per row: max, 3 unused, 4 partial sums, 128 outputs
 
 // Shared memory: [Q | P | K ring | V ring | barriers].  Full tiles: Q and P are 32 KB each and the
 // rings have 2 stages.  Decode tiles (<= 8 query rows): Q and P shrink to 2 KB each -- the UMMA
@@ -54,7 +68,7 @@ struct AttnFwdParams {
 // stages deep, which keeps enough K/V bytes in flight to stream the cache at memory speed.
 struct AttnFwdSmem {
   static constexpr int kMaxStages = 3;
-  static constexpr int kBars = 6 * kTileBytes + 4096;  // decode layout: 4 KB of Q/P + two 3-stage rings
+  static constexpr int kBars = 6 * kTileBytes + 16384; // decode layout: up to 16 KB of Q/P (32 rows) + two 3-stage rings
   static constexpr int kXch = kBars + 256;             // row-wise exchange of partial maxima / sums
   static constexpr int kBytes = kXch + 6144 + 1024;
 };
@@ -161,6 +175,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   int max_kv = t.pos0 + (t.n_rows - 1) * t.pos_step + 1;
   if (max_kv > t.kv_cap) max_kv = t.kv_cap;
   const int nblk = (max_kv + kAttnBlock - 1) / kAttnBlock;
+  // blocks [b0, nblk) are processed; ring slots and barrier phases count from b0
+  int b0 = 0, st_mode = 0, st_row = 0;
+  if (p.tile_ext != nullptr) {
+    b0 = p.tile_ext[4 * blockIdx.x];
+    st_mode = p.tile_ext[4 * blockIdx.x + 1];
+    st_row = p.tile_ext[4 * blockIdx.x + 2];
+    if (b0 > nblk) b0 = nblk;
+  }
 
   const uint32_t sQ = smem_u32(smem);
   const uint32_t sP = sQ + off_p;
@@ -172,11 +194,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (warp == 0) {
     if (lane == 0) {
       mbar_expect_tx(BAR(Q_FULL), 2 * q_half);
-      tma_load_2d(sQ, &tmQ, t.q_col0, t.q_row0, BAR(Q_FULL));
-      tma_load_2d(sQ + q_half, &tmQ, t.q_col0 + 64, t.q_row0, BAR(Q_FULL));
-      for (int b = 0; b < nblk; ++b) {
-        const int s = b % nstage;
-        const uint32_t ph = (b / nstage) & 1;
+      if (p.q3d) {
+        const int y = t.q_row0 % p.q_seq_rows, z = t.q_row0 / p.q_seq_rows;
+        tma_load_3d(sQ, &tmQ, t.q_col0, y, z, BAR(Q_FULL));
+        tma_load_3d(sQ + q_half, &tmQ, t.q_col0 + 64, y, z, BAR(Q_FULL));
+      } else {
+        tma_load_2d(sQ, &tmQ, t.q_col0, t.q_row0, BAR(Q_FULL));
+        tma_load_2d(sQ + q_half, &tmQ, t.q_col0 + 64, t.q_row0, BAR(Q_FULL));
+      }
+      for (int b = b0; b < nblk; ++b) {
+        const int s = (b - b0) % nstage;
+        const uint32_t ph = ((b - b0) / nstage) & 1;
         int src, row;
         cp_locate(p, t, b, src, row);
         if (NSRC == 1) src = 0;
@@ -203,11 +231,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);  // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, 128, 0, 1);  // P (K-major) x V (MN-major)
-      auto issue_s = [&](int b) -> bool {
-        const int s = b % nstage;               // K/V ring slot
-        const uint32_t ph = (b / nstage) & 1;
-        const int sb = b & 1;                   // S accumulator buffer
-        const uint32_t phs = (b >> 1) & 1;
+      auto issue_s = [&](int i) -> bool {       // i = block index relative to b0
+        const int s = i % nstage;               // K/V ring slot
+        const uint32_t ph = (i / nstage) & 1;
+        const int sb = i & 1;                   // S accumulator buffer
+        const uint32_t phs = (i >> 1) & 1;
         if (!mbar_wait(BAR(K_FULL + s), ph, abort_flag, p.status, 203)) return false;
         if (!mbar_wait(BAR(S_EMPTY + sb), phs ^ 1, abort_flag, p.status, 204)) return false;
         tc_fence_after();
@@ -222,10 +250,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         umma_commit(BAR(K_EMPTY + s));
         return true;
       };
+      const int nb = nblk - b0;
       bool ok = mbar_wait(BAR(Q_FULL), 0, abort_flag, p.status, 205);
-      if (ok && nblk > 0) ok = issue_s(0);
-      for (int b = 0; ok && b < nblk; ++b) {
-        if (b + 1 < nblk) ok = issue_s(b + 1);
+      if (ok && nb > 0) ok = issue_s(0);
+      for (int b = 0; ok && b < nb; ++b) {
+        if (b + 1 < nb) ok = issue_s(b + 1);
         if (!ok) break;
         const int s = b % nstage;
         const uint32_t ph = (b / nstage) & 1;
@@ -264,17 +293,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float o[32];
 #pragma unroll
     for (int i = 0; i < 32; ++i) o[i] = 0.f;
+    float* st_ptr = nullptr;     // this row's saved state (resumable rows)
+    if (st_mode != 0 && r < t.n_rows) {
+      const int rps = p.q_rows_per_seq > 0 ? p.q_rows_per_seq : 1;
+      st_ptr = p.state + static_cast<long long>(st_row + (r / rps) * p.q_seq_rows + r % rps) * kAttnStateFloats;
+      if (st_mode == 2) {
+        m_run = st_ptr[0];
+        l_part = st_ptr[4 + split];
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float4 v = *reinterpret_cast<const float4*>(st_ptr + 8 + split * 32 + j);
+          o[j] = v.x; o[j + 1] = v.y; o[j + 2] = v.z; o[j + 3] = v.w;
+        }
+      }
+    }
+    const int nb = nblk - b0;
     uint8_t* p_row = smem + off_p;
     float* xch = reinterpret_cast<float*>(smem + AttnFwdSmem::kXch);  // [2][128][4] maxima, then [128][4] sums
     bool alive = true;
     float alpha_prev = 0.f;
 
-    for (int b = 0; b < nblk; ++b) {
+    for (int b = 0; b < nb; ++b) {              // b counts from the tile's first block b0
       const int s = b & 1;
       const uint32_t ph = (b >> 1) & 1;
       if (!mbar_wait(BAR(S_FULL + s), ph, abort_flag, p.status, 208)) { alive = false; break; }
       tc_fence_after();
-      const int nvis = kv_len - b * kAttnBlock - split * 32;  // visible keys among this thread's 32
+      const int nvis = kv_len - (b0 + b) * kAttnBlock - split * 32;  // visible keys among this thread's 32
       uint32_t x[32];
       tmem_ld32(tmem_base + lane_off + TM_S + s * 128 + split * 32, x);
       tmem_ld_wait();
@@ -330,8 +374,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       m_run = m_new;
       alpha_prev = alpha;
     }
-    if (alive && nblk > 0) {
-      if (mbar_wait(BAR(O_FULL), (nblk - 1) & 1, abort_flag, p.status, 209)) {
+    if (alive && nb > 0) {
+      if (mbar_wait(BAR(O_FULL), (nb - 1) & 1, abort_flag, p.status, 209)) {
         tc_fence_after();
         uint32_t xo[32];
         tmem_ld32(tmem_base + lane_off + TM_O + split * 32, xo);
@@ -347,7 +391,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float* lx = xch + 1024;
     lx[r * 4 + split] = l_part;
     mbar_arrive(BAR(XCH + quad));
-    if (alive && mbar_wait(BAR(XCH + quad), nblk & 1, abort_flag, p.status, 211) && r < t.n_rows) {
+    if (st_mode == 1) {
+      // resumable rows: hand the running state on instead of normalising
+      if (alive && st_ptr != nullptr) {
+        if (split == 0) st_ptr[0] = m_run;
+        st_ptr[4 + split] = l_part;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(st_ptr + 8 + split * 32 + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+      }
+    } else if (alive && mbar_wait(BAR(XCH + quad), nb & 1, abort_flag, p.status, 211) && r < t.n_rows) {
       const float4 ll = *reinterpret_cast<const float4*>(lx + r * 4);
       const float l_run = (ll.x + ll.y) + (ll.z + ll.w);
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
@@ -412,7 +465,8 @@ RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long
                          long long ldo, float* lse, const void* tiles, int n_tiles, float scale,
                          int cp_blocks_per_chunk, int cp_zigzag, int decode_rows,
                          const int* page_table, void* stage_k, void* stage_v, int* stage_flags,
-                         int stage_rows, int cp_rank, void* stream) {
+                         int stage_rows, int cp_rank, const int* tile_ext, float* state,
+                         int q_rows_per_seq, int q_seq_rows, int q_group, void* stream) {
   using namespace rlk;
   RLK_REQUIRE(n_tiles > 0, "attn_fwd: no tiles");
   RLK_REQUIRE(n_src == 1 || (n_src >= 2 && n_src <= 8), "attn_fwd: n_src must be 1..8");
@@ -433,8 +487,26 @@ RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long
   p.status = device_status_word();
   p.page_table = page_table;
   p.q_rows_box = decode_rows ? 8 : 128;
+  p.tile_ext = tile_ext;
+  p.state = state;
+  p.q_rows_per_seq = q_rows_per_seq;
+  p.q_seq_rows = q_seq_rows;
+  RLK_REQUIRE(tile_ext == nullptr || (state != nullptr && n_src == 1 && q_seq_rows > 0),
+              "attn_fwd: resumable rows need a state buffer, one KV source and the row geometry");
   CUtensorMap tmQ;
-  int rc = make_tmap_2d_sw128(&tmQ, Q, q_rows, q_cols, ldq, p.q_rows_box, 64, 2);
+  int rc;
+  if (q_group > 0) {
+    // a tile's rows: q_rows_per_seq rows of each of q_group consecutive sequences
+    RLK_REQUIRE(decode_rows && q_rows_per_seq > 0 && q_seq_rows > 0 && q_rows_per_seq * q_group <= 32 &&
+                    (q_rows_per_seq * q_group) % 8 == 0 && q_rows % q_seq_rows == 0 && q_cols == 128,
+                "attn_fwd: grouped query tiles hold 8 to 32 rows of 128 columns");
+    p.q_rows_box = q_rows_per_seq * q_group;
+    p.q3d = 1;
+    rc = make_tmap_3d_sw128_box(&tmQ, Q, q_rows / q_seq_rows, q_seq_rows, q_cols, ldq, ldq * q_seq_rows,
+                                q_group, q_rows_per_seq, 64, 2);
+  } else {
+    rc = make_tmap_2d_sw128(&tmQ, Q, q_rows, q_cols, ldq, p.q_rows_box, 64, 2);
+  }
   if (rc) return rc;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (n_src == 1) {

@@ -103,7 +103,7 @@ struct GemmSmem {
   static constexpr int kStageA = BM * BK * 2;
   static constexpr int kStageB = BN * BK * 2;
   static constexpr int kStage = kStageA + kStageB;
-  static constexpr int kStages = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int kStages = (BN >= 192) ? 4 : (BN >= 128 ? 6 : 8);
   static constexpr int kBarBytes = 512;           // room for the barriers of kMaxStages stages
   static constexpr int kBytes = 227 * 1024;       // the launch may use up to all of an SM's shared memory
 };
@@ -126,7 +126,8 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   using S = GemmSmem<BN>;
   const uint32_t kStages = static_cast<uint32_t>(p.stages);   // ring depth chosen by the host (<= kMaxStages)
   // TMEM columns: two accumulators (+ three packed-bf16 tree levels when chunked, BN==128 only)
-  constexpr uint32_t kTmemCols = (BN == 128) ? 512 : (2 * BN < 32 ? 32 : 2 * BN);
+  constexpr uint32_t kAcc = (BN == 192) ? 256 : BN;   // column stride between the two accumulators
+  constexpr uint32_t kTmemCols = (BN == 128 || BN == 192) ? 512 : (2 * BN < 32 ? 32 : 2 * BN);
   constexpr uint32_t kStackCol = 2 * BN;  // first column of the tree stack (BN == 128)
 
   extern __shared__ uint8_t smem_raw[];
@@ -259,7 +260,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           const uint32_t a = u & 1;
           if (!mbar_wait(acce0 + 8 * a, ((u >> 1) & 1) ^ 1, abort_flag, p.status, 102)) break;
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + a * BN;
+          const uint32_t d_tmem = tmem_base + a * kAcc;
           for (int kb = 0; kb < p.kb_per_chunk; ++kb) {
             if (!mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 103)) break;
             tc_fence_after();
@@ -304,7 +305,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll 1
           for (int col0 = 0; col0 < BN; col0 += 32) {
             uint32_t r[32];
-            tmem_ld32(tmem_base + lane_off + a * BN + col0, r);
+            tmem_ld32(tmem_base + lane_off + a * kAcc + col0, r);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j)
@@ -315,7 +316,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll 1
           for (int col0 = 0; col0 < BN; col0 += 32) {
             uint32_t r[32];
-            tmem_ld32(tmem_base + lane_off + a * BN + col0, r);
+            tmem_ld32(tmem_base + lane_off + a * kAcc + col0, r);
             tmem_ld_wait();
             float z[32];
 #pragma unroll
@@ -379,7 +380,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll
                 for (int q = 0; q < 4; ++q) cur[lv][q] = sbase[lv * kLevel + sl * 4 + q];
             uint32_t r[32];
-            tmem_ld32(tmem_base + lane_off + a * BN + sl * 32, r);
+            tmem_ld32(tmem_base + lane_off + a * kAcc + sl * 32, r);
             tmem_ld_wait();
             uint32_t v[16];
 #pragma unroll
@@ -439,7 +440,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 #pragma unroll 1
         for (int col0 = half * kColsPerWarp; col0 < (half + 1) * kColsPerWarp; col0 += 32) {
           uint32_t r[32];
-          tmem_ld32(tmem_base + lane_off + a * BN + col0, r);
+          tmem_ld32(tmem_base + lane_off + a * kAcc + col0, r);
           tmem_ld_wait();
           if (p.nchunks == 1) {
             if (row < p.M) {
@@ -660,7 +661,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   p.n_tiles = (p.N + BN - 1) / BN;
   const int tiles = p.m_tiles * p.n_tiles * p.split_chunks;
   int ctas_per_sm = (GemmSmem<BN>::kBytes + 1024) / (smem_bytes + 1024);   // shared memory
-  const int tmem_fit = 512 / ((BN == 128) ? 512 : (2 * BN < 32 ? 32 : 2 * BN));          // tensor memory columns
+  const int tmem_fit = 512 / ((BN == 128 || BN == 192) ? 512 : (2 * BN < 32 ? 32 : 2 * BN));   // tensor memory columns
   if (ctas_per_sm > tmem_fit) ctas_per_sm = tmem_fit;
   if (ctas_per_sm > 2) ctas_per_sm = 2;
   if (ctas_per_sm < 1) ctas_per_sm = 1;
@@ -769,11 +770,17 @@ RLK_API int rlk_det_gemm(const void* A, const void* B, void* C, int M, int N, in
     // (measured, M = 64, K = 4096: N = 24576 57 us at 256 vs 62 us at 128; N = 6144 equal at 32 / 64)
     while (bn > 32 && (long long)m_tiles * ((N + bn - 1) / bn) < sms * 5 / 8) bn >>= 1;
     if (b_mn || a_mn) bn = bn < 128 ? 128 : bn;
+    // one row of tiles (decode): a 256-wide tile takes in its k blocks at the SM's ingest rate, so
+    // 192-wide tiles on more SMs finish sooner when they still fit in one wave
+    // (N = 24576: 128 tiles instead of 96)
+    if (bn == 256 && m_tiles == 1 && !a_mn && !b_mn && N % 192 == 0 && N / 192 <= sms && N / 192 > (N + 255) / 256)
+      bn = 192;
   }
 #define RLK_GEMM_CASE(BN_, AM_, BM_)                                       \
   if (bn == BN_ && a_mn == AM_ && b_mn == BM_)                             \
     return launch_gemm<BN_, (AM_ != 0), (BM_ != 0)>(A, B, p, lda, ldb, s);
   RLK_GEMM_CASE(256, 0, 0)
+  RLK_GEMM_CASE(192, 0, 0)
   RLK_GEMM_CASE(128, 0, 0)
   RLK_GEMM_CASE(64, 0, 0)
   RLK_GEMM_CASE(32, 0, 0)

@@ -47,6 +47,11 @@ int make_tmap_2d_sw128(CUtensorMap* out, const void* base, uint64_t rows, uint64
 int make_tmap_3d_sw128(CUtensorMap* out, const void* base, uint64_t batch, uint64_t rows,
                        uint64_t cols, uint64_t row_stride_elems, uint64_t batch_stride_elems,
                        uint32_t box_rows, uint32_t box_cols, int elem_bytes);
+// Same with a box that spans box_batch consecutive batch entries (they land one after the other in
+// shared memory, box_rows rows of 128 bytes each).
+int make_tmap_3d_sw128_box(CUtensorMap* out, const void* base, uint64_t batch, uint64_t rows,
+                           uint64_t cols, uint64_t row_stride_elems, uint64_t batch_stride_elems,
+                           uint32_t box_batch, uint32_t box_rows, uint32_t box_cols, int elem_bytes);
 
 int sm_count();
 

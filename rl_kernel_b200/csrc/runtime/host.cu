@@ -97,6 +97,13 @@ int make_tmap_2d_sw128(CUtensorMap* out, const void* base, uint64_t rows, uint64
 int make_tmap_3d_sw128(CUtensorMap* out, const void* base, uint64_t batch, uint64_t rows,
                        uint64_t cols, uint64_t row_stride_elems, uint64_t batch_stride_elems,
                        uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
+  return make_tmap_3d_sw128_box(out, base, batch, rows, cols, row_stride_elems, batch_stride_elems, 1,
+                                box_rows, box_cols, elem_bytes);
+}
+
+int make_tmap_3d_sw128_box(CUtensorMap* out, const void* base, uint64_t batch, uint64_t rows,
+                           uint64_t cols, uint64_t row_stride_elems, uint64_t batch_stride_elems,
+                           uint32_t box_batch, uint32_t box_rows, uint32_t box_cols, int elem_bytes) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return set_error(RLK_ERR_CUDA, "cuTensorMapEncodeTiled entry point unavailable");
   RLK_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA base must be 16-byte aligned");
@@ -107,7 +114,8 @@ int make_tmap_3d_sw128(CUtensorMap* out, const void* base, uint64_t batch, uint6
   cuuint64_t dims[3] = {cols, rows, batch};
   cuuint64_t strides[2] = {row_stride_elems * static_cast<uint64_t>(elem_bytes),
                            batch_stride_elems * static_cast<uint64_t>(elem_bytes)};
-  cuuint32_t box[3] = {box_cols, box_rows, 1};
+  RLK_REQUIRE(box_batch >= 1 && box_rows >= 1 && box_batch * box_rows <= 256, "TMA box out of range");
+  cuuint32_t box[3] = {box_cols, box_rows, box_batch};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(out, dtype_for(elem_bytes), 3, const_cast<void*>(base), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,

@@ -296,6 +296,13 @@ class SharedPrefixKV:
     prompt_len: int
     blocks_per_seq: int
     seq_of_tile: torch.Tensor | None = None
+    # prompt blocks attended once per (prompt, KV head) for the whole group; the per-sequence
+    # tiles resume from the saved row state (decode_tiles_shared_prefix fills these)
+    prefix_tiles: torch.Tensor | None = None
+    prefix_ext: torch.Tensor | None = None
+    seq_ext: torch.Tensor | None = None
+    row_state: torch.Tensor | None = None
+    group: int = 0
 
 
 @dataclass
@@ -333,6 +340,8 @@ class Qwen3Engine:
         self.fuse_gemm_allreduce = True
         self.cp = None                               # CPAttention once enable_context_parallel ran
         self._decode_page_table = None               # set while a paged decode step runs
+        self._decode_shared = None                   # SharedPrefixKV whose prompt blocks are attended per group
+        self.group_prefix_attention = True           # False: every sequence walks its prompt blocks itself
         self._tiles: dict[tuple, tuple[torch.Tensor, torch.Tensor]] = {}
         for K in (params.q_local, params.i_local):
             if self.nchunks > 1 and (K // self.nchunks) % 64:
@@ -498,6 +507,18 @@ class Qwen3Engine:
         return dh2
 
     def _attention(self, q2d, k2d, v2d, o2d, lse, tiles, decode: bool = False):
+        sp = self._decode_shared if decode else None
+        if sp is not None and sp.prefix_tiles is not None and self.group_prefix_attention:
+            # The group's rows walk the shared prompt blocks together (one K/V fetch and one MMA
+            # chain per block for all samples), save their running softmax state, and every
+            # sequence resumes from it on its own response blocks: per row the same block
+            # updates in the same order as an uninterrupted run.
+            g = self.hq // self.hkv
+            nv.attn_fwd(q2d, [k2d], [v2d], o2d, None, sp.prefix_tiles, self.scale, decode=True,
+                        page_table=sp.page_table, resume=(sp.prefix_ext, sp.row_state, g, self.hq, sp.group))
+            nv.attn_fwd(q2d, [k2d], [v2d], o2d, lse, tiles, self.scale, decode=True,
+                        page_table=sp.page_table, resume=(sp.seq_ext, sp.row_state, g, self.hq, 0))
+            return
         nv.attn_fwd(q2d, [k2d], [v2d], o2d, lse, tiles, self.scale,
                     decode=decode and self.hq // self.hkv <= 8,
                     page_table=self._decode_page_table if decode else None)
@@ -935,7 +956,27 @@ class Qwen3Engine:
         t[:, 11] = (b * sp.blocks_per_seq + 1).to(torch.int32).to(self.dev)
         hk = torch.arange(self.hkv).view(1, -1).expand(nseq, self.hkv).reshape(-1)
         order = torch.argsort((b // group) * (self.hkv * group) + hk * group + b % group, stable=True)
-        return t[order.to(self.dev)].contiguous()
+        t = t[order.to(self.dev)].contiguous()
+        g = self.hq // self.hkv
+        P = sp.prompt_len
+        if P % 128 == 0 and P > 0 and nseq % group == 0 and g * group <= 32 and (g * group) % 8 == 0:
+            npr = nseq // group
+            pi = torch.arange(npr).view(-1, 1).expand(npr, self.hkv).reshape(-1)
+            ph = torch.arange(self.hkv).view(1, -1).expand(npr, self.hkv).reshape(-1)
+            z = torch.zeros_like(pi)
+            row0 = pi * group * self.hq + ph * g
+            pt = torch.stack([row0, z, z + g * group, z, ph * self.d, z + P - 1, z, z + P, z, z + 1, z,
+                              pi * group * sp.blocks_per_seq + 1], dim=-1)
+            sp.prefix_tiles = pt.to(torch.int32).to(self.dev).contiguous()
+            sp.prefix_ext = torch.stack([z, z + 1, row0, z], dim=-1).to(torch.int32).to(self.dev).contiguous()
+            se = torch.zeros(t.shape[0], 4, dtype=torch.int32, device=self.dev)
+            se[:, 0] = P // 128
+            se[:, 1] = 2
+            se[:, 2] = t[:, 0]
+            sp.seq_ext = se.contiguous()
+            sp.row_state = torch.zeros(nseq * self.hq, 136, dtype=torch.float32, device=self.dev)
+            sp.group = group
+        return t
 
     def decode_tiles(self, nseq: int, max_len: int) -> torch.Tensor:
         """Static part of the decode tile table; columns 5 (pos0) and 7 (kv_cap) change per step."""
@@ -968,6 +1009,7 @@ class Qwen3Engine:
             torch.add(shared.slot_base, pos - shared.prompt_len, out=slot)
         tiles[:, 7] = tiles[:, 5] + 1
         self._decode_page_table = shared.page_table if shared is not None else None
+        self._decode_shared = shared
         x = ws.get("d.embed", (B, H))
         nv.embedding_fwd(tokens, self.p.w["embed"], x, self.p.vocab_start)
         self.ctx.tp_all_reduce_(x)
@@ -976,6 +1018,7 @@ class Qwen3Engine:
             x, res = self._layer_fwd(l, x, res, B, pos, tiles=tiles, kbuf=kv.k[l], vbuf=kv.v[l],
                                      kv_slot=slot, q_view=(B * self.hq, self.d), tag="d")
         self._decode_page_table = None
+        self._decode_shared = None
         hf = ws.get("d.hf", (B, H))
         s_fin = ws.get("d.s_fin", (B, H))
         self._norm_after(x, self.p.w["norm"], hf, res, s_fin)

@@ -101,6 +101,32 @@ def test_grpo_step_rollout_equals_training_bitwise():
     assert torch.equal(outs[0]["train_logp"], outs[1]["train_logp"])
 
 
+def test_grouped_prompt_attention_in_decode_keeps_the_bits():
+    """Decode with a shared prompt: the group's rows walk the prompt blocks in one tile and every
+    sequence resumes from the saved row state; tokens, rollout log-probs and training log-probs must
+    equal the run in which every sequence walks its prompt blocks itself."""
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
+
+    spec = _spec()                      # 8 query heads on 2 KV heads: 4 rows per sequence and KV head
+    w = Qwen3DenseWeights.synthetic(spec, seed=7)
+    prompts = torch.randint(0, spec.vocab_size, (2, 256), generator=torch.Generator().manual_seed(9)).to(dev())
+    outs = []
+    for grouped in (True, False):
+        cfg = GRPOConfig(num_prompts=2, group_size=8, prompt_len=256, response_len=140, micro_batch_seqs=8,
+                         lr=1e-4, use_cuda_graph=grouped)
+        tr = GRPOTrainer(spec, cfg, dev(), weights=w)
+        tr.rollout_engine.group_prefix_attention = grouped
+        out = tr.step(prompts, step_index=0)
+        sync_and_check()
+        if grouped:
+            assert tr._shared is not None and tr._shared.prefix_tiles is not None
+        assert tr.mismatch_count(out["train_logp"], out["old_logp"]) == 0
+        outs.append({k: out[k].clone() for k in ("tokens", "old_logp")})
+    assert torch.equal(outs[0]["tokens"], outs[1]["tokens"])
+    assert torch.equal(outs[0]["old_logp"], outs[1]["old_logp"])
+
+
 def test_gradients_against_autograd():
     from rl_kernel_b200.models.qwen3 import Qwen3DenseWeights
     from rl_kernel_b200.models.qwen3.engine import PackedParams, Qwen3Engine

@@ -29,13 +29,21 @@ def test_accuracy_and_tile_invariance(shape):
     M, N, K = shape
     a, b = _mk(M, N, K)
     ref = a.float() @ b.float().t()
-    outs = {bn: _gemm(a, b, M, N, K, tile_n=bn) for bn in (256, 128, 64, 32)}
+    outs = {bn: _gemm(a, b, M, N, K, tile_n=bn) for bn in (256, 192, 128, 64, 32)}
     tol = 2 ** -8 * ref.abs().max().item() + 1e-3
     assert (outs[256].float() - ref).abs().max().item() <= tol
-    for bn in (128, 64, 32):
+    for bn in (192, 128, 64, 32):
         assert torch.equal(outs[256], outs[bn]), f"tile_n={bn} changed bits"
     f32 = _gemm(a, b, M, N, K, tile_n=128, dtype=torch.float32)
     assert torch.equal(f32.to(BF), outs[128])
+
+
+def test_decode_shape_picks_a_one_wave_tile_and_keeps_the_bits():
+    # 64 rows against the gate/up projection: the kernel's own choice (192-wide tiles, one wave)
+    # must give the bits of every other tile width
+    M, N, K = 64, 24576, 1024
+    a, b = _mk(M, N, K)
+    assert torch.equal(_gemm(a, b, M, N, K), _gemm(a, b, M, N, K, tile_n=128))
 
 
 def test_batch_invariance():
