@@ -232,7 +232,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (marks the config)")
     ap.add_argument("--response-len", type=int, default=RESPONSE_LEN, help="debug only")
     ap.add_argument("--micro-batch", type=int, default=8)
-    ap.add_argument("--train-micro-batch", type=int, default=2,
+    ap.add_argument("--train-micro-batch", type=int, default=4,
                     help="sequences per training micro-batch with stored activations (0 = recompute, --micro-batch)")
     ap.add_argument("--plan", default="", help="debug only: e.g. tp1xcp2 instead of the default plan for --gpus")
     args = ap.parse_args()

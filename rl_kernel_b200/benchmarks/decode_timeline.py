@@ -4,7 +4,7 @@ programmatic dependent launch, so the per-kernel device times of an ncu launch l
 cold cache) do not add up to the step; this listing shows where the step's time really goes.
 Times taken under the profiler are for analysis only -- report ``benchmarks.decode_step`` numbers.
 
-    python -m rl_kernel_b200.benchmarks.decode_timeline [layers] [batch]
+    python -m rl_kernel_b200.benchmarks.decode_timeline [layers] [batch] [shared prompt length]
 """
 from __future__ import annotations
 
@@ -23,15 +23,22 @@ def main() -> None:
     spec = Qwen3DenseSpec.official().with_layers(layers)
     params = PackedParams(spec, 0, 1, dev).init_synthetic_(1)
     eng = Qwen3Engine(spec, params, max_positions=max_len + 8)
-    kv = eng.new_kv_cache(B, max_len)
-    tiles = eng.decode_tiles(B, max_len)
+    shared_len = int(sys.argv[3]) if len(sys.argv) > 3 else 0
+    shared = None
+    if shared_len:
+        shared = eng.new_shared_prefix_cache(B // 8, 8, shared_len, max_len - shared_len)
+        kv = shared.kv
+        tiles = eng.decode_tiles_shared_prefix(shared, 8)
+    else:
+        kv = eng.new_kv_cache(B, max_len)
+        tiles = eng.decode_tiles(B, max_len)
     for t in kv.k + kv.v:
         t.normal_(0, 1)
     tok = torch.randint(0, spec.vocab_size, (B,), device=dev)
     pos = torch.full((B,), pos0, dtype=torch.int32, device=dev)
     keys = torch.arange(B, device=dev)
     def step():
-        hf = eng.decode_step(tok, pos, kv, tiles)
+        hf = eng.decode_step(tok, pos, kv, tiles, shared=shared)
         logits = eng.logits(hf)
         return eng.sample(logits, keys, temperature=1.0, seed=1)
     for _ in range(3):
