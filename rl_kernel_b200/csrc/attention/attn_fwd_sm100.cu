@@ -61,16 +61,17 @@ struct AttnFwdParams {
 
 constexpr int kAttnStateFloats = 136;   // per row: max, 3 unused, 4 partial sums, 128 outputs
 
-// Shared memory: [Q | P | K ring | V ring | barriers].  Full tiles: Q and P are 32 KB each and the
-// rings have 2 stages.  Decode tiles (<= 8 query rows): Q and P shrink to 2 KB each -- the UMMA
-// still reads 128 "rows" from those addresses, the ones past row 8 are whatever follows in shared
-// memory and only feed accumulator rows nobody reads -- and the freed space makes the rings 3
-// stages deep, which keeps enough K/V bytes in flight to stream the cache at memory speed.
+// Shared memory: [Q (| Q) | P | K ring | V ring | barriers | exchange].  Full tiles: Q and P are
+// 32 KB each and the rings have 2 stages.  Decode tiles (<= 32 query rows): two Q buffers and P of
+// at most 8 KB each -- the UMMA still reads 128 "rows" from those addresses, the ones past the
+// tile's rows are whatever follows in shared memory and only feed accumulator rows nobody reads --
+// and the freed space makes the rings 3 stages deep, which keeps enough K/V bytes in flight to
+// stream the cache at memory speed.
+template <bool DEC>
 struct AttnFwdSmem {
-  static constexpr int kMaxStages = 3;
-  static constexpr int kBars = 6 * kTileBytes + 16384; // decode layout: up to 16 KB of Q/P (32 rows) + two 3-stage rings
+  static constexpr int kBars = 6 * kTileBytes + (DEC ? 24576 : 0);
   static constexpr int kXch = kBars + 256;             // row-wise exchange of partial maxima / sums
-  static constexpr int kBytes = kXch + 6144 + 1024;
+  static constexpr int kBytes = kXch + 8192 + 1024;
 };
 
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -102,24 +103,27 @@ __device__ __forceinline__ void cp_locate(const AttnFwdParams& p, const AttnTile
   row = t.kv_row0 + lb * kAttnBlock;
 }
 
-template <int NSRC>
+// DEC: decode tiles (at most 32 query rows; small Q / P buffers, three-stage rings, persistent CTAs
+// that walk several tiles, resumable rows).  Full tiles compile without any of that, which keeps
+// the softmax loop's registers where they were.
+template <int NSRC, bool DEC>
 __global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ KvMaps<NSRC> kv,
                 const __grid_constant__ KvMaps<1> staged, const AttnFwdParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttnFwdSmem::kBars);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttnFwdSmem<DEC>::kBars);
   // barrier indices
-  enum { Q_FULL = 0, K_FULL = 1, K_EMPTY = 4, V_FULL = 7, V_EMPTY = 10, S_FULL = 13, S_EMPTY = 15,
-         P_FULL = 17, O_FULL = 18, XCH = 19, NBARS = 23 };
-  const bool decode = p.q_rows_box < 128;
-  const int nstage = decode ? 3 : 2;
+  enum { Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, K_EMPTY = 7, V_FULL = 10, V_EMPTY = 13, S_FULL = 16, S_EMPTY = 18,
+         P_FULL = 20, O_FULL = 21, XCH = 22, NBARS = 26 };
+  constexpr bool decode = DEC;
+  constexpr int nstage = decode ? 3 : 2;
   const uint32_t q_half = static_cast<uint32_t>(p.q_rows_box) * 128u;  // bytes of one 64-column half of Q / P
-  const uint32_t off_p = 2 * q_half;
-  const uint32_t off_k = 4 * q_half;
+  const uint32_t off_p = (decode ? 4 : 2) * q_half;   // decode: two Q buffers, then P
+  const uint32_t off_k = off_p + 2 * q_half;
   const uint32_t off_v = off_k + nstage * kTileBytes;
-  const int n_active = (decode ? 32 : 128) * kSplit;  // softmax threads that take part
+  constexpr int n_active = (decode ? 32 : 128) * kSplit;  // softmax threads that take part
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + NBARS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* stage_slot = reinterpret_cast<volatile int*>(tmem_slot + 2);
@@ -129,10 +133,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // Barriers and tensor memory are set up before the dependency wait, so this part overlaps the
-  // tail of the previous kernel of the stream; nothing before the wait touches global memory.
+  // Decode: barriers and tensor memory are set up before the dependency wait, so this part
+  // overlaps the tail of the previous kernel of the stream; nothing before the wait touches global
+  // memory.  Full tiles wait first and fetch their one tile descriptor right away, so that its
+  // latency hides behind the set-up instead.
+  AttnTile tile0{};
+  if (!DEC) {
+    griddep_sync();
+    tile0 = p.tiles[blockIdx.x];
+  }
   if (threadIdx.x == 0) {
-    mbar_init(BAR(Q_FULL), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(BAR(Q_FULL + s), 1);
+      mbar_init(BAR(Q_EMPTY + s), 1);
+    }
     for (int s = 0; s < 3; ++s) {
       mbar_init(BAR(K_FULL + s), 1);
       mbar_init(BAR(K_EMPTY + s), 1);
@@ -157,33 +171,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  griddep_sync();
+  if (DEC) griddep_sync();
 
-  const AttnTile t = p.tiles[blockIdx.x];
+  // A CTA walks tiles blockIdx.x, blockIdx.x + gridDim.x, ...  (decode launches are persistent: one
+  // CTA per SM; the loads of the next tile start while the current one is still in its softmax
+  // and epilogue, which hides the per-tile start-up).  Barrier phases therefore follow running
+  // counters -- blocks, S buffers, tiles -- that every role advances in the same way.
   const bool use_stage = NSRC > 1 && p.stage.rows > 0;
-  if (t.n_rows <= 0) {
-    // an empty tile still helps with the staging copies (its threads do nothing else)
-    if (use_stage && warp >= 2) cp_stage_gather(p.stage, threadIdx.x - 64, kAttnThreads - 64, 3, stage_slot);
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 1) {
-      tc_fence_after();
-      tmem_dealloc(tmem_base, 512);
-    }
-    return;
-  }
-  int max_kv = t.pos0 + (t.n_rows - 1) * t.pos_step + 1;
-  if (max_kv > t.kv_cap) max_kv = t.kv_cap;
-  const int nblk = (max_kv + kAttnBlock - 1) / kAttnBlock;
-  // blocks [b0, nblk) are processed; ring slots and barrier phases count from b0
-  int b0 = 0, st_mode = 0, st_row = 0;
-  if (p.tile_ext != nullptr) {
-    b0 = p.tile_ext[4 * blockIdx.x];
-    st_mode = p.tile_ext[4 * blockIdx.x + 1];
-    st_row = p.tile_ext[4 * blockIdx.x + 2];
-    if (b0 > nblk) b0 = nblk;
-  }
-
+  constexpr int nq = decode ? 2 : 1;             // Q buffers (decode tiles are small enough for two)
+  // full tiles: exactly one tile per CTA (the loops below then run once and fold away)
+  const int tile_step = decode ? static_cast<int>(gridDim.x) : 0x40000000;
   const uint32_t sQ = smem_u32(smem);
   const uint32_t sP = sQ + off_p;
   const uint32_t sK = sQ + off_k;
@@ -191,51 +188,85 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr uint32_t TM_S = 0;     // two S buffers: columns [0,128) and [128,256)
   constexpr uint32_t TM_O = 256;   // O_blk: columns [256,384)
 
+  struct TileInfo { AttnTile t; int nblk, b0, st_mode, st_row; };
+  auto read_tile = [&](int idx) {
+    TileInfo ti;
+    ti.t = DEC ? p.tiles[idx] : tile0;
+    int max_kv = ti.t.pos0 + (ti.t.n_rows - 1) * ti.t.pos_step + 1;
+    if (max_kv > ti.t.kv_cap) max_kv = ti.t.kv_cap;
+    ti.nblk = ti.t.n_rows > 0 ? (max_kv + kAttnBlock - 1) / kAttnBlock : 0;
+    // blocks [b0, nblk) are processed
+    ti.b0 = 0; ti.st_mode = 0; ti.st_row = 0;
+    if (decode && p.tile_ext != nullptr) {
+      ti.b0 = p.tile_ext[4 * idx];
+      ti.st_mode = p.tile_ext[4 * idx + 1];
+      ti.st_row = p.tile_ext[4 * idx + 2];
+      if (ti.b0 > ti.nblk) ti.b0 = ti.nblk;
+    }
+    return ti;
+  };
+
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(BAR(Q_FULL), 2 * q_half);
-      if (p.q3d) {
-        const int y = t.q_row0 % p.q_seq_rows, z = t.q_row0 / p.q_seq_rows;
-        tma_load_3d(sQ, &tmQ, t.q_col0, y, z, BAR(Q_FULL));
-        tma_load_3d(sQ + q_half, &tmQ, t.q_col0 + 64, y, z, BAR(Q_FULL));
-      } else {
-        tma_load_2d(sQ, &tmQ, t.q_col0, t.q_row0, BAR(Q_FULL));
-        tma_load_2d(sQ + q_half, &tmQ, t.q_col0 + 64, t.q_row0, BAR(Q_FULL));
-      }
-      for (int b = b0; b < nblk; ++b) {
-        const int s = (b - b0) % nstage;
-        const uint32_t ph = ((b - b0) / nstage) & 1;
-        int src, row;
-        cp_locate(p, t, b, src, row);
-        if (NSRC == 1) src = 0;
-        const CUtensorMap* mk = &kv.k[src];
-        const CUtensorMap* mv = &kv.v[src];
-        if (use_stage && src != p.stage.rank) {
-          // remote block: read the local copy once it has landed
-          if (!cp_stage_wait(p.stage, src, row / kAttnBlock, abort_flag, p.status, 212)) break;
-          row += src * p.stage.rows;
-          mk = &staged.k[0];
-          mv = &staged.v[0];
+      uint32_t kc = 0, tc = 0;       // blocks and tiles issued so far
+      bool ok = true;
+      for (int idx = blockIdx.x; ok && idx < p.n_tiles; idx += tile_step) {
+        const TileInfo ti = read_tile(idx);
+        const AttnTile& t = ti.t;
+        if (t.n_rows <= 0) continue;
+        const uint32_t qs = tc % nq, qph = (tc / nq) & 1;
+        ++tc;
+        if (!mbar_wait(BAR(Q_EMPTY + qs), qph ^ 1, abort_flag, p.status, 213)) break;
+        const uint32_t q_dst = sQ + qs * 2 * q_half;
+        mbar_expect_tx(BAR(Q_FULL + qs), 2 * q_half);
+        if (p.q3d) {
+          const int y = t.q_row0 % p.q_seq_rows, z = t.q_row0 / p.q_seq_rows;
+          tma_load_3d(q_dst, &tmQ, t.q_col0, y, z, BAR(Q_FULL + qs));
+          tma_load_3d(q_dst + q_half, &tmQ, t.q_col0 + 64, y, z, BAR(Q_FULL + qs));
+        } else {
+          tma_load_2d(q_dst, &tmQ, t.q_col0, t.q_row0, BAR(Q_FULL + qs));
+          tma_load_2d(q_dst + q_half, &tmQ, t.q_col0 + 64, t.q_row0, BAR(Q_FULL + qs));
         }
-        if (!mbar_wait(BAR(K_EMPTY + s), ph ^ 1, abort_flag, p.status, 201)) break;
-        mbar_expect_tx(BAR(K_FULL + s), kTileBytes);
-        tma_load_2d(sK + s * kTileBytes, mk, t.kv_col0, row, BAR(K_FULL + s));
-        tma_load_2d(sK + s * kTileBytes + kHalfBytes, mk, t.kv_col0 + 64, row, BAR(K_FULL + s));
-        if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1, abort_flag, p.status, 202)) break;
-        mbar_expect_tx(BAR(V_FULL + s), kTileBytes);
-        tma_load_2d(sV + s * kTileBytes, mv, t.kv_col0, row, BAR(V_FULL + s));
-        tma_load_2d(sV + s * kTileBytes + kHalfBytes, mv, t.kv_col0 + 64, row, BAR(V_FULL + s));
+        for (int b = ti.b0; b < ti.nblk; ++b, ++kc) {
+          const int s = kc % nstage;
+          const uint32_t ph = (kc / nstage) & 1;
+          int src, row;
+          cp_locate(p, t, b, src, row);
+          if (NSRC == 1) src = 0;
+          const CUtensorMap* mk = &kv.k[src];
+          const CUtensorMap* mv = &kv.v[src];
+          if (use_stage && src != p.stage.rank) {
+            // remote block: read the local copy once it has landed
+            if (!cp_stage_wait(p.stage, src, row / kAttnBlock, abort_flag, p.status, 212)) { ok = false; break; }
+            row += src * p.stage.rows;
+            mk = &staged.k[0];
+            mv = &staged.v[0];
+          }
+          if (!mbar_wait(BAR(K_EMPTY + s), ph ^ 1, abort_flag, p.status, 201)) { ok = false; break; }
+          mbar_expect_tx(BAR(K_FULL + s), kTileBytes);
+          tma_load_2d(sK + s * kTileBytes, mk, t.kv_col0, row, BAR(K_FULL + s));
+          tma_load_2d(sK + s * kTileBytes + kHalfBytes, mk, t.kv_col0 + 64, row, BAR(K_FULL + s));
+          if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1, abort_flag, p.status, 202)) { ok = false; break; }
+          mbar_expect_tx(BAR(V_FULL + s), kTileBytes);
+          tma_load_2d(sV + s * kTileBytes, mv, t.kv_col0, row, BAR(V_FULL + s));
+          tma_load_2d(sV + s * kTileBytes + kHalfBytes, mv, t.kv_col0 + 64, row, BAR(V_FULL + s));
+        }
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);  // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, 128, 0, 1);  // P (K-major) x V (MN-major)
-      auto issue_s = [&](int i) -> bool {       // i = block index relative to b0
-        const int s = i % nstage;               // K/V ring slot
-        const uint32_t ph = (i / nstage) & 1;
-        const int sb = i & 1;                   // S accumulator buffer
-        const uint32_t phs = (i >> 1) & 1;
+      uint32_t sc = 0;        // S products issued so far (K ring slot, S buffer)
+      uint32_t pc = 0;        // P*V products issued so far (V ring slot, P / O phases)
+      uint32_t tc = 0;
+      uint32_t q_cur = sQ;
+      auto issue_s = [&]() -> bool {
+        const int s = sc % nstage;              // K/V ring slot
+        const uint32_t ph = (sc / nstage) & 1;
+        const int sb = sc & 1;                  // S accumulator buffer
+        const uint32_t phs = (sc >> 1) & 1;
+        ++sc;
         if (!mbar_wait(BAR(K_FULL + s), ph, abort_flag, p.status, 203)) return false;
         if (!mbar_wait(BAR(S_EMPTY + sb), phs ^ 1, abort_flag, p.status, 204)) return false;
         tc_fence_after();
@@ -243,33 +274,45 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         for (int k = 0; k < 8; ++k) {
           const uint32_t offq = (k >> 2) * q_half + (k & 3) * 32;
           const uint32_t offk = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_bf16_ss(tmem_base + TM_S + sb * 128, umma_desc_sw128(sQ + offq, 16, 1024),
+          umma_bf16_ss(tmem_base + TM_S + sb * 128, umma_desc_sw128(q_cur + offq, 16, 1024),
                        umma_desc_sw128(sK + s * kTileBytes + offk, 16, 1024), idesc_s, k != 0);
         }
         umma_commit(BAR(S_FULL + sb));
         umma_commit(BAR(K_EMPTY + s));
         return true;
       };
-      const int nb = nblk - b0;
-      bool ok = mbar_wait(BAR(Q_FULL), 0, abort_flag, p.status, 205);
-      if (ok && nb > 0) ok = issue_s(0);
-      for (int b = 0; ok && b < nb; ++b) {
-        if (b + 1 < nb) ok = issue_s(b + 1);
-        if (!ok) break;
-        const int s = b % nstage;
-        const uint32_t ph = (b / nstage) & 1;
-        if (!mbar_wait(BAR(V_FULL + s), ph, abort_flag, p.status, 206)) break;
-        if (!mbar_wait(BAR(P_FULL), b & 1, abort_flag, p.status, 207)) break;
-        tc_fence_after();
+      bool ok = true;
+      for (int idx = blockIdx.x; ok && idx < p.n_tiles; idx += tile_step) {
+        const TileInfo ti = read_tile(idx);
+        if (ti.t.n_rows <= 0) continue;
+        const int nb = ti.nblk - ti.b0;
+        const uint32_t qs = tc % nq, qph = (tc / nq) & 1;
+        ++tc;
+        q_cur = sQ + qs * 2 * q_half;
+        ok = mbar_wait(BAR(Q_FULL + qs), qph, abort_flag, p.status, 205);
+        if (ok && nb > 0) ok = issue_s();
+        for (int b = 0; ok && b < nb; ++b) {
+          if (b + 1 < nb) ok = issue_s();
+          if (!ok) break;
+          if (b + 1 >= nb) umma_commit(BAR(Q_EMPTY + qs));   // every S product of this tile has been issued
+          const int s = pc % nstage;
+          const uint32_t ph = (pc / nstage) & 1;
+          const uint32_t pph = pc & 1;
+          ++pc;
+          if (!mbar_wait(BAR(V_FULL + s), ph, abort_flag, p.status, 206)) { ok = false; break; }
+          if (!mbar_wait(BAR(P_FULL), pph, abort_flag, p.status, 207)) { ok = false; break; }
+          tc_fence_after();
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t aoff = (k >> 2) * q_half + (k & 3) * 32;
-          umma_bf16_ss(tmem_base + TM_O, umma_desc_sw128(sP + aoff, 16, 1024),
-                       umma_desc_sw128(sV + s * kTileBytes + k * 2048, kHalfBytes, 1024), idesc_o,
-                       k != 0);
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t aoff = (k >> 2) * q_half + (k & 3) * 32;
+            umma_bf16_ss(tmem_base + TM_O, umma_desc_sw128(sP + aoff, 16, 1024),
+                         umma_desc_sw128(sV + s * kTileBytes + k * 2048, kHalfBytes, 1024), idesc_o,
+                         k != 0);
+          }
+          umma_commit(BAR(O_FULL));
+          umma_commit(BAR(V_EMPTY + s));
         }
-        umma_commit(BAR(O_FULL));
-        umma_commit(BAR(V_EMPTY + s));
+        if (ok && nb <= 0) umma_commit(BAR(Q_EMPTY + qs));
       }
     }
   } else if (!decode || (warp & 3) == 0) {
@@ -278,145 +321,159 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // lets the warp touch, split = (warp - 2) / 4 selects which 32 of the 128 S columns (keys) and
     // which 32 of the 128 O columns (head dims) the thread owns.  The four threads of a row
     // exchange their partial maxima through shared memory; everything else is private.
-    // (decode tiles have at most 8 rows: only the quad-0 warps take part)
+    // (decode tiles have at most 32 rows: only the quad-0 warps take part)
     const int quad = warp & 3;
     const int split = (warp - 2) >> 2;
     const int r = quad * 32 + lane;  // this thread's query row within the tile
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    int kv_len = t.pos0 + r * t.pos_step + 1;
-    if (kv_len > t.kv_cap) kv_len = t.kv_cap;
-    if (r >= t.n_rows) kv_len = 0;
+    uint8_t* p_row = smem + off_p;
+    float* xch = reinterpret_cast<float*>(smem + AttnFwdSmem<DEC>::kXch);  // [2][128][4] maxima, then [2][128][4] sums
+    uint32_t bc = 0;     // blocks done so far (S buffer, P / O phases, maxima slot)
+    uint32_t xc = 0;     // exchange rounds done so far (one per block, one per tile)
+    bool alive = true;
     // context parallel with staging: the compute warps first help copy the remote K/V blocks
-    // (the CTAs that start first do all of it; later ones find the work counter exhausted)
+    // (the CTAs that start first do all of it; later ones find the work counter exhausted);
+    // a CTA whose tile is empty helps too -- its threads do nothing else
     if (use_stage && !decode) cp_stage_gather(p.stage, threadIdx.x - 64, kAttnThreads - 64, 3, stage_slot);
-    float m_run = -INFINITY, l_part = 0.f;
-    float o[32];
+
+    for (int idx = blockIdx.x; alive && idx < p.n_tiles; idx += tile_step) {
+      const TileInfo ti = read_tile(idx);
+      const AttnTile& t = ti.t;
+      if (t.n_rows <= 0) continue;
+      const int nb = ti.nblk - ti.b0;
+      int kv_len = t.pos0 + r * t.pos_step + 1;
+      if (kv_len > t.kv_cap) kv_len = t.kv_cap;
+      if (r >= t.n_rows) kv_len = 0;
+      float m_run = -INFINITY, l_part = 0.f;
+      float o[32];
 #pragma unroll
-    for (int i = 0; i < 32; ++i) o[i] = 0.f;
-    float* st_ptr = nullptr;     // this row's saved state (resumable rows)
-    if (st_mode != 0 && r < t.n_rows) {
-      const int rps = p.q_rows_per_seq > 0 ? p.q_rows_per_seq : 1;
-      st_ptr = p.state + static_cast<long long>(st_row + (r / rps) * p.q_seq_rows + r % rps) * kAttnStateFloats;
-      if (st_mode == 2) {
-        m_run = st_ptr[0];
-        l_part = st_ptr[4 + split];
+      for (int i = 0; i < 32; ++i) o[i] = 0.f;
+      float* st_ptr = nullptr;     // this row's saved state (resumable rows)
+      if (ti.st_mode != 0 && r < t.n_rows) {
+        const int rps = p.q_rows_per_seq > 0 ? p.q_rows_per_seq : 1;
+        st_ptr = p.state + static_cast<long long>(ti.st_row + (r / rps) * p.q_seq_rows + r % rps) * kAttnStateFloats;
+        if (ti.st_mode == 2) {
+          m_run = st_ptr[0];
+          l_part = st_ptr[4 + split];
 #pragma unroll
-        for (int j = 0; j < 32; j += 4) {
-          const float4 v = *reinterpret_cast<const float4*>(st_ptr + 8 + split * 32 + j);
-          o[j] = v.x; o[j + 1] = v.y; o[j + 2] = v.z; o[j + 3] = v.w;
+          for (int j = 0; j < 32; j += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(st_ptr + 8 + split * 32 + j);
+            o[j] = v.x; o[j + 1] = v.y; o[j + 2] = v.z; o[j + 3] = v.w;
+          }
         }
       }
-    }
-    const int nb = nblk - b0;
-    uint8_t* p_row = smem + off_p;
-    float* xch = reinterpret_cast<float*>(smem + AttnFwdSmem::kXch);  // [2][128][4] maxima, then [128][4] sums
-    bool alive = true;
-    float alpha_prev = 0.f;
+      float alpha_prev = 0.f;
 
-    for (int b = 0; b < nb; ++b) {              // b counts from the tile's first block b0
-      const int s = b & 1;
-      const uint32_t ph = (b >> 1) & 1;
-      if (!mbar_wait(BAR(S_FULL + s), ph, abort_flag, p.status, 208)) { alive = false; break; }
-      tc_fence_after();
-      const int nvis = kv_len - (b0 + b) * kAttnBlock - split * 32;  // visible keys among this thread's 32
-      uint32_t x[32];
-      tmem_ld32(tmem_base + lane_off + TM_S + s * 128 + split * 32, x);
-      tmem_ld_wait();
-      float m_part = -INFINITY;
+      for (int b = 0; b < nb; ++b, ++bc, ++xc) {    // b counts from the tile's first block b0
+        const int s = bc & 1;
+        const uint32_t ph = (bc >> 1) & 1;
+        if (!mbar_wait(BAR(S_FULL + s), ph, abort_flag, p.status, 208)) { alive = false; break; }
+        tc_fence_after();
+        const int nvis = kv_len - (ti.b0 + b) * kAttnBlock - split * 32;  // visible keys among this thread's 32
+        uint32_t x[32];
+        tmem_ld32(tmem_base + lane_off + TM_S + s * 128 + split * 32, x);
+        tmem_ld_wait();
+        float m_part = -INFINITY;
 #pragma unroll
-      for (int j = 0; j < 32; ++j)
-        if (j < nvis) m_part = fmaxf(m_part, __uint_as_float(x[j]));
-      xch[(b & 1) * 512 + r * 4 + split] = m_part;
+        for (int j = 0; j < 32; ++j)
+          if (j < nvis) m_part = fmaxf(m_part, __uint_as_float(x[j]));
+        xch[(xc & 1) * 512 + r * 4 + split] = m_part;
+        mbar_arrive(BAR(XCH + quad));
+        if (!mbar_wait(BAR(XCH + quad), xc & 1, abort_flag, p.status, 210)) { alive = false; break; }
+        const float4 mm = *reinterpret_cast<const float4*>(xch + (xc & 1) * 512 + r * 4);
+        const float m_blk = fmaxf(fmaxf(mm.x, mm.y), fmaxf(mm.z, mm.w));
+        const float m_new = fmaxf(m_run, m_blk);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = fast_exp2((m_run - m_use) * p.scale_log2);  // m_run = -inf -> 0
+        const float neg_ms = -m_use * p.scale_log2;
+        float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          const float e0 = (j + 0 < nvis) ? fast_exp2(fmaf(__uint_as_float(x[j + 0]), p.scale_log2, neg_ms)) : 0.f;
+          const float e1 = (j + 1 < nvis) ? fast_exp2(fmaf(__uint_as_float(x[j + 1]), p.scale_log2, neg_ms)) : 0.f;
+          const float e2 = (j + 2 < nvis) ? fast_exp2(fmaf(__uint_as_float(x[j + 2]), p.scale_log2, neg_ms)) : 0.f;
+          const float e3 = (j + 3 < nvis) ? fast_exp2(fmaf(__uint_as_float(x[j + 3]), p.scale_log2, neg_ms)) : 0.f;
+          sum0 += e0; sum1 += e1; sum2 += e2; sum3 += e3;
+          pk[j / 2] = pack_bf16x2(e0, e1);
+          pk[j / 2 + 1] = pack_bf16x2(e2, e3);
+        }
+        // The previous block's P*V product is collected only now, after this block's exponentials
+        // are already in registers: the MMA of block b-1 runs while block b's scores are reduced.
+        // (It must be collected before P is overwritten and before the next P*V reuses the O columns.)
+        if (b > 0) {
+          if (!mbar_wait(BAR(O_FULL), (bc - 1) & 1, abort_flag, p.status, 209)) { alive = false; break; }
+          tc_fence_after();
+          uint32_t xo[32];
+          tmem_ld32(tmem_base + lane_off + TM_O + split * 32, xo);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], alpha_prev, __uint_as_float(xo[j]));
+        }
+        // this thread's 32 keys = 4 chunks of 16 bytes; keys [64h, 64h+64) live in half h of the P tile
+        if (r < p.q_rows_box) {
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4)
+            *reinterpret_cast<uint4*>(p_row + (split >> 1) * q_half + sw128_offset(r, (split & 1) * 4 + q4)) =
+                make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
+        }
+        fence_proxy_async_smem();  // make the generic-proxy P writes visible to the UMMA
+        tc_fence_before();
+        mbar_arrive(BAR(S_EMPTY + s));
+        mbar_arrive(BAR(P_FULL));
+        l_part = l_part * alpha + ((sum0 + sum1) + (sum2 + sum3));
+        m_run = m_new;
+        alpha_prev = alpha;
+      }
+      if (!alive) break;
+      if (nb > 0) {
+        if (mbar_wait(BAR(O_FULL), (bc - 1) & 1, abort_flag, p.status, 209)) {
+          tc_fence_after();
+          uint32_t xo[32];
+          tmem_ld32(tmem_base + lane_off + TM_O + split * 32, xo);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], alpha_prev, __uint_as_float(xo[j]));
+        } else {
+          alive = false;
+          break;
+        }
+      }
+      // ---------------------------------------------------------------- epilogue
+      // row sum = (l0 + l1) + (l2 + l3) over the four column slices
+      float* lx = xch + 1024 + (xc & 1) * 512;   // two slots: a row's threads may be one round apart
+      lx[r * 4 + split] = l_part;
       mbar_arrive(BAR(XCH + quad));
-      if (!mbar_wait(BAR(XCH + quad), b & 1, abort_flag, p.status, 210)) { alive = false; break; }
-      const float4 mm = *reinterpret_cast<const float4*>(xch + (b & 1) * 512 + r * 4);
-      const float m_blk = fmaxf(fmaxf(mm.x, mm.y), fmaxf(mm.z, mm.w));
-      const float m_new = fmaxf(m_run, m_blk);
-      const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-      const float alpha = fast_exp2((m_run - m_use) * p.scale_log2);  // m_run = -inf -> 0
-      const float neg_ms = -m_use * p.scale_log2;
-      float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-      uint32_t pk[16];
+      const bool synced = mbar_wait(BAR(XCH + quad), xc & 1, abort_flag, p.status, 211);
+      ++xc;
+      if (!synced) { alive = false; break; }
+      if (ti.st_mode == 1) {
+        // resumable rows: hand the running state on instead of normalising
+        if (st_ptr != nullptr) {
+          if (split == 0) st_ptr[0] = m_run;
+          st_ptr[4 + split] = l_part;
 #pragma unroll
-      for (int j = 0; j < 32; j += 4) {
-        const float e0 = (j + 0 < nvis) ? fast_exp2(fmaf(__uint_as_float(x[j + 0]), p.scale_log2, neg_ms)) : 0.f;
-        const float e1 = (j + 1 < nvis) ? fast_exp2(fmaf(__uint_as_float(x[j + 1]), p.scale_log2, neg_ms)) : 0.f;
-        const float e2 = (j + 2 < nvis) ? fast_exp2(fmaf(__uint_as_float(x[j + 2]), p.scale_log2, neg_ms)) : 0.f;
-        const float e3 = (j + 3 < nvis) ? fast_exp2(fmaf(__uint_as_float(x[j + 3]), p.scale_log2, neg_ms)) : 0.f;
-        sum0 += e0; sum1 += e1; sum2 += e2; sum3 += e3;
-        pk[j / 2] = pack_bf16x2(e0, e1);
-        pk[j / 2 + 1] = pack_bf16x2(e2, e3);
-      }
-      // The previous block's P*V product is collected only now, after this block's exponentials
-      // are already in registers: the MMA of block b-1 runs while block b's scores are reduced.
-      // (It must be collected before P is overwritten and before the next P*V reuses the O columns.)
-      if (b > 0) {
-        if (!mbar_wait(BAR(O_FULL), (b - 1) & 1, abort_flag, p.status, 209)) { alive = false; break; }
-        tc_fence_after();
-        uint32_t xo[32];
-        tmem_ld32(tmem_base + lane_off + TM_O + split * 32, xo);
-        tmem_ld_wait();
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(st_ptr + 8 + split * 32 + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+        }
+      } else if (r < t.n_rows) {
+        const float4 ll = *reinterpret_cast<const float4*>(lx + r * 4);
+        const float l_run = (ll.x + ll.y) + (ll.z + ll.w);
+        const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+        __nv_bfloat16* dst = p.O + static_cast<long long>(t.q_row0 + r) * p.ldo + t.q_col0 + split * 32;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], alpha_prev, __uint_as_float(xo[j]));
-      }
-      // this thread's 32 keys = 4 chunks of 16 bytes; keys [64h, 64h+64) live in half h of the P tile
-      if (r < p.q_rows_box) {
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
-          *reinterpret_cast<uint4*>(p_row + (split >> 1) * q_half + sw128_offset(r, (split & 1) * 4 + q4)) =
-              make_uint4(pk[4 * q4], pk[4 * q4 + 1], pk[4 * q4 + 2], pk[4 * q4 + 3]);
-      }
-      fence_proxy_async_smem();  // make the generic-proxy P writes visible to the UMMA
-      tc_fence_before();
-      mbar_arrive(BAR(S_EMPTY + s));
-      mbar_arrive(BAR(P_FULL));
-      l_part = l_part * alpha + ((sum0 + sum1) + (sum2 + sum3));
-      m_run = m_new;
-      alpha_prev = alpha;
-    }
-    if (alive && nb > 0) {
-      if (mbar_wait(BAR(O_FULL), (nb - 1) & 1, abort_flag, p.status, 209)) {
-        tc_fence_after();
-        uint32_t xo[32];
-        tmem_ld32(tmem_base + lane_off + TM_O + split * 32, xo);
-        tmem_ld_wait();
-#pragma unroll
-        for (int j = 0; j < 32; ++j) o[j] = fmaf(o[j], alpha_prev, __uint_as_float(xo[j]));
-      } else {
-        alive = false;
-      }
-    }
-    // ---------------------------------------------------------------- epilogue
-    // row sum = (l0 + l1) + (l2 + l3) over the four column slices
-    float* lx = xch + 1024;
-    lx[r * 4 + split] = l_part;
-    mbar_arrive(BAR(XCH + quad));
-    if (st_mode == 1) {
-      // resumable rows: hand the running state on instead of normalising
-      if (alive && st_ptr != nullptr) {
-        if (split == 0) st_ptr[0] = m_run;
-        st_ptr[4 + split] = l_part;
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-          *reinterpret_cast<float4*>(st_ptr + 8 + split * 32 + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
-      }
-    } else if (alive && mbar_wait(BAR(XCH + quad), nb & 1, abort_flag, p.status, 211) && r < t.n_rows) {
-      const float4 ll = *reinterpret_cast<const float4*>(lx + r * 4);
-      const float l_run = (ll.x + ll.y) + (ll.z + ll.w);
-      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-      __nv_bfloat16* dst = p.O + static_cast<long long>(t.q_row0 + r) * p.ldo + t.q_col0 + split * 32;
-#pragma unroll
-      for (int j = 0; j < 32; j += 8) {
-        uint4 v;
-        v.x = pack_bf16x2(o[j] * inv_l, o[j + 1] * inv_l);
-        v.y = pack_bf16x2(o[j + 2] * inv_l, o[j + 3] * inv_l);
-        v.z = pack_bf16x2(o[j + 4] * inv_l, o[j + 5] * inv_l);
-        v.w = pack_bf16x2(o[j + 6] * inv_l, o[j + 7] * inv_l);
-        *reinterpret_cast<uint4*>(dst + j) = v;
-      }
-      if (p.lse && split == 0) {
-        const float lse = (l_run > 0.f) ? fmaf(m_run, p.scale, logf(l_run)) : -INFINITY;
-        p.lse[t.lse_off + static_cast<long long>(r) * t.lse_stride] = lse;
+        for (int j = 0; j < 32; j += 8) {
+          uint4 v;
+          v.x = pack_bf16x2(o[j] * inv_l, o[j + 1] * inv_l);
+          v.y = pack_bf16x2(o[j + 2] * inv_l, o[j + 3] * inv_l);
+          v.z = pack_bf16x2(o[j + 4] * inv_l, o[j + 5] * inv_l);
+          v.w = pack_bf16x2(o[j + 6] * inv_l, o[j + 7] * inv_l);
+          *reinterpret_cast<uint4*>(dst + j) = v;
+        }
+        if (p.lse && split == 0) {
+          const float lse = (l_run > 0.f) ? fmaf(m_run, p.scale, logf(l_run)) : -INFINITY;
+          p.lse[t.lse_off + static_cast<long long>(r) * t.lse_stride] = lse;
+        }
       }
     }
   }
@@ -429,19 +486,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   }
 }
 
-template <int NSRC>
+template <int NSRC, bool DEC>
 static int launch_attn_fwd(const CUtensorMap& tmQ, const KvMaps<NSRC>& kv, const KvMaps<1>& staged,
                            const AttnFwdParams& p, cudaStream_t stream) {
-  auto kfn = attn_fwd_kernel<NSRC>;
+  auto kfn = attn_fwd_kernel<NSRC, DEC>;
   static bool attr_set[64] = {false};
   int dev = 0;
   RLK_CHECK_CUDA(cudaGetDevice(&dev));
   if (!attr_set[dev & 63]) {
     RLK_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        AttnFwdSmem::kBytes));
+                                        AttnFwdSmem<DEC>::kBytes));
     attr_set[dev & 63] = true;
   }
-  RLK_CHECK_CUDA(launch_pdl(kfn, dim3(p.n_tiles), dim3(kAttnThreads), AttnFwdSmem::kBytes, stream, tmQ, kv, staged, p));
+  // decode tiles are short and alike: one persistent CTA per SM walks them, so that a tile's loads
+  // overlap the previous tile's tail; full tiles keep one CTA each (the hardware hands them out as
+  // CTAs finish, which balances causal tiles of different lengths)
+  const int grid = (DEC && p.n_tiles > sm_count()) ? sm_count() : p.n_tiles;
+  RLK_CHECK_CUDA(launch_pdl(kfn, dim3(grid), dim3(kAttnThreads), AttnFwdSmem<DEC>::kBytes, stream, tmQ, kv, staged, p));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
@@ -491,8 +552,8 @@ RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long
   p.state = state;
   p.q_rows_per_seq = q_rows_per_seq;
   p.q_seq_rows = q_seq_rows;
-  RLK_REQUIRE(tile_ext == nullptr || (state != nullptr && n_src == 1 && q_seq_rows > 0),
-              "attn_fwd: resumable rows need a state buffer, one KV source and the row geometry");
+  RLK_REQUIRE(tile_ext == nullptr || (decode_rows && state != nullptr && n_src == 1 && q_seq_rows > 0),
+              "attn_fwd: resumable rows are decode tiles with a state buffer, one KV source and the row geometry");
   CUtensorMap tmQ;
   int rc;
   if (q_group > 0) {
@@ -513,7 +574,7 @@ RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long
     KvMaps<1> kv;
     if ((rc = make_tmap_2d_sw128(&kv.k[0], k_ptrs[0], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
     if ((rc = make_tmap_2d_sw128(&kv.v[0], v_ptrs[0], kv_rows, kv_cols, ldkv, 128, 64, 2))) return rc;
-    return launch_attn_fwd<1>(tmQ, kv, kv, p, s);
+    return decode_rows ? launch_attn_fwd<1, true>(tmQ, kv, kv, p, s) : launch_attn_fwd<1, false>(tmQ, kv, kv, p, s);
   }
   KvMaps<8> kv;
   for (int i = 0; i < 8; ++i) {
@@ -547,5 +608,5 @@ RLK_API int rlk_attn_fwd(const void* Q, long long q_rows, long long q_cols, long
     if ((rc = make_tmap_2d_sw128(&staged.v[0], stage_v, total, kv_cols, kv_cols, 128, 64, 2))) return rc;
     RLK_CHECK_CUDA(cudaMemsetAsync(stage_flags, 0, sizeof(int) * (n_src * (stage_rows / 128) * 2 + 1), s));
   }
-  return launch_attn_fwd<8>(tmQ, kv, staged, p, s);
+  return decode_rows ? launch_attn_fwd<8, true>(tmQ, kv, staged, p, s) : launch_attn_fwd<8, false>(tmQ, kv, staged, p, s);
 }
