@@ -296,32 +296,36 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         if (!mbar_wait(accf0 + 8 * a, (u >> 1) & 1, abort_flag, p.status, 104)) break;
         tc_fence_after();
         const bool last = (c == p.nchunks - 1);
-        if (BN == 128 && p.stats != nullptr) {
-          if (half == 0) {
+        if ((BN == 128 || BN == 256) && p.stats != nullptr) {
+          // 128-wide tiles: the first set of epilogue warps walks the tile's one vocabulary tile;
+          // 256-wide tiles: each set walks its own 128 columns = its own vocabulary tile
+          constexpr int kVT = BN / 128;                       // vocabulary tiles per GEMM tile
+          const int cbase = (BN == 256) ? half * 128 : 0;     // first column of this thread's vocabulary tile
+          if ((BN == 256 || half == 0) && n0 + cbase < p.N) {
           // fused selected-logp statistics: logit = bf16(acc); z = logit * inv_temp
           // (one thread walks all 128 columns of its row: the statistics have a fixed order)
-          const long long tgt_col = (p.targets && row < p.M) ? p.targets[row] - p.vocab_start - n0 : -1;
+          const long long tgt_col = (p.targets && row < p.M) ? p.targets[row] - p.vocab_start - n0 - cbase : -1;
           float m = -INFINITY;
 #pragma unroll 1
-          for (int col0 = 0; col0 < BN; col0 += 32) {
+          for (int col0 = 0; col0 < 128; col0 += 32) {
             uint32_t r[32];
-            tmem_ld32(tmem_base + lane_off + a * kAcc + col0, r);
+            tmem_ld32(tmem_base + lane_off + a * kAcc + cbase + col0, r);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (n0 + col0 + j < p.N)
+              if (n0 + cbase + col0 + j < p.N)
                 m = fmaxf(m, logp_scale(round_bf16(__uint_as_float(r[j])), p.inv_temp));
           }
           TileSum ts;
 #pragma unroll 1
-          for (int col0 = 0; col0 < BN; col0 += 32) {
+          for (int col0 = 0; col0 < 128; col0 += 32) {
             uint32_t r[32];
-            tmem_ld32(tmem_base + lane_off + a * kAcc + col0, r);
+            tmem_ld32(tmem_base + lane_off + a * kAcc + cbase + col0, r);
             tmem_ld_wait();
             float z[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              z[j] = (n0 + col0 + j < p.N) ? logp_scale(round_bf16(__uint_as_float(r[j])), p.inv_temp) : -INFINITY;
+              z[j] = (n0 + cbase + col0 + j < p.N) ? logp_scale(round_bf16(__uint_as_float(r[j])), p.inv_temp) : -INFINITY;
             if (m > -INFINITY) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) ts.add4(z[j], z[j + 1], z[j + 2], z[j + 3], m);
@@ -330,17 +334,17 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               float zt = 0.f;
 #pragma unroll
               for (int j = 0; j < 32; ++j) if (tgt_col - col0 == j) zt = z[j];
-              if (n0 + tgt_col < p.N) {
+              if (n0 + cbase + tgt_col < p.N) {
                 p.tgt_logit[row] = zt;
                 for (int pr = 0; pr < p.stats_world; ++pr)
                   if (pr != p.stats_rank) p.tgt_peer[pr][row] = zt;
               }
             }
             if (p.C != nullptr && row < p.M) {
-              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + n0 + col0;
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + n0 + cbase + col0;
 #pragma unroll
               for (int j = 0; j < 32; j += 8) {
-                if (n0 + col0 + j < p.N) {
+                if (n0 + cbase + col0 + j < p.N) {
                   uint4 v;
                   v.x = pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1]));
                   v.y = pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
@@ -353,7 +357,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
           if (row < p.M) {
             const float2 st2 = make_float2(m, ts.total());
-            const long long si = row * p.stats_stride + p.stats_tile0 + nt;
+            const long long si = row * p.stats_stride + p.stats_tile0 + nt * kVT + (BN == 256 ? half : 0);
             p.stats[si] = st2;
             for (int pr = 0; pr < p.stats_world; ++pr)
               if (pr != p.stats_rank) p.stats_peer[pr][si] = st2;
@@ -967,6 +971,11 @@ static int lmhead_stats_impl(const void* H, const void* W, int M, int N, int K, 
     p.stats_peer[i] = world > 1 ? static_cast<float2*>(stats_ptrs[i < world ? i : 0]) : nullptr;
     p.tgt_peer[i] = world > 1 ? static_cast<float*>(tgt_ptrs[i < world ? i : 0]) : nullptr;
   }
+  // enough 256-wide tiles for every SM: full tensor-core rate, each set of epilogue warps reduces
+  // its own vocabulary tile; otherwise 128-wide tiles (more of them)
+  const long long tiles256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
+  if (tiles256 >= 2 * sm_count())
+    return launch_gemm<256, false, false>(H, W, p, ldh, ldw, static_cast<cudaStream_t>(stream));
   return launch_gemm<128, false, false>(H, W, p, ldh, ldw, static_cast<cudaStream_t>(stream));
 }
 
