@@ -50,6 +50,8 @@ struct GemmParams {
   int a_box_rows;           // rows of A that TMA brings per tile (128, or fewer when M < 128)
   int stage_a_bytes;        // shared-memory bytes reserved for the A tile of one stage
   int stages;               // depth of the shared-memory ring
+  int tree_l0_smem;         // tile_n 256 with chunks: level 0 of the tree stack lives in shared memory
+                            //   behind the barriers (kTreeL0Pitch bytes per tile row)
   int b_static;             // 1: B was complete before the previous kernel of the stream started (a
                             //    weight): its first tiles are fetched before the dependency wait
   int split_chunks;         // > 1: every canonical chunk is its own tile and writes its bf16 leaf
@@ -97,6 +99,7 @@ __device__ __forceinline__ uint4 ar_tree_node(const uint4 a, const uint4 b) {
 }
 
 constexpr int kMaxStages = 16;
+constexpr int kTreeL0Pitch = 528;   // 512 bytes of packed bf16 per row + 16: 16-byte accesses of a warp spread over all banks
 
 template <int BN>
 struct GemmSmem {
@@ -364,15 +367,19 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           }
           }
         } else if (BN == 256 && p.nchunks > 1) {
-          // chunk tree with 128x256 tiles: both accumulators fill TMEM, so the tree stack lives in a
-          // per-CTA global buffer (L2 resident; a row's entries of a slice are only ever touched by
-          // the one thread that owns that row and slice).  Keeping level 0 in registers instead was
-          // tried: 64 more live registers spill under the 168-register cap and nothing is gained.
+          // chunk tree with 128x256 tiles: both accumulators fill TMEM, so the tree stack cannot live
+          // there.  Level 0 (four of the seven pushes and pops of a tile) sits in shared memory, in
+          // the space a fourth pipeline stage would take; levels 1 and 2 in a per-CTA global buffer
+          // (L2 resident).  A row's entries of a slice are only ever touched by the one thread that
+          // owns that row and slice.  (Level 0 in registers was tried: 64 more live registers spill
+          // under the 168-register cap.)
           int nmerge = 0;
           while ((c >> nmerge) & 1) ++nmerge;                       // levels to fold into this chunk
           uint4* sbase = p.tree_scratch + (static_cast<size_t>(blockIdx.x) * 3 * BM + row_in_tile) * 32;
           constexpr size_t kLevel = static_cast<size_t>(BM) * 32;   // uint4 per level
           const int sl0 = half * 4;   // this warp's four 32-column slices
+          uint4* l0row = reinterpret_cast<uint4*>(smem + kStages * stage_bytes + S::kBarBytes +
+                                                  row_in_tile * kTreeL0Pitch);
 #pragma unroll
           for (int si = 0; si < 4; ++si) {
             const int sl = sl0 + si;
@@ -382,7 +389,8 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int lv = 0; lv < 3; ++lv)
               if (lv < nmerge)
 #pragma unroll
-                for (int q = 0; q < 4; ++q) cur[lv][q] = sbase[lv * kLevel + sl * 4 + q];
+                for (int q = 0; q < 4; ++q)
+                  cur[lv][q] = (lv == 0 && p.tree_l0_smem) ? l0row[sl * 4 + q] : sbase[lv * kLevel + sl * 4 + q];
             uint32_t r[32];
             tmem_ld32(tmem_base + lane_off + a * kAcc + sl * 32, r);
             tmem_ld_wait();
@@ -404,9 +412,10 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             }
             const int col0 = sl * 32;
             if (!last) {
+              uint4* dst4 = (nmerge == 0 && p.tree_l0_smem) ? l0row + sl * 4 : sbase + nmerge * kLevel + sl * 4;
 #pragma unroll
               for (int q = 0; q < 4; ++q)
-                sbase[nmerge * kLevel + sl * 4 + q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+                dst4[q] = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
             } else if (row < p.M) {
               if (p.out_fp32) {
                 float* dst = reinterpret_cast<float*>(p.C) + c_off + static_cast<long long>(row) * p.ldc + n0 + col0;
@@ -654,7 +663,14 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
     const int fit = (GemmSmem<BN>::kBytes - 1024 - GemmSmem<BN>::kBarBytes - slack) / stage_bytes;
     if (p.stages > fit) p.stages = fit;
   }
-  const int smem_bytes = p.stages * stage_bytes + 1024 + GemmSmem<BN>::kBarBytes + slack;
+  int smem_bytes = p.stages * stage_bytes + 1024 + GemmSmem<BN>::kBarBytes + slack;
+  p.tree_l0_smem = 0;
+  if (BN == 256 && p.nchunks > 1 && p.tree_scratch != nullptr) {
+    // three stages instead of four; the freed space holds level 0 of the tree stack
+    p.stages = 3;
+    p.tree_l0_smem = 1;
+    smem_bytes = p.stages * stage_bytes + 1024 + GemmSmem<BN>::kBarBytes + slack + BM * kTreeL0Pitch;
+  }
   if (!A_MN) rc = make_tmap_2d_sw128(&tmA, A, p.M, p.K, lda, p.a_box_rows, 64, 2);
   else rc = make_tmap_2d_sw128(&tmA, A, p.K, p.M, lda, BK, 64, 2);
   if (rc) return rc;
@@ -757,8 +773,9 @@ RLK_API int rlk_det_gemm(const void* A, const void* B, void* C, int M, int N, in
     // many tiles: 128x256 tiles (full tensor-core rate) with the tree stack in an L2-resident
     // scratch; few tiles: 128x128 tiles with the stack in TMEM
     const long long tiles256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
-    // (the scratch-stack epilogue only keeps up with the MMA when a chunk has >= 1536 k)
-    bn = (tile_n == 256 || (tile_n == 0 && tiles256 >= sm_count() && K / nchunks >= 1536)) ? 256 : 128;
+    // (measured, 12288 x 4096 outputs, 8 chunks: chunks of 512 k run at 891 TFLOP/s on 128-wide
+    // tiles against 868 on 256-wide ones; chunks of 768 k at 867 against 997)
+    bn = (tile_n == 256 || (tile_n == 0 && tiles256 >= sm_count() && K / nchunks >= 768)) ? 256 : 128;
     if (a_mn) bn = 128;
     if (bn == 256) {
       p.tree_scratch = tree_scratch_for_device();
