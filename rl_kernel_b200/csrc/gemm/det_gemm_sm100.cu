@@ -265,8 +265,9 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + a * kAcc;
           for (int kb = 0; kb < p.kb_per_chunk; ++kb) {
+            // (no tcgen05 fence here: the operands come from TMA, whose completion the barrier
+            // itself orders; the fence after the accumulator wait above covers the epilogue's loads)
             if (!mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 103)) break;
-            tc_fence_after();
             umma_bf16_ss(d_tmem, desc64(da_lo, da_hi), desc64(db_lo, db_hi), idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
             for (uint32_t k = 1; k < BK / UMMA_K; ++k)

@@ -164,3 +164,4 @@ RLK_API int rlk_status_poll(void* stream, int* out_code) {
 }
 
 RLK_API int rlk_abi_version() { return 1; }
+
