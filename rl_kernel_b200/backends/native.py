@@ -32,6 +32,19 @@ def set_pdl(on: bool) -> bool:
     return bool(_lib().rlk_set_pdl(c_int(int(on))))
 
 
+def det_gemm_swiglu(x: torch.Tensor, wgu: torch.Tensor, act: torch.Tensor, blk: int) -> None:
+    """act[M, I] = SwiGLU(x @ wgu^T) for the packed gate/up weight (blocks of ``blk`` rows); the
+    gate/up tensor is not materialised.  Same bits as det_gemm + swiglu_fwd."""
+    _bf16(x, "x"); _bf16(wgu, "wgu"); _rowmajor2d(act, "act")
+    M, K = x.shape
+    I = wgu.shape[0] // 2
+    rc = _lib().rlk_det_gemm_swiglu(ext.ptr(x), ext.ptr(wgu), ext.ptr(act), c_int(M), c_int(I), c_int(K),
+                                    _ll(x.stride(0)), _ll(wgu.stride(0)), _ll(act.stride(0)), c_int(blk),
+                                    ext.stream_ptr(x.device))
+    ext.check(rc, "det_gemm_swiglu")
+    _count()
+
+
 class static_weights:
     """Context: the B operands (weights) of the GEMMs launched inside were complete before the
     kernel preceding each GEMM was launched, so the kernels may start streaming them while that

@@ -50,6 +50,11 @@ struct GemmParams {
   int a_box_rows;           // rows of A that TMA brings per tile (128, or fewer when M < 128)
   int stage_a_bytes;        // shared-memory bytes reserved for the A tile of one stage
   int stages;               // depth of the shared-memory ring
+  // Fused gate/up + SwiGLU (192-wide tiles only, act_blk > 0): B holds gate and up rows interleaved
+  // in blocks of act_blk rows ([g_0 | u_0 | g_1 | u_1 ...]); a tile multiplies by 96 gate rows and
+  // the 96 matching up rows, and the epilogue writes silu(bf16(gate)) * bf16(up) -- the bits of
+  // the separate SwiGLU kernel on the bf16 gate/up tensor -- to C [M, act_I].
+  int act_blk, act_I;
   int tree_l0_smem;         // tile_n 256 with chunks: level 0 of the tree stack lives in shared memory
                             //   behind the barriers (kTreeL0Pitch bytes per tile row)
   int b_static;             // 1: B was complete before the previous kernel of the stream started (a
@@ -120,6 +125,12 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
   const int r = t - g * per_group;
   mt = first_m + (r % gsize);
   nt = r / gsize;
+}
+
+// Fused gate/up + SwiGLU tiles: first gate row of tile nt (its up rows start act_blk rows later).
+__device__ __forceinline__ int act_gate_row(int nt, int act_blk) {
+  const int c0 = nt * 96;
+  return (c0 / act_blk) * 2 * act_blk + c0 % act_blk;
 }
 
 template <int BN, bool A_MN, bool B_MN>
@@ -196,7 +207,11 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           mbar_expect_tx(fb, stage_tx);
           const uint32_t sb = smem_base + kb * stage_bytes + p.stage_a_bytes;
           const int k0 = (kb0 + static_cast<int>(kb)) * BK;
-          if (!B_MN) {
+          if (BN == 192 && p.act_blk > 0) {
+            const int gr = act_gate_row(nt, p.act_blk);
+            tma_load_2d(sb, &tmB, k0, gr, fb);
+            tma_load_2d(sb + 96 * 128, &tmB, k0, gr + p.act_blk, fb);
+          } else if (!B_MN) {
             tma_load_2d(sb, &tmB, k0, nt * BN, fb);
           } else {
 #pragma unroll
@@ -231,7 +246,11 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, &tmA, m0 + 64 * i, k0, fb);
           }
           if (!fresh) continue;
-          if (!B_MN) {
+          if (BN == 192 && p.act_blk > 0) {
+            const int gr = act_gate_row(nt, p.act_blk);
+            tma_load_2d(sb, &tmB, k0, gr, fb);
+            tma_load_2d(sb + 96 * 128, &tmB, k0, gr + p.act_blk, fb);
+          } else if (!B_MN) {
             tma_load_2d(sb, &tmB, k0, n0, fb);
           } else {
 #pragma unroll
@@ -366,6 +385,31 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             for (int pr = 0; pr < p.stats_world; ++pr)
               if (pr != p.stats_rank) p.stats_peer[pr][si] = st2;
           }
+          }
+        } else if (BN == 192 && p.act_blk > 0) {
+          // fused SwiGLU: accumulator columns [0, 96) are gate, [96, 192) the matching up columns;
+          // each set of epilogue warps takes 48 of the 96 output columns
+          // (the tensor-memory loads are warp-wide instructions: every lane runs them, rows past M
+          // only skip the stores)
+          const int c0 = nt * 96 + half * 48;                     // first activation column of this thread
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(row) * p.ldc + c0;
+#pragma unroll 1
+          for (int pc = 0; pc < 3; ++pc) {
+            uint32_t g[16], u2[16];
+            tmem_ld16(tmem_base + lane_off + a * kAcc + half * 48 + pc * 16, g);
+            tmem_ld16(tmem_base + lane_off + a * kAcc + 96 + half * 48 + pc * 16, u2);
+            tmem_ld_wait();
+            uint32_t o[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float g0 = round_bf16(__uint_as_float(g[2 * j])), g1 = round_bf16(__uint_as_float(g[2 * j + 1]));
+              const float u0 = round_bf16(__uint_as_float(u2[2 * j])), u1 = round_bf16(__uint_as_float(u2[2 * j + 1]));
+              o[j] = pack_bf16x2((g0 / (1.f + __expf(-g0))) * u0, (g1 / (1.f + __expf(-g1))) * u1);
+            }
+            if (row < p.M) {
+              *reinterpret_cast<uint4*>(dst + pc * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+              *reinterpret_cast<uint4*>(dst + pc * 16 + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+            }
           }
         } else if (BN == 256 && p.nchunks > 1) {
           // chunk tree with 128x256 tiles: both accumulators fill TMEM, so the tree stack cannot live
@@ -675,11 +719,13 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   if (!A_MN) rc = make_tmap_2d_sw128(&tmA, A, p.M, p.K, lda, p.a_box_rows, 64, 2);
   else rc = make_tmap_2d_sw128(&tmA, A, p.K, p.M, lda, BK, 64, 2);
   if (rc) return rc;
-  if (!B_MN) rc = make_tmap_2d_sw128(&tmB, B, p.N, p.K, ldb, BN, 64, 2);
+  if (BN == 192 && p.act_blk > 0) rc = make_tmap_2d_sw128(&tmB, B, p.N, p.K, ldb, 96, 64, 2);
+  else if (!B_MN) rc = make_tmap_2d_sw128(&tmB, B, p.N, p.K, ldb, BN, 64, 2);
   else rc = make_tmap_2d_sw128(&tmB, B, p.K, p.N, ldb, BK, 64, 2);
   if (rc) return rc;
   p.m_tiles = (p.M + BM - 1) / BM;
   p.n_tiles = (p.N + BN - 1) / BN;
+  if (BN == 192 && p.act_blk > 0) p.n_tiles = p.act_I / 96;
   const int tiles = p.m_tiles * p.n_tiles * p.split_chunks;
   int ctas_per_sm = (GemmSmem<BN>::kBytes + 1024) / (smem_bytes + 1024);   // shared memory
   const int tmem_fit = 512 / ((BN == 128 || BN == 192) ? 512 : (2 * BN < 32 ? 32 : 2 * BN));   // tensor memory columns
@@ -740,6 +786,27 @@ static uint4* tree_scratch_for_device() {
     ptr[dev] = static_cast<uint4*>(p);
   }
   return ptr[dev];
+}
+
+// act[M, I] = silu(bf16(X Wg^T)) * bf16(X Wu^T) for a packed gate/up weight Wgu [2 I, K] whose rows
+// come in blocks of `blk`: [g_0 | u_0 | g_1 | u_1 | ...] (blk = I: plain [gate | up]).  One kernel:
+// 192-wide tiles of 96 gate + 96 up columns, SwiGLU in the epilogue; the gate/up tensor is never
+// written.  Bits equal rlk_det_gemm followed by rlk_swiglu_fwd.  I and blk must be multiples of 96.
+RLK_API int rlk_det_gemm_swiglu(const void* X, const void* Wgu, void* act, int M, int I, int K,
+                                long long ldx, long long ldw, long long ld_act, int blk, void* stream) {
+  using namespace rlk;
+  RLK_REQUIRE(M > 0 && I > 0 && K > 0 && K % 8 == 0, "det_gemm_swiglu: bad shape");
+  RLK_REQUIRE(blk > 0 && I % blk == 0 && blk % 96 == 0, "det_gemm_swiglu: the gate/up block must be a multiple of 96 columns");
+  RLK_REQUIRE((reinterpret_cast<uintptr_t>(act) & 15) == 0 && (ld_act * 2) % 16 == 0, "det_gemm_swiglu: act must be 16-byte aligned");
+  GemmParams p{};
+  p.M = M; p.N = 2 * I; p.K = K;
+  p.nchunks = 1;
+  p.kb_per_chunk = (K + 63) / 64;
+  p.C = act; p.ldc = ld_act;
+  p.status = device_status_word();
+  p.act_blk = blk;
+  p.act_I = I;
+  return launch_gemm<192, false, false>(X, Wgu, p, ldx, ldw, static_cast<cudaStream_t>(stream));
 }
 
 // C[M,N] = A * B^T.

@@ -371,6 +371,7 @@ class Qwen3Engine:
                            accumulate=accumulate)
 
     fold_tree_into_norm = True     # decode: the chunk tree of o_proj / down is evaluated by the next norm
+    fuse_decode_swiglu = True      # decode: the gate/up GEMM writes the SwiGLU output directly
 
     def _row_parallel_leaves(self, a, w, name: str, nchunks: int) -> _Leaves:
         M, N = a.shape[0], w.shape[0]
@@ -471,10 +472,15 @@ class Qwen3Engine:
                  store_tag: str | None = None) -> torch.Tensor:
         """Feed-forward block on the normalised stream ``h2`` [T, H] -> [T, H] (before the residual)."""
         w, ws, H = self.p.w, self.ws, self.spec.hidden_size
-        gu = ws.get(f"{store_tag or tag}.gu", (T, 2 * self.p.i_local))
-        self._gemm(h2, w[f"l{l}.wgu"], gu)
         act = ws.get(f"{tag}.act", (T, self.p.i_local))
-        nv.swiglu_fwd(gu, act, self.p.i_local, self.blk)
+        if tag == "d" and keep is None and T <= 128 and self.blk % 96 == 0 and self.fuse_decode_swiglu:
+            # decode: SwiGLU in the epilogue of the gate/up GEMM (nobody needs the gate/up tensor)
+            gu = None
+            nv.det_gemm_swiglu(h2, w[f"l{l}.wgu"], act, self.blk)
+        else:
+            gu = ws.get(f"{store_tag or tag}.gu", (T, 2 * self.p.i_local))
+            self._gemm(h2, w[f"l{l}.wgu"], gu)
+            nv.swiglu_fwd(gu, act, self.p.i_local, self.blk)
         if self.fold_tree_into_norm and tag == "d" and self.ctx.tp_size == 1 and self.nchunks > 1 and T <= 512:
             return self._row_parallel_leaves(act, w[f"l{l}.wd"], "d.leaf_down", self.nchunks)
         down = ws.get(f"{tag}.down", (T, H))

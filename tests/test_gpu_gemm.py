@@ -46,6 +46,23 @@ def test_decode_shape_picks_a_one_wave_tile_and_keeps_the_bits():
     assert torch.equal(_gemm(a, b, M, N, K), _gemm(a, b, M, N, K, tile_n=128))
 
 
+@pytest.mark.parametrize("M", [8, 64, 128])
+def test_fused_gate_up_swiglu_equals_gemm_then_swiglu(M):
+    from rl_kernel_b200.backends import native as nv
+
+    I, K, blk = 1536, 512, 192          # gate / up rows interleaved in blocks of 192
+    a = (torch.randn(M, K, device=dev()) * 0.5).to(BF)
+    wgu = (torch.randn(2 * I, K, device=dev()) * 0.05).to(BF)
+    gu = torch.empty(M, 2 * I, device=dev(), dtype=BF)
+    nv.det_gemm(a, wgu, gu, M=M, N=2 * I, K=K)
+    ref = torch.empty(M, I, device=dev(), dtype=BF)
+    nv.swiglu_fwd(gu, ref, I, blk)
+    act = torch.zeros(M, I, device=dev(), dtype=BF)
+    nv.det_gemm_swiglu(a, wgu, act, blk)
+    sync_and_check()
+    assert torch.equal(act, ref)
+
+
 def test_batch_invariance():
     M, N, K = 777, 1024, 2048
     a, b = _mk(M, N, K, 1)
