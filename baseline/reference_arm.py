@@ -6,7 +6,7 @@ a package called ``rl_engine``).  The child is ``baseline/ref_runner.py``.
 
 What the reference can run here: its own Qwen3-8B model class (``Qwen3DenseBIModel``) on its
 Triton operator profile (the native extension is not built: the install happened on a machine
-without a GPU) on ONE GPU.  Its multi-GPU path needs Megatron-LM, vLLM and the
+without a GPU, where the reference's build script skips it) on ONE GPU.  Its multi-GPU path needs Megatron-LM, vLLM and the
 vime orchestrator, none of which ship in the reference tree, so N > 1 reports ``unavailable``.
 """
 from __future__ import annotations

@@ -2,7 +2,8 @@
 // drawn with the Gumbel-max trick and a counter-based Philox4x32-10 generator.
 //
 //   token = argmax_j ( z_j + G_j ),  z = logit / T,  G_j = -log(-log(u_j)),
-//   u_j = Philox(seed; counter = (row_key, step, global vocab id j))
+//   u_j = word (j mod 4) of Philox(seed; counter = (j div 4, row_key, step)), j the global vocab id
+// (one Philox4x32 evaluation serves four consecutive ids).
 // Every vocabulary id owns its own random number, so the draw does not depend on how the
 // vocabulary is sharded over tensor-parallel ranks: each rank reduces its shard to (best value,
 // best id) and the global winner is the maximum over ranks (ties -> smaller id).
@@ -24,7 +25,7 @@ __device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint
   const uint32_t n0 = hi1 ^ c[1] ^ k0, n1 = lo1, n2 = hi0 ^ c[3] ^ k1, n3 = lo0;
   c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
 }
-__device__ __forceinline__ uint32_t philox_u32(uint64_t seed, uint32_t c0, uint32_t c1, uint32_t c2) {
+__device__ __forceinline__ void philox_4x32(uint64_t seed, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t (&out)[4]) {
   uint32_t c[4] = {c0, c1, c2, 0u};
   uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
 #pragma unroll
@@ -33,7 +34,7 @@ __device__ __forceinline__ uint32_t philox_u32(uint64_t seed, uint32_t c0, uint3
     k0 += 0x9E3779B9u;
     k1 += 0xBB67AE85u;
   }
-  return c[0];
+  out[0] = c[0]; out[1] = c[1]; out[2] = c[2]; out[3] = c[3];
 }
 __device__ __forceinline__ float gumbel_from_u32(uint32_t r) {
   const float u = (static_cast<float>(r >> 8) + 0.5f) * (1.0f / 16777216.0f);  // (0,1)
@@ -65,6 +66,8 @@ __global__ void __launch_bounds__(256) sample_gumbel_kernel(const SampleParams p
   const float thr = p.min_keep ? p.min_keep[row] : -INFINITY;
   float best = -INFINITY;
   long long best_id = 0x7fffffffffffffffll;
+  uint32_t r4[4] = {0u, 0u, 0u, 0u};
+  long long r4_group = -1;          // the four-id group whose random words r4 holds
   for (int c = c_begin + threadIdx.x; c < c_end; c += blockDim.x) {
     const uint4 v = *reinterpret_cast<const uint4*>(src + c * 8);
     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
@@ -74,7 +77,15 @@ __global__ void __launch_bounds__(256) sample_gumbel_kernel(const SampleParams p
       if (z < thr) continue;
       const long long id = p.vocab_start + c * 8 + k;
       float s = z;
-      if (!p.greedy) s += gumbel_from_u32(philox_u32(p.seed, static_cast<uint32_t>(id), key, p.step));
+      if (!p.greedy) {
+        const long long grp = id >> 2;
+        if (grp != r4_group) {
+          philox_4x32(p.seed, static_cast<uint32_t>(grp), key, p.step, r4);
+          r4_group = grp;
+        }
+        const int wsel = static_cast<int>(id & 3);
+        s += gumbel_from_u32(wsel == 0 ? r4[0] : wsel == 1 ? r4[1] : wsel == 2 ? r4[2] : r4[3]);
+      }
       if (s > best || (s == best && id < best_id)) { best = s; best_id = id; }
     }
   }
