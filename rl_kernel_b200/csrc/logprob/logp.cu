@@ -75,8 +75,10 @@ logp_merge_kernel(const float2* __restrict__ stats, long long stats_row_stride, 
       const float2 v = st[t];
       if (v.x > -INFINITY) { y = v.y; e = logp_exp(__fsub_rn(v.x, M)); }
     }
-    const int n = min(32, n_tiles - t0);
-    for (int j = 0; j < n; ++j) {
+    // (unrolled: the shuffles of all 32 tiles are in flight at once and only the fma chain is
+    // serial; tiles past the end carry y = e = 0 and are skipped like empty ones)
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
       const float yj = __shfl_sync(0xffffffffu, y, j), ej = __shfl_sync(0xffffffffu, e, j);
       if (ej != 0.f || yj != 0.f) S = fmaf(yj, ej, S);
     }
