@@ -116,7 +116,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttnFwdSmem<DEC>::kBars);
   // barrier indices
   enum { Q_FULL = 0, Q_EMPTY = 2, K_FULL = 4, K_EMPTY = 7, V_FULL = 10, V_EMPTY = 13, S_FULL = 16, S_EMPTY = 18,
-         P_FULL = 20, O_FULL = 21, XCH = 22, NBARS = 26 };
+         P_FULL = 20, O_FULL = 21, XCH = 22, ST_FULL = 26, ST_EMPTY = 28, NBARS = 30 };
   constexpr bool decode = DEC;
   constexpr int nstage = decode ? 3 : 2;
   const uint32_t q_half = static_cast<uint32_t>(p.q_rows_box) * 128u;  // bytes of one 64-column half of Q / P
@@ -159,6 +159,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     mbar_init(BAR(P_FULL), n_active);
     for (int q = 0; q < 4; ++q) mbar_init(BAR(XCH + q), 32 * kSplit);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(BAR(ST_FULL + s), 1);
+      mbar_init(BAR(ST_EMPTY + s), n_active);
+    }
     mbar_init(BAR(O_FULL), 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -188,7 +192,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   constexpr uint32_t TM_S = 0;     // two S buffers: columns [0,128) and [128,256)
   constexpr uint32_t TM_O = 256;   // O_blk: columns [256,384)
 
-  struct TileInfo { AttnTile t; int nblk, b0, st_mode, st_row; };
+  struct TileInfo { AttnTile t; int nblk, b0, st_mode, st_row; bool st_smem; };
+  // Resuming tiles whose rows are consecutive in the state array get their saved state copied into
+  // shared memory by the producer (two slots in the space between the V ring and the barriers, free
+  // when the tiles have few rows), so its latency is off the softmax warps' path.
+  const uint32_t sp_off = off_v + nstage * kTileBytes;
+  const int sp_room = decode ? (24576 - 6 * static_cast<int>(q_half)) / 2 : 0;     // bytes per slot
   auto read_tile = [&](int idx) {
     TileInfo ti;
     ti.t = DEC ? p.tiles[idx] : tile0;
@@ -203,12 +212,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       ti.st_row = p.tile_ext[4 * idx + 2];
       if (ti.b0 > ti.nblk) ti.b0 = ti.nblk;
     }
+    ti.st_smem = decode && ti.st_mode == 2 && p.q_rows_per_seq > 0 && ti.t.n_rows <= p.q_rows_per_seq &&
+                 ti.t.n_rows * kAttnStateFloats * 4 <= sp_room;
     return ti;
   };
 
   if (warp == 0) {
     if (lane == 0) {
       uint32_t kc = 0, tc = 0;       // blocks and tiles issued so far
+      uint32_t stc = 0;              // saved-state copies issued so far
       bool ok = true;
       for (int idx = blockIdx.x; ok && idx < p.n_tiles; idx += tile_step) {
         const TileInfo ti = read_tile(idx);
@@ -226,6 +238,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         } else {
           tma_load_2d(q_dst, &tmQ, t.q_col0, t.q_row0, BAR(Q_FULL + qs));
           tma_load_2d(q_dst + q_half, &tmQ, t.q_col0 + 64, t.q_row0, BAR(Q_FULL + qs));
+        }
+        if (ti.st_smem) {
+          const uint32_t ss = stc & 1, sph = (stc >> 1) & 1;
+          ++stc;
+          if (!mbar_wait(BAR(ST_EMPTY + ss), sph ^ 1, abort_flag, p.status, 214)) break;
+          const uint32_t nbytes = static_cast<uint32_t>(t.n_rows) * kAttnStateFloats * 4;
+          mbar_expect_tx(BAR(ST_FULL + ss), nbytes);
+          bulk_load_1d(sQ + sp_off + ss * sp_room, p.state + static_cast<long long>(ti.st_row) * kAttnStateFloats,
+                       nbytes, BAR(ST_FULL + ss));
         }
         for (int b = ti.b0; b < ti.nblk; ++b, ++kc) {
           const int s = kc % nstage;
@@ -330,6 +351,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float* xch = reinterpret_cast<float*>(smem + AttnFwdSmem<DEC>::kXch);  // [2][128][4] maxima, then [2][128][4] sums
     uint32_t bc = 0;     // blocks done so far (S buffer, P / O phases, maxima slot)
     uint32_t xc = 0;     // exchange rounds done so far (one per block, one per tile)
+    uint32_t stc = 0;    // saved-state copies consumed so far
     bool alive = true;
     // context parallel with staging: the compute warps first help copy the remote K/V blocks
     // (the CTAs that start first do all of it; later ones find the work counter exhausted);
@@ -349,7 +371,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 #pragma unroll
       for (int i = 0; i < 32; ++i) o[i] = 0.f;
       float* st_ptr = nullptr;     // this row's saved state (resumable rows)
-      if (ti.st_mode != 0 && r < t.n_rows) {
+      if (ti.st_smem) {
+        const uint32_t ss = stc & 1, sph = (stc >> 1) & 1;
+        ++stc;
+        if (!mbar_wait(BAR(ST_FULL + ss), sph, abort_flag, p.status, 215)) { alive = false; break; }
+        if (r < t.n_rows) {
+          const float* sp = reinterpret_cast<const float*>(smem + sp_off + ss * sp_room) + r * kAttnStateFloats;
+          m_run = sp[0];
+          l_part = sp[4 + split];
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(sp + 8 + split * 32 + j);
+            o[j] = v.x; o[j + 1] = v.y; o[j + 2] = v.z; o[j + 3] = v.w;
+          }
+        }
+        mbar_arrive(BAR(ST_EMPTY + ss));
+      } else if (ti.st_mode != 0 && r < t.n_rows) {
         const int rps = p.q_rows_per_seq > 0 ? p.q_rows_per_seq : 1;
         st_ptr = p.state + static_cast<long long>(ti.st_row + (r / rps) * p.q_seq_rows + r % rps) * kAttnStateFloats;
         if (ti.st_mode == 2) {

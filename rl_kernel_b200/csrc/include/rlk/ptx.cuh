@@ -127,6 +127,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int 
       ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
+// Untiled bulk copy global -> shared (this CTA), completion on an mbarrier.  Both addresses 16-byte
+// aligned, size a multiple of 16 bytes.  No multicast.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
 __device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"(tmap), "r"(src), "r"(x), "r"(y)
