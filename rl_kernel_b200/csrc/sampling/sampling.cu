@@ -2,7 +2,8 @@
 // drawn with the Gumbel-max trick and a counter-based Philox4x32-10 generator.
 //
 //   token = argmax_j ( z_j + G_j ),  z = logit / T,  G_j = -log(-log(u_j)),
-//   u_j = word (j mod 4) of Philox(seed; counter = (j div 4, row_key, step)), j the global vocab id
+//   u_j = word (j mod 4) of Philox(seed; counter = (j div 4, row_key low word, step, row_key high
+//   word)), j the global vocab id
 // (one Philox4x32 evaluation serves four consecutive ids).
 // Every vocabulary id owns its own random number, so the draw does not depend on how the
 // vocabulary is sharded over tensor-parallel ranks: each rank reduces its shard to (best value,
@@ -25,8 +26,9 @@ __device__ __forceinline__ void philox_round(uint32_t (&c)[4], uint32_t k0, uint
   const uint32_t n0 = hi1 ^ c[1] ^ k0, n1 = lo1, n2 = hi0 ^ c[3] ^ k1, n3 = lo0;
   c[0] = n0; c[1] = n1; c[2] = n2; c[3] = n3;
 }
-__device__ __forceinline__ void philox_4x32(uint64_t seed, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t (&out)[4]) {
-  uint32_t c[4] = {c0, c1, c2, 0u};
+__device__ __forceinline__ void philox_4x32(uint64_t seed, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                            uint32_t (&out)[4]) {
+  uint32_t c[4] = {c0, c1, c2, c3};
   uint32_t k0 = static_cast<uint32_t>(seed), k1 = static_cast<uint32_t>(seed >> 32);
 #pragma unroll
   for (int i = 0; i < 10; ++i) {
@@ -62,7 +64,11 @@ __global__ void __launch_bounds__(256) sample_gumbel_kernel(const SampleParams p
   const int nchunks = p.n_local / 8;
   const int per_seg = (nchunks + kSampleSegs - 1) / kSampleSegs;
   const int c_begin = seg * per_seg, c_end = min(nchunks, c_begin + per_seg);
-  const uint32_t key = static_cast<uint32_t>(p.row_keys ? p.row_keys[row] : row);
+  // 64-bit row key: the low word is the per-sequence / per-position key, the high word may carry
+  // anything else that must change the draw (e.g. the training step of a captured decode graph,
+  // whose scalar arguments are frozen at capture)
+  const unsigned long long rk = static_cast<unsigned long long>(p.row_keys ? p.row_keys[row] : row);
+  const uint32_t key = static_cast<uint32_t>(rk), key_hi = static_cast<uint32_t>(rk >> 32);
   const float thr = p.min_keep ? p.min_keep[row] : -INFINITY;
   float best = -INFINITY;
   long long best_id = 0x7fffffffffffffffll;
@@ -80,7 +86,7 @@ __global__ void __launch_bounds__(256) sample_gumbel_kernel(const SampleParams p
       if (!p.greedy) {
         const long long grp = id >> 2;
         if (grp != r4_group) {
-          philox_4x32(p.seed, static_cast<uint32_t>(grp), key, p.step, r4);
+          philox_4x32(p.seed, static_cast<uint32_t>(grp), key, p.step, key_hi, r4);
           r4_group = grp;
         }
         const int wsel = static_cast<int>(id & 3);

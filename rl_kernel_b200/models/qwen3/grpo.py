@@ -205,6 +205,10 @@ class GRPOTrainer:
             # which rollout engine generated it
             self._seq_key = (torch.arange(B, dtype=torch.int64, device=self.dev)
                              + self.engine_index * B) * 65536
+            # the training step goes into the high word of the sampling keys through a device
+            # tensor: a captured decode graph freezes scalar arguments such as the seed, and the
+            # noise must still differ from one training step to the next
+            self._step_key = torch.zeros(1, dtype=torch.int64, device=self.dev)
             self._out_tok = torch.zeros(B, c.response_len, dtype=torch.int64, device=self.dev)
             self._out_lp = torch.zeros(B, c.response_len, dtype=torch.float32, device=self.dev)
             self._col = torch.zeros(1, dtype=torch.int64, device=self.dev)
@@ -215,7 +219,8 @@ class GRPOTrainer:
         hf = eng.decode_step(self._tok, self._pos, self._kv, self._dtiles, shared=self._shared)
         logits = eng.logits(hf)
         torch.add(self._seq_key, self._pos, out=self._keys)
-        ids, lp = eng.sample(logits, self._keys, temperature=c.temperature, seed=seed)
+        self._keys.add_(self._step_key)
+        ids, lp = eng.sample(logits, self._keys, temperature=c.temperature, seed=c.seed)
         col = self._col.expand(ids.shape[0]).unsqueeze(1)
         self._out_tok.scatter_(1, col, ids.unsqueeze(1))
         self._out_lp.scatter_(1, col, lp.unsqueeze(1))
@@ -245,8 +250,10 @@ class GRPOTrainer:
         self._pos.fill_(P - 1)
         self._col.zero_()
         logits = eng.logits(last)
+        self._step_key.fill_((int(step_seed) & 0x7FFFFFFF) << 32)
         torch.add(self._seq_key, self._pos, out=self._keys)
-        ids, lp = eng.sample(logits, self._keys, temperature=c.temperature, seed=step_seed)
+        self._keys.add_(self._step_key)
+        ids, lp = eng.sample(logits, self._keys, temperature=c.temperature, seed=c.seed)
         self._out_tok[:, 0].copy_(ids)
         self._out_lp[:, 0].copy_(lp)
         self._tok.copy_(ids)

@@ -127,6 +127,26 @@ def test_grouped_prompt_attention_in_decode_keeps_the_bits():
     assert torch.equal(outs[0]["old_logp"], outs[1]["old_logp"])
 
 
+def test_captured_decode_graph_draws_new_noise_every_training_step():
+    """The decode graph freezes its scalar arguments; the step still has to reach the sampler."""
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
+
+    spec = _spec()
+    w = Qwen3DenseWeights.synthetic(spec, seed=11)
+    prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(3)).to(dev())
+    cfg = GRPOConfig(num_prompts=2, group_size=4, prompt_len=128, response_len=48, micro_batch_seqs=8,
+                     use_cuda_graph=True)
+    tr = GRPOTrainer(spec, cfg, dev(), weights=w)
+    tr.publish_weights()
+    t1, _ = tr.rollout(prompts, step_seed=1)
+    t2, _ = tr.rollout(prompts, step_seed=2)     # replays the graph captured with step_seed = 1
+    t1b, _ = tr.rollout(prompts, step_seed=1)
+    sync_and_check()
+    assert torch.equal(t1, t1b)
+    assert not torch.equal(t1[:, 130:], t2[:, 130:])
+
+
 def test_gradients_against_autograd():
     from rl_kernel_b200.models.qwen3 import Qwen3DenseWeights
     from rl_kernel_b200.models.qwen3.engine import PackedParams, Qwen3Engine
