@@ -208,7 +208,7 @@ def run_ours(args) -> dict:
                    "activations": "stored" if cfg.store_activations else "per-layer recompute",
                    "l2_policy": "inputs larger than L2 (16 GB of weights stream every pass)",
                    "includes": "weight publish, prefill, CUDA-graph decode+sampling, reference-policy scoring, "
-                               "train fwd/bwd with recompute, exact grad-norm clip, AdamW"},
+                               "train fwd/bwd (see activations), exact grad-norm clip, AdamW"},
         "logp_mismatch_count": mismatches, "logp_tokens_compared": mism_tokens,
         "clocks": clocks,
         "e2e": {"value": tokens_per_step * args.steps / (wall_ms / 1e3), "unit": "tokens/s",
@@ -216,6 +216,8 @@ def run_ours(args) -> dict:
                 "timing": "host wall clock around the same steps incl. H2D of prompts and D2H of loss"},
         "gpu_launches": int(launches),
         "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
+        "peak_mem_reserved_gb": round(torch.cuda.max_memory_reserved(dev) / 2 ** 30, 2),
+        "device_mem_free_gb": round(torch.cuda.mem_get_info(dev)[0] / 2 ** 30, 2),
         "phase_ms_last_step": trainer.phase_ms(),
     }
     if world > 1:
