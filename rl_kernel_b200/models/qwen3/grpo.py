@@ -213,8 +213,10 @@ class GRPOTrainer:
             self._out_lp = torch.zeros(B, c.response_len, dtype=torch.float32, device=self.dev)
             self._col = torch.zeros(1, dtype=torch.int64, device=self.dev)
 
-    def _decode_once(self, seed: int):
-        """tok[B] at pos[B] -> next token + its logp, appended at column `col`; advances state."""
+    def _decode_once(self):
+        """tok[B] at pos[B] -> next token + its logp, appended at column `col`; advances state.
+        (The training step reaches the sampler through ``_step_key``, not through an argument: this
+        function is captured in a CUDA graph.)"""
         eng, c = self.rollout_engine, self.cfg
         hf = eng.decode_step(self._tok, self._pos, self._kv, self._dtiles, shared=self._shared)
         logits = eng.logits(hf)
@@ -267,7 +269,7 @@ class GRPOTrainer:
                 s = torch.cuda.Stream(self.dev)
                 s.wait_stream(torch.cuda.current_stream(self.dev))
                 with torch.cuda.stream(s):
-                    self._decode_once(step_seed)
+                    self._decode_once()
                 torch.cuda.current_stream(self.dev).wait_stream(s)
                 self._tok.copy_(snap[0]); self._pos.copy_(snap[1]); self._col.copy_(snap[2])
                 self._graph = torch.cuda.CUDAGraph()
@@ -276,9 +278,9 @@ class GRPOTrainer:
                 with torch.cuda.graph(self._graph):
                     if coll is not None:
                         with coll.graph_capture():
-                            self._decode_once(step_seed)
+                            self._decode_once()
                     else:
-                        self._decode_once(step_seed)
+                        self._decode_once()
                 if coll is not None:
                     coll.graph_commit()
                 self.graph_launches = nv.LAUNCH_COUNT - n0
@@ -290,7 +292,7 @@ class GRPOTrainer:
             nv.LAUNCH_COUNT += (R - 1) * self.graph_launches
         else:
             for _ in range(R - 1):
-                self._decode_once(step_seed)
+                self._decode_once()
         tokens = torch.cat([prompts.repeat_interleave(G, dim=0), self._out_tok], dim=1).contiguous()
         return tokens, self._out_lp.clone()
 
