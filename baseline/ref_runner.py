@@ -7,6 +7,16 @@
     update  : torch autograd through the reference's operator profile + torch.optim.AdamW
 Same synthetic data shape as the main arm: 8 prompts x group 8, prompt 512 + response 1024.
 Prints one JSON line; any failure is reported as {"impl": "reference", "unavailable": ...}.
+
+Row limit of one ``forward`` call.  The reference's Triton operator profile computes the LM head
+with ``_det_gemm_fp32_kernel`` (rl_engine/backends/shared/triton/gemm/det_gemm.py:679-723), whose
+output pointers are ``c_ptr + offs_m * stride_cm + offs_n * stride_cn`` in 32-bit integers.  With
+the full vocabulary (stride_cm = 151936) the product passes 2^31 from row 14135 on and the store
+lands outside the tensor.  An earlier version of this runner prefilled all 64 sequences x 512
+prompt tokens in one ``forward`` (32768 rows) and met exactly that: "illegal memory access" in the
+first forward.  The reference's own workloads never do this (its trainer scores a few sequences
+per call), so the runner now prefills the 8 distinct prompts once (4096 rows), expands the cache
+to the 64 samples, and checks ``MAX_FORWARD_ROWS`` before every call.
 """
 from __future__ import annotations
 
@@ -17,6 +27,8 @@ import sys
 import time
 
 PROMPTS, GROUP, PROMPT_LEN = 8, 8, 512
+VOCAB = 151936
+MAX_FORWARD_ROWS = (2 ** 31 - 1) // VOCAB - 128      # rows of one forward call: 32-bit output offsets (see above)
 
 
 def main() -> int:
@@ -27,6 +39,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--micro-batch", type=int, default=2)
     ap.add_argument("--step-timeout", type=int, default=2400)
+    ap.add_argument("--time-budget", type=float, default=1500.0,
+                    help="seconds for warm-up + timed steps together; fewer steps are run (and reported) when "
+                         "the requested ones do not fit")
     a = ap.parse_args()
     try:
         out = run(a)
@@ -70,6 +85,11 @@ def run(a) -> dict:
                                  generator=torch.Generator().manual_seed(99)).pin_memory()
     host_loss = torch.empty(1).pin_memory()
 
+    def check_rows(rows: int) -> None:
+        if rows > MAX_FORWARD_ROWS:
+            raise ValueError(f"{rows} rows in one forward call exceed the reference's 32-bit LM-head offsets "
+                             f"({MAX_FORWARD_ROWS} rows at vocabulary {VOCAB})")
+
     def alarm(_sig, _frm):
         raise TimeoutError(f"one reference step exceeded {a.step_timeout} s")
 
@@ -77,12 +97,20 @@ def run(a) -> dict:
 
     def one_step(i: int) -> None:
         signal.alarm(a.step_timeout)
-        prompts = host_prompts[i].to(dev, non_blocking=True).repeat_interleave(GROUP, 0)
-        # ---- rollout
+        uniq = host_prompts[i].to(dev, non_blocking=True)
+        prompts = uniq.repeat_interleave(GROUP, 0)
+        # ---- rollout: every distinct prompt is prefilled once, its K/V then serve the whole group
         with torch.no_grad():
+            check_rows(PROMPTS * P)
+            pcache = model.allocate_cache(PROMPTS, S, dev)
+            out = model.forward(uniq, kv_cache=pcache)
+            logits = out["logits"][:, -1].float().repeat_interleave(GROUP, 0)
             cache = model.allocate_cache(B, S, dev)
-            out = model.forward(prompts, kv_cache=cache)
-            logits = out["logits"][:, -1].float()
+            cache.k.copy_(pcache.k.repeat_interleave(GROUP, 1))
+            cache.v.copy_(pcache.v.repeat_interleave(GROUP, 1))
+            cache.lengths.copy_(pcache.lengths.repeat_interleave(GROUP, 1))
+            cache.valid.copy_(pcache.valid.repeat_interleave(GROUP, 1))
+            del pcache, out
             toks, lps = [], []
             pos = torch.full((B, 1), P, device=dev, dtype=torch.long)
             for t in range(R):
@@ -106,6 +134,7 @@ def run(a) -> dict:
         mask = torch.ones(B, R, dtype=torch.bool, device=dev)
         opt.zero_grad(set_to_none=True)
         loss_total = torch.zeros((), device=dev)
+        check_rows(a.micro_batch * S)
         for b0 in range(0, B, a.micro_batch):
             tk = tokens[b0:b0 + a.micro_batch]
             with torch.no_grad():
@@ -125,27 +154,40 @@ def run(a) -> dict:
         torch.cuda.current_stream().synchronize()
         signal.alarm(0)
 
+    # warm-up and timed steps share one time budget: the reference's step is minutes long at full
+    # size, and a run that is cut off from outside reports nothing at all
+    t_begin = time.perf_counter()
+    warm_done, step_s = 0, 0.0
     for i in range(a.warmup):
+        ts = time.perf_counter()
         one_step(i)
-    torch.cuda.synchronize()
+        torch.cuda.synchronize()
+        step_s = time.perf_counter() - ts
+        warm_done += 1
+        left = a.time_budget - (time.perf_counter() - t_begin)
+        if left < step_s * (a.warmup - warm_done + 1) and warm_done >= 1:
+            break                       # keep room for at least one timed step
+    left = a.time_budget - (time.perf_counter() - t_begin)
+    steps = max(1, min(a.steps, int(left // max(step_s, 1e-3)))) if warm_done else a.steps
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     e0.record()
-    for i in range(a.warmup, total):
+    for i in range(a.warmup, a.warmup + steps):
         one_step(i)
     e1.record()
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
-    ms = e0.elapsed_time(e1) / a.steps
+    ms = e0.elapsed_time(e1) / steps
     tokens_per_step = B * S
     return {"metric": "qwen3_8b_grpo_step_tokens_per_s", "value": tokens_per_step / (ms / 1e3), "unit": "tokens/s",
-            "n_gpus": 1, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "n_gpus": 1, "steps": steps, "warmup": warm_done, "steps_requested": a.steps,
+            "warmup_requested": a.warmup, "ms_per_step": ms, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "impl": "reference",
             "data": "synthetic (uniform-random prompt ids, Bernoulli rewards, random-init weights)",
             "config": {"model": "Qwen3-8B" if not a.layers else f"Qwen3-8B-shape-{a.layers}L", "global_batch": B,
                        "seq_len": S, "parallelism": "single GPU", "operator_profile": "triton_cuda_bf16",
                        "micro_batch_seqs": a.micro_batch},
-            "e2e": {"value": tokens_per_step * a.steps / wall, "unit": "tokens/s",
+            "e2e": {"value": tokens_per_step * steps / wall, "unit": "tokens/s",
                     "h2d_bytes_per_step": PROMPTS * P * 8, "d2h_bytes_per_step": 4}}
 
 

@@ -735,12 +735,16 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   const int grid = tiles < sm_count() * ctas_per_sm ? tiles : sm_count() * ctas_per_sm;
   auto kfn = det_gemm_kernel<BN, A_MN, B_MN>;
   static bool attr_set[64] = {false};
+  static std::mutex attr_mu;
   int dev = 0;
   RLK_CHECK_CUDA(cudaGetDevice(&dev));
-  if (!attr_set[dev & 63]) {
-    RLK_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        GemmSmem<BN>::kBytes));
-    attr_set[dev & 63] = true;
+  {
+    std::lock_guard<std::mutex> lock(attr_mu);
+    if (!attr_set[dev & 63]) {
+      RLK_CHECK_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          GemmSmem<BN>::kBytes));
+      attr_set[dev & 63] = true;
+    }
   }
   RLK_CHECK_CUDA(launch_pdl(kfn, dim3(grid), dim3(gemm_threads<BN>()), smem_bytes, stream, tmA, tmB, p));
   RLK_CHECK_CUDA(cudaGetLastError());
@@ -902,6 +906,8 @@ RLK_API int rlk_det_gemm_split(const void* A, const void* B, void* C, void* scra
   RLK_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0, "det_gemm_split: bad shape");
   RLK_REQUIRE(nchunks == 2 || nchunks == 4 || nchunks == 8, "det_gemm_split: nchunks must be 2, 4 or 8");
   RLK_REQUIRE(K % (nchunks * 64) == 0, "det_gemm_split: K/nchunks must be a multiple of 64");
+  RLK_REQUIRE(A != nullptr && B != nullptr, "det_gemm_split: A and B must not be null");
+  RLK_REQUIRE(ldc >= N, "det_gemm_split: ldc (%lld) must be at least N (%d)", ldc, N);
   RLK_REQUIRE((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (reinterpret_cast<uintptr_t>(scratch) & 15) == 0 &&
                   scratch != nullptr && (ldc * 2) % 16 == 0, "det_gemm_split: C and scratch must be 16-byte aligned");
   GemmParams p{};
@@ -981,6 +987,9 @@ RLK_API int rlk_det_gemm_split_static(const void* A, const void* B, void* C, int
   RLK_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0, "det_gemm_split_static: bad shape");
   RLK_REQUIRE(nchunks == 2 || nchunks == 4 || nchunks == 8, "det_gemm_split_static: nchunks must be 2, 4 or 8");
   RLK_REQUIRE(K % (nchunks * 64) == 0, "det_gemm_split_static: K/nchunks must be a multiple of 64");
+  // unlike rlk_det_gemm_split there is no leaves-only mode: the partials never leave the library
+  RLK_REQUIRE(A != nullptr && B != nullptr && C != nullptr, "det_gemm_split_static: A, B and C must not be null");
+  RLK_REQUIRE(ldc >= N, "det_gemm_split_static: ldc (%lld) must be at least N (%d)", ldc, N);
   RLK_REQUIRE((reinterpret_cast<uintptr_t>(C) & 15) == 0 && (ldc * 2) % 16 == 0,
               "det_gemm_split_static: C must be 16-byte aligned with a 16-byte multiple pitch");
   const long long need = 2ll * nchunks * M * ldc;

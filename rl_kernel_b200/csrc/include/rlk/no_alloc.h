@@ -30,7 +30,11 @@
 //   * a device-side wait that gives up (the bounded-wait safety net) still ends the kernel, but
 //     this variant has no status word to record it in; callers that need that report use
 //     rlk_det_gemm_split.
-// Arguments are those of rlk_det_gemm_split without `scratch`.
+// Arguments are those of rlk_det_gemm_split without `scratch`, with two differences: C must not be
+// null (rlk_det_gemm_split's leaves-only mode, C == nullptr, has no meaning here because the
+// partials never leave the library), and ldc >= N is required so that the last chunk's partials
+// stay inside the checked size.  A null A, B or C, or ldc < N, fails with RLK_ERR_BAD_ARG before
+// anything is launched.
 #pragma once
 
 #ifdef __cplusplus

@@ -54,4 +54,4 @@ class DeepSpeedTrainingWorker(RolloutBatchMixin):
         if weight_version <= self.weight_version and self.weight_version != 0:
             raise ValueError("weight_version must increase")
         self.weight_version = weight_version
-        return self.publisher.publish(self._full_state(), weight_version, {"layout": "full-state", "source": "deepspeed"})
+        return self.publisher.publish(self._full_state(), weight_version, {"layout": {"kind": "full-state"}, "source": "deepspeed"})

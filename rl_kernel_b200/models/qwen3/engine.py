@@ -1052,7 +1052,11 @@ class Qwen3Engine:
         if self.ctx.tp_size > 1:
             vals = self.ctx.tp_all_gather(val)           # [tp, n]
             idss = self.ctx.tp_all_gather(ids)
-            best = vals.argmax(0, keepdim=True)          # ties: lowest rank = lowest ids
+            # the winner is the largest perturbed logit; among equal values the lowest rank wins (its
+            # ids are the smallest), spelled out because argmax does not promise a tie order
+            ranks = torch.arange(vals.shape[0], device=vals.device).view(-1, 1).expand_as(vals)
+            best = torch.where(vals == vals.max(0, keepdim=True).values, ranks,
+                               torch.full_like(ranks, vals.shape[0])).min(0, keepdim=True).values
             ids = idss.gather(0, best)[0].contiguous()
         ntile = self.spec.num_vocab_tiles
         stats = self.ws.get("s.stats", (n, ntile, 2), torch.float32)

@@ -128,6 +128,10 @@ class GRPOTrainer:
         # Data parallelism: ``cfg.num_prompts`` counts the whole job; a replica (one TP x CP group)
         # rolls out and trains num_prompts / dp of them and the gradients are summed over replicas.
         self.cp, self.dp = self.ctx.cp_size, self.ctx.dp_size
+        # sampling keys pack (global sequence, position) into the low 32 bits -- 16 bits each -- and
+        # the training step into the high word; larger jobs would carry into the step's bits
+        if cfg.num_seqs >= 65536 or cfg.seq_len > 65536:
+            raise ValueError(f"sampling keys hold 65535 sequences x 65536 positions; got {cfg.num_seqs} x {cfg.seq_len}")
         if cfg.num_prompts % (self.cp * self.dp) or cfg.micro_batch_seqs < 1:
             raise ValueError(f"num_prompts {cfg.num_prompts} must be a multiple of cp x dp = {self.cp * self.dp}")
         self.rep_prompts = cfg.num_prompts // self.dp          # prompts of this replica

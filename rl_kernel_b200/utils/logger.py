@@ -44,3 +44,7 @@ def warn_once(logger: logging.Logger, msg: str) -> None:
 def info_on_rank(logger: logging.Logger, msg: str, rank: int = 0) -> None:
     if _rank() == rank:
         logger.info(msg)
+
+
+# the package-wide logger (the reference exposes the same name: ``from rl_engine.utils.logger import logger``)
+logger = init_logger("rl_kernel_b200", os.environ.get("RL_KERNEL_LOG_LEVEL", "WARNING"))

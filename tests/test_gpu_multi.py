@@ -311,7 +311,7 @@ def _push_worker(rank, world, port, out):
             bridge.add_target(PackedParams(spec, r, 2, torch.device("cpu")), base_ptr=bases[r],
                               version_flag_ptr=bases[r] + dst_layout.numel * 2)
         m = bridge.publish(7)
-        ok &= m.metadata["targets"] == 2
+        ok &= m.metadata["rl_kernel_bridge"]["targets"] == 2 and m.metadata["layout"]["kind"] == "tp-canonical"
     flag = mine[dst_layout.numel * 2: dst_layout.numel * 2 + 8].view(torch.int64)
     okd = torch.zeros(1, dtype=torch.int32, device=dev)
     ext.check(lib.rlk_version_wait(ext.ptr(flag), ctypes.c_ulonglong(7), ext.ptr(okd), ext.stream_ptr(dev)), "wait")

@@ -106,7 +106,7 @@ def test_deepspeed_worker_trains_and_publishes():
     res = w.train(ro)
     assert res.tokens_compared == B * R and not torch.equal(before, eng.module["lm_head"].weight)
     m = w.publish_weights(1)
-    assert "lm_head.weight" in m.tensors and m.metadata["layout"] == "full-state"
+    assert "lm_head.weight" in m.tensors and m.metadata["layout"]["kind"] == "full-state"
 
 
 class FakeRay:
