@@ -128,13 +128,18 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t sDS = smem_u32(smem + DqSmem::kDS);
   constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DQ = 256;
 
+  // Producer and MMA warps: all 32 lanes walk the loops (warp-uniform state lives in uniform
+  // registers, where the TMA / MMA / barrier instructions take their operands from), one elected
+  // lane issues, waits are warp votes.
   if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(BAR(Q_FULL), 2 * kTile);
-      tma_load_2d(sQ, &tmQ, t.q_col0, t.q_row0, BAR(Q_FULL));
-      tma_load_2d(sQ + kHalf, &tmQ, t.q_col0 + 64, t.q_row0, BAR(Q_FULL));
-      tma_load_2d(sDO, &tmDO, t.q_col0, t.q_row0, BAR(Q_FULL));
-      tma_load_2d(sDO + kHalf, &tmDO, t.q_col0 + 64, t.q_row0, BAR(Q_FULL));
+    {
+      if (elect_one()) {
+        mbar_expect_tx(BAR(Q_FULL), 2 * kTile);
+        tma_load_2d(sQ, &tmQ, t.q_col0, t.q_row0, BAR(Q_FULL));
+        tma_load_2d(sQ + kHalf, &tmQ, t.q_col0 + 64, t.q_row0, BAR(Q_FULL));
+        tma_load_2d(sDO, &tmDO, t.q_col0, t.q_row0, BAR(Q_FULL));
+        tma_load_2d(sDO + kHalf, &tmDO, t.q_col0 + 64, t.q_row0, BAR(Q_FULL));
+      }
       for (int b = 0; b < nblk; ++b) {
         const int s = b & 1;
         const uint32_t ph = (b >> 1) & 1;
@@ -145,59 +150,67 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         const CUtensorMap* mk = &kv.k[src];
         const CUtensorMap* mv = &kv.v[src];
         if (use_stage && src != p.stage.rank) {
-          if (!cp_stage_wait(p.stage, src, row / kAttnBlock, abort_flag, p.status, 320)) break;
+          if (!__all_sync(0xffffffffu, cp_stage_wait(p.stage, src, row / kAttnBlock, abort_flag, p.status, 320))) break;
           row += src * p.stage.rows;
           mk = &staged.k[0];
           mv = &staged.v[0];
         }
-        if (!mbar_wait(BAR(K_EMPTY + s), ph ^ 1, abort_flag, p.status, 301)) break;
-        mbar_expect_tx(BAR(K_FULL + s), kTile);
-        tma_load_2d(sK + s * kTile, mk, t.kv_col0, row, BAR(K_FULL + s));
-        tma_load_2d(sK + s * kTile + kHalf, mk, t.kv_col0 + 64, row, BAR(K_FULL + s));
-        if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1, abort_flag, p.status, 302)) break;
-        mbar_expect_tx(BAR(V_FULL + s), kTile);
-        tma_load_2d(sV + s * kTile, mv, t.kv_col0, row, BAR(V_FULL + s));
-        tma_load_2d(sV + s * kTile + kHalf, mv, t.kv_col0 + 64, row, BAR(V_FULL + s));
+        if (!mbar_wait_warp(BAR(K_EMPTY + s), ph ^ 1, abort_flag, p.status, 301)) break;
+        if (elect_one()) {
+          mbar_expect_tx(BAR(K_FULL + s), kTile);
+          tma_load_2d(sK + s * kTile, mk, t.kv_col0, row, BAR(K_FULL + s));
+          tma_load_2d(sK + s * kTile + kHalf, mk, t.kv_col0 + 64, row, BAR(K_FULL + s));
+        }
+        if (!mbar_wait_warp(BAR(V_EMPTY + s), ph ^ 1, abort_flag, p.status, 302)) break;
+        if (elect_one()) {
+          mbar_expect_tx(BAR(V_FULL + s), kTile);
+          tma_load_2d(sV + s * kTile, mv, t.kv_col0, row, BAR(V_FULL + s));
+          tma_load_2d(sV + s * kTile + kHalf, mv, t.kv_col0 + 64, row, BAR(V_FULL + s));
+        }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_kmn = umma_idesc_bf16(128, 128, 0, 1);
-      bool ok = mbar_wait(BAR(Q_FULL), 0, abort_flag, p.status, 303);
+      bool ok = mbar_wait_warp(BAR(Q_FULL), 0, abort_flag, p.status, 303);
       for (int b = 0; ok && b < nblk; ++b) {
         const int s = b & 1;
         const uint32_t ph = (b >> 1) & 1;
-        if (!mbar_wait(BAR(K_FULL + s), ph, abort_flag, p.status, 304)) break;
-        if (!mbar_wait(BAR(V_FULL + s), ph, abort_flag, p.status, 305)) break;
+        if (!mbar_wait_warp(BAR(K_FULL + s), ph, abort_flag, p.status, 304)) break;
+        if (!mbar_wait_warp(BAR(V_FULL + s), ph, abort_flag, p.status, 305)) break;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kHalf + (k & 3) * 32;
-          umma_bf16_ss(tmem_base + TM_S, umma_desc_sw128(sQ + off, 16, 1024),
-                       umma_desc_sw128(sK + s * kTile + off, 16, 1024), idesc_kk, k != 0);
-        }
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = (k >> 2) * kHalf + (k & 3) * 32;
+            umma_bf16_ss(tmem_base + TM_S, umma_desc_sw128(sQ + off, 16, 1024),
+                         umma_desc_sw128(sK + s * kTile + off, 16, 1024), idesc_kk, k != 0);
+          }
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kHalf + (k & 3) * 32;
-          umma_bf16_ss(tmem_base + TM_DP, umma_desc_sw128(sDO + off, 16, 1024),
-                       umma_desc_sw128(sV + s * kTile + off, 16, 1024), idesc_kk, k != 0);
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = (k >> 2) * kHalf + (k & 3) * 32;
+            umma_bf16_ss(tmem_base + TM_DP, umma_desc_sw128(sDO + off, 16, 1024),
+                         umma_desc_sw128(sV + s * kTile + off, 16, 1024), idesc_kk, k != 0);
+          }
+          umma_commit(BAR(SDP_FULL));
+          umma_commit(BAR(V_EMPTY + s));
         }
-        umma_commit(BAR(SDP_FULL));
-        umma_commit(BAR(V_EMPTY + s));
-        if (!mbar_wait(BAR(DS_FULL), b & 1, abort_flag, p.status, 306)) break;
+        if (!mbar_wait_warp(BAR(DS_FULL), b & 1, abort_flag, p.status, 306)) break;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t aoff = (k >> 2) * kHalf + (k & 3) * 32;
-          umma_bf16_ss(tmem_base + TM_DQ, umma_desc_sw128(sDS + aoff, 16, 1024),
-                       umma_desc_sw128(sK + s * kTile + k * 2048, kHalf, 1024), idesc_kmn,
-                       (b | k) != 0);
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t aoff = (k >> 2) * kHalf + (k & 3) * 32;
+            umma_bf16_ss(tmem_base + TM_DQ, umma_desc_sw128(sDS + aoff, 16, 1024),
+                         umma_desc_sw128(sK + s * kTile + k * 2048, kHalf, 1024), idesc_kmn,
+                         (b | k) != 0);
+          }
+          umma_commit(BAR(K_EMPTY + s));
+          umma_commit(BAR(DS_EMPTY));
         }
-        umma_commit(BAR(K_EMPTY + s));
-        umma_commit(BAR(DS_EMPTY));
       }
-      umma_commit(BAR(ACC_FULL));
+      if (elect_one()) umma_commit(BAR(ACC_FULL));
     }
   } else {
     // warp -> (quad, split): quad = TMEM lane quadrant, split = which 32 of the 128 columns
@@ -378,17 +391,18 @@ attn_bwd_dkv_kernel(const __grid_constant__ KvMaps<NSRC> qdo, const __grid_const
   const uint32_t sP = smem_u32(smem + DkvSmem::kP), sDS = smem_u32(smem + DkvSmem::kDS);
   constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DK = 256, TM_DV = 384;
 
-  if (warp == 0) {
-    if (lane == 0) {
-      mbar_expect_tx(BAR(KV_FULL), 2 * kTile);
-      tma_load_2d(sK, &tmK, t.kv_col0, t.kv_row, BAR(KV_FULL));
-      tma_load_2d(sK + kHalf, &tmK, t.kv_col0 + 64, t.kv_row, BAR(KV_FULL));
-      tma_load_2d(sV, &tmV, t.kv_col0, t.kv_row, BAR(KV_FULL));
-      tma_load_2d(sV + kHalf, &tmV, t.kv_col0 + 64, t.kv_row, BAR(KV_FULL));
+  if (warp == 0) {     // (all lanes walk the loops, one elected lane issues: see the dQ kernel)
+    {
+      if (elect_one()) {
+        mbar_expect_tx(BAR(KV_FULL), 2 * kTile);
+        tma_load_2d(sK, &tmK, t.kv_col0, t.kv_row, BAR(KV_FULL));
+        tma_load_2d(sK + kHalf, &tmK, t.kv_col0 + 64, t.kv_row, BAR(KV_FULL));
+        tma_load_2d(sV, &tmV, t.kv_col0, t.kv_row, BAR(KV_FULL));
+        tma_load_2d(sV + kHalf, &tmV, t.kv_col0 + 64, t.kv_row, BAR(KV_FULL));
+      }
       for (int it = 0; it < n_iter; ++it) {
         const int g = it / n_qt, qt = qt0 + it % n_qt;
-        if (!mbar_wait(BAR(Q_EMPTY), (it & 1) ^ 1, abort_flag, p.status, 311)) break;
-        mbar_expect_tx(BAR(Q_FULL), 2 * kTile);
+        if (!mbar_wait_warp(BAR(Q_EMPTY), (it & 1) ^ 1, abort_flag, p.status, 311)) break;
         int src, lb;
         cp_locate_block(p.cp, qt, src, lb);
         if (NSRC == 1) src = 0;
@@ -397,53 +411,60 @@ attn_bwd_dkv_kernel(const __grid_constant__ KvMaps<NSRC> qdo, const __grid_const
         const CUtensorMap* mq = &qdo.k[src];
         const CUtensorMap* md = &qdo.v[src];
         if (use_stage && src != p.stage.rank) {
-          if (!cp_stage_wait(p.stage, src, row / 128, abort_flag, p.status, 321)) break;
+          if (!__all_sync(0xffffffffu, cp_stage_wait(p.stage, src, row / 128, abort_flag, p.status, 321))) break;
           row += src * p.stage.rows;
           mq = &staged.k[0];
           md = &staged.v[0];
         }
-        tma_load_2d(sQ, mq, col, row, BAR(Q_FULL));
-        tma_load_2d(sQ + kHalf, mq, col + 64, row, BAR(Q_FULL));
-        tma_load_2d(sDO, md, col, row, BAR(Q_FULL));
-        tma_load_2d(sDO + kHalf, md, col + 64, row, BAR(Q_FULL));
+        if (elect_one()) {
+          mbar_expect_tx(BAR(Q_FULL), 2 * kTile);
+          tma_load_2d(sQ, mq, col, row, BAR(Q_FULL));
+          tma_load_2d(sQ + kHalf, mq, col + 64, row, BAR(Q_FULL));
+          tma_load_2d(sDO, md, col, row, BAR(Q_FULL));
+          tma_load_2d(sDO + kHalf, md, col + 64, row, BAR(Q_FULL));
+        }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc_kk = umma_idesc_bf16(128, 128, 0, 0);
       constexpr uint32_t idesc_mm = umma_idesc_bf16(128, 128, 1, 1);
-      bool ok = mbar_wait(BAR(KV_FULL), 0, abort_flag, p.status, 312);
+      bool ok = mbar_wait_warp(BAR(KV_FULL), 0, abort_flag, p.status, 312);
       for (int it = 0; ok && it < n_iter; ++it) {
-        if (!mbar_wait(BAR(Q_FULL), it & 1, abort_flag, p.status, 313)) break;
+        if (!mbar_wait_warp(BAR(Q_FULL), it & 1, abort_flag, p.status, 313)) break;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {  // S[q][key] = Q K^T
-          const uint32_t off = (k >> 2) * kHalf + (k & 3) * 32;
-          umma_bf16_ss(tmem_base + TM_S, umma_desc_sw128(sQ + off, 16, 1024),
-                       umma_desc_sw128(sK + off, 16, 1024), idesc_kk, k != 0);
-        }
+          for (int k = 0; k < 8; ++k) {  // S[q][key] = Q K^T
+            const uint32_t off = (k >> 2) * kHalf + (k & 3) * 32;
+            umma_bf16_ss(tmem_base + TM_S, umma_desc_sw128(sQ + off, 16, 1024),
+                         umma_desc_sw128(sK + off, 16, 1024), idesc_kk, k != 0);
+          }
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {  // dP[q][key] = dO V^T
-          const uint32_t off = (k >> 2) * kHalf + (k & 3) * 32;
-          umma_bf16_ss(tmem_base + TM_DP, umma_desc_sw128(sDO + off, 16, 1024),
-                       umma_desc_sw128(sV + off, 16, 1024), idesc_kk, k != 0);
+          for (int k = 0; k < 8; ++k) {  // dP[q][key] = dO V^T
+            const uint32_t off = (k >> 2) * kHalf + (k & 3) * 32;
+            umma_bf16_ss(tmem_base + TM_DP, umma_desc_sw128(sDO + off, 16, 1024),
+                         umma_desc_sw128(sV + off, 16, 1024), idesc_kk, k != 0);
+          }
+          umma_commit(BAR(SDP_FULL));
         }
-        umma_commit(BAR(SDP_FULL));
-        if (!mbar_wait(BAR(PDS_FULL), it & 1, abort_flag, p.status, 314)) break;
+        if (!mbar_wait_warp(BAR(PDS_FULL), it & 1, abort_flag, p.status, 314)) break;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {  // dV[key][d] += P^T dO   (contraction over the 128 query rows)
-          umma_bf16_ss(tmem_base + TM_DV, umma_desc_sw128(sP + k * 2048, kHalf, 1024),
-                       umma_desc_sw128(sDO + k * 2048, kHalf, 1024), idesc_mm, (it | k) != 0);
-        }
+          for (int k = 0; k < 8; ++k) {  // dV[key][d] += P^T dO   (contraction over the 128 query rows)
+            umma_bf16_ss(tmem_base + TM_DV, umma_desc_sw128(sP + k * 2048, kHalf, 1024),
+                         umma_desc_sw128(sDO + k * 2048, kHalf, 1024), idesc_mm, (it | k) != 0);
+          }
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {  // dK[key][d] += dS^T Q
-          umma_bf16_ss(tmem_base + TM_DK, umma_desc_sw128(sDS + k * 2048, kHalf, 1024),
-                       umma_desc_sw128(sQ + k * 2048, kHalf, 1024), idesc_mm, (it | k) != 0);
+          for (int k = 0; k < 8; ++k) {  // dK[key][d] += dS^T Q
+            umma_bf16_ss(tmem_base + TM_DK, umma_desc_sw128(sDS + k * 2048, kHalf, 1024),
+                         umma_desc_sw128(sQ + k * 2048, kHalf, 1024), idesc_mm, (it | k) != 0);
+          }
+          umma_commit(BAR(Q_EMPTY));
         }
-        umma_commit(BAR(Q_EMPTY));
       }
-      umma_commit(BAR(ACC_FULL));
+      if (elect_one()) umma_commit(BAR(ACC_FULL));
     }
   } else {
     const int quad = warp & 3;

@@ -217,8 +217,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     return ti;
   };
 
+  // The producer and MMA warps walk their loops with all 32 lanes (the loop state is warp-uniform
+  // and stays in uniform registers, where the TMA / MMA / barrier instructions take their operands
+  // from); one elected lane issues.  Waits are warp votes, so a timeout leaves no lane behind.
   if (warp == 0) {
-    if (lane == 0) {
+    {
       uint32_t kc = 0, tc = 0;       // blocks and tiles issued so far
       uint32_t stc = 0;              // saved-state copies issued so far
       bool ok = true;
@@ -228,25 +231,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (t.n_rows <= 0) continue;
         const uint32_t qs = tc % nq, qph = (tc / nq) & 1;
         ++tc;
-        if (!mbar_wait(BAR(Q_EMPTY + qs), qph ^ 1, abort_flag, p.status, 213)) break;
+        if (!mbar_wait_warp(BAR(Q_EMPTY + qs), qph ^ 1, abort_flag, p.status, 213)) break;
         const uint32_t q_dst = sQ + qs * 2 * q_half;
-        mbar_expect_tx(BAR(Q_FULL + qs), 2 * q_half);
-        if (p.q3d) {
-          const int y = t.q_row0 % p.q_seq_rows, z = t.q_row0 / p.q_seq_rows;
-          tma_load_3d(q_dst, &tmQ, t.q_col0, y, z, BAR(Q_FULL + qs));
-          tma_load_3d(q_dst + q_half, &tmQ, t.q_col0 + 64, y, z, BAR(Q_FULL + qs));
-        } else {
-          tma_load_2d(q_dst, &tmQ, t.q_col0, t.q_row0, BAR(Q_FULL + qs));
-          tma_load_2d(q_dst + q_half, &tmQ, t.q_col0 + 64, t.q_row0, BAR(Q_FULL + qs));
+        if (elect_one()) {
+          mbar_expect_tx(BAR(Q_FULL + qs), 2 * q_half);
+          if (p.q3d) {
+            const int y = t.q_row0 % p.q_seq_rows, z = t.q_row0 / p.q_seq_rows;
+            tma_load_3d(q_dst, &tmQ, t.q_col0, y, z, BAR(Q_FULL + qs));
+            tma_load_3d(q_dst + q_half, &tmQ, t.q_col0 + 64, y, z, BAR(Q_FULL + qs));
+          } else {
+            tma_load_2d(q_dst, &tmQ, t.q_col0, t.q_row0, BAR(Q_FULL + qs));
+            tma_load_2d(q_dst + q_half, &tmQ, t.q_col0 + 64, t.q_row0, BAR(Q_FULL + qs));
+          }
         }
         if (ti.st_smem) {
           const uint32_t ss = stc & 1, sph = (stc >> 1) & 1;
           ++stc;
-          if (!mbar_wait(BAR(ST_EMPTY + ss), sph ^ 1, abort_flag, p.status, 214)) break;
+          if (!mbar_wait_warp(BAR(ST_EMPTY + ss), sph ^ 1, abort_flag, p.status, 214)) break;
           const uint32_t nbytes = static_cast<uint32_t>(t.n_rows) * kAttnStateFloats * 4;
-          mbar_expect_tx(BAR(ST_FULL + ss), nbytes);
-          bulk_load_1d(sQ + sp_off + ss * sp_room, p.state + static_cast<long long>(ti.st_row) * kAttnStateFloats,
-                       nbytes, BAR(ST_FULL + ss));
+          if (elect_one()) {
+            mbar_expect_tx(BAR(ST_FULL + ss), nbytes);
+            bulk_load_1d(sQ + sp_off + ss * sp_room, p.state + static_cast<long long>(ti.st_row) * kAttnStateFloats,
+                         nbytes, BAR(ST_FULL + ss));
+          }
         }
         for (int b = ti.b0; b < ti.nblk; ++b, ++kc) {
           const int s = kc % nstage;
@@ -258,24 +265,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const CUtensorMap* mv = &kv.v[src];
           if (use_stage && src != p.stage.rank) {
             // remote block: read the local copy once it has landed
-            if (!cp_stage_wait(p.stage, src, row / kAttnBlock, abort_flag, p.status, 212)) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, cp_stage_wait(p.stage, src, row / kAttnBlock, abort_flag, p.status, 212))) { ok = false; break; }
             row += src * p.stage.rows;
             mk = &staged.k[0];
             mv = &staged.v[0];
           }
-          if (!mbar_wait(BAR(K_EMPTY + s), ph ^ 1, abort_flag, p.status, 201)) { ok = false; break; }
-          mbar_expect_tx(BAR(K_FULL + s), kTileBytes);
-          tma_load_2d(sK + s * kTileBytes, mk, t.kv_col0, row, BAR(K_FULL + s));
-          tma_load_2d(sK + s * kTileBytes + kHalfBytes, mk, t.kv_col0 + 64, row, BAR(K_FULL + s));
-          if (!mbar_wait(BAR(V_EMPTY + s), ph ^ 1, abort_flag, p.status, 202)) { ok = false; break; }
-          mbar_expect_tx(BAR(V_FULL + s), kTileBytes);
-          tma_load_2d(sV + s * kTileBytes, mv, t.kv_col0, row, BAR(V_FULL + s));
-          tma_load_2d(sV + s * kTileBytes + kHalfBytes, mv, t.kv_col0 + 64, row, BAR(V_FULL + s));
+          if (!mbar_wait_warp(BAR(K_EMPTY + s), ph ^ 1, abort_flag, p.status, 201)) { ok = false; break; }
+          if (elect_one()) {
+            mbar_expect_tx(BAR(K_FULL + s), kTileBytes);
+            tma_load_2d(sK + s * kTileBytes, mk, t.kv_col0, row, BAR(K_FULL + s));
+            tma_load_2d(sK + s * kTileBytes + kHalfBytes, mk, t.kv_col0 + 64, row, BAR(K_FULL + s));
+          }
+          if (!mbar_wait_warp(BAR(V_EMPTY + s), ph ^ 1, abort_flag, p.status, 202)) { ok = false; break; }
+          if (elect_one()) {
+            mbar_expect_tx(BAR(V_FULL + s), kTileBytes);
+            tma_load_2d(sV + s * kTileBytes, mv, t.kv_col0, row, BAR(V_FULL + s));
+            tma_load_2d(sV + s * kTileBytes + kHalfBytes, mv, t.kv_col0 + 64, row, BAR(V_FULL + s));
+          }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc_s = umma_idesc_bf16(128, 128, 0, 0);  // Q (K-major) x K (K-major)
       constexpr uint32_t idesc_o = umma_idesc_bf16(128, 128, 0, 1);  // P (K-major) x V (MN-major)
       uint32_t sc = 0;        // S products issued so far (K ring slot, S buffer)
@@ -288,18 +299,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int sb = sc & 1;                  // S accumulator buffer
         const uint32_t phs = (sc >> 1) & 1;
         ++sc;
-        if (!mbar_wait(BAR(K_FULL + s), ph, abort_flag, p.status, 203)) return false;
-        if (!mbar_wait(BAR(S_EMPTY + sb), phs ^ 1, abort_flag, p.status, 204)) return false;
+        if (!mbar_wait_warp(BAR(K_FULL + s), ph, abort_flag, p.status, 203)) return false;
+        if (!mbar_wait_warp(BAR(S_EMPTY + sb), phs ^ 1, abort_flag, p.status, 204)) return false;
         tc_fence_after();
+        if (elect_one()) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t offq = (k >> 2) * q_half + (k & 3) * 32;
-          const uint32_t offk = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_bf16_ss(tmem_base + TM_S + sb * 128, umma_desc_sw128(q_cur + offq, 16, 1024),
-                       umma_desc_sw128(sK + s * kTileBytes + offk, 16, 1024), idesc_s, k != 0);
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t offq = (k >> 2) * q_half + (k & 3) * 32;
+            const uint32_t offk = (k >> 2) * kHalfBytes + (k & 3) * 32;
+            umma_bf16_ss(tmem_base + TM_S + sb * 128, umma_desc_sw128(q_cur + offq, 16, 1024),
+                         umma_desc_sw128(sK + s * kTileBytes + offk, 16, 1024), idesc_s, k != 0);
+          }
+          umma_commit(BAR(S_FULL + sb));
+          umma_commit(BAR(K_EMPTY + s));
         }
-        umma_commit(BAR(S_FULL + sb));
-        umma_commit(BAR(K_EMPTY + s));
         return true;
       };
       bool ok = true;
@@ -310,30 +323,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const uint32_t qs = tc % nq, qph = (tc / nq) & 1;
         ++tc;
         q_cur = sQ + qs * 2 * q_half;
-        ok = mbar_wait(BAR(Q_FULL + qs), qph, abort_flag, p.status, 205);
+        ok = mbar_wait_warp(BAR(Q_FULL + qs), qph, abort_flag, p.status, 205);
         if (ok && nb > 0) ok = issue_s();
         for (int b = 0; ok && b < nb; ++b) {
           if (b + 1 < nb) ok = issue_s();
           if (!ok) break;
-          if (b + 1 >= nb) umma_commit(BAR(Q_EMPTY + qs));   // every S product of this tile has been issued
+          if (b + 1 >= nb && elect_one()) umma_commit(BAR(Q_EMPTY + qs));   // every S product of this tile has been issued
           const int s = pc % nstage;
           const uint32_t ph = (pc / nstage) & 1;
           const uint32_t pph = pc & 1;
           ++pc;
-          if (!mbar_wait(BAR(V_FULL + s), ph, abort_flag, p.status, 206)) { ok = false; break; }
-          if (!mbar_wait(BAR(P_FULL), pph, abort_flag, p.status, 207)) { ok = false; break; }
+          if (!mbar_wait_warp(BAR(V_FULL + s), ph, abort_flag, p.status, 206)) { ok = false; break; }
+          if (!mbar_wait_warp(BAR(P_FULL), pph, abort_flag, p.status, 207)) { ok = false; break; }
           tc_fence_after();
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const uint32_t aoff = (k >> 2) * q_half + (k & 3) * 32;
-            umma_bf16_ss(tmem_base + TM_O, umma_desc_sw128(sP + aoff, 16, 1024),
-                         umma_desc_sw128(sV + s * kTileBytes + k * 2048, kHalfBytes, 1024), idesc_o,
-                         k != 0);
+            for (int k = 0; k < 8; ++k) {
+              const uint32_t aoff = (k >> 2) * q_half + (k & 3) * 32;
+              umma_bf16_ss(tmem_base + TM_O, umma_desc_sw128(sP + aoff, 16, 1024),
+                           umma_desc_sw128(sV + s * kTileBytes + k * 2048, kHalfBytes, 1024), idesc_o,
+                           k != 0);
+            }
+            umma_commit(BAR(O_FULL));
+            umma_commit(BAR(V_EMPTY + s));
           }
-          umma_commit(BAR(O_FULL));
-          umma_commit(BAR(V_EMPTY + s));
         }
-        if (ok && nb <= 0) umma_commit(BAR(Q_EMPTY + qs));
+        if (ok && nb <= 0 && elect_one()) umma_commit(BAR(Q_EMPTY + qs));
       }
     }
   } else if (!decode || (warp & 3) == 0) {

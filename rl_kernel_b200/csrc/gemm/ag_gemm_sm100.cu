@@ -101,8 +101,10 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int kbs = p.K / ABK;
   const int own_tiles = p.rows_per_rank / ABM;
 
+  // Producer and MMA warps: all 32 lanes walk the loops (warp-uniform state), one elected lane
+  // issues, waits are warp votes.
   if (warp == 0) {
-    if (lane == 0) {
+    {
       uint32_t it = 0;
       for (int t = blockIdx.x; t < total; t += gridDim.x) {
         int ord, nt;
@@ -122,41 +124,43 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
               break;
             }
           }
-          if (*abort_flag) break;
+          if (__any_sync(0xffffffffu, *abort_flag != 0)) break;
           asm volatile("fence.proxy.async;" ::: "memory");  // generic-proxy stores -> TMA reads
         }
         for (int kb = 0; kb < kbs; ++kb, ++it) {
           const uint32_t s = it % kAgStages, ph = (it / kAgStages) & 1;
-          if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 502)) break;
+          if (!mbar_wait_warp(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 502)) break;
           const uint32_t fb = full0 + 8 * s;
-          mbar_expect_tx(fb, kAgStage);
           const uint32_t sa = smem_base + s * kAgStage;
+          if (!elect_one()) continue;
+          mbar_expect_tx(fb, kAgStage);
           tma_load_2d(sa, &tmA, kb * ABK, mt * ABM, fb);
           tma_load_2d(sa + kAgStageA, &tmB, kb * ABK, nt * ABN, fb);
         }
-        if (*abort_flag) break;
+        if (__any_sync(0xffffffffu, *abort_flag != 0)) break;
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = umma_idesc_bf16(ABM, ABN, 0, 0);
       uint32_t it = 0, u = 0;
-      for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x, ++u) {
+      for (int t = blockIdx.x; t < total && !__any_sync(0xffffffffu, *abort_flag != 0); t += gridDim.x, ++u) {
         const uint32_t a = u & 1;
-        if (!mbar_wait(acce0 + 8 * a, ((u >> 1) & 1) ^ 1, abort_flag, p.status, 503)) break;
+        if (!mbar_wait_warp(acce0 + 8 * a, ((u >> 1) & 1) ^ 1, abort_flag, p.status, 503)) break;
         tc_fence_after();
         for (int kb = 0; kb < kbs; ++kb, ++it) {
           const uint32_t s = it % kAgStages, ph = (it / kAgStages) & 1;
-          if (!mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 504)) break;
+          if (!mbar_wait_warp(full0 + 8 * s, ph, abort_flag, p.status, 504)) break;
           tc_fence_after();
           const uint32_t sa = smem_base + s * kAgStage, sb = sa + kAgStageA;
+          if (!elect_one()) continue;
 #pragma unroll
           for (int k = 0; k < ABK / 16; ++k)
             umma_bf16_ss(tmem_base + a * ABN, umma_desc_sw128(sa + k * 32, 16, 1024),
                          umma_desc_sw128(sb + k * 32, 16, 1024), idesc, (kb | k) != 0 ? 1u : 0u);
           umma_commit(empty0 + 8 * s);
         }
-        umma_commit(accf0 + 8 * a);
+        if (elect_one()) umma_commit(accf0 + 8 * a);
       }
     }
   } else if (warp < 6) {

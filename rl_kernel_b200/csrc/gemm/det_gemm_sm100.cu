@@ -50,6 +50,9 @@ struct GemmParams {
   int a_box_rows;           // rows of A that TMA brings per tile (128, or fewer when M < 128)
   int stage_a_bytes;        // shared-memory bytes reserved for the A tile of one stage
   int stages;               // depth of the shared-memory ring
+  int kslabs;               // 64-wide k blocks per ring stage (1, 2 or 4).  More than one: both operands are
+                            //   K-major and a stage is brought by ONE 3-D TMA box per operand ([slab][row][64]),
+                            //   so the two single-lane roles pay their per-stage waits once per 128 or 256 k
   // Fused gate/up + SwiGLU (192-wide tiles only, act_blk > 0): B holds gate and up rows interleaved
   // in blocks of act_blk rows ([g_0 | u_0 | g_1 | u_1 ...]); a tile multiplies by 96 gate rows and
   // the 96 matching up rows, and the epilogue writes silu(bf16(gate)) * bf16(up) -- the bits of
@@ -86,7 +89,19 @@ struct GemmParams {
   int ar_use_epoch;
   __nv_bfloat16* ar_out;
   long long ar_ld_out;
+#ifdef RLK_GEMM_TRACE
+  // profiling build only: clock64 stamps of CTA 0's two single-thread roles, [5][kTraceLen]
+  // (producer: after the empty wait, after the TMA issue; MMA thread: after the full wait, after
+  // the MMA issue, after the commit)
+  long long* trace;
+#endif
 };
+#ifdef RLK_GEMM_TRACE
+constexpr int kTraceLen = 512;
+#define RLK_TRACE(row, idx) do { if (p.trace && blockIdx.x == 0 && (idx) < kTraceLen) p.trace[(row) * kTraceLen + (idx)] = clock64(); } while (0)
+#else
+#define RLK_TRACE(row, idx) do { } while (0)
+#endif
 
 __device__ __forceinline__ uint4 ar_ld_peer_v4(const void* p) {
   uint4 v;
@@ -147,7 +162,9 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  const uint32_t stage_bytes = static_cast<uint32_t>(p.stage_a_bytes) + S::kStageB;   // one k block: A tile, B tile
+  const uint32_t kslabs = static_cast<uint32_t>(p.kslabs);
+  const uint32_t a_region = kslabs * static_cast<uint32_t>(p.stage_a_bytes);           // A slabs of a stage, then its B slabs
+  const uint32_t stage_bytes = a_region + kslabs * S::kStageB;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * stage_bytes);
   // bars: full[kStages], empty[kStages], acc_full[2], acc_empty[2], then tmem ptr + abort flag
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 4);
@@ -190,29 +207,36 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    // The whole warp walks the loop (its state is warp-uniform, so it can live in uniform
+    // registers, which is where the TMA and barrier instructions take their operands from); one
+    // elected lane issues.
+    {
       uint32_t it = 0, pre = 0;
       uint32_t ps = 0, pph = 0, psa = smem_base;   // ring slot, its phase, its shared-memory address
-      const uint32_t stage_tx = (A_MN ? S::kStageA : static_cast<uint32_t>(p.a_box_rows) * BK * 2) + S::kStageB;
+      const uint32_t stage_tx = kslabs * ((A_MN ? S::kStageA : static_cast<uint32_t>(p.a_box_rows) * BK * 2) + S::kStageB);
       if (p.b_static && static_cast<int>(blockIdx.x) < total_tiles) {
         // weights do not depend on the previous kernel: start streaming the first tile's B blocks
         // while that kernel is still running
         int mt, nt;
         tile_coords(blockIdx.x / p.split_chunks, p.m_tiles, p.n_tiles, mt, nt);
-        const uint32_t kbs = static_cast<uint32_t>(p.nchunks * p.kb_per_chunk);
+        const uint32_t kbs = static_cast<uint32_t>(p.nchunks * p.kb_per_chunk) / kslabs;   // ring stages of a tile
         const int kb0 = (blockIdx.x % p.split_chunks) * p.kb_per_chunk;
         pre = kbs < kStages ? kbs : kStages;
         for (uint32_t kb = 0; kb < pre; ++kb) {
           const uint32_t fb = full0 + 8 * kb;
+          const uint32_t sb = smem_base + kb * stage_bytes + a_region;
+          const int k0 = (kb0 + static_cast<int>(kb * kslabs)) * BK;
+          if (!elect_one()) continue;
           mbar_expect_tx(fb, stage_tx);
-          const uint32_t sb = smem_base + kb * stage_bytes + p.stage_a_bytes;
-          const int k0 = (kb0 + static_cast<int>(kb)) * BK;
           if (BN == 192 && p.act_blk > 0) {
             const int gr = act_gate_row(nt, p.act_blk);
-            tma_load_2d(sb, &tmB, k0, gr, fb);
-            tma_load_2d(sb + 96 * 128, &tmB, k0, gr + p.act_blk, fb);
+            for (uint32_t sl = 0; sl < kslabs; ++sl) {
+              tma_load_2d(sb + sl * S::kStageB, &tmB, k0 + sl * BK, gr, fb);
+              tma_load_2d(sb + sl * S::kStageB + 96 * 128, &tmB, k0 + sl * BK, gr + p.act_blk, fb);
+            }
           } else if (!B_MN) {
-            tma_load_2d(sb, &tmB, k0, nt * BN, fb);
+            if (kslabs > 1) tma_load_3d(sb, &tmB, 0, nt * BN, k0 / BK, fb);
+            else tma_load_2d(sb, &tmB, k0, nt * BN, fb);
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, &tmB, nt * BN + 64 * i, k0, fb);
@@ -225,22 +249,24 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int chunk = t % p.split_chunks;
         tile_coords(t / p.split_chunks, p.m_tiles, p.n_tiles, mt, nt);
         const int m0 = mt * BM, n0 = nt * BN;
-        const int kbs = p.nchunks * p.kb_per_chunk;
+        const int kbs = p.nchunks * p.kb_per_chunk / static_cast<int>(kslabs);   // ring stages of this tile
         const int kb0 = chunk * p.kb_per_chunk;
+        const int k_step = BK * static_cast<int>(kslabs);
         int k0 = kb0 * BK;
-        for (int kb = 0; kb < kbs; ++kb, ++it, k0 += BK) {
+        for (int kb = 0; kb < kbs; ++kb, ++it, k0 += k_step) {
           const uint32_t fb = full0 + 8 * ps;
           const bool fresh = it >= pre;   // else: armed, and B requested, before the dependency wait
-          if (fresh) {
-            if (!mbar_wait(empty0 + 8 * ps, pph ^ 1, abort_flag, p.status, 101)) break;
-            mbar_expect_tx(fb, stage_tx);
-          }
+          if (fresh && !mbar_wait_warp(empty0 + 8 * ps, pph ^ 1, abort_flag, p.status, 101)) break;
+          RLK_TRACE(0, it);
           const uint32_t sa = psa;
-          const uint32_t sb = sa + p.stage_a_bytes;
-          // ring position of the next k block (a single thread runs this loop: no divisions)
+          const uint32_t sb = sa + a_region;
+          // ring position of the next stage (no divisions in this loop)
           if (++ps == kStages) { ps = 0; pph ^= 1; psa = smem_base; } else { psa += stage_bytes; }
+          if (!elect_one()) continue;
+          if (fresh) mbar_expect_tx(fb, stage_tx);
           if (!A_MN) {
-            tma_load_2d(sa, &tmA, k0, m0, fb);
+            if (kslabs > 1) tma_load_3d(sa, &tmA, 0, m0, k0 / BK, fb);
+            else tma_load_2d(sa, &tmA, k0, m0, fb);
           } else {
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * 8192, &tmA, m0 + 64 * i, k0, fb);
@@ -248,54 +274,78 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           if (!fresh) continue;
           if (BN == 192 && p.act_blk > 0) {
             const int gr = act_gate_row(nt, p.act_blk);
-            tma_load_2d(sb, &tmB, k0, gr, fb);
-            tma_load_2d(sb + 96 * 128, &tmB, k0, gr + p.act_blk, fb);
+            for (uint32_t sl = 0; sl < kslabs; ++sl) {
+              tma_load_2d(sb + sl * S::kStageB, &tmB, k0 + sl * BK, gr, fb);
+              tma_load_2d(sb + sl * S::kStageB + 96 * 128, &tmB, k0 + sl * BK, gr + p.act_blk, fb);
+            }
           } else if (!B_MN) {
-            tma_load_2d(sb, &tmB, k0, n0, fb);
+            if (kslabs > 1) tma_load_3d(sb, &tmB, 0, n0, k0 / BK, fb);
+            else tma_load_2d(sb, &tmB, k0, n0, fb);
           } else {
 #pragma unroll
             for (int i = 0; i < BN / 64; ++i) tma_load_2d(sb + i * 8192, &tmB, n0 + 64 * i, k0, fb);
           }
+          RLK_TRACE(1, it);
         }
         if (*abort_flag) break;
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // (whole warp in the loop, one elected lane issues: see the producer)
+    {
       constexpr uint32_t idesc = umma_idesc_bf16(BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       // One thread issues every MMA, so each instruction of this loop is on the critical path of a
       // small tile.  The shared-memory descriptors differ only in their 14-bit start-address field
       // (address / 16, bits 0-13; shared memory ends below 2^18, so adding never carries out of
       // it): build them once and step the low word per k step and per ring slot.
       const uint64_t da_base = A_MN ? umma_desc_sw128(smem_base, 8192, 1024) : umma_desc_sw128(smem_base, 16, 1024);
-      const uint64_t db_base = B_MN ? umma_desc_sw128(smem_base + p.stage_a_bytes, 8192, 1024)
-                                    : umma_desc_sw128(smem_base + p.stage_a_bytes, 16, 1024);
+      const uint64_t db_base = B_MN ? umma_desc_sw128(smem_base + a_region, 8192, 1024)
+                                    : umma_desc_sw128(smem_base + a_region, 16, 1024);
       const uint32_t da_hi = static_cast<uint32_t>(da_base >> 32), db_hi = static_cast<uint32_t>(db_base >> 32);
       const uint32_t da_lo0 = static_cast<uint32_t>(da_base), db_lo0 = static_cast<uint32_t>(db_base);
       constexpr uint32_t ka_step = (A_MN ? 2048u : 32u) >> 4, kb_step = (B_MN ? 2048u : 32u) >> 4;
       const uint32_t slot_step = stage_bytes >> 4;
+      const uint32_t a_slab_step = static_cast<uint32_t>(p.stage_a_bytes) >> 4, b_slab_step = S::kStageB >> 4;
+      const int stages_per_chunk = p.kb_per_chunk / static_cast<int>(kslabs);
       uint32_t s = 0, ph = 0, da_lo = da_lo0, db_lo = db_lo0, u = 0;
+#ifdef RLK_GEMM_TRACE
+      int tr = 0;
+#endif
       auto desc64 = [](uint32_t lo, uint32_t hi) { return (static_cast<uint64_t>(hi) << 32) | lo; };
       for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
         for (int c = 0; c < p.nchunks; ++c, ++u) {
           const uint32_t a = u & 1;
-          if (!mbar_wait(acce0 + 8 * a, ((u >> 1) & 1) ^ 1, abort_flag, p.status, 102)) break;
+          if (!mbar_wait_warp(acce0 + 8 * a, ((u >> 1) & 1) ^ 1, abort_flag, p.status, 102)) break;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + a * kAcc;
-          for (int kb = 0; kb < p.kb_per_chunk; ++kb) {
+          for (int kb = 0; kb < stages_per_chunk; ++kb) {
             // (no tcgen05 fence here: the operands come from TMA, whose completion the barrier
             // itself orders; the fence after the accumulator wait above covers the epilogue's loads)
-            if (!mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 103)) break;
-            umma_bf16_ss(d_tmem, desc64(da_lo, da_hi), desc64(db_lo, db_hi), idesc, kb != 0 ? 1u : 0u);
+            if (!mbar_wait_warp(full0 + 8 * s, ph, abort_flag, p.status, 103)) break;
+            RLK_TRACE(2, tr);
+            if (elect_one()) {
+              umma_bf16_ss(d_tmem, desc64(da_lo, da_hi), desc64(db_lo, db_hi), idesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-            for (uint32_t k = 1; k < BK / UMMA_K; ++k)
-              umma_bf16_ss(d_tmem, desc64(da_lo + k * ka_step, da_hi), desc64(db_lo + k * kb_step, db_hi), idesc, 1u);
-            umma_commit(empty0 + 8 * s);  // frees the smem stage when these MMAs retire
+              for (uint32_t k = 1; k < BK / UMMA_K; ++k)
+                umma_bf16_ss(d_tmem, desc64(da_lo + k * ka_step, da_hi), desc64(db_lo + k * kb_step, db_hi), idesc, 1u);
+              for (uint32_t sl = 1; sl < kslabs; ++sl) {      // further k slabs of this stage (K-major operands only)
+                const uint32_t al = da_lo + sl * a_slab_step, bl = db_lo + sl * b_slab_step;
+#pragma unroll
+                for (uint32_t k = 0; k < BK / UMMA_K; ++k)
+                  umma_bf16_ss(d_tmem, desc64(al + k * ka_step, da_hi), desc64(bl + k * kb_step, db_hi), idesc, 1u);
+              }
+              RLK_TRACE(3, tr);
+              umma_commit(empty0 + 8 * s);  // frees the smem stage when these MMAs retire
+              RLK_TRACE(4, tr);
+            }
+#ifdef RLK_GEMM_TRACE
+            ++tr;
+#endif
             if (++s == kStages) { s = 0; ph ^= 1; da_lo = da_lo0; db_lo = db_lo0; }
             else { da_lo += slot_step; db_lo += slot_step; }
           }
-          umma_commit(accf0 + 8 * a);  // accumulator of this chunk complete
+          if (elect_one()) umma_commit(accf0 + 8 * a);  // accumulator of this chunk complete
         }
       }
     }
@@ -680,6 +730,12 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
   }
 }
 
+// Ring depth / CTAs per SM of the small-M (decode) launches; 0 = the built-in choice.
+static int g_small_m_stages = 0, g_small_m_ctas = 0, g_small_m_kslabs = 0;
+#ifdef RLK_GEMM_TRACE
+static long long* g_trace_ptr = nullptr;
+#endif
+
 template <int BN, bool A_MN, bool B_MN>
 static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long long lda,
                        long long ldb, cudaStream_t stream) {
@@ -693,18 +749,28 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   // The UMMA still addresses 128 A rows; with a short A box the rows past it alias the B tile /
   // next stage (finite garbage feeding accumulator rows nobody stores), and the stage shrinks so
   // two CTAs fit on an SM -- more loads in flight for the bandwidth-bound small-M case.
-  p.stage_a_bytes = A_MN ? GemmSmem<BN>::kStageA : (p.a_box_rows * BK * 2 + 1023) / 1024 * 1024;
-  // Ring depth: the default for full tiles; with a short A box (small M: the kernel is bound by
-  // how many weight bytes each SM keeps in flight) as deep as shared memory allows.
-  const int stage_bytes = p.stage_a_bytes + GemmSmem<BN>::kStageB;
+  p.stage_a_bytes = A_MN ? GemmSmem<BN>::kStageA : (p.a_box_rows * BK * 2 + 1023) / 1024 * 1024;   // per k slab
+  // k slabs per ring stage.  Few rows (decode): the tile is paced by the per-stage waits and issues
+  // of its producer and MMA warps, so a stage carries 128 k; full tiles are bound by the tensor
+  // pipe and keep one slab per stage.
+  p.kslabs = 1;
+  if (!A_MN && !B_MN && p.M < BM && p.K % BK == 0) {
+    int want = g_small_m_kslabs > 0 ? g_small_m_kslabs : 2;
+    while (want > 1 && (p.kb_per_chunk % want != 0 || p.kb_per_chunk / want < 2)) want >>= 1;
+    p.kslabs = want;
+  }
+  const int stage_bytes = p.kslabs * (p.stage_a_bytes + GemmSmem<BN>::kStageB);
   const int slack = GemmSmem<BN>::kStageA - p.stage_a_bytes;   // reads past the last stage stay in bounds
-  // Ring depth.  Small M (short A box): measured on a 64-row decode step inside a CUDA graph, two
-  // CTAs per SM with four stages each beat one CTA with 8 to 16 stages (1.066 against 1.10 ms for
-  // four layers), and so did they beat three CTAs, or stages of several k blocks per barrier pair:
-  // the second CTA streams while the first is between tiles.
+  // Ring depth.  Full tiles: the per-width default.  Few rows (measured at 64 rows, K = 4096 and
+  // 12288, L2 flushed): when one wave of CTAs covers all tiles (QKV, gate/up) one CTA per SM with a
+  // deep ring is fastest (N = 6144: 21.5 us with 6 stages of 128 k against 29.7 us with 4 stages of
+  // 64 k); with several short tiles per SM (the chunked row-parallel projections) two CTAs per SM
+  // with 3 stages each, so that one CTA issues while the other is between tiles.
   p.stages = GemmSmem<BN>::kStages;
   if (!A_MN && p.M < BM) {
-    p.stages = 4;
+    const long long n_tiles_all = static_cast<long long>((p.N + BN - 1) / BN) * (p.split_chunks < 1 ? 1 : p.split_chunks);
+    const bool one_wave = n_tiles_all <= sm_count();
+    p.stages = g_small_m_stages > 0 ? g_small_m_stages : (p.kslabs > 1 ? (one_wave ? 6 : 3) : 4);
     const int fit = (GemmSmem<BN>::kBytes - 1024 - GemmSmem<BN>::kBarBytes - slack) / stage_bytes;
     if (p.stages > fit) p.stages = fit;
   }
@@ -716,10 +782,13 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
     p.tree_l0_smem = 1;
     smem_bytes = p.stages * stage_bytes + 1024 + GemmSmem<BN>::kBarBytes + slack + BM * kTreeL0Pitch;
   }
-  if (!A_MN) rc = make_tmap_2d_sw128(&tmA, A, p.M, p.K, lda, p.a_box_rows, 64, 2);
+  // (with several slabs per stage a K-major operand [rows, K] is addressed as [K / 64][rows][64])
+  if (!A_MN && p.kslabs > 1) rc = make_tmap_3d_sw128_box(&tmA, A, p.K / BK, p.M, 64, lda, 64, p.kslabs, p.a_box_rows, 64, 2);
+  else if (!A_MN) rc = make_tmap_2d_sw128(&tmA, A, p.M, p.K, lda, p.a_box_rows, 64, 2);
   else rc = make_tmap_2d_sw128(&tmA, A, p.K, p.M, lda, BK, 64, 2);
   if (rc) return rc;
   if (BN == 192 && p.act_blk > 0) rc = make_tmap_2d_sw128(&tmB, B, p.N, p.K, ldb, 96, 64, 2);
+  else if (!B_MN && p.kslabs > 1) rc = make_tmap_3d_sw128_box(&tmB, B, p.K / BK, p.N, 64, ldb, 64, p.kslabs, BN, 64, 2);
   else if (!B_MN) rc = make_tmap_2d_sw128(&tmB, B, p.N, p.K, ldb, BN, 64, 2);
   else rc = make_tmap_2d_sw128(&tmB, B, p.K, p.N, ldb, BK, 64, 2);
   if (rc) return rc;
@@ -731,7 +800,11 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   const int tmem_fit = 512 / ((BN == 128 || BN == 192) ? 512 : (2 * BN < 32 ? 32 : 2 * BN));   // tensor memory columns
   if (ctas_per_sm > tmem_fit) ctas_per_sm = tmem_fit;
   if (ctas_per_sm > 2) ctas_per_sm = 2;
+  if (!A_MN && p.M < BM && g_small_m_ctas > 0 && ctas_per_sm > g_small_m_ctas) ctas_per_sm = g_small_m_ctas;
   if (ctas_per_sm < 1) ctas_per_sm = 1;
+#ifdef RLK_GEMM_TRACE
+  p.trace = g_trace_ptr;
+#endif
   const int grid = tiles < sm_count() * ctas_per_sm ? tiles : sm_count() * ctas_per_sm;
   auto kfn = det_gemm_kernel<BN, A_MN, B_MN>;
   static bool attr_set[64] = {false};
@@ -775,6 +848,23 @@ chunk_tree_kernel(const __nv_bfloat16* __restrict__ leaves, long long chunk_stri
 }
 
 }  // namespace rlk
+
+// Benchmark knob: ring depth and CTAs per SM of the launches with fewer than 128 rows (0 = built-in).
+RLK_API int rlk_gemm_small_m_tuning(int stages, int ctas_per_sm) {
+  RLK_REQUIRE(stages >= 0 && stages <= rlk::kMaxStages && ctas_per_sm >= 0 && ctas_per_sm <= 2, "gemm tuning out of range");
+  rlk::g_small_m_stages = stages;
+  rlk::g_small_m_ctas = ctas_per_sm;
+  return RLK_OK;
+}
+// Benchmark knob: 64-wide k blocks per ring stage of those launches (1, 2 or 4; 0 = built-in).
+RLK_API int rlk_gemm_small_m_kslabs(int kslabs) {
+  RLK_REQUIRE(kslabs == 0 || kslabs == 1 || kslabs == 2 || kslabs == 4, "kslabs must be 0, 1, 2 or 4");
+  rlk::g_small_m_kslabs = kslabs;
+  return RLK_OK;
+}
+#ifdef RLK_GEMM_TRACE
+RLK_API int rlk_gemm_set_trace(void* ptr) { rlk::g_trace_ptr = static_cast<long long*>(ptr); return RLK_OK; }
+#endif
 
 // Per-device scratch of the tile_n 256 chunk tree: one stack of 3 levels per CTA of a full grid.
 static uint4* tree_scratch_for_device() {

@@ -98,6 +98,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Warp-collective form for a converged warp whose lanes all walk the same loop (the loop state then
+// stays warp-uniform and one elected lane issues the TMA / MMA instructions): every lane polls, and
+// the vote makes the outcome -- in particular a timeout -- the same in all lanes, so the warp never
+// reaches a later warp-wide instruction with part of its lanes gone.
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int code) {
+  const bool ok = mbar_wait(bar, parity, abort_flag, status, code);
+  return __all_sync(0xffffffffu, ok);
+}
+
 // ----------------------------------------------------------------------------------- fences
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -82,17 +82,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int total = *p.n_tiles;
   const uint32_t smem_base = smem_u32(smem);
 
+  // Producer and MMA warps: all 32 lanes walk the loops (warp-uniform state), one elected lane
+  // issues, waits are warp votes.
   if (warp == 0) {
-    if (lane == 0) {
+    {
       uint32_t it = 0;
       for (int t = blockIdx.x; t < total; t += gridDim.x) {
         const GroupTile g = p.tiles[t];
         for (int kb = 0; kb < g.kblocks; ++kb, ++it) {
           const uint32_t s = it % kGStages, ph = (it / kGStages) & 1;
-          if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 401)) break;
+          if (!mbar_wait_warp(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, 401)) break;
           const uint32_t fb = full0 + 8 * s;
-          mbar_expect_tx(fb, kGStage);
           const uint32_t sa = smem_base + s * kGStage, sb = sa + kGStageA;
+          if (!elect_one()) continue;
+          mbar_expect_tx(fb, kGStage);
           if (!A_MN) {
             tma_load_2d(sa, &tmA, g.ka0 + kb * GBK, g.a_m0, fb);
           } else {
@@ -110,20 +113,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    {
       constexpr uint32_t idesc = umma_idesc_bf16(GBM, GBN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t it = 0, u = 0;
       for (int t = blockIdx.x; t < total && !*abort_flag; t += gridDim.x, ++u) {
         const int kblocks = p.tiles[t].kblocks;
         const uint32_t a = u & 1;
-        if (!mbar_wait(acce0 + 8 * a, ((u >> 1) & 1) ^ 1, abort_flag, p.status, 402)) break;
+        if (!mbar_wait_warp(acce0 + 8 * a, ((u >> 1) & 1) ^ 1, abort_flag, p.status, 402)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + a * GBN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t s = it % kGStages, ph = (it / kGStages) & 1;
-          if (!mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, 403)) break;
+          if (!mbar_wait_warp(full0 + 8 * s, ph, abort_flag, p.status, 403)) break;
           tc_fence_after();
           const uint32_t sa = smem_base + s * kGStage, sb = sa + kGStageA;
+          if (!elect_one()) continue;
 #pragma unroll
           for (int k = 0; k < GBK / 16; ++k) {
             const uint64_t da = A_MN ? umma_desc_sw128(sa + k * 2048, 8192, 1024)
@@ -134,7 +138,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
           umma_commit(empty0 + 8 * s);
         }
-        umma_commit(accf0 + 8 * a);
+        if (elect_one()) umma_commit(accf0 + 8 * a);
       }
     }
   } else {

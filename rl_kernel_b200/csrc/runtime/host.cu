@@ -114,7 +114,7 @@ int make_tmap_3d_sw128_box(CUtensorMap* out, const void* base, uint64_t batch, u
   cuuint64_t dims[3] = {cols, rows, batch};
   cuuint64_t strides[2] = {row_stride_elems * static_cast<uint64_t>(elem_bytes),
                            batch_stride_elems * static_cast<uint64_t>(elem_bytes)};
-  RLK_REQUIRE(box_batch >= 1 && box_rows >= 1 && box_batch * box_rows <= 256, "TMA box out of range");
+  RLK_REQUIRE(box_batch >= 1 && box_batch <= 256 && box_rows >= 1 && box_rows <= 256, "TMA box out of range");
   cuuint32_t box[3] = {box_cols, box_rows, box_batch};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = fn(out, dtype_for(elem_bytes), 3, const_cast<void*>(base), dims, strides, box, estr,
