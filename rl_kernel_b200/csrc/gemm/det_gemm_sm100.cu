@@ -50,6 +50,8 @@ struct GemmParams {
   int a_box_rows;           // rows of A that TMA brings per tile (128, or fewer when M < 128)
   int stage_a_bytes;        // shared-memory bytes reserved for the A tile of one stage
   int stages;               // depth of the shared-memory ring
+  int tma_store;            // 1: plain bf16 tiles of 128+ columns leave through shared memory and TMA stores
+                            //    (two 128 x 64 staging slabs behind the barriers, one per set of epilogue warps)
   int kslabs;               // 64-wide k blocks per ring stage (1, 2 or 4).  More than one: both operands are
                             //   K-major and a stage is brought by ONE 3-D TMA box per operand ([slab][row][64]),
                             //   so the two single-lane roles pay their per-stage waits once per 128 or 256 k
@@ -151,7 +153,7 @@ __device__ __forceinline__ int act_gate_row(int nt, int act_blk) {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(gemm_threads<BN>(), 1)
 det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
   using S = GemmSmem<BN>;
   const uint32_t kStages = static_cast<uint32_t>(p.stages);   // ring depth chosen by the host (<= kMaxStages)
   // TMEM columns: two accumulators (+ three packed-bf16 tree levels when chunked, BN==128 only)
@@ -544,6 +546,46 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
               }
             }
           }
+        } else if ((BN == 128 || BN == 256) && p.tma_store) {
+          // Plain bf16 tile: accumulator -> registers -> swizzled staging slab -> one TMA store per
+          // 128 x 64 block.  (Row-per-thread global stores, 16 bytes each to 32 different rows per
+          // instruction, fill the SM's memory-instruction queue and hold up the MMA warp's issue for
+          // the length of the epilogue: measured 596 against 519 cycles per k block at 128 x 256.)
+          // Each set of four epilogue warps owns one slab and a named barrier of its 128 threads.
+          uint8_t* slab = smem + kStages * stage_bytes + 1024 + half * (BM * 128);
+          const uint32_t slab_u32 = smem_u32(slab);
+          const bool store_leader = (warp == 2 + 4 * half) && lane == 0;
+          const int bar_id = 3 + half;
+#pragma unroll 1
+          for (int g0 = 0; g0 < kColsPerWarp; g0 += 64) {
+            const int col0 = half * kColsPerWarp + g0;
+            uint32_t r0[32], r1[32];
+            tmem_ld32(tmem_base + lane_off + a * kAcc + col0, r0);
+            tmem_ld32(tmem_base + lane_off + a * kAcc + col0 + 32, r1);
+            if (store_leader) tma_store_wait_read();          // the slab's previous store has been read out
+            tmem_ld_wait();
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r0[8 * q]), __uint_as_float(r0[8 * q + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r0[8 * q + 2]), __uint_as_float(r0[8 * q + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r0[8 * q + 4]), __uint_as_float(r0[8 * q + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r0[8 * q + 6]), __uint_as_float(r0[8 * q + 7]));
+              *reinterpret_cast<uint4*>(slab + sw128_offset(row_in_tile, q)) = v;
+              v.x = pack_bf16x2(__uint_as_float(r1[8 * q]), __uint_as_float(r1[8 * q + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r1[8 * q + 2]), __uint_as_float(r1[8 * q + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r1[8 * q + 4]), __uint_as_float(r1[8 * q + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r1[8 * q + 6]), __uint_as_float(r1[8 * q + 7]));
+              *reinterpret_cast<uint4*>(slab + sw128_offset(row_in_tile, 4 + q)) = v;
+            }
+            fence_proxy_async_smem();                          // generic-proxy writes -> the TMA store's reads
+            asm volatile("bar.sync %0, 128;" ::"r"(bar_id) : "memory");
+            if (store_leader && n0 + col0 < p.N) {
+              tma_store_2d(&tmC, slab_u32, n0 + col0, mt * BM);
+              tma_store_commit();
+            }
+          }
         } else
 #pragma unroll 1
         for (int col0 = half * kColsPerWarp; col0 < (half + 1) * kColsPerWarp; col0 += 32) {
@@ -720,6 +762,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         }
       }
     }
+    if ((BN == 128 || BN == 256) && p.tma_store && lane == 0 && (warp == 2 || warp == 6)) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -732,6 +775,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
 
 // Ring depth / CTAs per SM of the small-M (decode) launches; 0 = the built-in choice.
 static int g_small_m_stages = 0, g_small_m_ctas = 0, g_small_m_kslabs = 0;
+static int g_tma_store = 1;
 #ifdef RLK_GEMM_TRACE
 static long long* g_trace_ptr = nullptr;
 #endif
@@ -775,6 +819,13 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
     if (p.stages > fit) p.stages = fit;
   }
   int smem_bytes = p.stages * stage_bytes + 1024 + GemmSmem<BN>::kBarBytes + slack;
+  // plain bf16 tiles of full-size launches leave through staging slabs and TMA stores
+  p.tma_store = ((BN == 128 || BN == 256) && p.M >= BM && p.nchunks == 1 && p.split_chunks == 1 && !p.out_fp32 && !p.accumulate &&
+                 p.stats == nullptr && p.act_blk == 0 && p.ar_world <= 1 && p.C != nullptr && g_tma_store) ? 1 : 0;
+  if (p.tma_store) {
+    smem_bytes = p.stages * stage_bytes + 1024 + 1024 + 2 * BM * 128;      // ring, alignment, barriers, two slabs
+    if (smem_bytes > GemmSmem<BN>::kBytes) p.tma_store = 0, smem_bytes = p.stages * stage_bytes + 1024 + GemmSmem<BN>::kBarBytes + slack;
+  }
   p.tree_l0_smem = 0;
   if (BN == 256 && p.nchunks > 1 && p.tree_scratch != nullptr) {
     // three stages instead of four; the freed space holds level 0 of the tree stack
@@ -792,6 +843,11 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   else if (!B_MN) rc = make_tmap_2d_sw128(&tmB, B, p.N, p.K, ldb, BN, 64, 2);
   else rc = make_tmap_2d_sw128(&tmB, B, p.K, p.N, ldb, BK, 64, 2);
   if (rc) return rc;
+  CUtensorMap tmC = tmA;                                  // placeholder when the tile is stored directly
+  if (p.tma_store) {
+    rc = make_tmap_2d_sw128(&tmC, p.C, p.M, p.N, p.ldc, BM, 64, 2);
+    if (rc) return rc;
+  }
   p.m_tiles = (p.M + BM - 1) / BM;
   p.n_tiles = (p.N + BN - 1) / BN;
   if (BN == 192 && p.act_blk > 0) p.n_tiles = p.act_I / 96;
@@ -819,7 +875,7 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
       attr_set[dev & 63] = true;
     }
   }
-  RLK_CHECK_CUDA(launch_pdl(kfn, dim3(grid), dim3(gemm_threads<BN>()), smem_bytes, stream, tmA, tmB, p));
+  RLK_CHECK_CUDA(launch_pdl(kfn, dim3(grid), dim3(gemm_threads<BN>()), smem_bytes, stream, tmA, tmB, tmC, p));
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;
 }
@@ -855,6 +911,12 @@ RLK_API int rlk_gemm_small_m_tuning(int stages, int ctas_per_sm) {
   rlk::g_small_m_stages = stages;
   rlk::g_small_m_ctas = ctas_per_sm;
   return RLK_OK;
+}
+// Benchmark knob: 1 = full-size plain bf16 tiles leave through TMA stores (default), 0 = direct stores.
+RLK_API int rlk_gemm_tma_store(int on) {
+  const int old = rlk::g_tma_store;
+  rlk::g_tma_store = on ? 1 : 0;
+  return old;
 }
 // Benchmark knob: 64-wide k blocks per ring stage of those launches (1, 2 or 4; 0 = built-in).
 RLK_API int rlk_gemm_small_m_kslabs(int kslabs) {
