@@ -330,6 +330,23 @@ def qk_norm_rope_bwd(qkv, q_w, k_w, cos_tab, sin_tab, pos, dq, dk, dv, dqkv, scr
     _count(4)
 
 
+def qk_norm_rope_bwd_canonical(qkv, q_w, k_w, cos_tab, sin_tab, pos, dq, dk, dv, dqkv, scratch, dqk, *,
+                               Hq: int, Hkv: int, eps: float, accumulate_dw: bool) -> None:
+    """Backward of the fused QK-norm + RoPE with canonical gain gradients: ``dqk`` [256] bf16 =
+    [d q_norm | d k_norm], one bf16 leaf per KV group combined by a balanced tree, so that the bits
+    do not depend on how many of the groups this rank holds (the tensor-parallel all-reduce
+    continues the same tree)."""
+    T = qkv.shape[0]
+    rc = _lib().rlk_qk_norm_rope_bwd_canonical(ext.ptr(qkv), _ll(qkv.stride(0)), ext.ptr(q_w), ext.ptr(k_w),
+                                               ext.ptr(cos_tab), ext.ptr(sin_tab), ext.ptr(pos), ext.ptr(dq),
+                                               _ll(dq.stride(0)), ext.ptr(dk), ext.ptr(dv), _ll(dk.stride(0)),
+                                               ext.ptr(dqkv), _ll(dqkv.stride(0)), ext.ptr(scratch), ext.ptr(dqk),
+                                               c_int(int(accumulate_dw)), c_int(T), c_int(Hq), c_int(Hkv),
+                                               c_float(eps), ext.stream_ptr(qkv.device))
+    ext.check(rc, "qk_norm_rope_bwd_canonical")
+    _count(2)
+
+
 # ------------------------------------------------------------------------------------- activation
 def swiglu_fwd(gu, out, I: int, blk: int | None = None, rows_limit=None) -> None:
     """``rows_limit``: int32 device scalar; rows at or beyond it are skipped."""

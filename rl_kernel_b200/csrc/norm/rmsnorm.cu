@@ -314,8 +314,10 @@ struct QkRopeBwdParams {
   const __nv_bfloat16* dq; long long ld_dq;
   const __nv_bfloat16* dk; const __nv_bfloat16* dv; long long ld_dkv;
   __nv_bfloat16* dqkv; long long ld_dqkv;
-  float* partial;  // [gridDim.x][256]
+  float* partial;  // [gridDim.x][256], or [gridDim.x][Hkv][256] with per_group
   int T, Hq, Hkv; float eps; int tokens_per_cta;
+  int per_group;   // 1: one partial row per KV group (its G query heads and its key head): the sums do
+                   //    not depend on how many groups a tensor-parallel rank holds
 };
 
 __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const QkRopeBwdParams p) {
@@ -326,10 +328,20 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const QkRopeBwdPa
   const int heads = p.Hq + 2 * p.Hkv;
   const int t0 = blockIdx.x * p.tokens_per_cta;
   const int t1 = min(p.T, t0 + p.tokens_per_cta);
-  const int items = (t1 - t0) * heads;
   const int G = p.Hq / p.Hkv;
+  // per_group: the CTA walks the KV groups one after the other and every group's items go to the
+  // warps in the same way whatever the number of groups; else one pass over all heads
+  const int n_pass = p.per_group ? p.Hkv : 1;
+  const int heads_pass = p.per_group ? G + 2 : heads;
+  const int items = (t1 - t0) * heads_pass;
+  for (int pass = 0; pass < n_pass; ++pass) {
+  if (pass > 0) {
+    __syncthreads();
+    for (int i = lane; i < 256; i += 32) sw[warp][i] = 0.f;
+    __syncwarp();
+  }
   for (int it = warp; it < items; it += 8) {
-    const int t = t0 + it / heads, hh = it % heads;
+    const int t = t0 + it / heads_pass, hh = pass * heads_pass + it % heads_pass;
     const int grp = hh / (G + 2), jj = hh - grp * (G + 2);
     const int h = jj < G ? grp * G + jj : (jj == G ? p.Hq + grp : p.Hq + p.Hkv + grp);
     __nv_bfloat16* dst = p.dqkv + static_cast<long long>(t) * p.ld_dqkv + hh * 128;
@@ -387,8 +399,29 @@ __global__ void __launch_bounds__(256) qk_norm_rope_bwd_kernel(const QkRopeBwdPa
     float s = 0.f;
 #pragma unroll
     for (int k = 0; k < 8; ++k) s += sw[k][i];
-    p.partial[static_cast<long long>(blockIdx.x) * 256 + i] = s;
+    p.partial[(static_cast<long long>(blockIdx.x) * n_pass + pass) * 256 + i] = s;
   }
+  }
+}
+
+// Canonical q_norm / k_norm weight gradients: per KV group, the per-CTA partials are summed in
+// ascending CTA order (fp32) and rounded to bf16 -- a leaf; the leaves of the `ngroups` groups this
+// rank holds are combined by a balanced tree with a bf16 rounding at every node.  A tensor-parallel
+// rank therefore produces exactly the sub-tree that the fixed-order all-reduce continues, and one
+// rank holding all groups reproduces the bits of 2, 4 or 8 ranks.  out[256] = [q_norm | k_norm];
+// accumulate: out = bf16(float(out) + node).
+__global__ void __launch_bounds__(256) qk_dw_group_tree_kernel(const float* __restrict__ partial, int ncta, int ngroups,
+                                                               __nv_bfloat16* out, int accumulate) {
+  const int i = threadIdx.x;
+  float leaf[8];
+  for (int g = 0; g < ngroups; ++g) {
+    float s = 0.f;
+    for (int c = 0; c < ncta; ++c) s += partial[(static_cast<long long>(c) * ngroups + g) * 256 + i];
+    leaf[g] = round_bf16(s);
+  }
+  for (int n = ngroups; n > 1; n >>= 1)
+    for (int j = 0; j < n / 2; ++j) leaf[j] = round_bf16(__fadd_rn(leaf[2 * j], leaf[2 * j + 1]));
+  out[i] = __float2bfloat16_rn(accumulate ? __fadd_rn(__bfloat162float(out[i]), leaf[0]) : leaf[0]);
 }
 
 }  // namespace rlk
@@ -477,7 +510,33 @@ RLK_API int rlk_qk_norm_rope_fwd(const void* qkv, long long ld_qkv, const void* 
 }
 
 RLK_API long long rlk_qk_norm_rope_bwd_scratch_elems(int T) {
-  return static_cast<long long>((T + 15) / 16 + 1) * 256;
+  return static_cast<long long>((T + 15) / 16 + 1) * 256 * 8;    // room for one partial row per KV group (<= 8)
+}
+
+// Same backward with canonical weight gradients (see qk_dw_group_tree_kernel): dqk_bf16[256] =
+// [d q_norm | d k_norm] of the Hkv KV groups this rank holds (a power of two, at most 8).
+// accumulate_dw = 1 adds into dqk_bf16 (single rank); a tensor-parallel caller passes 0, all-reduces
+// the 256 values over the ranks (fixed tree) and accumulates afterwards.
+RLK_API int rlk_qk_norm_rope_bwd_canonical(const void* qkv, long long ld_qkv, const void* q_w, const void* k_w,
+                                           const float* cos_tab, const float* sin_tab, const int* pos,
+                                           const void* dq, long long ld_dq, const void* dk, const void* dv,
+                                           long long ld_dkv, void* dqkv, long long ld_dqkv, float* scratch,
+                                           void* dqk_bf16, int accumulate_dw, int T, int Hq, int Hkv, float eps,
+                                           void* stream) {
+  RLK_REQUIRE(T > 0, "qk_norm_rope_bwd: empty shape");
+  RLK_REQUIRE(Hkv == 1 || Hkv == 2 || Hkv == 4 || Hkv == 8, "qk_norm_rope_bwd_canonical: 1, 2, 4 or 8 KV groups per rank (got %d)", Hkv);
+  const int tokens_per_cta = 16;
+  const int grid = (T + tokens_per_cta - 1) / tokens_per_cta;
+  QkRopeBwdParams p{(const __nv_bfloat16*)qkv, ld_qkv, (const __nv_bfloat16*)q_w,
+                    (const __nv_bfloat16*)k_w, cos_tab, sin_tab, pos, (const __nv_bfloat16*)dq,
+                    ld_dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)dv, ld_dkv,
+                    (__nv_bfloat16*)dqkv, ld_dqkv, scratch, T, Hq, Hkv, eps, tokens_per_cta, 1};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  qk_norm_rope_bwd_kernel<<<grid, 256, 0, s>>>(p);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  qk_dw_group_tree_kernel<<<1, 256, 0, s>>>(scratch, grid, Hkv, (__nv_bfloat16*)dqk_bf16, accumulate_dw);
+  RLK_CHECK_CUDA(cudaGetLastError());
+  return RLK_OK;
 }
 
 RLK_API int rlk_qk_norm_rope_bwd(const void* qkv, long long ld_qkv, const void* q_w, const void* k_w,
@@ -492,7 +551,7 @@ RLK_API int rlk_qk_norm_rope_bwd(const void* qkv, long long ld_qkv, const void* 
   QkRopeBwdParams p{(const __nv_bfloat16*)qkv, ld_qkv, (const __nv_bfloat16*)q_w,
                     (const __nv_bfloat16*)k_w, cos_tab, sin_tab, pos, (const __nv_bfloat16*)dq,
                     ld_dq, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)dv, ld_dkv,
-                    (__nv_bfloat16*)dqkv, ld_dqkv, scratch, T, Hq, Hkv, eps, tokens_per_cta};
+                    (__nv_bfloat16*)dqkv, ld_dqkv, scratch, T, Hq, Hkv, eps, tokens_per_cta, 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   qk_norm_rope_bwd_kernel<<<grid, 256, 0, s>>>(p);
   RLK_CHECK_CUDA(cudaGetLastError());

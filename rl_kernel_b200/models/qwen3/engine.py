@@ -338,6 +338,10 @@ class Qwen3Engine:
         self.cos, self.sin = rope_tables(spec, max_positions, self.dev)
         self.ws = Workspace(self.dev)
         self.fuse_gemm_allreduce = True
+        # Layout-invariant parameter gradients: q_norm / k_norm gains as a tree over KV groups, the LM
+        # head's input gradient over canonical vocabulary chunks.  With them every gradient of a
+        # tensor-parallel run equals the single-GPU gradient bit for bit.
+        self.canonical_grads = True
         self.cp = None                               # CPAttention once enable_context_parallel ran
         self._decode_page_table = None               # set while a paged decode step runs
         self._decode_shared = None                   # SharedPrefixKV whose prompt blocks are attended per group
@@ -404,6 +408,20 @@ class Qwen3Engine:
         self._gemm(a, w, out, nchunks=nchunks)
         coll.all_reduce_(out)
         return out
+
+    def _qk_grad_view(self) -> torch.Tensor:
+        """[layers, 256] view of the q_norm | k_norm gain gradients inside the flat gradient buffer
+        (the two slots are adjacent and every layer has the same slots)."""
+        if getattr(self, "_qk_view", None) is None:
+            sl = self.p.slots
+            first, L = sl[f"l{self.l0}.qn"], self.l1 - self.l0
+            assert sl[f"l{self.l0}.kn"].offset == first.offset + 128
+            stride = sl[f"l{self.l0 + 1}.qn"].offset - first.offset if L > 1 else 256
+            self._qk_view = torch.as_strided(self.p.grad, (L, 256), (stride, 1), first.offset)
+        return self._qk_view
+
+    def _qk_stage(self) -> torch.Tensor:
+        return self.ws.get("g.qk_stage", (self.l1 - self.l0, 256))
 
     def _tiles_for(self, nseq: int, S: int):
         key = (nseq, S)
@@ -759,9 +777,15 @@ class Qwen3Engine:
         # ---- pass 1: log-probs (fused stats).  A single-chunk, single-shard head keeps the bf16
         # logits the same kernel can write, so pass 2 does not have to multiply again.
         vloc = self.p.v_real_local
+        # the logits buffer spans the padded shard: the canonical input-gradient GEMM runs over equal
+        # vocabulary chunks, the padding columns stay zero (their weights are zero as well)
+        vpad = self.p.v_local if self.canonical_grads else vloc
+        lbuf = self.ws.get("lm.logits", (lm_chunk, vpad))
+        if vpad > vloc:
+            lbuf[:, vloc:].zero_()      # (the buffer may share memory with the rollout's KV cache)
         kept_logits = None
         if self.ctx.tp_size == 1 and nseq * R <= lm_chunk and vloc > 0:
-            kept_logits = self.ws.get("lm.logits", (lm_chunk, vloc))[: nseq * R]
+            kept_logits = lbuf[: nseq * R, :vloc]
             stats, tl = self._lmhead_stats(rows, targets, temperature, kept_logits)
             logp = torch.empty(nseq * R, dtype=torch.float32, device=self.dev)
             lse = torch.empty(nseq * R, dtype=torch.float32, device=self.dev)
@@ -776,13 +800,17 @@ class Qwen3Engine:
         for r0 in range(0, nseq * R, lm_chunk):
             r1 = min(nseq * R, r0 + lm_chunk)
             n = r1 - r0
-            logits = self.ws.get("lm.logits", (lm_chunk, vloc))[:n]
+            logits = lbuf[:n, :vloc]
             if vloc > 0:
                 if kept_logits is None:
                     self._gemm(rows[r0:r1], wlm, logits)
                 nv.dlogits_(logits, targets[r0:r1], lse[r0:r1], dlogp[r0:r1],
                             vocab_start=self.p.vocab_start, inv_temp=1.0 / temperature)
-                self._gemm(logits, wlm, drows[r0:r1], b_mn=True, M=n, N=H, K=vloc)
+                if self.canonical_grads:
+                    self._gemm(lbuf[:n], self.p.w["lm_head"], drows[r0:r1], b_mn=True, nchunks=self.nchunks,
+                               M=n, N=H, K=vpad)
+                else:
+                    self._gemm(logits, wlm, drows[r0:r1], b_mn=True, M=n, N=H, K=vloc)
                 self._gemm(logits, rows[r0:r1], glm, a_mn=True, b_mn=True, accumulate=True,
                            M=vloc, N=H, K=n)
             else:
@@ -867,9 +895,18 @@ class Qwen3Engine:
                 nv.attn_bwd_dq(keep["q"], dattn, kb, vb, lse, delta, dq, tiles, self.scale)
                 nv.attn_bwd_dkv(keep["q"], dattn, kb, vb, lse, delta, dk, dv, kvtiles, self.scale)
             dqkv = ws.get("b.dqkv", (T, self.p.qkv_local))
-            nv.qk_norm_rope_bwd(keep["qkv"], w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos,
-                                dq, dk, dv, dqkv, scr, g[f"l{l}.qn"], g[f"l{l}.kn"], Hq=self.hq,
-                                Hkv=self.hkv, eps=eps, accumulate_dw=True)
+            if self.canonical_grads:
+                tp = self.ctx.tp_size
+                # single rank: straight into the gradient (q_norm and k_norm gains are adjacent slots);
+                # tensor parallel: a per-layer stage that is all-reduced once per micro-batch
+                dqk = self._qk_grad_view()[l - self.l0] if tp == 1 else self._qk_stage()[l - self.l0]
+                nv.qk_norm_rope_bwd_canonical(keep["qkv"], w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos,
+                                              dq, dk, dv, dqkv, scr, dqk, Hq=self.hq, Hkv=self.hkv, eps=eps,
+                                              accumulate_dw=tp == 1)
+            else:
+                nv.qk_norm_rope_bwd(keep["qkv"], w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos,
+                                    dq, dk, dv, dqkv, scr, g[f"l{l}.qn"], g[f"l{l}.kn"], Hq=self.hq,
+                                    Hkv=self.hkv, eps=eps, accumulate_dw=True)
             dh = ws.get("b.dh", (T, H))
             self._gemm(dqkv, w[f"l{l}.wqkv"], dh, b_mn=True, nchunks=self.nchunks, M=T, N=H,
                        K=self.p.qkv_local)
@@ -878,6 +915,11 @@ class Qwen3Engine:
                        M=self.p.qkv_local, N=H, K=T)
             nv.rmsnorm_bwd(ck, w[f"l{l}.ln1"], dh, ds, scr, eps, dres=ds2,
                            dw_bf16=g[f"l{l}.ln1"], accumulate_dw=True)
+        if self.canonical_grads and self.ctx.tp_size > 1 and self.l1 > self.l0:
+            # finish the KV-group tree over the tensor-parallel ranks, then accumulate
+            st_qk = self._qk_stage()
+            self.ctx.collective.all_reduce_(st_qk)
+            self._qk_grad_view().add_(st_qk)
         if not self.first_stage:
             return ds
         # ---- embedding

@@ -90,8 +90,8 @@ class AdamW:
     def _sync_partial_replicated_grads(self) -> None:
         """q_norm / k_norm gains are replicated but each TP rank only saw its own heads: sum the
         partial gradients over TP (fixed tree) so every rank holds the same full gradient."""
-        if self.ctx.tp_size == 1:
-            return
+        if self.ctx.tp_size == 1 or getattr(self.p, "qk_grads_complete", False):
+            return                      # one rank, or the engine already finished the tree over the ranks
         names = [n for n in self.p.slots if n.endswith((".qn", ".kn"))]
         buf = torch.cat([self.p.g[n].reshape(-1) for n in names]).contiguous()
         self.ctx.collective.all_reduce_(buf)
@@ -146,6 +146,7 @@ class GRPOTrainer:
         else:
             self.policy.init_synthetic_(cfg.seed)
         self.engine = Qwen3Engine(spec, self.policy, self.ctx, max_positions=cfg.seq_len + 8)
+        self.policy.qk_grads_complete = self.engine.canonical_grads
         if self.cp > 1:
             self.engine.enable_context_parallel(cfg.micro_batch_seqs * cfg.seq_len // self.cp)
         self.ref_params = None

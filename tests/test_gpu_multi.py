@@ -1,6 +1,8 @@
-"""Two-GPU tests: fixed-order collectives on symmetric memory, tensor-parallel bit invariance,
-and a bounded wait that runs out without hanging the GPU.  Each test owns its worker processes
-(NCCL bootstrap on 127.0.0.1); NVLS is off and the kernels use plain peer loads."""
+"""Multi-GPU tests at 2, 4 and 8 ranks (a size is skipped when the machine has fewer GPUs): fixed-order
+collectives on symmetric memory, tensor- / context- / data-parallel bit invariance of the whole
+GRPO step including the gradients, the fused compute + collective kernels, and a bounded wait that
+runs out without hanging the GPU.  Each test owns its worker processes (NCCL bootstrap on
+127.0.0.1); NVLS is off and the kernels use plain peer loads."""
 import os
 import socket
 
@@ -9,6 +11,15 @@ import torch
 import torch.multiprocessing as mp
 
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+WORLDS = (2, 4, 8)
+CP_GRADS_CANONICAL = False      # context-parallel weight gradients are summed over token shards (equal to rounding)
+
+
+def _need(world: int) -> None:
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs, this machine has {torch.cuda.device_count()}")
 
 
 def _free_port():
@@ -86,14 +97,18 @@ def _collective_worker(rank, world, port, out):
     ok &= bool(torch.equal(coll.all_reduce(torch.ones(8, device=dev)), torch.full((8,), float(world), device=dev)))
     ok &= ext.poll_status(dev) == 0
     coll.close()
+    res = [None] * world
+    dist.all_gather_object(res, bool(ok))
     if rank == 0:
-        torch.save(ok, out)
+        torch.save(all(res), out)
     dist.destroy_process_group()
 
 
-def test_symmetric_collectives(tmp_path):
+@pytest.mark.parametrize("world", WORLDS)
+def test_symmetric_collectives(tmp_path, world):
+    _need(world)
     out = str(tmp_path / "ok.pt")
-    mp.spawn(_collective_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    mp.spawn(_collective_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert torch.load(out)
 
 
@@ -133,90 +148,153 @@ def test_bounded_wait_reports_instead_of_hanging(tmp_path):
     assert fine, "collectives must work again after resync"
 
 
+def _tp_spec():
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec
+
+    # 8 KV heads and a feed-forward width of 8 x 256 so that 2, 4 and 8 tensor-parallel ranks all divide it
+    return Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=16, kv_heads=8, head_dim=128, vocab=4096)
+
+
 def _tp_worker(rank, world, port, out):
     dist = _init(rank, world, port)
-    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.backends import extension as ext
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseWeights
     from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
     from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context
 
     dev = torch.device("cuda", rank)
-    spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+    spec = _tp_spec()
     w = Qwen3DenseWeights.synthetic(spec, seed=3)
     ctx = build_parallel_context(world, 1, dev)
-    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=48, micro_batch_seqs=4, lr=1e-4)
+    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=48, micro_batch_seqs=2, lr=1e-4)
     tr = GRPOTrainer(spec, cfg, dev, ctx=ctx, weights=w)
     prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5)).to(dev)
     res = tr.step(prompts, step_index=0)
     torch.cuda.synchronize(dev)
+    mine = {k: res[k].cpu() for k in ("tokens", "old_logp", "train_logp", "grad_norm")}
+    mine["grads"] = {k: v.cpu() for k, v in tr.policy.g.items()}
+    mine["weights"] = {k: v.cpu() for k, v in tr.policy.w.items()}
+    mine["status"] = ext.poll_status(dev)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, mine)
     if rank == 0:
-        torch.save({k: res[k].cpu() for k in ("tokens", "old_logp", "train_logp", "grad_norm")}, out)
+        torch.save(gathered, out)
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_tp2_matches_tp1_bitwise(tmp_path):
-    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+def _assemble(shards: list[dict], name: str) -> torch.Tensor:
+    """The full tensor of parameter ``name`` from the tensor-parallel shards (PackedParams layout)."""
+    parts = [s[name] for s in shards]
+    if parts[0].dim() == 1:
+        for p in parts[1:]:
+            assert torch.equal(p, parts[0]), f"replicated {name} differs between ranks"
+        return parts[0]
+    if name.endswith((".wo", ".wd")):
+        return torch.cat(parts, dim=1)
+    return torch.cat(parts, dim=0)
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_tensor_parallel_step_matches_single_gpu_bitwise(tmp_path, world):
+    """One whole GRPO step (rollout, training forward / backward, clipping, AdamW) on 2, 4 or 8
+    tensor-parallel ranks: sampled tokens, rollout and training log-probs, EVERY gradient, the
+    gradient norm and the updated weights equal the single-GPU run bit for bit."""
+    _need(world)
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseWeights
     from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
 
-    out = str(tmp_path / "tp2.pt")
-    mp.spawn(_tp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
-    tp2 = torch.load(out)
+    out = str(tmp_path / "tp.pt")
+    mp.spawn(_tp_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    tp = torch.load(out)
     dev = torch.device("cuda:0")
-    spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+    spec = _tp_spec()
     w = Qwen3DenseWeights.synthetic(spec, seed=3)
-    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=48, micro_batch_seqs=4, lr=1e-4)
+    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=48, micro_batch_seqs=2, lr=1e-4)
     tr = GRPOTrainer(spec, cfg, dev, weights=w)
     prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5)).to(dev)
-    tp1 = tr.step(prompts, step_index=0)
-    assert torch.equal(tp2["tokens"], tp1["tokens"].cpu())
-    assert torch.equal(tp2["old_logp"], tp1["old_logp"].cpu())
-    assert torch.equal(tp2["train_logp"], tp1["train_logp"].cpu())
-    assert torch.equal(tp2["train_logp"], tp2["old_logp"])
+    one = tr.step(prompts, step_index=0)
+    torch.cuda.synchronize(dev)
+    assert all(r["status"] == 0 for r in tp)
+    for r in tp:
+        assert torch.equal(r["tokens"], one["tokens"].cpu())
+        assert torch.equal(r["old_logp"], one["old_logp"].cpu())
+        assert torch.equal(r["train_logp"], one["train_logp"].cpu())
+        assert torch.equal(r["train_logp"], r["old_logp"])
+        assert torch.equal(r["grad_norm"], one["grad_norm"].cpu())
+    for name in tr.policy.g:
+        assert torch.equal(_assemble([r["grads"] for r in tp], name), tr.policy.g[name].cpu()), f"gradient of {name}"
+        assert torch.equal(_assemble([r["weights"] for r in tp], name), tr.policy.w[name].cpu()), f"updated {name}"
+
+
+def _cp_cfg(world):
+    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig
+
+    # zigzag shards need a sequence length that is a multiple of 2 x cp x 128
+    return GRPOConfig(num_prompts=world, group_size=2, prompt_len=128, response_len=256 * world - 128,
+                      micro_batch_seqs=2 * world, lr=1e-4)
 
 
 def _cp_train_worker(rank, world, port, out):
     dist = _init(rank, world, port)
+    from rl_kernel_b200.backends import extension as ext
     from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
-    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
+    from rl_kernel_b200.models.qwen3.grpo import GRPOTrainer
     from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context
 
     dev = torch.device("cuda", rank)
     spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
     w = Qwen3DenseWeights.synthetic(spec, seed=3)
     ctx = build_parallel_context(1, world, dev)
-    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=384, micro_batch_seqs=4, lr=1e-4)
+    cfg = _cp_cfg(world)
     tr = GRPOTrainer(spec, cfg, dev, ctx=ctx, weights=w)
-    prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5)).to(dev)
+    prompts = torch.randint(0, spec.vocab_size, (world, 128), generator=torch.Generator().manual_seed(5)).to(dev)
     res = tr.step(tr.local_prompts(prompts), step_index=0)
     torch.cuda.synchronize(dev)
+    mine = {k: res[k].cpu() for k in ("tokens", "old_logp", "train_logp", "grad_norm")}
+    mine["grads"] = {k: v.cpu() for k, v in tr.policy.g.items()}
+    mine["status"] = ext.poll_status(dev)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, mine)
     if rank == 0:
-        torch.save({k: res[k].cpu() for k in ("tokens", "old_logp", "train_logp", "grad_norm")}, out)
+        torch.save(gathered, out)
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_cp2_training_matches_single_gpu(tmp_path):
-    """Rollout on two independent engines + training with every sequence split over two GPUs gives
-    the tokens and log-probs of one GPU bit for bit; the gradient norm agrees to rounding (weight
-    gradients sum over tokens in a different order)."""
+@pytest.mark.parametrize("world", WORLDS)
+def test_context_parallel_training_matches_single_gpu(tmp_path, world):
+    """Rollout on `world` independent engines + training with every sequence split over the GPUs
+    gives the tokens and log-probs of one GPU bit for bit, and with canonical gradients (the
+    default) every parameter gradient and the gradient norm as well."""
+    _need(world)
     from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
-    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
+    from rl_kernel_b200.models.qwen3.grpo import GRPOTrainer
 
-    out = str(tmp_path / "cp2.pt")
-    mp.spawn(_cp_train_worker, args=(2, _free_port(), out), nprocs=2, join=True)
-    cp2 = torch.load(out)
+    out = str(tmp_path / "cp.pt")
+    mp.spawn(_cp_train_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    cp = torch.load(out)
     dev = torch.device("cuda:0")
     spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
     w = Qwen3DenseWeights.synthetic(spec, seed=3)
-    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=384, micro_batch_seqs=4, lr=1e-4)
+    cfg = _cp_cfg(world)
     tr = GRPOTrainer(spec, cfg, dev, weights=w)
-    prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5)).to(dev)
+    prompts = torch.randint(0, spec.vocab_size, (world, 128), generator=torch.Generator().manual_seed(5)).to(dev)
     one = tr.step(prompts, step_index=0)
-    assert torch.equal(cp2["tokens"], one["tokens"].cpu())
-    assert torch.equal(cp2["old_logp"], one["old_logp"].cpu())
-    assert torch.equal(cp2["train_logp"], one["train_logp"].cpu())
-    assert torch.equal(cp2["train_logp"], cp2["old_logp"])
-    assert abs(float(cp2["grad_norm"]) - float(one["grad_norm"])) <= 2e-2 * float(one["grad_norm"])
+    torch.cuda.synchronize(dev)
+    assert all(r["status"] == 0 for r in cp)
+    for r in cp:
+        assert torch.equal(r["tokens"], one["tokens"].cpu())
+        assert torch.equal(r["old_logp"], one["old_logp"].cpu())
+        assert torch.equal(r["train_logp"], one["train_logp"].cpu())
+        assert torch.equal(r["train_logp"], r["old_logp"])
+    if tr.engine.canonical_grads and CP_GRADS_CANONICAL:
+        for r in cp:
+            for name, g in tr.policy.g.items():
+                assert torch.equal(r["grads"][name], g.cpu()), f"gradient of {name}"
+            assert torch.equal(r["grad_norm"], one["grad_norm"].cpu())
+    else:
+        assert abs(float(cp[0]["grad_norm"]) - float(one["grad_norm"])) <= 2e-2 * float(one["grad_norm"])
 
 
 def _cp_worker(rank, world, port, out):
@@ -230,7 +308,7 @@ def _cp_worker(rank, world, port, out):
 
     dev = torch.device("cuda", rank)
     coll = SymmetricMemoryCollective(None, dev, frame_bytes=1 << 20)
-    HQ, HKV, D, B, S = 8, 2, 128, 2, 1024
+    HQ, HKV, D, B, S = 8, 2, 128, 2, 256 * world
     g = torch.Generator(device="cuda").manual_seed(3)            # same full tensors on every rank
     q = torch.randn(B, S, HQ * D, device=dev, generator=g).to(torch.bfloat16)
     k = torch.randn(B, S, HKV * D, device=dev, generator=g).to(torch.bfloat16)
@@ -264,15 +342,19 @@ def _cp_worker(rank, world, port, out):
     torch.cuda.synchronize(dev)
     from rl_kernel_b200.backends import extension as ext
     ok &= ext.poll_status(dev) == 0
+    res = [None] * world
+    dist.all_gather_object(res, bool(ok))
     if rank == 0:
-        torch.save(ok, out)
+        torch.save(all(res), out)
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_cp_attention_fwd_bwd_equals_single_gpu_bitwise(tmp_path):
+@pytest.mark.parametrize("world", WORLDS)
+def test_cp_attention_fwd_bwd_equals_single_gpu_bitwise(tmp_path, world):
+    _need(world)
     out = str(tmp_path / "cp.pt")
-    mp.spawn(_cp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    mp.spawn(_cp_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert torch.load(out)
 
 
@@ -288,10 +370,10 @@ def _push_worker(rank, world, port, out):
 
     dev = torch.device("cuda", rank)
     lib = ext.load()
-    spec = Qwen3DenseSpec.scaled(layers=2, hidden=256, ffn=512, q_heads=4, kv_heads=2, head_dim=128, vocab=1024)
+    spec = Qwen3DenseSpec.scaled(layers=2, hidden=256, ffn=512, q_heads=16, kv_heads=8, head_dim=128, vocab=1024)
     w = Qwen3DenseWeights.synthetic(spec, seed=9)
-    # destination: a TP2 rollout shard on every rank, living in exportable memory
-    dst_layout = PackedParams(spec, rank, 2, dev)
+    # destination: one tensor-parallel rollout shard per rank, living in exportable memory
+    dst_layout = PackedParams(spec, rank, world, dev)
     nbytes = dst_layout.numel * 2 + 256
     h = ctypes.create_string_buffer(lib.rlk_symm_ipc_handle_bytes())
     p = ctypes.c_void_p(0)
@@ -301,23 +383,25 @@ def _push_worker(rank, world, port, out):
     mine = torch.as_tensor(_DevicePtrView(p.value, nbytes), device=dev)
     ok = True
     if rank == 0:
-        # source: the TP1 trainer shard on rank 0 pushes to both rollout shards (rank 0 local, rank 1 peer)
+        # source: the TP1 trainer shard on rank 0 pushes to every rollout shard (its own and the peers')
         src = PackedParams(spec, 0, 1, dev).load(w)
         bridge = NVLinkPushBridge(src, dev)
-        peer = ctypes.c_void_p(0)
-        ext.check(lib.rlk_ipc_open(handles[1], ctypes.byref(peer)), "ipc_open")
-        bases = [p.value, peer.value]
-        for r in range(2):
-            bridge.add_target(PackedParams(spec, r, 2, torch.device("cpu")), base_ptr=bases[r],
+        bases = [p.value]
+        for r in range(1, world):
+            peer = ctypes.c_void_p(0)
+            ext.check(lib.rlk_ipc_open(handles[r], ctypes.byref(peer)), "ipc_open")
+            bases.append(peer.value)
+        for r in range(world):
+            bridge.add_target(PackedParams(spec, r, world, torch.device("cpu")), base_ptr=bases[r],
                               version_flag_ptr=bases[r] + dst_layout.numel * 2)
         m = bridge.publish(7)
-        ok &= m.metadata["rl_kernel_bridge"]["targets"] == 2 and m.metadata["layout"]["kind"] == "tp-canonical"
+        ok &= m.metadata["rl_kernel_bridge"]["targets"] == world and m.metadata["layout"]["kind"] == "tp-canonical"
     flag = mine[dst_layout.numel * 2: dst_layout.numel * 2 + 8].view(torch.int64)
     okd = torch.zeros(1, dtype=torch.int32, device=dev)
     ext.check(lib.rlk_version_wait(ext.ptr(flag), ctypes.c_ulonglong(7), ext.ptr(okd), ext.stream_ptr(dev)), "wait")
     torch.cuda.synchronize(dev)
     ok &= int(okd.item()) == 1
-    want = PackedParams(spec, rank, 2, dev).load(w)
+    want = PackedParams(spec, rank, world, dev).load(w)
     ok &= torch.equal(mine[: dst_layout.numel * 2].view(torch.bfloat16), want.flat)
     res = [None] * world
     dist.all_gather_object(res, bool(ok))
@@ -327,9 +411,11 @@ def _push_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_weight_push_reshards_over_nvlink(tmp_path):
+@pytest.mark.parametrize("world", WORLDS)
+def test_weight_push_reshards_over_nvlink(tmp_path, world):
+    _need(world)
     out = str(tmp_path / "push.pt")
-    mp.spawn(_push_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    mp.spawn(_push_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert torch.load(out)
 
 
@@ -337,7 +423,7 @@ def _moe_case(dev, ep_rank, ep_size, coll):
     from rl_kernel_b200.models.qwen3_moe import MoEPackedParams, Qwen3MoeEngine, Qwen3MoeSpec
 
     spec = Qwen3MoeSpec.tiny()
-    B, S, P = 4, 256, 64
+    B, S, P = 8, 256, 64
     tokens = torch.randint(0, spec.vocab_size, (B, S), generator=torch.Generator().manual_seed(9)).to(dev)
     per = B // ep_size
     mine = tokens[ep_rank * per:(ep_rank + 1) * per].contiguous()
@@ -367,12 +453,14 @@ def _moe_ep_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_moe_expert_parallel_matches_single_gpu(tmp_path):
-    """Two expert-parallel ranks (tokens and experts both split, dispatch / combine over NVLink)
+@pytest.mark.parametrize("world", WORLDS)
+def test_moe_expert_parallel_matches_single_gpu(tmp_path, world):
+    """2, 4 or 8 expert-parallel ranks (tokens and experts both split, dispatch / combine over NVLink)
     reproduce one GPU: log-probs and expert weight gradients bit for bit, replicated-parameter
     gradients to rounding (they are summed over the ranks instead of over one long token axis)."""
+    _need(world)
     out = str(tmp_path / "moe.pt")
-    mp.spawn(_moe_ep_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    mp.spawn(_moe_ep_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     ep = torch.load(out)
     spec, params, logp = _moe_case(torch.device("cuda:0"), 0, 1, None)
     assert all(r["status"] == 0 for r in ep)
@@ -381,7 +469,7 @@ def test_moe_expert_parallel_matches_single_gpu(tmp_path):
     assert torch.equal(torch.cat([r["w2"] for r in ep]), params.g["l1.w2"].cpu())
     for name, key in (("router", "l0.router"), ("wqkv", "l1.wqkv")):
         a, b = ep[0][name].float(), params.g[key].float().cpu()
-        assert torch.equal(ep[0][name], ep[1][name]), "replicated gradients must agree across ranks"
+        assert all(torch.equal(ep[0][name], r[name]) for r in ep), "replicated gradients must agree across ranks"
         assert (a - b).abs().max().item() <= 0.05 * b.abs().max().item() + 1e-6, name
 
 
@@ -419,14 +507,16 @@ def _ag_gemm_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_all_gather_gemm_equals_gemm_of_gathered_matrix(tmp_path):
+@pytest.mark.parametrize("world", WORLDS)
+def test_all_gather_gemm_equals_gemm_of_gathered_matrix(tmp_path, world):
+    _need(world)
     out = str(tmp_path / "ag.pt")
-    mp.spawn(_ag_gemm_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    mp.spawn(_ag_gemm_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert torch.load(out)
 
 
 def _pcp_worker(rank, world, port, out):
-    """Page pool spread over two GPUs (block b of every sequence lives on rank b % 2); each rank
+    """Page pool spread over the GPUs (block b of every sequence lives on rank b % world); each rank
     computes a disjoint slice of the query rows and reads the other rank's pages over NVLink."""
     dist = _init(rank, world, port)
     from rl_kernel_b200.backends import extension as ext
@@ -455,7 +545,8 @@ def _pcp_worker(rank, world, port, out):
             cache.set_remote_page(0, b, owner, tables[owner][b] & 0xFFFFFF)
     torch.cuda.synchronize(dev)
     dist.barrier()
-    lo, hi = (0, 384) if rank == 0 else (384, n)         # disjoint query slices
+    per = (n + world - 1) // world
+    lo, hi = rank * per, min(n, (rank + 1) * per)        # disjoint query slices
     o = paged_attention(q[lo:hi].contiguous(), cache, [0], [torch.arange(lo, hi)], peer_pools=(pm["k"], pm["v"]))
     ref = causal_attention(q, k, v, [0, n])
     torch.cuda.synchronize(dev)
@@ -469,9 +560,11 @@ def _pcp_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_paged_context_parallel_reads_remote_pages(tmp_path):
+@pytest.mark.parametrize("world", (2, 4))
+def test_paged_context_parallel_reads_remote_pages(tmp_path, world):
+    _need(world)
     out = str(tmp_path / "pcp.pt")
-    mp.spawn(_pcp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    mp.spawn(_pcp_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert torch.load(out)
 
 
@@ -538,9 +631,9 @@ def _dp_worker(rank, world, port, out):
     spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
     w = Qwen3DenseWeights.synthetic(spec, seed=3)
     ctx = build_parallel_context(1, 1, dev, dp=world)
-    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=48, micro_batch_seqs=2, lr=1e-4)
+    cfg = GRPOConfig(num_prompts=world, group_size=2, prompt_len=128, response_len=48, micro_batch_seqs=2, lr=1e-4)
     tr = GRPOTrainer(spec, cfg, dev, ctx=ctx, weights=w)
-    prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5)).to(dev)
+    prompts = torch.randint(0, spec.vocab_size, (world, 128), generator=torch.Generator().manual_seed(5)).to(dev)
     res = tr.step(tr.local_prompts(prompts), step_index=0)
     torch.cuda.synchronize(dev)
     mine = {k: res[k].cpu() for k in ("tokens", "old_logp", "train_logp", "grad_norm", "rewards")}
@@ -553,26 +646,29 @@ def _dp_worker(rank, world, port, out):
     dist.destroy_process_group()
 
 
-def test_data_parallel_replicas_match_single_gpu(tmp_path):
-    """Two whole-model replicas, each rolling out and training its own prompts: sequences and
-    log-probs equal the single-GPU run bit for bit, the summed gradient agrees to rounding and both
-    replicas end the step with identical weights."""
+@pytest.mark.parametrize("world", WORLDS)
+def test_data_parallel_replicas_match_single_gpu(tmp_path, world):
+    """2, 4 or 8 whole-model replicas, each rolling out and training its own prompts: sequences and
+    log-probs equal the single-GPU run bit for bit, the summed gradient agrees to rounding (the
+    replicas' sums meet in a fixed tree instead of one running sum) and all replicas end the step
+    with identical weights."""
+    _need(world)
     from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
     from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
 
     out = str(tmp_path / "dp.pt")
-    mp.spawn(_dp_worker, args=(2, _free_port(), out), nprocs=2, join=True)
+    mp.spawn(_dp_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     dp = torch.load(out)
     dev = torch.device("cuda:0")
     spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
     w = Qwen3DenseWeights.synthetic(spec, seed=3)
-    cfg = GRPOConfig(num_prompts=2, group_size=2, prompt_len=128, response_len=48, micro_batch_seqs=2, lr=1e-4)
+    cfg = GRPOConfig(num_prompts=world, group_size=2, prompt_len=128, response_len=48, micro_batch_seqs=2, lr=1e-4)
     tr = GRPOTrainer(spec, cfg, dev, weights=w)
-    prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(5)).to(dev)
+    prompts = torch.randint(0, spec.vocab_size, (world, 128), generator=torch.Generator().manual_seed(5)).to(dev)
     one = tr.step(prompts, step_index=0)
     for key in ("tokens", "old_logp", "train_logp", "rewards"):
         assert torch.equal(torch.cat([r[key] for r in dp]), one[key].cpu()), key
     assert torch.equal(dp[0]["train_logp"], dp[0]["old_logp"])
-    assert torch.equal(dp[0]["w"], dp[1]["w"])
-    assert torch.equal(dp[0]["grad_norm"], dp[1]["grad_norm"])
+    assert all(torch.equal(dp[0]["w"], r["w"]) for r in dp)
+    assert all(torch.equal(dp[0]["grad_norm"], r["grad_norm"]) for r in dp)
     assert abs(float(dp[0]["grad_norm"]) - float(one["grad_norm"])) <= 2e-2 * float(one["grad_norm"])
