@@ -6,11 +6,14 @@ optimizer) tokens/s, with the train-vs-rollout log-prob mismatch count.
         --master-port P bench.py --gpus N --steps K --warmup W
     python bench.py --impl reference ...     # the unmodified reference from baseline/_ref
 
-Weak scaling: every GPU brings 8 prompts x group 8 x (512 + 1024) tokens.  Default layout: data
-parallel (one whole-model replica per GPU); ``--plan tp4xcp2`` etc. select tensor / context
-parallel layouts (``parallel_plan``).  Data is synthetic (uniform-random prompt ids,
-Bernoulli(0.5) rewards), weights are random-init N(0, 0.02) of the official architecture.
-One JSON line is printed by rank 0.
+Weak scaling: every GPU brings 8 prompts x group 8 x (512 + 1024) tokens; tokens/s counts the
+prompt and the response tokens of every sequence.  Default layout: data parallel (one whole-model
+replica per GPU); ``--plan tp4xcp2`` etc. select tensor / context parallel layouts
+(``parallel_plan``).  On 2, 4 or 8 GPUs the default run also measures the layout the reference's
+headline runs use (tensor x context parallel: tp2, tp2xcp2, tp4xcp2) for a few steps after the
+main measurement and reports it under ``named_layout`` (``--no-named-layout`` skips it).
+Data is synthetic (uniform-random prompt ids, Bernoulli(0.5) rewards), weights are random-init
+N(0, 0.02) of the official architecture.  One JSON line is printed by rank 0.
 """
 from __future__ import annotations
 
@@ -103,7 +106,14 @@ def parallel_plan(n: int, override: str = "") -> dict:
     return plan
 
 
-def run_ours(args) -> dict:
+NAMED_LAYOUT = {2: "tp2", 4: "tp2xcp2", 8: "tp4xcp2"}      # the reference's headline layout (TP4 x CP2 on 8 GPUs) and its halves
+
+
+def _measure(args, plan: dict, dev, world: int, rank: int, local: int, *, warmup: int, steps: int, clocks: bool) -> dict:
+    """Builds a trainer for ``plan``, runs ``warmup`` untimed and ``steps`` timed GRPO steps and
+    returns the measurements (collective over all ranks; every rank gets the same numbers)."""
+    import gc
+
     import torch
     import torch.distributed as dist
 
@@ -112,25 +122,15 @@ def run_ours(args) -> dict:
     from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
     from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world != args.gpus:
-        raise SystemExit(f"WORLD_SIZE={world} but --gpus {args.gpus}: launch with torch.distributed.run")
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    plan = parallel_plan(args.gpus, args.plan)
     ctx = build_parallel_context(plan["tp"], plan["cp"], dev, dp=plan["dp"])
-
     spec = Qwen3DenseSpec.official()
     if args.layers:
         spec = spec.with_layers(args.layers)
     # one training replica spans all GPUs; a micro-batch keeps micro_batch x seq_len tokens per rank
     cfg = GRPOConfig(num_prompts=PROMPTS_PER_GPU * args.gpus, group_size=GROUP,
                      prompt_len=PROMPT_LEN, response_len=args.response_len,
-                     micro_batch_seqs=args.micro_batch * plan["cp"], share_rollout_weights=True, seed=1234,
+                     micro_batch_seqs=args.micro_batch * plan["cp"], share_rollout_weights=False,
+                     rollout_weights_in_grad_buffer=True, seed=1234,
                      store_activations=plan["cp"] == 1 and args.train_micro_batch > 0,
                      train_micro_batch_seqs=args.train_micro_batch if plan["cp"] == 1 else 0)
     trainer = GRPOTrainer(spec, cfg, dev, ctx=ctx)
@@ -139,7 +139,7 @@ def run_ours(args) -> dict:
 
     # per-step prompts live in pinned host memory; each step copies its own batch to the device
     gen = torch.Generator().manual_seed(99)
-    total = args.warmup + args.steps
+    total = warmup + steps
     host_prompts = torch.randint(0, spec.vocab_size, (total, n_prompts_global, PROMPT_LEN), generator=gen,
                                  dtype=torch.int64).pin_memory()
     dev_prompts = torch.empty(n_prompts_global, PROMPT_LEN, dtype=torch.int64, device=dev)
@@ -166,24 +166,24 @@ def run_ours(args) -> dict:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for i in range(args.warmup):
+    for i in range(warmup):
         one_step(i)
     mismatches, mism_tokens = 0, 0
     barrier()
     sampler = ClockSampler(local)
-    if rank == 0:
+    if rank == 0 and clocks:
         sampler.start()
     n0 = nv.LAUNCH_COUNT
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     ev0.record()
-    for i in range(args.warmup, total):
+    for i in range(warmup, total):
         one_step(i)
     ev1.record()
     barrier()
     wall = time.perf_counter() - t0
     dev_ms = ev0.elapsed_time(ev1)
-    clocks = sampler.stop() if rank == 0 else {}
+    clk = sampler.stop() if rank == 0 and clocks else {}
     launches = nv.LAUNCH_COUNT - n0
     t = torch.tensor([dev_ms, wall * 1e3], dtype=torch.float64, device=dev)
     cnt = torch.tensor([float(mismatches), float(mism_tokens)], dtype=torch.float64, device=dev)
@@ -192,34 +192,96 @@ def run_ours(args) -> dict:
         dist.all_reduce(cnt, op=dist.ReduceOp.SUM)      # summed over replicas ...
     per_replica = plan["tp"] * plan["cp"]               # ... every rank of a replica counted the same tokens
     dev_ms, wall_ms = float(t[0]), float(t[1])
-    mismatches, mism_tokens = int(cnt[0]) // per_replica, int(cnt[1]) // per_replica
-    ms_per_step = dev_ms / args.steps
-    value = tokens_per_step / (ms_per_step / 1e3)
+    out = {
+        "plan": plan["name"], "tokens_per_step": tokens_per_step, "ms_per_step": dev_ms / steps,
+        "value": tokens_per_step / (dev_ms / steps / 1e3), "e2e_value": tokens_per_step * steps / (wall_ms / 1e3),
+        "mismatches": int(cnt[0]) // per_replica, "tokens_compared": int(cnt[1]) // per_replica, "clocks": clk,
+        "launches": int(launches), "h2d": int(dev_prompts.numel() * 8), "d2h": int(host_result.numel() * 4),
+        "cfg": cfg, "phase_ms": trainer.phase_ms(),
+        "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
+        "peak_mem_reserved_gb": round(torch.cuda.max_memory_reserved(dev) / 2 ** 30, 2),
+        "device_mem_free_gb": round(torch.cuda.mem_get_info(dev)[0] / 2 ** 30, 2),
+    }
+    # give the memory back before another layout is measured in the same process
+    for c in (ctx.collective, ctx.cp_collective, ctx.dp_collective):
+        if c is not None and hasattr(c, "close"):
+            try:
+                c.close()
+            except Exception:  # noqa: BLE001 - teardown only
+                pass
+    del trainer, ctx
+    gc.collect()
+    torch.cuda.empty_cache()
+    return out
+
+
+def run_ours(args) -> dict:
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"WORLD_SIZE={world} but --gpus {args.gpus}: launch with torch.distributed.run")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    plan = parallel_plan(args.gpus, args.plan)
+    m = _measure(args, plan, dev, world, rank, local, warmup=args.warmup, steps=args.steps, clocks=True)
+    cfg = m["cfg"]
     result = {
-        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "metric": METRIC, "value": m["value"], "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": m["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (uniform-random prompt ids, Bernoulli rewards, random-init weights)",
         "impl": "rl_kernel_b200",
         "config": {"model": "Qwen3-8B" if not args.layers else f"Qwen3-8B-shape-{args.layers}L",
-                   "global_batch": n_prompts_global * GROUP, "seq_len": PROMPT_LEN + args.response_len,
+                   "global_batch": PROMPTS_PER_GPU * args.gpus * GROUP, "seq_len": PROMPT_LEN + args.response_len,
                    "prompt_len": PROMPT_LEN, "response_len": args.response_len, "group_size": GROUP,
                    "parallelism": plan["name"], "micro_batch_seqs": args.micro_batch,
                    "train_micro_batch_seqs": cfg.train_micro_batch_seqs or cfg.micro_batch_seqs,
                    "activations": "stored" if cfg.store_activations else "per-layer recompute",
+                   "tokens_counted": "prompt + response tokens of every sequence (global_batch x seq_len per step)",
                    "l2_policy": "inputs larger than L2 (16 GB of weights stream every pass)",
-                   "includes": "weight publish, prefill, CUDA-graph decode+sampling, reference-policy scoring, "
-                               "train fwd/bwd (see activations), exact grad-norm clip, AdamW"},
-        "logp_mismatch_count": mismatches, "logp_tokens_compared": mism_tokens,
-        "clocks": clocks,
-        "e2e": {"value": tokens_per_step * args.steps / (wall_ms / 1e3), "unit": "tokens/s",
-                "h2d_bytes_per_step": int(dev_prompts.numel() * 8), "d2h_bytes_per_step": int(host_result.numel() * 4),
+                   "includes": "weight publish (push kernel into the rollout engine's buffer), prefill, CUDA-graph "
+                               "decode+sampling, reference-policy scoring, train fwd/bwd (see activations), exact "
+                               "grad-norm clip, AdamW"},
+        "logp_mismatch_count": m["mismatches"], "logp_tokens_compared": m["tokens_compared"],
+        "clocks": m["clocks"],
+        "e2e": {"value": m["e2e_value"], "unit": "tokens/s",
+                "h2d_bytes_per_step": m["h2d"], "d2h_bytes_per_step": m["d2h"],
                 "timing": "host wall clock around the same steps incl. H2D of prompts and D2H of loss"},
-        "gpu_launches": int(launches),
-        "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2 ** 30, 2),
-        "peak_mem_reserved_gb": round(torch.cuda.max_memory_reserved(dev) / 2 ** 30, 2),
-        "device_mem_free_gb": round(torch.cuda.mem_get_info(dev)[0] / 2 ** 30, 2),
-        "phase_ms_last_step": trainer.phase_ms(),
+        "gpu_launches": m["launches"],
+        "peak_mem_gb": m["peak_mem_gb"], "peak_mem_reserved_gb": m["peak_mem_reserved_gb"],
+        "device_mem_free_gb": m["device_mem_free_gb"],
+        "phase_ms_last_step": m["phase_ms"],
     }
+    named = NAMED_LAYOUT.get(args.gpus)
+    if named and not args.plan and args.named_layout:
+        # The same job in the tensor x context parallel layout of the reference's headline runs (its
+        # fused GEMM + all-reduce, context-parallel attention and vocabulary-parallel LM head are all in
+        # the step).  A watchdog prints the main result if this part does not finish.
+        done = threading.Event()
+
+        def watchdog():
+            if not done.wait(args.named_layout_timeout):
+                if rank == 0:
+                    result["named_layout"] = {"plan": named, "unavailable": f"did not finish within {args.named_layout_timeout} s"}
+                    print(json.dumps(result), flush=True)
+                os._exit(0)
+
+        threading.Thread(target=watchdog, daemon=True).start()
+        try:
+            n = _measure(args, parse_plan(named), dev, world, rank, local, warmup=3, steps=args.named_layout_steps, clocks=False)
+            result["named_layout"] = {"plan": n["plan"], "value": n["value"], "unit": "tokens/s", "ms_per_step": n["ms_per_step"],
+                                      "steps": args.named_layout_steps, "warmup": 3,
+                                      "logp_mismatch_count": n["mismatches"], "logp_tokens_compared": n["tokens_compared"],
+                                      "gpu_launches": n["launches"], "phase_ms_last_step": n["phase_ms"],
+                                      "peak_mem_gb": n["peak_mem_gb"]}
+        except Exception as exc:  # noqa: BLE001 - the main measurement stands on its own
+            result["named_layout"] = {"plan": named, "unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+        done.set()
     if world > 1:
         dist.destroy_process_group()
     return result if rank == 0 else {}
@@ -237,6 +299,11 @@ def main() -> int:
     ap.add_argument("--train-micro-batch", type=int, default=4,
                     help="sequences per training micro-batch with stored activations (0 = recompute, --micro-batch)")
     ap.add_argument("--plan", default="", help="debug only: e.g. tp1xcp2 instead of the default plan for --gpus")
+    ap.add_argument("--named-layout", dest="named_layout", action="store_true", default=True,
+                    help="after the main measurement also measure the tensor x context parallel layout (default)")
+    ap.add_argument("--no-named-layout", dest="named_layout", action="store_false")
+    ap.add_argument("--named-layout-steps", type=int, default=2)
+    ap.add_argument("--named-layout-timeout", type=float, default=900.0)
     args = ap.parse_args()
     if args.impl == "reference":
         from baseline.reference_arm import run_reference

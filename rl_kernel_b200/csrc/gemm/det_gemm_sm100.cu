@@ -100,14 +100,25 @@ struct GemmParams {
 };
 #ifdef RLK_GEMM_TRACE
 constexpr int kTraceLen = 512;
+#define RLK_TRACE_T(row, idx) do { if (p.trace && blockIdx.x == 0 && threadIdx.x == 64 && (idx) < kTraceLen) p.trace[(row) * kTraceLen + (idx)] = clock64(); } while (0)
 #define RLK_TRACE(row, idx) do { if (p.trace && blockIdx.x == 0 && (idx) < kTraceLen) p.trace[(row) * kTraceLen + (idx)] = clock64(); } while (0)
 #else
 #define RLK_TRACE(row, idx) do { } while (0)
+#define RLK_TRACE_T(row, idx) do { } while (0)
 #endif
 
 __device__ __forceinline__ uint4 ar_ld_peer_v4(const void* p) {
   uint4 v;
   asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+// Weak 16-byte load that bypasses L1 (the peers' partial tiles: their visibility is established by
+// the acquire on the tile's flag plus the CTA barrier; strong .sys loads would complete one after
+// the other within a thread -- measured 2.7 us each over NVLink -- instead of overlapping).
+__device__ __forceinline__ uint4 ar_ld_peer_weak_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.cg.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
   return v;
 }
@@ -118,6 +129,77 @@ __device__ __forceinline__ uint4 ar_tree_node(const uint4 a, const uint4 b) {
   o.z = pack_bf16x2(__fadd_rn(bf16_lo(a.z), bf16_lo(b.z)), __fadd_rn(bf16_hi(a.z), bf16_hi(b.z)));
   o.w = pack_bf16x2(__fadd_rn(bf16_lo(a.w), bf16_lo(b.w)), __fadd_rn(bf16_hi(a.w), bf16_hi(b.w)));
   return o;
+}
+
+// Pulls one 128 x BN tile's partials from the W ranks' frames (this rank's own from local memory,
+// the others over NVLink with 16-byte loads, NB pieces per thread in flight so that a tile costs
+// one or two round trips), combines them with the balanced tree and writes the result.
+template <int BN, int W, int NB>
+__device__ __forceinline__ void ar_pull_tile(const GemmParams& p, int m0, int n0, int et) {
+  constexpr int kPerRow = BN / 8;                         // 16-byte pieces per tile row
+  const unsigned char* frames[W];
+#pragma unroll
+  for (int r = 0; r < W; ++r) frames[r] = p.ar_frame[r];
+  const int M = p.M, N = p.N;
+  const long long ldc = p.ldc;
+  unsigned char* out = reinterpret_cast<unsigned char*>(p.ar_out);
+  for (int base = et; base < BM * kPerRow; base += 256 * NB) {
+    // every piece of every rank is requested before the first one is used: a thread pays one
+    // NVLink round trip and one local one per batch, not one per piece
+    uint4 v[NB][W];
+#pragma unroll
+    for (int u = 0; u < NB; ++u) {
+      const int idx = base + u * 256;
+      const int rr = idx / kPerRow, cc = (idx % kPerRow) * 8;
+      if (idx < BM * kPerRow && m0 + rr < M && n0 + cc < N) {
+        const long long off = (static_cast<long long>(m0 + rr) * ldc + n0 + cc) * 2;
+#pragma unroll
+        for (int r = 0; r < W; ++r) v[u][r] = ar_ld_peer_weak_v4(frames[r] + off);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < NB; ++u) {
+      const int idx = base + u * 256;
+      const int rr = idx / kPerRow, cc = (idx % kPerRow) * 8;
+      if (!(idx < BM * kPerRow && m0 + rr < M && n0 + cc < N)) continue;
+      const long long off = (static_cast<long long>(m0 + rr) * ldc + n0 + cc) * 2;
+#pragma unroll
+      for (int n = W; n > 1; n >>= 1)
+#pragma unroll
+        for (int j = 0; j < n / 2; ++j) v[u][j] = ar_tree_node(v[u][2 * j], v[u][2 * j + 1]);
+      // (the frame is laid out with the caller's output pitch: the byte offsets coincide)
+      *reinterpret_cast<uint4*>(out + off) = v[u][0];
+    }
+  }
+}
+
+// Waits (bounded) until every peer has published its partial of tile t, then reduces the tile.
+// Called by all 256 epilogue threads; returns false when a wait gave up.
+template <int BN>
+__device__ __noinline__ bool ar_finish_tile(const GemmParams& p, int t, int m0, int n0, int et,
+                                               unsigned long long seq, volatile int* abort_flag) {
+  if (et < p.ar_world && et != p.ar_rank) {
+    const unsigned long long* f = p.ar_flags[p.ar_rank] + et * kMaxSlices + t;
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t it = 0;
+    unsigned long long v;
+    while (true) {
+      asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(f) : "memory");
+      if (v >= seq) break;
+      if ((++it & 63) == 0 && (*abort_flag || globaltimer_ns() - t0 > RLK_WAIT_LIMIT_NS)) {
+        *abort_flag = 1;
+        if (p.status) atomicCAS(p.status, 0, 105);
+        break;
+      }
+    }
+  }
+  asm volatile("bar.sync 2, 256;" ::: "memory");
+  RLK_TRACE_T(3, (t - blockIdx.x) / gridDim.x);            // peers' flags seen
+  if (*abort_flag) return false;
+  if (p.ar_world == 2) ar_pull_tile<BN, 2, 8>(p, m0, n0, et);
+  else if (p.ar_world == 4) ar_pull_tile<BN, 4, 4>(p, m0, n0, et);
+  else ar_pull_tile<BN, 8, 2>(p, m0, n0, et);
+  return true;
 }
 
 constexpr int kMaxStages = 16;
@@ -359,6 +441,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     const int row_in_tile = quad * 32 + lane;   // one thread owns one output row
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     uint32_t u = 0;
+    int ar_prev_t = -1, ar_prev_m0 = 0, ar_prev_n0 = 0;     // fused all-reduce: the tile whose reduction is still due
     griddep_sync();            // C, the statistics and the tree scratch may still be in use by the previous kernel
     for (int t = blockIdx.x; t < total_tiles && !*abort_flag; t += gridDim.x) {
       int mt, nt;
@@ -370,6 +453,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const uint32_t a = u & 1;
         if (!mbar_wait(accf0 + 8 * a, (u >> 1) & 1, abort_flag, p.status, 104)) break;
         tc_fence_after();
+        if (c == 0) RLK_TRACE_T(4, (t - blockIdx.x) / gridDim.x);   // first accumulator of the tile ready
         const bool last = (c == p.nchunks - 1);
         if ((BN == 128 || BN == 256) && p.stats != nullptr) {
           // 128-wide tiles: the first set of epilogue warps walks the tile's one vocabulary tile;
@@ -708,59 +792,27 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tc_fence_before();
         mbar_arrive(acce0 + 8 * a);
       }
-      if (p.ar_world > 1 && half == 1) {
-        // the second set of epilogue warps only drains accumulators; its partial-tile stores must
-        // be visible before the first set signals the peers
-        __threadfence_system();
-        asm volatile("bar.arrive 2, 256;" ::: "memory");
-      }
-      if (p.ar_world > 1 && half == 0) {
-        // ---- fused all-reduce of this tile (the MMA warp is already working on the next tile)
-        const int et = threadIdx.x - 64;  // 0..127 among the first set of epilogue threads
-        if (BN >= 128) asm volatile("bar.sync 2, 256;" ::: "memory");   // wait for the other half's stores
+      if (p.ar_world > 1) {
+        // ---- fused all-reduce, one tile behind the accumulator drain.  This tile's partial is in the
+        // frame: make it visible and tell the peers; then finish the PREVIOUS tile, whose peers have
+        // had a whole tile's time to answer, so the flag round trip is off the critical path.
+        const int et = threadIdx.x - 64;  // 0..255 among the epilogue threads (tiles of 128 columns)
         const unsigned long long seq = p.ar_use_epoch ? p.ar_seq + p.ar_epoch[0] * p.ar_epoch[1] : p.ar_seq;
-        __threadfence_system();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        RLK_TRACE_T(0, (t - blockIdx.x) / gridDim.x);      // drained
+        // (no fence per thread: the barrier orders the 256 threads' stores before the flag threads'
+        // st.release.sys, and a release is cumulative over what its thread has observed)
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        RLK_TRACE_T(1, (t - blockIdx.x) / gridDim.x);      // fenced
         if (et < p.ar_world && et != p.ar_rank)
           asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p.ar_flags[et] + p.ar_rank * kMaxSlices + t), "l"(seq) : "memory");
-        if (et < p.ar_world && et != p.ar_rank) {
-          const unsigned long long* f = p.ar_flags[p.ar_rank] + et * kMaxSlices + t;
-          const uint64_t t0 = globaltimer_ns();
-          uint32_t it = 0;
-          unsigned long long v;
-          while (true) {
-            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(f) : "memory");
-            if (v >= seq) break;
-            if ((++it & 63) == 0 && (*abort_flag || globaltimer_ns() - t0 > RLK_WAIT_LIMIT_NS)) {
-              *abort_flag = 1;
-              if (p.status) atomicCAS(p.status, 0, 105);
-              break;
-            }
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*abort_flag) break;
-        constexpr int kPerRow = BN / 8;                         // 16-byte pieces per tile row
-        const int m0 = mt * BM;
-        for (int idx = et; idx < BM * kPerRow; idx += 128) {
-          const int rr = idx / kPerRow, cc = (idx % kPerRow) * 8;
-          if (m0 + rr < p.M && n0 + cc < p.N) {
-            const long long off = (static_cast<long long>(m0 + rr) * p.ldc + n0 + cc) * 2;
-            uint4 v[8];
-#pragma unroll
-            for (int r = 0; r < 8; ++r)
-              if (r < p.ar_world)
-                v[r] = (r == p.ar_rank) ? *reinterpret_cast<const uint4*>(p.ar_frame[r] + off)
-                                        : ar_ld_peer_v4(p.ar_frame[r] + off);
-#pragma unroll
-            for (int n = 8; n > 1; n >>= 1)
-              if (n <= p.ar_world)
-#pragma unroll
-                for (int j = 0; j < n / 2; ++j) v[j] = ar_tree_node(v[2 * j], v[2 * j + 1]);
-            *reinterpret_cast<uint4*>(p.ar_out + static_cast<long long>(m0 + rr) * p.ar_ld_out + n0 + cc) = v[0];
-          }
-        }
+        if (ar_prev_t >= 0 && !ar_finish_tile<BN>(p, ar_prev_t, ar_prev_m0, ar_prev_n0, et, seq, abort_flag)) break;
+        RLK_TRACE_T(2, (t - blockIdx.x) / gridDim.x);      // previous tile reduced
+        ar_prev_t = t; ar_prev_m0 = mt * BM; ar_prev_n0 = n0;
       }
+    }
+    if (p.ar_world > 1 && ar_prev_t >= 0 && !*abort_flag) {
+      const unsigned long long seq = p.ar_use_epoch ? p.ar_seq + p.ar_epoch[0] * p.ar_epoch[1] : p.ar_seq;
+      ar_finish_tile<BN>(p, ar_prev_t, ar_prev_m0, ar_prev_n0, static_cast<int>(threadIdx.x) - 64, seq, abort_flag);
     }
     if ((BN == 128 || BN == 256) && p.tma_store && lane == 0 && (warp == 2 || warp == 6)) tma_store_wait_all();
   }

@@ -725,17 +725,21 @@ CUDAIPCTensorBridge = IPCWeightBridge
 
 
 # ------------------------------------------------------------------------------- NVLink push (K17)
-def reshard_blocks(src_params, dst_params, dst_index: int) -> list[tuple]:
+def reshard_blocks(src_params, dst_params, dst_index: int, *, replicated_from_every_rank: bool = False) -> list[tuple]:
     """2-D block copies that move the part of ``src_params`` (a PackedParams shard of a TP group of
     size tp_s) that destination shard ``dst_params`` (TP size tp_d) needs.  Returns tuples
-    (src_off, dst_off, src_pitch, dst_pitch, rows, row_bytes, dst_mask) in BYTES."""
+    (src_off, dst_off, src_pitch, dst_pitch, rows, row_bytes, dst_mask) in BYTES.
+    Replicated vectors (norm gains) are sent by source rank 0 only, because every source rank holds
+    the same values and all of them reach every destination; ``replicated_from_every_rank`` is for a
+    source rank that is the ONLY writer of its destination (a rank that publishes into its own
+    colocated rollout shard)."""
     out = []
     ts, rs = src_params.tp_size, src_params.tp_rank
     td, rd = dst_params.tp_size, dst_params.tp_rank
     for name, s in src_params.slots.items():
         d = dst_params.slots[name]
         if len(s.shape) == 1:                                       # replicated vector
-            if rs == 0 or ts == 1:
+            if rs == 0 or ts == 1 or replicated_from_every_rank:
                 out.append((s.offset * 2, d.offset * 2, s.numel * 2, d.numel * 2, 1, s.numel * 2, 1 << dst_index))
             continue
         row_split = name.endswith(("wqkv", "wgu")) or name in ("embed", "lm_head")
@@ -772,14 +776,16 @@ class NVLinkPushBridge(LocalTensorCopyBridge):
         self._descs = None
         self._counter = torch.zeros(1, dtype=torch.int32, device=device)
 
-    def add_target(self, dst_params, base_ptr: int | None = None, version_flag_ptr: int | None = None) -> int:
+    def add_target(self, dst_params, base_ptr: int | None = None, version_flag_ptr: int | None = None, *,
+                   sole_writer: bool = False) -> int:
         """Register a destination shard; ``base_ptr`` is its flat buffer as mapped in THIS process
-        (defaults to dst_params.flat for same-process targets)."""
+        (defaults to dst_params.flat for same-process targets).  ``sole_writer``: no other source
+        rank pushes into this destination, so this rank also sends the replicated vectors."""
         idx = len(self._targets)
         if idx >= 8:
             raise WeightBridgeError("at most 8 destinations per push")
         self._targets.append((base_ptr if base_ptr is not None else dst_params.flat.data_ptr(), version_flag_ptr))
-        self._blocks += reshard_blocks(self.src, dst_params, idx)
+        self._blocks += reshard_blocks(self.src, dst_params, idx, replicated_from_every_rank=sole_writer)
         self._descs = None
         return idx
 

@@ -69,9 +69,10 @@ class PackedParams:
 
     def __init__(self, spec: Qwen3DenseSpec, tp_rank: int, tp_size: int, device: torch.device,
                  with_grad: bool = False, *, layers: tuple[int, int] | None = None,
-                 has_embed: bool = True, has_head: bool = True):
+                 has_embed: bool = True, has_head: bool = True, storage: torch.Tensor | None = None):
         """``layers`` = (first, end) and ``has_embed`` / ``has_head`` select what a pipeline stage owns
-        (default: the whole model)."""
+        (default: the whole model).  ``storage``: an existing flat bf16 tensor of at least ``numel``
+        elements to place the parameters in (its contents are kept)."""
         if spec.canonical_tp % tp_size:
             raise ValueError(f"tp_size {tp_size} must divide canonical_tp {spec.canonical_tp}")
         self.spec, self.tp_rank, self.tp_size, self.device = spec, tp_rank, tp_size, device
@@ -100,7 +101,12 @@ class PackedParams:
             off += (s.numel + 7) // 8 * 8
         self.slots = {s.name: s for s in slots}
         self.numel = off
-        self.flat = torch.zeros(off, dtype=BF16, device=device)
+        if storage is not None:
+            if storage.dtype != BF16 or storage.numel() < off or not storage.is_contiguous():
+                raise ValueError("storage must be a contiguous bf16 tensor of at least numel elements")
+            self.flat = storage[:off]
+        else:
+            self.flat = torch.zeros(off, dtype=BF16, device=device)
         self.grad = torch.zeros(off, dtype=BF16, device=device) if with_grad else None
         self.w = {s.name: self.flat[s.offset:s.offset + s.numel].view(s.shape) for s in slots}
         self.g = ({s.name: self.grad[s.offset:s.offset + s.numel].view(s.shape) for s in slots}
@@ -337,7 +343,13 @@ class Qwen3Engine:
         self.scale = 1.0 / math.sqrt(self.d)
         self.cos, self.sin = rope_tables(spec, max_positions, self.dev)
         self.ws = Workspace(self.dev)
-        self.fuse_gemm_allreduce = True
+        # Row-parallel projections with many rows: the GEMM writes its partial into the symmetric
+        # frame and the two-shot all-reduce kernel follows (False), or one fused kernel pulls the
+        # peers' tiles in its epilogue (True).  Measured on two GPUs at 12288 x 4096 outputs the
+        # fused kernel loses (0.78 against 0.49 ms at K = 2048 per rank): its one-shot pulls move
+        # (W - 1) x the tile over NVLink inside the epilogue, 25 us per tile, which the mainloop
+        # cannot hide.
+        self.fuse_gemm_allreduce = False
         # Layout-invariant parameter gradients: q_norm / k_norm gains as a tree over KV groups, the LM
         # head's input gradient over canonical vocabulary chunks.  With them every gradient of a
         # tensor-parallel run equals the single-GPU gradient bit for bit.

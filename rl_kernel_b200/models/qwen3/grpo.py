@@ -41,6 +41,10 @@ class GRPOConfig:
     use_cuda_graph: bool = True
     use_reference_model: bool = True
     share_rollout_weights: bool = False   # True: rollout reads the trainer's buffer (zero-copy publish)
+    # The rollout engine's own weight buffer lives in the memory of the gradient buffer: gradients
+    # are dead between the optimizer step and the next backward, which is exactly when the rollout
+    # runs.  Every step publishes with the weight-push kernel (csrc/collectives/weight_sync.cu).
+    rollout_weights_in_grad_buffer: bool = False
     share_kv_and_activation_memory: bool = True
     share_prompt_pages: bool = True       # group members read their prompt's K/V pages in place
     store_activations: bool = False       # training keeps layer intermediates instead of recomputing them
@@ -155,7 +159,19 @@ class GRPOTrainer:
             self.ref_params.flat.copy_(self.policy.flat)
         # rollout weights: a separate buffer that receives every published version, unless the
         # engines are colocated and configured to alias the trainer's shard
-        self.rollout_params = self.policy if cfg.share_rollout_weights else PackedParams(spec, tp_r, tp, device)
+        self._push = None
+        if cfg.share_rollout_weights:
+            self.rollout_params = self.policy
+        elif cfg.rollout_weights_in_grad_buffer:
+            from rl_kernel_b200.integrations.common.weights import NVLinkPushBridge
+
+            self.rollout_params = PackedParams(spec, tp_r, tp, device, storage=self.policy.grad)
+            self._version_flag = torch.zeros(32, dtype=torch.int64, device=device)
+            self._push = NVLinkPushBridge(self.policy, device, source_worker="trainer", source_rank=tp_r)
+            self._push.add_target(self.rollout_params, version_flag_ptr=self._version_flag.data_ptr(), sole_writer=True)
+            self._last_update_id = None
+        else:
+            self.rollout_params = PackedParams(spec, tp_r, tp, device)
         self.rollout_engine = Qwen3Engine(spec, self.rollout_params, self.rollout_ctx, max_positions=cfg.seq_len + 8)
         kv_bytes = self.rollout_engine.kv_cache_bytes(self.roll_seqs, cfg.seq_len)
         if cfg.share_prompt_pages and cfg.prompt_len % 128 == 0:
@@ -181,10 +197,17 @@ class GRPOTrainer:
 
     # ---------------------------------------------------------------- weight sync
     def publish_weights(self) -> int:
-        """Train -> rollout weight sync: one device copy of the flat shard; monotonic version."""
-        if self.rollout_params is not self.policy:
-            self.rollout_params.flat.copy_(self.policy.flat)
+        """Train -> rollout weight sync with a monotonic version: the weight-push kernel when the
+        trainer owns a push bridge, one device copy of the flat shard otherwise, nothing when the
+        rollout engine aliases the trainer's buffer."""
         self.weight_version += 1
+        if self._push is not None:
+            m = self._push.publish(weight_version=self.weight_version)
+            if self._last_update_id is not None:
+                self._push.release(self._last_update_id)
+            self._last_update_id = m.update_id
+        elif self.rollout_params is not self.policy:
+            self.rollout_params.flat.copy_(self.policy.flat)
         return self.weight_version
 
     # ---------------------------------------------------------------- rollout
