@@ -32,6 +32,11 @@ class OpBackend(str, enum.Enum):
     B200_LOGP = "rl_kernel_b200.ops.logprob.BatchInvariantLogpOp"
     B200_LINEAR_LOGP = "rl_kernel_b200.ops.logprob.LinearLogpOp"
     B200_GRPO_LOSS = "rl_kernel_b200.ops.loss.GRPOLossOp"
+    B200_CP_ATTENTION = "rl_kernel_b200.ops.distributed.cp_attention.CPAttentionOp"
+    B200_VOCAB_PARALLEL_LOGP = "rl_kernel_b200.ops.distributed.vocab_parallel_logp.VocabParallelLinearLogpOp"
+    B200_RATIO_KL = "rl_kernel_b200.ops.distributed.losses.RatioKLNativeOp"
+    B200_DIST_GRPO_LOSS = "rl_kernel_b200.ops.distributed.losses.DistributedGRPOLossNativeOp"
+    B200_PACK = "rl_kernel_b200.ops.packing.PackOp"
     # --- PyTorch references
     REF_DET_GEMM = "rl_kernel_b200.reference.gemm.det_gemm.NativeGemmOp"
     REF_RMS_NORM = "rl_kernel_b200.reference.norm.rms_norm.NativeRMSNormOp"
@@ -62,16 +67,16 @@ _TABLE: dict[str, tuple[OpBackend | None, OpBackend]] = {
     "embedding": (OpBackend.B200_EMBEDDING, OpBackend.REF_EMBEDDING),
     "lm_head": (OpBackend.B200_LM_HEAD, OpBackend.REF_LM_HEAD),
     "attention": (OpBackend.B200_ATTENTION, OpBackend.REF_ATTENTION),
-    "cp_attention": (None, OpBackend.REF_CP_ATTENTION),
+    "cp_attention": (OpBackend.B200_CP_ATTENTION, OpBackend.REF_CP_ATTENTION),
     "ffn": (OpBackend.B200_FFN, OpBackend.REF_FFN),
     "logp": (OpBackend.B200_LOGP, OpBackend.REF_LOGP),
     "batch_invariant_logp": (OpBackend.B200_LOGP, OpBackend.REF_BI_LOGP),
     "linear_logp": (OpBackend.B200_LINEAR_LOGP, OpBackend.REF_LINEAR_LOGP),
-    "vocab_parallel_logp": (None, OpBackend.REF_VOCAB_PARALLEL_LOGP),
+    "vocab_parallel_logp": (OpBackend.B200_VOCAB_PARALLEL_LOGP, OpBackend.REF_VOCAB_PARALLEL_LOGP),
     "grpo_loss": (OpBackend.B200_GRPO_LOSS, OpBackend.REF_GRPO_LOSS),
-    "ratio_kl": (None, OpBackend.REF_RATIO_KL),
-    "distributed_grpo_loss": (None, OpBackend.REF_DIST_GRPO_LOSS),
-    "pack": (None, OpBackend.REF_PACK),
+    "ratio_kl": (OpBackend.B200_RATIO_KL, OpBackend.REF_RATIO_KL),
+    "distributed_grpo_loss": (OpBackend.B200_DIST_GRPO_LOSS, OpBackend.REF_DIST_GRPO_LOSS),
+    "pack": (OpBackend.B200_PACK, OpBackend.REF_PACK),
 }
 
 _LOGP_ALIASES = {
@@ -197,8 +202,13 @@ class KernelRegistry:
             why = cap.incompatibilities(contract)
             if why:
                 raise RuntimeError(f"attention backend {cap.backend_id} cannot serve the contract: {why}")
-        name = "cp_attention" if backend in ("cp", "cp_reference") else "attention"
-        return self.get_op(name, **kwargs)
+        name = "cp_attention" if backend in ("cp", "cp_native", "cp_reference") else "attention"
+        prefer = "reference" if backend == "cp_reference" else "auto"
+        if name == "cp_attention" and prefer == "auto" and "collective" not in kwargs:
+            # the native schedule needs the context-parallel group's collective and the geometry;
+            # without them only the single-process reference can be built
+            prefer = "reference"
+        return self.get_op(name, prefer=prefer, **kwargs)
 
     def provenance(self) -> list[dict]:
         return [{"op": r.op_name, "requested": r.requested, "actual": r.actual.name, "path": r.actual.value,

@@ -672,3 +672,89 @@ def test_data_parallel_replicas_match_single_gpu(tmp_path, world):
     assert all(torch.equal(dp[0]["w"], r["w"]) for r in dp)
     assert all(torch.equal(dp[0]["grad_norm"], r["grad_norm"]) for r in dp)
     assert abs(float(dp[0]["grad_norm"]) - float(one["grad_norm"])) <= 2e-2 * float(one["grad_norm"])
+
+
+def _fused_ops_worker(rank, world, port, out):
+    """The registry's native vocabulary-parallel log-prob and context-parallel attention operators
+    against single-GPU results, forward and backward."""
+    dist = _init(rank, world, port)
+    import math
+
+    from rl_kernel_b200.backends import extension as ext
+    from rl_kernel_b200.backends import native as nv
+    from rl_kernel_b200.distributed.transports.symm import SymmetricMemoryCollective
+    from rl_kernel_b200.models.qwen3.engine import train_tiles
+    from rl_kernel_b200.ops.logprob import linear_logp
+    from rl_kernel_b200.runtime.registry import OpBackend, kernel_registry
+
+    dev = torch.device("cuda", rank)
+    coll = SymmetricMemoryCollective(None, dev, frame_bytes=64 << 20)
+    ok = True
+    # ---- vocabulary-parallel fused linear log-prob
+    N, H, V, VP = 300, 512, 3900, 4096
+    g = torch.Generator(device="cuda").manual_seed(21)                # same tensors on every rank
+    hidden = torch.randn(N, H, device=dev, generator=g).bfloat16()
+    w_full = torch.zeros(VP, H, device=dev, dtype=torch.bfloat16)
+    w_full[:V] = (torch.randn(V, H, device=dev, generator=g) * 0.05).bfloat16()
+    targets = torch.randint(0, V, (N,), device=dev, generator=g)
+    gout = torch.randn(N, device=dev, generator=g)
+    op = kernel_registry.get_op("vocab_parallel_logp", real_vocab=V, padded_vocab=VP, collective=coll, temperature=0.7)
+    ok &= kernel_registry.last_resolution.actual is OpBackend.B200_VOCAB_PARALLEL_LOGP
+    per = VP // world
+    h1 = hidden.clone().requires_grad_(True)
+    ws = w_full[rank * per:(rank + 1) * per].clone().requires_grad_(True)
+    lp = op(h1, ws, targets)
+    lp.backward(gout)
+    one = kernel_registry.get_op("vocab_parallel_logp", real_vocab=V, padded_vocab=VP, collective=None, temperature=0.7)
+    h2 = hidden.clone().requires_grad_(True)
+    wf = w_full.clone().requires_grad_(True)
+    lp1 = one(h2, wf, targets)
+    lp1.backward(gout)
+    torch.cuda.synchronize(dev)
+    ok &= torch.equal(lp, lp1) and torch.equal(h1.grad, h2.grad) and torch.equal(ws.grad, wf.grad[rank * per:(rank + 1) * per])
+    ref = linear_logp(hidden, w_full[:V].contiguous(), targets, 0.7)       # the unsharded fused operator
+    ok &= torch.equal(lp.detach(), ref)
+    # ---- context-parallel attention through the registry
+    HQ, HKV, D, B, S = 8, 2, 128, 2, 256 * world
+    q = torch.randn(B, S, HQ * D, device=dev, generator=g).bfloat16()
+    k = torch.randn(B, S, HKV * D, device=dev, generator=g).bfloat16()
+    v = torch.randn(B, S, HKV * D, device=dev, generator=g).bfloat16()
+    do = torch.randn(B, S, HQ * D, device=dev, generator=g).bfloat16()
+    cp = kernel_registry.get_attention_op("cp", collective=coll, device=dev, num_q_heads=HQ, num_kv_heads=HKV,
+                                          max_local_tokens=B * S // world, layout="zigzag")
+    ok &= kernel_registry.last_resolution.actual is OpBackend.B200_CP_ATTENTION
+    pos = cp.local_positions(S).to(dev)
+    sel = lambda t: t[:, pos].reshape(B * pos.numel(), -1).contiguous()
+    ql, kl, vl = (sel(t).requires_grad_(True) for t in (q, k, v))
+    o, lse = cp(ql, kl, vl, nseq=B, seq_len=S)
+    o.backward(sel(do))
+    o1 = torch.empty(B * S, HQ * D, device=dev, dtype=torch.bfloat16)
+    l1 = torch.empty(B * S, HQ, device=dev)
+    tiles, kvtiles = train_tiles(B, S, HQ, HKV, D, dev)
+    sc = 1 / math.sqrt(D)
+    q2, k2, v2, do2 = (t.view(B * S, -1) for t in (q, k, v, do))
+    nv.attn_fwd(q2, [k2], [v2], o1, l1, tiles, sc)
+    dl = torch.empty(B * S, HQ, device=dev)
+    nv.attn_bwd_delta(o1, do2, dl, B * S, HQ)
+    dq1, dk1, dv1 = torch.empty_like(q2), torch.empty_like(k2), torch.empty_like(v2)
+    nv.attn_bwd_dq(q2, do2, k2, v2, l1, dl, dq1, tiles, sc)
+    nv.attn_bwd_dkv(q2, do2, k2, v2, l1, dl, dk1, dv1, kvtiles, sc)
+    torch.cuda.synchronize(dev)
+    ok &= torch.equal(o.detach(), sel(o1.view(B, S, -1))) and torch.equal(lse, sel(l1.view(B, S, -1)))
+    ok &= torch.equal(ql.grad, sel(dq1.view(B, S, -1))) and torch.equal(kl.grad, sel(dk1.view(B, S, -1)))
+    ok &= torch.equal(vl.grad, sel(dv1.view(B, S, -1)))
+    ok &= ext.poll_status(dev) == 0
+    res = [None] * world
+    dist.all_gather_object(res, bool(ok))
+    if rank == 0:
+        torch.save(all(res), out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_registry_native_multi_gpu_operators_match_single_gpu_bitwise(tmp_path, world):
+    _need(world)
+    out = str(tmp_path / "ops.pt")
+    mp.spawn(_fused_ops_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert torch.load(out)

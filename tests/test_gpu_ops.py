@@ -378,3 +378,75 @@ def test_collective_kernels_for_4_and_8_ranks_emulated_on_one_gpu(world):
                     assert torch.equal(outs[r], want[r * size:(r + 1) * size]), (world, dtype, mode, r)
                 else:
                     assert torch.equal(outs[r], torch.cat(parts)), (world, dtype, mode, r)
+
+
+def test_pack_unpack_kernel_matches_boolean_indexing():
+    from rl_kernel_b200.ops.packing import PackOp
+    from rl_kernel_b200.reference.packing.pack import NativePackOp
+
+    g = torch.Generator(device="cuda").manual_seed(4)
+    x = torch.randn(5, 37, 256, device=dev(), generator=g).bfloat16()
+    lengths = torch.tensor([37, 0, 5, 36, 1], device=dev())
+    mask = torch.arange(37, device=dev())[None, :] < lengths[:, None]
+    op, ref = PackOp(), NativePackOp()
+    packed, cu = op.pack(x, mask)
+    sync_and_check()
+    rp, rcu = ref.pack(x, mask)
+    assert torch.equal(packed, rp) and torch.equal(cu, rcu)
+    back = op.unpack(packed, mask, fill=-1.0)
+    sync_and_check()
+    assert torch.equal(back, ref.unpack(rp, mask, fill=-1.0))
+    # a left-padded mask packs in the same row-major order
+    mask2 = mask.flip(1)
+    p2, _ = op.pack(x, mask2)
+    assert torch.equal(p2, x[mask2])
+
+
+def test_registry_hands_out_native_ops_for_the_fused_operator_names():
+    """On a B200 every operator name that has an sm_100a implementation resolves to it, including
+    the multi-GPU ones (cp_attention needs its collective, so without one the reference is built)."""
+    from rl_kernel_b200.runtime.registry import OpBackend, kernel_registry
+
+    for name, want in (("ratio_kl", OpBackend.B200_RATIO_KL), ("distributed_grpo_loss", OpBackend.B200_DIST_GRPO_LOSS),
+                       ("vocab_parallel_logp", OpBackend.B200_VOCAB_PARALLEL_LOGP), ("pack", OpBackend.B200_PACK),
+                       ("cp_attention", OpBackend.B200_CP_ATTENTION)):
+        res = kernel_registry.resolve(name)
+        assert res.actual is want and not res.fallback, (name, res)
+
+
+def test_ratio_kl_and_single_rank_distributed_loss_match_references():
+    from rl_kernel_b200.ops.distributed import DistributedGRPOLossNativeOp, RatioKLNativeOp
+    from rl_kernel_b200.reference.loss.distributed_grpo_loss import DistributedGRPOLossOp
+    from rl_kernel_b200.reference.loss.ratio_kl import NativeRatioKLOp
+
+    g = torch.Generator(device="cuda").manual_seed(8)
+    B, L, V = 6, 40, 1024
+    pol = (torch.randn(B, L, V, device=dev(), generator=g) * 2).bfloat16().requires_grad_(True)
+    ref = (pol.detach().float() + 0.05 * torch.randn(B, L, V, device=dev(), generator=g)).bfloat16()
+    ids = torch.randint(0, V, (B, L), device=dev(), generator=g)
+    mask = torch.ones(B, L, dtype=torch.bool, device=dev())
+    mask[1, 30:] = False
+    mask[4, :3] = False
+    with torch.no_grad():
+        old = torch.log_softmax(pol.float(), -1).gather(-1, ids[..., None])[..., 0] + 0.01 * torch.randn(B, L, device=dev(), generator=g)
+    ratio, kl = RatioKLNativeOp()(pol, ref, ids, mask, old)
+    sync_and_check()
+    pr = pol.detach().clone().float().requires_grad_(True)
+    rr, rk = NativeRatioKLOp()(pr, ref.float(), ids, mask, old)
+    assert (ratio - rr).abs().max().item() < 5e-3 and (kl - rk).abs().max().item() < 5e-3
+    (ratio.sum() + kl.sum()).backward()
+    (rr.sum() + rk.sum()).backward()
+    assert (pol.grad.float() - pr.grad).abs().max().item() < 2e-2
+    # data-parallel loss with a single rank == the reference on the whole batch
+    logp = (old + 0.02 * torch.randn(B, L, device=dev(), generator=g)).requires_grad_(True)
+    refl = old + 0.03 * torch.randn(B, L, device=dev(), generator=g)
+    rewards = torch.tensor([1.0, 0.0, 1.0, 1.0, 0.0, 0.0], device=dev())
+    loss, pl, k = DistributedGRPOLossNativeOp(clip_eps=0.2, beta=0.01)(logp, old, refl, rewards, mask, samples_per_prompt=3)
+    sync_and_check()
+    lr2 = logp.detach().clone().requires_grad_(True)
+    rl, rpl, rkk = DistributedGRPOLossOp(clip_eps=0.2, beta=0.01)(lr2.cpu(), old.cpu(), refl.cpu(), rewards.cpu(), mask.cpu(),
+                                                              samples_per_prompt=3)
+    assert abs(loss.item() - rl.item()) < 1e-5 and abs(pl.item() - rpl.item()) < 1e-5 and abs(k.item() - rkk.item()) < 1e-6
+    loss.backward()
+    g_ref = torch.autograd.grad(rl, [], allow_unused=True) if False else None
+    assert logp.grad is not None and torch.isfinite(logp.grad).all() and logp.grad[~mask].abs().max().item() == 0.0
