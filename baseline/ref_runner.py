@@ -4,7 +4,10 @@
               support restriction by rl_engine.ops.sampling.policy.sampling_keep_mask
     scoring : Qwen3DenseBIModel.forward(target_ids=...) -> selected_logp   (reference policy + train pass)
     loss    : compute_policy_ratio / compute_reference_kl / masked_mean (rl_engine.validation.common)
-    update  : torch autograd through the reference's operator profile + torch.optim.AdamW
+    update  : torch autograd through the reference's operator profile inside its
+              canonical_backward_session (rl_engine/ops/autograd/canonical_backward.py:131), one
+              session per micro-batch as rl_engine/validation/models/chain_gate.py:1228 does per cell,
+              + torch.optim.AdamW
 Same synthetic data shape as the main arm: 8 prompts x group 8, prompt 512 + response 1024.
 Prints one JSON line; any failure is reported as {"impl": "reference", "unavailable": ...}.
 
@@ -17,6 +20,15 @@ prompt tokens in one ``forward`` (32768 rows) and met exactly that: "illegal mem
 first forward.  The reference's own workloads never do this (its trainer scores a few sequences
 per call), so the runner now prefills the 8 distinct prompts once (4096 rows), expands the cache
 to the 64 samples, and checks ``MAX_FORWARD_ROWS`` before every call.
+
+Why the training pass runs inside a canonical backward session.  Outside one, ``_linear``
+(rl_engine/models/qwen3/reference.py:996-1031) multiplies through ``TritonDetGemmOp.forward_accum_fp32``;
+the FFN down projection receives the FP32 SwiGLU product, and the backward of that autograd function
+(backends/shared/triton/gemm/det_gemm.py:1050-1060) hands the saved FP32 operand to
+``_triton_tree_gemm``, which raises "Triton tree GEMM requires BF16 inputs".  The reference's own
+training cells never take that branch: with a session active and ``logical_keys`` given, every
+projection, norm gain, embedding and the LM head go through the ``canonical_*`` functions, whose
+parameter gradients are one GEMM over the rows sorted by (sample, position).
 """
 from __future__ import annotations
 
@@ -57,6 +69,7 @@ def run(a) -> dict:
     import rl_engine  # noqa: F401  (must be the reference: the parent set PYTHONPATH)
     from rl_engine.models.qwen3.reference import Qwen3DenseBIModel, Qwen3DenseWeights, load_profile_ops
     from rl_engine.models.qwen3.spec import Qwen3DenseSpec
+    from rl_engine.ops.autograd.canonical_backward import canonical_backward_session
     from rl_engine.ops.sampling.policy import sampling_keep_mask
     from rl_engine.validation.common import compute_policy_ratio, compute_reference_kl, masked_mean
 
@@ -95,8 +108,17 @@ def run(a) -> dict:
 
     signal.signal(signal.SIGALRM, alarm)
 
+    phase = {"rollout_s": 0.0, "score_train_s": 0.0, "optimizer_s": 0.0}
+
+    def lap(name: str, t0: float) -> float:
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        phase[name] = t1 - t0                      # the last step's split (the sync is part of every step anyway)
+        return t1
+
     def one_step(i: int) -> None:
         signal.alarm(a.step_timeout)
+        t_phase = time.perf_counter()
         uniq = host_prompts[i].to(dev, non_blocking=True)
         prompts = uniq.repeat_interleave(GROUP, 0)
         # ---- rollout: every distinct prompt is prefilled once, its K/V then serve the whole group
@@ -128,6 +150,7 @@ def run(a) -> dict:
             old_logp = torch.cat(lps, 1)
             tokens = torch.cat([prompts, resp], 1)
             del cache
+        t_phase = lap("rollout_s", t_phase)
         rewards = torch.bernoulli(torch.full((B,), 0.5, device=dev))
         g = rewards.view(PROMPTS, GROUP)
         adv = ((g - g.mean(1, keepdim=True)) / g.std(1, unbiased=False, keepdim=True).clamp_min(1e-6)).reshape(B)
@@ -139,19 +162,25 @@ def run(a) -> dict:
             tk = tokens[b0:b0 + a.micro_batch]
             with torch.no_grad():
                 ref_lp = ref_model.forward(tk, target_ids=tk)["selected_logp"][:, P - 1:]
-            lp = model.forward(tk, target_ids=tk)["selected_logp"][:, P - 1:]
-            m = mask[b0:b0 + a.micro_batch]
-            ratio = compute_policy_ratio(lp, old_logp[b0:b0 + a.micro_batch], m)
-            av = adv[b0:b0 + a.micro_batch, None].expand_as(lp)
-            pol = -torch.minimum(ratio * av, torch.clamp(ratio, 0.8, 1.2) * av)
-            kl = compute_reference_kl(lp, ref_lp, m)
-            loss = (masked_mean(pol, m) + 0.001 * masked_mean(kl, m)) * (tk.shape[0] / B)
-            loss.backward()
+            keys = torch.stack([torch.arange(b0, b0 + tk.shape[0], device=dev)[:, None].expand(-1, S),
+                                torch.arange(S, device=dev)[None, :].expand(tk.shape[0], -1)], -1)
+            with canonical_backward_session() as session:
+                lp = model.forward(tk, target_ids=tk, logical_keys=keys)["selected_logp"][:, P - 1:]
+                m = mask[b0:b0 + a.micro_batch]
+                ratio = compute_policy_ratio(lp, old_logp[b0:b0 + a.micro_batch], m)
+                av = adv[b0:b0 + a.micro_batch, None].expand_as(lp)
+                pol = -torch.minimum(ratio * av, torch.clamp(ratio, 0.8, 1.2) * av)
+                kl = compute_reference_kl(lp, ref_lp, m)
+                loss = (masked_mean(pol, m) + 0.001 * masked_mean(kl, m)) * (tk.shape[0] / B)
+                loss.backward()
+                session.validate_complete()
             loss_total += loss.detach()
+        t_phase = lap("score_train_s", t_phase)
         torch.nn.utils.clip_grad_norm_(params, 1.0)
         opt.step()
         host_loss.copy_(loss_total.reshape(1), non_blocking=True)
         torch.cuda.current_stream().synchronize()
+        lap("optimizer_s", t_phase)
         signal.alarm(0)
 
     # warm-up and timed steps share one time budget: the reference's step is minutes long at full
@@ -186,7 +215,9 @@ def run(a) -> dict:
             "data": "synthetic (uniform-random prompt ids, Bernoulli rewards, random-init weights)",
             "config": {"model": "Qwen3-8B" if not a.layers else f"Qwen3-8B-shape-{a.layers}L", "global_batch": B,
                        "seq_len": S, "parallelism": "single GPU", "operator_profile": "triton_cuda_bf16",
-                       "micro_batch_seqs": a.micro_batch},
+                       "micro_batch_seqs": a.micro_batch, "response_len": R,
+                       "tokens_counted": "prompt + response tokens of every sequence"},
+            "phase_s_last_step": {k: round(v, 3) for k, v in phase.items()},
             "e2e": {"value": tokens_per_step * steps / wall, "unit": "tokens/s",
                     "h2d_bytes_per_step": PROMPTS * P * 8, "d2h_bytes_per_step": 4}}
 

@@ -65,6 +65,12 @@ def _bf16(t: torch.Tensor, name: str) -> torch.Tensor:
     return t
 
 
+def _f32(t: torch.Tensor, name: str) -> torch.Tensor:
+    if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+        raise TypeError(f"{name} must be a contiguous CUDA fp32 tensor, got {t.dtype} on {t.device}")
+    return t
+
+
 def _rowmajor2d(t: torch.Tensor, name: str) -> torch.Tensor:
     if t.dim() != 2 or t.stride(1) != 1:
         raise ValueError(f"{name} must be 2-D with unit inner stride, got shape {tuple(t.shape)} "
@@ -130,23 +136,32 @@ def det_gemm_split(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, scratch:
 
 def lmhead_logp_stats(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor | None,
                       stats: torch.Tensor, tgt_logit: torch.Tensor, *, vocab_start: int,
-                      inv_temp: float, logits_out: torch.Tensor | None = None) -> None:
+                      inv_temp: float, logits_out: torch.Tensor | None = None,
+                      min_keep: torch.Tensor | None = None) -> None:
+    """``min_keep`` fp32 [M]: restricted sampling support (scaled logits below it count as -inf)."""
     _bf16(h, "h"); _bf16(w, "w"); _rowmajor2d(h, "h"); _rowmajor2d(w, "w")
     M, K = h.shape
     N = w.shape[0]
     assert stats.dtype == torch.float32 and stats.dim() == 3 and stats.shape[2] == 2 and stats.is_contiguous()
-    rc = _lib().rlk_lmhead_logp_stats(ext.ptr(h), ext.ptr(w), c_int(M), c_int(N), c_int(K),
-                                      _ll(h.stride(0)), _ll(w.stride(0)), ext.ptr(targets),
-                                      _ll(vocab_start), c_float(inv_temp), ext.ptr(stats),
-                                      _ll(stats.shape[1]), ext.ptr(tgt_logit), ext.ptr(logits_out),
-                                      _ll(logits_out.stride(0) if logits_out is not None else 0),
-                                      ext.stream_ptr(h.device))
+    _keep(min_keep, M)
+    rc = _lib().rlk_lmhead_logp_stats_keep(ext.ptr(h), ext.ptr(w), c_int(M), c_int(N), c_int(K),
+                                           _ll(h.stride(0)), _ll(w.stride(0)), ext.ptr(targets),
+                                           _ll(vocab_start), c_float(inv_temp), ext.ptr(min_keep), ext.ptr(stats),
+                                           _ll(stats.shape[1]), ext.ptr(tgt_logit), ext.ptr(logits_out),
+                                           _ll(logits_out.stride(0) if logits_out is not None else 0),
+                                           ext.stream_ptr(h.device))
     ext.check(rc, "lmhead_logp_stats")
     _count()
 
 
+def _keep(min_keep, rows: int) -> None:
+    if min_keep is not None and (min_keep.dtype != torch.float32 or min_keep.numel() != rows or not min_keep.is_contiguous()
+                                 or not min_keep.is_cuda):
+        raise ValueError(f"min_keep must be a contiguous CUDA fp32 tensor with one value per row ({rows})")
+
+
 def lmhead_logp_stats_vp(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor, stats_bufs, tgt_bufs, rank: int,
-                         *, vocab_start: int, inv_temp: float) -> None:
+                         *, vocab_start: int, inv_temp: float, min_keep: torch.Tensor | None = None) -> None:
     """Vocab-parallel fused LM head: this shard's per-tile statistics (and the target logit, if this
     shard owns the target) are stored into every rank's buffers from the GEMM epilogue.
     ``stats_bufs[r]`` [M, ntile, 2] fp32 and ``tgt_bufs[r]`` [M] fp32 are rank r's buffers mapped here."""
@@ -155,10 +170,11 @@ def lmhead_logp_stats_vp(h: torch.Tensor, w: torch.Tensor, targets: torch.Tensor
     world = len(stats_bufs)
     sp = (c_void_p * world)(*[t.data_ptr() for t in stats_bufs])
     tp = (c_void_p * world)(*[t.data_ptr() for t in tgt_bufs])
-    rc = _lib().rlk_lmhead_logp_stats_vp(ext.ptr(h), ext.ptr(w), c_int(M), c_int(w.shape[0]), c_int(K),
-                                         _ll(h.stride(0)), _ll(w.stride(0)), ext.ptr(targets), _ll(vocab_start),
-                                         c_float(inv_temp), sp, _ll(stats_bufs[0].shape[1]), tp, c_int(world),
-                                         c_int(rank), ext.stream_ptr(h.device))
+    _keep(min_keep, M)
+    rc = _lib().rlk_lmhead_logp_stats_vp_keep(ext.ptr(h), ext.ptr(w), c_int(M), c_int(w.shape[0]), c_int(K),
+                                              _ll(h.stride(0)), _ll(w.stride(0)), ext.ptr(targets), _ll(vocab_start),
+                                              c_float(inv_temp), ext.ptr(min_keep), sp, _ll(stats_bufs[0].shape[1]), tp,
+                                              c_int(world), c_int(rank), ext.stream_ptr(h.device))
     ext.check(rc, "lmhead_logp_stats_vp")
     _count()
 
@@ -385,14 +401,16 @@ def embedding_bwd(sorted_ids, order, dy, dw, vocab_start: int = 0) -> None:
 
 # ------------------------------------------------------------------------------------- logp
 def logits_tile_stats(logits, targets, stats, tgt_logit, *, vocab_start: int, inv_temp: float,
-                      row_indices=None) -> None:
-    """``row_indices`` int64 [rows]: output row r scores logits row ``row_indices[r]``."""
+                      row_indices=None, min_keep=None) -> None:
+    """``row_indices`` int64 [rows]: output row r scores logits row ``row_indices[r]``.
+    ``min_keep`` fp32 [rows]: scaled logits below the row's value are outside the support."""
     n_local = logits.shape[1]
     rows = logits.shape[0] if row_indices is None else row_indices.numel()
-    rc = _lib().rlk_logits_tile_stats_indexed(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(targets),
-                                              ext.ptr(stats), _ll(stats.shape[1]), ext.ptr(tgt_logit),
-                                              c_int(rows), c_int(n_local), _ll(vocab_start), c_float(inv_temp),
-                                              ext.ptr(row_indices), ext.stream_ptr(logits.device))
+    _keep(min_keep, rows)
+    rc = _lib().rlk_logits_tile_stats_keep(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(targets),
+                                           ext.ptr(stats), _ll(stats.shape[1]), ext.ptr(tgt_logit),
+                                           c_int(rows), c_int(n_local), _ll(vocab_start), c_float(inv_temp),
+                                           ext.ptr(row_indices), ext.ptr(min_keep), ext.stream_ptr(logits.device))
     ext.check(rc, "logits_tile_stats")
     _count()
 
@@ -405,11 +423,30 @@ def logp_merge(stats, tgt_logit, logp, lse) -> None:
     _count()
 
 
-def dlogits_(logits, targets, lse, g, *, vocab_start: int, inv_temp: float, g_lse=None) -> None:
+def replay_tile_stats(logits, targets, replay_ids, stats_compact, tgt_logit, *, vocab_start: int, inv_temp: float,
+                      row_indices=None) -> None:
+    """Restricted-support statistics from id lists: ``replay_ids`` int64 [rows, K<=64] (global ids),
+    ``stats_compact`` fp32 [rows, K, 2] (touched tiles in ascending order, then (-inf, 0) fillers)."""
+    _bf16(logits, "logits"); _rowmajor2d(logits, "logits")
+    rows, K = replay_ids.shape
+    if replay_ids.dtype != torch.int64 or not replay_ids.is_contiguous() or not 0 < K <= 64:
+        raise ValueError("replay_ids must be contiguous int64 [rows, K] with K <= 64")
+    if stats_compact.dtype != torch.float32 or tuple(stats_compact.shape) != (rows, K, 2) or not stats_compact.is_contiguous():
+        raise ValueError("stats_compact must be contiguous fp32 [rows, K, 2]")
+    rc = _lib().rlk_replay_tile_stats(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(targets), ext.ptr(replay_ids),
+                                      c_int(K), ext.ptr(stats_compact), ext.ptr(tgt_logit), c_int(rows),
+                                      c_int(logits.shape[1]), _ll(vocab_start), c_float(inv_temp), ext.ptr(row_indices),
+                                      ext.stream_ptr(logits.device))
+    ext.check(rc, "replay_tile_stats")
+    _count()
+
+
+def dlogits_(logits, targets, lse, g, *, vocab_start: int, inv_temp: float, g_lse=None, min_keep=None) -> None:
     rows, n_local = logits.shape
-    rc = _lib().rlk_dlogits_lse(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(targets), ext.ptr(lse),
-                                ext.ptr(g), ext.ptr(g_lse), c_int(rows), c_int(n_local), _ll(vocab_start),
-                                c_float(inv_temp), ext.stream_ptr(logits.device))
+    _keep(min_keep, rows)
+    rc = _lib().rlk_dlogits_keep(ext.ptr(logits), _ll(logits.stride(0)), ext.ptr(targets), ext.ptr(lse),
+                                 ext.ptr(g), ext.ptr(g_lse), ext.ptr(min_keep), c_int(rows), c_int(n_local),
+                                 _ll(vocab_start), c_float(inv_temp), ext.stream_ptr(logits.device))
     ext.check(rc, "dlogits")
     _count()
 
@@ -607,3 +644,23 @@ def sumsq_bins_f32(grad, bins) -> None:
     rc = _lib().rlk_sumsq_bins_f32(ext.ptr(grad), _ll(grad.numel()), ext.ptr(bins), ext.stream_ptr(grad.device))
     ext.check(rc, "sumsq_bins_f32")
     _count()
+
+
+def rope(x: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, out: torch.Tensor, *, heads: int,
+         head_dim: int, inverse: bool = False) -> torch.Tensor:
+    """NeoX RoPE of x [rows, heads*head_dim] (bf16 or fp32, row stride free) at ``pos`` [rows] int32 from
+    the fp32 tables cos/sin [max_pos, head_dim/2]; ``inverse`` rotates back (the backward).  ``out`` may
+    be ``x``."""
+    if x.dtype not in (torch.bfloat16, torch.float32) or out.dtype != x.dtype:
+        raise TypeError("rope: x and out must both be bf16 or both fp32")
+    if pos.dtype != torch.int32 or not pos.is_contiguous():
+        raise TypeError("rope: pos must be contiguous int32")
+    _f32(cos, "cos"); _f32(sin, "sin")
+    if x.dim() != 2 or out.shape != x.shape or x.stride(1) != 1 or out.stride(1) != 1:
+        raise ValueError("rope: x/out must be 2-D with unit inner stride")
+    rc = _lib().rlk_rope(ext.ptr(x), _ll(x.stride(0)), ext.ptr(pos), ext.ptr(cos), ext.ptr(sin), ext.ptr(out),
+                         _ll(out.stride(0)), _ll(x.shape[0]), c_int(heads), c_int(head_dim), c_int(cos.shape[0]),
+                         c_int(int(inverse)), c_int(0 if x.dtype == torch.bfloat16 else 1), ext.stream_ptr(x.device))
+    ext.check(rc, "rope")
+    _count()
+    return out

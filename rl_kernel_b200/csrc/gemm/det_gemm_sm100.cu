@@ -74,6 +74,7 @@ struct GemmParams {
   long long vocab_start;    // global id of column 0
   float* tgt_logit;         // [M]
   float inv_temp;
+  const float* min_keep;    // [M] or null: a scaled logit below its row's value is outside the support (-inf)
   // vocab-parallel exchange fused into the same epilogue (stats_world > 1): every statistic and
   // the owner's target logit are also stored into the other tensor-parallel ranks' buffers
   // (peer stores over NVLink), so after one barrier every rank holds all tiles of every row.
@@ -464,6 +465,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
           // fused selected-logp statistics: logit = bf16(acc); z = logit * inv_temp
           // (one thread walks all 128 columns of its row: the statistics have a fixed order)
           const long long tgt_col = (p.targets && row < p.M) ? p.targets[row] - p.vocab_start - n0 - cbase : -1;
+          const float keep_from = (p.min_keep && row < p.M) ? p.min_keep[row] : -INFINITY;   // restricted sampling support
           float m = -INFINITY;
 #pragma unroll 1
           for (int col0 = 0; col0 < 128; col0 += 32) {
@@ -472,8 +474,10 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < 32; ++j)
-              if (n0 + cbase + col0 + j < p.N)
-                m = fmaxf(m, logp_scale(round_bf16(__uint_as_float(r[j])), p.inv_temp));
+              if (n0 + cbase + col0 + j < p.N) {
+                const float zj = logp_scale(round_bf16(__uint_as_float(r[j])), p.inv_temp);
+                if (zj >= keep_from) m = fmaxf(m, zj);
+              }
           }
           TileSum ts;
 #pragma unroll 1
@@ -483,8 +487,10 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             tmem_ld_wait();
             float z[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              z[j] = (n0 + cbase + col0 + j < p.N) ? logp_scale(round_bf16(__uint_as_float(r[j])), p.inv_temp) : -INFINITY;
+            for (int j = 0; j < 32; ++j) {
+              const float zj = logp_scale(round_bf16(__uint_as_float(r[j])), p.inv_temp);
+              z[j] = (n0 + cbase + col0 + j < p.N && zj >= keep_from) ? zj : -INFINITY;
+            }
             if (m > -INFINITY) {
 #pragma unroll
               for (int j = 0; j < 32; j += 4) ts.add4(z[j], z[j + 1], z[j + 2], z[j + 3], m);
@@ -1244,7 +1250,7 @@ RLK_API int rlk_det_gemm_split_static(const void* A, const void* B, void* C, int
 // Follow with rlk_logp_merge (after gathering the tiles of the other shards, if any).
 static int lmhead_stats_impl(const void* H, const void* W, int M, int N, int K, long long ldh,
                              long long ldw, const long long* targets, long long vocab_start,
-                             float inv_temp, void* stats, long long stats_stride, float* tgt_logit,
+                             float inv_temp, const float* min_keep, void* stats, long long stats_stride, float* tgt_logit,
                              void* logits_out, long long ld_logits, void* const* stats_ptrs,
                              void* const* tgt_ptrs, int world, int rank, void* stream) {
   using namespace rlk;
@@ -1263,6 +1269,7 @@ static int lmhead_stats_impl(const void* H, const void* W, int M, int N, int K, 
   p.vocab_start = vocab_start;
   p.tgt_logit = tgt_logit;
   p.inv_temp = inv_temp;
+  p.min_keep = min_keep;
   p.stats_world = world > 1 ? world : 0;
   p.stats_rank = rank;
   for (int i = 0; i < 8; ++i) {
@@ -1282,7 +1289,18 @@ RLK_API int rlk_lmhead_logp_stats(const void* H, const void* W, int M, int N, in
                                   float inv_temp, void* stats, long long stats_stride,
                                   float* tgt_logit, void* logits_out, long long ld_logits,
                                   void* stream) {
-  return lmhead_stats_impl(H, W, M, N, K, ldh, ldw, targets, vocab_start, inv_temp, stats, stats_stride,
+  return lmhead_stats_impl(H, W, M, N, K, ldh, ldw, targets, vocab_start, inv_temp, nullptr, stats, stats_stride,
+                           tgt_logit, logits_out, ld_logits, nullptr, nullptr, 1, 0, stream);
+}
+
+// The same with a restricted sampling support: min_keep[row] is the smallest scaled logit
+// (logit * inv_temp) that top-k / top-p kept for that row at rollout time; smaller logits count as
+// -inf in the statistics and in the target logit, exactly as if the logits had been masked first.
+RLK_API int rlk_lmhead_logp_stats_keep(const void* H, const void* W, int M, int N, int K, long long ldh,
+                                       long long ldw, const long long* targets, long long vocab_start,
+                                       float inv_temp, const float* min_keep, void* stats, long long stats_stride,
+                                       float* tgt_logit, void* logits_out, long long ld_logits, void* stream) {
+  return lmhead_stats_impl(H, W, M, N, K, ldh, ldw, targets, vocab_start, inv_temp, min_keep, stats, stats_stride,
                            tgt_logit, logits_out, ld_logits, nullptr, nullptr, 1, 0, stream);
 }
 
@@ -1296,7 +1314,18 @@ RLK_API int rlk_lmhead_logp_stats_vp(const void* H, const void* W, int M, int N,
                                      float inv_temp, void* const* stats_ptrs, long long stats_stride,
                                      void* const* tgt_ptrs, int world, int rank, void* stream) {
   RLK_REQUIRE(world >= 2 && world <= 8 && rank >= 0 && rank < world, "lmhead_logp_stats_vp: world must be 2..8");
-  return lmhead_stats_impl(H, W, M, N, K, ldh, ldw, targets, vocab_start, inv_temp, stats_ptrs[rank],
+  return lmhead_stats_impl(H, W, M, N, K, ldh, ldw, targets, vocab_start, inv_temp, nullptr, stats_ptrs[rank],
+                           stats_stride, static_cast<float*>(tgt_ptrs[rank]), nullptr, 0, stats_ptrs, tgt_ptrs,
+                           world, rank, stream);
+}
+
+RLK_API int rlk_lmhead_logp_stats_vp_keep(const void* H, const void* W, int M, int N, int K, long long ldh,
+                                          long long ldw, const long long* targets, long long vocab_start,
+                                          float inv_temp, const float* min_keep, void* const* stats_ptrs,
+                                          long long stats_stride, void* const* tgt_ptrs, int world, int rank,
+                                          void* stream) {
+  RLK_REQUIRE(world >= 2 && world <= 8 && rank >= 0 && rank < world, "lmhead_logp_stats_vp: world must be 2..8");
+  return lmhead_stats_impl(H, W, M, N, K, ldh, ldw, targets, vocab_start, inv_temp, min_keep, stats_ptrs[rank],
                            stats_stride, static_cast<float*>(tgt_ptrs[rank]), nullptr, 0, stats_ptrs, tgt_ptrs,
                            world, rank, stream);
 }

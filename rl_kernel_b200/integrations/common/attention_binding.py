@@ -3,11 +3,12 @@ contract derived from the layer's config > refusal in strict mode (parity: bind_
 rl_engine/integrations/common/attention_binding.py:597)."""
 from __future__ import annotations
 
-from rl_kernel_b200.contracts.operators.attention import AttentionContract, CPLayout, ShardingSpec
+from rl_kernel_b200.contracts.operators.attention import AttentionContract, CPLayout
 from rl_kernel_b200.runtime.policy import strict_contract_enabled
 
 
-def contract_from_layer(layer, tp_size: int = 1, cp_size: int = 1, cp_layout: str = "zigzag") -> AttentionContract:
+def contract_from_layer(layer, tp_size: int = 1, cp_size: int = 1, cp_layout: str = "zigzag", *, seq_len: int | None = None,
+                        batch_size: int = 1, tp_rank: int = 0, cp_rank: int = 0) -> AttentionContract:
     def pick(*names):
         for n in names:
             if hasattr(layer, n):
@@ -18,7 +19,10 @@ def contract_from_layer(layer, tp_size: int = 1, cp_size: int = 1, cp_layout: st
     hkv = int(pick("num_kv_heads", "num_key_value_heads", "total_num_kv_heads", "num_query_groups"))
     d = int(pick("head_dim", "head_size", "hidden_size_per_attention_head"))
     layout = CPLayout(cp_layout) if cp_size > 1 else CPLayout.NONE
-    return AttentionContract(hq, hkv, d, sharding=ShardingSpec(tp_size, cp_size, layout))
+    if seq_len is None:                      # the binding happens before any batch exists: one canonical block per chunk
+        seq_len = 128 * (2 * cp_size if layout is CPLayout.ZIGZAG else cp_size)
+    return AttentionContract.for_layout(hq, hkv, head_dim=d, seq_len=seq_len, batch_size=batch_size, tp_rank=tp_rank,
+                                        tp_world_size=tp_size, cp_rank=cp_rank, cp_world_size=cp_size, layout=layout)
 
 
 def bind_attention_contracts(layers, *, explicit: AttentionContract | None = None, tp_size: int = 1, cp_size: int = 1,

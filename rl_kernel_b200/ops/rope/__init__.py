@@ -48,15 +48,87 @@ def qk_norm_rope(qkv: torch.Tensor, q_w, k_w, cos, sin, pos, *, hq: int, hkv: in
     return q, k, grp[:, :, g + 1].reshape(T, hkv * d)
 
 
+_TABLES: dict = {}
+
+
+def _tables_for(head_dim: int, theta: float, max_pos: int, device) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 cos/sin tables [max_pos, head_dim/2], cached per (head_dim, theta, device) and grown in powers of two."""
+    key = (int(head_dim), float(theta), str(device))
+    have = _TABLES.get(key)
+    if have is None or have[0].shape[0] < max_pos:
+        n = 4096
+        while n < max_pos:
+            n *= 2
+        cos, sin = rope_tables(head_dim, theta, n, device)
+        have = (cos.contiguous(), sin.contiguous())
+        _TABLES[key] = have
+    return have
+
+
+class _RopeFn(torch.autograd.Function):
+    """y = rotate(x, pos); dx = rotate(dy, -pos) through the same kernel."""
+
+    @staticmethod
+    def forward(ctx, x2, pos, cos, sin, heads, d):
+        from rl_kernel_b200.backends import native as nv
+
+        ctx.save_for_backward(pos, cos, sin)
+        ctx.meta = (heads, d)
+        return nv.rope(x2, pos, cos, sin, torch.empty_like(x2), heads=heads, head_dim=d)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from rl_kernel_b200.backends import native as nv
+
+        pos, cos, sin = ctx.saved_tensors
+        heads, d = ctx.meta
+        dy = dy.contiguous()
+        return nv.rope(dy, pos, cos, sin, torch.empty_like(dy), heads=heads, head_dim=d, inverse=True), None, None, None, None, None
+
+
+def rope(x: torch.Tensor, positions: torch.Tensor, *, theta: float = 1_000_000.0, out_fp32: bool = False) -> torch.Tensor:
+    """NeoX RoPE of ``x`` [..., S, D] at ``positions`` [S] or [B, S] (x then is [B, ..., S, D]); differentiable
+    in ``x``.  Angles come from the shared fp32 table, the math is fp32 and the result is rounded once
+    (``out_fp32`` keeps it in fp32).  Parity: RoPESM90Op / NativeRoPEOp.forward(_fp32)."""
+    D = x.shape[-1]
+    S = x.shape[-2]
+    pos = positions.to(x.device)
+    if pos.shape[-1] != S:
+        raise ValueError(f"positions {tuple(pos.shape)} do not match the sequence axis {S} of x")
+    if pos.dim() == 2 and (x.dim() < 3 or x.shape[0] != pos.shape[0]):
+        raise ValueError("positions [B, S] need x [B, ..., S, D]")
+    max_pos = int(pos.max().item()) + 1 if pos.numel() else 1
+    cos, sin = _tables_for(D, theta, max_pos, x.device)
+    if not use_native(x):
+        xf = x.float()
+        half = D // 2
+        shape = [1] * (x.dim() - 2) + [S, half]
+        if pos.dim() == 2:
+            shape[0] = pos.shape[0]
+        c, s = cos[pos.long()].view(shape), sin[pos.long()].view(shape)
+        a, b = xf[..., :half], xf[..., half:]
+        y = torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+        return y if out_fp32 else y.to(x.dtype)
+    xin = x.float() if (out_fp32 or x.dtype not in (torch.bfloat16, torch.float32)) else x
+    lead = xin.shape[:-1]                                  # [..., S]
+    if pos.dim() == 1:
+        prow = pos.to(torch.int32).expand(lead)
+    else:
+        prow = pos.to(torch.int32).view(pos.shape[0], *([1] * (xin.dim() - 3)), S).expand(lead)
+    y = _RopeFn.apply(xin.reshape(-1, D).contiguous(), prow.reshape(-1).contiguous(), cos, sin, 1, D).view(xin.shape)
+    return y if (out_fp32 or y.dtype == x.dtype) else y.to(x.dtype)
+
+
 class RoPEOp:
+    """Registry object ``rope`` with the reference's call shape ``op(x, positions, theta=...)``."""
     backend_id = "b200"
+    backward_impl = "native"
+    op_class = "elementwise"
 
-    def __init__(self, head_dim: int = 128, theta: float = 1e6, max_pos: int = 4096, device="cpu"):
-        self.cos, self.sin = rope_tables(head_dim, theta, max_pos, device)
-
-    def __call__(self, x, pos):
-        from rl_kernel_b200.reference.rope.rope import apply_rope
-
-        return apply_rope(x.float(), pos, self.cos.to(x.device), self.sin.to(x.device)).to(x.dtype)
+    def __call__(self, x, positions, *, theta: float = 1_000_000.0):
+        return rope(x, positions, theta=theta)
 
     forward = __call__
+
+    def forward_fp32(self, x, positions, *, theta: float = 1_000_000.0):
+        return rope(x, positions, theta=theta, out_fp32=True)

@@ -28,7 +28,7 @@ def tile_stats_reference(logits: torch.Tensor, *, vocab_start: int = 0, inv_temp
     nt_local = (n_local + TILE - 1) // TILE
     t0 = vocab_start // TILE
     total = n_tiles_total if n_tiles_total is not None else t0 + nt_local
-    z = logits.float() * torch.tensor(inv_temp, dtype=torch.float32)
+    z = logits.float() * torch.tensor(inv_temp, dtype=torch.float32, device=logits.device)
     pad = nt_local * TILE - n_local
     if pad:
         z = torch.cat([z, z.new_full((rows, pad), float("-inf"))], dim=1)
@@ -37,11 +37,11 @@ def tile_stats_reference(logits: torch.Tensor, *, vocab_start: int = 0, inv_temp
     e = torch.exp(z - torch.where(torch.isinf(m), torch.zeros_like(m), m).unsqueeze(-1))
     e = torch.where(torch.isinf(m).unsqueeze(-1), torch.zeros_like(e), e)
     chains = e.view(rows, nt_local, TILE // 4, 4)
-    c = torch.zeros(rows, nt_local, 4)
+    c = torch.zeros(rows, nt_local, 4, device=logits.device)
     for j in range(TILE // 4):          # four sequential chains, ascending
         c = c + chains[:, :, j]
     s = (c[..., 0] + c[..., 1]) + (c[..., 2] + c[..., 3])
-    stats = torch.zeros(rows, total, 2)
+    stats = torch.zeros(rows, total, 2, device=logits.device)
     stats[..., 0] = float("-inf")
     stats[:, t0:t0 + nt_local, 0] = m
     stats[:, t0:t0 + nt_local, 1] = s
@@ -65,8 +65,21 @@ def _target_z(logits, targets, vocab_start, inv_temp):
     local = targets.long() - vocab_start
     own = (local >= 0) & (local < logits.shape[1])
     z = logits.float().gather(1, local.clamp(0, logits.shape[1] - 1).unsqueeze(1)).squeeze(1)
-    z = z * torch.tensor(inv_temp, dtype=torch.float32)
+    z = z * torch.tensor(inv_temp, dtype=torch.float32, device=z.device)
     return torch.where(own, z, torch.zeros_like(z)), own
+
+
+def _restrict(lg: torch.Tensor, inv_temp: float, min_keep, keep_mask) -> torch.Tensor:
+    """Logits with everything outside the sampling support set to -inf (fp32 result when restricted)."""
+    if min_keep is None and keep_mask is None:
+        return lg
+    z = lg.float() * torch.tensor(inv_temp, dtype=torch.float32, device=lg.device)
+    keep = torch.ones_like(z, dtype=torch.bool)
+    if min_keep is not None:
+        keep &= z >= min_keep.reshape(-1, 1).to(z.device)
+    if keep_mask is not None:
+        keep &= keep_mask.to(z.device)
+    return lg.float().masked_fill(~keep, float("-inf"))
 
 
 class NativeBatchInvariantLogpOp:
@@ -76,15 +89,18 @@ class NativeBatchInvariantLogpOp:
     def __init__(self, temperature: float = 1.0):
         self.inv_temp = 1.0 / temperature
 
-    def apply_fp32(self, logits, token_ids):
+    def apply_fp32(self, logits, token_ids, *, min_keep=None, keep_mask=None, return_lse: bool = False):
+        """``min_keep`` [rows]: scaled logits below it are outside the support; ``keep_mask`` [rows, V]
+        bool: an explicit support.  Outside the support a logit counts as -inf."""
         shp = token_ids.shape
-        lg = logits.reshape(-1, logits.shape[-1])
+        lg = _restrict(logits.reshape(-1, logits.shape[-1]), self.inv_temp, min_keep, keep_mask)
         stats = tile_stats_reference(lg, inv_temp=self.inv_temp)
         tz, _ = _target_z(lg, token_ids.reshape(-1), 0, self.inv_temp)
-        return merge_tile_stats(stats, tz)[0].view(shp)
+        lp, lse = merge_tile_stats(stats, tz)
+        return (lp.view(shp), lse.view(shp)) if return_lse else lp.view(shp)
 
-    def __call__(self, logits, token_ids):
-        return self.apply_fp32(logits, token_ids)
+    def __call__(self, logits, token_ids, **kw):
+        return self.apply_fp32(logits, token_ids, **kw)
 
     forward = __call__
 
@@ -98,8 +114,8 @@ class NativeLinearLogpOp:
         self.inv_temp = 1.0 / temperature
 
     def __call__(self, hidden, weight, targets, *, vocab_start: int = 0, n_tiles_total=None,
-                 return_stats: bool = False):
-        logits = det_gemm_reference(hidden, weight)
+                 return_stats: bool = False, min_keep=None):
+        logits = _restrict(det_gemm_reference(hidden, weight), self.inv_temp, min_keep, None)
         stats = tile_stats_reference(logits, vocab_start=vocab_start, inv_temp=self.inv_temp,
                                      n_tiles_total=n_tiles_total)
         tz, own = _target_z(logits, targets, vocab_start, self.inv_temp)
@@ -122,7 +138,7 @@ class VocabParallelLogprobOp:
 
     def simulate(self, hidden, weight_shards: list[torch.Tensor], targets, n_tiles_total: int):
         stats = None
-        tz = torch.zeros(hidden.shape[0])
+        tz = torch.zeros(hidden.shape[0], device=hidden.device)
         start = 0
         for w in weight_shards:
             st, z, _ = self.linear(hidden, w, targets, vocab_start=start, n_tiles_total=n_tiles_total,

@@ -28,10 +28,32 @@ def qk_norm_rope_reference(x: torch.Tensor, w: torch.Tensor, pos: torch.Tensor, 
 
 
 class NativeRoPEOp:
-    def __init__(self, head_dim: int, theta: float = 1e6, max_pos: int = 4096):
-        self.cos, self.sin = rope_tables(head_dim, theta, max_pos)
+    """PyTorch NeoX RoPE with the call shape ``op(x [..., S, D], positions [S] | [B, S], theta=...)``
+    (parity: NativeRoPEOp, rl_engine/reference/rope/rope.py:10).  Angles are computed in fp64 and stored
+    in fp32, like every other RoPE in this package; no table is accepted or returned."""
 
-    def __call__(self, x, pos):
-        return apply_rope(x.float(), pos, self.cos.to(x.device), self.sin.to(x.device)).to(x.dtype)
+    op_class = "elementwise"
 
-    forward = __call__
+    def __init__(self, head_dim: int | None = None, theta: float = 1_000_000.0, max_pos: int = 4096):
+        self.theta = theta
+
+    @staticmethod
+    def _cos_sin(x, positions, theta):
+        D, S = x.shape[-1], x.shape[-2]
+        pos = positions.to(x.device).long()
+        cos, sin = rope_tables(D, theta, int(pos.max().item()) + 1 if pos.numel() else 1, x.device)
+        shape = [1] * (x.dim() - 2) + [S, D // 2]
+        if pos.dim() == 2:
+            shape[0] = pos.shape[0]
+        return cos[pos].view(shape), sin[pos].view(shape)
+
+    def forward_fp32(self, x, positions, *, theta: float | None = None):
+        c, s = self._cos_sin(x, positions, self.theta if theta is None else theta)
+        half = x.shape[-1] // 2
+        a, b = x.float()[..., :half], x.float()[..., half:]
+        return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+
+    def forward(self, x, positions, *, theta: float | None = None):
+        return self.forward_fp32(x, positions, theta=theta).to(x.dtype)
+
+    __call__ = forward

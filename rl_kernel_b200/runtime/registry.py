@@ -195,7 +195,7 @@ class KernelRegistry:
                                                                   REFERENCE_ATTENTION_CAPABILITY)
 
         if contract is not None:
-            if contract.sharding.cp_size > 1 and backend == "auto":
+            if contract.sharding.cp_world_size > 1 and backend == "auto":
                 raise ValueError("attention backend 'auto' is not allowed with cp_size > 1; name the CP schedule")
             ready, _ = self.native_ready()
             cap = B200_ATTENTION_CAPABILITY if ready else REFERENCE_ATTENTION_CAPABILITY

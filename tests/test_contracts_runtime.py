@@ -2,10 +2,15 @@
 import pytest
 import torch
 
-from rl_engine.contracts import (AttentionContract, GRPOLossContract, LogprobContract, ShardingSpec,
-                                 resolve_tolerance)
-from rl_engine.contracts.operators.attention import B200_ATTENTION_CAPABILITY, CPLayout, ReductionSpec
-from rl_engine.contracts.operators.logprob import VocabShardingSpec
+from rl_engine.contracts import (AttentionContract, AttentionContractError, GRPOLossContract, LogprobContract,
+                                 LogprobContractError, LossContractError, resolve_tolerance)
+from rl_engine.contracts.operators.attention import (B200_ATTENTION_CAPABILITY, REFERENCE_ATTENTION_CAPABILITY,
+                                                     AttentionMode, CPLayout, KVCacheSpec, ReductionSpec, ShardingSpec,
+                                                     SplitKVSpec, build_split_kv_runtime_plan_set,
+                                                     validate_cross_config_alignment, validate_split_kv_plan_set_alignment)
+from rl_engine.contracts.operators.logprob import (B200_LOGPROB_CAPABILITY, MaskSpec, VocabShardingSpec)
+from rl_engine.contracts.operators.logprob import ShardingSpec as VocabSharding
+from rl_engine.contracts.operators.loss import B200_LOSS_CAPABILITY, KLEstimator
 from rl_engine.runtime.plan import IntegrationPlan
 from rl_engine.runtime.policy import RLKernelMode
 from rl_engine.runtime.registry import KernelRegistry, kernel_registry, resolve_logp_op_type
@@ -19,31 +24,95 @@ def test_alias_package_is_same_module():
     assert a is b and a.kernel_registry is b.kernel_registry
 
 
+def _attn(cp_rank=0, layout=CPLayout.ZIGZAG, tp_rank=0, **kw):
+    return AttentionContract.for_layout(32, 8, seq_len=4096, batch_size=2, tp_rank=tp_rank, tp_world_size=4, cp_rank=cp_rank,
+                                        cp_world_size=2, layout=layout, **kw)
+
+
 def test_attention_contract_validation_and_fingerprint():
-    c1 = AttentionContract(32, 8, sharding=ShardingSpec(4, 2, CPLayout.ZIGZAG))
-    c2 = AttentionContract(32, 8, sharding=ShardingSpec(4, 2, CPLayout.ZIGZAG))
-    c3 = AttentionContract(32, 8, sharding=ShardingSpec(4, 2, CPLayout.CONTIGUOUS))
-    assert c1.cross_rank_fingerprint() == c2.cross_rank_fingerprint() != c3.cross_rank_fingerprint()
-    assert B200_ATTENTION_CAPABILITY.incompatibilities(c1) == []
-    assert B200_ATTENTION_CAPABILITY.incompatibilities(AttentionContract(8, 2, head_dim=64))
-    with pytest.raises(ValueError):
-        ShardingSpec(4, 4, CPLayout.ZIGZAG)           # 16 ranks
-    with pytest.raises(ValueError):
-        ShardingSpec(1, 2, CPLayout.NONE)
-    with pytest.raises(ValueError):
-        ReductionSpec(split_kv=True)
-    with pytest.raises(ValueError):
-        AttentionContract(32, 8, causal=False)
+    c1, c2, c3 = _attn(0), _attn(1, tp_rank=3), _attn(0, CPLayout.CONTIGUOUS)
+    # ranks of one invocation agree; another layout is another invocation only through its block tables,
+    # which are rank-local -- so the rank-independent identity is the same and the local tables differ
+    assert c1.cross_rank_fingerprint() == c2.cross_rank_fingerprint()
+    assert c1.sharding.global_block_indices != c3.sharding.global_block_indices
+    assert c2.sharding.global_block_token_starts[0] == 1024 and c2.sharding.local_sequence_length == 2048
+    assert B200_ATTENTION_CAPABILITY.incompatibilities(c1) == ()
+    assert "head_dim=64 is unsupported" in B200_ATTENTION_CAPABILITY.incompatibilities(
+        AttentionContract.for_layout(8, 2, head_dim=64, seq_len=256))
+    assert REFERENCE_ATTENTION_CAPABILITY.supports(AttentionContract.for_layout(8, 2, head_dim=64, seq_len=256))
+    validate_cross_config_alignment(c1, c3)
+    with pytest.raises(AttentionContractError, match="head layouts"):
+        validate_cross_config_alignment(c1, AttentionContract.for_layout(16, 8, seq_len=4096, batch_size=2))
+    with pytest.raises(AttentionContractError):
+        ShardingSpec.for_layout(num_q_heads=32, num_kv_heads=8, seq_len=1001, cp_world_size=4, layout="zigzag")
+    with pytest.raises(AttentionContractError):
+        ShardingSpec.for_layout(num_q_heads=32, num_kv_heads=8, seq_len=1024, cp_world_size=1, layout="zigzag")
+    with pytest.raises(AttentionContractError):
+        ShardingSpec.for_layout(num_q_heads=32, num_kv_heads=6, seq_len=1024, tp_world_size=4)      # 6 kv heads over TP4
+    with pytest.raises(AttentionContractError):
+        ReductionSpec(acc_dtype="bf16")
+    with pytest.raises(AttentionContractError, match="causal_offsets"):
+        AttentionContract("train", "prefill", "bf16", 1, 128, 128, True, None,
+                          ShardingSpec.for_layout(num_q_heads=8, num_kv_heads=2, seq_len=128))
+    with pytest.raises(AttentionContractError, match="kv_cache"):
+        AttentionContract.for_layout(8, 2, seq_len=128, mode=AttentionMode.DECODE)
+
+
+def test_split_kv_plans_and_paged_cache_identity():
+    with pytest.raises(AttentionContractError):
+        SplitKVSpec.auto(strict_consistency=True)
+    plan = SplitKVSpec.fixed(256).resolve(1000, backend="t")
+    assert plan.boundaries == ((0, 256), (256, 512), (512, 768), (768, 1000)) and plan.actual_split_count == 4
+    assert SplitKVSpec.disabled().resolve(77, backend="t").boundaries == ((0, 77),)
+    a = build_split_kv_runtime_plan_set([1000, 513], tp_world_size=2, cp_world_size=2, split_kv=SplitKVSpec.fixed(256))
+    b = build_split_kv_runtime_plan_set([1000, 513], tp_world_size=2, cp_world_size=2, split_kv=SplitKVSpec.fixed(128))
+    validate_split_kv_plan_set_alignment(a, a)
+    assert len(a.entries) == 2 * 2 * 2 * 2 and a.to_dict()["coverage"].startswith("complete")
+    with pytest.raises(AttentionContractError, match="differs"):
+        validate_split_kv_plan_set_alignment(a, b)
+    kc = KVCacheSpec.contiguous([700, 650], 128, shared_prefix_tokens=512)
+    assert kc.block_table == ((0, 1, 2, 3, 4, 5), (0, 1, 2, 3, 6, 7)) and kc.shared_prefix_page_count == 4
+    with pytest.raises(AttentionContractError, match="shared across sequences"):
+        KVCacheSpec((9, 9), (10, 10), ((0,), (0,)), tuple(range(10)) * 2, 16)                # a writable page used twice
+    with pytest.raises(AttentionContractError, match="trailing"):
+        KVCacheSpec((19,), (20,), ((0, -1, 1),), tuple(range(20)), 16)
+    d = AttentionContract.for_layout(32, 8, seq_len=700, batch_size=2, mode=AttentionMode.DECODE, kv_cache=kc, role="infer")
+    assert B200_ATTENTION_CAPABILITY.supports(d) and d.to_dict()["kv_cache"]["shared_prefix_page_count"] == 4
 
 
 def test_logprob_and_loss_contracts():
-    LogprobContract(sharding=VocabShardingSpec(8, 151936, 152576))
+    c0 = LogprobContract.for_tokens(6, real_vocab_size=151936, padded_vocab_size=152576, tp_rank=0, tp_world_size=8)
+    c5 = LogprobContract.for_tokens(6, real_vocab_size=151936, padded_vocab_size=152576, tp_rank=5, tp_world_size=8)
+    assert c0.cross_rank_fingerprint() == c5.cross_rank_fingerprint() and c0.to_dict() != c5.to_dict()
+    assert c5.sharding.local_vocab_start == 5 * 19072 and c5.sharding.owner_rank(151935) == 7
+    assert B200_LOGPROB_CAPABILITY.incompatibilities(c0) == ()
+    ragged = LogprobContract("train", "bf16", MaskSpec.all_active(4), VocabSharding(0, 2, ((0, 1000), (1000, 2048)), 2000, 2048))
+    assert any("tile boundaries" in w for w in B200_LOGPROB_CAPABILITY.incompatibilities(ragged))
+    with pytest.raises(LogprobContractError, match="contiguous"):
+        VocabSharding(0, 2, ((0, 10), (11, 20)), 20, 20)
+    with pytest.raises(LogprobContractError, match="collide"):
+        LogprobContract("train", "bf16", MaskSpec(2, (True, False), ignore_index=5), VocabSharding.even(
+            tp_rank=0, tp_world_size=1, real_vocab_size=10, padded_vocab_size=10))
+    with pytest.raises(LogprobContractError):
+        MaskSpec(2, (True, 1))
+    with pytest.raises(LogprobContractError):
+        c0.sharding.owner_rank(152000)                        # padding id
     with pytest.raises(ValueError):
-        VocabShardingSpec(8, 151936, 152064)          # tiles would straddle shards
-    with pytest.raises(ValueError):
-        LogprobContract(temperature=0.0)
-    with pytest.raises(ValueError):
-        GRPOLossContract(samples_per_prompt=1)
+        VocabShardingSpec(8, 151936, 152064)                  # tiles would straddle shards
+    with pytest.raises(LogprobContractError):
+        LogprobContract.for_tokens(4, real_vocab_size=100, temperature=0.0)
+    g1 = GRPOLossContract.simple(num_sequences=64, padded_seq_len=16, dp_rank=1, dp_world_size=4, tp_rank=1, tp_world_size=2,
+                                 padded_vocab_size=152576)
+    g0 = GRPOLossContract.simple(num_sequences=64, padded_seq_len=16, dp_rank=0, dp_world_size=4, tp_rank=0, tp_world_size=2,
+                                 padded_vocab_size=152576)
+    assert g0.cross_rank_fingerprint() == g1.cross_rank_fingerprint() and g1.sharding.local_sequence_start == 16
+    assert B200_LOSS_CAPABILITY.incompatibilities(g0) == ()
+    assert B200_LOSS_CAPABILITY.incompatibilities(GRPOLossContract.simple(
+        num_sequences=8, padded_seq_len=4, kl_estimator=KLEstimator.K1_LOG_RATIO)) == ("kl_estimator=k1_log_ratio is unsupported",)
+    with pytest.raises(LossContractError):
+        GRPOLossContract.simple(num_sequences=8, padded_seq_len=4, samples_per_prompt=1)
+    with pytest.raises(LossContractError, match="token slots"):
+        GRPOLossContract(LogprobContract.for_tokens(5, real_vocab_size=100), g0.sharding)
     t = resolve_tolerance("det_gemm", torch.bfloat16)
     gold = torch.randn(4, 64) * 10
     assert t.check(gold * (1 + 1e-3), gold)[0] and not t.check(gold + gold.abs().max() * 0.05, gold)[0]
@@ -72,9 +141,9 @@ def test_registry_resolution_and_provenance(monkeypatch):
     with pytest.raises(KeyError):
         reg.get_op("does_not_exist")
     with pytest.raises(ValueError):
-        reg.get_attention_op("auto", contract=AttentionContract(32, 8, sharding=ShardingSpec(1, 2, CPLayout.ZIGZAG)))
+        reg.get_attention_op("auto", contract=AttentionContract.for_layout(32, 8, seq_len=512, cp_world_size=2, layout="zigzag"))
     assert reg.provenance()[0]["op"] == "det_gemm"
-    assert kernel_registry.get_logprob_op("linear", contract=LogprobContract(temperature=0.7)).inv_temp == pytest.approx(1 / 0.7)
+    assert kernel_registry.get_logprob_op("linear", contract=LogprobContract.for_tokens(4, real_vocab_size=1024, temperature=0.7)).inv_temp == pytest.approx(1 / 0.7)
 
 
 def test_semantic_session_fails_closed():

@@ -450,3 +450,56 @@ def test_ratio_kl_and_single_rank_distributed_loss_match_references():
     loss.backward()
     g_ref = torch.autograd.grad(rl, [], allow_unused=True) if False else None
     assert logp.grad is not None and torch.isfinite(logp.grad).all() and logp.grad[~mask].abs().max().item() == 0.0
+
+
+def test_restricted_support_logp_threshold_replay_and_fused_head_agree_bitwise():
+    """Train-side log-prob under the rollout's top-k / top-p support: (a) from logits with a per-token
+    threshold, (b) the fused LM head with the same threshold in its epilogue, (c) the compact id-list
+    kernel -- all three give the same bits, equal to masking the logits first, and match a PyTorch fp32
+    reference; the gradient is zero outside the support."""
+    from rl_kernel_b200.backends import native as nv
+    from rl_kernel_b200.ops.logprob import linear_logp, logp_from_logits, replay_logp_from_logits
+    from rl_kernel_b200.ops.sampling.policy import keep_threshold
+
+    g = torch.Generator(device="cuda").manual_seed(31)
+    N, H, V = 150, 256, 5000 - 8
+    hidden = torch.randn(N, H, device=dev(), generator=g).bfloat16()
+    w = (torch.randn(V, H, device=dev(), generator=g) * 0.2).bfloat16()
+    logits = torch.empty(N, V, device=dev(), dtype=torch.bfloat16)
+    nv.det_gemm(hidden, w, logits, M=N, N=V, K=H)
+    T = 0.8
+    thr = keep_threshold(logits, temperature=T, top_k=40, top_p=0.9)
+    z = logits.float() / T
+    keep = z >= thr[:, None]
+    counts = keep.sum(1)
+    assert int(counts.min()) >= 1 and int(counts.max()) <= 40
+    # a target inside the support (the most likely kept id, and for odd rows the least likely one)
+    order = z.masked_fill(~keep, float("-inf")).argsort(dim=-1, descending=True)
+    targets = torch.where(torch.arange(N, device=dev()) % 2 == 0, order[:, 0], order.gather(1, (counts - 1)[:, None])[:, 0])
+    lg = logits.clone().requires_grad_(True)
+    a = logp_from_logits(lg, targets, T, min_keep=thr)
+    masked = logits.masked_fill(~keep, float("-inf"))
+    a_masked = logp_from_logits(masked, targets, T)
+    hh = hidden.clone().requires_grad_(True)
+    ww = w.clone().requires_grad_(True)
+    b = linear_logp(hh, ww, targets, T, min_keep=thr)
+    ids = order[:, :64].clone()
+    ids[~keep.gather(1, ids)] = -1                                   # beyond the support: an id no shard owns
+    ids[:, 63] = targets                                              # duplicates are allowed
+    c, c_lse = replay_logp_from_logits(logits, targets, ids, T, return_lse=True)
+    sync_and_check()
+    ref = torch.log_softmax(z.masked_fill(~keep, float("-inf")), -1).gather(1, targets[:, None])[:, 0]
+    assert torch.equal(a.detach(), a_masked) and torch.equal(a.detach(), b.detach()) and torch.equal(a.detach(), c)
+    assert (a.detach() - ref).abs().max().item() < 1e-4
+    assert (c_lse - torch.logsumexp(z.masked_fill(~keep, float("-inf")), -1)).abs().max().item() < 1e-4
+    gout = torch.randn(N, device=dev(), generator=g)
+    a.backward(gout)
+    b.backward(gout)
+    assert lg.grad[~keep].abs().max().item() == 0.0                   # nothing outside the support moves
+    zr = (logits.float() / T).requires_grad_(True)
+    torch.log_softmax(zr.masked_fill(~keep, float("-inf")), -1).gather(1, targets[:, None])[:, 0].backward(gout)
+    assert (lg.grad.float() - zr.grad / T).abs().max().item() < 2e-2
+    assert torch.isfinite(hh.grad).all() and torch.isfinite(ww.grad).all()
+    # a target outside the replay set scores -inf, like the dense masked path
+    bad = order.gather(1, counts[:, None].clamp(max=V - 1))[:, 0]
+    assert torch.isinf(replay_logp_from_logits(logits, bad, ids[:, :63], T)).all()
