@@ -24,50 +24,61 @@ def native_tile_stats_available() -> bool:
 
 
 class _CudaKernels:
-    """The two numeric kernels the contract-driven driver needs."""
+    """The two numeric kernels the contract-driven driver needs (``VocabParallelLogprobKernels``)."""
 
-    @staticmethod
-    def tile_stats(shard: torch.Tensor, vocab_start: int, real_vocab: int, num_tiles: int):
-        """(tile_max, tile_sum) [rows, local tiles] of a bf16 shard whose columns at or beyond the real
-        vocabulary are excluded."""
+    def __init__(self, temperature: float = 1.0):
+        self.inv_temp = 1.0 / temperature
+
+    def tile_stats(self, shard: torch.Tensor, vocab_start: int, real_vocab: int, num_tiles: int):
+        """(tile_max, tile_sum) [rows, num_tiles] of a bf16 shard; columns at or beyond the real vocabulary are
+        excluded."""
         from rl_kernel_b200.backends import native as nv
 
         rows, vl = shard.shape
         keep = max(0, min(vl, real_vocab - vocab_start))
-        nt_local = (vl + TILE - 1) // TILE
-        stats = torch.empty(rows, num_tiles, 2, device=shard.device, dtype=torch.float32)
+        t0 = vocab_start // TILE
+        stats = torch.empty(rows, t0 + num_tiles, 2, device=shard.device, dtype=torch.float32)
         stats[..., 0] = float("-inf")
         stats[..., 1] = 0
-        tl = torch.zeros(rows, device=shard.device, dtype=torch.float32)
         if keep:
-            nv.logits_tile_stats(shard[:, :keep], None, stats, tl, vocab_start=vocab_start, inv_temp=1.0)
-        t0 = vocab_start // TILE
-        return stats[:, t0:t0 + nt_local, 0].contiguous(), stats[:, t0:t0 + nt_local, 1].contiguous()
+            tl = torch.zeros(rows, device=shard.device, dtype=torch.float32)
+            nv.logits_tile_stats(shard[:, :keep], None, stats, tl, vocab_start=vocab_start, inv_temp=self.inv_temp)
+        return stats[:, t0:, 0].contiguous(), stats[:, t0:, 1].contiguous()
 
-    @staticmethod
-    def backward(shard: torch.Tensor, targets: torch.Tensor, lse: torch.Tensor, grad_logp: torch.Tensor,
-                 grad_lse: torch.Tensor | None, vocab_start: int, real_vocab: int) -> torch.Tensor:
+    def backward(self, shard: torch.Tensor, lse: torch.Tensor, coef_logp: torch.Tensor, coef_lse: torch.Tensor,
+                 target_local: torch.Tensor, vocab_start: int, real_vocab: int, has_lse_grad: bool) -> torch.Tensor:
         from rl_kernel_b200.backends import native as nv
 
         rows, vl = shard.shape
         keep = max(0, min(vl, real_vocab - vocab_start))
         d = torch.zeros_like(shard)
         if keep:
-            d[:, :keep] = shard[:, :keep]
-            view = d[:, :keep]
-            nv.dlogits_(view, targets.contiguous(), lse.contiguous(), grad_logp.float().contiguous(), vocab_start=vocab_start,
-                        inv_temp=1.0, g_lse=None if grad_lse is None else grad_lse.float().contiguous())
+            work = shard[:, :keep].contiguous()
+            # the kernel locates the target by its GLOBAL id; rows whose target lives elsewhere get an id no column has
+            tg = torch.where(target_local >= 0, target_local + vocab_start, torch.full_like(target_local, -1)).contiguous()
+            nv.dlogits_(work, tg, lse.contiguous(), coef_logp.contiguous(), vocab_start=vocab_start, inv_temp=self.inv_temp,
+                        g_lse=coef_lse.contiguous() if has_lse_grad else None)
+            d[:, :keep] = work
         return d
 
 
 class CudaVocabParallelLogprobOp(VocabParallelLogprobOp):
     backend_id = "b200-vocab-parallel-logp"
+    last_route = None
 
-    def apply(self, local_logits, target_ids, contract, *, tp_group=None, **kw):
+    def apply(self, local_logits, target_ids, *, contract, tp_group=None, num_vocab_tiles=None, validate: bool = True,
+              deterministic: bool = True):
         usable = (native_tile_stats_available() and local_logits.is_cuda and local_logits.dtype == torch.bfloat16
-                  and contract.sharding.local_vocab_start % TILE == 0 and local_logits.shape[1] % 8 == 0)
+                  and num_vocab_tiles is None and contract.numerics.tile == TILE
+                  and contract.sharding.local_vocab_start % TILE == 0 and local_logits.shape[1] % 8 == 0
+                  and local_logits.is_contiguous())
         if not usable:
             self.last_route = "pytorch"
-            return super().apply(local_logits, target_ids, contract, tp_group=tp_group, **kw)
+            return super().apply(local_logits, target_ids, contract=contract, tp_group=tp_group,
+                                 num_vocab_tiles=num_vocab_tiles, validate=validate, deterministic=deterministic)
         self.last_route = "b200"
-        return apply_with_kernels(local_logits, target_ids, contract, _CudaKernels, tp_group=tp_group, **kw)
+        return apply_with_kernels(local_logits, target_ids, contract=contract, tp_group=tp_group,
+                                  num_vocab_tiles=num_vocab_tiles, validate=validate,
+                                  kernels=_CudaKernels(contract.numerics.temperature))
+
+    __call__ = apply

@@ -1,0 +1,1 @@
+"""Package extension point; implementations are registered explicitly."""

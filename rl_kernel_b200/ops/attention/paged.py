@@ -126,3 +126,114 @@ def paged_attention(q: torch.Tensor, cache: PagedKVCache, seqs: list[int], q_pos
         nv.attn_fwd(q2, k_list, v_list, o2, lse, tiles, scale, page_table=table)
         out = o2.view(T, hq, d)
     return (out, lse) if return_lse else out
+
+
+def write_kv_slots(k_pool: torch.Tensor, v_pool: torch.Tensor, key: torch.Tensor, value: torch.Tensor,
+                   slot_mapping: torch.Tensor) -> None:
+    """Store the new tokens' K/V rows [T, Hkv * D] at flat pool rows ``slot_mapping`` [T] (negative = padding token:
+    skipped).  Pools are [num_pages * 128, Hkv * D] views of the cache."""
+    slots = slot_mapping.reshape(-1).long()
+    key, value = key.reshape(key.shape[0], -1), value.reshape(value.shape[0], -1)
+    if key.is_cuda and (key.shape[1] * key.element_size()) % 16 == 0 and key.stride(1) == 1 and value.stride(1) == 1:
+        from rl_kernel_b200.ops.packing import _move
+
+        _move(key, slots.contiguous(), k_pool, True)       # the kernel skips indices outside [0, rows)
+        _move(value, slots.contiguous(), v_pool, True)
+        return
+    ok = slots >= 0
+    k_pool[slots[ok]] = key[ok]
+    v_pool[slots[ok]] = value[ok]
+
+
+def paged_attention_block_table(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, block_table: torch.Tensor,
+                                seq_lens, query_start_loc, *, num_kv_heads: int, scale: float | None = None,
+                                out: torch.Tensor | None = None, return_lse: bool = False,
+                                peer_pools: tuple[list[torch.Tensor], list[torch.Tensor]] | None = None):
+    """Causal attention of a continuous batch over a block-table KV cache (the metadata a serving engine keeps).
+
+    q [T, Hq, D]: the new tokens of all requests back to back; request i owns rows
+    ``query_start_loc[i]:query_start_loc[i+1]`` and its cache (new tokens included) holds ``seq_lens[i]`` tokens, so its
+    queries sit at positions ``seq_lens[i] - n_i .. seq_lens[i] - 1``.  ``block_table`` [B, max_blocks] int32 lists the
+    128-token pages of every request (-1 padded; entries may carry an owner rank in bits 24+ together with
+    ``peer_pools``).  ``seq_lens`` / ``query_start_loc`` are host sequences (a serving engine has them on the CPU).
+    Decode rows (one new token) and prefill chunks may be mixed in one call."""
+    T, hq, d = q.shape
+    hkv, g = num_kv_heads, hq // num_kv_heads
+    scale = scale if scale is not None else 1.0 / math.sqrt(d)
+    lens = [int(x) for x in (seq_lens.tolist() if isinstance(seq_lens, torch.Tensor) else seq_lens)]
+    qsl = [int(x) for x in (query_start_loc.tolist() if isinstance(query_start_loc, torch.Tensor) else query_start_loc)]
+    B, maxb = block_table.shape
+    if len(lens) != B or len(qsl) != B + 1:
+        raise ValueError("seq_lens needs one entry and query_start_loc one boundary more than the block table has rows")
+    if not q.is_cuda:
+        return _paged_reference(q, k_pool, v_pool, block_table, lens, qsl, hkv, scale, out, return_lse)
+    from rl_kernel_b200.backends import native as nv
+
+    if d != 128:
+        raise ValueError("head_dim must be 128")
+    table = block_table.to(torch.int32).contiguous().view(-1)          # row i starts at i * max_blocks
+    decode_rows, prefill_rows = [], []
+    for i in range(B):
+        n, t0 = qsl[i + 1] - qsl[i], qsl[i]
+        if n == 0:
+            continue
+        p0 = lens[i] - n
+        if p0 < 0:
+            raise ValueError(f"request {i}: {n} query tokens but only {lens[i]} cached")
+        if n == 1:
+            for hk in range(hkv):
+                r0 = t0 * hq + hk * g
+                decode_rows.append([r0, 0, g, 0, hk * d, p0, 0, lens[i], r0, 1, 0, i * maxb + 1])
+        else:
+            for qt in range((n + 127) // 128 - 1, -1, -1):
+                for h in range(hq):
+                    r0 = t0 + qt * 128
+                    prefill_rows.append([r0, h * d, min(128, n - qt * 128), 0, (h // g) * d, p0 + qt * 128, 1, lens[i],
+                                         r0 * hq + h, hq, 0, i * maxb + 1])
+    k_list, v_list = peer_pools if peer_pools is not None else ([k_pool], [v_pool])
+    o = out.view(T, hq, d) if out is not None else torch.empty_like(q)
+    lse = torch.empty(T, hq, device=q.device, dtype=torch.float32)
+    if decode_rows:                      # the GQA group's heads are the rows of one tile: q viewed as [T * Hq, D]
+        tiles = torch.tensor(decode_rows, dtype=torch.int32, device=q.device)
+        q2 = torch.zeros(T * hq + 128, d, device=q.device, dtype=q.dtype)
+        q2[: T * hq] = q.reshape(T * hq, d)
+        o2 = torch.empty_like(q2)
+        nv.attn_fwd(q2, k_list, v_list, o2, lse, tiles, scale, decode=g <= 8, page_table=table)
+        if prefill_rows:
+            sel = torch.tensor(sorted({r[0] // hq for r in decode_rows}), device=q.device)
+            o[sel] = o2[: T * hq].view(T, hq, d)[sel]
+        else:
+            o.copy_(o2[: T * hq].view(T, hq, d))
+    if prefill_rows:
+        tiles = torch.tensor(prefill_rows, dtype=torch.int32, device=q.device)
+        q2 = q.reshape(T, hq * d).contiguous()
+        o2 = torch.empty_like(q2) if decode_rows else o.view(T, hq * d)
+        lse2 = torch.empty_like(lse) if decode_rows else lse
+        nv.attn_fwd(q2, k_list, v_list, o2, lse2, tiles, scale, page_table=table)
+        if decode_rows:
+            rows = torch.cat([torch.arange(qsl[i], qsl[i + 1]) for i in range(B) if qsl[i + 1] - qsl[i] > 1]).to(q.device)
+            o[rows] = o2.view(T, hq, d)[rows]
+            lse[rows] = lse2[rows]
+    return (o, lse) if return_lse else o
+
+
+def _paged_reference(q, k_pool, v_pool, block_table, lens, qsl, hkv, scale, out, return_lse):
+    """The same semantics with gathered pages and the PyTorch attention (CPU, tests)."""
+    from rl_kernel_b200.reference.attention.standard_attn import NativeAttentionOp
+
+    T, hq, d = q.shape
+    o = out.view(T, hq, d) if out is not None else torch.empty_like(q)
+    lse = torch.zeros(T, hq)
+    op = NativeAttentionOp()
+    for i in range(len(lens)):
+        n = qsl[i + 1] - qsl[i]
+        if n == 0:
+            continue
+        pages = (block_table[i, : (lens[i] + PAGE - 1) // PAGE].long() & 0xFFFFFF)
+        rows = (pages[:, None] * PAGE + torch.arange(PAGE)[None]).reshape(-1)[: lens[i]]
+        k = k_pool[rows].view(1, lens[i], hkv, d)
+        v = v_pool[rows].view(1, lens[i], hkv, d)
+        oi, li = op(q[qsl[i]:qsl[i + 1]].unsqueeze(0), k, v, causal=True, scale=scale, q_pos0=lens[i] - n, return_lse=True)
+        o[qsl[i]:qsl[i + 1]] = oi[0]
+        lse[qsl[i]:qsl[i + 1]] = li[0]
+    return (o, lse) if return_lse else o

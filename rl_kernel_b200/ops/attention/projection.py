@@ -35,16 +35,59 @@ class _TPCopy(torch.autograd.Function):
         return (c.all_reduce(g.contiguous()) if c is not None else g), None
 
 
+class _SPAllGather(torch.autograd.Function):
+    """Sequence parallelism, entering a column-parallel GEMM.  Forward: rank-ordered all-gather of the token
+    rows [T / tp, H] -> [T, H]; backward: fixed-tree reduce-scatter of the partial input gradients, which is
+    the all-reduce of ``_TPCopy`` with every rank keeping only its rows."""
+
+    @staticmethod
+    def forward(ctx, x, collective):
+        ctx.collective = collective
+        if collective is None:
+            return x
+        return collective.all_gather(x.contiguous()).reshape(-1, *x.shape[1:])
+
+    @staticmethod
+    def backward(ctx, g):
+        c = ctx.collective
+        return (c.reduce_scatter(g.contiguous()) if c is not None else g), None
+
+
+class _SPReduceScatter(torch.autograd.Function):
+    """Sequence parallelism, leaving a row-parallel GEMM.  Forward: fixed-tree reduce-scatter of the partial
+    outputs (each rank keeps its [T / tp, H] rows of the sum ``_TPAllReduce`` would give); backward: all-gather."""
+
+    @staticmethod
+    def forward(ctx, x, collective):
+        ctx.collective = collective
+        return collective.reduce_scatter(x.contiguous()) if collective is not None else x
+
+    @staticmethod
+    def backward(ctx, g):
+        c = ctx.collective
+        return (c.all_gather(g.contiguous()).reshape(-1, *g.shape[1:]) if c is not None else g), None
+
+
 class AttentionProjectionOp:
-    def __init__(self, canonical_tp: int = 8, tp_size: int = 1, collective=None):
+    """``sequence_parallel``: activations outside the projections are sharded by token rows over the TP group
+    (all-gather before the QKV GEMM, reduce-scatter after the output GEMM; parity: the SP branches of
+    rl_engine/ops/attention/projection.py:35-130).  The sums are the same trees as without it, so the bits of
+    every token row are unchanged."""
+
+    def __init__(self, canonical_tp: int = 8, tp_size: int = 1, collective=None, sequence_parallel: bool = False):
         if canonical_tp % tp_size:
             raise ValueError("tp_size must divide canonical_tp")
+        if sequence_parallel and (tp_size == 1 or collective is None):
+            raise ValueError("sequence parallelism needs a tensor-parallel group")
         self.nchunks = canonical_tp // tp_size
         self.collective = collective if tp_size > 1 else None
+        self.sequence_parallel = sequence_parallel
 
     def qkv(self, hidden: torch.Tensor, w_qkv_local: torch.Tensor) -> torch.Tensor:
-        return det_gemm_linear(_TPCopy.apply(hidden, self.collective), w_qkv_local)
+        enter = _SPAllGather if self.sequence_parallel else _TPCopy
+        return det_gemm_linear(enter.apply(hidden, self.collective), w_qkv_local)
 
     def output(self, attn_local: torch.Tensor, w_o_local: torch.Tensor) -> torch.Tensor:
         partial = det_gemm_linear(attn_local, w_o_local, self.nchunks)
-        return _TPAllReduce.apply(partial, self.collective)
+        leave = _SPReduceScatter if self.sequence_parallel else _TPAllReduce
+        return leave.apply(partial, self.collective)
