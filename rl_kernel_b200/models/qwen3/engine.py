@@ -354,6 +354,11 @@ class Qwen3Engine:
         # head's input gradient over canonical vocabulary chunks.  With them every gradient of a
         # tensor-parallel run equals the single-GPU gradient bit for bit.
         self.canonical_grads = True
+        # Under context parallelism the same holds for every parameter: the per-token operands of a gradient are
+        # brought into logical token order and each CP rank computes a row slice of the gradient over ALL tokens
+        # (distributed/algorithms/canonical_cp.py); the LM head runs vocabulary-parallel over the CP group.  The
+        # rows a rank does not own stay zero, so the sum over the CP group assembles the exact single-GPU gradient.
+        self.cp_canonical_grads = True
         self.cp = None                               # CPAttention once enable_context_parallel ran
         self._decode_page_table = None               # set while a paged decode step runs
         self._decode_shared = None                   # SharedPrefixKV whose prompt blocks are attended per group
@@ -372,6 +377,62 @@ class Qwen3Engine:
         if self.ctx.cp_size > 1 and self.cp is None:
             self.cp = CPAttention(self.ctx.cp_collective, self.dev, num_q_heads=self.hq, num_kv_heads=self.hkv,
                                   max_local_tokens=max_local_tokens, layout=layout)
+
+    # -------------------------------------------------------------------------- canonical CP gradients
+    @property
+    def _cp_canon(self) -> bool:
+        return self.cp is not None and self.canonical_grads and self.cp_canonical_grads
+
+    def _cp_order(self, nseq: int, S: int) -> torch.Tensor:
+        """Row of the rank-major gathered token tensor that holds logical token (sequence, position)."""
+        key = ("cp_order", nseq, S)
+        if key not in self._tiles:
+            from rl_kernel_b200.distributed.algorithms.canonical_cp import uniform_gather_indices
+
+            self._tiles[key] = (uniform_gather_indices(nseq, S, self.ctx.cp_size, self.cp.layout).to(self.dev), None)
+        return self._tiles[key][0]
+
+    def _cp_gather(self, t: torch.Tensor, name: str, cp_geom) -> torch.Tensor:
+        """t [T_local, C] of this rank's tokens -> [nseq * S, C] of all tokens in logical order."""
+        nseq, S = cp_geom
+        g = self.ctx.cp_collective.all_gather(t.contiguous())            # [cp, T_local, C], bits unchanged
+        out = self.ws.get(name, (nseq * S, t.shape[1]), t.dtype)
+        torch.index_select(g.view(-1, t.shape[1]), 0, self._cp_order(nseq, S), out=out)
+        return out
+
+    def _cp_rows(self, n_rows: int) -> tuple[int, int]:
+        """The rows of an [n_rows, *] gradient this CP rank computes (equal slices on 128-row boundaries)."""
+        cp, r = self.ctx.cp_size, self.ctx.cp_rank
+        per = -(-(-(-n_rows // cp)) // 128) * 128
+        lo = min(n_rows, r * per)
+        return lo, min(n_rows, lo + per)
+
+    def _dw(self, dy, x, grad, *, M: int, N: int, T: int, cp_geom=None) -> None:
+        """grad [M, N] += dy [T, M]^T @ x [T, N], tokens reduced in logical order."""
+        if cp_geom is None or not self._cp_canon:
+            self._gemm(dy, x, grad, a_mn=True, b_mn=True, accumulate=True, M=M, N=N, K=T)
+            return
+        dyg = self._cp_gather(dy, "cpg.dy", cp_geom)
+        xg = self._cp_gather(x, "cpg.x", cp_geom)
+        lo, hi = self._cp_rows(M)
+        if hi > lo:
+            self._gemm(dyg[:, lo:hi], xg, grad[lo:hi], a_mn=True, b_mn=True, accumulate=True, M=hi - lo, N=N,
+                       K=dyg.shape[0])
+
+    def _gain_bwd(self, x, w, dy, dx, scr, eps, grad, *, dres=None, owner: int = 0, cp_geom=None) -> None:
+        """RMSNorm backward; the gain gradient is accumulated into ``grad`` (under canonical CP by one owner rank,
+        from the gathered rows in logical order; the owner rotates over the norms to spread the extra pass)."""
+        if cp_geom is None or not self._cp_canon:
+            nv.rmsnorm_bwd(x, w, dy, dx, scr, eps, dres=dres, dw_bf16=grad, accumulate_dw=True)
+            return
+        H = x.shape[1]
+        nv.rmsnorm_bwd(x, w, dy, dx, scr, eps, dres=dres, dw_bf16=self.ws.get("cpg.dw_dummy", (H,)), accumulate_dw=False)
+        xg = self._cp_gather(x, "cpg.nx", cp_geom)
+        dyg = self._cp_gather(dy, "cpg.ndy", cp_geom)
+        if owner % self.ctx.cp_size == self.ctx.cp_rank:
+            Tg = xg.shape[0]
+            scr_g = self.ws.get("cpg.scr", (nv.rmsnorm_bwd_scratch_elems(Tg, H),), torch.float32)
+            nv.rmsnorm_bwd(xg, w, dyg, self.ws.get("cpg.ndx", (Tg, H)), scr_g, eps, dw_bf16=grad, accumulate_dw=True)
 
     # -------------------------------------------------------------------------- helpers
     def _gemm(self, a, b, out, *, a_mn=False, b_mn=False, nchunks=1, accumulate=False, M=None, N=None, K=None):
@@ -524,22 +585,20 @@ class Qwen3Engine:
         keep["act"] = self.ws.get("r.act", (T, self.p.i_local))
         nv.swiglu_fwd(keep["gu"], keep["act"], self.p.i_local, self.blk)
 
-    def _mlp_bwd(self, l: int, ds: torch.Tensor, keep: dict, T: int) -> torch.Tensor:
+    def _mlp_bwd(self, l: int, ds: torch.Tensor, keep: dict, T: int, cp_geom=None) -> torch.Tensor:
         """Backward of ``_mlp_fwd``: ``ds`` = d(loss)/d(output) -> d(loss)/d(h2), summed over TP;
         weight gradients are accumulated."""
         w, g, ws, H = self.p.w, self.p.g, self.ws, self.spec.hidden_size
         dact = ws.get("b.dact", (T, self.p.i_local))
         self._gemm(ds, w[f"l{l}.wd"], dact, b_mn=True, M=T, N=self.p.i_local, K=H)
-        self._gemm(ds, keep["act"], g[f"l{l}.wd"], a_mn=True, b_mn=True, accumulate=True,
-                   M=H, N=self.p.i_local, K=T)
+        self._dw(ds, keep["act"], g[f"l{l}.wd"], M=H, N=self.p.i_local, T=T, cp_geom=cp_geom)
         dgu = ws.get("b.dgu", (T, 2 * self.p.i_local))
         nv.swiglu_bwd(keep["gu"], dact, dgu, self.p.i_local, self.blk)
         dh2 = ws.get("b.dh", (T, H))
         self._gemm(dgu, w[f"l{l}.wgu"], dh2, b_mn=True, nchunks=self.nchunks, M=T, N=H,
                    K=2 * self.p.i_local)
         self.ctx.tp_all_reduce_(dh2)
-        self._gemm(dgu, keep["h2"], g[f"l{l}.wgu"], a_mn=True, b_mn=True, accumulate=True,
-                   M=2 * self.p.i_local, N=H, K=T)
+        self._dw(dgu, keep["h2"], g[f"l{l}.wgu"], M=2 * self.p.i_local, N=H, T=T, cp_geom=cp_geom)
         return dh2
 
     def _attention(self, q2d, k2d, v2d, o2d, lse, tiles, decode: bool = False):
@@ -778,6 +837,10 @@ class Qwen3Engine:
             # every layer (about 100 KB per token and layer at Qwen3-8B width)
             st.extra["stored"], st.extra["keeps"] = True, []
         hf = self.forward_hidden(tok_local, save=st, cp_seq_len=S if cp else None, stage_in=stage_in)
+        if self._cp_canon:
+            logp_local, dhf = self._head_cp_canonical(hf, tokens, resp_start, dlogp_fn, temperature, lm_chunk, sel, ridx)
+            self.stage_input_grad = self._backward(st, tok_local, dhf)
+            return logp_local
         hf3 = hf.view(nseq, Sl, H)
         rows = self.ws.get("lm.rows", (nseq * R, H))
         if cp:
@@ -837,6 +900,91 @@ class Qwen3Engine:
         self.stage_input_grad = self._backward(st, tok_local, dhf)   # None unless a pipeline stage
         return logp.view(nseq, R)
 
+    def _head_cp_canonical(self, hf, tokens, resp_start: int, dlogp_fn, temperature: float, lm_chunk: int, sel, ridx):
+        """LM head of a context-parallel micro-batch with layout-invariant results.
+
+        The final hidden rows of ALL ranks are gathered into logical order, so the head sees exactly the rows a single
+        GPU would; the vocabulary shard of this tensor-parallel rank is split once more over the CP ranks, and every
+        rank computes the statistics, d(logits) and the weight-gradient rows of its slice for all rows.  Tile
+        statistics are exchanged unchanged and merged in ascending tile order; the input gradient sums the canonical
+        vocabulary chunks in the fixed tree (inside the kernel, then over the CP group, then over the TP group).
+        Returns (logp [nseq, R_local] of this rank's scored positions, d(final hidden) [nseq * S_local, H])."""
+        nseq, S = tokens.shape
+        H, ws = self.spec.hidden_size, self.ws
+        cpc, cp, c = self.ctx.cp_collective, self.ctx.cp_size, self.ctx.cp_rank
+        Sl = S // cp
+        R = S - resp_start
+        n = nseq * R
+        inv_t = 1.0 / temperature
+        hf_g = self._cp_gather(hf, "cpg.hf", (nseq, S)).view(nseq, S, H)
+        rows = ws.get("lm.rows_g", (n, H))
+        rows.view(nseq, R, H).copy_(hf_g[:, resp_start - 1:S - 1])
+        targets = tokens[:, resp_start:].reshape(-1).contiguous()
+        # ---- this rank's vocabulary slice of the TP shard
+        if self.p.v_local % (cp * VOCAB_TILE) or self.nchunks % cp:
+            raise ValueError("the padded vocabulary shard must split into cp slices of whole 128-id tiles and chunks")
+        vs = self.p.v_local // cp
+        v0 = c * vs
+        vreal = max(0, min(vs, self.p.v_real_local - v0))
+        gstart = self.p.vocab_start + v0                       # first global id of the slice
+        w_slice = self.p.w["lm_head"][v0:v0 + vs]
+        g_slice = self.p.g["lm_head"][v0:v0 + vs]
+        nch = self.nchunks // cp
+        ntile, nts = self.spec.num_vocab_tiles, vs // VOCAB_TILE
+        logp = torch.empty(n, dtype=torch.float32, device=self.dev)
+        lse = torch.empty(n, dtype=torch.float32, device=self.dev)
+        # ---- pass 1: tile statistics of the slice, exchanged over CP and TP, merged in tile order
+        for r0 in range(0, n, lm_chunk):
+            r1 = min(n, r0 + lm_chunk)
+            m = r1 - r0
+            stats = ws.get("lm.stats_s", (m, nts, 2), torch.float32)
+            stats[..., 0] = float("-inf")
+            stats[..., 1] = 0
+            tl = ws.get("lm.tl_s", (m,), torch.float32)
+            tl.zero_()
+            if vreal > 0:
+                # the kernel indexes tiles globally: hand it a view that starts at tile 0 of this slice
+                full = ws.get("lm.stats_f", (m, ntile, 2), torch.float32)
+                nv.lmhead_logp_stats(rows[r0:r1], w_slice[:vreal], targets[r0:r1], full, tl, vocab_start=gstart,
+                                     inv_temp=inv_t)
+                t0 = gstart // VOCAB_TILE
+                nlive = (vreal + VOCAB_TILE - 1) // VOCAB_TILE
+                stats[:, :nlive] = full[:, t0:t0 + nlive]
+            shard = cpc.all_gather(stats).permute(1, 0, 2, 3).reshape(m, cp * nts, 2)        # this TP shard's tiles
+            tls = cpc.all_gather(tl).sum(0)
+            if self.ctx.tp_size > 1:
+                shard = self.ctx.tp_all_gather(shard.contiguous()).permute(1, 0, 2, 3).reshape(m, ntile, 2)
+                tls = self.ctx.tp_all_gather(tls).sum(0)
+            nv.logp_merge(shard.contiguous(), tls.contiguous(), logp[r0:r1], lse[r0:r1])
+        logp_local = logp.view(nseq, R)[:, ridx].contiguous()
+        dlogp_local = dlogp_fn(logp_local)
+        dlogp = torch.zeros(nseq, R, dtype=torch.float32, device=self.dev)
+        dlogp[:, ridx] = dlogp_local.float()
+        cpc.all_reduce_(dlogp)                                   # every column has one owner: exact
+        dlogp = dlogp.reshape(-1)
+        # ---- pass 2: logits of the slice -> d(logits) -> d(rows) (canonical chunks), dW rows of the slice
+        drows = ws.get("lm.drows_g", (n, H))
+        lbuf = ws.get("lm.logits_s", (min(n, lm_chunk), vs))
+        if vreal < vs:
+            lbuf[:, vreal:].zero_()
+        for r0 in range(0, n, lm_chunk):
+            r1 = min(n, r0 + lm_chunk)
+            m = r1 - r0
+            if vreal > 0:
+                logits = lbuf[:m, :vreal]
+                self._gemm(rows[r0:r1], w_slice[:vreal], logits)
+                nv.dlogits_(logits, targets[r0:r1], lse[r0:r1], dlogp[r0:r1], vocab_start=gstart, inv_temp=inv_t)
+                self._gemm(lbuf[:m], w_slice, drows[r0:r1], b_mn=True, nchunks=nch, M=m, N=H, K=vs)
+                self._gemm(logits, rows[r0:r1], g_slice[:vreal], a_mn=True, b_mn=True, accumulate=True, M=vreal, N=H, K=m)
+            else:
+                drows[r0:r1].zero_()
+        cpc.all_reduce_(drows)
+        self.ctx.tp_all_reduce_(drows)
+        dhf = ws.get("b.dhf", (nseq * Sl, H))
+        dhf.zero_()
+        dhf.view(nseq, Sl, H).index_copy_(1, sel, drows.view(nseq, R, H)[:, ridx])
+        return logp_local, dhf
+
     def _backward(self, st: TrainState, tokens: torch.Tensor, dhf: torch.Tensor | None,
                   ds_in: torch.Tensor | None = None) -> torch.Tensor | None:
         """Backward of this stage's layers.  Last stage: ``dhf`` is the gradient of the final-norm
@@ -854,11 +1002,14 @@ class Qwen3Engine:
         scr = ws.get("b.scr", (max(nv.rmsnorm_bwd_scratch_elems(T, H), nv.qk_norm_rope_bwd_scratch_elems(T)),),
                      torch.float32)
         ds = ws.get("b.ds", (T, H))          # gradient of the residual stream
+        cg = cp_geom if self._cp_canon else None
         if self.last_stage:
             # final norm: s_fin -> hf
-            nv.rmsnorm_bwd(st.final_s, w["norm"], dhf, ds, scr, eps, dw_bf16=g["norm"], accumulate_dw=True)
+            self._gain_bwd(st.final_s, w["norm"], dhf, ds, scr, eps, g["norm"], owner=0, cp_geom=cg)
         else:
             ds.copy_(ds_in)
+        if cg is not None and self.ctx.tp_size > 1 and self.l1 > self.l0:
+            self._qk_stage().zero_()                 # only the owner of a layer writes its row
         if cp:
             # peers read these while computing their dK / dV
             lse, delta = self.cp.bufs.local("lse"), self.cp.bufs.local("delta")
@@ -888,15 +1039,14 @@ class Qwen3Engine:
                 self._layer_fwd(l, ck, None, T, pos, tiles=tiles, kbuf=kb, vbuf=vb, lse=lse,
                                 keep=keep, tag="r", cp_geom=cp_geom)
             # ---- MLP backward.  s_out = s_mid + down  =>  d(down) = ds, d(s_mid) += ds
-            dh2 = self._mlp_bwd(l, ds, keep, T)
+            dh2 = self._mlp_bwd(l, ds, keep, T, cg)
             ds2 = ws.get("b.ds2", (T, H))
-            nv.rmsnorm_bwd(keep["s_mid"], w[f"l{l}.ln2"], dh2, ds2, scr, eps, dres=ds,
-                           dw_bf16=g[f"l{l}.ln2"], accumulate_dw=True)
+            self._gain_bwd(keep["s_mid"], w[f"l{l}.ln2"], dh2, ds2, scr, eps, g[f"l{l}.ln2"], dres=ds,
+                           owner=2 * l + 1, cp_geom=cg)
             # ---- attention block backward.  s_mid = s_in + o  =>  d(o) = ds2
             dattn = self.cp.bufs.local("do")[:T] if cp else ws.get("b.dattn", (T, self.p.q_local))
             self._gemm(ds2, w[f"l{l}.wo"], dattn, b_mn=True, M=T, N=self.p.q_local, K=H)
-            self._gemm(ds2, keep["attn"], g[f"l{l}.wo"], a_mn=True, b_mn=True, accumulate=True,
-                       M=H, N=self.p.q_local, K=T)
+            self._dw(ds2, keep["attn"], g[f"l{l}.wo"], M=H, N=self.p.q_local, T=T, cp_geom=cg)
             nv.attn_bwd_delta(keep["attn"], dattn, delta, T, self.hq)
             dq = ws.get("b.dq", (T, self.p.q_local))
             dk = ws.get("b.dk", (T, self.p.kv_local))
@@ -912,9 +1062,28 @@ class Qwen3Engine:
                 # single rank: straight into the gradient (q_norm and k_norm gains are adjacent slots);
                 # tensor parallel: a per-layer stage that is all-reduced once per micro-batch
                 dqk = self._qk_grad_view()[l - self.l0] if tp == 1 else self._qk_stage()[l - self.l0]
-                nv.qk_norm_rope_bwd_canonical(keep["qkv"], w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos,
-                                              dq, dk, dv, dqkv, scr, dqk, Hq=self.hq, Hkv=self.hkv, eps=eps,
-                                              accumulate_dw=tp == 1)
+                if cg is None:
+                    nv.qk_norm_rope_bwd_canonical(keep["qkv"], w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos,
+                                                  dq, dk, dv, dqkv, scr, dqk, Hq=self.hq, Hkv=self.hkv, eps=eps,
+                                                  accumulate_dw=tp == 1)
+                else:
+                    # this rank's rows give dqkv; the gain gradients come from all tokens in logical order,
+                    # evaluated by the layer's owner rank
+                    nv.qk_norm_rope_bwd_canonical(keep["qkv"], w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos,
+                                                  dq, dk, dv, dqkv, scr, ws.get("cpg.dqk_dummy", (256,)), Hq=self.hq,
+                                                  Hkv=self.hkv, eps=eps, accumulate_dw=False)
+                    qkv_g = self._cp_gather(keep["qkv"], "cpg.qkv", cg)
+                    dq_g = self._cp_gather(dq, "cpg.dq", cg)
+                    dk_g = self._cp_gather(dk, "cpg.dk", cg)
+                    dv_g = self._cp_gather(dv, "cpg.dv", cg)
+                    if l % self.ctx.cp_size == self.ctx.cp_rank:
+                        Tg = qkv_g.shape[0]
+                        pos_g = ws.get("cpg.pos", (Tg,), torch.int32)
+                        pos_g.view(cg[0], cg[1]).copy_(torch.arange(cg[1], device=self.dev, dtype=torch.int32))
+                        scr_g = ws.get("cpg.qscr", (nv.qk_norm_rope_bwd_scratch_elems(Tg),), torch.float32)
+                        nv.qk_norm_rope_bwd_canonical(qkv_g, w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos_g,
+                                                      dq_g, dk_g, dv_g, ws.get("cpg.dqkv", (Tg, self.p.qkv_local)), scr_g,
+                                                      dqk, Hq=self.hq, Hkv=self.hkv, eps=eps, accumulate_dw=tp == 1)
             else:
                 nv.qk_norm_rope_bwd(keep["qkv"], w[f"l{l}.qn"], w[f"l{l}.kn"], self.cos, self.sin, pos,
                                     dq, dk, dv, dqkv, scr, g[f"l{l}.qn"], g[f"l{l}.kn"], Hq=self.hq,
@@ -923,10 +1092,8 @@ class Qwen3Engine:
             self._gemm(dqkv, w[f"l{l}.wqkv"], dh, b_mn=True, nchunks=self.nchunks, M=T, N=H,
                        K=self.p.qkv_local)
             self.ctx.tp_all_reduce_(dh)
-            self._gemm(dqkv, keep["h"], g[f"l{l}.wqkv"], a_mn=True, b_mn=True, accumulate=True,
-                       M=self.p.qkv_local, N=H, K=T)
-            nv.rmsnorm_bwd(ck, w[f"l{l}.ln1"], dh, ds, scr, eps, dres=ds2,
-                           dw_bf16=g[f"l{l}.ln1"], accumulate_dw=True)
+            self._dw(dqkv, keep["h"], g[f"l{l}.wqkv"], M=self.p.qkv_local, N=H, T=T, cp_geom=cg)
+            self._gain_bwd(ck, w[f"l{l}.ln1"], dh, ds, scr, eps, g[f"l{l}.ln1"], dres=ds2, owner=2 * l, cp_geom=cg)
         if self.canonical_grads and self.ctx.tp_size > 1 and self.l1 > self.l0:
             # finish the KV-group tree over the tensor-parallel ranks, then accumulate
             st_qk = self._qk_stage()
@@ -935,6 +1102,14 @@ class Qwen3Engine:
         if not self.first_stage:
             return ds
         # ---- embedding
+        if cg is not None:
+            # all tokens in logical order on one owner rank (the other ranks contribute nothing)
+            ds_g = self._cp_gather(ds, "cpg.ds", cg)
+            ids_g = self._cp_gather(tokens.reshape(-1, 1).contiguous(), "cpg.ids", cg).reshape(-1)
+            if self.ctx.cp_rank == 0:
+                sid, order = torch.sort(ids_g, stable=True)
+                nv.embedding_bwd(sid.contiguous(), order.contiguous(), ds_g, g["embed"], self.p.vocab_start)
+            return None
         sid, order = torch.sort(tokens.reshape(-1), stable=True)
         nv.embedding_bwd(sid.contiguous(), order.contiguous(), ds, g["embed"], self.p.vocab_start)
         return None

@@ -102,9 +102,9 @@ class Qwen3MoeEngine(Qwen3Engine):
         self.moe.forward(h2, self._moe_weights(l), out, base=shared)
         return out
 
-    def _mlp_bwd(self, l, ds, keep, T):
+    def _mlp_bwd(self, l, ds, keep, T, cp_geom=None):
         # the expert buffers still hold this layer's recomputed forward
-        dshared = super()._mlp_bwd(l, ds, keep, T)
+        dshared = super()._mlp_bwd(l, ds, keep, T, cp_geom)
         dx = self.ws.get("b.moe_dx", (T, self.spec.hidden_size))
         self.moe.backward(keep["h2"], ds, self._moe_weights(l), dx, dx_base=dshared)
         return dx

@@ -14,7 +14,7 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
 WORLDS = (2, 4, 8)
-CP_GRADS_CANONICAL = False      # context-parallel weight gradients are summed over token shards (equal to rounding)
+CP_GRADS_CANONICAL = True       # every parameter gradient of a context-parallel run equals the single-GPU one bit for bit
 
 
 def _need(world: int) -> None:
