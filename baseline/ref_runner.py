@@ -43,6 +43,28 @@ VOCAB = 151936
 MAX_FORWARD_ROWS = (2 ** 31 - 1) // VOCAB - 128      # rows of one forward call: 32-bit output offsets (see above)
 
 
+PROGRESS: dict = {}
+
+
+def _partial_report(budget: float) -> str:
+    """What was measured before the time budget ran out (the reference's step is not interruptible, so an
+    over-long run is reported with the rates seen so far instead of a number)."""
+    pr, ph = PROGRESS.get("progress"), PROGRESS.get("phase")
+    if not pr:
+        return f"the reference did not finish its set-up within {budget:.0f} s"
+    now = PROGRESS["clock"]()
+    spent = now - pr["t_phase"]
+    if pr["phase"] == "rollout":
+        return (f"one reference step does not fit the arm's {budget:.0f} s budget: step {pr['step']} was still in its rollout "
+                f"after {spent:.0f} s with {pr['decode_tokens_done']} decode tokens done")
+    done, total = pr["microbatches_done"], pr["microbatches"]
+    per = spent / max(done, 1)
+    est = ph["rollout_s"] + per * total
+    return (f"one reference step does not fit the arm's {budget:.0f} s budget: step {pr['step']} took {ph['rollout_s']:.0f} s "
+            f"for its rollout and {spent:.0f} s for {done} of {total} scoring+training micro-batches "
+            f"(about {per:.1f} s each), i.e. about {est:.0f} s per step")
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--steps", type=int, default=1)
@@ -50,7 +72,6 @@ def main() -> int:
     ap.add_argument("--response-len", type=int, default=1024)
     ap.add_argument("--layers", type=int, default=0)
     ap.add_argument("--micro-batch", type=int, default=2)
-    ap.add_argument("--step-timeout", type=int, default=2400)
     ap.add_argument("--time-budget", type=float, default=1500.0,
                     help="seconds for warm-up + timed steps together; fewer steps are run (and reported) when "
                          "the requested ones do not fit")
@@ -58,7 +79,7 @@ def main() -> int:
     try:
         out = run(a)
     except BaseException as exc:  # noqa: BLE001 - reported to the parent
-        out = {"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc)[:300]}"}
+        out = {"impl": "reference", "unavailable": f"{type(exc).__name__}: {str(exc)[:600]}"}
     print(json.dumps(out), flush=True)
     return 0
 
@@ -104,11 +125,15 @@ def run(a) -> dict:
                              f"({MAX_FORWARD_ROWS} rows at vocabulary {VOCAB})")
 
     def alarm(_sig, _frm):
-        raise TimeoutError(f"one reference step exceeded {a.step_timeout} s")
+        raise TimeoutError(_partial_report(a.time_budget))
 
     signal.signal(signal.SIGALRM, alarm)
+    signal.alarm(int(a.time_budget))                      # one budget for everything: warm-up and timed steps
 
     phase = {"rollout_s": 0.0, "score_train_s": 0.0, "optimizer_s": 0.0}
+    progress = {"step": -1, "phase": "start", "microbatches_done": 0, "microbatches": B // a.micro_batch,
+                "decode_tokens_done": 0, "t_phase": 0.0}
+    PROGRESS.update(progress=progress, phase=phase, clock=time.perf_counter)
 
     def lap(name: str, t0: float) -> float:
         torch.cuda.synchronize()
@@ -117,8 +142,8 @@ def run(a) -> dict:
         return t1
 
     def one_step(i: int) -> None:
-        signal.alarm(a.step_timeout)
         t_phase = time.perf_counter()
+        progress.update(step=i, phase="rollout", microbatches_done=0, decode_tokens_done=0, t_phase=t_phase)
         uniq = host_prompts[i].to(dev, non_blocking=True)
         prompts = uniq.repeat_interleave(GROUP, 0)
         # ---- rollout: every distinct prompt is prefilled once, its K/V then serve the whole group
@@ -142,7 +167,10 @@ def run(a) -> dict:
                 tok = torch.multinomial(probs, 1)
                 toks.append(tok)
                 lps.append(torch.log_softmax(z, -1).gather(1, tok))
+                progress["decode_tokens_done"] = t + 1
                 if t + 1 < R:
+                    if t % 32 == 0:
+                        torch.cuda.synchronize()          # lets the time budget interrupt a long rollout
                     out = model.decode_step(tok, cache, position_ids=pos)
                     logits = out["logits"][:, -1].float()
                     pos = pos + 1
@@ -151,6 +179,7 @@ def run(a) -> dict:
             tokens = torch.cat([prompts, resp], 1)
             del cache
         t_phase = lap("rollout_s", t_phase)
+        progress.update(phase="score_train", t_phase=t_phase)
         rewards = torch.bernoulli(torch.full((B,), 0.5, device=dev))
         g = rewards.view(PROMPTS, GROUP)
         adv = ((g - g.mean(1, keepdim=True)) / g.std(1, unbiased=False, keepdim=True).clamp_min(1e-6)).reshape(B)
@@ -175,13 +204,15 @@ def run(a) -> dict:
                 loss.backward()
                 session.validate_complete()
             loss_total += loss.detach()
+            torch.cuda.synchronize()                      # a micro-batch is seconds long: the sync costs nothing
+            progress["microbatches_done"] += 1
         t_phase = lap("score_train_s", t_phase)
         torch.nn.utils.clip_grad_norm_(params, 1.0)
         opt.step()
         host_loss.copy_(loss_total.reshape(1), non_blocking=True)
         torch.cuda.current_stream().synchronize()
         lap("optimizer_s", t_phase)
-        signal.alarm(0)
+        progress["phase"] = "done"
 
     # warm-up and timed steps share one time budget: the reference's step is minutes long at full
     # size, and a run that is cut off from outside reports nothing at all
@@ -198,6 +229,10 @@ def run(a) -> dict:
             break                       # keep room for at least one timed step
     left = a.time_budget - (time.perf_counter() - t_begin)
     steps = max(1, min(a.steps, int(left // max(step_s, 1e-3)))) if warm_done else a.steps
+    if warm_done and left < step_s:
+        raise TimeoutError(f"one reference step takes {step_s:.0f} s (rollout {phase['rollout_s']:.0f} s, scoring+training "
+                           f"{phase['score_train_s']:.0f} s); a warm-up step and a timed step do not both fit the arm's "
+                           f"{a.time_budget:.0f} s budget")
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     e0.record()
@@ -205,6 +240,7 @@ def run(a) -> dict:
         one_step(i)
     e1.record()
     torch.cuda.synchronize()
+    signal.alarm(0)
     wall = time.perf_counter() - t0
     ms = e0.elapsed_time(e1) / steps
     tokens_per_step = B * S

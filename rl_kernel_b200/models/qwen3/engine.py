@@ -708,25 +708,28 @@ class Qwen3Engine:
 
     # -------------------------------------------------------------------------- log-probs
     def logp_from_hidden(self, hf: torch.Tensor, targets: torch.Tensor, *, temperature: float = 1.0,
-                         chunk: int = 8192, want_lse: bool = False):
+                         chunk: int = 8192, want_lse: bool = False, min_keep: torch.Tensor | None = None):
         """Selected-token log-prob of ``targets`` [R] from final hidden rows ``hf`` [R, H] through the
-        fused LM-head epilogue; the [R, V] logits are never written."""
+        fused LM-head epilogue; the [R, V] logits are never written.  ``min_keep`` [R] fp32 restricts the
+        softmax of every row to the scaled logits at or above its value: the support the sampler drew from
+        under top-k / top-p."""
         R = hf.shape[0]
         ntile = self.spec.num_vocab_tiles
         logp = torch.empty(R, dtype=torch.float32, device=self.dev)
         lse = torch.empty(R, dtype=torch.float32, device=self.dev) if want_lse else None
         for r0 in range(0, R, chunk):
             r1 = min(R, r0 + chunk)
-            stats, tl = self._lmhead_stats(hf[r0:r1], targets[r0:r1], temperature, None)
+            stats, tl = self._lmhead_stats(hf[r0:r1], targets[r0:r1], temperature, None,
+                                           None if min_keep is None else min_keep[r0:r1])
             nv.logp_merge(stats, tl, logp[r0:r1], lse[r0:r1] if want_lse else None)
         return (logp, lse) if want_lse else logp
 
-    def _lmhead_stats(self, hrows, targets, temperature, logits_out):
+    def _lmhead_stats(self, hrows, targets, temperature, logits_out, min_keep=None):
         n = hrows.shape[0]
         ntile = self.spec.num_vocab_tiles
         tp = self.ctx.tp_size
         if tp > 1 and logits_out is None and hasattr(self.ctx.collective, "frame_tensor"):
-            return self._lmhead_stats_fused_exchange(hrows, targets, temperature)
+            return self._lmhead_stats_fused_exchange(hrows, targets, temperature, min_keep)
         stats = self.ws.get("lm.stats", (n, ntile, 2), torch.float32)
         tl = self.ws.get("lm.tl", (n,), torch.float32)
         if tp > 1:
@@ -740,7 +743,7 @@ class Qwen3Engine:
                 torch.tensor([float("-inf"), 0.0], device=self.dev)
         if self.p.v_real_local > 0:
             nv.lmhead_logp_stats(hrows, w, targets, stats, tl, vocab_start=self.p.vocab_start,
-                                 inv_temp=1.0 / temperature, logits_out=logits_out)
+                                 inv_temp=1.0 / temperature, logits_out=logits_out, min_keep=min_keep)
         if tp > 1:
             # every rank filled only its own tiles / target: combine (exact: disjoint support)
             per = ntile // tp
@@ -751,7 +754,7 @@ class Qwen3Engine:
 
     LM_EXCHANGE_ROWS = 8192
 
-    def _lmhead_stats_fused_exchange(self, hrows, targets, temperature):
+    def _lmhead_stats_fused_exchange(self, hrows, targets, temperature, min_keep=None):
         """Vocab-parallel LM head with the statistics exchange inside the GEMM: every rank's epilogue
         stores its tiles' (max, sum-exp) and, for the rows whose target it owns, the target logit
         straight into all ranks' buffers over NVLink; one barrier later every rank merges complete
@@ -783,7 +786,7 @@ class Qwen3Engine:
         w = self.p.w["lm_head"][: self.p.v_real_local]
         if self.p.v_real_local > 0:
             nv.lmhead_logp_stats_vp(hrows, w, targets, pm[f"stats{q}"], pm[f"tl{q}"], self.ctx.tp_rank,
-                                    vocab_start=self.p.vocab_start, inv_temp=1.0 / temperature)
+                                    vocab_start=self.p.vocab_start, inv_temp=1.0 / temperature, min_keep=min_keep)
         self.ctx.collective.barrier()
         return pm.local(f"stats{q}")[:n], pm.local(f"tl{q}")[:n]
 
@@ -813,7 +816,7 @@ class Qwen3Engine:
 
     def train_forward_backward(self, tokens: torch.Tensor, resp_start: int, dlogp_fn, *,
                                temperature: float = 1.0, lm_chunk: int = 4096, stage_in=None,
-                               store_activations: bool = False):
+                               store_activations: bool = False, min_keep: torch.Tensor | None = None):
         """One micro-batch: forward with checkpoints, LM head + log-probs on response positions,
         ``dlogp_fn(logp [nseq, Rl]) -> dlogp [nseq, Rl]`` supplies d(loss)/d(logp), then the full
         backward accumulates into ``params.grad``.  Returns logp [nseq, Rl] (fp32).
@@ -822,6 +825,8 @@ class Qwen3Engine:
         ``resp_start-1 .. S-2`` are scored.  ``tokens`` is always the full [nseq, S] matrix; with
         context parallelism this rank embeds and scores only its own positions and the Rl columns
         of logp are the response indices ``response_index(S, resp_start)[1]``.
+        ``min_keep`` [nseq, S - resp_start] fp32: the rollout's per-token sampling-support threshold (top-k /
+        top-p); the log-prob and its gradient are then those of the distribution restricted to that support.
         """
         nseq, S = tokens.shape
         H = self.spec.hidden_size
@@ -838,7 +843,8 @@ class Qwen3Engine:
             st.extra["stored"], st.extra["keeps"] = True, []
         hf = self.forward_hidden(tok_local, save=st, cp_seq_len=S if cp else None, stage_in=stage_in)
         if self._cp_canon:
-            logp_local, dhf = self._head_cp_canonical(hf, tokens, resp_start, dlogp_fn, temperature, lm_chunk, sel, ridx)
+            logp_local, dhf = self._head_cp_canonical(hf, tokens, resp_start, dlogp_fn, temperature, lm_chunk, sel, ridx,
+                                                      min_keep)
             self.stage_input_grad = self._backward(st, tok_local, dhf)
             return logp_local
         hf3 = hf.view(nseq, Sl, H)
@@ -849,6 +855,9 @@ class Qwen3Engine:
             rows.view(nseq, R, H).copy_(hf3[:, resp_start - 1:S - 1])
         targets = tokens[:, resp_start:][:, ridx].reshape(-1).contiguous() if cp else \
             tokens[:, resp_start:].reshape(-1).contiguous()
+        keep = None
+        if min_keep is not None:
+            keep = (min_keep[:, ridx] if cp else min_keep).reshape(-1).float().contiguous()
         # ---- pass 1: log-probs (fused stats).  A single-chunk, single-shard head keeps the bf16
         # logits the same kernel can write, so pass 2 does not have to multiply again.
         vloc = self.p.v_real_local
@@ -861,12 +870,12 @@ class Qwen3Engine:
         kept_logits = None
         if self.ctx.tp_size == 1 and nseq * R <= lm_chunk and vloc > 0:
             kept_logits = lbuf[: nseq * R, :vloc]
-            stats, tl = self._lmhead_stats(rows, targets, temperature, kept_logits)
+            stats, tl = self._lmhead_stats(rows, targets, temperature, kept_logits, keep)
             logp = torch.empty(nseq * R, dtype=torch.float32, device=self.dev)
             lse = torch.empty(nseq * R, dtype=torch.float32, device=self.dev)
             nv.logp_merge(stats, tl, logp, lse)
         else:
-            logp, lse = self.logp_from_hidden(rows, targets, temperature=temperature, want_lse=True)
+            logp, lse = self.logp_from_hidden(rows, targets, temperature=temperature, want_lse=True, min_keep=keep)
         dlogp = dlogp_fn(logp.view(nseq, R)).reshape(-1).contiguous()
         # ---- pass 2: per chunk, logits -> dlogits -> dH, dW
         drows = self.ws.get("lm.drows", (nseq * R, H))
@@ -880,7 +889,8 @@ class Qwen3Engine:
                 if kept_logits is None:
                     self._gemm(rows[r0:r1], wlm, logits)
                 nv.dlogits_(logits, targets[r0:r1], lse[r0:r1], dlogp[r0:r1],
-                            vocab_start=self.p.vocab_start, inv_temp=1.0 / temperature)
+                            vocab_start=self.p.vocab_start, inv_temp=1.0 / temperature,
+                            min_keep=None if keep is None else keep[r0:r1])
                 if self.canonical_grads:
                     self._gemm(lbuf[:n], self.p.w["lm_head"], drows[r0:r1], b_mn=True, nchunks=self.nchunks,
                                M=n, N=H, K=vpad)
@@ -900,7 +910,8 @@ class Qwen3Engine:
         self.stage_input_grad = self._backward(st, tok_local, dhf)   # None unless a pipeline stage
         return logp.view(nseq, R)
 
-    def _head_cp_canonical(self, hf, tokens, resp_start: int, dlogp_fn, temperature: float, lm_chunk: int, sel, ridx):
+    def _head_cp_canonical(self, hf, tokens, resp_start: int, dlogp_fn, temperature: float, lm_chunk: int, sel, ridx,
+                           min_keep=None):
         """LM head of a context-parallel micro-batch with layout-invariant results.
 
         The final hidden rows of ALL ranks are gathered into logical order, so the head sees exactly the rows a single
@@ -920,6 +931,7 @@ class Qwen3Engine:
         rows = ws.get("lm.rows_g", (n, H))
         rows.view(nseq, R, H).copy_(hf_g[:, resp_start - 1:S - 1])
         targets = tokens[:, resp_start:].reshape(-1).contiguous()
+        keep = None if min_keep is None else min_keep.reshape(-1).float().contiguous()
         # ---- this rank's vocabulary slice of the TP shard
         if self.p.v_local % (cp * VOCAB_TILE) or self.nchunks % cp:
             raise ValueError("the padded vocabulary shard must split into cp slices of whole 128-id tiles and chunks")
@@ -946,7 +958,7 @@ class Qwen3Engine:
                 # the kernel indexes tiles globally: hand it a view that starts at tile 0 of this slice
                 full = ws.get("lm.stats_f", (m, ntile, 2), torch.float32)
                 nv.lmhead_logp_stats(rows[r0:r1], w_slice[:vreal], targets[r0:r1], full, tl, vocab_start=gstart,
-                                     inv_temp=inv_t)
+                                     inv_temp=inv_t, min_keep=None if keep is None else keep[r0:r1])
                 t0 = gstart // VOCAB_TILE
                 nlive = (vreal + VOCAB_TILE - 1) // VOCAB_TILE
                 stats[:, :nlive] = full[:, t0:t0 + nlive]
@@ -973,7 +985,8 @@ class Qwen3Engine:
             if vreal > 0:
                 logits = lbuf[:m, :vreal]
                 self._gemm(rows[r0:r1], w_slice[:vreal], logits)
-                nv.dlogits_(logits, targets[r0:r1], lse[r0:r1], dlogp[r0:r1], vocab_start=gstart, inv_temp=inv_t)
+                nv.dlogits_(logits, targets[r0:r1], lse[r0:r1], dlogp[r0:r1], vocab_start=gstart, inv_temp=inv_t,
+                            min_keep=None if keep is None else keep[r0:r1])
                 self._gemm(lbuf[:m], w_slice, drows[r0:r1], b_mn=True, nchunks=nch, M=m, N=H, K=vs)
                 self._gemm(logits, rows[r0:r1], g_slice[:vreal], a_mn=True, b_mn=True, accumulate=True, M=vreal, N=H, K=m)
             else:
@@ -1269,15 +1282,35 @@ class Qwen3Engine:
             self._gemm(hf, self.p.w["lm_head"][:vloc], out)
         return out
 
+    def keep_threshold(self, logits: torch.Tensor, *, temperature: float, top_k: int = 0, top_p: float = 1.0):
+        """Per-row smallest scaled logit that top-k / top-p keep (None when nothing is cut), from this rank's
+        logits shard [n, V_local]; under tensor parallelism the shards are gathered first so that every rank
+        derives the same threshold from the whole row."""
+        if (not top_k or top_k <= 0) and top_p >= 1.0:
+            return None
+        n = logits.shape[0]
+        vr = self.p.v_real_local
+        rows = logits[:, :vr] if vr < logits.shape[1] else logits
+        if self.ctx.tp_size > 1:
+            full = self.ctx.tp_all_gather(logits.contiguous())                       # [tp, n, V_local]
+            rows = full.permute(1, 0, 2).reshape(n, -1)[:, : self.spec.vocab_size].contiguous()
+        thr = self.ws.get("s.thr", (n,), torch.float32)
+        nv.sample_keep_threshold(rows if rows.stride(1) == 1 else rows.contiguous(), thr, inv_temp=1.0 / temperature,
+                                 top_k=top_k, top_p=top_p)
+        return thr
+
     def sample(self, logits: torch.Tensor, row_keys: torch.Tensor, *, temperature: float, seed: int,
-               greedy: bool = False):
+               greedy: bool = False, top_k: int = 0, top_p: float = 1.0, return_threshold: bool = False):
         """Sample one id per row and return (ids, logp of the sampled id under the same temperature),
-        the log-prob computed with the tile contract shared with the training path."""
+        the log-prob computed with the tile contract shared with the training path.  With ``top_k`` /
+        ``top_p`` the draw and the log-prob are over the restricted support; ``return_threshold`` adds the
+        per-row threshold that defines it (what the trainer replays as ``min_keep``)."""
         n = logits.shape[0]
         ids = self.ws.get("s.ids", (n,), torch.int64)
         val = self.ws.get("s.val", (n,), torch.float32)
+        thr = self.keep_threshold(logits, temperature=temperature, top_k=top_k, top_p=top_p)
         nv.sample_gumbel(logits, ids, val, vocab_start=self.p.vocab_start, inv_temp=1.0 / temperature,
-                         seed=seed, step=0, greedy=greedy, row_keys=row_keys)
+                         seed=seed, step=0, greedy=greedy, row_keys=row_keys, min_keep=thr)
         if self.ctx.tp_size > 1:
             vals = self.ctx.tp_all_gather(val)           # [tp, n]
             idss = self.ctx.tp_all_gather(ids)
@@ -1294,7 +1327,7 @@ class Qwen3Engine:
         stats[..., 1] = 0
         tl.zero_()
         nv.logits_tile_stats(logits, ids, stats, tl, vocab_start=self.p.vocab_start,
-                             inv_temp=1.0 / temperature)
+                             inv_temp=1.0 / temperature, min_keep=thr)
         if self.ctx.tp_size > 1:
             per = ntile // self.ctx.tp_size
             gs = self.ctx.tp_all_gather(stats[:, self.ctx.tp_rank * per:(self.ctx.tp_rank + 1) * per].contiguous())
@@ -1302,4 +1335,6 @@ class Qwen3Engine:
             tl = self.ctx.tp_all_gather(tl).sum(0)
         logp = self.ws.get("s.logp", (n,), torch.float32)
         nv.logp_merge(stats, tl, logp, None)
+        if return_threshold:
+            return ids, logp, thr
         return ids, logp

@@ -28,6 +28,11 @@ class GRPOConfig:
     prompt_len: int = 512
     response_len: int = 1024
     temperature: float = 1.0
+    # sampling support of the rollout (0 / 1.0 = the whole vocabulary).  When either cuts the support, the
+    # rollout records every token's keep threshold and reference scoring and training replay it, so
+    # rollout and training log-probs are those of the same restricted distribution.
+    top_k: int = 0
+    top_p: float = 1.0
     clip_eps: float = 0.2
     kl_coef: float = 0.001
     lr: float = 1e-6
@@ -57,6 +62,10 @@ class GRPOConfig:
     @property
     def seq_len(self) -> int:
         return self.prompt_len + self.response_len
+
+    @property
+    def restricted_support(self) -> bool:
+        return (self.top_k is not None and self.top_k > 0) or self.top_p < 1.0
 
 
 class AdamW:
@@ -239,6 +248,8 @@ class GRPOTrainer:
             self._step_key = torch.zeros(1, dtype=torch.int64, device=self.dev)
             self._out_tok = torch.zeros(B, c.response_len, dtype=torch.int64, device=self.dev)
             self._out_lp = torch.zeros(B, c.response_len, dtype=torch.float32, device=self.dev)
+            self._out_thr = torch.zeros(B, c.response_len, dtype=torch.float32, device=self.dev) \
+                if c.restricted_support else None
             self._col = torch.zeros(1, dtype=torch.int64, device=self.dev)
 
     def _decode_once(self):
@@ -250,10 +261,13 @@ class GRPOTrainer:
         logits = eng.logits(hf)
         torch.add(self._seq_key, self._pos, out=self._keys)
         self._keys.add_(self._step_key)
-        ids, lp = eng.sample(logits, self._keys, temperature=c.temperature, seed=c.seed)
+        ids, lp, thr = eng.sample(logits, self._keys, temperature=c.temperature, seed=c.seed, top_k=c.top_k,
+                                  top_p=c.top_p, return_threshold=True)
         col = self._col.expand(ids.shape[0]).unsqueeze(1)
         self._out_tok.scatter_(1, col, ids.unsqueeze(1))
         self._out_lp.scatter_(1, col, lp.unsqueeze(1))
+        if thr is not None:
+            self._out_thr.scatter_(1, col, thr.unsqueeze(1))
         self._tok.copy_(ids)
         self._pos.add_(1)
         self._col.add_(1)
@@ -283,9 +297,12 @@ class GRPOTrainer:
         self._step_key.fill_((int(step_seed) & 0x7FFFFFFF) << 32)
         torch.add(self._seq_key, self._pos, out=self._keys)
         self._keys.add_(self._step_key)
-        ids, lp = eng.sample(logits, self._keys, temperature=c.temperature, seed=c.seed)
+        ids, lp, thr = eng.sample(logits, self._keys, temperature=c.temperature, seed=c.seed, top_k=c.top_k,
+                                  top_p=c.top_p, return_threshold=True)
         self._out_tok[:, 0].copy_(ids)
         self._out_lp[:, 0].copy_(lp)
+        if thr is not None:
+            self._out_thr[:, 0].copy_(thr)
         self._tok.copy_(ids)
         self._pos.fill_(P)
         self._col.fill_(1)
@@ -322,11 +339,12 @@ class GRPOTrainer:
             for _ in range(R - 1):
                 self._decode_once()
         tokens = torch.cat([prompts.repeat_interleave(G, dim=0), self._out_tok], dim=1).contiguous()
+        self.last_support = self._out_thr.clone() if self._out_thr is not None else None
         return tokens, self._out_lp.clone()
 
     # ---------------------------------------------------------------- scoring with frozen weights
     @torch.no_grad()
-    def score(self, params: PackedParams, tokens: torch.Tensor) -> torch.Tensor:
+    def score(self, params: PackedParams, tokens: torch.Tensor, min_keep: torch.Tensor | None = None) -> torch.Tensor:
         """Selected-token log-probs of the response tokens under ``params`` (no gradients):
         [n, Rl], the columns being this rank's response indices (all of them without CP)."""
         c = self.cfg
@@ -343,8 +361,9 @@ class GRPOTrainer:
                 tl = eng.local_tokens(tk)
                 hf = eng.forward_hidden(tl, cp_seq_len=S if self.cp > 1 else None).view(n, tl.shape[1], -1)
                 rows = hf[:, sel].reshape(n * sel.numel(), -1).contiguous()
+                mk = None if min_keep is None else min_keep[b0:b0 + c.micro_batch_seqs][:, ridx].reshape(-1).contiguous()
                 lp = eng.logp_from_hidden(rows, tk[:, c.prompt_len:][:, ridx].reshape(-1).contiguous(),
-                                          temperature=c.temperature)
+                                          temperature=c.temperature, min_keep=mk)
                 out.append(lp.view(n, sel.numel()).clone())
             return torch.cat(out)
         finally:
@@ -370,6 +389,9 @@ class GRPOTrainer:
         ev[0].record()
         self.publish_weights()
         tokens, old_logp = self.rollout(prompts, step_seed=c.seed + 7919 * step_index)
+        support = self.last_support                     # [B_engine, R] keep thresholds, or None
+        if support is not None and self.cp > 1:
+            _, support = self._gather_rollouts(tokens, support)
         tokens, old_logp = self._gather_rollouts(tokens, old_logp)
         ev[1].record()
         if rewards_fn is None:
@@ -384,7 +406,7 @@ class GRPOTrainer:
         Rl = ridx.numel()
         mask = torch.ones(B, Rl, dtype=torch.uint8, device=self.dev)
         old_local = old_logp if self.cp == 1 else old_logp[:, ridx].contiguous()
-        ref_logp = self.score(self.ref_params, tokens) if self.ref_params is not None else None
+        ref_logp = self.score(self.ref_params, tokens, support) if self.ref_params is not None else None
         ev[2].record()
         total_active = float(c.num_seqs * R)          # the loss is normalised over the whole job
         self.policy.grad.zero_()
@@ -405,7 +427,8 @@ class GRPOTrainer:
 
             lp = self.engine.train_forward_backward(tokens[b0:b1], c.prompt_len, dlogp_fn,
                                                     temperature=c.temperature,
-                                                    store_activations=c.store_activations)
+                                                    store_activations=c.store_activations,
+                                                    min_keep=None if support is None else support[b0:b1])
             train_logp[b0:b1].copy_(lp)
         tot = torch.stack(loss_terms).sum(0)
         if self.cp > 1:
@@ -430,7 +453,7 @@ class GRPOTrainer:
         ev[4].record()
         self.phase_events = ev     # rollout, reference scoring, train fwd/bwd, optimizer
         return {"tokens": tokens, "old_logp": old_logp, "train_logp": train_logp, "rewards": rewards,
-                "loss_sums": tot, "grad_norm": self.opt.last_grad_norm, "total_active": total_active}
+                "support": support, "loss_sums": tot, "grad_norm": self.opt.last_grad_norm, "total_active": total_active}
 
     def phase_ms(self) -> dict[str, float]:
         """Device time of the last step's phases (call after a synchronize)."""

@@ -202,3 +202,31 @@ def test_stored_activation_backward_equals_recompute_bitwise():
     assert torch.equal(out[0][0], out[1][0])
     assert torch.equal(out[0][1], out[1][1])
     assert out[0][1].float().abs().sum().item() > 0
+
+
+def test_top_p_rollout_and_training_logprobs_agree_bitwise():
+    """With top-k / top-p the rollout draws from, and scores under, a restricted support; the recorded per-token
+    thresholds make reference scoring and training evaluate the same distribution: 0 mismatching log-probs, and
+    every sampled token lies inside its support."""
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
+
+    spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+    w = Qwen3DenseWeights.synthetic(spec, seed=3)
+    cfg = GRPOConfig(num_prompts=2, group_size=4, prompt_len=128, response_len=96, micro_batch_seqs=4, temperature=0.9,
+                     top_k=50, top_p=0.8, lr=1e-4)
+    tr = GRPOTrainer(spec, cfg, dev(), weights=w)
+    prompts = torch.randint(0, spec.vocab_size, (2, 128), generator=torch.Generator().manual_seed(9)).to(dev())
+    res = tr.step(prompts, step_index=0)
+    sync_and_check()
+    assert res["support"] is not None and res["support"].shape == (8, 96) and torch.isfinite(res["support"]).all()
+    assert tr.mismatch_count(res["train_logp"], res["old_logp"]) == 0
+    assert torch.isfinite(res["old_logp"]).all() and (res["old_logp"] <= 0).all()
+    # the same seed without a restriction samples other tokens / other log-probs at some position
+    free = GRPOTrainer(spec, GRPOConfig(num_prompts=2, group_size=4, prompt_len=128, response_len=96, micro_batch_seqs=4,
+                                        temperature=0.9, lr=1e-4), dev(), weights=w)
+    res2 = free.step(prompts, step_index=0)
+    assert res2["support"] is None and not torch.equal(res2["old_logp"], res["old_logp"])
+    # restricted log-probs are never below the unrestricted ones of the same token (the support only shrinks)
+    lp_free = free.score(free.policy, res["tokens"])
+    assert (res["old_logp"] >= lp_free - 1e-5).all()

@@ -472,7 +472,7 @@ def test_restricted_support_logp_threshold_replay_and_fused_head_agree_bitwise()
     z = logits.float() / T
     keep = z >= thr[:, None]
     counts = keep.sum(1)
-    assert int(counts.min()) >= 1 and int(counts.max()) <= 40
+    assert int(counts.min()) >= 1 and int(counts.max()) <= 60          # bf16 ties at the boundary stay together
     # a target inside the support (the most likely kept id, and for odd rows the least likely one)
     order = z.masked_fill(~keep, float("-inf")).argsort(dim=-1, descending=True)
     targets = torch.where(torch.arange(N, device=dev()) % 2 == 0, order[:, 0], order.gather(1, (counts - 1)[:, None])[:, 0])
