@@ -196,12 +196,17 @@ class _LinearLogpFn(torch.autograd.Function):
         for r0 in range(0, rows, chunk):
             r1 = min(rows, r0 + chunk)
             n = r1 - r0
-            logits = torch.empty(n, V, device=hidden.device, dtype=hidden.dtype)
-            nv.det_gemm(hidden[r0:r1], weight, logits, M=n, N=V, K=H)
+            npad = (n + 7) // 8 * 8           # the dW contraction runs over rows: zero rows pad it to the GEMM's K step
+            buf = torch.empty(npad, V, device=hidden.device, dtype=hidden.dtype)
+            logits, hrows = buf[:n], hidden[r0:r1]
+            nv.det_gemm(hrows, weight, logits, M=n, N=V, K=H)
             nv.dlogits_(logits, targets[r0:r1], lse[r0:r1], g[r0:r1], vocab_start=0, inv_temp=inv_temp,
                         min_keep=None if min_keep is None else min_keep[r0:r1])
             nv.det_gemm(logits, weight, dh[r0:r1], M=n, N=H, K=V, b_mn=True)
-            nv.det_gemm(logits, hidden[r0:r1], dw, M=V, N=H, K=n, a_mn=True, b_mn=True, accumulate=True)
+            if npad != n:
+                buf[n:].zero_()
+                hrows = torch.cat([hrows, hrows.new_zeros(npad - n, H)])
+            nv.det_gemm(buf, hrows, dw, M=V, N=H, K=npad, a_mn=True, b_mn=True, accumulate=True)
         return dh, dw, None, None, None, None
 
 
