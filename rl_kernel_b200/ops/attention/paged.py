@@ -218,22 +218,23 @@ def paged_attention_block_table(q: torch.Tensor, k_pool: torch.Tensor, v_pool: t
 
 
 def _paged_reference(q, k_pool, v_pool, block_table, lens, qsl, hkv, scale, out, return_lse):
-    """The same semantics with gathered pages and the PyTorch attention (CPU, tests)."""
-    from rl_kernel_b200.reference.attention.standard_attn import NativeAttentionOp
+    """The same semantics with gathered pages on the CPU: the block-wise reference with per-row products, whose
+    result for a query row does not depend on which other rows (chunk, batch) it is computed with."""
+    from rl_kernel_b200.reference.attention.blockwise import blockwise_attention_reference
 
     T, hq, d = q.shape
     o = out.view(T, hq, d) if out is not None else torch.empty_like(q)
     lse = torch.zeros(T, hq)
-    op = NativeAttentionOp()
     for i in range(len(lens)):
         n = qsl[i + 1] - qsl[i]
         if n == 0:
             continue
         pages = (block_table[i, : (lens[i] + PAGE - 1) // PAGE].long() & 0xFFFFFF)
         rows = (pages[:, None] * PAGE + torch.arange(PAGE)[None]).reshape(-1)[: lens[i]]
-        k = k_pool[rows].view(1, lens[i], hkv, d)
-        v = v_pool[rows].view(1, lens[i], hkv, d)
-        oi, li = op(q[qsl[i]:qsl[i + 1]].unsqueeze(0), k, v, causal=True, scale=scale, q_pos0=lens[i] - n, return_lse=True)
-        o[qsl[i]:qsl[i + 1]] = oi[0]
-        lse[qsl[i]:qsl[i + 1]] = li[0]
+        k = k_pool[rows].view(lens[i], hkv, d)
+        v = v_pool[rows].view(lens[i], hkv, d)
+        oi, li = blockwise_attention_reference(q[qsl[i]:qsl[i + 1]], k, v, torch.arange(lens[i] - n, lens[i]), scale=scale,
+                                               strict=True)
+        o[qsl[i]:qsl[i + 1]] = oi
+        lse[qsl[i]:qsl[i + 1]] = li
     return (o, lse) if return_lse else o

@@ -65,6 +65,9 @@ def det_gemm_db(dy: torch.Tensor, x: torch.Tensor, *, out: torch.Tensor | None =
 
     T, N = dy.shape
     K = x.shape[1]
+    if T % 8:                                   # the token contraction steps by 8 rows: zero rows add exact zeros at the end
+        pad = 8 - T % 8
+        dy, x, T = torch.cat([dy, dy.new_zeros(pad, N)]), torch.cat([x, x.new_zeros(pad, K)]), T + pad
     if out is None:
         out = torch.zeros(N, K, device=dy.device, dtype=torch.bfloat16)
         accumulate = False

@@ -277,10 +277,6 @@ OP_SPECS: dict[str, OperatorSpec] = {
                                      "rl_engine.backends.cuda.attention.prefix_shared_attn.PrefixSharedAttentionOp",
                                      "rl_engine.validation.operators.operator_specs.GtestPrefixSharedAttentionOp", (),
                                      adapter="prefix_shared", tol="attention", hq=4, hkv=2),
-    "cp_attention": _spec("cp_attention", "attention", "rl_engine.reference.attention.cp_attention.DeterministicCPAttentionReferenceOp",
-                          "rl_engine.ops.distributed.cp_attention.CPAttentionOp",
-                          "rl_engine.reference.attention.cp_attention.DeterministicCPAttentionReferenceOp", (), adapter="cp_attention",
-                          tol="attention", hq=4, hkv=2),
     "pack": _spec("pack", "layout", "rl_engine.validation.operators.operator_specs.GtestPackOp",
                   "rl_engine.validation.operators.operator_specs.GtestDevicePackOp",
                   "rl_engine.validation.operators.operator_specs.GtestPackOp", (), adapter="pack", width=256),
@@ -369,8 +365,8 @@ class _TokenRowsPos(_TokenRows):
     def call(self, spec, op, st, x, keys, layout):
         h = spec.params["heads"]
         pos = torch.tensor([k[1] if k is not None else 0 for k in keys], device=x.device)
-        # [T, H, 1, D] with one position per row: the sequence axis is the singleton next to D
-        return op(x.view(x.shape[0], h, 1, -1), pos.view(-1, 1)).reshape(x.shape[0], -1)
+        # rows are tokens: heads lead, so that the token axis is the sequence axis next to D
+        return op(x.view(x.shape[0], h, -1).transpose(0, 1), pos).transpose(0, 1).reshape(x.shape[0], -1)
 
     def gold(self, spec, st, batch):
         keys = list(batch.logical_keys())

@@ -1,0 +1,35 @@
+"""The operator validation harness on the sm_100a candidates: every operator green in all four judgments
+(forward / gradient accuracy against the fp32 gold, forward / gradient invariance per logical token across
+packed, permuted, singleton, chunked and padded presentations of one logical batch)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_four_judgment_matrix_is_green_for_the_device_candidates():
+    from rl_kernel_b200.validation.operators.four_judgment_matrix import four_judgment_matrix
+
+    m = four_judgment_matrix(device="cuda", dtype=torch.bfloat16, candidate="b200")
+    assert m.green, m.render() + "\n" + "\n".join(str(c) for c in m.red_cells())
+
+
+def test_forward_invariance_reports_an_injected_row_dependence():
+    """The harness is not vacuous: a candidate whose output depends on its row index turns the matrix red."""
+    from rl_kernel_b200.validation.operators import operator_specs as specs
+    from rl_kernel_b200.validation.operators.forward_invariance import run_forward_invariance
+
+    good = specs.FACTORIES["swiglu"]
+
+    class Leaky:
+        def __call__(self, g, u):
+            y = good()(g, u)
+            y[1::2] += 1.0e-2
+            return y
+
+    specs.FACTORIES["swiglu"] = Leaky
+    try:
+        rep = run_forward_invariance("swiglu", candidate="b200", device="cuda", dtype=torch.bfloat16)
+    finally:
+        specs.FACTORIES["swiglu"] = good
+    assert not rep.forward_invariant and "BN/permuted" in rep.failing()

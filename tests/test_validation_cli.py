@@ -16,6 +16,27 @@ def test_four_judgment_matrix_is_green_on_cpu():
     assert m.green, m.render() + "\n" + str(m.red_cells())
 
 
+def test_forward_invariance_reports_an_injected_row_dependence():
+    from rl_engine.validation.operators import operator_specs as specs
+    from rl_engine.validation.operators.forward_invariance import run_forward_invariance
+
+    good = specs.FACTORIES["swiglu"]
+
+    class Leaky:
+        def __call__(self, g, u):
+            y = good()(g, u).clone()
+            y[1::2] += 1.0e-2
+            return y
+
+    specs.FACTORIES["swiglu"] = Leaky
+    try:
+        rep = run_forward_invariance("swiglu", device="cpu", dtype=torch.float32)
+    finally:
+        specs.FACTORIES["swiglu"] = good
+    assert not rep.forward_invariant and "B1/singletons" in rep.failing()
+    assert run_forward_invariance("swiglu", device="cpu", dtype=torch.float32).forward_invariant
+
+
 def _exp(extra_case=None):
     cases = [{"name": "ref", "knobs": {}}, {"name": "b1", "knobs": {"batch_size": 1}},
              {"name": "tp2", "knobs": {"tp_size": 2}}, {"name": "decode", "knobs": {"decode_from": 8}}]
