@@ -146,7 +146,12 @@ def cmd_validate(args) -> int:
         from rl_kernel_b200.validation.cross_config.config import ExperimentConfig
         from rl_kernel_b200.validation.cross_config.runner import run_experiment
 
-        summary = run_experiment(ExperimentConfig.load(args.config), args.out, resume=not args.no_resume)
+        import dataclasses
+
+        exp = ExperimentConfig.load(args.config)
+        if args.backend:
+            exp = dataclasses.replace(exp, backend=args.backend)
+        summary = run_experiment(exp, args.out, resume=not args.no_resume)
         print(json.dumps(summary, indent=1))
         rc |= 0 if summary["all_bitwise_equal"] else 1
     if args.seal and args.config:
@@ -201,6 +206,8 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--out", default="runs")
     p.add_argument("--no-resume", action="store_true")
     p.add_argument("--seal", action="store_true")
+    p.add_argument("--backend", choices=("auto", "reference", "engine"), default=None,
+                   help="scoring backend of the cross-config run: reference (CPU model) or engine (sm_100a Qwen3Engine)")
     p.set_defaults(fn=cmd_validate)
     p = sub.add_parser("report")
     p.add_argument("run_dir")

@@ -36,8 +36,11 @@ class ExperimentConfig:
     num_sequences: int = 4
     seq_len: int = 24
     model: dict = field(default_factory=dict)
+    backend: str = "reference"            # reference (CPU batch-invariant model) | engine (sm_100a Qwen3Engine) | auto
 
     def __post_init__(self):
+        if self.backend not in ("reference", "engine", "auto"):
+            raise ValueError(f"backend {self.backend!r} is not one of reference / engine / auto")
         names = [c.name for c in self.cases]
         if len(set(names)) != len(names):
             raise ValueError("case names must be unique")

@@ -33,3 +33,21 @@ def test_forward_invariance_reports_an_injected_row_dependence():
     finally:
         specs.FACTORIES["swiglu"] = good
     assert not rep.forward_invariant and "BN/permuted" in rep.failing()
+
+
+def test_cross_config_runner_drives_the_engine_and_sees_an_injected_offset(tmp_path):
+    """Same sequences as whole batch, singletons, micro-batches, right-padded and prefill + cached decode through
+    Qwen3Engine: every logical token's log-prob keeps its bits; a smoke-only operator override is reported."""
+    from rl_kernel_b200.validation.cross_config.config import ExperimentConfig
+    from rl_kernel_b200.validation.cross_config.runner import run_experiment
+
+    cases = [{"name": "ref", "knobs": {}}, {"name": "b1", "knobs": {"batch_size": 1}}, {"name": "b3", "knobs": {"batch_size": 3}},
+             {"name": "padr", "knobs": {"padding": "right", "chunk_size": 40}}, {"name": "decode", "knobs": {"decode_from": 100}},
+             {"name": "tp2", "knobs": {"tp_size": 2}}]
+    base = {"experiment_id": "eng", "reference_case": "ref", "num_sequences": 4, "seq_len": 136, "backend": "engine"}
+    s = run_experiment(ExperimentConfig.from_dict({**base, "cases": cases}), tmp_path)
+    assert s["all_bitwise_equal"], s
+    assert s["blocked_cases"] == ["tp2"]
+    bad = cases + [{"name": "off", "knobs": {"operator_override": "smoke_only.logp_offset"}}]
+    s2 = run_experiment(ExperimentConfig.from_dict({**base, "experiment_id": "eng2", "cases": bad}), tmp_path)
+    assert not s2["all_bitwise_equal"] and s2["cases"]["off"]["mismatch_count"] > 0
