@@ -1254,7 +1254,10 @@ static int lmhead_stats_impl(const void* H, const void* W, int M, int N, int K, 
                              void* logits_out, long long ld_logits, void* const* stats_ptrs,
                              void* const* tgt_ptrs, int world, int rank, void* stream) {
   using namespace rlk;
-  RLK_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0, "lmhead_logp_stats: bad shape");
+  // the stats epilogue masks ids >= N and the weight rows beyond N read as zero through the tensor map, so N is free
+  // unless the logits are also written (their rows then need a 16-byte pitch)
+  RLK_REQUIRE(M > 0 && N > 0 && K > 0 && K % 8 == 0 && (N % 8 == 0 || logits_out == nullptr),
+              "lmhead_logp_stats: bad shape");
   RLK_REQUIRE(vocab_start % kVocabTile == 0, "lmhead_logp_stats: vocab_start must be a multiple of 128");
   GemmParams p{};
   p.M = M; p.N = N; p.K = K;

@@ -63,20 +63,29 @@ class _VPLinearLogpFn(torch.autograd.Function):
         g = g.float().contiguous()
         dh = torch.empty_like(hidden)
         dw = torch.zeros_like(weight)
-        logits = torch.zeros(min(rows, op.chunk), vpad, device=hidden.device, dtype=hidden.dtype)
+        # GEMM extents step by 8: the real ids round up into the (zero) padding rows of the shard, whose logits are 0 and
+        # whose gradient is set to 0; the token contraction of dW rounds up with zero rows
+        v8 = min(vpad, (vloc + 7) // 8 * 8)
+        cap = (min(rows, op.chunk) + 7) // 8 * 8
+        logits = torch.zeros(cap, vpad, device=hidden.device, dtype=hidden.dtype)
         for r0 in range(0, rows, op.chunk):
             r1 = min(rows, r0 + op.chunk)
             n = r1 - r0
-            lg = logits[:n]
+            n8 = (n + 7) // 8 * 8
+            lg, hrows = logits[:n], hidden[r0:r1]
             if vloc > 0:
-                nv.det_gemm(hidden[r0:r1], weight[:vloc], lg[:, :vloc], M=n, N=vloc, K=H)
-                nv.dlogits_(lg[:, :vloc], targets[r0:r1], lse[r0:r1], g[r0:r1], vocab_start=op.vocab_start,
+                nv.det_gemm(hrows, weight[:v8], lg[:, :v8], M=n, N=v8, K=H)
+                nv.dlogits_(lg[:, :v8], targets[r0:r1], lse[r0:r1], g[r0:r1], vocab_start=op.vocab_start,
                             inv_temp=op.inv_temp)
+                if v8 != vloc:
+                    lg[:, vloc:v8].zero_()
                 # canonical vocabulary chunks: the padded shard splits into equal pieces, the padding
                 # columns are zero, and the tree over the ranks finishes the same sum for every world
                 nv.det_gemm(lg, weight, dh[r0:r1], M=n, N=H, K=vpad, b_mn=True, nchunks=op.nchunks)
-                nv.det_gemm(lg[:, :vloc], hidden[r0:r1], dw[:vloc], M=vloc, N=H, K=n, a_mn=True, b_mn=True,
-                            accumulate=True)
+                if n8 != n:
+                    logits[n:n8].zero_()
+                    hrows = torch.cat([hrows, hrows.new_zeros(n8 - n, H)])
+                nv.det_gemm(logits[:n8, :v8], hrows, dw[:v8], M=v8, N=H, K=n8, a_mn=True, b_mn=True, accumulate=True)
             else:
                 dh[r0:r1].zero_()
         if op.world > 1:

@@ -33,3 +33,22 @@ def summarize_kernel_drift(candidate: torch.Tensor, gold: torch.Tensor, mask: to
     d = g - c
     return {"count": n, "max_abs_error": float(diff.max()), "mean_abs_error": float(diff.mean()),
             "mismatch_count": mism, "approx_kl": float((torch.exp(d) - d - 1).mean())}
+
+
+def masked_sum(x: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    return (x * mask.to(x.dtype)).sum()
+
+
+def active_token_count(mask: torch.Tensor) -> torch.Tensor:
+    return mask.bool().sum()
+
+
+def compute_policy_ratio(logp: torch.Tensor, old_logp: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    """exp(logp - old_logp); inactive tokens read as ratio 1."""
+    return torch.exp((logp - old_logp.float()).masked_fill(~mask.bool(), 0.0))
+
+
+def compute_reference_kl(logp: torch.Tensor, ref_logp: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+    """k3 estimator exp(d) - d - 1 with d = ref_logp - logp; zero on inactive tokens."""
+    d = (ref_logp.float() - logp).masked_fill(~mask.bool(), 0.0)
+    return torch.exp(d) - d - 1.0
