@@ -51,5 +51,28 @@ def resolve_tolerance(op_name: str, dtype: torch.dtype | str, profile: str = "ws
     return ToleranceSpec(float(entry["atol"]), float(entry["rtol"]), entry.get("scale", "elementwise"))
 
 
+def load_contract(profile: str = "ws1") -> dict:
+    """The whole precision profile (the tolerance contract) as a plain dict."""
+    return load_precision_profile(profile)
+
+
+def tolerance_contract_fingerprint(profile: str = "ws1") -> str:
+    """sha256 of the canonical JSON of the profile: artifacts judged under different contracts never compare."""
+    import hashlib
+
+    return hashlib.sha256(json.dumps(load_precision_profile(profile), sort_keys=True, separators=(",", ":")).encode()).hexdigest()
+
+
+def cross_config_threshold(dtype_a: str, dtype_b: str | None = None, profile: str = "ws1") -> float:
+    """Fixed |dlogp| bound between a rollout and a training score computed in the given dtypes."""
+    table = load_precision_profile(profile)["cross_config"]["fixed_threshold"]
+    names = {"bf16": "bfloat16", "fp16": "float16", "fp32": "float32", "half": "float16", "float": "float32"}
+    keys = [names.get(str(d).removeprefix("torch."), str(d).removeprefix("torch.")) for d in (dtype_a, dtype_b or dtype_a)]
+    for k in keys:
+        if k not in table:
+            raise KeyError(f"no cross-config threshold for dtype {k!r}")
+    return max(float(table[k]) for k in keys)
+
+
 def chain_thresholds(profile: str = "ws1") -> dict:
     return dict(load_precision_profile(profile)["chain"])

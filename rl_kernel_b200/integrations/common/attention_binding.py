@@ -3,6 +3,10 @@ contract derived from the layer's config > refusal in strict mode (parity: bind_
 rl_engine/integrations/common/attention_binding.py:597)."""
 from __future__ import annotations
 
+from dataclasses import dataclass
+from enum import Enum
+from typing import Any
+
 from rl_kernel_b200.contracts.operators.attention import AttentionContract, CPLayout
 from rl_kernel_b200.runtime.policy import strict_contract_enabled
 
@@ -42,3 +46,51 @@ def bind_attention_contracts(layers, *, explicit: AttentionContract | None = Non
             setattr(layer, "rl_kernel_attention_contract", c)
         out.append(c)
     return out
+
+
+# ------------------------------------------------------------------------------------------------ binding findings
+class BindingErrorCode(str, Enum):
+    """Stable machine-readable reasons a rollout / training binding is rejected (parity: BindingErrorCode,
+    rl_engine/integrations/common/attention_binding.py:105-135)."""
+    IDENTITY_MISSING = "IDENTITY_MISSING"
+    IDENTITY_MISMATCH = "IDENTITY_MISMATCH"
+    REDUCTION_SEMANTIC_MISMATCH = "REDUCTION_SEMANTIC_MISMATCH"
+    REDUCTION_MANDATE_VIOLATION = "REDUCTION_MANDATE_VIOLATION"
+    LSE_NOT_EXPORTED = "LSE_NOT_EXPORTED"
+    ROLE_COLLISION = "ROLE_COLLISION"
+    DETERMINISM_INCOMPATIBLE = "DETERMINISM_INCOMPATIBLE"
+    TOPOLOGY_MISMATCH = "TOPOLOGY_MISMATCH"
+    SPLIT_KV_RUNTIME_MISSING = "SPLIT_KV_RUNTIME_MISSING"
+    SPLIT_KV_MISMATCH = "SPLIT_KV_MISMATCH"
+    SPLIT_KV_FALLBACK = "SPLIT_KV_FALLBACK"
+    ATTENTION_PREPROCESS_MISMATCH = "ATTENTION_PREPROCESS_MISMATCH"
+    ATTENTION_PROJECTION_MISMATCH = "ATTENTION_PROJECTION_MISMATCH"
+    ATTENTION_CORE_MISMATCH = "ATTENTION_CORE_MISMATCH"
+    ATTENTION_BACKEND_MISSING = "ATTENTION_BACKEND_MISSING"
+    ATTENTION_NOT_PRODUCTION_READY = "ATTENTION_NOT_PRODUCTION_READY"
+
+
+class BindingTier(str, Enum):
+    """IDENTITY: the two sides do not describe the same computation.  SEMANTIC: they do, but with arithmetic that
+    cannot agree bit for bit.  ADVISORY: recorded, not blocking."""
+    IDENTITY = "identity"
+    SEMANTIC = "semantic"
+    ADVISORY = "advisory"
+
+
+@dataclass(frozen=True)
+class BindingIssue:
+    code: BindingErrorCode
+    tier: BindingTier
+    field: str
+    message: str
+    rollout: Any = None
+    training: Any = None
+
+    def to_dict(self) -> dict:
+        return {"code": self.code.value, "tier": self.tier.value, "field": self.field, "message": self.message,
+                "rollout": self.rollout, "training": self.training}
+
+    @property
+    def blocking(self) -> bool:
+        return self.tier is not BindingTier.ADVISORY

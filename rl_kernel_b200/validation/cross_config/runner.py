@@ -86,3 +86,78 @@ def main(argv=None) -> int:
 
 if __name__ == "__main__":
     sys.exit(main())
+
+
+# ================================================================================================ paired alignment runs
+def run_alignment(config, out_dir, *, rollout, training, materializers, bitwise: bool = False, resume: bool = True) -> dict:
+    """Plan ``config`` (an ``AlignmentExperimentConfig``), materialise every case on both sides, score it with the two
+    paired scorers under the read-only guard, compare the artifacts under the tolerance contract (``bitwise``: at
+    threshold zero) and keep sealed, resumable attempts under ``out_dir/<experiment>/paired/<case>/<n>/`` (parity: the
+    paired runner of rl_engine/validation/cross_config/runner.py:60-714)."""
+    from rl_kernel_b200.validation.cross_config import _execution as ex, _provenance as pv, _resume as rs
+    from rl_kernel_b200.validation.cross_config._json import strict_json_dumps
+    from rl_kernel_b200.validation.cross_config.comparison import FixedThresholdComparator
+    from rl_kernel_b200.validation.cross_config.execution_plan import build_execution_plan
+    from rl_kernel_b200.validation.cross_config.runtime import RuntimeTools
+    from rl_kernel_b200.validation.cross_config.schema import CanonicalScoringBatch, ScoreArtifact, ScoreSide
+
+    plan = build_execution_plan(config)
+    r_spec, t_spec = ex.validate_scorer_identity(rollout, training)
+    tools = RuntimeTools()
+    env = pv.execution_environment_provenance()
+    fps = {"rollout": ex.scorer_implementation_fingerprint(rollout), "training": ex.scorer_implementation_fingerprint(training),
+           **{f"materializer.{m.target}": m.implementation_fingerprint() for m in materializers}}
+    root = Path(out_dir) / config.definition.experiment_id / "paired"
+    batch = CanonicalScoringBatch.from_identity(config.definition.identity)
+    comparator = FixedThresholdComparator(bitwise=bitwise)
+    summary = {"experiment_id": config.definition.experiment_id, "bitwise": bitwise, "cases": {}, "issues": [i.to_dict() for i in plan.issues],
+               "environment": env, "model_state": ex.paired_model_state_fingerprints(rollout, training)}
+    for entry in plan.entries:
+        case = entry.case
+        m = tools.materialize(case, materializers, strict_fallback=config.definition.strict_fallback)
+        row = {"changed_paths": list(case.changed_paths), "materialization": m.case.status.value, "isolation_scope": m.case.isolation_scope.value}
+        summary["cases"][case.case_id] = row
+        if not m.executable:
+            row.update(status="not_executable", evidence=pv.json_safe(dict(m.case.evidence)))
+            continue
+        efp = pv.execution_fingerprint(m, scorer_fingerprints=fps, environment=env)
+        case_dir = root / case.case_id
+        attempts = sorted((p for p in case_dir.iterdir() if p.is_dir()), key=lambda p: int(p.name)) if case_dir.exists() else []
+        stored = next((r for a in reversed(attempts) if (r := rs.completed_attempt_matches(a, execution_fingerprint=efp, case_id=case.case_id))), None) if resume else None
+        if stored is not None:
+            row.update(status=stored["status"], passed=stored["passed"], mismatch_count=stored["mismatch_count"],
+                       active_token_count=stored["active_token_count"], reused=True)
+            continue
+        attempt = case_dir / str(len(attempts))
+        attempt.mkdir(parents=True)
+        attempt_id = f"{case.case_id}/{attempt.name}"
+        arts = {}
+        for side, scorer, spec in ((ScoreSide.ROLLOUT, rollout, r_spec), (ScoreSide.TRAINING, training, t_spec)):
+            opts = dict(m.adapters[side.value].options) if side.value in m.adapters else {}
+            with ex.read_only_scoring_guard(scorer):
+                ranks = scorer.score(batch, options=opts)
+            top = ex.validate_rank_outputs(ranks, batch, expected_world_size=spec.world_size)
+            prov = pv.side_provenance(side, m, actual={k: v for k, v in top.actual.items()}, implementation_fingerprint=fps[side.value],
+                                      world_size=spec.world_size)
+            arts[side] = ScoreArtifact(case.case_id, attempt_id, side, case.identity, spec, top.selected_logprobs, batch.active_mask, prov)
+            (attempt / f"{side.value}.json").write_text(strict_json_dumps({**pv.score_metadata(arts[side]), "provenance": prov.to_dict()}, indent=1))
+        result = comparator.compare(arts[ScoreSide.ROLLOUT], arts[ScoreSide.TRAINING])
+        tokens = result.token_artifact
+        torch.save({"rollout_logprobs": arts[ScoreSide.ROLLOUT].selected_logprobs.masked_fill(~batch.active_mask, 0.0),
+                    "training_logprobs": arts[ScoreSide.TRAINING].selected_logprobs.masked_fill(~batch.active_mask, 0.0),
+                    "active_mask": batch.active_mask, **({"mismatch_mask": tokens.mismatch_mask} if tokens is not None else {})},
+                   attempt / "tensors.pt")
+        rd = {k: v for k, v in result.to_dict().items() if k != "token_artifact"}
+        (attempt / "request.json").write_text(strict_json_dumps({"case_id": case.case_id, "execution_fingerprint": efp,
+                                                                  "requested": pv.json_safe(dict(case.requested)),
+                                                                  "operators": entry.operators.to_dict()}, indent=1))
+        (attempt / "result.json").write_text(strict_json_dumps(rd, indent=1))
+        rs.seal_attempt(attempt)
+        row.update(status=result.status.value, passed=result.passed, mismatch_count=result.mismatch_count,
+                   active_token_count=result.active_token_count, reused=False, diagnostics=pv.json_safe(dict(result.diagnostics)))
+    ran = [c for c in summary["cases"].values() if "passed" in c]
+    summary["all_passed"] = bool(ran) and all(c["passed"] for c in ran)
+    summary["not_executable"] = sorted(k for k, c in summary["cases"].items() if c.get("status") == "not_executable")
+    (Path(out_dir) / config.definition.experiment_id).mkdir(parents=True, exist_ok=True)
+    (Path(out_dir) / config.definition.experiment_id / "paired_summary.json").write_text(strict_json_dumps(pv.json_safe(summary), indent=1))
+    return summary

@@ -136,3 +136,160 @@ def score_case(exp: ExperimentConfig, case: CaseConfig) -> tuple[torch.Tensor, d
 
 __all__ = ["BACKENDS", "ENGINE_MODEL", "REFERENCE_MODEL", "UnsupportedCase", "score_case", "score_engine", "score_reference",
            "sequences"]
+
+
+# ================================================================================================ knob materialisation
+# (parity: KnobApplication / RuntimeBinding / RuntimeTools, rl_engine/validation/cross_config/runtime.py:27-465)
+import hashlib as _hashlib
+import json as _json
+from dataclasses import dataclass as _dataclass, field as _field
+from typing import Any as _Any, Iterable as _Iterable, Mapping as _Mapping, Protocol as _Protocol, Sequence as _Sequence
+
+from rl_kernel_b200.validation.cross_config.planner import V1_KNOBS as _V1_KNOBS, _flatten, _plain, _set_path
+from rl_kernel_b200.validation.cross_config.schema import (ExperimentCase, IsolationScope, KnobDescriptor, MaterializationStatus,
+                                                           MaterializedCase, SerializableModel, freeze)
+
+
+def _fp(value) -> str:
+    return _hashlib.sha256(_json.dumps(_plain(value), sort_keys=True, separators=(",", ":"), default=str).encode()).hexdigest()
+
+
+@_dataclass(frozen=True)
+class KnobApplication(SerializableModel):
+    """What an adapter did with one knob on one target: the value it set, the value the runtime reports back, and how
+    far the two can be trusted."""
+    path: str
+    target: str                                   # rollout | training
+    requested: _Any
+    materialized: _Any
+    actual: _Any = None
+    status: MaterializationStatus = MaterializationStatus.APPLIED
+    evidence: _Mapping[str, _Any] = _field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        object.__setattr__(self, "status", MaterializationStatus(self.status))
+        object.__setattr__(self, "evidence", freeze(self.evidence))
+        if self.target not in ("rollout", "training"):
+            raise ValueError("target must be rollout or training")
+        if self.status is MaterializationStatus.APPLIED and self.actual is not None and self.actual != self.materialized:
+            raise ValueError(f"{self.path}: status APPLIED but the runtime reports {self.actual!r}, not {self.materialized!r}")
+
+
+@_dataclass(frozen=True)
+class AdapterMaterialization:
+    target: str
+    applications: tuple[KnobApplication, ...]
+    options: _Mapping[str, _Any] = _field(default_factory=dict)      # what the scorer factory is called with
+
+    def __post_init__(self) -> None:
+        object.__setattr__(self, "applications", tuple(self.applications))
+        object.__setattr__(self, "options", freeze(self.options))
+
+
+class RuntimeMaterializer(_Protocol):
+    """One side's adapter: turns normalised knob values into factory options and reports what it applied."""
+    target: str
+
+    def implementation_fingerprint(self) -> str: ...
+
+    def materialize(self, case: ExperimentCase, normalized: _Mapping[str, _Any]) -> AdapterMaterialization: ...
+
+
+@_dataclass(frozen=True)
+class RuntimeMaterialization:
+    case: MaterializedCase
+    adapters: _Mapping[str, AdapterMaterialization]
+    strict_fallback: bool = True
+
+    @property
+    def executable_in_strict_mode(self) -> bool:
+        return self.case.status is MaterializationStatus.APPLIED
+
+    @property
+    def executable(self) -> bool:
+        ok = {MaterializationStatus.APPLIED} | (set() if self.strict_fallback else {MaterializationStatus.FALLBACK,
+                                                                                    MaterializationStatus.UNOBSERVABLE})
+        return self.case.status in ok
+
+
+class RuntimeMaterializationError(RuntimeError):
+    pass
+
+
+_STATUS_ORDER = (MaterializationStatus.ERROR, MaterializationStatus.UNSUPPORTED, MaterializationStatus.FALLBACK,
+                 MaterializationStatus.UNOBSERVABLE, MaterializationStatus.APPLIED)
+
+
+def aggregate_status(statuses: _Iterable[MaterializationStatus]) -> MaterializationStatus:
+    """The worst status wins: one unsupported knob makes the case unsupported."""
+    seen = set(statuses)
+    for s in _STATUS_ORDER:
+        if s in seen:
+            return s
+    return MaterializationStatus.APPLIED
+
+
+class RuntimeTools:
+    """Materialises a planned case on both sides and decides what can be reused between two cases."""
+
+    def __init__(self, descriptors: _Mapping[str, KnobDescriptor] = _V1_KNOBS):
+        self.descriptors = dict(descriptors)
+
+    def materialize(self, case: ExperimentCase, adapters: _Sequence[RuntimeMaterializer], *, strict_fallback: bool = True
+                    ) -> RuntimeMaterialization:
+        flat = _flatten(case.requested)
+        per_target: dict[str, AdapterMaterialization] = {}
+        statuses, materialized, evidence = [], {}, {}
+        for ad in adapters:
+            mine = {p: v for p, v in flat.items() if p in self.descriptors and ad.target in self.descriptors[p].targets}
+            try:
+                m = ad.materialize(case, mine)
+            except Exception as exc:  # noqa: BLE001 - an adapter failure is a case status, not a crash of the run
+                statuses.append(MaterializationStatus.ERROR)
+                evidence[ad.target] = {"error": f"{type(exc).__name__}: {exc}"}
+                continue
+            if m.target != ad.target:
+                raise RuntimeMaterializationError(f"adapter for {ad.target} returned a materialisation for {m.target}")
+            covered = {a.path for a in m.applications}
+            missing = sorted(set(mine) - covered)
+            if missing:
+                raise RuntimeMaterializationError(f"{ad.target} adapter left knobs unreported: {missing}")
+            per_target[ad.target] = m
+            for a in m.applications:
+                statuses.append(a.status)
+                _set_path(materialized, f"{a.target}.{a.path}", a.materialized)
+                if a.evidence:
+                    evidence[f"{a.target}.{a.path}"] = dict(a.evidence)
+        scopes = [self.descriptors[p].lifecycle for p in flat if p in self.descriptors]
+
+        def scoped(scope: IsolationScope) -> str:
+            return _fp({p: v for p, v in flat.items() if p in self.descriptors and self.descriptors[p].lifecycle.rank >= scope.rank})
+
+        mc = MaterializedCase(case, case.requested, materialized,
+                              max(scopes, key=lambda s: s.rank) if scopes else IsolationScope.REQUEST,
+                              scoped(IsolationScope.ENGINE_CONSTRUCTION), scoped(IsolationScope.DISTRIBUTED_CONTEXT),
+                              scoped(IsolationScope.PROCESS), aggregate_status(statuses), evidence)
+        return RuntimeMaterialization(mc, per_target, strict_fallback)
+
+    @staticmethod
+    def require_executable(m: RuntimeMaterialization) -> None:
+        if not m.executable:
+            raise RuntimeMaterializationError(f"case {m.case.case.case_id} materialised as {m.case.status.value}: "
+                                              f"{dict(m.case.evidence)}")
+
+    @staticmethod
+    def can_reuse(previous: RuntimeMaterialization, current: RuntimeMaterialization) -> str:
+        """What survives from the previous case: 'engine' (only request-level knobs moved), 'context' (rebuild the engine
+        inside the same distributed context), 'process' (same process, new context) or 'nothing'."""
+        a, b = previous.case, current.case
+        if a.process_fingerprint != b.process_fingerprint:
+            return "nothing"
+        if a.distributed_context_fingerprint != b.distributed_context_fingerprint:
+            return "process"
+        if a.construction_fingerprint != b.construction_fingerprint:
+            return "context"
+        return "engine"
+
+
+__all__ += ["AdapterMaterialization", "KnobApplication", "RuntimeMaterialization", "RuntimeMaterializationError", "RuntimeMaterializer",
+            "RuntimeTools", "aggregate_status"]

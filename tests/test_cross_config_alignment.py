@@ -1,0 +1,193 @@
+"""Alignment experiments: schema, planner, materialisation, paired scoring on the CPU reference model, comparison,
+determinism probes, strict JSON, sealed resume."""
+import json
+
+import pytest
+import torch
+
+from rl_engine.validation.cross_config import _execution as ex
+from rl_engine.validation.cross_config._json import strict_json_loads
+from rl_engine.validation.cross_config._resume import completed_attempt_matches, verify_seal
+from rl_engine.validation.cross_config.adapters import KnobMaterializer, ReferenceModelScorer, reference_materializers
+from rl_engine.validation.cross_config.comparison import compare_score_artifacts, recompute_mismatch_mask
+from rl_engine.validation.cross_config.config import config_from_dict
+from rl_engine.validation.cross_config.determinism import (compare_determinism, engine_probe, megatron_probe_from_config,
+                                                           vllm_probe_from_env)
+from rl_engine.validation.cross_config.execution_plan import build_execution_plan
+from rl_engine.validation.cross_config.planner import MAX_PLAN_CASES, Planner, PlanningError
+from rl_engine.validation.cross_config.runner import run_alignment
+from rl_engine.validation.cross_config.runtime import RuntimeTools
+from rl_engine.validation.cross_config.schema import (AlignmentStatus, CanonicalScoringBatch, IsolationScope, MaterializationStatus,
+                                                      RuntimeProvenance, ScoreArtifact, ScorerSpec, ScoreSide, SemanticIdentitySpec)
+
+
+def _identity(B=3, S=12, vocab=4096, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, vocab, (B, S), generator=g)
+    sel = torch.roll(ids, -1, 1)
+    act = torch.ones(B, S, dtype=torch.bool)
+    act[:, -1] = False
+    act[:, :3] = False
+    return SemanticIdentitySpec.from_tensors(checkpoint_id="synthetic-seed0", model_version="qwen3-scaled", token_ids=ids,
+                                             selected_token_ids=sel, active_mask=act)
+
+
+def _raw(**over):
+    i = _identity()
+    raw = {"schema_version": "cross_config.experiment_config.v1", "experiment_id": "exp", "scenario_id": "s0",
+           "identity": {k: v for k, v in i.to_dict().items() if k != "schema_version"},
+           "baseline": {"batch": {"size": 3}, "rollout": {"tensor_parallel_size": 1, "dtype": "fp32"},
+                        "training": {"compute_dtype": "fp32"}, "logp": {"backend": "reference"}},
+           "interventions": [{"path": "batch.size", "values": [3, 1]}, {"path": "rollout.tensor_parallel_size", "values": [1, 2]}]}
+    raw.update(over)
+    return raw
+
+
+def test_identity_and_batch_validation():
+    i = _identity()
+    assert i.active_token_count == 3 * 8
+    b = CanonicalScoringBatch.from_identity(i)
+    assert b.input_ids.shape == (3, 12)
+    with pytest.raises(ValueError):
+        SemanticIdentitySpec("c", "m", "p", ((1, 2), (3,)), ((1, 2), (3,)), ((True, True), (True,)), "pre")
+    with pytest.raises(ValueError):
+        CanonicalScoringBatch(i, b.input_ids + 1, b.selected_token_ids, b.active_mask, b.attention_mask)
+    json.loads(i.to_json())
+
+
+def test_planner_cases_issues_and_bounds():
+    cfg = config_from_dict(_raw())
+    plan = cfg.plan()
+    assert [c.changed_paths for c in plan.cases] == [(), ("batch.size",), ("rollout.tensor_parallel_size",)]
+    assert plan.cases[0].requested["rollout"]["dtype"] == "float32" and plan.cases[0].requested["logp"]["backend"] == "rlkernel.reference_logp"
+    assert len({c.case_id for c in plan.cases}) == 3
+    assert Planner().isolation_scope(("batch.size",)) is IsolationScope.REQUEST
+    assert Planner().isolation_scope(("batch.size", "rollout.tensor_parallel_size")) is IsolationScope.PROCESS
+    pair = config_from_dict(_raw(strategy="pairwise", pairwise_paths=[["batch.size", "rollout.tensor_parallel_size"]]))
+    assert len(pair.plan().cases) == 4
+    for bad, code in ((_raw(baseline={"batch": {"size": 0}}), "UNSUPPORTED_VALUE"), (_raw(baseline={"nope": 1}), "UNSUPPORTED_PATH"),
+                      (_raw(interventions=[{"path": "logp.backend", "values": ["pytorch"]}]), "DERIVED_KNOB"),
+                      (_raw(pairwise_paths=[["batch.size", "rollout.dtype"]]), "PAIRS_WITHOUT_STRATEGY")):
+        with pytest.raises(PlanningError) as e:
+            config_from_dict(bad).plan()
+        assert code in {i.code for i in e.value.issues}
+    big = _raw(interventions=[{"path": "batch.size", "values": list(range(1, MAX_PLAN_CASES + 3))}])
+    with pytest.raises(PlanningError, match="PLAN_TOO_LARGE"):
+        config_from_dict(big).plan()
+    for bad in (_raw(extra=1), _raw(schema_version="v0"), _raw(scenario={"atol": 1.0})):
+        with pytest.raises(ValueError):
+            config_from_dict(bad)
+    ep = build_execution_plan(cfg)
+    assert all(e.case.case_id.startswith("cross-config-") and e.case.execution_binding["base_case_id"] for e in ep.entries)
+    assert len(ep.rows()) == 3
+
+
+def test_materialisation_reports_unsupported_knobs_and_reuse_scope():
+    cfg = config_from_dict(_raw(interventions=[{"path": "batch.size", "values": [1]}, {"path": "training.sharding", "values": ["fsdp"]},
+                                               {"path": "rollout.dtype", "values": ["bf16"]}],
+                                baseline={"batch": {"size": 3}, "rollout": {"dtype": "fp32"}, "training": {"sharding": "unsharded"}}))
+    cases = cfg.plan().cases
+    tools, mats = RuntimeTools(), reference_materializers()
+    ms = [tools.materialize(c, mats) for c in cases]
+    assert [m.case.status for m in ms] == [MaterializationStatus.APPLIED, MaterializationStatus.APPLIED, MaterializationStatus.UNSUPPORTED,
+                                           MaterializationStatus.APPLIED]
+    assert not ms[2].executable and "training.training.sharding" in ms[2].case.evidence
+    assert tools.can_reuse(ms[0], ms[1]) == "engine" and tools.can_reuse(ms[0], ms[3]) == "context" and tools.can_reuse(ms[0], ms[2]) == "nothing"
+    assert ms[1].adapters["rollout"].options["batch_size"] == 1
+    lazy = KnobMaterializer("rollout", {})
+    lazy.materialize = lambda case, normalized: type(ms[0].adapters["rollout"])("rollout", ())     # reports nothing
+    with pytest.raises(Exception, match="unreported"):
+        tools.materialize(cases[0], (lazy,))
+
+
+def test_paired_run_on_reference_model_is_bitwise_and_resumes(tmp_path):
+    cfg = config_from_dict(_raw())
+    ro, tr = ReferenceModelScorer("rollout", prefill_tokens=5), ReferenceModelScorer("training")
+    s = run_alignment(cfg, tmp_path, rollout=ro, training=tr, materializers=reference_materializers(), bitwise=True)
+    assert s["all_passed"] and len(s["cases"]) == 3 and not s["not_executable"], s
+    assert all(c["mismatch_count"] == 0 and c["active_token_count"] == 24 and not c["reused"] for c in s["cases"].values())
+    again = run_alignment(cfg, tmp_path, rollout=ro, training=tr, materializers=reference_materializers(), bitwise=True)
+    assert all(c["reused"] for c in again["cases"].values()) and again["all_passed"]
+    cid = next(iter(s["cases"]))
+    attempt = tmp_path / "exp" / "paired" / cid / "0"
+    assert verify_seal(attempt)
+    (attempt / "result.json").write_text((attempt / "result.json").read_text().replace('"mismatch_count": 0', '"mismatch_count": 1'))
+    assert not verify_seal(attempt) and completed_attempt_matches(attempt, execution_fingerprint="x", case_id=cid) is None
+    third = run_alignment(cfg, tmp_path, rollout=ro, training=tr, materializers=reference_materializers(), bitwise=True)
+    assert not third["cases"][cid]["reused"] and (tmp_path / "exp" / "paired" / cid / "1").exists()
+
+
+def test_scoring_guard_and_rank_validation():
+    sc = ReferenceModelScorer("training")
+    with pytest.raises(ex.OperatorExecutionError, match="mutated"):
+        with ex.read_only_scoring_guard(sc):
+            next(iter(sc.state_tensors().values())).view(-1)[0] += 1
+    b = CanonicalScoringBatch.from_identity(_identity())
+    good = torch.zeros(3, 12)
+    assert ex.validate_rank_outputs([ex.RankScore(0, 2, good), ex.RankScore(1, 2, good)], b).rank == 0
+    with pytest.raises(ex.RankCompletenessError):
+        ex.validate_rank_outputs([ex.RankScore(0, 2, good)], b)
+    with pytest.raises(ex.RankCompletenessError, match="bits"):
+        ex.validate_rank_outputs([ex.RankScore(0, 2, good), ex.RankScore(1, 2, good + 1e-6)], b)
+    with pytest.raises(ex.OperatorExecutionError):
+        ex.validate_rank_outputs([ex.RankScore(0, 1, good * float("nan"))], b)
+    with pytest.raises(ex.ScorerIdentityError):
+        ex.validate_scorer_identity(sc, sc)
+    with pytest.raises(ex.ScorerIdentityError):
+        ex.scorer_spec(sc, ScoreSide.ROLLOUT)
+
+
+def _artifact(side, lp, identity=None, dtype="bfloat16", case="c", attempt="c/0"):
+    i = identity or _identity()
+    spec = ScorerSpec(side, "x", dtype)
+    return ScoreArtifact(case, attempt, side, i, spec, lp, torch.tensor(i.active_mask), RuntimeProvenance({}, {}, {}, {}))
+
+
+def test_comparator_statuses():
+    base = -torch.rand(3, 12)
+    r = _artifact(ScoreSide.ROLLOUT, base)
+    assert compare_score_artifacts(r, _artifact(ScoreSide.TRAINING, base + 0.01)).status is AlignmentStatus.PASS
+    res = compare_score_artifacts(r, _artifact(ScoreSide.TRAINING, base + 0.01), bitwise=True)
+    assert res.status is AlignmentStatus.FAIL and res.mismatch_count == 24 and res.diagnostics["bitwise_mismatch_count"] == 24
+    far = base.clone()
+    far[1, 5] -= 0.2
+    res = compare_score_artifacts(r, _artifact(ScoreSide.TRAINING, far))
+    assert res.status is AlignmentStatus.FAIL and res.mismatch_count == 1 and tuple(res.diagnostics["worst_token"]) == (1, 5)
+    assert compare_score_artifacts(r, _artifact(ScoreSide.TRAINING, base, dtype="float32")).fixed_threshold == 0.06
+    nanpad = base.clone()
+    nanpad[:, -1] = float("nan")                       # inactive positions may hold anything
+    assert compare_score_artifacts(r, _artifact(ScoreSide.TRAINING, nanpad)).passed
+    nanact = base.clone()
+    nanact[0, 5] = float("nan")
+    assert compare_score_artifacts(r, _artifact(ScoreSide.TRAINING, nanact)).status is AlignmentStatus.INVALID_ARTIFACT
+    other = compare_score_artifacts(r, _artifact(ScoreSide.TRAINING, base, identity=_identity(seed=1)))
+    assert other.status is AlignmentStatus.INVALID_IDENTITY and any("token_ids" in e for e in other.identity_errors)
+    assert compare_score_artifacts(r, _artifact(ScoreSide.TRAINING, base, case="d")).status is AlignmentStatus.INVALID_ARTIFACT
+    z = recompute_mismatch_mask(torch.tensor([0.0]), torch.tensor([-0.0]), torch.tensor([True]), 0.0)
+    assert bool(z[0])                                  # threshold zero means equal bits
+
+
+def test_determinism_probes():
+    class Cfg:
+        deterministic_mode = True
+        tensor_model_parallel_size = 2
+
+    env = {"NCCL_ALGO": "Ring", "VLLM_BATCH_INVARIANT": "1"}
+    rep = compare_determinism(rollout=vllm_probe_from_env(env), training=megatron_probe_from_config(Cfg(), env))
+    assert rep.compatible and "tf32_disabled" in rep.differences
+    rep = compare_determinism(rollout=vllm_probe_from_env({**env, "NCCL_ALGO": "Tree"}), training=megatron_probe_from_config(Cfg(), env))
+    assert not rep.compatible and rep.issues[0].field == "env.NCCL_ALGO"
+    rep = compare_determinism(rollout=vllm_probe_from_env({}), training=megatron_probe_from_config(Cfg(), {}))
+    assert not rep.compatible and rep.issues[0].field == "rollout.VLLM_BATCH_INVARIANT"
+    own = compare_determinism(rollout=engine_probe("rollout", env={"NCCL_ALGO": "Tree"}), training=engine_probe("training", env={"NCCL_ALGO": "Ring"}))
+    assert own.compatible and "NCCL_ALGO" in own.differences       # own collectives: NCCL's algorithm is recorded, not blocking
+    json.dumps(own.to_dict())
+    with pytest.raises(ValueError):
+        compare_determinism(rollout=engine_probe("training"), training=engine_probe("training"))
+
+
+def test_strict_json():
+    assert strict_json_loads('{"a": 1.5}') == {"a": 1.5}
+    for bad in ('{"a": 1, "a": 2}', '{"a": NaN}', '{"a": 1e999}', '{"a": Infinity}'):
+        with pytest.raises(ValueError):
+            strict_json_loads(bad)

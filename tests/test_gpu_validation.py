@@ -51,3 +51,29 @@ def test_cross_config_runner_drives_the_engine_and_sees_an_injected_offset(tmp_p
     bad = cases + [{"name": "off", "knobs": {"operator_override": "smoke_only.logp_offset"}}]
     s2 = run_experiment(ExperimentConfig.from_dict({**base, "experiment_id": "eng2", "cases": bad}), tmp_path)
     assert not s2["all_bitwise_equal"] and s2["cases"]["off"]["mismatch_count"] > 0
+
+
+def test_paired_alignment_run_on_the_engine_rollout_path_equals_training_path_bitwise(tmp_path):
+    """Rollout side = prefill + cached decode, training side = one full forward, both through Qwen3Engine: every
+    active token's selected log-prob has the same bits, for the whole batch and for singleton requests."""
+    from rl_kernel_b200.validation.cross_config.adapters import EngineScorer, engine_materializers
+    from rl_kernel_b200.validation.cross_config.config import config_from_dict
+    from rl_kernel_b200.validation.cross_config.runner import run_alignment
+    from rl_kernel_b200.validation.cross_config.schema import SemanticIdentitySpec
+
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 4096, (4, 160), generator=g)
+    act = torch.ones(4, 160, dtype=torch.bool)
+    act[:, -1] = False
+    act[:, :32] = False
+    ident = SemanticIdentitySpec.from_tensors(checkpoint_id="synthetic-seed0", model_version="qwen3-scaled", token_ids=ids,
+                                              selected_token_ids=torch.roll(ids, -1, 1), active_mask=act)
+    raw = {"schema_version": "cross_config.experiment_config.v1", "experiment_id": "eng-pair", "scenario_id": "s0",
+           "identity": {k: v for k, v in ident.to_dict().items() if k != "schema_version"},
+           "baseline": {"batch": {"size": 4}, "rollout": {"dtype": "bf16"}, "training": {"compute_dtype": "bf16"}, "logp": {"backend": "b200"}},
+           "interventions": [{"path": "batch.size", "values": [4, 1]}, {"path": "rollout.tensor_parallel_size", "values": [1, 2]}]}
+    s = run_alignment(config_from_dict(raw), tmp_path, rollout=EngineScorer("rollout", prefill_tokens=100), training=EngineScorer("training"),
+                      materializers=engine_materializers(), bitwise=True)
+    ran = [c for c in s["cases"].values() if "passed" in c]
+    assert len(ran) == 2 and s["all_passed"], s
+    assert len(s["not_executable"]) == 1           # tensor parallel size 2 is refused by the one-GPU adapter, not ignored
