@@ -10,11 +10,11 @@ from rl_kernel_b200.reference.loss.ratio_kl import ratio_kl_from_logps
 
 class _GRPOLossFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, logp, old_logp, ref_logp, adv, mask, clip_lo, clip_hi, beta):
+    def forward(ctx, logp, old_logp, ref_logp, adv, mask, clip_lo, clip_hi, beta, denominator=None):
         from rl_kernel_b200.backends import native as nv
 
         m8 = mask.to(torch.uint8).contiguous()
-        cnt = float(mask.sum().clamp_min(1).item())
+        cnt = float(mask.sum().clamp_min(1).item()) if denominator is None else float(denominator)
         r = nv.grpo_loss(logp.float().contiguous(), old_logp.float().contiguous(),
                          None if ref_logp is None else ref_logp.float().contiguous(), adv.float().contiguous(), m8,
                          clip_lo=clip_lo, clip_hi=clip_hi, beta=beta, inv_norm=1.0 / cnt)
@@ -25,18 +25,20 @@ class _GRPOLossFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g_loss, g_pol, g_kl):
         (dlogp,) = ctx.saved_tensors
-        return dlogp * g_loss, None, None, None, None, None, None, None
+        return dlogp * g_loss, None, None, None, None, None, None, None, None
 
 
 def grpo_loss(logp, old_logp, ref_logp, sample_advantages, mask, *, clip_eps: float = 0.2, beta: float = 0.0,
-              clip_eps_high: float | None = None):
+              clip_eps_high: float | None = None, denominator: float | None = None):
     """(loss, policy_loss, kl) for logp/old/ref [B, L], per-sequence advantages [B], mask [B, L].
-    Gradients flow into ``logp`` through the total loss."""
+    Gradients flow into ``logp`` through the total loss.  ``denominator``: the token count the sums are divided by
+    (default: this call's own active tokens); a micro-batch of a larger step passes the step's global count, so that
+    its per-token gradients are the bits the whole batch would give."""
     hi = clip_eps if clip_eps_high is None else clip_eps_high
     if not use_native(logp):
         return grpo_loss_from_logps(logp, old_logp, ref_logp, sample_advantages, mask, clip_eps=clip_eps, beta=beta,
-                                    clip_eps_high=hi)
-    return _GRPOLossFn.apply(logp, old_logp, ref_logp, sample_advantages, mask, clip_eps, hi, beta)
+                                    clip_eps_high=hi, denominator=denominator)
+    return _GRPOLossFn.apply(logp, old_logp, ref_logp, sample_advantages, mask, clip_eps, hi, beta, denominator)
 
 
 def ratio_kl(logp, old_logp, ref_logp, mask):
@@ -60,8 +62,9 @@ class GRPOLossOp:
     def __init__(self, clip_eps: float = 0.2, beta: float = 0.0):
         self.clip_eps, self.beta = clip_eps, beta
 
-    def __call__(self, logp, old_logp, ref_logp, sample_advantages, mask):
-        return grpo_loss(logp, old_logp, ref_logp, sample_advantages, mask, clip_eps=self.clip_eps, beta=self.beta)
+    def __call__(self, logp, old_logp, ref_logp, sample_advantages, mask, *, denominator: float | None = None):
+        return grpo_loss(logp, old_logp, ref_logp, sample_advantages, mask, clip_eps=self.clip_eps, beta=self.beta,
+                         denominator=denominator)
 
     forward = __call__
     group_advantages = staticmethod(group_advantages)

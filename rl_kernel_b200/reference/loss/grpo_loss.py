@@ -15,14 +15,19 @@ def _masked_mean(x, mask):
 
 
 def grpo_loss_from_logps(logp, old_logp, ref_logp, sample_adv, mask, *, clip_eps: float = 0.2,
-                         beta: float = 0.0, clip_eps_high: float | None = None):
-    """(loss, policy_loss, kl) from per-token log-probs; gradients flow into ``logp``."""
+                         beta: float = 0.0, clip_eps_high: float | None = None, denominator: float | None = None):
+    """(loss, policy_loss, kl) from per-token log-probs; gradients flow into ``logp``.  ``denominator`` replaces the
+    call's own active-token count (a micro-batch passes the step's global count)."""
     hi = clip_eps if clip_eps_high is None else clip_eps_high
     ratio, kl = ratio_kl_from_logps(logp, old_logp, ref_logp, mask)
     m = mask.bool()
     adv = sample_adv.reshape(-1, 1).expand_as(m).float().masked_fill(~m, 0.0)
     pol = -torch.minimum(ratio * adv, torch.clamp(ratio, 1.0 - clip_eps, 1.0 + hi) * adv)
-    policy_loss, klm = _masked_mean(pol, m), _masked_mean(kl, m)
+    if denominator is None:
+        policy_loss, klm = _masked_mean(pol, m), _masked_mean(kl, m)
+    else:
+        inv = 1.0 / float(denominator)
+        policy_loss, klm = (pol * m).sum() * inv, (kl * m).sum() * inv
     return policy_loss + beta * klm, policy_loss, klm
 
 

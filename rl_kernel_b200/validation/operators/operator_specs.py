@@ -619,11 +619,11 @@ class _Loss:
         mask = torch.tensor(padded.physical_loss_mask, dtype=torch.bool, device=dev)
         lp = pick(st["logp"]).detach().clone().requires_grad_(True)
         adv = torch.stack([st["adv"][s] for s in sids])
-        loss, _pol, _kl = op(lp, pick(st["old"]), pick(st["ref"]), adv, mask, clip_eps=0.2, beta=0.01)
-        # the operator normalises by ITS mask count; rescale to the fixture's global active count so that runs over
-        # different subsets are commensurable (the chain's loss_denominator)
-        scale = float(mask.sum()) / float(batch.active_token_count())
-        (loss * scale).backward()
+        # every run divides by the fixture's global active-token count (the chain's loss denominator), so that runs over
+        # subsets of the batch are commensurable term by term
+        loss, _pol, _kl = op(lp, pick(st["old"]), pick(st["ref"]), adv, mask, clip_eps=0.2, beta=0.01,
+                             denominator=float(batch.active_token_count()))
+        loss.backward()
         keys = [k for row in padded.restore_map for k in row]
         return _back(keys, lp.grad.reshape(B * L, 1))
 
