@@ -166,3 +166,76 @@ def test_distributed_logprob_comparison_is_topology_invariant(tmp_path):
         assert all(r["tp_outputs_bitwise_replicated"] for r in rep["ranks"])
         prints[(tp, cp)] = (rep["bitwise_fingerprints"]["logp_active_sha256"], rep["bitwise_fingerprints"]["lse_active_sha256"])
     assert prints[(1, 1)] == prints[(2, 2)]
+
+
+def test_attention_debug_matrix_runs_every_row():
+    from rl_engine.contracts.diagnostics.attention_axes import attention_debug_probe_metadata, attention_debug_taxonomy
+    from rl_engine.contracts.diagnostics.attention_matrix import attention_debug_matrix_row
+    from rl_engine.contracts.diagnostics.modules import module_debug_axis, module_debug_matrix
+    from rl_engine.reference.attention.ablation import PROBES, make_debug_inputs, run_attention_debug_matrix, run_attention_subprobe
+
+    r = run_attention_debug_matrix(make_debug_inputs(seq=160, head_dim=16))
+    by_id = {row["id"]: row for row in r["rows"]}
+    assert r["passed"] and len(by_id) == 11 and by_id["A0"]["status"] == "baseline" and by_id["A4"]["status"] == "rejected"
+    assert all(by_id[f"C{i}"]["status"] == "pass" and by_id[f"C{i}"]["out_max_abs"] == 0.0 for i in range(3))
+    assert all(by_id[f"A{i}"]["out_max_abs"] > 0 for i in (1, 2, 3, 5, 6, 7))
+    tax = attention_debug_taxonomy()
+    assert tax["root_cause_axis_count"] == 7 and set(PROBES) == {p for a in tax["root_cause_axes"].values() for p in a["subprobes"]} - {"tp_head_ownership"}
+    assert run_attention_subprobe("rope_theta", make_debug_inputs(seq=64, head_dim=16))["out_max_abs"] > 0
+    assert attention_debug_probe_metadata("split_kv")["root_cause_axis"] == "distributed_schedule"
+    assert attention_debug_matrix_row("A7").probe == "merge_order" and module_debug_axis("logp", "vocab_lse_reduction").kind == "diagnostic"
+    assert module_debug_matrix()["modules"]["ffn"]["rows"] == ["F0", "F1", "F2", "F3", "F4"]
+
+
+def test_cp_attention_reference_strict_and_ring_paths():
+    from rl_engine.reference.attention.cp_attention import (AttentionRingSchedule, DeterministicCPAttentionReferenceOp,
+                                                            compare_cp_attention_backward)
+
+    g = torch.Generator().manual_seed(0)
+    S = 96
+    q, k, v = torch.randn(S, 4, 16, generator=g), torch.randn(S, 2, 16, generator=g), torch.randn(S, 2, 16, generator=g)
+    one = DeterministicCPAttentionReferenceOp(1)(q, k, v)
+    for cp in (2, 4):
+        assert torch.equal(DeterministicCPAttentionReferenceOp(cp)(q, k, v)[0], one[0])
+        ring = DeterministicCPAttentionReferenceOp(cp, strict_bitwise=False)(q, k, v)
+        assert 0 < float((ring[0] - one[0]).abs().max()) < 1e-5
+    s = AttentionRingSchedule.build(cp_world_size=2, seq_len=96)
+    assert s.owned(1) == [(24, 48), (48, 72)] and len(s.arrivals(0)) == 4 and s.provenance()["blocks"] == 8
+    rep = compare_cp_attention_backward(q, k, v, torch.randn(S, 4, 16, generator=g), cp_world_size=2)
+    assert rep.dq.max_abs == 0.0 and rep.dk.max_rel < 1e-5 and len(rep.ranks) == 2
+
+
+def test_kv_consistency_op_checks_inventory_and_accelerator():
+    from rl_engine.validation.models.chain_gradients import missing_required_grads, required_grad_names
+    from rl_engine.validation.operators import accelerator as acc
+    from rl_engine.validation.operators.elementwise_inventory import inventory_items, unexecuted_cells, unresolved_needs_fix
+    from rl_engine.validation.operators.kv_consistency import (DecodePrefillCase, assert_decode_prefill_consistent,
+                                                               assert_stateful_kv_consistent)
+
+    r = assert_decode_prefill_consistent(device="cpu", cases=[DecodePrefillCase("b", 1, 132, 127, head_dim=16)])
+    assert r.bitwise and len(r.cells) == 5
+    s = assert_stateful_kv_consistent(device="cpu", case=DecodePrefillCase("s", 1, 50, 44, head_dim=16))
+    assert s.bitwise and s.writes == 7
+    assert not unexecuted_cells() and not unresolved_needs_fix() and len(inventory_items()) >= 15
+    assert len(required_grad_names(num_hidden_layers=36)) == 3 + 36 * 11
+    assert missing_required_grads([f"model.{n}" for n in required_grad_names(num_hidden_layers=2)][1:], num_hidden_layers=2) == ("embed_tokens.weight",)
+    assert acc.arch_key(acc.resolve_device("cpu")) == "cpu" and acc.disable_tf32("cpu") is False
+    if not torch.cuda.is_available():
+        with pytest.raises(acc.AcceleratorUnavailable):
+            acc.resolve_device(profile="b200_bf16")
+
+
+def test_every_legacy_alias_resolves():
+    import importlib
+
+    from rl_engine._legacy import LEGACY_ALIASES
+
+    bad = []
+    for old in sorted(LEGACY_ALIASES):
+        if old.endswith("__main__"):
+            continue
+        try:
+            importlib.import_module("rl_engine." + old)
+        except Exception as exc:  # noqa: BLE001
+            bad.append(f"{old}: {type(exc).__name__}: {exc}")
+    assert not bad, "\n".join(bad)
