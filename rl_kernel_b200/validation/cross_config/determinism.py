@@ -85,17 +85,24 @@ def _value(v: Any) -> Any:
     return getattr(v, "value", v)
 
 
+def _get(config: Any, name: str, default: Any = None) -> Any:
+    """Attribute of a config object or key of a mapping."""
+    if isinstance(config, Mapping):
+        return config.get(name, default)
+    return getattr(config, name, default)
+
+
 def megatron_probe_from_config(config: Any, env: Optional[Mapping[str, str]] = None) -> DeterminismProbe:
     """Training-side probe from anything exposing ``deterministic_mode`` (a ModelParallelConfig, a namespace, a double)."""
     e = dict(env or {})
-    on = bool(getattr(config, "deterministic_mode", False))
+    on = bool(_get(config, "deterministic_mode", False))
     return DeterminismProbe("training", "megatron", "deterministic_mode", on, {k: e.get(k) for k in COMPARED_NCCL_KEYS}, None, None, on,
                             False, {"nvte_allow_nondeterministic_algo": e.get("NVTE_ALLOW_NONDETERMINISTIC_ALGO"),
-                                    "cross_entropy_loss_fusion": getattr(config, "cross_entropy_loss_fusion", None),
-                                    "attention_backend": _value(getattr(config, "attention_backend", None)),
-                                    "tensor_model_parallel_size": getattr(config, "tensor_model_parallel_size", None),
-                                    "context_parallel_size": getattr(config, "context_parallel_size", None),
-                                    "sequence_parallel": getattr(config, "sequence_parallel", None), "manages_tf32": False,
+                                    "cross_entropy_loss_fusion": _get(config, "cross_entropy_loss_fusion", None),
+                                    "attention_backend": _value(_get(config, "attention_backend", None)),
+                                    "tensor_model_parallel_size": _get(config, "tensor_model_parallel_size", None),
+                                    "context_parallel_size": _get(config, "context_parallel_size", None),
+                                    "sequence_parallel": _get(config, "sequence_parallel", None), "manages_tf32": False,
                                     "manages_bf16_reduced_precision_reduction": False})
 
 
@@ -106,9 +113,9 @@ def vllm_probe_from_env(env: Mapping[str, str], *, model_config: Any = None) -> 
                             False if on else None, False, False,
                             {"vllm_allreduce_use_symm_mem": env.get("VLLM_ALLREDUCE_USE_SYMM_MEM"),
                              "vllm_use_aot_compile": env.get("VLLM_USE_AOT_COMPILE"),
-                             "enforce_eager": getattr(model_config, "enforce_eager", None),
-                             "disable_cascade_attn": getattr(model_config, "disable_cascade_attn", None),
-                             "quantization": getattr(model_config, "quantization", None), "manages_tf32": True,
+                             "enforce_eager": _get(model_config, "enforce_eager", None),
+                             "disable_cascade_attn": _get(model_config, "disable_cascade_attn", None),
+                             "quantization": _get(model_config, "quantization", None), "manages_tf32": True,
                              "manages_bf16_reduced_precision_reduction": True})
 
 

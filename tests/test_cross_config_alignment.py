@@ -191,3 +191,62 @@ def test_strict_json():
     for bad in ('{"a": 1, "a": 2}', '{"a": NaN}', '{"a": 1e999}', '{"a": Infinity}'):
         with pytest.raises(ValueError):
             strict_json_loads(bad)
+
+
+def test_cpu_fixture_detects_a_smoke_offset_operator_and_viewer_renders(tmp_path, capsys):
+    from rl_engine.validation.fixtures.cpu_cross_config import run_cpu_case, run_cpu_experiment
+    from rl_engine.validation.reports.viewer import load_bundle, main as view, worst_tokens
+
+    base = _raw(baseline={"batch": {"size": 3}, "rollout": {"dtype": "fp32"}, "training": {"compute_dtype": "fp32"},
+                          "logp": {"backend": "reference"}}, interventions=[{"path": "batch.size", "values": [1]}])
+    good = run_cpu_experiment(config_from_dict(base), tmp_path)
+    assert good["all_passed"] and len(good["cases"]) == 2
+    one = run_cpu_case(config_from_dict(base), 1)
+    assert torch.equal(one["rollout"], one["training"])
+    bad_raw = dict(base, experiment_id="exp-bad", operators={"selected_logprob": {"rollout": {"backend": "reference"},
+                                                                                  "training": {"backend": "smoke_only.logp_offset"}}})
+    bad = run_cpu_experiment(config_from_dict(bad_raw), tmp_path, bitwise=False)
+    assert not bad["all_passed"] and all(c["mismatch_count"] == c["active_token_count"] for c in bad["cases"].values())
+    bundle = load_bundle(tmp_path / "exp-bad")
+    cid = next(iter(bundle["cases"]))
+    assert abs(worst_tokens(bundle, cid, 3)[0]["abs_diff"] - 0.25) < 1e-5
+    assert view([str(tmp_path / "exp-bad"), "--case", cid, "--html", str(tmp_path / "v.html")]) == 1
+    assert "RED" in capsys.readouterr().out and (tmp_path / "v.html").read_text().startswith("<!doctype html>")
+    assert view([str(tmp_path / "exp")]) == 0 and view([str(tmp_path / "nothing-here")]) == 2
+
+
+def test_framework_materialisers_translate_attention_knobs():
+    from rl_engine.integrations.common.knobs import WS2_ATTENTION_KNOBS, WS2_ATTENTION_NORMALIZERS
+    from rl_engine.integrations.common.state import clear_active_integration, get_active_integration, set_active_integration
+    from rl_engine.integrations.engines.rollout.vllm.adapter import VllmIntegration
+    from rl_engine.integrations.engines.rollout.vllm.cross_config import VllmProvenanceAdapter, VllmRolloutMaterializer
+    from rl_engine.integrations.engines.train.megatron.cross_config import MegatronAttentionMaterializer, MegatronProvenanceAdapter
+    from rl_engine.validation.cross_config.schema import ExperimentDefinition, InterventionSpec
+
+    d = ExperimentDefinition("e", "s", _identity(), {"batch": {"size": 2}, "rollout": {"tensor_parallel_size": 2, "kv_block_size": 128, "batch_invariant": True},
+                                                     "training": {"tensor_parallel_size": 2, "context_parallel_size": 1, "deterministic_mode": True,
+                                                                  "cp_comm_type": "peer_memory"}, "attention": {"reduction_order": "global_block_index"}},
+                             (InterventionSpec("training.context_parallel_size", (2,)), InterventionSpec("attention.reduction_order", ("arrival",)),
+                              InterventionSpec("rollout.kv_block_size", (16,)), InterventionSpec("training.cp_comm_type", ("p2p",))))
+    plan = Planner(knobs=WS2_ATTENTION_KNOBS, normalizers=WS2_ATTENTION_NORMALIZERS).plan(d)
+    tools = RuntimeTools(WS2_ATTENTION_KNOBS)
+    got = {c.changed_paths: tools.materialize(c, (VllmRolloutMaterializer(), MegatronAttentionMaterializer())) for c in plan.cases}
+    assert got[()].case.status is MaterializationStatus.APPLIED and "attention_contract_fingerprint" in got[()].adapters["training"].options
+    assert got[("training.context_parallel_size",)].case.status is MaterializationStatus.APPLIED
+    for path in ("attention.reduction_order", "rollout.kv_block_size", "training.cp_comm_type"):
+        assert got[(path,)].case.status is MaterializationStatus.UNSUPPORTED, path
+    assert tools.can_reuse(got[()], got[("training.context_parallel_size",)]) == "nothing"
+    pa = VllmProvenanceAdapter(cache_config={"block_size": 128, "cache_dtype": "fp8"}, env={"VLLM_BATCH_INVARIANT": "1"})
+    assert pa.frozen_scope_violations() == ("cache_dtype='fp8' (expected 'auto')",) and pa.kv_page_size == 128 and pa.determinism_probe().enabled
+    ma = MegatronProvenanceAdapter({"deterministic_mode": True, "pipeline_model_parallel_size": 2})
+    assert ma.frozen_scope_violations() and ma.determinism_probe().enabled
+    integ = VllmIntegration()
+    set_active_integration("vllm", integ)
+    try:
+        assert get_active_integration("vllm") is integ
+        with pytest.raises(RuntimeError):
+            set_active_integration("vllm", VllmIntegration())
+        with pytest.raises(ValueError):
+            set_active_integration("megatron", integ)
+    finally:
+        clear_active_integration("vllm")

@@ -70,7 +70,7 @@ def test_paired_alignment_run_on_the_engine_rollout_path_equals_training_path_bi
                                               selected_token_ids=torch.roll(ids, -1, 1), active_mask=act)
     raw = {"schema_version": "cross_config.experiment_config.v1", "experiment_id": "eng-pair", "scenario_id": "s0",
            "identity": {k: v for k, v in ident.to_dict().items() if k != "schema_version"},
-           "baseline": {"batch": {"size": 4}, "rollout": {"dtype": "bf16"}, "training": {"compute_dtype": "bf16"}, "logp": {"backend": "b200"}},
+           "baseline": {"batch": {"size": 4}, "rollout": {"dtype": "bf16", "tensor_parallel_size": 1}, "training": {"compute_dtype": "bf16"}, "logp": {"backend": "b200"}},
            "interventions": [{"path": "batch.size", "values": [4, 1]}, {"path": "rollout.tensor_parallel_size", "values": [1, 2]}]}
     s = run_alignment(config_from_dict(raw), tmp_path, rollout=EngineScorer("rollout", prefill_tokens=100), training=EngineScorer("training"),
                       materializers=engine_materializers(), bitwise=True)
