@@ -153,3 +153,47 @@ def test_ray_actor_manager_with_fake_ray():
         mgr.spawn("a", "rollout", W, 1)
     mgr.shutdown()
     assert not mgr.workers
+
+
+def test_vime_providers_over_structural_requests():
+    from types import SimpleNamespace as NS
+
+    import torch
+
+    from rl_engine.integrations.vime import attention as att, linear_logp_provider as llp, logp
+
+    g = torch.Generator().manual_seed(0)
+    T, V, H = 9, 1024, 64
+    logits, tg = torch.randn(T, V, generator=g), torch.randint(0, 1000, (T,), generator=g)
+    md = {"real_vocab_size": 1000, "padded_vocab_size": 1024}
+    r = logp.provider(NS(logits=logits, target_ids=tg, metadata=md, context_parallel=NS(world_size=1, rank=0, layout="single"),
+                         tensor_parallel_group=None, with_entropy=True))
+    ref = torch.log_softmax(logits[:, :1000], -1).gather(1, tg[:, None])
+    assert (r.selected_logprobs - ref).abs().max() < 1e-5 and r.entropy.shape == (T,) and not r.provenance["cp_row_ownership"]["cp_is_merge_axis"]
+    keep = torch.rand(T, V, generator=g) > 0.5
+    keep[torch.arange(T), tg] = True
+    r2 = logp.provider(NS(logits=logits, target_ids=tg, metadata=md, log_prob_keep_mask=keep))
+    ref2 = torch.log_softmax(logits.masked_fill(~keep, float("-inf"))[:, :1000], -1).gather(1, tg[:, None])
+    assert (r2.selected_logprobs - ref2).abs().max() < 1e-5 and r2.provenance["execution"]["top_p_replay"]
+    for bad in (NS(logits=logits, target_ids=tg, metadata={"real_vocab_size": 1000, "padded_vocab_size": 2048}),
+                NS(logits=logits, target_ids=tg[:-1], metadata=md),
+                NS(logits=logits, target_ids=tg, metadata=md, context_parallel=NS(world_size=2, rank=0, layout="single"))):
+        try:
+            logp.provider(bad)
+            raise AssertionError("accepted an inconsistent request")
+        except logp.SelectedLogprobProviderUnavailable as exc:
+            assert exc.selected_logprob_provider_unavailable
+    hid = torch.randn(T, H, generator=g)
+    W = torch.zeros(V, H)
+    W[:1000] = torch.randn(1000, H, generator=g) * 0.1
+    r3 = llp.provider(NS(hidden=hid, weight=W, target_ids=tg, metadata=md, temperature=0.7))
+    ref3 = torch.log_softmax((hid @ W.t())[:, :1000] / 0.7, -1).gather(1, tg[:, None])
+    assert (r3.selected_logprobs - ref3).abs().max() < 1e-5 and not r3.provenance["execution"]["logits_materialized"]
+    q, k, v = torch.randn(32, 4, 16, generator=g), torch.randn(32, 2, 16, generator=g), torch.randn(32, 2, 16, generator=g)
+    r4 = att.attention_provider(NS(q=q, k=k, v=v, metadata={"global_sequence_length": 16, "num_sequences": 2}))
+    assert r4.out.shape == q.shape and r4.lse.shape == (32, 4)
+    try:
+        att.attention_provider(NS(q=q, k=k, v=v, sliding_window=(128, 0), metadata={"global_sequence_length": 16, "num_sequences": 2}))
+        raise AssertionError("accepted a sliding window")
+    except att.AttentionProviderUnavailable:
+        pass
