@@ -72,38 +72,91 @@ def cmd_plan(args) -> int:
     return 0
 
 
-def _validate_topology(tp: int, cp: int, gpus: int) -> None:
-    if tp * cp != gpus:
-        raise SystemExit(f"tp ({tp}) x cp ({cp}) must equal --gpus ({gpus})")
+def _parse_plan(text: str) -> dict:
+    """"tp4xcp2", "dp8", "tp2xdp4" -> {"tp": .., "cp": .., "dp": ..}."""
+    plan = {"tp": 1, "cp": 1, "dp": 1}
+    for part in text.lower().split("x"):
+        for key in plan:
+            if part.startswith(key) and part[len(key):].isdigit():
+                plan[key] = int(part[len(key):])
+                break
+        else:
+            raise SystemExit(f"cannot parse plan component {part!r} (expected e.g. tp4xcp2, dp8, tp2xdp4)")
+    return plan
+
+
+def _validate_topology(tp: int, cp: int, gpus: int, dp: int = 1) -> None:
+    if tp * cp * dp != gpus:
+        raise SystemExit(f"tp ({tp}) x cp ({cp}) x dp ({dp}) must equal --gpus ({gpus})")
     for n in (tp, cp):
         if n not in (1, 2, 4, 8):
             raise SystemExit("tp and cp must be 1, 2, 4 or 8")
 
 
+def _free_port() -> int:
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def launch_command(argv: list[str], gpus: int, port: int | None = None) -> list[str]:
+    """The command that runs ``rlk <argv>`` as one rank per GPU on this node."""
+    return [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={gpus}", "--master-addr", "127.0.0.1",
+            "--master-port", str(port or _free_port()), "-m", "rl_kernel_b200.entrypoints.repro", *argv]
+
+
 def cmd_run(args) -> int:
     import torch
 
-    _validate_topology(args.tp, args.cp, args.gpus)
+    plan = _parse_plan(args.plan) if args.plan else {"tp": args.tp, "cp": args.cp, "dp": max(1, args.gpus // (args.tp * args.cp))}
+    _validate_topology(plan["tp"], plan["cp"], args.gpus, plan["dp"])
     if not torch.cuda.is_available():
         raise SystemExit("rlk run needs a CUDA device (use `rlk validate` for the CPU checks)")
-    busy = _gpu_busy()
-    if busy and not args.allow_busy:
-        raise SystemExit(f"GPUs already run compute processes: {busy}; pass --allow-busy to run anyway")
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.gpus > 1 and world == 1:
+        # one process per GPU: re-launch this command under the elastic launcher and hand its exit code back
+        import subprocess
+
+        if torch.cuda.device_count() < args.gpus:
+            raise SystemExit(f"--gpus {args.gpus} but only {torch.cuda.device_count()} CUDA devices are visible")
+        busy = _gpu_busy()
+        if busy and not args.allow_busy:
+            raise SystemExit(f"GPUs already run compute processes: {busy}; pass --allow-busy to run anyway")
+        return subprocess.call(launch_command(args.raw_argv + ["--allow-busy"], args.gpus))
+    if world != args.gpus:
+        raise SystemExit(f"WORLD_SIZE={world} but --gpus {args.gpus}")
+    rank, local = int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    if world == 1:
+        busy = _gpu_busy()
+        if busy and not args.allow_busy:
+            raise SystemExit(f"GPUs already run compute processes: {busy}; pass --allow-busy to run anyway")
     from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec
     from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
 
-    dev = torch.device("cuda:0")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    ctx = None
+    if world > 1:
+        import torch.distributed as dist
+
+        from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context
+
+        dist.init_process_group("nccl", device_id=dev)
+        ctx = build_parallel_context(plan["tp"], plan["cp"], dev, dp=plan["dp"])
     spec = Qwen3DenseSpec.official() if args.official else Qwen3DenseSpec.scaled(
         layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
     cfg = GRPOConfig(num_prompts=args.prompts, group_size=args.group, prompt_len=args.prompt_len,
-                     response_len=args.response_len, micro_batch_seqs=args.micro_batch, lr=args.lr, seed=args.seed,
-                     share_rollout_weights=args.official)
-    trainer = GRPOTrainer(spec, cfg, dev)
+                     response_len=args.response_len, micro_batch_seqs=args.micro_batch * plan["cp"], lr=args.lr, seed=args.seed,
+                     share_rollout_weights=args.official and world == 1)
+    trainer = GRPOTrainer(spec, cfg, dev, ctx=ctx) if ctx is not None else GRPOTrainer(spec, cfg, dev)
     run_dir = Path(args.out)
-    run_dir.mkdir(parents=True, exist_ok=True)
+    if rank == 0:
+        run_dir.mkdir(parents=True, exist_ok=True)
     gen = torch.Generator().manual_seed(args.seed)
     total_mism = 0
-    with open(run_dir / "rounds.jsonl", "w") as f:
+    with open(run_dir / "rounds.jsonl" if rank == 0 else os.devnull, "w") as f:
         for step in range(args.steps):
             prompts = torch.randint(0, spec.vocab_size, (cfg.num_prompts, cfg.prompt_len), generator=gen).to(dev)
             t0 = time.perf_counter()
@@ -116,20 +169,75 @@ def cmd_run(args) -> int:
                    "reward_mean": float(out["rewards"].mean()), "grad_norm": float(out["grad_norm"]),
                    "step_seconds": time.perf_counter() - t0, "phase_ms": trainer.phase_ms()}
             f.write(json.dumps(rec) + "\n")
-            print(json.dumps(rec))
-    (run_dir / "summary.json").write_text(json.dumps({"steps": args.steps, "total_mismatches": total_mism,
-                                                       "model": spec.model_id}))
+            if rank == 0:
+                print(json.dumps(rec))
+    if rank == 0:
+        (run_dir / "summary.json").write_text(json.dumps({"steps": args.steps, "total_mismatches": total_mism, "model": spec.model_id,
+                                                           "gpus": args.gpus, "plan": plan}))
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+        dist.destroy_process_group()
     return 0 if total_mism == 0 else 2
+
+
+def _verify_rounds(run_dir: Path) -> tuple[dict, bool]:
+    recs = [json.loads(line) for line in (run_dir / "rounds.jsonl").read_text().splitlines() if line.strip()]
+    bad = [r for r in recs if r["mismatch_count"] != 0]
+    return {"kind": "training_rounds", "steps": len(recs), "steps_with_mismatches": len(bad),
+            "tokens_compared": sum(r["tokens_compared"] for r in recs), "total_mismatches": sum(r["mismatch_count"] for r in recs)}, bool(recs) and not bad
+
+
+def _verify_attempts(run_dir: Path, case_id: str | None) -> tuple[dict, bool]:
+    """Re-check the sealed attempts of a cross-config (``cases/``) or paired-alignment (``paired/``) run: every seal must
+    verify, and every stored comparison must be reproducible from the stored tensors.  ``case_id`` restricts the check."""
+    import torch
+
+    from rl_kernel_b200.validation.cross_config._resume import comparison_matches, load_tensor_bundle, read_json_object, verify_seal
+    from rl_kernel_b200.validation.cross_config.artifacts import AttemptStore
+
+    out = {"kind": "cross_config", "cases": {}}
+    ok = True
+    found = False
+    for sub, paired in (("cases", False), ("paired", True)):
+        for root in sorted(run_dir.glob(f"**/{sub}")):
+            for case_dir in sorted(p for p in root.iterdir() if p.is_dir()):
+                if case_id and case_dir.name != case_id:
+                    continue
+                attempts = sorted((p for p in case_dir.iterdir() if p.is_dir() and p.name.isdigit()), key=lambda p: int(p.name))
+                if not attempts:
+                    continue
+                found = True
+                last = attempts[-1]
+                sealed = verify_seal(last) if paired else AttemptStore.verify(last)
+                row = {"attempts": len(attempts), "sealed": sealed}
+                if sealed and paired:
+                    res = read_json_object(last / "result.json")
+                    row.update(status=res["status"], passed=res["passed"], mismatch_count=res["mismatch_count"],
+                               recomputed=comparison_matches(res, load_tensor_bundle(last / "tensors.pt")))
+                    ok &= row["recomputed"] and res["passed"]
+                elif sealed and (last / "comparison.json").exists():
+                    cmp = json.loads((last / "comparison.json").read_text())
+                    row.update(mismatch_count=cmp["mismatch_count"])
+                    ok &= cmp["mismatch_count"] == 0
+                ok &= sealed
+                out["cases"][case_dir.name] = row
+    if case_id and not found:
+        raise SystemExit(f"no case {case_id!r} under {run_dir}")
+    return out, ok and found
 
 
 def cmd_verify(args) -> int:
     run_dir = Path(args.run_dir)
-    recs = [json.loads(line) for line in (run_dir / "rounds.jsonl").read_text().splitlines() if line.strip()]
-    bad = [r for r in recs if r["mismatch_count"] != 0]
-    print(json.dumps({"steps": len(recs), "steps_with_mismatches": len(bad),
-                      "tokens_compared": sum(r["tokens_compared"] for r in recs),
-                      "total_mismatches": sum(r["mismatch_count"] for r in recs)}))
-    return 0 if recs and not bad else 2
+    if not run_dir.exists():
+        raise SystemExit(f"{run_dir} does not exist")
+    if (run_dir / "rounds.jsonl").exists() and not args.case_id:
+        info, ok = _verify_rounds(run_dir)
+    else:
+        info, ok = _verify_attempts(run_dir, args.case_id)
+    print(json.dumps(info, indent=1))
+    return 0 if ok else 2
 
 
 def cmd_validate(args) -> int:
@@ -194,11 +302,13 @@ def build_parser() -> argparse.ArgumentParser:
         p.add_argument(f"--{name}", type=typ, default=dflt)
     p.add_argument("--lr", type=float, default=1e-6)
     p.add_argument("--official", action="store_true", help="full Qwen3-8B shape")
+    p.add_argument("--plan", default="", help="parallel layout over --gpus, e.g. tp4xcp2, dp8, tp2xdp4 (default: --tp x --cp, rest data parallel)")
     p.add_argument("--allow-busy", action="store_true")
     p.add_argument("--out", default="runs/latest")
     p.set_defaults(fn=cmd_run)
     p = sub.add_parser("verify")
     p.add_argument("run_dir")
+    p.add_argument("--case-id", default=None, help="check one case of a cross-config / paired run directory")
     p.set_defaults(fn=cmd_verify)
     p = sub.add_parser("validate")
     p.add_argument("--device", default="auto")
@@ -217,7 +327,9 @@ def build_parser() -> argparse.ArgumentParser:
 
 
 def main(argv=None) -> int:
-    args = build_parser().parse_args(argv)
+    raw = list(sys.argv[1:] if argv is None else argv)
+    args = build_parser().parse_args(raw)
+    args.raw_argv = raw
     return int(args.fn(args) or 0)
 
 

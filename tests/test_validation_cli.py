@@ -102,3 +102,35 @@ def test_chain_gate_on_reference_model():
     ids = torch.randint(0, 512, (3, 12), generator=torch.Generator().manual_seed(0))
     res = run_chain_gate(Qwen3DenseBIModel(spec, w, tp_size=2), Qwen3DenseBIModel(spec, w), ids, decode_from=6)
     assert res.passed, (res.cells, res.aggregates, res.first_drift)
+
+
+def test_pyproject_entry_points_resolve():
+    import importlib
+    import tomllib
+    from pathlib import Path
+
+    data = tomllib.loads((Path(__file__).resolve().parents[1] / "pyproject.toml").read_text())
+    targets = {**data["project"]["scripts"], **data["project"]["entry-points"]["vllm.general_plugins"]}
+    assert set(data["project"]["scripts"]) == {"rlk", "rlk-repro", "rlk-drift-view"}
+    for name, target in targets.items():
+        mod, fn = target.split(":")
+        assert callable(getattr(importlib.import_module(mod), fn)), name
+
+
+def test_rlk_verify_checks_sealed_attempts_and_case_ids(tmp_path, capsys):
+    from rl_engine.entrypoints.repro import _parse_plan, launch_command, main as rlk
+
+    run_experiment(_exp(), tmp_path)
+    assert rlk(["verify", str(tmp_path)]) == 0
+    assert rlk(["verify", str(tmp_path), "--case-id", "tp2"]) == 0
+    victim = next((tmp_path / "t" / "cases" / "b1").iterdir()) / "score.pt"
+    victim.write_bytes(victim.read_bytes() + b"x")
+    assert rlk(["verify", str(tmp_path)]) == 2
+    with pytest.raises(SystemExit):
+        rlk(["verify", str(tmp_path), "--case-id", "nope"])
+    assert _parse_plan("tp4xcp2") == {"tp": 4, "cp": 2, "dp": 1} and _parse_plan("tp2xdp4")["dp"] == 4
+    with pytest.raises(SystemExit):
+        _parse_plan("pp2")
+    cmd = launch_command(["run", "--gpus", "8", "--plan", "tp4xcp2"], 8, port=29511)
+    assert cmd[1:4] == ["-m", "torch.distributed.run", "--nnodes=1"] and "--nproc-per-node=8" in cmd and cmd[-4:] == ["--gpus", "8", "--plan", "tp4xcp2"]
+    assert "127.0.0.1" in cmd
