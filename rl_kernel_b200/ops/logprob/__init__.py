@@ -190,23 +190,28 @@ class _LinearLogpFn(torch.autograd.Function):
         inv_temp, chunk = ctx.meta
         rows, H = hidden.shape
         V = weight.shape[0]
+        v8 = (V + 7) // 8 * 8                    # GEMM extents step by 8: a vocabulary that is not a multiple (rare) is padded with zero rows
+        wmat = weight if v8 == V else torch.cat([weight, weight.new_zeros(v8 - V, H)])
         g = g.float().contiguous()
         dh = torch.empty_like(hidden)
-        dw = torch.zeros_like(weight)
+        dw = torch.zeros_like(wmat)
         for r0 in range(0, rows, chunk):
             r1 = min(rows, r0 + chunk)
             n = r1 - r0
             npad = (n + 7) // 8 * 8           # the dW contraction runs over rows: zero rows pad it to the GEMM's K step
-            buf = torch.empty(npad, V, device=hidden.device, dtype=hidden.dtype)
+            buf = torch.empty(npad, v8, device=hidden.device, dtype=hidden.dtype)
             logits, hrows = buf[:n], hidden[r0:r1]
-            nv.det_gemm(hrows, weight, logits, M=n, N=V, K=H)
+            nv.det_gemm(hrows, wmat, logits, M=n, N=v8, K=H)
             nv.dlogits_(logits, targets[r0:r1], lse[r0:r1], g[r0:r1], vocab_start=0, inv_temp=inv_temp,
                         min_keep=None if min_keep is None else min_keep[r0:r1])
-            nv.det_gemm(logits, weight, dh[r0:r1], M=n, N=H, K=V, b_mn=True)
+            if v8 != V:
+                logits[:, V:].zero_()          # padding ids are outside the softmax: no gradient
+            nv.det_gemm(logits, wmat, dh[r0:r1], M=n, N=H, K=v8, b_mn=True)
             if npad != n:
                 buf[n:].zero_()
                 hrows = torch.cat([hrows, hrows.new_zeros(npad - n, H)])
-            nv.det_gemm(buf, hrows, dw, M=V, N=H, K=npad, a_mn=True, b_mn=True, accumulate=True)
+            nv.det_gemm(buf, hrows, dw, M=v8, N=H, K=npad, a_mn=True, b_mn=True, accumulate=True)
+        dw = dw if v8 == V else dw[:V].contiguous()
         return dh, dw, None, None, None, None
 
 
@@ -221,8 +226,6 @@ def linear_logp(hidden: torch.Tensor, weight: torch.Tensor, targets: torch.Tenso
     mk = _keep_rows(min_keep, h.shape[0], h.device)
     if not use_native(h, weight):
         return NativeLinearLogpOp(temperature)(h, weight, targets.reshape(-1), min_keep=mk).view(shp)
-    if weight.shape[0] % 8:
-        raise ValueError("vocab size must be a multiple of 8 for the fused LM head")
     return _LinearLogpFn.apply(h.contiguous(), weight.contiguous(), targets.reshape(-1).contiguous(),
                                1.0 / temperature, chunk, mk).view(shp)
 
