@@ -230,3 +230,14 @@ def test_top_p_rollout_and_training_logprobs_agree_bitwise():
     # restricted log-probs are never below the unrestricted ones of the same token (the support only shrinks)
     lp_free = free.score(free.policy, res["tokens"])
     assert (res["old_logp"] >= lp_free - 1e-5).all()
+
+
+def test_dense_experiment_arm_with_library_logp_reports_the_drift_the_strict_path_removes(tmp_path):
+    from rl_kernel_b200.integrations.orchestrators.vime.experiments.dense import run_arm, validate_run, weight_audit
+
+    s = run_arm.run_arm(tmp_path / "arm", phase="short", group="library_logp", seed=1234, num_rollout=2)
+    assert s["strict_mismatches"] == 0 and s["library_mismatches"] > 0
+    v = validate_run.validate_run(tmp_path / "arm")
+    assert v["valid"], v
+    again = run_arm.run_arm(tmp_path / "arm", phase="short", group="library_logp", seed=1234, num_rollout=2)
+    assert again["tokens"] == s["tokens"]                      # a finished arm is not run twice

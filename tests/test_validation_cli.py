@@ -134,3 +134,40 @@ def test_rlk_verify_checks_sealed_attempts_and_case_ids(tmp_path, capsys):
     cmd = launch_command(["run", "--gpus", "8", "--plan", "tp4xcp2"], 8, port=29511)
     assert cmd[1:4] == ["-m", "torch.distributed.run", "--nnodes=1"] and "--nproc-per-node=8" in cmd and cmd[-4:] == ["--gpus", "8", "--plan", "tp4xcp2"]
     assert "127.0.0.1" in cmd
+
+
+def test_dense_experiment_planning_validation_and_collection(tmp_path):
+    from rl_engine.integrations.orchestrators.vime.experiments.dense import collect_results, run, run_arm, validate_run, weight_audit
+
+    plan = run.run_phase(tmp_path, "module_ablation", dry_run=True)["arms"]
+    assert plan["module_ablation/M011/seed1234"]["status"] == "unavailable" and plan["module_ablation/M111/seed1234"]["status"] == "planned"
+    with pytest.raises(run_arm.ArmUnavailable):
+        run_arm.resolve_arm(run_arm.load_matrix(), "short", "native")
+    assert run_arm.resolve_arm(run_arm.load_matrix(), "short", "G11")["framework_use_rollout_logprobs"] is True
+
+    def fake_arm(group, logp_case, mism, lib=None, steps=3):
+        d = tmp_path / "short" / group / "seed1234"
+        d.mkdir(parents=True)
+        (d / "arm.json").write_text(json.dumps({"phase": "short", "group": group, "seed": 1234, "num_rollout": steps, "attention_case": "R/R",
+                                                "ffn_case": "R/R", "logp_case": logp_case}))
+        recs = [{"step": i, "tokens_compared": 512, "mismatch_count": mism if i == 1 else 0, "max_abs_dlogp": 0.0, "reward_mean": 0.5,
+                 "grad_norm": 1.0, "step_seconds": 0.1 + i, **({"library_mismatch_count": lib} if lib is not None else {})} for i in range(steps)]
+        (d / "rounds.jsonl").write_text("\n".join(json.dumps(r) for r in recs) + "\n")
+        (d / "readback.json").write_text(json.dumps({"fallbacks": []}))
+        (d / "summary.json").write_text("{}")
+        (d / "DONE").write_text("ok")
+        return d
+
+    good, lib, bad = fake_arm("consistency", "R/R", 0), fake_arm("library_logp", "R/P", 0, lib=200), fake_arm("G11", "R/R", 7)
+    assert validate_run.validate_run(good)["valid"] and validate_run.validate_run(lib)["library_mismatches"] == 600
+    v = validate_run.validate_run(bad)
+    assert not v["valid"] and "bit-equal" in v["issues"][0]
+    (good / "DONE").unlink()
+    assert not validate_run.validate_run(good)["valid"]
+    (good / "DONE").write_text("ok")
+    rows = collect_results.collect(tmp_path)
+    assert [r["group"] for r in rows] == ["G11", "consistency", "library_logp"] and [r["valid"] for r in rows] == [False, True, True]
+    paths = collect_results.write_tables(rows, tmp_path / "out")
+    assert paths["markdown"].read_text().count("\n") == 5 and paths["csv"].read_text().startswith("phase,group,seed")
+    a = weight_audit.audit_weights({"w": torch.ones(2), "v": torch.zeros(1)}, {"w": torch.ones(2) * 2})
+    assert not a["in_sync"] and a["differing"] == ["w"] and a["missing_in_rollout"] == ["v"]
