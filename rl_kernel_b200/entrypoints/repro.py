@@ -167,6 +167,7 @@ def cmd_run(args) -> int:
             rec = {"step": step, "mismatch_count": mism, "tokens_compared": out["old_logp"].numel(),
                    "max_abs_dlogp": float((out["train_logp"] - out["old_logp"]).abs().max()),
                    "reward_mean": float(out["rewards"].mean()), "grad_norm": float(out["grad_norm"]),
+                   "loss": float(out["loss_sums"][4]), "policy_loss": float(out["loss_sums"][5]), "kl": float(out["loss_sums"][6]), "weight_version": int(trainer.weight_version),
                    "step_seconds": time.perf_counter() - t0, "phase_ms": trainer.phase_ms()}
             f.write(json.dumps(rec) + "\n")
             if rank == 0:
@@ -183,10 +184,33 @@ def cmd_run(args) -> int:
 
 
 def _verify_rounds(run_dir: Path) -> tuple[dict, bool]:
+    """Acceptance checks of a training run: every step compared tokens and found no mismatch, every metric is finite,
+    steps are consecutive and the published weight version grows by one per step."""
+    import math
+
     recs = [json.loads(line) for line in (run_dir / "rounds.jsonl").read_text().splitlines() if line.strip()]
     bad = [r for r in recs if r["mismatch_count"] != 0]
-    return {"kind": "training_rounds", "steps": len(recs), "steps_with_mismatches": len(bad),
-            "tokens_compared": sum(r["tokens_compared"] for r in recs), "total_mismatches": sum(r["mismatch_count"] for r in recs)}, bool(recs) and not bad
+    issues = []
+    if [r["step"] for r in recs] != list(range(len(recs))):
+        issues.append("steps are not consecutive from 0")
+    for r in recs:
+        for k in ("max_abs_dlogp", "reward_mean", "grad_norm", "loss"):
+            if r.get(k) is not None and not math.isfinite(float(r[k])):
+                issues.append(f"step {r['step']}: {k} is not finite")
+        if r.get("tokens_compared", 0) <= 0:
+            issues.append(f"step {r['step']}: no tokens compared")
+    versions = [r["weight_version"] for r in recs if r.get("weight_version") is not None]
+    if versions and any(b - a != 1 for a, b in zip(versions, versions[1:])):
+        issues.append("weight versions do not grow by one per step")
+    summary = run_dir / "summary.json"
+    if summary.exists():
+        want = json.loads(summary.read_text()).get("steps")
+        if want is not None and want != len(recs):
+            issues.append(f"summary.json names {want} steps, rounds.jsonl holds {len(recs)}")
+    info = {"kind": "training_rounds", "steps": len(recs), "steps_with_mismatches": len(bad),
+            "tokens_compared": sum(r["tokens_compared"] for r in recs), "total_mismatches": sum(r["mismatch_count"] for r in recs),
+            "weight_versions": [versions[0], versions[-1]] if versions else None, "issues": issues}
+    return info, bool(recs) and not bad and not issues
 
 
 def _verify_attempts(run_dir: Path, case_id: str | None) -> tuple[dict, bool]:

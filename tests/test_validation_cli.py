@@ -171,3 +171,21 @@ def test_dense_experiment_planning_validation_and_collection(tmp_path):
     assert paths["markdown"].read_text().count("\n") == 5 and paths["csv"].read_text().startswith("phase,group,seed")
     a = weight_audit.audit_weights({"w": torch.ones(2), "v": torch.zeros(1)}, {"w": torch.ones(2) * 2})
     assert not a["in_sync"] and a["differing"] == ["w"] and a["missing_in_rollout"] == ["v"]
+
+
+def test_rlk_verify_acceptance_checks_on_training_rounds(tmp_path):
+    from rl_engine.entrypoints.repro import main as rlk
+
+    def write(recs, steps=None):
+        (tmp_path / "rounds.jsonl").write_text("\n".join(json.dumps(r) for r in recs) + "\n")
+        (tmp_path / "summary.json").write_text(json.dumps({"steps": len(recs) if steps is None else steps}))
+
+    rec = lambda i, **kw: {"step": i, "mismatch_count": 0, "tokens_compared": 100, "max_abs_dlogp": 0.0, "reward_mean": 0.5, "grad_norm": 1.0,  # noqa: E731
+                           "loss": 0.1, "weight_version": i + 1, **kw}
+    write([rec(0), rec(1), rec(2)])
+    assert rlk(["verify", str(tmp_path)]) == 0
+    for bad in ([rec(0), rec(1, mismatch_count=3)], [rec(0), rec(1, grad_norm=float("nan"))], [rec(0), rec(1, weight_version=5)], [rec(0), rec(2)]):
+        write(bad)
+        assert rlk(["verify", str(tmp_path)]) == 2
+    write([rec(0), rec(1)], steps=200)
+    assert rlk(["verify", str(tmp_path)]) == 2
