@@ -81,11 +81,14 @@ def build(force: bool = False, verbose: bool = False, jobs: int | None = None) -
             if log:
                 print(log)
     if rebuilt or not LIB_PATH.exists():
-        cmd = [nvcc_path(), "-shared", "-o", str(LIB_PATH), *[str(r[0]) for r in results],
+        tmp = LIB_PATH.with_suffix(f".so.tmp{os.getpid()}")       # link beside the target, then rename: readers never see half a file
+        cmd = [nvcc_path(), "-shared", "-o", str(tmp), *[str(r[0]) for r in results],
                "-gencode", "arch=compute_100a,code=sm_100a", "-lcudart"]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
+            tmp.unlink(missing_ok=True)
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
+        os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

@@ -92,6 +92,10 @@ struct GemmParams {
   int ar_use_epoch;
   __nv_bfloat16* ar_out;
   long long ar_ld_out;
+  // reduce-scatter form of the fused epilogue (rs_row1 > rs_row0): this rank finishes only the tiles of rows
+  // [rs_row0, rs_row1) -- a whole number of 128-row tiles -- and ar_out is biased so that row rs_row0 lands on the
+  // caller's row 0.  Every rank still publishes all its partial tiles; the peers pull the ones they own.
+  int rs_row0, rs_row1;
 #ifdef RLK_GEMM_TRACE
   // profiling build only: clock64 stamps of CTA 0's two single-thread roles, [5][kTraceLen]
   // (producer: after the empty wait, after the TMA issue; MMA thread: after the full wait, after
@@ -179,6 +183,9 @@ __device__ __forceinline__ void ar_pull_tile(const GemmParams& p, int m0, int n0
 template <int BN>
 __device__ __noinline__ bool ar_finish_tile(const GemmParams& p, int t, int m0, int n0, int et,
                                                unsigned long long seq, volatile int* abort_flag) {
+  // reduce-scatter: a tile outside this rank's rows is somebody else's to finish (same answer in all 256 threads,
+  // so the barrier below is skipped by all of them or by none)
+  if (p.rs_row1 > p.rs_row0 && (m0 >= p.rs_row1 || m0 + BM <= p.rs_row0)) return true;
   if (et < p.ar_world && et != p.ar_rank) {
     const unsigned long long* f = p.ar_flags[p.ar_rank] + et * kMaxSlices + t;
     const uint64_t t0 = globaltimer_ns();
@@ -1180,6 +1187,54 @@ RLK_API int rlk_det_gemm_ar(void* state, const void* A, const void* B, void* out
   p.ar_epoch = st->dev_epoch;
   p.ar_use_epoch = st->w.use_epoch;
   p.ar_out = static_cast<__nv_bfloat16*>(out);
+  p.ar_ld_out = ld_out;
+  return launch_gemm<128, false, false>(A, B, p, lda, ldb, static_cast<cudaStream_t>(stream));
+}
+
+// GEMM + fixed-order reduce-scatter over token rows in ONE kernel (sequence-parallel row-parallel projections):
+// out [M / world, N] = rows [rank * M / world, (rank + 1) * M / world) of the tree-all-reduce of the ranks' partial
+// products.  Same protocol, frames and tree as rlk_det_gemm_ar -- the bits of a row are those the all-reduce form
+// gives -- but a rank pulls and reduces only the tiles of its own rows, so each partial tile crosses NVLink once
+// instead of world - 1 times.  M must be a multiple of 128 * world (whole tiles per rank).
+RLK_API int rlk_det_gemm_rs(void* state, const void* A, const void* B, void* out, int M, int N, int K,
+                            long long lda, long long ldb, long long ld_out, int nchunks, void* stream) {
+  using namespace rlk;
+  SymmState* st = static_cast<SymmState*>(state);
+  RLK_REQUIRE(st != nullptr && st->w.world > 1, "det_gemm_rs: needs a symmetric-memory group of 2+ ranks");
+  RLK_REQUIRE(M > 0 && N > 0 && K > 0 && N % 8 == 0 && K % 8 == 0, "det_gemm_rs: bad shape");
+  RLK_REQUIRE(M % (128 * st->w.world) == 0, "det_gemm_rs: M (%d) must be a multiple of 128 x world (%d)", M, st->w.world);
+  RLK_REQUIRE(nchunks == 1 || nchunks == 2 || nchunks == 4 || nchunks == 8, "det_gemm_rs: nchunks must be 1, 2, 4 or 8");
+  RLK_REQUIRE(nchunks == 1 || K % (nchunks * 64) == 0, "det_gemm_rs: K/nchunks must be a multiple of 64");
+  RLK_REQUIRE(ld_out >= N, "det_gemm_rs: ld_out (%lld) must be at least N (%d)", ld_out, N);
+  RLK_REQUIRE(2ll * M * ld_out <= st->w.frame_bytes, "det_gemm_rs: %lld bytes exceed the frame capacity %lld",
+              2ll * M * ld_out, st->w.frame_bytes);
+  const long long tiles = static_cast<long long>((M + 127) / 128) * ((N + 127) / 128);
+  RLK_REQUIRE(tiles < kMaxSlices - 1, "det_gemm_rs: %lld tiles exceed the flag slots", tiles);
+  RLK_REQUIRE(A && B && out && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (ld_out * 2) % 16 == 0,
+              "det_gemm_rs: out must be 16-byte aligned");
+  st->seq += 1;
+  const int frame = static_cast<int>(st->seq & 1);
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.nchunks = nchunks;
+  p.kb_per_chunk = nchunks == 1 ? (K + 63) / 64 : K / nchunks / 64;
+  p.C = st->peers[st->w.rank] + kFlagBytes + frame * st->w.frame_bytes;
+  p.ldc = ld_out;
+  p.status = device_status_word();
+  p.ar_world = st->w.world;
+  p.ar_rank = st->w.rank;
+  for (int r = 0; r < st->w.world; ++r) {
+    p.ar_frame[r] = st->peers[r] + kFlagBytes + frame * st->w.frame_bytes;
+    p.ar_flags[r] = reinterpret_cast<unsigned long long*>(st->peers[r]);
+  }
+  p.ar_seq = st->seq;
+  p.ar_epoch = st->dev_epoch;
+  p.ar_use_epoch = st->w.use_epoch;
+  const int rows = M / st->w.world;
+  p.rs_row0 = st->w.rank * rows;
+  p.rs_row1 = p.rs_row0 + rows;
+  // only rows [rs_row0, rs_row1) are ever written: bias the base so that they land on the caller's rows 0..rows-1
+  p.ar_out = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uintptr_t>(out) - static_cast<uintptr_t>(2ll * p.rs_row0 * ld_out));
   p.ar_ld_out = ld_out;
   return launch_gemm<128, false, false>(A, B, p, lda, ldb, static_cast<cudaStream_t>(stream));
 }

@@ -137,6 +137,22 @@ class SymmetricMemoryCollective:
         nv._count()
         return out
 
+    def gemm_reduce_scatter(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, nchunks: int = 1) -> torch.Tensor:
+        """out [M / world, N] = this rank's token rows of the tree-all-reduce of (a_local @ b_local^T), as ONE kernel
+        (rlk_det_gemm_rs): the sequence-parallel form of ``gemm_all_reduce``.  Same bits per row; each partial tile
+        crosses NVLink once.  M must be a multiple of 128 x world."""
+        self._check_open()
+        M, K = a.shape
+        N = b.shape[0]
+        if out.shape[0] * self.world != M or out.shape[1] != N:
+            raise ValueError(f"out must be [{M // self.world}, {N}], got {tuple(out.shape)}")
+        ext.check(self._lib.rlk_det_gemm_rs(self._state, ext.ptr(a), ext.ptr(b), ext.ptr(out), c_int(M), c_int(N),
+                                            c_int(K), c_longlong(a.stride(0)), c_longlong(b.stride(0)),
+                                            c_longlong(out.stride(0)), c_int(nchunks), ext.stream_ptr(self.device)),
+                  "det_gemm_rs")
+        nv._count()
+        return out
+
     def all_reduce_int_(self, t: torch.Tensor) -> torch.Tensor:
         """Integer sums are associative: gather and add (exact in any order)."""
         if self.world == 1:

@@ -68,6 +68,45 @@ class _SPReduceScatter(torch.autograd.Function):
         return (c.all_gather(g.contiguous()).reshape(-1, *g.shape[1:]) if c is not None else g), None
 
 
+class _SPGemmReduceScatter(torch.autograd.Function):
+    """Row-parallel GEMM and its reduce-scatter as ONE kernel (``gemm_reduce_scatter`` of the symmetric-memory
+    collective): a rank pulls and reduces only the 128-row tiles of its own token rows from inside the GEMM epilogue.
+    Backward is that of ``_SPReduceScatter`` after ``det_gemm_linear``: all-gather dy, then the two gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, w, nchunks, collective):
+        ctx.save_for_backward(x, w)
+        ctx.nchunks, ctx.collective = nchunks, collective
+        out = torch.empty(x.shape[0] // collective.world, w.shape[0], device=x.device, dtype=x.dtype)
+        return collective.gemm_reduce_scatter(x.contiguous(), w.contiguous(), out, nchunks)
+
+    @staticmethod
+    def backward(ctx, g):
+        from rl_kernel_b200.ops.gemm.det_gemm import det_gemm_da, det_gemm_db
+
+        x, w = ctx.saved_tensors
+        dy = ctx.collective.all_gather(g.contiguous()).reshape(-1, g.shape[-1])
+        dx = det_gemm_da(dy, w, nchunks=1) if ctx.needs_input_grad[0] else None
+        dw = det_gemm_db(dy, x) if ctx.needs_input_grad[1] else None
+        return dx, dw, None, None
+
+
+def sp_row_parallel_linear(x: torch.Tensor, w: torch.Tensor, nchunks: int, collective, *, fused: bool | None = None) -> torch.Tensor:
+    """Sequence-parallel exit of a row-parallel projection: ``reduce_scatter(x @ w^T)`` over token rows.  ``fused``
+    (default: whenever the collective and the shape allow) runs GEMM and reduce-scatter as one kernel; both forms give
+    the same bits."""
+    can = (hasattr(collective, "gemm_reduce_scatter") and x.is_cuda and x.dtype == torch.bfloat16
+           and x.shape[0] % (128 * collective.world) == 0)
+    if fused is None:
+        fused = can
+    if fused:
+        if not can:
+            raise ValueError("the fused GEMM + reduce-scatter needs the symmetric-memory collective, bf16 CUDA operands and "
+                             "a token count that is a multiple of 128 x tp")
+        return _SPGemmReduceScatter.apply(x, w, nchunks, collective)
+    return _SPReduceScatter.apply(det_gemm_linear(x, w, nchunks), collective)
+
+
 class AttentionProjectionOp:
     """``sequence_parallel``: activations outside the projections are sharded by token rows over the TP group
     (all-gather before the QKV GEMM, reduce-scatter after the output GEMM; parity: the SP branches of
@@ -88,6 +127,6 @@ class AttentionProjectionOp:
         return det_gemm_linear(enter.apply(hidden, self.collective), w_qkv_local)
 
     def output(self, attn_local: torch.Tensor, w_o_local: torch.Tensor) -> torch.Tensor:
-        partial = det_gemm_linear(attn_local, w_o_local, self.nchunks)
-        leave = _SPReduceScatter if self.sequence_parallel else _TPAllReduce
-        return leave.apply(partial, self.collective)
+        if self.sequence_parallel:
+            return sp_row_parallel_linear(attn_local.reshape(-1, attn_local.shape[-1]), w_o_local, self.nchunks, self.collective)
+        return _TPAllReduce.apply(det_gemm_linear(attn_local, w_o_local, self.nchunks), self.collective)

@@ -7,7 +7,7 @@ from __future__ import annotations
 import torch
 
 from rl_kernel_b200.ops.activation import swiglu_packed
-from rl_kernel_b200.ops.attention.projection import _SPAllGather, _SPReduceScatter, _TPAllReduce, _TPCopy
+from rl_kernel_b200.ops.attention.projection import _SPAllGather, _TPAllReduce, _TPCopy, sp_row_parallel_linear
 from rl_kernel_b200.ops.gemm.det_gemm import det_gemm_linear
 
 
@@ -21,12 +21,14 @@ def qwen3_ffn(x: torch.Tensor, w_gu: torch.Tensor, w_down: torch.Tensor, *, cano
     coll = collective if tp_size > 1 else None
     if sequence_parallel and coll is None:
         raise ValueError("sequence parallelism needs a tensor-parallel group")
-    enter, leave = (_SPAllGather, _SPReduceScatter) if sequence_parallel else (_TPCopy, _TPAllReduce)
+    enter = _SPAllGather if sequence_parallel else _TPCopy
     lead = x.shape[:-1]
     gu = det_gemm_linear(enter.apply(x.reshape(-1, x.shape[-1]), coll), w_gu)
     act = swiglu_packed(gu, blk)
-    y = leave.apply(det_gemm_linear(act, w_down, nchunks), coll)
-    return y if sequence_parallel else y.reshape(*lead, y.shape[-1])
+    if sequence_parallel:       # GEMM + reduce-scatter in one kernel where the collective has it
+        return sp_row_parallel_linear(act, w_down, nchunks, coll)
+    y = _TPAllReduce.apply(det_gemm_linear(act, w_down, nchunks), coll)
+    return y.reshape(*lead, y.shape[-1])
 
 
 class Qwen3FFNOp:

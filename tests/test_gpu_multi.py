@@ -758,3 +758,65 @@ def test_registry_native_multi_gpu_operators_match_single_gpu_bitwise(tmp_path, 
     out = str(tmp_path / "ops.pt")
     mp.spawn(_fused_ops_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     assert torch.load(out)
+
+
+def _gemm_rs_worker(rank, world, port, out):
+    """Fused GEMM + reduce-scatter: rows of the fused all-reduce, of the unfused GEMM -> reduce-scatter, and the
+    sequence-parallel FFN through it, all bit-equal; gradients equal the unfused path's."""
+    dist = _init(rank, world, port)
+    from rl_kernel_b200.distributed.transports.symm import SymmetricMemoryCollective
+    from rl_kernel_b200.ops.attention.projection import sp_row_parallel_linear
+    from rl_kernel_b200.ops.ffn.qwen3 import qwen3_ffn
+
+    dev = torch.device("cuda", rank)
+    coll = SymmetricMemoryCollective(None, dev, frame_bytes=64 << 20)
+    ok = True
+    M, N, K, nchunks = 256 * world, 1024, 512 * (8 // world), 8 // world
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)          # every rank holds its own K shard
+    a = torch.randn(M, K, device=dev, generator=g).bfloat16()
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).bfloat16()
+    full = coll.gemm_all_reduce(a, w, torch.empty(M, N, device=dev, dtype=torch.bfloat16), nchunks)
+    rows = slice(rank * M // world, (rank + 1) * M // world)
+    for _ in range(3):                                                   # repeated calls walk both frames
+        rs = coll.gemm_reduce_scatter(a, w, torch.empty(M // world, N, device=dev, dtype=torch.bfloat16), nchunks)
+        ok &= torch.equal(rs, full[rows])
+    a1, w1 = a.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    a2, w2 = a.clone().requires_grad_(True), w.clone().requires_grad_(True)
+    y1 = sp_row_parallel_linear(a1, w1, nchunks, coll, fused=True)
+    y2 = sp_row_parallel_linear(a2, w2, nchunks, coll, fused=False)
+    go = torch.randn(M // world, N, device=dev, generator=g).bfloat16()
+    y1.backward(go)
+    y2.backward(go)
+    ok &= torch.equal(y1, y2) and torch.equal(y1, full[rows]) and torch.equal(a1.grad, a2.grad) and torch.equal(w1.grad, w2.grad)
+    # the sequence-parallel FFN (fused exit) against the replicated-activation FFN
+    H, I = 512, 2048
+    g2 = torch.Generator(device="cuda").manual_seed(7)                   # same tensors on every rank
+    x = torch.randn(M, H, device=dev, generator=g2).bfloat16()
+    wgu = (torch.randn(2 * I, H, device=dev, generator=g2) * 0.05).bfloat16()
+    wd = (torch.randn(H, I, device=dev, generator=g2) * 0.05).bfloat16()
+    per = I // world
+    blk = I // 8
+    # gate/up rows are interleaved per canonical shard of I / 8 columns: [gate blk, up blk] x 8
+    gu = wgu.view(8, 2, blk, H)[rank * (8 // world):(rank + 1) * (8 // world)].reshape(-1, H).contiguous()
+    dn = wd[:, rank * per:(rank + 1) * per].contiguous()
+    y_rep = qwen3_ffn(x, gu, dn, canonical_tp=8, tp_size=world, collective=coll)
+    y_sp = qwen3_ffn(x[rows].contiguous(), gu, dn, canonical_tp=8, tp_size=world, collective=coll, sequence_parallel=True)
+    ok &= torch.equal(y_sp, y_rep[rows])
+    torch.cuda.synchronize(dev)
+    from rl_kernel_b200.backends import extension as ext
+
+    ok &= ext.poll_status(dev) == 0
+    oks = [None] * world
+    dist.all_gather_object(oks, bool(ok))
+    if rank == 0:
+        torch.save(all(oks), out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_fused_gemm_reduce_scatter_equals_all_reduce_rows_bitwise(tmp_path, world):
+    _need(world)
+    out = str(tmp_path / "rs.pt")
+    mp.spawn(_gemm_rs_worker, args=(world, _free_port(), out), nprocs=world, join=True)
+    assert torch.load(out)
