@@ -179,27 +179,35 @@ class PackedParams:
                 self.w[name][self.v_real_local:].zero_()
         return self
 
-    def export_local(self) -> dict[str, torch.Tensor]:
-        """This rank's shard back in HF key names (TP=1: the full HF state)."""
+    def export_local(self, table: dict[str, torch.Tensor] | None = None) -> dict[str, torch.Tensor]:
+        """This rank's shard back in HF key names (TP=1: the full HF state).  ``table``: the packed tensors to read
+        (default the weights ``self.w``; ``self.g`` gives the gradients under the same names)."""
         spec = self.spec
+        W = self.w if table is None else table
         if self.tp_size != 1:
             raise NotImplementedError("export_local assembles full tensors only for tp_size == 1")
-        out = {"embed_tokens.weight": self.w["embed"][:spec.vocab_size],
-               "lm_head.weight": self.w["lm_head"][:spec.vocab_size], "norm.weight": self.w["norm"]}
+        out = {"embed_tokens.weight": W["embed"][:spec.vocab_size],
+               "lm_head.weight": W["lm_head"][:spec.vocab_size], "norm.weight": W["norm"]}
         for l in range(spec.num_hidden_layers):
             p = f"layers.{l}"
-            q, k, v = unpack_qkv(spec, self.w[f"l{l}.wqkv"])
-            gte, up = unpack_gate_up(spec, self.w[f"l{l}.wgu"])
-            out.update({f"{p}.input_layernorm.weight": self.w[f"l{l}.ln1"],
-                        f"{p}.post_attention_layernorm.weight": self.w[f"l{l}.ln2"],
-                        f"{p}.self_attn.q_norm.weight": self.w[f"l{l}.qn"],
-                        f"{p}.self_attn.k_norm.weight": self.w[f"l{l}.kn"],
+            q, k, v = unpack_qkv(spec, W[f"l{l}.wqkv"])
+            gte, up = unpack_gate_up(spec, W[f"l{l}.wgu"])
+            out.update({f"{p}.input_layernorm.weight": W[f"l{l}.ln1"],
+                        f"{p}.post_attention_layernorm.weight": W[f"l{l}.ln2"],
+                        f"{p}.self_attn.q_norm.weight": W[f"l{l}.qn"],
+                        f"{p}.self_attn.k_norm.weight": W[f"l{l}.kn"],
                         f"{p}.self_attn.q_proj.weight": q, f"{p}.self_attn.k_proj.weight": k,
                         f"{p}.self_attn.v_proj.weight": v,
-                        f"{p}.self_attn.o_proj.weight": self.w[f"l{l}.wo"],
+                        f"{p}.self_attn.o_proj.weight": W[f"l{l}.wo"],
                         f"{p}.mlp.gate_proj.weight": gte, f"{p}.mlp.up_proj.weight": up,
-                        f"{p}.mlp.down_proj.weight": self.w[f"l{l}.wd"]})
+                        f"{p}.mlp.down_proj.weight": W[f"l{l}.wd"]})
         return out
+
+    def export_local_grads(self) -> dict[str, torch.Tensor]:
+        """Gradients in HF key names (needs ``with_grad=True``; TP=1)."""
+        if self.grad is None:
+            raise RuntimeError("these parameters were built without a gradient buffer")
+        return self.export_local(self.g)
 
 
 # ------------------------------------------------------------------------------ attention tiles

@@ -71,3 +71,138 @@ def run_chain_gate(model, gold_model, input_ids: torch.Tensor, *, decode_from: i
         res.first_drift = locate_first_drift(nodes, gold_model.captured_node_outputs(), model.node_names())
     res.passed = ok_acc and all(res.cells.values())
     return res
+
+
+# ================================================================================================ the gate on the device engine
+@dataclass
+class EngineChainGateResult(ChainGateResult):
+    gradient_cells: dict[str, float] = field(default_factory=dict)      # cell -> worst relative gradient difference
+    gradient_accuracy: dict[str, float] = field(default_factory=dict)   # parameter kind -> worst relative error vs fp32 autograd
+    missing_grads: tuple[str, ...] = ()
+    device: str = ""
+
+
+def gold_chain_forward(spec, ids: torch.Tensor, W: dict[str, torch.Tensor]):
+    """The decoder chain in plain fp32 PyTorch (differentiable in ``W``): -> (final-norm hidden [B, S, H], logits)."""
+    import math
+
+    B, S = ids.shape
+    D, eps = spec.head_dim, spec.rms_norm_eps
+
+    def rms(t, w):
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * w
+
+    inv = 1.0 / (spec.rope_theta ** (torch.arange(0, D, 2, dtype=torch.float64, device=ids.device) / D))
+    ang = torch.arange(S, dtype=torch.float64, device=ids.device)[:, None] * inv
+    cos, sin = ang.cos().float()[None, :, None], ang.sin().float()[None, :, None]
+
+    def rope(t):
+        a, b = t[..., : D // 2], t[..., D // 2:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], -1)
+
+    g = spec.num_attention_heads // spec.num_key_value_heads
+    mask = torch.triu(torch.ones(S, S, dtype=torch.bool, device=ids.device), 1)
+    x = W["embed_tokens.weight"][ids]
+    for l in range(spec.num_hidden_layers):
+        p = f"layers.{l}"
+        h = rms(x, W[f"{p}.input_layernorm.weight"])
+        q = (h @ W[f"{p}.self_attn.q_proj.weight"].t()).view(B, S, -1, D)
+        k = (h @ W[f"{p}.self_attn.k_proj.weight"].t()).view(B, S, -1, D)
+        v = (h @ W[f"{p}.self_attn.v_proj.weight"].t()).view(B, S, -1, D)
+        q, k = rope(rms(q, W[f"{p}.self_attn.q_norm.weight"])), rope(rms(k, W[f"{p}.self_attn.k_norm.weight"]))
+        kk, vv = k.repeat_interleave(g, 2), v.repeat_interleave(g, 2)
+        sc = torch.einsum("bqhd,bkhd->bhqk", q, kk) / math.sqrt(D)
+        a = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(sc.masked_fill(mask, float("-inf")), -1), vv).reshape(B, S, -1)
+        x = x + a @ W[f"{p}.self_attn.o_proj.weight"].t()
+        h2 = rms(x, W[f"{p}.post_attention_layernorm.weight"])
+        x = x + (torch.nn.functional.silu(h2 @ W[f"{p}.mlp.gate_proj.weight"].t()) * (h2 @ W[f"{p}.mlp.up_proj.weight"].t())) @ \
+            W[f"{p}.mlp.down_proj.weight"].t()
+    hf = rms(x, W["norm.weight"])
+    return hf, hf @ W["lm_head.weight"].t()
+
+
+def run_engine_chain_gate(spec, weights, input_ids: torch.Tensor, *, device: str = "cuda", prompt_len: int | None = None,
+                          decode_from: int | None = None, grad_rel_limit: float = 3e-2, cell_rel_limit: float = 2e-2) -> EngineChainGateResult:
+    """The chain gate on ``Qwen3Engine`` (sm_100a kernels).
+
+    Forward cells -- whole batch, singletons, permuted, a batch padded with one more sequence, micro-batches of two,
+    prefill + cached decode -- must give every scored token the same bits.  Accuracy: selected log-probs against the fp32
+    chain under the chain thresholds.  Gradient cells: one real backward per cell with a fixed d(loss)/d(logp) per
+    token; every required trainable parameter must have a gradient, the micro-batched and the permuted run must agree
+    with the whole batch inside ``cell_rel_limit`` (their token order in the weight-gradient sums differs), and the
+    whole batch must agree with fp32 autograd through the gold chain inside ``grad_rel_limit``."""
+    from rl_kernel_b200.models.qwen3.engine import PackedParams, Qwen3Engine
+    from rl_kernel_b200.validation.models.chain_gradients import group_by_kind, missing_required_grads
+
+    dev = torch.device(device)
+    ids = input_ids.to(dev)
+    B, S = ids.shape
+    P = prompt_len if prompt_len is not None else S // 2
+    res = EngineChainGateResult(device=torch.cuda.get_device_name(dev))
+    params = PackedParams(spec, 0, 1, dev, with_grad=True).load(weights)
+    eng = Qwen3Engine(spec, params, max_positions=max(512, 2 * S))
+    H = spec.hidden_size
+    g = torch.Generator().manual_seed(1)
+    dl_full = (torch.randn(B, S - P, generator=g) * 1e-2).to(dev)             # d(loss)/d(logp) per response token
+
+    def score(tokens):
+        hf = eng.forward_hidden(tokens.contiguous()).view(tokens.shape[0], S, H)
+        rows = hf[:, P - 1: S - 1].reshape(-1, H).contiguous()
+        return eng.logp_from_hidden(rows, tokens[:, P:].reshape(-1)).view(tokens.shape[0], S - P).clone()
+
+    with torch.no_grad():
+        lp = score(ids)
+        res.cells["packed/full"] = True
+        res.cells["singletons"] = bit_equal(torch.cat([score(ids[i:i + 1]) for i in range(B)]), lp)
+        perm = torch.arange(B - 1, -1, -1, device=dev)
+        res.cells["permuted"] = bit_equal(score(ids[perm]), lp[perm])
+        res.cells["padded_batch"] = bit_equal(score(torch.cat([ids, ids[:1]]))[:B], lp)
+        res.cells["micro_batches"] = bit_equal(torch.cat([score(ids[i:i + 2]) for i in range(0, B, 2)]), lp)
+        if decode_from is not None and P <= decode_from < S - 1:
+            kv = eng.new_kv_cache(B, S + 1)
+            pre = eng.forward_hidden(ids[:, :decode_from].contiguous(), kv=kv).view(B, decode_from, H)
+            h = pre[:, -1].contiguous().clone()
+            tiles = eng.decode_tiles(B, S + 1)
+            cols = []
+            for t in range(decode_from - 1, S - 1):
+                if t >= decode_from:
+                    h = eng.decode_step(ids[:, t].contiguous(), torch.full((B,), t, dtype=torch.int32, device=dev), kv, tiles)
+                cols.append(eng.logp_from_hidden(h.contiguous(), ids[:, t + 1].contiguous()).clone())
+            res.cells["chunked/decode"] = bit_equal(torch.stack(cols, 1), lp[:, decode_from - 1 - (P - 1):])
+    # ---- accuracy against the fp32 chain
+    Wg = {k: v.float().to(dev).requires_grad_(True) for k, v in weights.items()}
+    _, logits = gold_chain_forward(spec, ids, Wg)
+    gold_lp = torch.log_softmax(logits[:, P - 1: S - 1], -1).gather(-1, ids[:, P:, None])[..., 0]
+    res.aggregates = parity_aggregates(lp, gold_lp.detach())
+    (gold_lp * dl_full).sum().backward()
+    gold_grads = {k: v.grad for k, v in Wg.items()}
+
+    # ---- gradient cells
+    def backward_cell(batches):
+        params.grad.zero_()
+        for rows in batches:
+            eng.train_forward_backward(ids[rows].contiguous(), P, lambda lp_, rows=rows: dl_full[rows].contiguous())
+        torch.cuda.synchronize(dev)
+        return {k: v.float().clone() for k, v in params.export_local_grads().items()}
+
+    all_rows = torch.arange(B, device=dev)
+    full = backward_cell([all_rows])
+    res.missing_grads = missing_required_grads(full, num_hidden_layers=spec.num_hidden_layers)
+
+    def rel(a, b):
+        return float((a - b).abs().max() / b.abs().max().clamp_min(1e-30))
+
+    cells = {"micro_batches": backward_cell([all_rows[i:i + 2] for i in range(0, B, 2)]),
+             "permuted": backward_cell([all_rows.flip(0)]), "repeat": backward_cell([all_rows])}
+    for name, grads in cells.items():
+        res.gradient_cells[name] = max(rel(grads[k], full[k]) for k in full)
+    for kind, names in group_by_kind(list(full)).items():
+        res.gradient_accuracy[kind] = max(rel(full[n], gold_grads[n]) for n in names)
+    th = chain_thresholds()
+    ok_acc = (res.aggregates["max_abs_dlogp"] <= th["max_abs_dlogp"] and res.aggregates["approx_kl0"] <= th["approx_kl0"]
+              and res.aggregates["clipfrac0"] <= th["clipfrac0"])
+    ok_grad = (not res.missing_grads and res.gradient_cells["repeat"] == 0.0
+               and all(v <= cell_rel_limit for v in res.gradient_cells.values())
+               and all(v <= grad_rel_limit for v in res.gradient_accuracy.values()))
+    res.passed = ok_acc and ok_grad and all(res.cells.values())
+    return res

@@ -77,3 +77,15 @@ def test_paired_alignment_run_on_the_engine_rollout_path_equals_training_path_bi
     ran = [c for c in s["cases"].values() if "passed" in c]
     assert len(ran) == 2 and s["all_passed"], s
     assert len(s["not_executable"]) == 1           # tensor parallel size 2 is refused by the one-GPU adapter, not ignored
+
+
+def test_chain_gate_on_the_engine_forward_cells_bitwise_and_gradients_against_fp32_autograd():
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.validation.models.chain_gate import run_engine_chain_gate
+
+    spec = Qwen3DenseSpec.scaled(layers=2, hidden=512, ffn=1536, q_heads=4, kv_heads=2, head_dim=128, vocab=4096)
+    w = Qwen3DenseWeights.synthetic(spec, seed=3)
+    ids = torch.randint(0, spec.vocab_size, (4, 256), generator=torch.Generator().manual_seed(0))
+    res = run_engine_chain_gate(spec, w, ids, prompt_len=128, decode_from=200)
+    assert res.passed, (res.cells, res.aggregates, res.gradient_cells, res.gradient_accuracy, res.missing_grads)
+    assert set(res.cells) == {"packed/full", "singletons", "permuted", "padded_batch", "micro_batches", "chunked/decode"}
