@@ -173,3 +173,63 @@ def test_profiler_reports_blocked_without_a_gpu_and_serialises(tmp_path):
     out = json.loads(prof.to_json(str(tmp_path / "p.json")))
     assert out[0]["name"] == "rmsnorm_fwd_12288x4096" and out[0]["ms"] is None
     prof.to_csv(str(tmp_path / "p.csv"))
+
+
+def test_semantic_resolution_overrides_and_module_executor():
+    import torch
+
+    from rl_engine.runtime.executor import (ModuleForwardExecutor, StatelessForwardConfig, StatelessForwardInputs, collect_stateless_metrics,
+                                            score_rewards, summarize_tensor_tree)
+    from rl_engine.runtime.operators import OperatorBridge, OperatorOverride
+    from rl_engine.runtime.semantic_registry import (OperatorRequirements, OperatorResolutionError, OperatorResolutionPolicy,
+                                                     implementation_fingerprint, semantic_catalog)
+    from rl_engine.validation.fixtures.cpu_cross_config import SyntheticCpuCausalLM
+
+    cpu = OperatorRequirements("selected_logprob", device_type="cpu", dtype="float32")
+    r = semantic_catalog.resolve(cpu)
+    assert r.actual_backend == "reference" and not r.fallback
+    with pytest.raises(OperatorResolutionError) as e:
+        semantic_catalog.resolve(cpu, backend="b200-tcgen05")
+    assert len(e.value.trace.decisions) == 2 and "cpu" in str(e.value)
+    r2 = semantic_catalog.resolve(cpu, backend="b200-tcgen05", policy=OperatorResolutionPolicy.permissive())
+    assert r2.fallback and r2.actual_backend == "reference"
+    op = semantic_catalog.instantiate(r2)
+    prov = semantic_catalog.instance_provenance(r2, op)
+    assert prov.backend_id == "reference" and len(prov.implementation_fingerprint) == 64 and prov.native_library_sha256 is None
+    assert implementation_fingerprint(type(op)) == implementation_fingerprint(type(op)) != implementation_fingerprint(OperatorBridge)
+    with pytest.raises(OperatorResolutionError):
+        semantic_catalog.resolve(OperatorRequirements("no_such_op"))
+    bridge = OperatorBridge()
+    ov = OperatorOverride.for_target("selected_logprob", "training", "reference")
+    res = bridge.resolve_override(ov, requirements={"rollout": cpu, "training": cpu})
+    assert res.for_target("training").requested_backend == "reference" and res.for_target("rollout").requested_backend is None
+    assert OperatorOverride("attention", rollout_backend="auto").rollout_backend is None
+    # nn.Module scoring with an attention-backend fallback chain
+    lm = SyntheticCpuCausalLM(vocab_size=512, hidden=32)
+
+    class Picky(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.inner, self.config = lm, type("Cfg", (), {"use_cache": True, "_attn_implementation": "eager"})()
+
+        def forward(self, ids, **kw):
+            if self.config._attn_implementation == "flash_attention_2":
+                raise ImportError("flash_attn is not installed")
+            assert self.config.use_cache is False
+            return {"logits": self.inner(ids)}
+
+    model = Picky()
+    ids = torch.randint(0, 512, (5, 12), generator=torch.Generator().manual_seed(0))
+    cm = torch.zeros(5, 12, dtype=torch.bool)
+    cm[:, 6:] = True
+    ex = ModuleForwardExecutor(model, StatelessForwardConfig(micro_batch=2, attention_backend="flash_attention_2"))
+    out = ex.score(StatelessForwardInputs(ids, completion_mask=cm))
+    assert out.attention_backend == "sdpa" and "flash_attn" in out.fallback_reason and model.config.use_cache is True
+    ref = torch.log_softmax(lm(ids)[:, :-1], -1).gather(-1, ids[:, 1:, None])[..., 0]
+    assert torch.allclose(out.outputs.selected_logprobs[:, 5:], ref[:, 5:], atol=1e-5) and float(out.outputs.selected_logprobs[:, :5].abs().max()) == 0.0
+    assert out.metrics["micro_batches"] == 3 and collect_stateless_metrics(out, out)["calls"] == 2
+    assert summarize_tensor_tree({"a": torch.zeros(4), "b": [torch.zeros(2, 2)]}).tensors == 2
+    rewards = score_rewards(lambda x, **kw: {"scores": x.float().sum(-1, keepdim=True)}, ids, micro_batch=2)
+    assert rewards.shape == (5,)
+    with pytest.raises(ValueError):
+        StatelessForwardConfig(use_cache=True)
