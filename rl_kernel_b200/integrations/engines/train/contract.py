@@ -69,3 +69,267 @@ class StatelessScoringWorker:
     def score(self, rollout: RolloutStageResult) -> torch.Tensor:
         lp = self.executor.score(rollout.tokens)
         return lp[:, -rollout.rollout_logp.shape[1]:]
+
+
+# ================================================================================================ rollout payloads
+# (parity: the payload side of rl_engine/integrations/engines/train/contract.py:58-1026: serving engines hand back grouped
+#  candidates in several shapes; workers read them through these functions and attach scores in place)
+import math
+from typing import Any, Optional, Sequence
+
+
+@dataclass(frozen=True)
+class TorchRLTrainingConfig:
+    learning_rate: float = 1e-6
+    clip_eps: float = 0.2
+    kl_coef: float = 0.0
+    max_grad_norm: float = 1.0
+    micro_batch_size: int = 8
+    temperature: float = 1.0
+    advantage_eps: float = 1e-6
+    pad_token_id: int = 0
+    use_rollout_logprobs: bool = False          # take the sampler's log-probs as old log-probs instead of recomputing them
+    seed: int = 1234
+
+    def __post_init__(self) -> None:
+        if self.learning_rate <= 0 or self.micro_batch_size <= 0 or self.temperature <= 0:
+            raise ValueError("learning_rate, micro_batch_size and temperature must be positive")
+        if not 0 <= self.clip_eps < 1 or self.kl_coef < 0:
+            raise ValueError("clip_eps must lie in [0, 1) and kl_coef must not be negative")
+
+
+def _get(obj: Any, *names: str, default=None):
+    for n in names:
+        if isinstance(obj, dict):
+            if n in obj:
+                return obj[n]
+        elif hasattr(obj, n):
+            return getattr(obj, n)
+    return default
+
+
+def _ints(v: Any) -> list[int]:
+    if isinstance(v, torch.Tensor):
+        v = v.tolist()
+    out = [int(x) for x in v]
+    if any(isinstance(x, bool) for x in v):
+        raise TypeError("token ids must be integers")
+    return out
+
+
+def _floats(v: Any) -> list[float]:
+    if isinstance(v, torch.Tensor):
+        v = v.tolist()
+    return [float(x) for x in v]
+
+
+def _groups(payload: Any) -> list[Any]:
+    """The prompt groups of a payload: a list of groups, or an object / dict with ``grouped_outputs`` / ``groups`` / ``outputs``."""
+    inner = _get(payload, "grouped_outputs", "groups", default=None)
+    if inner is None:
+        inner = payload
+    if not isinstance(inner, (list, tuple)):
+        raise TypeError("a rollout payload is a sequence of prompt groups (or carries one as grouped_outputs / groups)")
+    return list(inner)
+
+
+def _candidates(group: Any) -> tuple[list[int], list[Any]]:
+    """(prompt ids, candidates) of one group.  A group is a serving engine's request output (``prompt_token_ids`` plus
+    ``outputs``), a dict of that shape, or a plain list of candidates."""
+    outs = _get(group, "outputs", "candidates", "samples", default=None)
+    prompt = _get(group, "prompt_token_ids", "prompt_ids", default=None)
+    if outs is None:
+        if not isinstance(group, (list, tuple)):
+            raise TypeError("a prompt group needs outputs / candidates")
+        outs = group
+    return ([] if prompt is None else _ints(prompt)), list(outs)
+
+
+def candidate_token_ids(candidate: Any) -> list[int]:
+    ids = _get(candidate, "token_ids", "completion_token_ids", "response_token_ids", "tokens", default=None)
+    if ids is None:
+        if isinstance(candidate, (list, tuple, torch.Tensor)):
+            return _ints(candidate)
+        raise TypeError("a candidate needs token_ids")
+    return _ints(ids)
+
+
+def candidate_prompt_token_ids(candidate: Any, group_prompt: Sequence[int] = ()) -> list[int]:
+    own = _get(candidate, "prompt_token_ids", "prompt_ids", default=None)
+    return _ints(own) if own is not None else list(group_prompt)
+
+
+def candidate_reward(candidate: Any) -> Optional[float]:
+    r = _get(candidate, "reward", "score", default=None)
+    if r is None:
+        md = _get(candidate, "metadata", "extra", default=None)
+        r = _get(md, "reward", default=None) if md is not None else None
+    if r is None:
+        return None
+    r = float(r)
+    if not math.isfinite(r):
+        raise ValueError("a candidate's reward must be finite")
+    return r
+
+
+def candidate_reference_logps(candidate: Any) -> Optional[list[float]]:
+    v = _get(candidate, "reference_logprobs", "ref_logprobs", "reference_logps", default=None)
+    return None if v is None else _floats(v)
+
+
+def candidate_rollout_logps(candidate: Any) -> Optional[list[float]]:
+    v = _get(candidate, "rollout_logprobs", "token_logprobs", "logprobs", default=None)
+    if v is None:
+        return None
+    if v and isinstance(v[0], dict):                      # a serving engine's per-token {id: Logprob} maps
+        ids = candidate_token_ids(candidate)
+        return [float(_get(d[t], "logprob", default=d[t])) for d, t in zip(v, ids)]
+    return _floats(v)
+
+
+def extract_rollout_candidate_groups(payload: Any) -> list[list[list[int]]]:
+    return [[candidate_token_ids(c) for c in _candidates(g)[1]] for g in _groups(payload)]
+
+
+def extract_rollout_token_groups(payload: Any) -> list[list[int]]:
+    """Prompt ids of every group."""
+    return [_candidates(g)[0] for g in _groups(payload)]
+
+
+def extract_rollout_reward_groups(payload: Any) -> list[list[float]]:
+    out = []
+    for g in _groups(payload):
+        rs = [candidate_reward(c) for c in _candidates(g)[1]]
+        if any(r is None for r in rs):
+            raise ValueError("every candidate needs a reward before the batch is built")
+        out.append(rs)
+    return out
+
+
+def extract_rollout_reference_logp_groups(payload: Any) -> list[list[list[float]]]:
+    out = []
+    for g in _groups(payload):
+        ls = [candidate_reference_logps(c) for c in _candidates(g)[1]]
+        if any(x is None for x in ls):
+            raise ValueError("every candidate needs reference log-probs")
+        out.append(ls)
+    return out
+
+
+def _set(candidate: Any, name: str, value: Any) -> None:
+    if isinstance(candidate, dict):
+        candidate[name] = value
+    else:
+        try:
+            setattr(candidate, name, value)
+        except AttributeError as exc:
+            raise TypeError(f"cannot attach {name} to a {type(candidate).__name__}; use objects or dicts as candidates") from exc
+
+
+def attach_stateless_scores_to_payload(payload: Any, *, rewards: Optional[torch.Tensor] = None,
+                                       reference_logps: Optional[torch.Tensor] = None, completion_mask: Optional[torch.Tensor] = None) -> Any:
+    """Write a scoring worker's results back onto the candidates, in payload order: ``rewards`` [B]; ``reference_logps``
+    [B, L] with ``completion_mask`` [B, L] marking each candidate's own tokens (right-padded)."""
+    flat = [c for g in _groups(payload) for c in _candidates(g)[1]]
+    if rewards is not None:
+        if rewards.shape[0] != len(flat):
+            raise ValueError(f"{rewards.shape[0]} rewards for {len(flat)} candidates")
+        for c, r in zip(flat, rewards.tolist()):
+            _set(c, "reward", float(r))
+    if reference_logps is not None:
+        if reference_logps.shape[0] != len(flat):
+            raise ValueError(f"{reference_logps.shape[0]} log-prob rows for {len(flat)} candidates")
+        for i, c in enumerate(flat):
+            n = len(candidate_token_ids(c))
+            row = reference_logps[i][completion_mask[i].bool()] if completion_mask is not None else reference_logps[i, :n]
+            if row.numel() != n:
+                raise ValueError(f"candidate {i}: {row.numel()} log-probs for {n} tokens")
+            _set(c, "reference_logprobs", row.tolist())
+    return payload
+
+
+def build_stateless_inputs_from_rollout_payload(payload: Any, *, pad_token_id: int = 0):
+    """Right-padded [B, S] ids with attention and completion masks: what a stateless scoring worker needs."""
+    from rl_kernel_b200.runtime.executor import StatelessForwardInputs
+
+    rows, comp = [], []
+    for g in _groups(payload):
+        prompt, cands = _candidates(g)
+        for c in cands:
+            p = candidate_prompt_token_ids(c, prompt)
+            t = candidate_token_ids(c)
+            if not p or not t:
+                raise ValueError("every candidate needs a non-empty prompt and completion")
+            rows.append(p + t)
+            comp.append((len(p), len(t)))
+    S = max(len(r) for r in rows)
+    ids = torch.full((len(rows), S), pad_token_id, dtype=torch.long)
+    attn = torch.zeros(len(rows), S, dtype=torch.bool)
+    cm = torch.zeros(len(rows), S, dtype=torch.bool)
+    for i, (r, (np_, nt)) in enumerate(zip(rows, comp)):
+        ids[i, : len(r)] = torch.tensor(r)
+        attn[i, : len(r)] = True
+        cm[i, np_: np_ + nt] = True
+    return StatelessForwardInputs(ids, attn, cm)
+
+
+def compute_group_relative_advantages(reward_groups: Sequence[Sequence[float]], eps: float = 1e-6) -> list[list[float]]:
+    """(r - mean) / std per prompt group, two-pass variance; a group whose rewards are all equal gets zeros."""
+    out = []
+    for g in reward_groups:
+        r = torch.tensor(list(g), dtype=torch.float32)
+        d = r - r.mean()
+        var = (d * d).mean()
+        out.append((d / var.clamp_min(eps ** 2).sqrt()).tolist())
+    return out
+
+
+def broadcast_sequence_advantages(advantages: torch.Tensor, completion_mask: torch.Tensor) -> torch.Tensor:
+    """[B] -> [B, L]: the sequence's advantage on its own tokens, zero elsewhere."""
+    return advantages.float().view(-1, 1) * completion_mask.float()
+
+
+def objective_reference_logps(reference_logps: Optional[torch.Tensor], policy_logps: torch.Tensor, kl_coef: float) -> Optional[torch.Tensor]:
+    """What the loss takes as reference: nothing without a KL term, the scored reference otherwise (it must exist)."""
+    if kl_coef == 0:
+        return None
+    if reference_logps is None:
+        raise ValueError("a KL term needs reference log-probs")
+    if reference_logps.shape != policy_logps.shape:
+        raise ValueError("reference and policy log-probs must have one shape")
+    return reference_logps
+
+
+def make_rollout_result(payload: Any, *, samples_per_prompt: Optional[int] = None, pad_token_id: int = 0, weight_version: int = 0
+                        ) -> RolloutStageResult:
+    """A ``RolloutStageResult`` from a grouped payload whose candidates carry token ids, rollout log-probs and rewards.
+    Prompts must have one length and completions are right-padded to the longest."""
+    prompts = extract_rollout_token_groups(payload)
+    cands = extract_rollout_candidate_groups(payload)
+    rewards = extract_rollout_reward_groups(payload)
+    g = samples_per_prompt or len(cands[0])
+    if any(len(c) != g for c in cands):
+        raise ValueError("every prompt group must hold samples_per_prompt candidates")
+    P = len(prompts[0])
+    if P == 0 or any(len(p) != P for p in prompts):
+        raise ValueError("prompts must be non-empty and of one length")
+    flat = [c for grp in _groups(payload) for c in _candidates(grp)[1]]
+    R = max(len(t) for grp in cands for t in grp)
+    B = len(flat)
+    tokens = torch.full((B, P + R), pad_token_id, dtype=torch.long)
+    mask = torch.zeros(B, R, dtype=torch.bool)
+    lp = torch.zeros(B, R, dtype=torch.float32)
+    i = 0
+    for prompt, grp in zip(prompts, cands):
+        for t in grp:
+            tokens[i, :P] = torch.tensor(prompt)
+            tokens[i, P: P + len(t)] = torch.tensor(t)
+            mask[i, : len(t)] = True
+            rl = candidate_rollout_logps(flat[i])
+            if rl is None or len(rl) != len(t):
+                raise ValueError(f"candidate {i} needs one rollout log-prob per token")
+            lp[i, : len(t)] = torch.tensor(rl)
+            i += 1
+    res = RolloutStageResult(tokens, mask, lp, torch.tensor([r for grp in rewards for r in grp], dtype=torch.float32), P, g, weight_version)
+    res.validate()
+    return res

@@ -41,7 +41,7 @@ class DeepSpeedTrainingWorker(RolloutBatchMixin):
         self.engine.backward(loss)
         self.engine.step()
         gn = getattr(self.engine, "get_global_grad_norm", lambda: 0.0)() or 0.0
-        return TrainingStageResult(float(loss), float(pol), float(kl), float(gn), logp.detach(),
+        return TrainingStageResult(float(loss.detach()), float(pol.detach()), float(kl.detach()), float(gn), logp.detach(),
                                    self.mismatches(logp.detach(), rollout), int(rollout.response_mask.sum()),
                                    self.weight_version)
 

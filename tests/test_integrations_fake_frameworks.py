@@ -197,3 +197,40 @@ def test_vime_providers_over_structural_requests():
         raise AssertionError("accepted a sliding window")
     except att.AttentionProviderUnavailable:
         pass
+
+
+def test_rollout_payload_contract_round_trip():
+    from types import SimpleNamespace as NS
+
+    import pytest
+    import torch
+
+    from rl_engine.integrations.engines.train import contract as C
+
+    def completion(ids, lps):
+        return NS(token_ids=ids, logprobs=[{t: NS(logprob=l)} for t, l in zip(ids, lps)])
+
+    payload = [NS(prompt_token_ids=[5, 6, 7], outputs=[completion([1, 2], [-0.1, -0.2]), completion([3], [-0.3])]),
+               {"prompt_token_ids": [8, 9, 10], "outputs": [{"token_ids": [4, 4, 4], "rollout_logprobs": [-1.0, -1.1, -1.2]},
+                                                            {"token_ids": [2, 1], "rollout_logprobs": [-0.5, -0.6]}]}]
+    assert C.extract_rollout_candidate_groups(payload) == [[[1, 2], [3]], [[4, 4, 4], [2, 1]]]
+    assert C.extract_rollout_token_groups(payload) == [[5, 6, 7], [8, 9, 10]]
+    with pytest.raises(ValueError):
+        C.extract_rollout_reward_groups(payload)
+    inp = C.build_stateless_inputs_from_rollout_payload(payload, pad_token_id=0)
+    assert inp.input_ids.shape == (4, 6) and inp.completion_mask.sum().item() == 8 and inp.attention_mask[1].tolist() == [True] * 4 + [False] * 2
+    ref = torch.arange(24, dtype=torch.float32).view(4, 6)
+    C.attach_stateless_scores_to_payload(payload, rewards=torch.tensor([1.0, 0.0, 0.5, 0.5]), reference_logps=ref, completion_mask=inp.completion_mask)
+    assert C.extract_rollout_reward_groups(payload) == [[1.0, 0.0], [0.5, 0.5]]
+    assert C.extract_rollout_reference_logp_groups(payload)[1][0] == [15.0, 16.0, 17.0]
+    adv = C.compute_group_relative_advantages(C.extract_rollout_reward_groups(payload))
+    assert abs(adv[0][0] - 1.0) < 1e-5 and adv[1] == [0.0, 0.0]
+    res = C.make_rollout_result(payload, pad_token_id=0, weight_version=3)
+    assert res.tokens.shape == (4, 6) and res.response_mask.sum().item() == 8 and abs(float(res.rollout_logp[2, 2]) + 1.2) < 1e-6
+    assert res.samples_per_prompt == 2 and res.prompt_len == 3
+    assert C.broadcast_sequence_advantages(torch.tensor([2.0, -1.0]), torch.tensor([[1, 1, 0], [1, 0, 0]])).tolist() == [[2.0, 2.0, 0.0], [-1.0, 0.0, 0.0]]
+    assert C.objective_reference_logps(None, torch.zeros(2), 0.0) is None
+    with pytest.raises(ValueError):
+        C.objective_reference_logps(None, torch.zeros(2), 0.1)
+    with pytest.raises(ValueError):
+        C.TorchRLTrainingConfig(clip_eps=1.5)
