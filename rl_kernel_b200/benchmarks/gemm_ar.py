@@ -10,6 +10,8 @@ chunks).  CUDA events, max over ranks, L2 flushed between iterations.  Roofline 
 max(2 M N K_loc / measured bf16 peak, (W-1)/W * M * N * 2 bytes * 2 / 770 GB/s) -- an all-reduce moves
 every element once in (reduce-scatter) and once out (all-gather) over each GPU's links.  The fused
 kernel and (a) give the same bits (checked); NCCL's sum has no fixed order and is only timed.
+The ``rs_*`` keys time the sequence-parallel exit (each rank keeps its M / W token rows): the fused GEMM + reduce-scatter
+kernel against det_gemm + this library's reduce-scatter and det_gemm + NCCL ``reduce_scatter_tensor``.
 """
 from __future__ import annotations
 
@@ -60,6 +62,22 @@ def main() -> None:
     def gemm_only():
         nv.det_gemm(x, w, part, M=M, N=N, K=Kl, nchunks=nchunks, tile_n=128)
 
+    # sequence-parallel exit: every rank keeps its M / W token rows of the sum
+    rs_ok = M % (128 * world) == 0
+    out_rs = torch.empty(M // world if rs_ok else 1, N, device=dev, dtype=torch.bfloat16)
+    out_rs_n = torch.empty_like(out_rs)
+
+    def fused_rs():
+        coll.gemm_reduce_scatter(x, w, out_rs, nchunks)
+
+    def own_rs():
+        nv.det_gemm(x, w, out_o, M=M, N=N, K=Kl, nchunks=nchunks, tile_n=128)
+        return coll.reduce_scatter(out_o)
+
+    def nccl_rs():
+        nv.det_gemm(x, w, out_n, M=M, N=N, K=Kl, nchunks=nchunks, tile_n=128)
+        dist.reduce_scatter_tensor(out_rs_n, out_n)
+
     def timed(fn):
         for _ in range(3):
             fn()
@@ -78,6 +96,17 @@ def main() -> None:
     t_f, t_o, t_n, t_g = timed(fused), timed(own), timed(nccl), timed(gemm_only)
     same = torch.tensor([int(torch.equal(out_f, out_o))], device=dev)
     dist.all_reduce(same, op=dist.ReduceOp.MIN)
+    rs = {}
+    if rs_ok:
+        t_rf, t_ro, t_rn = timed(fused_rs), timed(own_rs), timed(nccl_rs)
+        rows = slice(rank * M // world, (rank + 1) * M // world)
+        same_rs = torch.tensor([int(torch.equal(out_rs, out_f[rows]))], device=dev)
+        dist.all_reduce(same_rs, op=dist.ReduceOp.MIN)
+        # a reduce-scatter moves every element once over each GPU's links (in), not twice
+        floor_rs = max(2.0 * M * N * Kl / 1655.3 / 1e9, (world - 1) / world * M * N * 2 / 770.0 / 1e6)
+        rs = {"rs_fused_ms": t_rf, "rs_gemm_plus_own_reduce_scatter_ms": t_ro, "rs_gemm_plus_nccl_reduce_scatter_ms": t_rn,
+              "rs_speedup_vs_nccl": t_rn / t_rf, "rs_roofline_ms": floor_rs, "rs_fraction_of_roofline": floor_rs / t_rf,
+              "rs_bitwise_equal_to_all_reduce_rows": bool(same_rs.item())}
     status = ext.poll_status(dev)
     if rank == 0:
         peak, link = 1655.3, 770.0
@@ -86,7 +115,7 @@ def main() -> None:
                           "fused_ms": t_f, "gemm_plus_own_all_reduce_ms": t_o, "gemm_plus_nccl_all_reduce_ms": t_n,
                           "gemm_alone_ms": t_g, "speedup_vs_nccl": t_n / t_f, "roofline_ms": floor,
                           "fraction_of_roofline": floor / t_f, "bitwise_equal_to_unfused": bool(same.item()),
-                          "device_status": status}))
+                          "device_status": status, **rs}))
     coll.close()
     dist.destroy_process_group()
 
