@@ -4,8 +4,6 @@ module, trains on a rollout with the strict log-prob + GRPO operators, and publi
 rl_engine/integrations/engines/train/deepspeed/adapter.py:74-316)."""
 from __future__ import annotations
 
-import contextlib
-
 import torch
 
 from rl_kernel_b200.integrations.common.weights import WeightPublisher
@@ -13,6 +11,26 @@ from rl_kernel_b200.integrations.engines.train.contract import (RolloutBatchMixi
                                                                  TrainingStageResult)
 from rl_kernel_b200.ops.loss import grpo_loss
 from rl_kernel_b200.ops.logprob import linear_logp
+
+
+def gather_zero3_parameter(param, group=None) -> torch.Tensor:
+    """Assemble a ZeRO-3 partitioned parameter: every rank of ``group`` holds ``param.ds_tensor`` (a flat slice, the last
+    one zero-padded); the whole is their concatenation in rank order cut to ``ds_numel`` and shaped ``ds_shape``.
+    Without an initialised process group the local partition must already be the whole parameter."""
+    import torch.distributed as dist
+
+    part = param.ds_tensor.detach().reshape(-1)
+    numel = int(getattr(param, "ds_numel", part.numel()))
+    shape = tuple(getattr(param, "ds_shape", param.shape))
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        parts = [torch.empty_like(part) for _ in range(dist.get_world_size(group))]
+        dist.all_gather(parts, part.contiguous(), group=group)
+        flat = torch.cat(parts)
+    else:
+        flat = part
+    if flat.numel() < numel:
+        raise ValueError(f"partitions hold {flat.numel()} elements, the parameter has {numel}")
+    return flat[:numel].reshape(shape).clone()
 
 
 class DeepSpeedTrainingWorker(RolloutBatchMixin):
@@ -46,9 +64,20 @@ class DeepSpeedTrainingWorker(RolloutBatchMixin):
                                    self.weight_version)
 
     def _full_state(self) -> dict[str, torch.Tensor]:
-        ctx = self.gather_context(self.engine.module.parameters()) if self.gather_context else contextlib.nullcontext()
-        with ctx:                                      # ZeRO-3: gather the partitioned parameters
-            return {k: v.detach().clone() for k, v in self.engine.module.state_dict().items()}
+        """The whole model on every rank.  ZeRO-3 keeps only a 1 / dp flat partition of every parameter on a rank
+        (``param.ds_tensor``; ``ds_shape`` / ``ds_numel`` describe the whole).  Order of preference: an injected
+        ``gather_context`` (``deepspeed.zero.GatheredParameters``), else this worker's own rank-ordered all-gather of the
+        partitions, else the state dict as it is (ZeRO stage 0-2: parameters are whole)."""
+        module = self.engine.module
+        params = dict(module.named_parameters())
+        partitioned = {k: p for k, p in params.items() if hasattr(p, "ds_tensor")}
+        if self.gather_context is not None:
+            with self.gather_context(module.parameters()):
+                return {k: v.detach().clone() for k, v in module.state_dict().items()}
+        state = {k: v.detach().clone() for k, v in module.state_dict().items() if k not in partitioned}
+        for name, p in partitioned.items():
+            state[name] = gather_zero3_parameter(p, getattr(self.engine, "dp_process_group", None) or getattr(p, "ds_process_group", None))
+        return state
 
     def publish_weights(self, weight_version: int):
         if weight_version <= self.weight_version and self.weight_version != 0:

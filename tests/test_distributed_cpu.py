@@ -227,3 +227,25 @@ def test_cp_partial_states_merge_in_block_order_to_full_attention():
         AttentionCPCommunicationPlan(par, backend="p2p_nccl_reference").validate()   # reference plans need a manifest
     prov = AttentionCPCommunicationPlan(par, backend="peer_memory").provenance()
     assert prov["cp_comm_redundant_compute_factor"] == 1 and prov["cp_comm_strict_kv_communication"] == "tma_peer_loads"
+
+
+def _zero3_worker(rank, world, port, out):
+    from rl_engine.integrations.engines.train.deepspeed.adapter import gather_zero3_parameter
+
+    _init(rank, world, port)
+    whole = torch.arange(10, dtype=torch.float32).view(2, 5)
+    per = 6                                                  # 10 elements over 2 ranks, padded to 12
+    flat = torch.cat([whole.reshape(-1), torch.zeros(2)])
+    p = torch.nn.Parameter(torch.zeros(0))
+    p.ds_tensor, p.ds_numel, p.ds_shape = flat[rank * per:(rank + 1) * per].clone(), 10, (2, 5)
+    got = gather_zero3_parameter(p)
+    if rank == 0:
+        torch.save(bool(torch.equal(got, whole)), out)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_zero3_partitions_are_gathered_in_rank_order(tmp_path):
+    out = str(tmp_path / "z3.pt")
+    mp.spawn(_zero3_worker, args=(2, _port(), out), nprocs=2, join=True)
+    assert torch.load(out)
