@@ -189,3 +189,30 @@ def test_rlk_verify_acceptance_checks_on_training_rounds(tmp_path):
         assert rlk(["verify", str(tmp_path)]) == 2
     write([rec(0), rec(1)], steps=200)
     assert rlk(["verify", str(tmp_path)]) == 2
+
+
+def test_operator_check_cli_and_weight_preparation(tmp_path, capsys):
+    from rl_engine.models.qwen3.prepare_weights import main as prepare
+    from rl_engine.validation.operators.__main__ import main as check
+
+    assert check(["list"]) == 0 and "rms_norm" in capsys.readouterr().out
+    assert check(["operator", "swiglu"]) == 0
+    assert check(["forward-invariance", "rope"]) == 0
+    assert check(["gradient-invariance", "rms_norm"]) == 0
+    assert check(["stateful-kv"]) == 0
+    capsys.readouterr()
+    assert check(["sweep", "--json", "--output", str(tmp_path / "evidence.json")]) == 0
+    doc = json.loads((tmp_path / "evidence.json").read_text())
+    assert doc["green"] and doc["inventory"] == {"unexecuted": [], "needs_fix": []} and doc["accelerator"]["arch_key"] == "cpu"
+    if not torch.cuda.is_available():
+        with pytest.raises(Exception):
+            check(["operator", "swiglu", "--device", "cuda"])
+    out = tmp_path / "w"
+    assert prepare(["--output", str(out), "--synthetic", "--layers", "1", "--hidden", "256", "--ffn", "512", "--vocab", "1024"]) == 0
+    first = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert prepare(["--output", str(out), "--verify-only"]) == 0
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["content_hash"] == first["content_hash"]
+    shard = next(out.glob("*.safetensors"))
+    (tmp_path / "sha.json").write_text(json.dumps({shard.name: "0" * 64}))
+    with pytest.raises(ValueError, match="checksum"):
+        prepare(["--output", str(out), "--verify-only", "--sha256-file", str(tmp_path / "sha.json")])
