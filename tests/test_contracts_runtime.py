@@ -233,3 +233,54 @@ def test_semantic_resolution_overrides_and_module_executor():
     assert rewards.shape == (5,)
     with pytest.raises(ValueError):
         StatelessForwardConfig(use_cache=True)
+
+
+def test_numerical_contract_surface():
+    import copy
+
+    import torch
+
+    from rl_engine.contracts import numerical as N
+
+    c = N.load_contract()
+    N.validate_contract_schema(c)
+    pol = N.resolve_dtype_policy()
+    assert pol.execution_dtype == "bfloat16" and pol.tf32_candidate_execution == "disabled" and "b200_bf16" in pol.backend_profiles
+    t = N.resolve_judgment_tolerance("forward_accuracy", "logprob", torch.bfloat16, arch_key="sm100")
+    assert (t.mode, t.atol, t.rtol, t.comparison_rhs_role) == ("tolerance", 0.06, 0.0, "fp32_reference") and N.resolve_logprob_threshold("bf16") == 0.06
+    inv = N.resolve_judgment_tolerance("forward_invariance", "attention", "bfloat16")
+    assert inv.mode == "bitwise" and inv.check(torch.ones(2), torch.ones(2))[0] and not inv.check(torch.ones(2), torch.ones(2) + 1e-7)[0]
+    assert N.resolve_tolerance_support("gradient_accuracy", "reduction", "fp16").status == "optional"
+    with pytest.raises(N.ContractResolveError):
+        N.resolve_judgment_tolerance("forward_accuracy", "reduction", "float8")
+    with pytest.raises(N.ContractResolveError):
+        N.assert_comparison_roles("forward_accuracy", "baseline", "fp32_reference")
+    N.assert_comparison_roles("train_infer_logprob_parity", "training_style_teacher_forcing", "inference_style_rollout_decode")
+    good = N.BackendProvenance("b200_bf16", "b200-tcgen05", "b200-tcgen05", "bfloat16", "float32", "bfloat16", "float32", False, False)
+    N.validate_backend_provenance(good)
+    for bad in (dict(candidate_tf32_enabled=True), dict(actual_backend="reference"), dict(execution_dtype="float32"), dict(backend_profile="rocm")):
+        with pytest.raises(N.ContractResolveError):
+            N.validate_backend_provenance(N.BackendProvenance(**{**good.to_dict(), **bad}))
+    lp = -torch.rand(4, 8)
+    agg = N.compute_logprob_aggregates(lp + 0.01, lp, torch.ones(4, 8, dtype=torch.bool))
+    v = N.judge_logprob_aggregates(agg, "bfloat16")
+    assert v.passed and abs(agg.max_abs_dlogp - 0.01) < 1e-6 and agg.clipfrac0 == 0.0 and agg.comparison_lhs_role == "training_style_teacher_forcing"
+    assert not N.judge_logprob_aggregates(agg, "float32").passed
+    far = lp.clone()
+    far[0, 0] += 0.5
+    assert not N.judge_logprob_aggregates(N.compute_logprob_aggregates(far, lp), "bfloat16").passed
+    with pytest.raises(N.ContractResolveError):
+        N.compute_logprob_aggregates(lp, lp, torch.zeros(4, 8, dtype=torch.bool))
+    nan = lp.clone()
+    nan[1, 1] = float("nan")
+    with pytest.raises(N.ContractResolveError):
+        N.compute_logprob_aggregates(nan, lp)
+    broken = copy.deepcopy(c)
+    broken["policy"]["backend_private_tolerance_relaxation"] = True
+    with pytest.raises(N.ContractSchemaError):
+        N.validate_contract_schema(broken)
+    broken = copy.deepcopy(c)
+    broken["judgments"]["forward_invariance"]["by_op_class"]["attention"]["bfloat16"]["atol"] = 1e-6
+    with pytest.raises(N.ContractSchemaError):
+        N.validate_contract_schema(broken)
+    assert N.default_clip_interval() == (0.8, 1.2) and len(N.tolerance_contract_fingerprint()) == 64
