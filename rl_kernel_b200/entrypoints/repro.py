@@ -295,6 +295,18 @@ def cmd_report(args) -> int:
     from rl_kernel_b200.validation.reports.drift_report import write_drift_report
 
     src = Path(args.run_dir)
+    if (src / "paired").exists():
+        from rl_kernel_b200.validation.reports.drift_report import build_drift_report, render_drift_report, write_drift_bundle, write_drift_trace
+
+        rep = build_drift_report(src)
+        out = Path(args.out or src / "report")
+        out.mkdir(parents=True, exist_ok=True)
+        (out / "report.json").write_text(json.dumps(rep, indent=1, sort_keys=True, default=str))
+        (out / "report.html").write_text(render_drift_report(rep))
+        write_drift_trace(rep, out / "trace.json")
+        write_drift_bundle(rep, out / "bundle.zip")
+        print(json.dumps({"overall": rep["overall"], "cases": len(rep["cases"]), "report": str(out / "report.html"), "bundle": str(out / "bundle.zip")}))
+        return 0 if rep["overall"] == "pass" else 1
     summary_file = src / "summary.json"
     if summary_file.exists() and "cases" in json.loads(summary_file.read_text()):
         summary = json.loads(summary_file.read_text())

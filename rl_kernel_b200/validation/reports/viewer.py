@@ -18,6 +18,13 @@ import torch
 
 def load_bundle(path: str | Path) -> dict[str, Any]:
     root = Path(path)
+    if root.is_file() and root.suffix == ".zip":
+        from rl_kernel_b200.validation.reports.drift_report import load_drift_bundle
+
+        rep = load_drift_bundle(root)["report"]
+        return {"root": str(root), "kind": "drift_bundle", "events": [], "summary": {k: rep.get(k) for k in ("experiment_id", "overall", "bitwise")},
+                "cases": {c["case_id"]: {"status": c.get("status"), "mismatch_count": c.get("mismatch_count"), "active_token_count": c.get("active_token_count"),
+                                         "changed_paths": []} for c in rep.get("cases", [])}}
     if root.is_file():
         root = root.parent
     bundle: dict[str, Any] = {"root": str(root), "events": [], "cases": {}}

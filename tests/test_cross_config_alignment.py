@@ -250,3 +250,30 @@ def test_framework_materialisers_translate_attention_knobs():
             set_active_integration("megatron", integ)
     finally:
         clear_active_integration("vllm")
+
+
+def test_drift_report_bundle_from_sealed_attempts(tmp_path):
+    from rl_engine.validation.fixtures.cpu_cross_config import run_cpu_experiment
+    from rl_engine.validation.reports.drift_report import (build_cross_config_attempt_report, build_drift_report, build_drift_trace,
+                                                           load_drift_bundle, render_drift_report, write_drift_bundle)
+
+    base = _raw(experiment_id="rep", baseline={"batch": {"size": 3}, "rollout": {"dtype": "fp32"}, "training": {"compute_dtype": "fp32"},
+                                               "logp": {"backend": "reference"}},
+                interventions=[{"path": "batch.size", "values": [1]}],
+                operators={"selected_logprob": {"rollout": {"backend": "reference"}, "training": {"backend": "smoke_only.logp_offset"}}})
+    run_cpu_experiment(config_from_dict(base), tmp_path, bitwise=False)
+    rep = build_drift_report(tmp_path / "rep")
+    assert rep["overall"] == "failure" and len(rep["cases"]) == 2
+    c = rep["cases"][0]
+    assert c["status"] == "fail" and c["recomputed_comparison_matches"] and abs(c["worst_tokens"][0]["abs_diff"] - 0.25) < 1e-5
+    assert c["sides"]["training"]["actual"]["logp.backend"] == "smoke_only.logp_offset" and sum(c["delta_histogram"]) == 24
+    trace = build_drift_trace(rep)
+    assert sum(1 for e in trace["traceEvents"] if e.get("cat") == "case") == 2
+    page = render_drift_report(rep)
+    assert page.startswith("<!doctype html>") and "FAIL" in page and "<script" not in page
+    bundle = load_drift_bundle(write_drift_bundle(rep, tmp_path / "b.zip"))
+    assert bundle["report"]["experiment_id"] == "rep" and bundle["html"]
+    attempt = next((tmp_path / "rep" / "paired").iterdir()) / "0"
+    (attempt / "result.json").write_text("{}")
+    broken = build_cross_config_attempt_report(attempt)
+    assert broken["level"] == "failure" and "seal" in broken["reason"]
