@@ -216,3 +216,14 @@ def test_operator_check_cli_and_weight_preparation(tmp_path, capsys):
     (tmp_path / "sha.json").write_text(json.dumps({shard.name: "0" * 64}))
     with pytest.raises(ValueError, match="checksum"):
         prepare(["--output", str(out), "--verify-only", "--sha256-file", str(tmp_path / "sha.json")])
+
+
+def test_operator_spec_paths_resolve():
+    import importlib
+
+    from rl_engine.validation.operators.operator_specs import OP_SPECS, _local
+
+    for name, spec in OP_SPECS.items():
+        for path in {**spec.candidate_paths, "gold": spec.gold_path}.values():
+            mod, attr = _local(path).rsplit(".", 1)
+            assert hasattr(importlib.import_module(mod), attr), (name, path)
