@@ -12,14 +12,31 @@ namespace rlk {
 
 __device__ __forceinline__ float silu_f(float g) { return g / (1.f + __expf(-g)); }
 
+// Which 16-byte piece (row r, first column c) this thread owns.  The grid is (row blocks, 256-piece column chunks):
+// a row with at least 256 pieces gets one block row per row, a narrower one shares a block with its neighbours, so
+// no thread pays a 64-bit division to find its row.  (swiglu_grid() is the host side of the same rule.)
+__device__ __forceinline__ bool swiglu_piece(int rows, int I, int& r, int& c) {
+  const int per_row = I / 8;
+  int piece;
+  if (per_row >= 256) {
+    r = blockIdx.x;
+    piece = blockIdx.y * 256 + threadIdx.x;
+  } else {
+    const int rpb = 256 / per_row, lr = threadIdx.x / per_row;
+    if (lr >= rpb) return false;
+    r = blockIdx.x * rpb + lr;
+    piece = threadIdx.x - lr * per_row;
+  }
+  c = piece * 8;
+  return r < rows && piece < per_row;
+}
+
 __global__ void __launch_bounds__(256)
 swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_gu, __nv_bfloat16* __restrict__ out,
                   long long ld_out, int rows, int I, int blk, const int* __restrict__ rows_limit) {
   griddep_sync();
-  const int per_row = I / 8;
-  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= static_cast<long long>(rows) * per_row) return;
-  const int r = static_cast<int>(idx / per_row), c = static_cast<int>(idx % per_row) * 8;
+  int r, c;
+  if (!swiglu_piece(rows, I, r, c)) return;
   if (rows_limit && r >= *rows_limit) return;  // row count known only on the device (MoE)
   const long long gc = static_cast<long long>(c / blk) * 2 * blk + (c % blk);  // column of gate[c]
   const uint4 g = *reinterpret_cast<const uint4*>(gu + r * ld_gu + gc);
@@ -37,10 +54,8 @@ __global__ void __launch_bounds__(256)
 swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_gu, const __nv_bfloat16* __restrict__ dout,
                   long long ld_dout, __nv_bfloat16* __restrict__ dgu, long long ld_dgu, int rows, int I, int blk,
                   const int* __restrict__ rows_limit) {
-  const int per_row = I / 8;
-  const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (idx >= static_cast<long long>(rows) * per_row) return;
-  const int r = static_cast<int>(idx / per_row), c = static_cast<int>(idx % per_row) * 8;
+  int r, c;
+  if (!swiglu_piece(rows, I, r, c)) return;
   if (rows_limit && r >= *rows_limit) return;
   const long long gc = static_cast<long long>(c / blk) * 2 * blk + (c % blk);  // column of gate[c]
   const uint4 g = *reinterpret_cast<const uint4*>(gu + r * ld_gu + gc);
@@ -71,14 +86,20 @@ swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, long long ld_gu, const _
 }  // namespace rlk
 using namespace rlk;
 
+static dim3 swiglu_grid(int rows, int I) {
+  const int per_row = I / 8;
+  if (per_row >= 256) return dim3(static_cast<unsigned>(rows), static_cast<unsigned>((per_row + 255) / 256));
+  const int rpb = 256 / per_row;
+  return dim3(static_cast<unsigned>((rows + rpb - 1) / rpb), 1);
+}
+
 // rows_limit (device int, may be null): rows at or beyond *rows_limit are skipped.
 RLK_API int rlk_swiglu_fwd_dyn(const void* gu, long long ld_gu, void* out, long long ld_out, int rows,
                                int I, int blk, const int* rows_limit, void* stream) {
   RLK_REQUIRE(rows > 0 && I > 0 && I % 8 == 0 && ld_gu % 8 == 0 && ld_out % 8 == 0,
               "swiglu: I and pitches must be multiples of 8");
   RLK_REQUIRE(blk > 0 && blk % 8 == 0 && I % blk == 0, "swiglu: blk must divide I and be a multiple of 8");
-  const long long n = static_cast<long long>(rows) * (I / 8);
-  RLK_CHECK_CUDA(launch_pdl(swiglu_fwd_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0,
+  RLK_CHECK_CUDA(launch_pdl(swiglu_fwd_kernel, swiglu_grid(rows, I), dim3(256), 0,
                             static_cast<cudaStream_t>(stream), (const __nv_bfloat16*)gu, ld_gu, (__nv_bfloat16*)out,
                             ld_out, rows, I, blk, rows_limit));
   RLK_CHECK_CUDA(cudaGetLastError());
@@ -96,8 +117,7 @@ RLK_API int rlk_swiglu_bwd_dyn(const void* gu, long long ld_gu, const void* dout
   RLK_REQUIRE(rows > 0 && I > 0 && I % 8 == 0 && ld_gu % 8 == 0 && ld_dout % 8 == 0 && ld_dgu % 8 == 0,
               "swiglu_bwd: I and pitches must be multiples of 8");
   RLK_REQUIRE(blk > 0 && blk % 8 == 0 && I % blk == 0, "swiglu_bwd: blk must divide I and be a multiple of 8");
-  const long long n = static_cast<long long>(rows) * (I / 8);
-  swiglu_bwd_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  swiglu_bwd_kernel<<<swiglu_grid(rows, I), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)gu, ld_gu, (const __nv_bfloat16*)dout, ld_dout, (__nv_bfloat16*)dgu, ld_dgu, rows, I, blk, rows_limit);
   RLK_CHECK_CUDA(cudaGetLastError());
   return RLK_OK;

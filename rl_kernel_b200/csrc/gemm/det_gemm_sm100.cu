@@ -240,10 +240,13 @@ __device__ __forceinline__ int act_gate_row(int nt, int act_blk) {
   return (c0 / act_blk) * 2 * act_blk + c0 % act_blk;
 }
 
-template <int BN, bool A_MN, bool B_MN>
+// AR: the instantiation with the fused all-reduce / reduce-scatter epilogue.  It is a template parameter rather than
+// a run-time branch because the tile reduction is a real function call whose registers (batched peer loads) would
+// otherwise count against every instantiation and cost the small-M kernels their second resident CTA.
+template <int BN, bool A_MN, bool B_MN, bool AR = false>
 __global__ void __launch_bounds__(gemm_threads<BN>(), 1)
 det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+                const __grid_constant__ CUtensorMap tmC, const __grid_constant__ GemmParams p) {
   using S = GemmSmem<BN>;
   const uint32_t kStages = static_cast<uint32_t>(p.stages);   // ring depth chosen by the host (<= kMaxStages)
   // TMEM columns: two accumulators (+ three packed-bf16 tree levels when chunked, BN==128 only)
@@ -805,7 +808,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         tc_fence_before();
         mbar_arrive(acce0 + 8 * a);
       }
-      if (p.ar_world > 1) {
+      if constexpr (AR) {
         // ---- fused all-reduce, one tile behind the accumulator drain.  This tile's partial is in the
         // frame: make it visible and tell the peers; then finish the PREVIOUS tile, whose peers have
         // had a whole tile's time to answer, so the flag round trip is off the critical path.
@@ -823,7 +826,7 @@ det_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         ar_prev_t = t; ar_prev_m0 = mt * BM; ar_prev_n0 = n0;
       }
     }
-    if (p.ar_world > 1 && ar_prev_t >= 0 && !*abort_flag) {
+    if constexpr (AR) if (ar_prev_t >= 0 && !*abort_flag) {
       const unsigned long long seq = p.ar_use_epoch ? p.ar_seq + p.ar_epoch[0] * p.ar_epoch[1] : p.ar_seq;
       ar_finish_tile<BN>(p, ar_prev_t, ar_prev_m0, ar_prev_n0, static_cast<int>(threadIdx.x) - 64, seq, abort_flag);
     }
@@ -845,7 +848,7 @@ static int g_tma_store = 1;
 static long long* g_trace_ptr = nullptr;
 #endif
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, bool AR = false>
 static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long long lda,
                        long long ldb, cudaStream_t stream) {
   GemmParams p = p0;
@@ -927,7 +930,8 @@ static int launch_gemm(const void* A, const void* B, const GemmParams& p0, long 
   p.trace = g_trace_ptr;
 #endif
   const int grid = tiles < sm_count() * ctas_per_sm ? tiles : sm_count() * ctas_per_sm;
-  auto kfn = det_gemm_kernel<BN, A_MN, B_MN>;
+  auto kfn = det_gemm_kernel<BN, A_MN, B_MN, AR>;
+  RLK_REQUIRE((p.ar_world > 1) == AR, "det_gemm: all-reduce parameters and the kernel's epilogue do not match");
   static bool attr_set[64] = {false};
   static std::mutex attr_mu;
   int dev = 0;
@@ -1188,7 +1192,7 @@ RLK_API int rlk_det_gemm_ar(void* state, const void* A, const void* B, void* out
   p.ar_use_epoch = st->w.use_epoch;
   p.ar_out = static_cast<__nv_bfloat16*>(out);
   p.ar_ld_out = ld_out;
-  return launch_gemm<128, false, false>(A, B, p, lda, ldb, static_cast<cudaStream_t>(stream));
+  return launch_gemm<128, false, false, true>(A, B, p, lda, ldb, static_cast<cudaStream_t>(stream));
 }
 
 // GEMM + fixed-order reduce-scatter over token rows in ONE kernel (sequence-parallel row-parallel projections):
@@ -1236,7 +1240,7 @@ RLK_API int rlk_det_gemm_rs(void* state, const void* A, const void* B, void* out
   // only rows [rs_row0, rs_row1) are ever written: bias the base so that they land on the caller's rows 0..rows-1
   p.ar_out = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uintptr_t>(out) - static_cast<uintptr_t>(2ll * p.rs_row0 * ld_out));
   p.ar_ld_out = ld_out;
-  return launch_gemm<128, false, false>(A, B, p, lda, ldb, static_cast<cudaStream_t>(stream));
+  return launch_gemm<128, false, false, true>(A, B, p, lda, ldb, static_cast<cudaStream_t>(stream));
 }
 
 // ---- the variant that allocates nothing (see rlk/no_alloc.h for the contract) ----------------

@@ -37,6 +37,75 @@ rope_kernel(const T* __restrict__ x, long long x_pitch, const int* __restrict__ 
   }
 }
 
+// Vector form: one thread owns 16 bytes of a head's first half and the matching 16 bytes of its second half
+// (V = 8 bf16 or 4 fp32 pairs), reads the pairs' cos / sin as 16-byte pieces of the table row and writes both
+// halves with 16-byte stores.  A block walks whole rows (several at once when a row has fewer than 256 pieces),
+// so no 64-bit division is paid per element.  Needs D/2 % V == 0 and 16-byte aligned rows.
+template <typename T>
+__global__ void __launch_bounds__(256)
+rope_vec_kernel(const T* __restrict__ x, long long x_pitch, const int* __restrict__ pos, const float* __restrict__ cos_t,
+                const float* __restrict__ sin_t, T* __restrict__ y, long long y_pitch, long long rows, int heads, int D,
+                int max_pos, int inverse, int per_row, int rows_per_block) {
+  constexpr int V = 16 / sizeof(T);
+  griddep_sync();
+  const int half = D >> 1;
+  const int per_half = half / V;                                  // 16-byte pieces per half head
+  const int lr = threadIdx.x / per_row, piece0 = threadIdx.x - lr * per_row;
+  const int step = rows_per_block > 1 ? per_row : 256;            // several rows per block: one piece per thread
+  if (lr >= rows_per_block) return;
+  for (long long r = static_cast<long long>(blockIdx.x) * rows_per_block + lr; r < rows;
+       r += static_cast<long long>(gridDim.x) * rows_per_block) {
+    int p = pos[r];
+    p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);             // a position outside the table is clamped
+    const float* cr = cos_t + static_cast<long long>(p) * half;
+    const float* sr = sin_t + static_cast<long long>(p) * half;
+    for (int piece = piece0; piece < per_row; piece += step) {
+      const int h = piece / per_half, j = (piece - h * per_half) * V;
+      const T* xr = x + r * x_pitch + static_cast<long long>(h) * D + j;
+      T* yr = y + r * y_pitch + static_cast<long long>(h) * D + j;
+      const uint4 ua = *reinterpret_cast<const uint4*>(xr);
+      const uint4 ub = *reinterpret_cast<const uint4*>(xr + half);
+      float c[V], s[V], a[V], b[V];
+#pragma unroll
+      for (int q = 0; q < V / 4; ++q) {
+        const float4 cq = __ldg(reinterpret_cast<const float4*>(cr + j) + q);
+        const float4 sq = __ldg(reinterpret_cast<const float4*>(sr + j) + q);
+        c[4 * q] = cq.x; c[4 * q + 1] = cq.y; c[4 * q + 2] = cq.z; c[4 * q + 3] = cq.w;
+        s[4 * q] = sq.x; s[4 * q + 1] = sq.y; s[4 * q + 2] = sq.z; s[4 * q + 3] = sq.w;
+      }
+      const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+      if constexpr (sizeof(T) == 2) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          a[2 * q] = bf16_lo(wa[q]); a[2 * q + 1] = bf16_hi(wa[q]);
+          b[2 * q] = bf16_lo(wb[q]); b[2 * q + 1] = bf16_hi(wb[q]);
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) { a[q] = __uint_as_float(wa[q]); b[q] = __uint_as_float(wb[q]); }
+      }
+      float o1[V], o2[V];
+#pragma unroll
+      for (int q = 0; q < V; ++q) {
+        const float sq = inverse ? -s[q] : s[q];
+        // explicit single-rounding multiplies and adds (no FMA contraction), as in the scalar form
+        o1[q] = __fsub_rn(__fmul_rn(a[q], c[q]), __fmul_rn(b[q], sq));
+        o2[q] = __fadd_rn(__fmul_rn(b[q], c[q]), __fmul_rn(a[q], sq));
+      }
+      uint4 r1, r2;
+      if constexpr (sizeof(T) == 2) {
+        r1 = make_uint4(pack_bf16x2(o1[0], o1[1]), pack_bf16x2(o1[2], o1[3]), pack_bf16x2(o1[4], o1[5]), pack_bf16x2(o1[6], o1[7]));
+        r2 = make_uint4(pack_bf16x2(o2[0], o2[1]), pack_bf16x2(o2[2], o2[3]), pack_bf16x2(o2[4], o2[5]), pack_bf16x2(o2[6], o2[7]));
+      } else {
+        r1 = make_uint4(__float_as_uint(o1[0]), __float_as_uint(o1[1]), __float_as_uint(o1[2]), __float_as_uint(o1[3]));
+        r2 = make_uint4(__float_as_uint(o2[0]), __float_as_uint(o2[1]), __float_as_uint(o2[2]), __float_as_uint(o2[3]));
+      }
+      *reinterpret_cast<uint4*>(yr) = r1;
+      *reinterpret_cast<uint4*>(yr + half) = r2;
+    }
+  }
+}
+
 }  // namespace rlk
 using namespace rlk;
 
@@ -54,6 +123,26 @@ RLK_API int rlk_rope(const void* x, long long x_pitch, const int* pos, const flo
   const long long want = (total + 255) / 256;
   const int grid = static_cast<int>(want < 8LL * sm_count() ? want : 8LL * sm_count());
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // 16-byte pieces when the layout allows it (every model shape does); the scalar kernel takes the rest
+  const int V = dtype == 0 ? 8 : 4;
+  const long long esz = dtype == 0 ? 2 : 4;
+  const bool vec = (D / 2) % V == 0 && (x_pitch * esz) % 16 == 0 && (y_pitch * esz) % 16 == 0 &&
+                   (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(y) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(cos_t) & 15) == 0 && (reinterpret_cast<uintptr_t>(sin_t) & 15) == 0;
+  if (vec) {
+    const int per_row = heads * (D / 2 / V);
+    const int rpb = per_row >= 256 ? 1 : 256 / per_row;
+    const long long blocks = (rows + rpb - 1) / rpb;
+    const int vgrid = static_cast<int>(blocks < 16LL * sm_count() ? blocks : 16LL * sm_count());
+    if (dtype == 0)
+      RLK_CHECK_CUDA(launch_pdl(rope_vec_kernel<__nv_bfloat16>, dim3(vgrid), dim3(256), 0, s, (const __nv_bfloat16*)x, x_pitch,
+                                pos, cos_t, sin_t, (__nv_bfloat16*)y, y_pitch, rows, heads, D, max_pos, inverse, per_row, rpb));
+    else
+      RLK_CHECK_CUDA(launch_pdl(rope_vec_kernel<float>, dim3(vgrid), dim3(256), 0, s, (const float*)x, x_pitch, pos, cos_t,
+                                sin_t, (float*)y, y_pitch, rows, heads, D, max_pos, inverse, per_row, rpb));
+    RLK_CHECK_CUDA(cudaGetLastError());
+    return RLK_OK;
+  }
   if (dtype == 0)
     RLK_CHECK_CUDA(launch_pdl(rope_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, (const __nv_bfloat16*)x, x_pitch, pos,
                               cos_t, sin_t, (__nv_bfloat16*)y, y_pitch, rows, heads, D, max_pos, inverse));
