@@ -120,12 +120,14 @@ def _measure(args, plan: dict, dev, world: int, rank: int, local: int, *, warmup
     from rl_kernel_b200.backends import native as nv
     from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec
     from rl_kernel_b200.models.qwen3.grpo import GRPOConfig, GRPOTrainer
-    from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context
+    from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context, cp_frame_bytes_for
 
-    ctx = build_parallel_context(plan["tp"], plan["cp"], dev, dp=plan["dp"])
     spec = Qwen3DenseSpec.official()
     if args.layers:
         spec = spec.with_layers(args.layers)
+    # (a training micro-batch keeps micro_batch x seq_len tokens on every rank, whatever the layout)
+    ctx = build_parallel_context(plan["tp"], plan["cp"], dev, dp=plan["dp"],
+                                 cp_frame_bytes=cp_frame_bytes_for(spec, plan["tp"], args.micro_batch * (PROMPT_LEN + args.response_len)))
     # one training replica spans all GPUs; a micro-batch keeps micro_batch x seq_len tokens per rank
     cfg = GRPOConfig(num_prompts=PROMPTS_PER_GPU * args.gpus, group_size=GROUP,
                      prompt_len=PROMPT_LEN, response_len=args.response_len,

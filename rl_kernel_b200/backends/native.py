@@ -381,6 +381,25 @@ def swiglu_bwd(gu, dout, dgu, I: int, blk: int | None = None, rows_limit=None) -
     _count()
 
 
+def swiglu_split_fwd(gate, up, out) -> None:
+    """out [rows, I] = silu(gate) * up for gate / up / out in separate 2-D bf16 tensors (unit inner stride,
+    row strides multiples of 8 elements, 16-byte aligned)."""
+    rc = _lib().rlk_swiglu_split_fwd(ext.ptr(gate), _ll(gate.stride(0)), ext.ptr(up), _ll(up.stride(0)), ext.ptr(out),
+                                     _ll(out.stride(0)), c_int(gate.shape[0]), c_int(gate.shape[1]),
+                                     ext.stream_ptr(gate.device))
+    ext.check(rc, "swiglu_split_fwd")
+    _count()
+
+
+def swiglu_split_bwd(gate, up, dout, dgate, dup) -> None:
+    rc = _lib().rlk_swiglu_split_bwd(ext.ptr(gate), _ll(gate.stride(0)), ext.ptr(up), _ll(up.stride(0)), ext.ptr(dout),
+                                     _ll(dout.stride(0)), ext.ptr(dgate), _ll(dgate.stride(0)), ext.ptr(dup),
+                                     _ll(dup.stride(0)), c_int(gate.shape[0]), c_int(gate.shape[1]),
+                                     ext.stream_ptr(gate.device))
+    ext.check(rc, "swiglu_split_bwd")
+    _count()
+
+
 # ------------------------------------------------------------------------------------- embedding
 def embedding_fwd(ids, w, out, vocab_start: int = 0) -> None:
     assert ids.dtype == torch.int64

@@ -55,7 +55,7 @@ def main(argv=None) -> None:
     w = torch.ones(4096, device=dev).bfloat16()
     qh = x.view(T, 32, 128)
     pos = (torch.arange(T, device=dev) % 4096)
-    add("rope", 2 * x.numel() * 2, lambda: rope(qh.transpose(0, 1), pos))
+    add("rope", 2 * x.numel() * 2, lambda: rope(qh.transpose(0, 1), pos, max_position=4096))
     add("rms_norm", 2 * x.numel() * 2, lambda: rms_norm(x, w))
     gate, up = x, torch.randn(T, 4096, device=dev, generator=g).bfloat16()
     add("swiglu", 3 * x.numel() * 2, lambda: swiglu(gate, up))

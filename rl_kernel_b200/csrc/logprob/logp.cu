@@ -15,29 +15,50 @@
 
 namespace rlk {
 
+// One thread owns one 128-id vocabulary tile of one row (its statistics have a fixed order), but the 256 bytes of a
+// tile are fetched by the whole warp: a warp's 32 tiles are 8 KB of contiguous logits, read as 16 fully coalesced
+// 512-byte requests into shared memory (tile pitch 272 bytes: the 16-byte reads of a quarter warp then fall into eight
+// different bank groups) and consumed by their owners from there.  Grid: (rows, groups of 128 tiles).
+constexpr int kTilePitch = 272;
 __global__ void __launch_bounds__(128)
 logits_tile_stats_kernel(const __nv_bfloat16* __restrict__ logits, long long ld, const long long* __restrict__ targets,
                          float2* __restrict__ stats, long long stats_row_stride, float* __restrict__ tgt_logit,
                          int rows, int n_local, long long vocab_start, int tile_start, int n_tiles_local,
                          float inv_temp, const long long* __restrict__ row_indices, const float* __restrict__ min_keep) {
+  __shared__ __align__(16) unsigned char stage[4][32 * kTilePitch];
   griddep_sync();
-  const long long gid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (gid >= static_cast<long long>(rows) * n_tiles_local) return;
-  const int row = static_cast<int>(gid / n_tiles_local);
-  const int lt = static_cast<int>(gid % n_tiles_local);
-  const int col0 = lt * kVocabTile;
+  const int row = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lt0 = (blockIdx.y * 4 + warp) * 32;          // first tile of this warp
+  if (lt0 >= n_tiles_local) return;
   // indexed form: output row `row` scores logits row row_indices[row] (the launch geometry
   // depends only on the number of scored rows and the vocabulary, never on the index values)
   const long long src_row = row_indices ? row_indices[row] : row;
-  const __nv_bfloat16* src = logits + src_row * ld + col0;
+  const __nv_bfloat16* wsrc = logits + src_row * ld + static_cast<long long>(lt0) * kVocabTile;
+  unsigned char* st = stage[warp];
+  uint4 piece[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {                          // all 16 requests in flight before the first store
+    const int p = i * 32 + lane;                          // 16-byte piece of the warp's 8 KB
+    piece[i] = make_uint4(0, 0, 0, 0);
+    if (lt0 * kVocabTile + p * 8 < n_local) piece[i] = *reinterpret_cast<const uint4*>(wsrc + p * 8);   // n_local % 8 == 0
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const int p = i * 32 + lane;
+    *reinterpret_cast<uint4*>(st + (p >> 4) * kTilePitch + (p & 15) * 16) = piece[i];
+  }
+  __syncwarp();
+  const int lt = lt0 + lane;
+  if (lt >= n_tiles_local) return;
+  const int col0 = lt * kVocabTile;
   // restricted sampling support: scaled logits below the row's threshold count as -inf
   const float keep_from = min_keep ? min_keep[row] : -INFINITY;
   float z[128];
 #pragma unroll
   for (int c = 0; c < 16; ++c) {
-    uint4 v = make_uint4(0, 0, 0, 0);
-    const bool in = col0 + c * 8 < n_local;  // n_local is a multiple of 8
-    if (in) v = *reinterpret_cast<const uint4*>(src + c * 8);
+    const bool in = col0 + c * 8 < n_local;
+    const uint4 v = *reinterpret_cast<const uint4*>(st + lane * kTilePitch + c * 16);
     const uint32_t u[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -52,7 +73,7 @@ logits_tile_stats_kernel(const __nv_bfloat16* __restrict__ logits, long long ld,
   if (targets) {
     const long long tl = targets[row] - vocab_start - col0;
     if (tl >= 0 && tl < kVocabTile && col0 + tl < n_local) {
-      const float zt = logp_scale(__bfloat162float(src[tl]), inv_temp);
+      const float zt = logp_scale(__bfloat162float(logits[src_row * ld + col0 + tl]), inv_temp);
       tgt_logit[row] = zt >= keep_from ? zt : -INFINITY;
     }
   }
@@ -235,8 +256,7 @@ RLK_API int rlk_logits_tile_stats_keep(const void* logits, long long ld, const l
   RLK_REQUIRE(rows > 0 && n_local > 0 && n_local % 8 == 0 && ld % 8 == 0, "tile_stats: bad shape");
   RLK_REQUIRE(vocab_start % kVocabTile == 0, "tile_stats: vocab_start must be a multiple of 128");
   const int n_tiles_local = (n_local + kVocabTile - 1) / kVocabTile;
-  const long long n = static_cast<long long>(rows) * n_tiles_local;
-  RLK_CHECK_CUDA(launch_pdl(logits_tile_stats_kernel, dim3(static_cast<unsigned>((n + 127) / 128)), dim3(128), 0,
+  RLK_CHECK_CUDA(launch_pdl(logits_tile_stats_kernel, dim3(static_cast<unsigned>(rows), static_cast<unsigned>((n_tiles_local + 127) / 128)), dim3(128), 0,
                             static_cast<cudaStream_t>(stream), (const __nv_bfloat16*)logits, ld, targets,
                             (float2*)stats, stats_row_stride, tgt_logit, rows, n_local, vocab_start,
                             static_cast<int>(vocab_start / kVocabTile), n_tiles_local, inv_temp, row_indices, min_keep));

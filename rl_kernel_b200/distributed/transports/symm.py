@@ -172,11 +172,23 @@ class SymmetricMemoryCollective:
         if pad:
             src = torch.zeros(nbytes + pad, dtype=torch.uint8, device=t.device)
             src[:nbytes] = t.view(torch.uint8).reshape(-1)
-        out = torch.empty(self.world * (nbytes + pad), dtype=torch.uint8, device=t.device)
-        ext.check(self._lib.rlk_symm_all_gather(self._state, ext.ptr(src), ext.ptr(out), c_longlong(nbytes + pad),
-                                                ext.stream_ptr(self.device)), "symm_all_gather")
-        nv._count()
-        out = out.view(self.world, nbytes + pad)[:, :nbytes]
+        total = nbytes + pad
+        out = torch.empty(self.world * total, dtype=torch.uint8, device=t.device)
+        if total <= self.frame_bytes:
+            ext.check(self._lib.rlk_symm_all_gather(self._state, ext.ptr(src), ext.ptr(out), c_longlong(total),
+                                                    ext.stream_ptr(self.device)), "symm_all_gather")
+            nv._count()
+        else:
+            # a rank's share is larger than a frame: frame-sized pieces, each gathered and then placed
+            flat, rows = src.view(torch.uint8).reshape(-1), out.view(self.world, total)
+            for off in range(0, total, self.frame_bytes):
+                n = min(self.frame_bytes, total - off)
+                piece = torch.empty(self.world * n, dtype=torch.uint8, device=t.device)
+                ext.check(self._lib.rlk_symm_all_gather(self._state, ext.ptr(flat[off:off + n]), ext.ptr(piece),
+                                                        c_longlong(n), ext.stream_ptr(self.device)), "symm_all_gather")
+                nv._count()
+                rows[:, off:off + n].copy_(piece.view(self.world, n))
+        out = out.view(self.world, total)[:, :nbytes]
         if pad:
             out = out.contiguous()
         return out.view(t.dtype).view((self.world,) + tuple(t.shape))

@@ -137,16 +137,18 @@ def cmd_run(args) -> int:
 
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    spec = Qwen3DenseSpec.official() if args.official else Qwen3DenseSpec.scaled(
+        layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
     ctx = None
     if world > 1:
         import torch.distributed as dist
 
-        from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context
+        from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context, cp_frame_bytes_for
 
         dist.init_process_group("nccl", device_id=dev)
-        ctx = build_parallel_context(plan["tp"], plan["cp"], dev, dp=plan["dp"])
-    spec = Qwen3DenseSpec.official() if args.official else Qwen3DenseSpec.scaled(
-        layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+        tokens_per_rank = args.micro_batch * (args.prompt_len + args.response_len)
+        ctx = build_parallel_context(plan["tp"], plan["cp"], dev, dp=plan["dp"],
+                                     cp_frame_bytes=cp_frame_bytes_for(spec, plan["tp"], tokens_per_rank))
     cfg = GRPOConfig(num_prompts=args.prompts, group_size=args.group, prompt_len=args.prompt_len,
                      response_len=args.response_len, micro_batch_seqs=args.micro_batch * plan["cp"], lr=args.lr, seed=args.seed,
                      share_rollout_weights=args.official and world == 1)

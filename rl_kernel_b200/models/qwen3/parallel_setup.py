@@ -8,7 +8,16 @@ import torch
 from rl_kernel_b200.models.qwen3.engine import ParallelContext
 
 
-def build_parallel_context(tp: int, cp: int, device: torch.device, dp: int = 1) -> ParallelContext:
+def cp_frame_bytes_for(spec, tp: int, tokens_per_rank: int) -> int:
+    """Frame size for the context-parallel collective: the largest tensor the canonical weight-gradient
+    path gathers is one rank's gate/up gradient [tokens_per_rank, 2 * intermediate / tp] in bf16; a frame
+    that holds it lets the gather run as one kernel (larger payloads still work, in frame-sized pieces)."""
+    need = int(tokens_per_rank) * 2 * (spec.intermediate_size // max(1, tp)) * 2
+    return max(256 << 20, (need + (1 << 20) - 1) >> 20 << 20)
+
+
+def build_parallel_context(tp: int, cp: int, device: torch.device, dp: int = 1, *,
+                           cp_frame_bytes: int | None = None) -> ParallelContext:
     import torch.distributed as dist
 
     if tp * cp * dp == 1 or not dist.is_initialized():
@@ -37,7 +46,8 @@ def build_parallel_context(tp: int, cp: int, device: torch.device, dp: int = 1) 
             if c == cp_rank and t == tp_rank:
                 dp_group = g
     coll = create_deterministic_collective(tp_group, device) if tp > 1 else None
-    cp_coll = create_deterministic_collective(cp_group, device) if cp > 1 else None
+    cp_kw = {"frame_bytes": int(cp_frame_bytes)} if cp_frame_bytes else {}
+    cp_coll = create_deterministic_collective(cp_group, device, **cp_kw) if cp > 1 else None
     ctx = ParallelContext(tp_rank, tp, cp_rank, cp, coll, cp_coll)
     ctx.tp_group, ctx.cp_group, ctx.dp_group = tp_group, cp_group, dp_group
     if dp > 1:

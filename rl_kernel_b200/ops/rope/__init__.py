@@ -86,10 +86,15 @@ class _RopeFn(torch.autograd.Function):
         return nv.rope(dy, pos, cos, sin, torch.empty_like(dy), heads=heads, head_dim=d, inverse=True), None, None, None, None, None
 
 
-def rope(x: torch.Tensor, positions: torch.Tensor, *, theta: float = 1_000_000.0, out_fp32: bool = False) -> torch.Tensor:
+def rope(x: torch.Tensor, positions: torch.Tensor, *, theta: float = 1_000_000.0, out_fp32: bool = False,
+         max_position: int | None = None) -> torch.Tensor:
     """NeoX RoPE of ``x`` [..., S, D] at ``positions`` [S] or [B, S] (x then is [B, ..., S, D]); differentiable
     in ``x``.  Angles come from the shared fp32 table, the math is fp32 and the result is rounded once
-    (``out_fp32`` keeps it in fp32).  Parity: RoPESM90Op / NativeRoPEOp.forward(_fp32)."""
+    (``out_fp32`` keeps it in fp32).  ``max_position`` (an upper bound on the positions, exclusive) saves the
+    device-to-host read that sizes the table otherwise.  A head-major view of token-major storage
+    (``x.transpose(-3, -2)`` contiguous, the layout a QKV projection leaves) is rotated in place of a copy: the
+    kernel walks the token rows and the result has the strides of ``x``.
+    Parity: RoPESM90Op / NativeRoPEOp.forward(_fp32)."""
     D = x.shape[-1]
     S = x.shape[-2]
     pos = positions.to(x.device)
@@ -97,7 +102,7 @@ def rope(x: torch.Tensor, positions: torch.Tensor, *, theta: float = 1_000_000.0
         raise ValueError(f"positions {tuple(pos.shape)} do not match the sequence axis {S} of x")
     if pos.dim() == 2 and (x.dim() < 3 or x.shape[0] != pos.shape[0]):
         raise ValueError("positions [B, S] need x [B, ..., S, D]")
-    max_pos = int(pos.max().item()) + 1 if pos.numel() else 1
+    max_pos = int(max_position) if max_position is not None else (int(pos.max().item()) + 1 if pos.numel() else 1)
     cos, sin = _tables_for(D, theta, max_pos, x.device)
     if not use_native(x):
         xf = x.float()
@@ -110,12 +115,17 @@ def rope(x: torch.Tensor, positions: torch.Tensor, *, theta: float = 1_000_000.0
         y = torch.cat([a * c - b * s, b * c + a * s], dim=-1)
         return y if out_fp32 else y.to(x.dtype)
     xin = x.float() if (out_fp32 or x.dtype not in (torch.bfloat16, torch.float32)) else x
-    lead = xin.shape[:-1]                                  # [..., S]
-    if pos.dim() == 1:
-        prow = pos.to(torch.int32).expand(lead)
+    p32 = pos.to(torch.int32)
+    if xin.dim() >= 3 and xin.shape[-3] > 1 and not xin.is_contiguous() and xin.transpose(-3, -2).is_contiguous():
+        # [..., H, S, D] view of [..., S, H, D] storage: rows are tokens, the heads of a token are adjacent
+        xt = xin.transpose(-3, -2)
+        H, lead = xt.shape[-2], xt.shape[:-2]              # lead = [..., S]
+        prow = p32.expand(lead) if pos.dim() == 1 else p32.view(pos.shape[0], *([1] * (len(lead) - 2)), S).expand(lead)
+        y = _RopeFn.apply(xt.reshape(-1, H * D), prow.reshape(-1).contiguous(), cos, sin, H, D).view(xt.shape).transpose(-3, -2)
     else:
-        prow = pos.to(torch.int32).view(pos.shape[0], *([1] * (xin.dim() - 3)), S).expand(lead)
-    y = _RopeFn.apply(xin.reshape(-1, D).contiguous(), prow.reshape(-1).contiguous(), cos, sin, 1, D).view(xin.shape)
+        lead = xin.shape[:-1]                              # [..., S]
+        prow = p32.expand(lead) if pos.dim() == 1 else p32.view(pos.shape[0], *([1] * (xin.dim() - 3)), S).expand(lead)
+        y = _RopeFn.apply(xin.reshape(-1, D).contiguous(), prow.reshape(-1).contiguous(), cos, sin, 1, D).view(xin.shape)
     return y if (out_fp32 or y.dtype == x.dtype) else y.to(x.dtype)
 
 

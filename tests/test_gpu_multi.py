@@ -59,6 +59,13 @@ def _collective_worker(rank, world, port, out):
         if n % (8 * world) == 0:
             rs = coll.reduce_scatter(parts[rank])
             ok &= torch.equal(rs, want[rank * (n // world):(rank + 1) * (n // world)])
+    # an all-gather whose per-rank share is larger than a frame goes in frame-sized pieces
+    nbig = (64 << 20) // 2 + 8008
+    bigs = [torch.randn(nbig, device=dev, generator=torch.Generator(device="cuda").manual_seed(900 + r)).to(torch.bfloat16)
+            for r in range(world)]
+    agb = coll.all_gather(bigs[rank])
+    ok &= all(torch.equal(agb[r], bigs[r]) for r in range(world))
+    del agb, bigs
     # staged all-reduce: the producer writes straight into the symmetric frame
     x = torch.full((256, 128), float(rank + 1), device=dev, dtype=torch.bfloat16)
     st = coll.staging_view(x.shape, x.dtype)

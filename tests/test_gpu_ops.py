@@ -105,12 +105,13 @@ def test_qk_norm_rope_forward_backward():
     assert (dkw.float() - kwf.grad).abs().max().item() < 0.01 * kwf.grad.abs().max().item() + 0.05
 
 
-@pytest.mark.parametrize("blk", [None, 192])
-def test_swiglu(blk):
+@pytest.mark.parametrize("rows,I,blk", [(100, 1536, None), (100, 1536, 192), (37, 4096, 512), (101, 256, None),
+                                        (300, 12288, 1536), (5, 40, 8)])
+def test_swiglu(rows, I, blk):
+    """Row widths on both sides of the 256-piece boundary of the launch grid, rows that do not fill a block."""
     from rl_kernel_b200.backends import native as nv
     from rl_kernel_b200.reference.activation.swiglu import swiglu_packed_reference
 
-    rows, I = 100, 1536
     gu = torch.randn(rows, 2 * I, device=dev()).to(BF)
     out = torch.empty(rows, I, device=dev(), dtype=BF)
     nv.swiglu_fwd(gu, out, I, blk)
@@ -123,6 +124,70 @@ def test_swiglu(blk):
     g = gu.float().requires_grad_(True)
     swiglu_packed_reference(g, blk).backward(dout.float())
     assert (dgu.float() - g.grad).abs().max().item() < 0.05
+
+
+@pytest.mark.parametrize("heads,D,dtype", [(32, 128, BF), (8, 128, BF), (1, 128, BF), (3, 64, torch.float32),
+                                           (2, 20, BF), (5, 24, torch.float32), (40, 128, BF)])
+def test_rope_standalone_matches_fp32_expression_bitwise(heads, D, dtype):
+    """Vector path (half head a multiple of 16 bytes) and scalar path, in place and out of place, strided rows,
+    forward and inverse: the bits of a*c - b*s / b*c + a*s in fp32 with one rounding."""
+    from rl_kernel_b200.backends import native as nv
+
+    g = torch.Generator(device="cuda").manual_seed(heads * 1000 + D)
+    rows, max_pos, half = 333, 700, D // 2
+    ang = torch.rand(max_pos, half, device=dev(), generator=g) * 6.28
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.randint(0, max_pos, (rows,), device=dev(), generator=g).to(torch.int32)
+    wide = torch.randn(rows, heads * D + 16, device=dev(), generator=g).to(dtype)
+    x = wide[:, :heads * D]                                   # row stride larger than the row
+    xf = x.float().view(rows, heads, D)
+    c, s_ = cos[pos.long()][:, None, :], sin[pos.long()][:, None, :]
+    a, b = xf[..., :half], xf[..., half:]
+    for inverse in (False, True):
+        sg = -s_ if inverse else s_
+        want = torch.cat([a * c - b * sg, b * c + a * sg], dim=-1).reshape(rows, heads * D).to(dtype)
+        out = torch.empty(rows, heads * D, device=dev(), dtype=dtype)
+        nv.rope(x, pos, cos, sin, out, heads=heads, head_dim=D, inverse=inverse)
+        sync_and_check()
+        assert torch.equal(out, want)
+        inplace = wide.clone()[:, :heads * D]
+        nv.rope(inplace, pos, cos, sin, inplace, heads=heads, head_dim=D, inverse=inverse)
+        sync_and_check()
+        assert torch.equal(inplace, want)
+
+
+def test_rope_op_head_major_view_is_rotated_without_a_copy_and_split_swiglu_matches_packed():
+    from rl_kernel_b200.ops.activation import swiglu, swiglu_packed
+    from rl_kernel_b200.ops.rope import rope
+
+    g = torch.Generator(device="cuda").manual_seed(11)
+    S, H, D = 77, 6, 128
+    store = torch.randn(2, S, H, D, device=dev(), generator=g).to(BF)
+    pos = torch.stack([torch.arange(S), torch.arange(9, 9 + S)]).to(dev())
+    for xs, ps in ((store[0], pos[0]), (store, pos), (store, pos[1])):
+        xv = xs.transpose(-3, -2).requires_grad_(True)                    # [.., H, S, D] over token-major storage
+        y = rope(xv, ps, max_position=4096)
+        sync_and_check()
+        xc = xs.transpose(-3, -2).contiguous().requires_grad_(True)
+        yc = rope(xc, ps)
+        assert y.shape == xv.shape and y.stride() == xv.stride() and torch.equal(y, yc)
+        gy = torch.randn(y.shape, device=dev(), generator=g).to(BF)
+        y.backward(gy)
+        yc.backward(gy)
+        assert torch.equal(xv.grad, xc.grad)
+    rows, I = 130, 1024
+    wide = torch.randn(rows, 2 * I + 8, device=dev(), generator=g).to(BF)
+    gate, up = wide[:, :I].detach().requires_grad_(True), wide[:, I:2 * I].detach().requires_grad_(True)   # strided rows
+    out = swiglu(gate, up)
+    sync_and_check()
+    gu = torch.cat([gate.detach(), up.detach()], -1).requires_grad_(True)
+    want = swiglu_packed(gu)
+    assert torch.equal(out, want)
+    go = torch.randn(rows, I, device=dev(), generator=g).to(BF)
+    out.backward(go)
+    want.backward(go)
+    assert torch.equal(gate.grad, gu.grad[:, :I]) and torch.equal(up.grad, gu.grad[:, I:])
+    assert torch.equal(swiglu(gate.detach().view(10, 13, I), up.detach().view(10, 13, I)), want.detach().view(10, 13, I))
 
 
 def test_embedding():
@@ -192,6 +257,27 @@ def test_logp_fused_equals_from_logits_and_vocab_parallel(temp):
     z = (logits.float() / temp).requires_grad_(True)
     (torch.log_softmax(z, -1).gather(1, tg[:, None])[:, 0] * g).sum().backward()
     assert (lc.float() - z.grad / temp).abs().max().item() < 0.02
+
+
+def test_logp_from_logits_wide_vocabulary_strided_rows_and_row_subsets():
+    """More than 128 vocabulary tiles (several tile groups per row), a ragged last tile, a row pitch wider than
+    the vocabulary: matches log_softmax and does not depend on which rows share the launch."""
+    from rl_kernel_b200.ops.logprob import logp_from_logits, logp_from_logits_indexed
+
+    g = torch.Generator(device="cuda").manual_seed(5)
+    T, V = 37, 20008
+    wide = (torch.randn(T, V + 24, device=dev(), generator=g) * 3).to(BF)
+    logits = wide[:, :V]
+    tg = torch.randint(0, V, (T,), device=dev(), generator=g)
+    tg[0], tg[1] = V - 1, 0
+    lp = logp_from_logits(logits, tg, 0.7)
+    sync_and_check()
+    ref = torch.log_softmax(logits.float() / 0.7, -1).gather(1, tg[:, None])[:, 0]
+    assert (lp - ref).abs().max().item() < 2e-4
+    assert torch.equal(logp_from_logits(logits[5:6], tg[5:6], 0.7), lp[5:6])
+    assert torch.equal(logp_from_logits(logits.contiguous(), tg, 0.7), lp)
+    idx = torch.tensor([36, 0, 17], device=dev())
+    assert torch.equal(logp_from_logits_indexed(logits.contiguous(), tg[idx], idx, temperature=0.7), lp[idx])
 
 
 def test_grpo_loss_and_advantages():
