@@ -1153,6 +1153,11 @@ RLK_API int rlk_det_gemm_split(const void* A, const void* B, void* C, void* scra
   return RLK_OK;
 }
 
+// 1: the fused all-reduce / reduce-scatter entries may use 128 x 256 tiles (0 keeps them on 128 x 128).  Every rank
+// of a group must use the same value (the tile numbering is part of the flag protocol).
+static int g_ar_wide_tiles = 1;
+RLK_API int rlk_det_gemm_ar_set_wide_tiles(int on) { g_ar_wide_tiles = on ? 1 : 0; return RLK_OK; }
+
 // GEMM + fixed-order all-reduce in ONE kernel (row-parallel projections: o_proj, FFN down):
 // out = all_reduce_tree_over_ranks( A_local @ B_local^T with nchunks canonical K chunks ).
 // `state` is the rlk_symm_create handle of the tensor-parallel group; every rank calls this with
@@ -1192,6 +1197,16 @@ RLK_API int rlk_det_gemm_ar(void* state, const void* A, const void* B, void* out
   p.ar_use_epoch = st->w.use_epoch;
   p.ar_out = static_cast<__nv_bfloat16*>(out);
   p.ar_ld_out = ld_out;
+  // many tiles: 128 x 256 tiles (the faster chunk-tree kernel, tree stack in the L2-resident scratch), as rlk_det_gemm
+  // picks them; few tiles: 128 x 128.  All ranks see the same shape, so they number the tiles alike.
+  const long long tiles256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
+  if (g_ar_wide_tiles && tiles256 >= sm_count() && (nchunks == 1 || K / nchunks >= 768)) {
+    if (nchunks > 1) {
+      p.tree_scratch = tree_scratch_for_device();
+      if (!p.tree_scratch) return set_error(RLK_ERR_CUDA, "det_gemm_ar: cannot allocate the tree scratch");
+    }
+    return launch_gemm<256, false, false, true>(A, B, p, lda, ldb, static_cast<cudaStream_t>(stream));
+  }
   return launch_gemm<128, false, false, true>(A, B, p, lda, ldb, static_cast<cudaStream_t>(stream));
 }
 
@@ -1240,6 +1255,16 @@ RLK_API int rlk_det_gemm_rs(void* state, const void* A, const void* B, void* out
   // only rows [rs_row0, rs_row1) are ever written: bias the base so that they land on the caller's rows 0..rows-1
   p.ar_out = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<uintptr_t>(out) - static_cast<uintptr_t>(2ll * p.rs_row0 * ld_out));
   p.ar_ld_out = ld_out;
+  // many tiles: 128 x 256 tiles (the faster chunk-tree kernel, tree stack in the L2-resident scratch), as rlk_det_gemm
+  // picks them; few tiles: 128 x 128.  All ranks see the same shape, so they number the tiles alike.
+  const long long tiles256 = static_cast<long long>((M + 127) / 128) * ((N + 255) / 256);
+  if (g_ar_wide_tiles && tiles256 >= sm_count() && (nchunks == 1 || K / nchunks >= 768)) {
+    if (nchunks > 1) {
+      p.tree_scratch = tree_scratch_for_device();
+      if (!p.tree_scratch) return set_error(RLK_ERR_CUDA, "det_gemm_ar: cannot allocate the tree scratch");
+    }
+    return launch_gemm<256, false, false, true>(A, B, p, lda, ldb, static_cast<cudaStream_t>(stream));
+  }
   return launch_gemm<128, false, false, true>(A, B, p, lda, ldb, static_cast<cudaStream_t>(stream));
 }
 

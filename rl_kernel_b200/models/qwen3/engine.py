@@ -942,7 +942,9 @@ class Qwen3Engine:
         keep = None if min_keep is None else min_keep.reshape(-1).float().contiguous()
         # ---- this rank's vocabulary slice of the TP shard
         if self.p.v_local % (cp * VOCAB_TILE) or self.nchunks % cp:
-            raise ValueError("the padded vocabulary shard must split into cp slices of whole 128-id tiles and chunks")
+            raise ValueError(f"canonical context-parallel LM head: the vocabulary shard ({self.p.v_local} ids, "
+                             f"{self.nchunks} canonical chunks on this tensor-parallel rank) must split into cp = {cp} "
+                             "slices of whole 128-id tiles and whole chunks (tp x cp <= canonical_tp)")
         vs = self.p.v_local // cp
         v0 = c * vs
         vreal = max(0, min(vs, self.p.v_real_local - v0))

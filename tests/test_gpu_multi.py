@@ -75,7 +75,9 @@ def _collective_worker(rank, world, port, out):
     # fused GEMM + all-reduce == local GEMM followed by the tree all-reduce, bit for bit
     from rl_kernel_b200.backends import native as nv
 
-    for (M, N, K, nch) in [(700, 512, 1024, 4), (1536, 1024, 512, 1), (128, 256, 512, 8)]:
+    # (the last three have enough tiles for the 128 x 256 form of the fused kernel: chunked, plain, ragged edges)
+    for (M, N, K, nch) in [(700, 512, 1024, 4), (1536, 1024, 512, 1), (128, 256, 512, 8), (12288, 1024, 3072, 4),
+                           (10000, 512, 256, 1), (9999 // 8 * 8, 1000, 1536, 2)]:
         g = torch.Generator(device="cuda").manual_seed(7 + rank)
         a = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
         b = torch.randn(N, K, device=dev, generator=g).to(torch.bfloat16)
@@ -234,6 +236,15 @@ def test_tensor_parallel_step_matches_single_gpu_bitwise(tmp_path, world):
         assert torch.equal(_assemble([r["weights"] for r in tp], name), tr.policy.w[name].cpu()), f"updated {name}"
 
 
+def _cp_spec(world):
+    """The LM head is split over the context-parallel ranks by canonical chunk, so the model needs at least
+    ``world`` canonical shards (one per KV head here); four query heads per KV head as in Qwen3-8B."""
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec
+
+    kv = max(2, world)
+    return Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=4 * kv, kv_heads=kv, head_dim=128, vocab=4096)
+
+
 def _cp_cfg(world):
     from rl_kernel_b200.models.qwen3.grpo import GRPOConfig
 
@@ -250,7 +261,7 @@ def _cp_train_worker(rank, world, port, out):
     from rl_kernel_b200.models.qwen3.parallel_setup import build_parallel_context
 
     dev = torch.device("cuda", rank)
-    spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+    spec = _cp_spec(world)
     w = Qwen3DenseWeights.synthetic(spec, seed=3)
     ctx = build_parallel_context(1, world, dev)
     cfg = _cp_cfg(world)
@@ -282,7 +293,7 @@ def test_context_parallel_training_matches_single_gpu(tmp_path, world):
     mp.spawn(_cp_train_worker, args=(world, _free_port(), out), nprocs=world, join=True)
     cp = torch.load(out)
     dev = torch.device("cuda:0")
-    spec = Qwen3DenseSpec.scaled(layers=2, hidden=1024, ffn=2048, q_heads=8, kv_heads=2, head_dim=128, vocab=4096)
+    spec = _cp_spec(world)
     w = Qwen3DenseWeights.synthetic(spec, seed=3)
     cfg = _cp_cfg(world)
     tr = GRPOTrainer(spec, cfg, dev, weights=w)
@@ -787,6 +798,18 @@ def _gemm_rs_worker(rank, world, port, out):
     for _ in range(3):                                                   # repeated calls walk both frames
         rs = coll.gemm_reduce_scatter(a, w, torch.empty(M // world, N, device=dev, dtype=torch.bfloat16), nchunks)
         ok &= torch.equal(rs, full[rows])
+    # enough tiles for the 128 x 256 form of the fused kernel: still the unfused bits, row slice included
+    from rl_kernel_b200.backends import native as nv
+
+    Mw, Kw = 12288, 1536
+    aw = torch.randn(Mw, Kw, device=dev, generator=g).bfloat16()
+    ww = (torch.randn(N, Kw, device=dev, generator=g) * 0.05).bfloat16()
+    part = torch.empty(Mw, N, device=dev, dtype=torch.bfloat16)
+    nv.det_gemm(aw, ww, part, M=Mw, N=N, K=Kw, nchunks=2)
+    unfused = coll.all_reduce(part)
+    fullw = coll.gemm_all_reduce(aw, ww, torch.empty(Mw, N, device=dev, dtype=torch.bfloat16), 2)
+    rsw = coll.gemm_reduce_scatter(aw, ww, torch.empty(Mw // world, N, device=dev, dtype=torch.bfloat16), 2)
+    ok &= torch.equal(fullw, unfused) and torch.equal(rsw, unfused[rank * Mw // world:(rank + 1) * Mw // world])
     a1, w1 = a.clone().requires_grad_(True), w.clone().requires_grad_(True)
     a2, w2 = a.clone().requires_grad_(True), w.clone().requires_grad_(True)
     y1 = sp_row_parallel_linear(a1, w1, nchunks, coll, fused=True)
