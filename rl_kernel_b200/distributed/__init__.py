@@ -4,5 +4,5 @@
 (rl_engine/distributed/__init__.py:4-16).
 """
 from rl_kernel_b200.distributed.algorithms.collectives import (  # noqa: F401
-    CollectiveTimeout, TorchDistributedDeterministicCollective, balanced_tree_sum, collective_for_group,
+    CollectiveMismatchError, CollectiveTimeout, TorchDistributedDeterministicCollective, balanced_tree_sum, collective_for_group,
     create_deterministic_collective)

@@ -24,6 +24,11 @@ class CollectiveTimeout(RuntimeError):
     """A peer did not arrive within the bounded wait; the context stays usable."""
 
 
+class CollectiveMismatchError(ValueError):
+    """The ranks of a group presented different operations, shapes or dtypes for the same collective call.
+    Raised on every rank by the host-side check, before anything is launched."""
+
+
 def balanced_tree_sum(parts: Sequence[torch.Tensor], dtype: torch.dtype | None = None) -> torch.Tensor:
     """Balanced binary tree over a power-of-two number of equally shaped tensors."""
     n = len(parts)
@@ -67,7 +72,7 @@ class TorchDistributedDeterministicCollective:
         sigs = [None] * self.world
         self._dist.all_gather_object(sigs, key, group=self.group)
         if any(s != sigs[0] for s in sigs):
-            raise ValueError(f"collective signature mismatch across ranks for {op}: {sigs}")
+            raise CollectiveMismatchError(f"collective signature mismatch across ranks for {op}: {sigs}")
         self._checked.add(key)
 
     def all_gather(self, t: torch.Tensor) -> torch.Tensor:

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import contextlib
 import ctypes
+import os
 import socket
 from ctypes import c_int, c_longlong, c_void_p
 
@@ -18,7 +19,7 @@ import torch
 
 from rl_kernel_b200.backends import extension as ext
 from rl_kernel_b200.backends import native as nv
-from rl_kernel_b200.distributed.algorithms.collectives import CollectiveTimeout
+from rl_kernel_b200.distributed.algorithms.collectives import CollectiveMismatchError, CollectiveTimeout
 
 _DT = {torch.bfloat16: 0, torch.float32: 1}
 
@@ -46,6 +47,11 @@ class SymmetricMemoryCollective:
         self._lib.rlk_symm_graph_end.restype = c_longlong
         self._state = c_void_p(0)
         self._closed = False
+        # Debug aid (``RLK_SYMM_VERIFY=1`` or ``verify_signatures = True`` on every rank): before each call the ranks
+        # compare (operation, shapes, dtype, call number) on the host and all raise CollectiveMismatchError when
+        # they differ -- before any kernel is launched, so nobody is left waiting for a peer that will not come.
+        self.verify_signatures = os.environ.get("RLK_SYMM_VERIFY", "0") not in ("", "0")
+        self._calls = 0
         if self.world == 1:
             return
         with torch.cuda.device(self.device):
@@ -68,6 +74,17 @@ class SymmetricMemoryCollective:
             dist.barrier(group=group)
 
     # ------------------------------------------------------------------ helpers
+    def _verify(self, op: str, *tensors: torch.Tensor, extra=()) -> None:
+        """Host-side cross-rank comparison of the call (see ``verify_signatures``); skipped during graph capture."""
+        self._calls += 1
+        if not self.verify_signatures or self.world == 1 or torch.cuda.is_current_stream_capturing():
+            return
+        mine = (op, tuple((tuple(t.shape), str(t.dtype)) for t in tensors), tuple(extra), self._calls)
+        sigs = [None] * self.world
+        self._dist.all_gather_object(sigs, mine, group=self.group)
+        if any(s != sigs[0] for s in sigs):
+            raise CollectiveMismatchError(f"ranks disagree on collective call {self._calls}: {sigs}")
+
     def _check_open(self):
         if self._closed:
             raise RuntimeError("collective is closed")
@@ -102,6 +119,7 @@ class SymmetricMemoryCollective:
         nbytes = t.numel() * t.element_size()
         if nbytes % 16:
             raise ValueError("all_reduce_: byte size must be a multiple of 16")
+        self._verify("all_reduce", t)
         base = t.data_ptr()
         for off in range(0, nbytes, self.frame_bytes):       # larger than a frame: frame-sized pieces
             n = min(self.frame_bytes, nbytes - off)
@@ -128,6 +146,7 @@ class SymmetricMemoryCollective:
         ONE kernel: tiles are exchanged over NVLink from inside the GEMM epilogue while later tiles
         are still being multiplied (csrc/gemm/det_gemm_sm100.cu, rlk_det_gemm_ar)."""
         self._check_open()
+        self._verify("gemm_all_reduce", a, b, out, extra=(nchunks,))
         M, K = a.shape
         N = b.shape[0]
         ext.check(self._lib.rlk_det_gemm_ar(self._state, ext.ptr(a), ext.ptr(b), ext.ptr(out), c_int(M), c_int(N),
@@ -146,6 +165,7 @@ class SymmetricMemoryCollective:
         N = b.shape[0]
         if out.shape[0] * self.world != M or out.shape[1] != N:
             raise ValueError(f"out must be [{M // self.world}, {N}], got {tuple(out.shape)}")
+        self._verify("gemm_reduce_scatter", a, b, out, extra=(nchunks,))
         ext.check(self._lib.rlk_det_gemm_rs(self._state, ext.ptr(a), ext.ptr(b), ext.ptr(out), c_int(M), c_int(N),
                                             c_int(K), c_longlong(a.stride(0)), c_longlong(b.stride(0)),
                                             c_longlong(out.stride(0)), c_int(nchunks), ext.stream_ptr(self.device)),
@@ -165,6 +185,7 @@ class SymmetricMemoryCollective:
         if self.world == 1:
             return t.unsqueeze(0)
         self._check_open()
+        self._verify("all_gather", t)
         t = t.contiguous()
         nbytes = t.numel() * t.element_size()
         pad = (-nbytes) % 16
@@ -205,6 +226,8 @@ class SymmetricMemoryCollective:
         n = t.shape[0] // self.world
         t = t.contiguous()
         per = t.numel() // self.world * t.element_size()
+        if not (t.dtype not in _DT or t.shape[0] % self.world or per % 16 or per * self.world > self.frame_bytes):
+            self._verify("reduce_scatter", t)
         if t.dtype not in _DT or t.shape[0] % self.world or per % 16 or per * self.world > self.frame_bytes:
             return self.all_reduce(t)[self.rank * n:(self.rank + 1) * n].contiguous()
         out = torch.empty((n,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)

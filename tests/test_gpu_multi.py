@@ -66,6 +66,32 @@ def _collective_worker(rank, world, port, out):
     agb = coll.all_gather(bigs[rank])
     ok &= all(torch.equal(agb[r], bigs[r]) for r in range(world))
     del agb, bigs
+    # negative cases of the protocol: each is refused on the host of EVERY rank before a kernel is launched, and the
+    # group keeps working afterwards
+    from rl_kernel_b200.distributed import CollectiveMismatchError
+
+    big_a = torch.zeros(128, 64, device=dev, dtype=torch.bfloat16)
+    try:                                                    # output larger than a frame (64 MiB here)
+        coll.gemm_all_reduce(torch.zeros(16384, 64, device=dev, dtype=torch.bfloat16),
+                             torch.zeros(4096, 64, device=dev, dtype=torch.bfloat16),
+                             torch.empty(16384, 4096, device=dev, dtype=torch.bfloat16), 1)
+        ok = False
+    except ext.NativeLibraryError as exc:
+        ok &= "frame capacity" in str(exc)
+    try:                                                    # rows that do not split into whole tiles per rank
+        coll.gemm_reduce_scatter(big_a, big_a, torch.empty(128 // world, 128, device=dev, dtype=torch.bfloat16), 1)
+        ok = False
+    except ext.NativeLibraryError as exc:
+        ok &= "multiple of 128 x world" in str(exc)
+    coll.verify_signatures = True
+    try:                                                    # ranks disagree on the size of an all-reduce
+        coll.all_reduce(torch.ones(1024 * (1 + rank), device=dev))
+        ok = False
+    except CollectiveMismatchError:
+        pass
+    ok &= bool(torch.equal(coll.all_reduce(torch.ones(1024, device=dev)), torch.full((1024,), float(world), device=dev)))
+    coll.verify_signatures = False
+    ok &= ext.poll_status(dev) == 0
     # staged all-reduce: the producer writes straight into the symmetric frame
     x = torch.full((256, 128), float(rank + 1), device=dev, dtype=torch.bfloat16)
     st = coll.staging_view(x.shape, x.dtype)
