@@ -107,6 +107,16 @@ def sp_row_parallel_linear(x: torch.Tensor, w: torch.Tensor, nchunks: int, colle
     return _SPReduceScatter.apply(det_gemm_linear(x, w, nchunks), collective)
 
 
+# Identity of the projections around attention, as reported to the rollout / training binding.
+PROJECTION_POLICY_ID = "rl_kernel_b200.attention_projection.canonical_k_chunk_tree.v1"
+DETERMINISTIC_PROJECTION_BACKEND_ID = "rl_kernel_b200.det_gemm.tcgen05"
+REFERENCE_PROJECTION_BACKEND_ID = "rl_kernel_b200.reference.det_gemm"
+QKV_COLLECTIVE_CONTRACT = {"tp_forward": "none", "tp_backward_dgrad": "fixed_tree_all_reduce", "sp_forward": "rank_order_all_gather",
+                           "sp_backward": "fixed_tree_reduce_scatter"}
+O_PROJ_COLLECTIVE_CONTRACT = {"tp_forward": "fixed_tree_all_reduce", "tp_backward_dgrad": "none",
+                              "sp_forward": "fixed_tree_reduce_scatter", "sp_backward": "rank_order_all_gather"}
+
+
 class AttentionProjectionOp:
     """``sequence_parallel``: activations outside the projections are sharded by token rows over the TP group
     (all-gather before the QKV GEMM, reduce-scatter after the output GEMM; parity: the SP branches of
@@ -130,3 +140,14 @@ class AttentionProjectionOp:
         if self.sequence_parallel:
             return sp_row_parallel_linear(attn_local.reshape(-1, attn_local.shape[-1]), w_o_local, self.nchunks, self.collective)
         return _TPAllReduce.apply(det_gemm_linear(attn_local, w_o_local, self.nchunks), self.collective)
+
+    def runtime_readback(self, *, device_type: str = "cuda") -> dict:
+        """Plans of the two projections (name -> facts) for the rollout / training binding."""
+        backend = DETERMINISTIC_PROJECTION_BACKEND_ID if device_type == "cuda" else REFERENCE_PROJECTION_BACKEND_ID
+        mode = "sp" if self.sequence_parallel else "tp"
+        tp = 1 if self.collective is None else int(getattr(self.collective, "world", 1))
+        common = {"backend": backend, "policy_id": PROJECTION_POLICY_ID, "fallback": False, "split_k": False, "k_order": "ascending",
+                  "acc_dtype": "fp32", "tp_world_size": tp, "sequence_parallel": self.sequence_parallel}
+        return {"qkv": {**common, "canonical_k_chunks": 1, "forward_collective": QKV_COLLECTIVE_CONTRACT[f"{mode}_forward"] if tp > 1 else "none"},
+                "o_proj": {**common, "canonical_k_chunks": self.nchunks * tp, "local_k_chunks": self.nchunks,
+                           "forward_collective": O_PROJ_COLLECTIVE_CONTRACT[f"{mode}_forward"] if tp > 1 else "none"}}
