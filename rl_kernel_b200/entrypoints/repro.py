@@ -54,6 +54,29 @@ def cmd_doctor(args) -> int:
     return 0 if ok else 1
 
 
+def cmd_ops(args) -> int:
+    """Every operator of the registry with its candidate backends in resolution order (``--json`` for machines)."""
+    from rl_kernel_b200.runtime.registry import kernel_registry
+
+    table = kernel_registry.describe()
+    if args.op:
+        unknown = [o for o in args.op if o not in table]
+        if unknown:
+            print(f"unknown operator(s): {unknown}; known: {sorted(table)}", file=sys.stderr)
+            return 2
+        table = {o: table[o] for o in args.op}
+    if args.json:
+        print(json.dumps(table, indent=1))
+        return 0
+    for op, cands in table.items():
+        print(op)
+        for c in cands:
+            mark = "*" if c is next((x for x in cands if x["usable"]), None) else " "
+            print(f"  {mark} {c['id']:<12} {c['kind']:<10} {'usable' if c['usable'] else 'skipped: ' + c['reason']}")
+            print(f"      {c['path']}")
+    return 0
+
+
 def cmd_prepare(args) -> int:
     prof = {"python": sys.executable, "created": time.time(), "gpus": args.gpus, "run_root": str(Path(args.run_root).resolve())}
     Path(args.profile).write_text(json.dumps(prof, indent=1))
@@ -325,6 +348,10 @@ def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="rlk", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
     sub.add_parser("doctor").set_defaults(fn=cmd_doctor)
+    p = sub.add_parser("ops", help="list operators and the backend each would resolve to on this machine")
+    p.add_argument("op", nargs="*")
+    p.add_argument("--json", action="store_true")
+    p.set_defaults(fn=cmd_ops)
     p = sub.add_parser("prepare")
     p.add_argument("--profile", default=PROFILE_NAME)
     p.add_argument("--gpus", type=int, default=1)
