@@ -23,7 +23,10 @@ from typing import Optional, Sequence
 
 import torch
 
-from rl_kernel_b200.contracts.operators.attention import SplitKVSpec
+import math
+
+from rl_kernel_b200.contracts.operators.attention import (SplitKVExecutionPlan, SplitKVMode, SplitKVRuntimeCoordinate,
+                                                          SplitKVRuntimePlanEntry, SplitKVRuntimePlanSet, SplitKVSpec)
 from rl_kernel_b200.reference.attention.blockwise import (BLOCK, DeterministicCPAttentionReferenceOp as _StrictCPOp,
                                                           blockwise_attention_reference, merge_two_states, zigzag_chunks)
 
@@ -263,7 +266,226 @@ def compare_cp_attention_backward(q, k, v, dout, *, cp_world_size: int, layout: 
     return AttentionBackwardComparisonReport(cp_world_size, layout, _drift(many.dq, one.dq), _drift(many.dk, one.dk), _drift(many.dv, one.dv), ranks)
 
 
-__all__ = ["AttentionBackwardComparisonReport", "AttentionBackwardGradients", "AttentionBackwardRankDrift", "AttentionPartialState",
-           "AttentionRingBlock", "AttentionRingSchedule", "DeterministicAttentionCore", "DeterministicAttentionCoreResult",
-           "DeterministicCPAttentionReferenceOp", "GradientDriftStats", "compare_cp_attention_backward",
-           "merge_attention_partial_states"]
+
+# ------------------------------------------------------------------------------------------------ saved forward state
+STRICT_ATTENTION_CORE_ID = DeterministicAttentionCore.core_id
+STRICT_ATTENTION_SCHEDULE_ID = "ascending_128_key_blocks.per_row_products.v1"
+
+
+def _tensor_fingerprint(t: torch.Tensor) -> str:
+    return hashlib.sha256(t.detach().contiguous().cpu().view(torch.uint8).numpy().tobytes()).hexdigest()
+
+
+@dataclass(frozen=True)
+class AttentionSavedForwardState:
+    """What a training forward keeps for its backward: the fp32 output and log-sum-exp of every query row, the geometry
+    they were computed under, and digests of the operands, so that a backward fed other tensors (a stale K/V after a
+    cache write, a different sharding) is refused instead of producing plausible numbers."""
+    out: torch.Tensor                       # [S, Hq, D] fp32
+    lse: torch.Tensor                       # [S, Hq] fp32
+    scale: float
+    cp_world_size: int
+    layout: str
+    kv_chunk_size: Optional[int]
+    query_positions: tuple[tuple[int, ...], ...]      # per rank, the logical positions of its query rows
+    q_shape: tuple[int, ...]
+    k_shape: tuple[int, ...]
+    v_shape: tuple[int, ...]
+    q_dtype: torch.dtype
+    k_dtype: torch.dtype
+    v_dtype: torch.dtype
+    q_fingerprint: str
+    k_fingerprint: str
+    v_fingerprint: str
+    out_fingerprint: str
+    lse_fingerprint: str
+    strict_bitwise: bool
+    strict_schedule: Optional[str]
+
+    def __post_init__(self) -> None:
+        if self.out.dtype is not torch.float32 or self.lse.dtype is not torch.float32:
+            raise ValueError("saved attention out/lse must be FP32")
+        if self.out.ndim != 3 or self.lse.shape != self.out.shape[:2]:
+            raise ValueError("saved attention out [S, H, D] / lse [S, H] shapes are invalid")
+        if not math.isfinite(self.scale) or self.scale <= 0:
+            raise ValueError("saved attention scale must be positive and finite")
+        if self.strict_schedule != (STRICT_ATTENTION_SCHEDULE_ID if self.strict_bitwise else None):
+            raise ValueError("saved attention strict schedule does not match strict_bitwise")
+        if self.kv_chunk_size is not None and self.kv_chunk_size < 1:
+            raise ValueError("kv_chunk_size must be >= 1 when provided")
+
+    def validate_operands(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
+        for name, t, shape, dtype, fp in (("q", q, self.q_shape, self.q_dtype, self.q_fingerprint), ("k", k, self.k_shape, self.k_dtype, self.k_fingerprint),
+                                          ("v", v, self.v_shape, self.v_dtype, self.v_fingerprint)):
+            if tuple(t.shape) != shape or t.dtype != dtype:
+                raise ValueError(f"backward operand {name} is {tuple(t.shape)} {t.dtype}; the forward saw {shape} {dtype}")
+            if _tensor_fingerprint(t) != fp:
+                raise ValueError(f"backward operand {name} differs from the tensor the forward state was saved for")
+        if _tensor_fingerprint(self.out) != self.out_fingerprint or _tensor_fingerprint(self.lse) != self.lse_fingerprint:
+            raise ValueError("the saved out / lse were modified after the forward")
+
+
+@dataclass(frozen=True)
+class AttentionBackwardPathResult:
+    """One materialised backward path (a CP degree and an optional KV chunking) with the state it started from."""
+    name: str
+    out: torch.Tensor
+    lse: torch.Tensor
+    gradients: AttentionBackwardGradients
+    saved_forward_state: AttentionSavedForwardState
+    provenance: dict
+
+
+@dataclass(frozen=True)
+class AttentionBackwardPathDrift:
+    candidate_name: str
+    reference_name: str
+    out: GradientDriftStats
+    lse: GradientDriftStats
+    dq: GradientDriftStats
+    dk: GradientDriftStats
+    dv: GradientDriftStats
+    ranks: tuple[AttentionBackwardRankDrift, ...]
+
+    def to_dict(self) -> dict[str, object]:
+        return {"candidate": self.candidate_name, "reference": self.reference_name, "out": self.out.to_dict(), "lse": self.lse.to_dict(),
+                "dq": self.dq.to_dict(), "dk": self.dk.to_dict(), "dv": self.dv.to_dict(), "ranks": [r.to_dict() for r in self.ranks]}
+
+
+def backward_path_name(*, cp_world_size: int, kv_chunk_size: Optional[int]) -> str:
+    return f"cp{cp_world_size}" + ("" if kv_chunk_size is None else f"_kvchunk{kv_chunk_size}") + "_backward_reference"
+
+
+def save_forward_state(op: DeterministicCPAttentionReferenceOp, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *,
+                       kv_chunk_size: Optional[int] = None) -> AttentionSavedForwardState:
+    """Run ``op``'s forward in fp32 and keep what the explicit backward needs."""
+    S, D = q.shape[0], q.shape[-1]
+    out, lse = op.forward_with_lse(q.float(), k.float(), v.float())
+    out, lse = out.float().contiguous(), lse.float().contiguous()
+    scale = op.scale if op.scale is not None else 1.0 / math.sqrt(D)
+    return AttentionSavedForwardState(
+        out, lse, float(scale), op.cp, op.layout, kv_chunk_size, tuple(tuple(int(x) for x in p.tolist()) for p in op.shard_positions(S)),
+        tuple(q.shape), tuple(k.shape), tuple(v.shape), q.dtype, k.dtype, v.dtype, _tensor_fingerprint(q), _tensor_fingerprint(k),
+        _tensor_fingerprint(v), _tensor_fingerprint(out), _tensor_fingerprint(lse), op.strict_bitwise,
+        STRICT_ATTENTION_SCHEDULE_ID if op.strict_bitwise else None)
+
+
+def backward_from_saved_state(state: AttentionSavedForwardState, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                              dout: torch.Tensor) -> AttentionBackwardGradients:
+    """The attention backward written out (no autograd), from the saved log-sum-exp:
+
+        P = exp(scale * Q K^T - lse),  delta = rowsum(dO * O),  dV += P^T dO,  dS = P * (dO V^T - delta),
+        dQ += scale * dS K,  dK += scale * dS^T Q
+
+    evaluated rank by rank over that rank's query rows and, within a rank, over key chunks of ``kv_chunk_size`` in
+    ascending order; dK / dV accumulate in (rank, chunk) order, a fixed order for every run.  Causality is by logical
+    position, so any layout gives the gradients of the same function."""
+    state.validate_operands(q, k, v)
+    if tuple(dout.shape) != tuple(state.out.shape):
+        raise ValueError(f"dout must have the output shape {tuple(state.out.shape)}, got {tuple(dout.shape)}")
+    S, Hq, D = q.shape
+    Hkv = k.shape[1]
+    g = Hq // Hkv
+    qf, do = q.float(), dout.float()
+    kf = k.float().repeat_interleave(g, dim=1)                   # [S, Hq, D]
+    vf = v.float().repeat_interleave(g, dim=1)
+    dq = torch.zeros(S, Hq, D)
+    dk_h, dv_h = torch.zeros(S, Hq, D), torch.zeros(S, Hq, D)
+    delta = (do * state.out).sum(-1)                             # [S, Hq]
+    chunk = state.kv_chunk_size or S
+    keys = torch.arange(S)
+    for pos in state.query_positions:
+        rows = torch.tensor(pos, dtype=torch.long)
+        if rows.numel() == 0:
+            continue
+        ql, dol, lsel, dl = qf[rows], do[rows], state.lse[rows], delta[rows]
+        last = int(rows.max()) + 1
+        for a in range(0, last, chunk):
+            e = min(last, a + chunk)
+            vis = keys[a:e][None, :] <= rows[:, None]                                   # [n, c]
+            sc = torch.einsum("nhd,chd->hnc", ql, kf[a:e]) * state.scale
+            p = torch.exp(sc - lsel.t().unsqueeze(-1))
+            p = torch.where(vis[None], p, torch.zeros_like(p))
+            dv_h[a:e] += torch.einsum("hnc,nhd->chd", p, dol)
+            dp = torch.einsum("nhd,chd->hnc", dol, vf[a:e])
+            ds = p * (dp - dl.t().unsqueeze(-1))
+            dq[rows] += torch.einsum("hnc,chd->nhd", ds, kf[a:e]) * state.scale
+            dk_h[a:e] += torch.einsum("hnc,nhd->chd", ds, ql) * state.scale
+    dk = dk_h.view(S, Hkv, g, D).sum(2)
+    dv = dv_h.view(S, Hkv, g, D).sum(2)
+    return AttentionBackwardGradients(dq, dk, dv)
+
+
+def backward_path(q, k, v, dout, *, cp_world_size: int = 1, layout: str = "zigzag", kv_chunk_size: Optional[int] = None,
+                  scale: Optional[float] = None, strict_bitwise: bool = True, name: Optional[str] = None) -> AttentionBackwardPathResult:
+    op = DeterministicCPAttentionReferenceOp(cp_world_size, layout, strict_bitwise=strict_bitwise, scale=scale)
+    state = save_forward_state(op, q, k, v, kv_chunk_size=kv_chunk_size)
+    grads = backward_from_saved_state(state, q, k, v, dout)
+    prov = {"cp_world_size": cp_world_size, "layout": layout, "kv_chunk_size": kv_chunk_size, "core": STRICT_ATTENTION_CORE_ID,
+            "schedule": state.strict_schedule, "forward": op.execution_provenance(q.shape[0]),
+            "split_kv": split_kv_execution_plan_provenance(q.shape[0], cp_world_size=cp_world_size, kv_chunk_size=kv_chunk_size,
+                                                           backend="deterministic_cp_reference")}
+    return AttentionBackwardPathResult(name or backward_path_name(cp_world_size=cp_world_size, kv_chunk_size=kv_chunk_size), state.out,
+                                       state.lse, grads, state, prov)
+
+
+def compare_backward_paths(candidate: AttentionBackwardPathResult, reference: AttentionBackwardPathResult) -> AttentionBackwardPathDrift:
+    ranks = tuple(AttentionBackwardRankDrift(r, _drift(candidate.gradients.dq[list(pos)], reference.gradients.dq[list(pos)]))
+                  for r, pos in enumerate(candidate.saved_forward_state.query_positions) if pos)
+    c, r = candidate.gradients, reference.gradients
+    fin = torch.isfinite(reference.lse)
+    return AttentionBackwardPathDrift(candidate.name, reference.name, _drift(candidate.out, reference.out),
+                                      _drift(candidate.lse[fin], reference.lse[fin]), _drift(c.dq, r.dq), _drift(c.dk, r.dk), _drift(c.dv, r.dv), ranks)
+
+
+# ------------------------------------------------------------------------------------------------ split-KV plans
+def _split_bounds(length: int, parts: int) -> list[tuple[int, int]]:
+    base, rem = divmod(length, parts)
+    out, s = [], 0
+    for i in range(parts):
+        e = s + base + (1 if i < rem else 0)
+        out.append((s, e))
+        s = e
+    return out
+
+
+def _plan(owner: tuple[int, int], kv_chunk_size: Optional[int], backend: str, source: str) -> SplitKVExecutionPlan:
+    a, e = owner
+    if kv_chunk_size is None:
+        mode, bounds = SplitKVMode.DISABLED, ((a, e),)
+    else:
+        mode, bounds = SplitKVMode.FIXED, tuple((x, min(x + kv_chunk_size, e)) for x in range(a, e, kv_chunk_size))
+    return SplitKVExecutionPlan(mode, kv_chunk_size, mode, kv_chunk_size, bounds, backend=backend, source=source)
+
+
+def split_kv_execution_plan_provenance(length: int, *, cp_world_size: int, kv_chunk_size: Optional[int], backend: str) -> list[dict]:
+    """The plan every CP owner's key range was actually consumed with, as provenance records."""
+    if length < 1 or cp_world_size < 1 or (kv_chunk_size is not None and kv_chunk_size < 1):
+        raise ValueError("length, cp_world_size and kv_chunk_size must be >= 1")
+    return [{"owner_cp_rank": o, **_plan(b, kv_chunk_size, backend, "reference_execution").to_dict()}
+            for o, b in enumerate(_split_bounds(length, cp_world_size)) if b[1] > b[0]]
+
+
+def build_reference_split_kv_runtime_plan_set(total_kv_tokens: Sequence[int], *, tp_world_size: int, cp_world_size: int,
+                                              kv_chunk_size: Optional[int], backend: str = "deterministic_cp_reference"
+                                              ) -> SplitKVRuntimePlanSet:
+    """Complete batch x TP x CP consumer x CP owner plans of the reference path (what a runtime must report to be bound)."""
+    totals = tuple(int(t) for t in total_kv_tokens)
+    if not totals or any(t < cp_world_size for t in totals):
+        raise ValueError("reference runtime plan sets require at least one KV token per CP owner")
+    if tp_world_size < 1 or cp_world_size < 1 or (kv_chunk_size is not None and kv_chunk_size < 1):
+        raise ValueError("world sizes and kv_chunk_size must be >= 1")
+    entries = [SplitKVRuntimePlanEntry(SplitKVRuntimeCoordinate(b, t, c, o), owner, _plan(owner, kv_chunk_size, backend, "reference_execution"))
+               for b, total in enumerate(totals) for t in range(tp_world_size) for c in range(cp_world_size)
+               for o, owner in enumerate(_split_bounds(total, cp_world_size))]
+    return SplitKVRuntimePlanSet(len(totals), tp_world_size, cp_world_size, totals, tuple(entries))
+
+
+CPAttentionReferenceOp = DeterministicCPAttentionReferenceOp
+
+__all__ = ["AttentionBackwardComparisonReport", "AttentionBackwardGradients", "AttentionBackwardPathDrift", "AttentionBackwardPathResult",
+           "AttentionBackwardRankDrift", "AttentionPartialState", "AttentionRingBlock", "AttentionRingSchedule", "AttentionSavedForwardState",
+           "CPAttentionReferenceOp", "DeterministicAttentionCore", "DeterministicAttentionCoreResult", "DeterministicCPAttentionReferenceOp",
+           "GradientDriftStats", "STRICT_ATTENTION_CORE_ID", "STRICT_ATTENTION_SCHEDULE_ID", "backward_from_saved_state", "backward_path",
+           "backward_path_name", "build_reference_split_kv_runtime_plan_set", "compare_backward_paths", "compare_cp_attention_backward",
+           "merge_attention_partial_states", "save_forward_state", "split_kv_execution_plan_provenance"]
