@@ -103,3 +103,60 @@ def test_artifact_validation(tmp_path):
         assert needle in text, (needle, text)
     assert "missing vllm/rollout readback" in va.validate_readbacks([_readback("megatron", "training")])["errors"]
     assert va.main([str(rbd), str(tmp_path / "rb")]) == 2                        # no dumps there
+
+
+def test_integration_evidence_feeds_artifact_validation(tmp_path, monkeypatch):
+    """Read-backs written by the framework adapter are what the artifact validation reads."""
+    import pytest
+
+    from rl_kernel_b200.integrations.common.runtime import FrameworkOperatorIntegration
+    from rl_kernel_b200.runtime.plan import IntegrationPlan
+
+    monkeypatch.setenv("RL_KERNEL_READBACK_DIR", str(tmp_path / "rb"))
+
+    class Op:
+        def __init__(self, backend_id, provenance=None):
+            self.backend_id, self.provenance, self.calls = backend_id, provenance or {"runtime_platform": "cuda"}, 0
+
+        def __call__(self, x):
+            self.calls += 1
+            return x + 1
+
+    def native(x):
+        return x - 1
+
+    for framework, side in (("vllm", "rollout"), ("megatron", "training")):
+        ops = {"attention": Op("rl_kernel_b200.attention"), "ffn": Op("rl_kernel_b200.ffn"), "logp": Op("rl_kernel_b200.linear_logp.bitwise.v1")}
+        integ = FrameworkOperatorIntegration(framework, side, IntegrationPlan.uniform("R/R"), rl_kernel_operators=ops)
+        with pytest.raises(RuntimeError, match="missing hooks"):
+            integ.assert_strict_evidence()
+        for m in ops:
+            integ.record_installed_hook(m, f"{framework}.{m}.forward")
+            assert integ.route(m, native, 1) == 2                                   # the plan selects the installed operator
+        integ.record_profile_call("attention")
+        integ.assert_strict_evidence()
+        rb = integ.readback()
+        assert rb["operators"]["logp"]["call_count"] == 1 and rb["profile_calls"] == {"attention": 1} and rb["target"] in ("rollout", "training")
+        with pytest.raises(RuntimeError, match="did not use the installed"):
+            integ.record_execution("ffn", native)
+        with pytest.raises(ValueError):
+            integ.record_execution("ffn", ops["ffn"], execution_mode="interpreted")
+        integ.record_execution("ffn", ops["ffn"], execution_mode="compiled_cuda_graph")
+        assert integ.readback()["operators"]["ffn"]["execution_mode"] == "compiled_cuda_graph"
+    rep = va.validate_readbacks(va.load_readbacks(tmp_path / "rb"))
+    assert rep["passed"], rep["errors"]
+    # a plan that leaves a module to the framework routes to the native callable and records it as production
+    mixed = FrameworkOperatorIntegration("vllm", "rollout", IntegrationPlan.uniform("P/R"))
+    assert mixed.route("ffn", native, 1) == 0 and mixed.readback()["operators"]["ffn"]["implementation"] == "production"
+    assert mixed.readback()["operators"]["ffn"]["backend_id"] == "vllm.production.ffn"
+    # a strict operator whose own provenance admits a fallback is refused and remembered
+    strict = FrameworkOperatorIntegration("megatron", "train", IntegrationPlan.uniform("R/R"),
+                                          rl_kernel_operators={"logp": Op("rl_kernel_b200.linear_logp.bitwise.v1",
+                                                                          {"runtime_platform": "cuda", "fallback": True, "actual_backend": "torch"})})
+    with pytest.raises(RuntimeError, match="reported fallback"):
+        strict.route("logp", native, 1)
+    assert strict.readback()["fallbacks"][0]["module"] == "logp"
+    with pytest.raises(RuntimeError, match="no operator was installed"):
+        strict.route("attention", native, 1)
+    with pytest.raises(ValueError, match="unknown integration module"):
+        strict.record_installed_hook("sampler", "x")
