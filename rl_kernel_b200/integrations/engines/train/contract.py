@@ -333,3 +333,114 @@ def make_rollout_result(payload: Any, *, samples_per_prompt: Optional[int] = Non
     res = RolloutStageResult(tokens, mask, lp, torch.tensor([r for grp in rewards for r in grp], dtype=torch.float32), P, g, weight_version)
     res.validate()
     return res
+
+
+# ================================================================================================ training batches
+# (parity: RolloutBatchMixin._batch_from_rollout_or_synthetic / _batch_from_candidate_groups,
+#  rl_engine/integrations/engines/train/contract.py:84-305)
+def batch_from_candidate_groups(candidate_groups: Sequence[Sequence[Sequence[int]]], prompt_groups: Sequence[Sequence[int]] | None = None, *,
+                                reward_groups: Sequence[Sequence[float]] | None = None,
+                                reference_logp_groups: Sequence[Sequence[Sequence[float]]] | None = None,
+                                rollout_logp_groups: Sequence[Sequence[Sequence[float]]] | None = None, completion_len: int | None = None,
+                                pad_token_id: int = 0, advantage_eps: float = 1e-6, dtype: torch.dtype = torch.float32,
+                                device: torch.device | str = "cpu"):
+    """A ``SyntheticRLKernelBatch``-shaped training batch from grouped completions.  Prompts (one per group, one length)
+    are left-aligned, completions right-padded (or cut) to ``completion_len``; advantages are group-relative from the
+    rewards (a reward a payload does not carry is replaced by a token-id proxy, named as such in the metadata);
+    reference / old log-probs default to zero with the source recorded."""
+    from rl_kernel_b200.validation.common.rl_batch import SyntheticRLKernelBatch
+
+    groups = [[list(map(int, c)) for c in grp] for grp in candidate_groups]
+    if not groups or any(not grp for grp in groups):
+        raise ValueError("every prompt group needs at least one completion")
+    prompts = [list(map(int, p)) for p in (prompt_groups or [[] for _ in groups])]
+    if len(prompts) != len(groups):
+        raise ValueError("one prompt per group")
+    P = len(prompts[0])
+    if any(len(p) != P for p in prompts):
+        raise ValueError("prompts must have one length")
+    L = completion_len or max(len(c) for grp in groups for c in grp)
+    if L < 1:
+        raise ValueError("completions are empty")
+    B = sum(len(grp) for grp in groups)
+    ids = torch.full((B, P + L), pad_token_id, dtype=torch.long)
+    cmask = torch.zeros(B, L, dtype=torch.bool)
+    old, ref = torch.zeros(B, L), torch.zeros(B, L)
+    rewards = torch.zeros(B)
+    adv_rows: list[float] = []
+    sizes = []
+    i = 0
+    have_r = reward_groups is not None and [len(g) for g in reward_groups] == [len(g) for g in groups]
+    for gi, grp in enumerate(groups):
+        rs = [float(x) for x in reward_groups[gi]] if have_r else [float(sum(c) % 97) / 97.0 for c in grp]
+        adv_rows += compute_group_relative_advantages([rs], advantage_eps)[0]
+        sizes.append(len(grp))
+        for ci, c in enumerate(grp):
+            n = min(len(c), L)
+            ids[i, :P] = torch.tensor(prompts[gi], dtype=torch.long) if P else ids[i, :P]
+            ids[i, P:P + n] = torch.tensor(c[:n], dtype=torch.long)
+            cmask[i, :n] = True
+            rewards[i] = rs[ci]
+            for src, dst in ((reference_logp_groups, ref), (rollout_logp_groups, old)):
+                if src is not None and len(src) > gi and len(src[gi]) > ci and len(src[gi][ci]) >= n:
+                    dst[i, :n] = torch.tensor([float(x) for x in src[gi][ci][:n]])
+            i += 1
+    adv = broadcast_sequence_advantages(torch.tensor(adv_rows), cmask)
+    attn = torch.cat([torch.ones(B, P, dtype=torch.bool), cmask], 1)
+    pmask = torch.cat([torch.ones(B, P, dtype=torch.bool), torch.zeros(B, L, dtype=torch.bool)], 1)
+    dev = torch.device(device)
+    md = {"num_prompts": len(groups), "samples_per_prompt": sizes[0] if len(set(sizes)) == 1 else None, "group_sizes": sizes, "batch_size": B,
+          "prompt_len": P, "completion_len": L, "total_seq_len": P + L, "valid_tokens": int(cmask.sum()), "dtype": dtype, "device": str(dev),
+          "reward_source": "payload_rewards" if have_r else "token_id_proxy",
+          "reference_logp_source": "payload_reference_logps" if reference_logp_groups is not None else "zeros",
+          "old_logp_source": "payload_rollout_logps" if rollout_logp_groups is not None else "zeros"}
+    return SyntheticRLKernelBatch(ids.to(dev), attn.to(dev), pmask.to(dev), cmask.to(dev), ids[:, P:].contiguous().to(dev), rewards.to(dtype).to(dev),
+                                  adv.to(dtype).to(dev), old.to(dtype).to(dev), ref.to(dtype).to(dev),
+                                  cmask.reshape(-1).nonzero().squeeze(-1).to(dev), md)
+
+
+def batch_from_rollout_or_synthetic(payload: Any, *, iteration: int = 0, num_prompts: int = 1, samples_per_prompt: int = 2, prompt_len: int = 4,
+                                    completion_len: int = 8, vocab_size: int = 64, valid_density: float = 0.75, seed: int = 0,
+                                    pad_token_id: int = 0, advantage_eps: float = 1e-6, dtype: torch.dtype = torch.float32,
+                                    device: torch.device | str = "cpu"):
+    """(batch, provenance).  A payload with grouped candidates becomes the batch (with whatever rewards, reference and
+    rollout log-probs it carries); anything else -- a smoke run without a serving engine -- gets the synthetic batch of
+    ``seed + iteration``, and the provenance says so."""
+    try:
+        cands = extract_rollout_candidate_groups(payload) if payload else []
+    except TypeError:                            # not a grouped payload at all (e.g. an engine's status object)
+        cands = []
+    if cands:
+        prompts = extract_rollout_token_groups(payload)
+
+        def optional(reader):                    # the strict readers raise when a candidate lacks the field
+            try:
+                return reader(payload)
+            except ValueError:
+                return []
+
+        rewards, refs = optional(extract_rollout_reward_groups), optional(extract_rollout_reference_logp_groups)
+        flat = [c for grp in _groups(payload) for c in _candidates(grp)[1]]
+        rl, k = [], 0
+        for grp in cands:
+            rl.append([candidate_rollout_logps(flat[k + j]) or [] for j in range(len(grp))])
+            k += len(grp)
+        have_rl = all(len(r) >= min(len(c), completion_len) and r for rg, cg in zip(rl, cands) for r, c in zip(rg, cg))
+        have_ref = bool(refs) and [len(g) for g in refs] == [len(g) for g in cands] and \
+            all(len(r) >= min(len(c), completion_len) for rg, cg in zip(refs, cands) for r, c in zip(rg, cg))
+        same_prompt_len = bool(prompts) and len({len(p) for p in prompts}) == 1
+        batch = batch_from_candidate_groups(cands, prompts if same_prompt_len else None, reward_groups=rewards or None,
+                                            reference_logp_groups=refs if have_ref else None, rollout_logp_groups=rl if have_rl else None,
+                                            completion_len=completion_len, pad_token_id=pad_token_id, advantage_eps=advantage_eps, dtype=dtype,
+                                            device=device)
+        toks = [c for grp in cands for c in grp]
+        return batch, {"training_data_source": "rollout_payload", "reward_source": batch.metadata["reward_source"],
+                       "reference_logp_source": batch.metadata["reference_logp_source"], "old_logp_source": batch.metadata["old_logp_source"],
+                       "rollout_prompt_groups": len(cands), "rollout_sequences": len(toks), "rollout_tokens": sum(len(t) for t in toks)}
+    from rl_kernel_b200.validation.common.rl_batch import make_synthetic_rl_kernel_batch
+
+    batch = make_synthetic_rl_kernel_batch(num_prompts=num_prompts, samples_per_prompt=samples_per_prompt, prompt_len=prompt_len,
+                                           completion_len=completion_len, vocab_size=vocab_size, valid_density=valid_density, dtype=dtype,
+                                           device=device, seed=seed + int(iteration))
+    return batch, {"training_data_source": "synthetic_fallback", "rollout_sequences": 0, "rollout_tokens": 0,
+                   "reward_source": "synthetic_rewards", "reference_logp_source": "synthetic", "old_logp_source": "synthetic"}

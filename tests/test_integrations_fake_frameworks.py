@@ -234,3 +234,33 @@ def test_rollout_payload_contract_round_trip():
         C.objective_reference_logps(None, torch.zeros(2), 0.1)
     with pytest.raises(ValueError):
         C.TorchRLTrainingConfig(clip_eps=1.5)
+
+
+def test_training_batch_from_rollout_payload_or_synthetic():
+    from rl_kernel_b200.integrations.engines.train.contract import batch_from_candidate_groups, batch_from_rollout_or_synthetic
+
+    payload = {"groups": [{"prompt_token_ids": [1, 2, 3],
+                           "candidates": [{"token_ids": [4, 5, 6, 7], "reward": 1.0, "logprobs": [-.1, -.2, -.3, -.4]},
+                                          {"token_ids": [8, 9], "reward": 0.0, "logprobs": [-.5, -.6]}]}]}
+    b, prov = batch_from_rollout_or_synthetic(payload, completion_len=4)
+    assert prov == {"training_data_source": "rollout_payload", "reward_source": "payload_rewards", "reference_logp_source": "zeros",
+                    "old_logp_source": "payload_rollout_logps", "rollout_prompt_groups": 1, "rollout_sequences": 2, "rollout_tokens": 6}
+    assert b.input_ids.tolist() == [[1, 2, 3, 4, 5, 6, 7], [1, 2, 3, 8, 9, 0, 0]] and b.completion_mask.tolist() == [[True] * 4, [True, True, False, False]]
+    assert torch.allclose(b.old_logps[1], torch.tensor([-.5, -.6, 0, 0])) and b.prompt_len == 3 and b.valid_indices.tolist() == [0, 1, 2, 3, 4, 5]
+    assert b.advantages[0, 0] > 0 > b.advantages[1, 0] and (b.advantages[1, 2:] == 0).all()             # group-relative, masked
+    for c in payload["groups"][0]["candidates"]:
+        c["reference_logprobs"] = [-1.0] * len(c["token_ids"])
+        del c["reward"]
+    b, prov = batch_from_rollout_or_synthetic(payload, completion_len=3)                                  # completions cut to 3
+    assert prov["reward_source"] == "token_id_proxy" and prov["reference_logp_source"] == "payload_reference_logps"
+    assert b.completion_len == 3 and (b.ref_logps[0] == -1).all() and b.ref_logps[1].tolist() == [-1.0, -1.0, 0.0]
+    s1, p1 = batch_from_rollout_or_synthetic(None, iteration=3, seed=10)
+    s2, _ = batch_from_rollout_or_synthetic({}, iteration=3, seed=10)
+    assert p1["training_data_source"] == "synthetic_fallback" and torch.equal(s1.input_ids, s2.input_ids)
+    assert not torch.equal(s1.input_ids, batch_from_rollout_or_synthetic(None, iteration=4, seed=10)[0].input_ids)
+    with pytest.raises(ValueError):
+        batch_from_candidate_groups([[]])
+    with pytest.raises(ValueError, match="one length"):
+        batch_from_candidate_groups([[[1]], [[2]]], [[1, 2], [3]])
+    uneven = batch_from_candidate_groups([[[1, 2], [3]], [[4]]], reward_groups=[[1.0, 0.0], [0.5]])
+    assert uneven.metadata["samples_per_prompt"] is None and uneven.metadata["group_sizes"] == [2, 1] and uneven.advantages[2].abs().max() == 0
