@@ -264,3 +264,81 @@ def test_training_batch_from_rollout_payload_or_synthetic():
         batch_from_candidate_groups([[[1]], [[2]]], [[1, 2], [3]])
     uneven = batch_from_candidate_groups([[[1, 2], [3]], [[4]]], reward_groups=[[1.0, 0.0], [0.5]])
     assert uneven.metadata["samples_per_prompt"] is None and uneven.metadata["group_sizes"] == [2, 1] and uneven.advantages[2].abs().max() == 0
+
+
+def test_deepspeed_engine_construction_with_a_stand_in_module(tmp_path):
+    import types
+
+    from rl_kernel_b200.integrations.common.weights import make_weight_bridge
+    from rl_kernel_b200.integrations.engines.train.deepspeed import adapter as ds
+
+    cfg = ds.DeepSpeedTrainingConfig(zero_stage=3, micro_batch_size=4, dtype=torch.float32,
+                                     deepspeed_config={"zero_optimization": {"stage3_param_persistence_threshold": 0}, "wall_clock_breakdown": True})
+    conf = ds.resolved_deepspeed_config(cfg)
+    assert conf["zero_optimization"] == {"stage": 3, "overlap_comm": False, "contiguous_gradients": True, "reduce_scatter": True,
+                                         "stage3_param_persistence_threshold": 0}
+    assert conf["bf16"] == {"enabled": False} and conf["wall_clock_breakdown"] is True and conf["communication_data_type"] == "fp32"
+    assert ds.resolved_zero_stage(conf) == 3 and ds.resolved_zero_stage({"zero_optimization": False}, fallback=2) == 0
+    assert ds.resolved_zero_stage({}, fallback=2) == 2
+    with pytest.raises(ValueError):
+        ds.DeepSpeedTrainingConfig(zero_stage=4)
+    with pytest.raises(ds.DeepSpeedUnavailableError):
+        ds.load_deepspeed()                                                   # not installed in this environment
+    # toolkit discovery: a directory with bin/nvcc and include/cuda.h is taken, PATH is extended, an explicit value wins
+    root = tmp_path / "cu"
+    (root / "bin").mkdir(parents=True)
+    (root / "include").mkdir()
+    (root / "bin" / "nvcc").write_text("")
+    (root / "include" / "cuda.h").write_text("")
+    assert ds.looks_like_cuda_home(root) and not ds.looks_like_cuda_home(tmp_path)
+    assert ds.configure_cuda_home({"CUDA_HOME": "/somewhere"}) == "/somewhere"
+    # output readers
+    h = torch.randn(2, 5, 16)
+    out = types.SimpleNamespace(last_hidden_state=h, logits=torch.randn(2, 5, 64))
+    assert ds.extract_hidden_states(out, expected_hidden_dim=16) is h and ds.extract_logits(out).shape[-1] == 64
+    assert ds.extract_hidden_states({"hidden_states": (torch.zeros(1), h)}) is h and ds.extract_hidden_states((torch.randn(2, 5, 64), h), expected_hidden_dim=16) is h
+    with pytest.raises(TypeError, match="width 16"):
+        ds.extract_hidden_states(types.SimpleNamespace(logits=torch.randn(2, 5, 64)), expected_hidden_dim=16)
+    assert ds.first_initialize_result((1, 2, 3)) == 1 and ds.first_initialize_result("e") == "e"
+    with pytest.raises(RuntimeError):
+        ds.first_initialize_result(())
+
+    class Tiny(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = torch.nn.Embedding(32, 16)
+            self.lm_head = torch.nn.Linear(16, 32, bias=False)
+
+        def forward(self, ids):
+            return types.SimpleNamespace(last_hidden_state=self.emb(ids), logits=None)
+
+    class Engine:
+        def __init__(self, model, config):
+            self.module, self.config = model, config
+            self.opt = torch.optim.SGD(model.parameters(), lr=0.1)
+
+        def backward(self, loss):
+            loss.backward()
+
+        def step(self):
+            self.opt.step()
+            self.opt.zero_grad()
+
+    seen = {}
+
+    def initialize(model, model_parameters, config, **kw):
+        seen.update(config=config, kw=kw, n=len(list(model_parameters)))
+        return Engine(model, config), None, None, None
+
+    fake = types.SimpleNamespace(initialize=initialize, zero=types.SimpleNamespace(GatheredParameters=lambda params, modifier_rank=None: __import__("contextlib").nullcontext()))
+    worker = ds.build_deepspeed_worker(Tiny(), make_weight_bridge("local-clone", source_worker="t", source_rank=0), cfg, deepspeed_module=fake)
+    assert seen["config"]["zero_optimization"]["stage"] == 3 and seen["n"] == 2 and worker.gather_context is not None
+    from rl_kernel_b200.integrations.engines.train.contract import RolloutStageResult
+
+    tokens = torch.randint(0, 32, (4, 3 + 5))
+    roll = RolloutStageResult(tokens, torch.ones(4, 5, dtype=torch.bool), torch.full((4, 5), -3.0), torch.tensor([1.0, 0.0, 0.5, 0.2]), 3, 2)
+    before = worker.engine.module.lm_head.weight.detach().clone()
+    res = worker.train(roll)
+    assert res.tokens_compared == 20 and not torch.equal(worker.engine.module.lm_head.weight, before)
+    manifest = worker.publish_weights(1)
+    assert manifest.weight_version == 1
