@@ -342,3 +342,58 @@ def test_deepspeed_engine_construction_with_a_stand_in_module(tmp_path):
     assert res.tokens_compared == 20 and not torch.equal(worker.engine.module.lm_head.weight, before)
     manifest = worker.publish_weights(1)
     assert manifest.weight_version == 1
+
+
+def test_megatron_install_records_hooks_patches_linears_and_uninstalls():
+    from rl_kernel_b200.integrations.engines.train.megatron.runtime import (MegatronUnavailable, resolve_megatron_classes,
+                                                                           uninstall_megatron_integration)
+
+    class Column(torch.nn.Module):
+        def __init__(self, w, bias=None, skip_bias_add=False):
+            super().__init__()
+            self.weight, self.bias, self.skip_bias_add = torch.nn.Parameter(w), bias, skip_bias_add
+
+        def forward(self, x):
+            return "framework", None
+
+    class Row(Column):
+        pass
+
+    class Out(torch.nn.Module):
+        def __init__(self, w):
+            super().__init__()
+            self.weight = torch.nn.Parameter(w)
+
+    class Norm(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.weight, self.eps = torch.nn.Parameter(torch.ones(16)), 1e-6
+
+        def forward(self, x):
+            return "framework"
+
+    integ = install_megatron_integration(column_linear_cls=Column, row_linear_cls=Row, output_layer_cls=Out, norm_cls=Norm,
+                                         plan=IntegrationPlan.uniform("R/R"))
+    rb = integ.readback()
+    assert rb["installed_hooks"]["logp"].endswith("Out.selected_logprobs") and rb["installed_hooks"]["attention"].endswith("Row.forward")
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(2, 5, 16, generator=g)
+    w1, w2, b = torch.randn(32, 16, generator=g), torch.randn(16, 32, generator=g), torch.randn(32, generator=g)
+    y, bias = Column(w1, b, skip_bias_add=True)(x)
+    assert y.shape == (2, 5, 32) and bias is b and torch.allclose(y, x @ w1.t(), atol=1e-4)
+    y2, none = Column(w1, b)(x)
+    assert none is None and torch.allclose(y2, x @ w1.t() + b, atol=1e-4)
+    z, _ = Row(w2)(y)
+    assert z.shape == (2, 5, 16) and torch.allclose(z, y @ w2.t(), atol=1e-3)
+    assert torch.allclose(Norm()(x), x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6), atol=1e-5)
+    hidden, tg = torch.randn(7, 16, generator=g), torch.randint(0, 32, (7,), generator=g)
+    lp = Out(w1).selected_logprobs(hidden, tg)
+    assert torch.allclose(lp, torch.log_softmax(hidden @ w1.t(), -1).gather(1, tg[:, None])[:, 0], atol=1e-4)
+    assert integ.readback()["operators"]["logp"]["call_count"] == 1
+    # installing again does not stack wrappers; uninstalling restores the framework's own methods and removes added ones
+    again = install_megatron_integration(column_linear_cls=Column, row_linear_cls=Row, output_layer_cls=Out, norm_cls=Norm,
+                                         plan=IntegrationPlan.uniform("R/R"))
+    assert uninstall_megatron_integration(again) == 4 and uninstall_megatron_integration(integ) == 0
+    assert Column(w1)(x) == ("framework", None) and Norm()(x) == "framework" and not hasattr(Out, "selected_logprobs")
+    with pytest.raises(MegatronUnavailable):
+        resolve_megatron_classes()
