@@ -22,10 +22,10 @@ class OperatorBridge:
         if hidden is not None:
             if lm_head_weight is None:
                 raise ValueError("hidden input needs lm_head_weight")
-            op = kernel_registry.get_op("linear_logp", temperature=self.temperature)
+            op = kernel_registry.get_op("linear_logp", temperature=self.temperature, operand_device=hidden.device)
             lp = op(hidden, lm_head_weight, token_ids)
         else:
-            op = kernel_registry.get_op("batch_invariant_logp", temperature=self.temperature)
+            op = kernel_registry.get_op("batch_invariant_logp", temperature=self.temperature, operand_device=logits.device)
             lp = op(logits, token_ids)
         res = kernel_registry.last_resolution
         backend = "reference" if res.actual.name.startswith("REF") else "b200-tcgen05"
