@@ -29,6 +29,21 @@ def _dev(a):
     return dev, dtype, acc.describe(dev).to_dict()
 
 
+def cmd_adapters(args) -> int:
+    import json as _json
+
+    from rl_kernel_b200.validation.operators.gradient_adapters import gradient_adapter_status_matrix
+
+    rows = gradient_adapter_status_matrix()
+    if args.json:
+        print(_json.dumps([r.to_dict() for r in rows], indent=1))
+    else:
+        for r in rows:
+            flag = "RED " if (r.untracked_red or r.tracked_red) else "    "
+            print(f"{flag}{r.backend_profile:<15} {r.chain_node:<26} {r.op_name:<24} {r.candidate_status:<22} {r.candidate_path or '-'}")
+    return 2 if any(r.untracked_red or r.tracked_red for r in rows) else 0
+
+
 def cmd_list(a) -> int:
     from rl_kernel_b200.validation.operators.operator_specs import OP_SPECS
 
@@ -121,6 +136,9 @@ def main(argv=None) -> int:
         p.add_argument("--seed", type=int, default=0)
 
     sub.add_parser("list").set_defaults(fn=cmd_list)
+    p = sub.add_parser("adapters", help="status matrix: backend profile x chain node -> adapter, candidate, coverage")
+    p.add_argument("--json", action="store_true")
+    p.set_defaults(fn=cmd_adapters)
     p = sub.add_parser("operator"); common(p, True); p.set_defaults(fn=cmd_operator)
     p = sub.add_parser("forward-invariance"); common(p, True); p.set_defaults(fn=lambda a: _invariance(a, False))
     p = sub.add_parser("gradient-invariance"); common(p, True); p.set_defaults(fn=lambda a: _invariance(a, True))

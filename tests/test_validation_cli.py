@@ -227,3 +227,44 @@ def test_operator_spec_paths_resolve():
         for path in {**spec.candidate_paths, "gold": spec.gold_path}.values():
             mod, attr = _local(path).rsplit(".", 1)
             assert hasattr(importlib.import_module(mod), attr), (name, path)
+
+
+def test_gradient_adapter_registry_and_status_matrix():
+    import dataclasses
+
+    from rl_kernel_b200.config.workload import load_manifest
+    from rl_kernel_b200.validation.operators import gradient_adapters as ga
+
+    assert set(ga.adapter_names()) == set(ga.OP_SPECS) and ga.get_adapter("rms_norm").chain_nodes == ("input_layernorm", "post_attention_layernorm",
+                                                                                                  "final_layernorm")
+    with pytest.raises(KeyError, match="unknown gradient adapter"):
+        ga.get_adapter("nope")
+    req = {a.op_name for a in ga.required_gradient_adapters()}
+    assert {"rms_norm", "det_gemm", "attention", "linear_logp", "swiglu", "rope", "embedding"} <= req and "sampling" not in req
+    assert "pack" in {a.op_name for a in ga.required_forward_adapters()}
+    rows = ga.gradient_adapter_status_matrix()
+    m = load_manifest()
+    assert not [r for r in rows if r.untracked_red or r.tracked_red]                       # every node a profile runs can be judged
+    for profile in m.backend_profiles:
+        nodes = [r.chain_node for r in rows if r.backend_profile == profile and r.chain_node != "-"]
+        assert nodes == list(m.chain_semantics["nodes"])
+    b200 = {r.chain_node: r for r in rows if r.backend_profile == "b200_bf16"}
+    assert b200["logprob"].op_name == "linear_logp" and b200["logprob"].expected_backend_id == "b200" and "weight" in b200["o_proj"].grad_tensor_names
+    assert {r.candidate_status for r in rows if r.chain_node == "-"} <= {"optional", "declared", "absent_not_required"}
+    assert b200["rope"].to_dict()["candidate_path"].endswith("RoPESM100Op")
+    # a chain node nobody maps is an untracked red row
+    saved = ga.CHAIN_NODE_OPERATORS.pop("rope")
+    try:
+        red = [r for r in ga.gradient_adapter_status_matrix(profiles=("b200_bf16",)) if r.untracked_red]
+        assert [r.chain_node for r in red] == ["rope"] and not red[0].adapter_registered
+    finally:
+        ga.CHAIN_NODE_OPERATORS["rope"] = saved
+    gold = ga.load_adapter_gold("swiglu")
+    g, u = torch.randn(3, 8), torch.randn(3, 8)
+    assert torch.allclose(gold(g, u), torch.nn.functional.silu(g) * u, atol=1e-6)
+    assert type(ga.load_adapter_operator("rms_norm", "pytorch")).__name__ == "NativeRMSNormOp"
+    with pytest.raises(RuntimeError, match="no candidate"):
+        ga.load_adapter_operator("rms_norm", "triton")
+    paths = ga.listed_source_paths(ga.get_adapter("attention"))
+    assert paths and all(p.exists() for p in paths)
+    assert dataclasses.is_dataclass(ga.get_adapter("pack")) and ga.get_adapter("pack").requirement == "layout_supported"
