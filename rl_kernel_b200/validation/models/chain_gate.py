@@ -206,3 +206,185 @@ def run_engine_chain_gate(spec, weights, input_ids: torch.Tensor, *, device: str
                and all(v <= grad_rel_limit for v in res.gradient_accuracy.values()))
     res.passed = ok_acc and ok_grad and all(res.cells.values())
     return res
+
+
+# ================================================================================================ the gate over the workload manifest
+# The same judgment driven by the manifest's logical batch: every cell lays the SAME logical tokens out differently
+# (padded batch, permuted batch, longer padding, one sample per call, chunked prefill through a KV cache, prefill plus
+# decode steps) and hands back values keyed by (sample, position); cells are compared key by key, the candidate is judged
+# against an fp32 gold model with the contract's chain aggregates, and the first drifting node is found from per-node
+# digests (parity: CellOutput / ChainGateReport / run_chain_gate cells, rl_engine/validation/models/chain_gate.py:94-1139).
+import hashlib as _hashlib
+from typing import Any as _Any, Sequence as _Sequence
+
+
+@dataclass
+class CellOutput:
+    cell_id: str
+    selected_logp: dict[tuple[str, int], torch.Tensor]
+    loss: torch.Tensor | None
+    node_digests: dict[str, str]
+    actual_backend: str = "cpu-reference"
+
+    def to_dict(self) -> dict[str, _Any]:
+        return {"cell_id": self.cell_id, "n_logp_tokens": len(self.selected_logp), "loss": None if self.loss is None else float(self.loss),
+                "node_digests": dict(self.node_digests), "actual_backend": self.actual_backend}
+
+
+@dataclass
+class CellComparison:
+    cell_id: str
+    reference_cell: str
+    tokens: int
+    mismatching_tokens: int
+    max_abs: float
+    worst_key: tuple[str, int] | None
+
+    @property
+    def passed(self) -> bool:
+        return self.mismatching_tokens == 0
+
+    def to_dict(self) -> dict[str, _Any]:
+        return {"cell_id": self.cell_id, "reference_cell": self.reference_cell, "tokens": self.tokens,
+                "mismatching_tokens": self.mismatching_tokens, "max_abs": self.max_abs, "worst_key": self.worst_key, "passed": self.passed}
+
+
+@dataclass
+class ChainGateReport:
+    workload_id: str
+    fixture_hash: str
+    seed: int
+    device: str
+    execution_dtype: str
+    cells: dict[str, CellOutput]
+    invariance: tuple[CellComparison, ...]
+    accuracy: dict[str, _Any] | None
+    first_drift: str | None
+    passed: bool
+    disclaimer: str = ("synthetic weights and ids: this judges the arithmetic of the chain under layout changes, not model quality")
+
+    def to_dict(self) -> dict[str, _Any]:
+        return {"workload_id": self.workload_id, "fixture_hash": self.fixture_hash, "seed": self.seed, "device": self.device,
+                "execution_dtype": self.execution_dtype, "cells": {k: v.to_dict() for k, v in self.cells.items()},
+                "invariance": [c.to_dict() for c in self.invariance], "accuracy": self.accuracy, "first_drift": self.first_drift,
+                "passed": self.passed, "disclaimer": self.disclaimer}
+
+
+def _digest(t: torch.Tensor) -> str:
+    return _hashlib.sha256(t.detach().contiguous().cpu().view(torch.uint8).numpy().tobytes()).hexdigest()[:16]
+
+
+def _scored(sample) -> range:
+    """Positions whose token is scored: active ones that have a prefix."""
+    return range(max(1, sample.prompt_len), sample.seq_len)
+
+
+def _padded_cell(model, batch, cell_id: str, *, padded_len: int | None = None, order: _Sequence[int] | None = None,
+                 capture: bool = False) -> CellOutput:
+    samples = [batch.samples[i] for i in (order or range(len(batch.samples)))]
+    L = padded_len or max(s.seq_len for s in samples)
+    ids = torch.zeros(len(samples), L, dtype=torch.long)
+    mask = torch.zeros(len(samples), L)
+    for b, s in enumerate(samples):
+        ids[b, :s.seq_len] = torch.tensor(s.token_ids)
+        mask[b, list(_scored(s))] = 1.0
+    out = model(ids, target_ids=ids, loss_mask=mask, capture_nodes=capture, return_logits=False)
+    lp = out["selected_logp"]
+    vals = {(s.sample_id, p): lp[b, p - 1].detach().clone() for b, s in enumerate(samples) for p in _scored(s)}
+    digests = {}
+    if capture:
+        keep = torch.cat([torch.arange(b * L, b * L + s.seq_len) for b, s in enumerate(samples)])
+        for name, t in model.captured_node_outputs().items():
+            if t.dim() >= 1 and t.shape[0] == len(samples) * L:
+                digests[name] = _digest(t[keep])            # rows of real tokens only, in logical order
+    return CellOutput(cell_id, vals, out.get("loss"), digests)
+
+
+def _singleton_cell(model, batch, cell_id: str) -> CellOutput:
+    vals, total, n = {}, 0.0, 0
+    for s in batch.samples:
+        ids = torch.tensor([s.token_ids])
+        lp = model(ids, target_ids=ids, return_logits=False)["selected_logp"]
+        for p in _scored(s):
+            vals[(s.sample_id, p)] = lp[0, p - 1].detach().clone()
+            total, n = total - float(lp[0, p - 1]), n + 1
+    return CellOutput(cell_id, vals, torch.tensor(total / max(1, n)), {})
+
+
+def _chunked_cell(model, batch, cell_id: str, chunk_size: int, *, decode: bool = False) -> CellOutput:
+    """Per sample: prefill in chunks of ``chunk_size`` through a KV cache (``decode``: the prompt in one call, then one
+    token per call)."""
+    vals = {}
+    for s in batch.samples:
+        ids = torch.tensor([s.token_ids])
+        cache = model.allocate_cache(1, s.seq_len + 1)
+        spans = ([(0, max(1, s.prompt_len))] + [(t, t + 1) for t in range(max(1, s.prompt_len), s.seq_len)]) if decode else \
+            [(a, min(s.seq_len, a + chunk_size)) for a in range(0, s.seq_len, chunk_size)]
+        for a, e in spans:
+            pos = torch.arange(a, e).unsqueeze(0)
+            hidden = model(ids[:, a:e], position_ids=pos, kv_cache=cache, return_logits=False)["hidden"][0]       # [e - a, H]
+            for j, t in enumerate(range(a, e)):
+                if t + 1 in _scored(s):
+                    vals[(s.sample_id, t + 1)] = model.selected_logprobs(hidden[j:j + 1], ids[0, t + 1:t + 2])[0].detach().clone()
+    return CellOutput(cell_id, vals, None, {})
+
+
+def compare_cells(cell: CellOutput, reference: CellOutput) -> CellComparison:
+    keys = sorted(reference.selected_logp)
+    if sorted(cell.selected_logp) != keys:
+        missing = set(keys) ^ set(cell.selected_logp)
+        return CellComparison(cell.cell_id, reference.cell_id, len(keys), len(missing), float("inf"), sorted(missing)[0])
+    a = torch.stack([cell.selected_logp[k] for k in keys]).float()
+    b = torch.stack([reference.selected_logp[k] for k in keys]).float()
+    diff = a.view(torch.int32) != b.view(torch.int32)
+    gap = (a - b).abs()
+    worst = keys[int(gap.argmax())] if bool(diff.any()) else None
+    return CellComparison(cell.cell_id, reference.cell_id, len(keys), int(diff.sum()), float(gap.max()), worst)
+
+
+def run_manifest_chain_gate(model, *, gold_model=None, manifest=None, cells: _Sequence[str] = ("permuted", "long_padding", "singletons",
+                                                                                              "chunked", "decode"),
+                            execution_dtype: str | torch.dtype = "float32", contract=None) -> ChainGateReport:
+    """Run ``model`` (a ``Qwen3DenseBIModel``-like object) over the manifest's logical batch in the named cells.  Passed =
+    every cell agrees bit for bit with ``BN/full`` on every scored token and, with a ``gold_model``, the chain aggregates
+    against the gold are within the contract's thresholds for ``execution_dtype``."""
+    from rl_kernel_b200.config.workload import (batch_permutation_from_manifest, build_logical_batch, chunk_plan_from_manifest, fixture_hash,
+                                                load_manifest)
+    from rl_kernel_b200.contracts.numerical import compute_logprob_aggregates, judge_logprob_aggregates
+
+    m = manifest or load_manifest()
+    batch = build_logical_batch(m)
+    out: dict[str, CellOutput] = {"BN/full": _padded_cell(model, batch, "BN/full", capture=True)}
+    longest = max(s.seq_len for s in batch.samples)
+    for name in cells:
+        if name == "permuted":
+            perm = list(batch_permutation_from_manifest(m))
+            out["BN/permuted"] = _padded_cell(model, batch, "BN/permuted", order=perm if len(perm) == len(batch.samples)
+                                              else list(range(len(batch.samples)))[::-1])
+        elif name == "long_padding":
+            out["BN/long_padding"] = _padded_cell(model, batch, "BN/long_padding", padded_len=longest + 37)
+        elif name == "singletons":
+            out["B1-singleton_aggregate/full"] = _singleton_cell(model, batch, "B1-singleton_aggregate/full")
+        elif name == "chunked":
+            out["B1/chunked"] = _chunked_cell(model, batch, "B1/chunked", chunk_plan_from_manifest(m).chunk_size)
+        elif name == "decode":
+            out["B1/decode"] = _chunked_cell(model, batch, "B1/decode", 1, decode=True)
+        else:
+            raise ValueError(f"unknown cell {name!r}")
+    base = out["BN/full"]
+    inv = tuple(compare_cells(c, base) for k, c in out.items() if k != "BN/full")
+    accuracy, first = None, None
+    ok = all(c.passed for c in inv)
+    if gold_model is not None:
+        gold = _padded_cell(gold_model, batch, "gold/BN/full", capture=True)
+        keys = sorted(base.selected_logp)
+        cand = torch.stack([base.selected_logp[k] for k in keys]).float()
+        ref = torch.stack([gold.selected_logp[k] for k in keys]).float()
+        verdict = judge_logprob_aggregates(compute_logprob_aggregates(cand, ref, report_kind="forward_accuracy", contract=contract),
+                                           execution_dtype, contract)
+        accuracy = verdict.to_dict()
+        ok = ok and verdict.passed
+        if not verdict.passed:
+            first = next((n for n in model.node_names() if n in base.node_digests and n in gold.node_digests
+                          and base.node_digests[n] != gold.node_digests[n]), None)
+    return ChainGateReport(m.workload_id, fixture_hash(m), m.seed, "cpu", str(execution_dtype).removeprefix("torch."), out, inv, accuracy, first, ok)

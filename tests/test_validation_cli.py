@@ -268,3 +268,43 @@ def test_gradient_adapter_registry_and_status_matrix():
     paths = ga.listed_source_paths(ga.get_adapter("attention"))
     assert paths and all(p.exists() for p in paths)
     assert dataclasses.is_dataclass(ga.get_adapter("pack")) and ga.get_adapter("pack").requirement == "layout_supported"
+
+
+def test_manifest_chain_gate_cells_accuracy_and_first_drift():
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.reference import Qwen3DenseBIModel
+    from rl_kernel_b200.validation.models.chain_gate import run_manifest_chain_gate
+
+    spec = Qwen3DenseSpec.scaled(layers=1, hidden=64, ffn=128, q_heads=4, kv_heads=2, head_dim=16, vocab=6600)
+    w = Qwen3DenseWeights.synthetic(spec, seed=1)
+    gold = Qwen3DenseBIModel(spec, w)
+    rep = run_manifest_chain_gate(Qwen3DenseBIModel(spec, w), gold_model=gold)
+    assert rep.passed and {c.cell_id for c in rep.invariance} == {"BN/permuted", "BN/long_padding", "B1-singleton_aggregate/full", "B1/chunked",
+                                                                    "B1/decode"}
+    assert all(c.tokens == 27 and c.mismatching_tokens == 0 for c in rep.invariance) and rep.accuracy["passed"] and rep.first_drift is None
+    d = rep.to_dict()
+    assert d["cells"]["BN/full"]["n_logp_tokens"] == 27 and "embedding" in d["cells"]["BN/full"]["node_digests"] and d["fixture_hash"]
+    # a bf16 candidate is judged against the fp32 gold with the bf16 thresholds
+    bf = run_manifest_chain_gate(Qwen3DenseBIModel(spec, w, execution_dtype=torch.bfloat16), gold_model=gold, cells=("singletons",),
+                                 execution_dtype=torch.bfloat16)
+    assert bf.passed and bf.accuracy["aggregates"]["max_abs_dlogp"] > 0
+    # a model whose arithmetic depends on which rows share a call is caught by the cells, with the worst token named
+
+    class Leaky(Qwen3DenseBIModel):
+        def selected_logprobs(self, rows, targets):
+            lp = super().selected_logprobs(rows, targets)
+            return lp + (1e-3 if rows.shape[0] > 30 else 0.0)
+
+    bad = run_manifest_chain_gate(Leaky(spec, w), cells=("singletons", "permuted"))
+    by = {c.cell_id: c for c in bad.invariance}
+    assert not bad.passed and by["B1-singleton_aggregate/full"].mismatching_tokens == 27 and by["BN/permuted"].passed
+    assert by["B1-singleton_aggregate/full"].worst_key is not None
+    # a candidate with one perturbed layer fails the accuracy judgment and the first drifting node is reported
+    w2 = Qwen3DenseWeights.synthetic(spec, seed=1)
+    key = next(k for k in w2.tensors if "mlp" in k and "down" in k) if hasattr(w2, "tensors") else None
+    if key is not None:
+        w2.tensors[key] = w2.tensors[key] * 4.0
+        off = run_manifest_chain_gate(Qwen3DenseBIModel(spec, w2), gold_model=gold, cells=())
+        assert not off.passed and off.first_drift == "layers.0.residual_mlp"
+    with pytest.raises(ValueError, match="unknown cell"):
+        run_manifest_chain_gate(Qwen3DenseBIModel(spec, w), cells=("nope",))
