@@ -77,6 +77,30 @@ def cmd_ops(args) -> int:
     return 0
 
 
+def cmd_chain_gate(args) -> int:
+    """The model chain gate over the workload manifest on a scaled CPU model (seconds; no GPU needed)."""
+    import torch
+
+    from rl_kernel_b200.models.qwen3 import Qwen3DenseSpec, Qwen3DenseWeights
+    from rl_kernel_b200.models.qwen3.reference import Qwen3DenseBIModel
+    from rl_kernel_b200.validation.models.chain_gate import run_manifest_chain_gate
+
+    spec = Qwen3DenseSpec.scaled(layers=args.layers, hidden=args.hidden, ffn=2 * args.hidden, q_heads=4, kv_heads=2, head_dim=args.hidden // 4,
+                                 vocab=args.vocab)
+    w = Qwen3DenseWeights.synthetic(spec, seed=args.seed)
+    dtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[args.dtype]
+    rep = run_manifest_chain_gate(Qwen3DenseBIModel(spec, w, execution_dtype=dtype), gold_model=Qwen3DenseBIModel(spec, w),
+                                  cells=tuple(c for c in args.cells.split(",") if c), execution_dtype=dtype)
+    out = rep.to_dict()
+    if args.out:
+        Path(args.out).parent.mkdir(parents=True, exist_ok=True)
+        Path(args.out).write_text(json.dumps(out, indent=1, default=str))
+    print(json.dumps({"passed": rep.passed, "first_drift": rep.first_drift,
+                      "cells": {c["cell_id"]: f"{c['mismatching_tokens']}/{c['tokens']}" for c in out["invariance"]},
+                      "accuracy": None if out["accuracy"] is None else out["accuracy"]["aggregates"]}, indent=1, default=str))
+    return 0 if rep.passed else 2
+
+
 def cmd_prepare(args) -> int:
     prof = {"python": sys.executable, "created": time.time(), "gpus": args.gpus, "run_root": str(Path(args.run_root).resolve())}
     Path(args.profile).write_text(json.dumps(prof, indent=1))
@@ -348,6 +372,15 @@ def build_parser() -> argparse.ArgumentParser:
     ap = argparse.ArgumentParser(prog="rlk", description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="cmd", required=True)
     sub.add_parser("doctor").set_defaults(fn=cmd_doctor)
+    p = sub.add_parser("chain-gate", help="model chain gate over the workload manifest on a scaled CPU model")
+    p.add_argument("--layers", type=int, default=2)
+    p.add_argument("--hidden", type=int, default=64)
+    p.add_argument("--vocab", type=int, default=6600)
+    p.add_argument("--dtype", choices=("float32", "bfloat16"), default="float32")
+    p.add_argument("--cells", default="permuted,long_padding,singletons,chunked,decode")
+    p.add_argument("--seed", type=int, default=1)
+    p.add_argument("--out", default=None)
+    p.set_defaults(fn=cmd_chain_gate)
     p = sub.add_parser("ops", help="list operators and the backend each would resolve to on this machine")
     p.add_argument("op", nargs="*")
     p.add_argument("--json", action="store_true")

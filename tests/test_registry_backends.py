@@ -139,3 +139,16 @@ def test_rlk_ops_lists_candidates(capsys):
     assert main(["ops", "rope"]) == 0
     text = capsys.readouterr().out
     assert text.startswith("rope\n") and "* reference" in text
+
+
+def test_rlk_chain_gate_command(tmp_path, capsys):
+    import json
+
+    from rl_kernel_b200.entrypoints.repro import main
+
+    out = tmp_path / "gate" / "report.json"
+    assert main(["chain-gate", "--layers", "1", "--cells", "singletons,chunked", "--out", str(out)]) == 0
+    summary = json.loads(capsys.readouterr().out)
+    assert summary["passed"] and summary["cells"] == {"B1-singleton_aggregate/full": "0/27", "B1/chunked": "0/27"}
+    rep = json.loads(out.read_text())
+    assert rep["cells"]["BN/full"]["n_logp_tokens"] == 27 and rep["accuracy"]["passed"]
