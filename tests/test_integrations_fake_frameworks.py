@@ -397,3 +397,59 @@ def test_megatron_install_records_hooks_patches_linears_and_uninstalls():
     assert Column(w1)(x) == ("framework", None) and Norm()(x) == "framework" and not hasattr(Out, "selected_logprobs")
     with pytest.raises(MegatronUnavailable):
         resolve_megatron_classes()
+
+
+def test_vllm_operators_provenance_page_validation_and_packed_ffn_binding():
+    import types
+
+    from rl_kernel_b200.integrations.engines.rollout.vllm.operators import PAGE, VllmAttentionOperator, VllmFFNOperator, VllmLogpOperator
+
+    g = torch.Generator().manual_seed(0)
+    # FFN: weights are read out of an engine-style MLP module ([gate; up] rows) and give silu(gate) * up @ down
+    H, I = 32, 64
+    mlp = types.SimpleNamespace(gate_up_proj=types.SimpleNamespace(weight=torch.randn(2 * I, H, generator=g) * 0.2),
+                                down_proj=types.SimpleNamespace(weight=torch.randn(H, I, generator=g) * 0.2))
+    ffn = VllmFFNOperator(canonical_tp=8, tp_size=1)
+    assert ffn.bind_packed_inference(mlp) == (H, I) and mlp.rlk_w_gu.shape == (2 * I, H) and mlp.rlk_ffn_version == 1
+    x = torch.randn(5, H, generator=g)
+    gate, up = mlp.gate_up_proj.weight[:I], mlp.gate_up_proj.weight[I:]
+    want = (torch.nn.functional.silu(x @ gate.t()) * (x @ up.t())) @ mlp.down_proj.weight.t()
+    assert torch.allclose(ffn(mlp, x), want, atol=1e-4) and ffn.provenance["calls"] == 1 and ffn.provenance["local_k_chunks"] == 8
+    fresh = types.SimpleNamespace(gate_up_proj=mlp.gate_up_proj, down_proj=mlp.down_proj)
+    assert torch.allclose(VllmFFNOperator()(fresh, x), want, atol=1e-4) and hasattr(fresh, "rlk_w_gu")      # bound on first use
+    with pytest.raises(ValueError, match="canonical shards"):
+        VllmFFNOperator(canonical_tp=8).bind_packed_inference(types.SimpleNamespace(
+            gate_up_proj=types.SimpleNamespace(weight=torch.zeros(2 * 12, H)), down_proj=types.SimpleNamespace(weight=torch.zeros(H, 12))))
+    # log-prob operator
+    lp_op = VllmLogpOperator(temperature=0.5, real_vocab=40)
+    w, hid, ids = torch.randn(48, H, generator=g), torch.randn(6, H, generator=g), torch.randint(0, 40, (6,), generator=g)
+    got = lp_op(hid, w, ids)
+    assert torch.allclose(got, torch.log_softmax((hid @ w[:40].t()) / 0.5, -1).gather(1, ids[:, None])[:, 0], atol=1e-4)
+    assert lp_op.provenance["calls"] == 1 and lp_op.provenance["real_vocab_size"] == 40 and lp_op.provenance["runtime_platform"] == "cpu-reference"
+    # attention over a block cache: provenance and the one-time page / slot validation
+    hq, hkv, d, nb = 4, 2, 16, 6
+    layer = types.SimpleNamespace(num_heads=hq, num_kv_heads=hkv, head_dim=d, head_size=d, scale=None)
+    cache = torch.zeros(2, nb, PAGE, hkv, d)
+    n = 5
+    q, k, v = (torch.randn(n, h * d, generator=g) for h in (hq, hkv, hkv))
+    md = types.SimpleNamespace(num_actual_tokens=n, slot_mapping=torch.arange(n) + 2 * PAGE, block_table=torch.tensor([[2, 0, 0]]),
+                               seq_lens=torch.tensor([n]), query_start_loc=torch.tensor([0, n]))
+    op = VllmAttentionOperator()
+    out = op(layer, q, k, v, kv_cache=cache, attn_metadata=md)
+    from rl_kernel_b200.ops.attention.attention import causal_attention
+
+    assert torch.allclose(out, causal_attention(q.view(n, hq, d), k.view(n, hkv, d), v.view(n, hkv, d), [0, n]).reshape(n, hq * d), atol=1e-5)
+    prov = op.provenance
+    assert prov["calls"]["paged"] == 1 and prov["phase"] == "prefill_or_mixed" and prov["split_kv"] == "disabled" and prov["kv_block"] == PAGE
+    bad = types.SimpleNamespace(num_actual_tokens=n, slot_mapping=torch.arange(n) + 2 * PAGE, block_table=torch.tensor([[9, 0]]),
+                                seq_lens=torch.tensor([n]), query_start_loc=torch.tensor([0, n]))
+    with pytest.raises(ValueError, match="outside the pool of 6 pages"):
+        VllmAttentionOperator()(layer, q, k, v, kv_cache=cache, attn_metadata=bad)
+    off = types.SimpleNamespace(num_actual_tokens=n, slot_mapping=torch.arange(n) + nb * PAGE, block_table=torch.tensor([[2, 0, 0]]),
+                                seq_lens=torch.tensor([n]), query_start_loc=torch.tensor([0, n]))
+    with pytest.raises(ValueError, match="token slots"):
+        VllmAttentionOperator()(layer, q, k, v, kv_cache=cache, attn_metadata=off)
+    short = types.SimpleNamespace(num_actual_tokens=1, slot_mapping=torch.tensor([PAGE * 3]), block_table=torch.tensor([[1, 2]]),
+                                  seq_lens=torch.tensor([3 * PAGE]), query_start_loc=torch.tensor([0, 1]))
+    with pytest.raises(ValueError, match="needs 3 pages"):
+        VllmAttentionOperator()(layer, q[:1], k[:1], v[:1], kv_cache=cache, attn_metadata=short)
