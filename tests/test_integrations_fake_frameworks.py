@@ -453,3 +453,67 @@ def test_vllm_operators_provenance_page_validation_and_packed_ffn_binding():
                                   seq_lens=torch.tensor([3 * PAGE]), query_start_loc=torch.tensor([0, 1]))
     with pytest.raises(ValueError, match="needs 3 pages"):
         VllmAttentionOperator()(layer, q[:1], k[:1], v[:1], kv_cache=cache, attn_metadata=short)
+
+
+def test_ray_manager_specs_options_typed_handles_and_runtime():
+    from rl_kernel_b200.integrations.common.ray_actor_manager import (RayActorOptions, RayRuntimeConfig, RayUnavailableError, RayWorkerSpec,
+                                                                      load_ray)
+
+    opts = RayActorOptions(num_gpus=0.5, resources={"nvlink_domain": 1}, name="trainer-0", max_restarts=2)
+    assert opts.to_ray_options() == {"num_gpus": 0.5, "name": "trainer-0", "max_restarts": 2, "resources": {"nvlink_domain": 1}}
+    assert RayRuntimeConfig(init_kwargs={"num_cpus": 4}).resolved_init_kwargs() == {"ignore_reinit_error": True, "num_cpus": 4}
+    with pytest.raises(RayUnavailableError):
+        load_ray()
+
+    class Ray(FakeRay):
+        def __init__(self):
+            self.inits, self.shutdowns, self.options = [], 0, []
+
+        def init(self, **kw):
+            self.inits.append(kw)
+
+        def shutdown(self):
+            self.shutdowns += 1
+
+        def remote(self, **kw):
+            self.options.append(kw)
+            return super().remote(**kw)
+
+    class Trainer:
+        def __init__(self, scale):
+            self.scale, self.released = scale, []
+
+        def train(self, rollout):
+            return rollout * self.scale
+
+        def publish_weights(self, weight_version, tag=None):
+            return {"weight_version": weight_version, "tag": tag}
+
+        def release_weights(self, update_id):
+            self.released.append(update_id)
+            return list(self.released)
+
+        def health_check(self):
+            return {"step": 7}
+
+    class Rollout:
+        def rollout(self, spec):
+            return [spec] * 2
+
+        def update_weights(self, manifest):
+            return manifest["weight_version"]
+
+        def release_weights(self):
+            return "released"
+
+    ray = Ray()
+    with RayActorManager(ray_module=ray, runtime=RayRuntimeConfig(shutdown_ray_on_close=True)) as mgr:
+        t = mgr.create_training_worker(RayWorkerSpec(Trainer, args=(3,), actor_options=opts))
+        r = mgr.create_rollout_worker(RayWorkerSpec(Rollout))
+        assert ray.inits == [{"ignore_reinit_error": True}] and ray.options[0]["name"] == "trainer-0" and ray.options[1] == {"num_gpus": 1.0}
+        assert t.train(5) == 15 and t.publish_weights(4, tag="x") == {"weight_version": 4, "tag": "x"} and t.release_weights("u1") == ["u1"]
+        assert r.rollout("p") == ["p", "p"] and r.update_weights({"weight_version": 4}) == 4 and r.release_weights() == "released"
+        assert set(mgr.workers) == {"trainer-0", "rollout-1"} and mgr.health_check() == {"trainer-0": True, "rollout-1": True}
+        with pytest.raises(ValueError, match="already exists"):
+            mgr.create_training_worker(RayWorkerSpec(Trainer, args=(1,), actor_options=opts))
+    assert ray.shutdowns == 1 and not mgr.workers
