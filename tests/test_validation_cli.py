@@ -308,3 +308,34 @@ def test_manifest_chain_gate_cells_accuracy_and_first_drift():
         assert not off.passed and off.first_drift == "layers.0.residual_mlp"
     with pytest.raises(ValueError, match="unknown cell"):
         run_manifest_chain_gate(Qwen3DenseBIModel(spec, w), cells=("nope",))
+
+
+def test_classified_four_judgment_grid():
+    from rl_kernel_b200.validation.operators import four_judgment_matrix as fj
+
+    rep = fj.build_classified_matrix()
+    assert len(rep.cells) == 2 * len(fj.REQUIRED_OPS) * len(fj.TIERS) * len(fj.JUDGMENTS)
+    assert set(rep.counts) <= {"pending_execution", "N/A"} and not fj.undefined_cells(rep) and not fj.hidden_required_na(rep), rep.counts
+    assert all(c.status == "N/A" and "layout_supported" in c.detail for c in rep.cells if c.op_name == "pack")
+    cell = next(c for c in rep.cells if c.profile == "b200_bf16" and c.op_name == "det_gemm" and c.tier == "short" and c.judgment == "forward_accuracy")
+    assert cell.case_id.startswith("gemm-short") and cell.candidate == "b200" and cell.evidence_kind == "representative_accuracy"
+    assert not rep.green                                                       # nothing has been executed yet
+    # executed judgments turn pending cells green (or red)
+    ran = fj.executed_results("reference_fp32", ("rms_norm", "swiglu"), candidate="pytorch")
+    ran[("reference_fp32", "swiglu")] = {**ran[("reference_fp32", "swiglu")], "gradient_invariance": ("fail", "B1/singletons:dx")}
+    rep2 = fj.build_classified_matrix(profiles=("reference_fp32",), executed=ran)
+    by = {(c.op_name, c.tier, c.judgment): c for c in rep2.cells}
+    assert by[("rms_norm", "primary", "forward_invariance")].status == "green"
+    assert by[("swiglu", "short", "gradient_invariance")].status == "red" and "B1/singletons" in by[("swiglu", "short", "gradient_invariance")].detail
+    assert by[("rope", "primary", "forward_accuracy")].status == "pending_execution"
+    with pytest.raises(ValueError, match="unknown backend profiles"):
+        fj.build_classified_matrix(profiles=("cuda_fp8",))
+    # an operator the profile runs but nothing can judge is red, never N/A
+    from rl_kernel_b200.validation.operators import gradient_adapters as ga
+
+    saved = ga.OP_SPECS["rope"].candidate_paths.pop("b200")
+    try:
+        red = [c for c in fj.build_classified_matrix(profiles=("b200_bf16",)).cells if c.op_name == "rope"]
+        assert red and all(c.status == "red" and "missing_candidate" in c.detail for c in red)
+    finally:
+        ga.OP_SPECS["rope"].candidate_paths["b200"] = saved
