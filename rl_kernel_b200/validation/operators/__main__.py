@@ -29,6 +29,34 @@ def _dev(a):
     return dev, dtype, acc.describe(dev).to_dict()
 
 
+def cmd_grid(args) -> int:
+    import json as _json
+
+    import torch as _torch
+
+    from rl_kernel_b200.validation.operators import four_judgment_matrix as fj
+
+    profiles = (args.profile,) if args.profile else None
+    executed = None
+    if args.execute:
+        prof = args.profile or ("b200_bf16" if args.device.startswith("cuda") else "reference_fp32")
+        profiles = (prof,)
+        cuda = args.device.startswith("cuda")
+        executed = fj.executed_results(prof, device=args.device, dtype=_torch.bfloat16 if cuda else _torch.float32,
+                                       candidate="b200" if cuda else "pytorch")
+    rep = fj.build_classified_matrix(profiles=profiles, executed=executed)
+    if args.json:
+        print(_json.dumps(rep.to_dict(), indent=1))
+    else:
+        for c in rep.cells:
+            if c.judgment == "forward_accuracy":
+                row = [x for x in rep.cells if (x.profile, x.op_name, x.tier) == (c.profile, c.op_name, c.tier)]
+                print(f"{c.profile:<15} {c.op_name:<12} {c.tier:<8} " + " ".join(f"{x.status:<18}" for x in row) + f" {c.case_id or '-'}")
+        print(rep.counts)
+    bad = [c for c in rep.cells if c.status == "red"]
+    return 2 if bad or (args.execute and not rep.green) else 0
+
+
 def cmd_adapters(args) -> int:
     import json as _json
 
@@ -136,6 +164,12 @@ def main(argv=None) -> int:
         p.add_argument("--seed", type=int, default=0)
 
     sub.add_parser("list").set_defaults(fn=cmd_list)
+    p = sub.add_parser("grid", help="coverage grid of the four judgments; --execute runs them on this host for one profile")
+    p.add_argument("--profile", default=None)
+    p.add_argument("--execute", action="store_true")
+    p.add_argument("--device", default="cpu")
+    p.add_argument("--json", action="store_true")
+    p.set_defaults(fn=cmd_grid)
     p = sub.add_parser("adapters", help="status matrix: backend profile x chain node -> adapter, candidate, coverage")
     p.add_argument("--json", action="store_true")
     p.set_defaults(fn=cmd_adapters)
