@@ -339,3 +339,17 @@ def test_classified_four_judgment_grid():
         assert red and all(c.status == "red" and "missing_candidate" in c.detail for c in red)
     finally:
         ga.OP_SPECS["rope"].candidate_paths["b200"] = saved
+
+
+def test_operators_cli_grid_and_adapters(capsys):
+    import json
+
+    from rl_kernel_b200.validation.operators.__main__ import main as check
+
+    assert check(["adapters", "--json"]) == 0
+    rows = json.loads(capsys.readouterr().out)
+    assert {r["backend_profile"] for r in rows} == {"b200_bf16", "reference_fp32"} and not any(r["untracked_red"] for r in rows)
+    assert check(["grid", "--profile", "b200_bf16", "--json"]) == 0
+    grid = json.loads(capsys.readouterr().out)
+    assert grid["counts"] == {"pending_execution": 72, "N/A": 8}
+    assert check(["grid", "--profile", "reference_fp32"]) == 0 and "pending_execution" in capsys.readouterr().out
