@@ -277,3 +277,57 @@ def test_drift_report_bundle_from_sealed_attempts(tmp_path):
     (attempt / "result.json").write_text("{}")
     broken = build_cross_config_attempt_report(attempt)
     assert broken["level"] == "failure" and "seal" in broken["reason"]
+
+
+def test_artifact_store_is_append_only_atomic_and_sealed(tmp_path):
+    import torch
+
+    from rl_kernel_b200.validation.cross_config.artifacts import ArtifactError, ArtifactStore
+
+    store = ArtifactStore(tmp_path)
+    cfg = {"model": "tiny", "knobs": {"tp": [1, 2]}}
+    d = store.initialize_experiment("exp-1", cfg, plan={"cases": ["a", "b"]})
+    assert store.initialize_experiment("exp-1", cfg, plan={"cases": ["a", "b"]}) == d                    # re-opening with the same content
+    with pytest.raises(ArtifactError, match="different content"):
+        store.initialize_experiment("exp-1", {**cfg, "model": "other"})
+    for bad in ("../x", "a/b", "", ".hidden", "x" * 200):
+        with pytest.raises(ArtifactError, match="safe path component"):
+            store.experiment_dir(bad)
+    req = {"case": "a", "seed": 1}
+    a0 = store.create_attempt("exp-1", "case-a", req)
+    a1 = store.create_attempt("exp-1", "case-a", req)
+    assert (a0.name, a1.name) == ("0", "1") and (a0 / "request.json").exists()
+    store.write_json(a0, "rollout", {"x": 1})
+    store.write_json(a0, "rollout.json", {"x": 1})                                                        # identical content: a no-op
+    with pytest.raises(ArtifactError, match="different content"):
+        store.write_json(a0, "rollout", {"x": 2})
+    with pytest.raises(ArtifactError):
+        store.write_json(a0, "../escape", {"x": 1})
+    bundle = store.write_tensor_bundle(a0, "tensors", {"logp": torch.arange(6.0)}, metadata={"tokens": 6})
+    with pytest.raises(ArtifactError, match="append-only"):
+        store.write_tensor_bundle(a0, "tensors", {"logp": torch.zeros(1)})
+    loaded = store.load_tensor_bundle(bundle)
+    assert torch.equal(loaded["tensors"]["logp"], torch.arange(6.0)) and loaded["metadata"] == {"tokens": 6}
+    assert store.completed_attempt("exp-1", "case-a") is None
+    store.complete_attempt(a0, {"mismatches": 0})
+    rec = store.validate_completed_attempt(a0)
+    assert set(rec["artifacts"]) == {"request.json", "rollout.json", "tensors.pt"} and rec["summary"] == {"mismatches": 0}
+    assert store.completed_attempt("exp-1", "case-a", req) == a0 and store.completed_attempt("exp-1", "case-a", {"case": "a", "seed": 2}) is None
+    with pytest.raises(ArtifactError, match="already complete"):
+        store.complete_attempt(a0)
+    with pytest.raises(ArtifactError, match="nothing can be added"):
+        store.write_json(a0, "late", {})
+    assert not [p for p in a0.iterdir() if ".tmp" in p.name]                                              # no half-written files are left behind
+    # tampering is found, and a newer intact attempt is preferred
+    (a0 / "rollout.json").write_text("{}")
+    with pytest.raises(ArtifactError, match="modified after completion"):
+        store.validate_completed_attempt(a0)
+    assert store.completed_attempt("exp-1", "case-a") is None
+    store.complete_attempt(a1)
+    assert store.completed_attempt("exp-1", "case-a") == a1
+    (a1 / "extra.json").write_text("{}")
+    with pytest.raises(ArtifactError, match="added"):
+        store.validate_completed_attempt(a1)
+    with pytest.raises(ArtifactError, match="not a tensor bundle"):
+        torch.save({"x": 1}, tmp_path / "other.pt")
+        store.load_tensor_bundle(tmp_path / "other.pt")
