@@ -189,7 +189,8 @@ class ChildSupervisor:
     """Runs ``fn(rank, *args)`` in ``nprocs`` children with a deadline and returns their saved values in rank order."""
 
     def __init__(self, start_method: Optional[str] = None):
-        self.ctx = mp.get_context(start_method or "spawn")
+        self.start_method = start_method or "spawn"
+        self.ctx = mp.get_context(self.start_method)
         self._children: list = []
 
     def active_child_pids(self) -> tuple[int, ...]:

@@ -161,3 +161,89 @@ def run_alignment(config, out_dir, *, rollout, training, materializers, bitwise:
     (Path(out_dir) / config.definition.experiment_id).mkdir(parents=True, exist_ok=True)
     (Path(out_dir) / config.definition.experiment_id / "paired_summary.json").write_text(strict_json_dumps(pv.json_safe(summary), indent=1))
     return summary
+
+
+# ================================================================================================ one case, one attempt
+@dataclasses.dataclass(frozen=True)
+class PairedRunResult:
+    """A completed attempt of one case, or a validated earlier attempt that was reused."""
+    case_id: str
+    attempt_id: str
+    attempt_dir: Path
+    resumed: bool
+    rollout_score: object = None
+    training_score: object = None
+    alignment: object = None
+    summary: dict = dataclasses.field(default_factory=dict)
+
+
+class PairedRunner:
+    """Score ONE materialised case on both sides and publish it as one append-only attempt of an ``ArtifactStore``
+    (parity: PairedRunner, rl_engine/validation/cross_config/runner.py:88-440).  ``run`` refuses a case that is not
+    executable, checks that the two scorers name opposite sides of the same model, scores under the read-only guard,
+    checks every rank's output, compares under the fixed-threshold contract and seals the attempt; with ``resume`` an
+    intact earlier attempt made for the same execution fingerprint is returned instead."""
+
+    def __init__(self, artifact_store, *, timeout_seconds: float = 30.0, start_method=None):
+        import math
+
+        from rl_kernel_b200.validation.cross_config._execution import ChildSupervisor
+        if not math.isfinite(timeout_seconds) or timeout_seconds <= 0.0:
+            raise ValueError("timeout_seconds must be finite and greater than zero")
+        self.artifact_store = artifact_store
+        self.timeout_seconds = float(timeout_seconds)
+        self._children = ChildSupervisor(start_method)
+        self.start_method = self._children.start_method
+
+    @property
+    def active_child_pids(self) -> tuple[int, ...]:
+        return self._children.active_child_pids()
+
+    def run(self, experiment_id: str, case, materialization, batch, rollout_scorer, training_scorer, *, materializers=(),
+            bitwise: bool = False, resume: bool = True) -> PairedRunResult:
+        from rl_kernel_b200.validation.cross_config import _execution as ex, _provenance as pv
+        from rl_kernel_b200.validation.cross_config.comparison import FixedThresholdComparator
+        from rl_kernel_b200.validation.cross_config.schema import ScoreArtifact, ScoreSide
+
+        if materialization.case.case.case_id != case.case_id:
+            raise ex.PairedRunnerError(f"materialization is for case {materialization.case.case.case_id!r}, not {case.case_id!r}")
+        if not materialization.executable:
+            raise ex.PairedRunnerError(f"case {case.case_id!r} is not executable: {materialization.case.status.value}")
+        r_spec, t_spec = ex.validate_scorer_identity(rollout_scorer, training_scorer)
+        env = pv.execution_environment_provenance()
+        fps = {"rollout": ex.scorer_implementation_fingerprint(rollout_scorer), "training": ex.scorer_implementation_fingerprint(training_scorer),
+               **{f"materializer.{m.target}": m.implementation_fingerprint() for m in materializers}}
+        efp = pv.execution_fingerprint(materialization, scorer_fingerprints=fps, environment=env)
+        request = {"case_id": case.case_id, "execution_fingerprint": efp, "bitwise": bool(bitwise),
+                   "requested": pv.json_safe(dict(case.requested))}
+        store = self.artifact_store
+        store.experiment_dir(experiment_id).mkdir(parents=True, exist_ok=True)
+        if resume:
+            prev = store.completed_attempt(experiment_id, case.case_id, request)
+            if prev is not None:
+                rec = store.validate_completed_attempt(prev)
+                return PairedRunResult(case.case_id, f"{case.case_id}/{prev.name}", prev, True, summary=dict(rec["summary"]))
+        attempt = store.create_attempt(experiment_id, case.case_id, request)
+        attempt_id = f"{case.case_id}/{attempt.name}"
+        arts = {}
+        for side, scorer, spec in ((ScoreSide.ROLLOUT, rollout_scorer, r_spec), (ScoreSide.TRAINING, training_scorer, t_spec)):
+            opts = dict(materialization.adapters[side.value].options) if side.value in materialization.adapters else {}
+            with ex.read_only_scoring_guard(scorer):
+                ranks = scorer.score(batch, options=opts)
+            top = ex.validate_rank_outputs(ranks, batch, expected_world_size=spec.world_size)
+            prov = pv.side_provenance(side, materialization, actual=dict(top.actual), implementation_fingerprint=fps[side.value],
+                                      world_size=spec.world_size)
+            arts[side] = ScoreArtifact(case.case_id, attempt_id, side, case.identity, spec, top.selected_logprobs, batch.active_mask, prov)
+            store.write_json(attempt, side.value, pv.json_safe({**pv.score_metadata(arts[side]), "provenance": prov.to_dict()}))
+        result = FixedThresholdComparator(bitwise=bitwise).compare(arts[ScoreSide.ROLLOUT], arts[ScoreSide.TRAINING])
+        tokens = result.token_artifact
+        store.write_tensor_bundle(attempt, "tensors", {
+            "rollout_logprobs": arts[ScoreSide.ROLLOUT].selected_logprobs.masked_fill(~batch.active_mask, 0.0),
+            "training_logprobs": arts[ScoreSide.TRAINING].selected_logprobs.masked_fill(~batch.active_mask, 0.0),
+            "active_mask": batch.active_mask, **({"mismatch_mask": tokens.mismatch_mask} if tokens is not None else {})},
+            metadata={"case_id": case.case_id, "attempt_id": attempt_id})
+        store.write_json(attempt, "result", pv.json_safe({k: v for k, v in result.to_dict().items() if k != "token_artifact"}))
+        summary = {"status": result.status.value, "passed": bool(result.passed), "mismatch_count": int(result.mismatch_count),
+                   "active_token_count": int(result.active_token_count), "execution_fingerprint": efp}
+        store.complete_attempt(attempt, summary)
+        return PairedRunResult(case.case_id, attempt_id, attempt, False, arts[ScoreSide.ROLLOUT], arts[ScoreSide.TRAINING], result, summary)

@@ -331,3 +331,34 @@ def test_artifact_store_is_append_only_atomic_and_sealed(tmp_path):
     with pytest.raises(ArtifactError, match="not a tensor bundle"):
         torch.save({"x": 1}, tmp_path / "other.pt")
         store.load_tensor_bundle(tmp_path / "other.pt")
+
+
+def test_paired_runner_publishes_one_append_only_attempt_per_case(tmp_path):
+    import rl_kernel_b200.validation.cross_config as cc
+    from rl_kernel_b200.validation.cross_config.execution_plan import build_execution_plan
+
+    assert {"PairedRunner", "PairedRunResult", "Planner", "ArtifactStore", "compare_score_artifacts", "load_config"} <= set(cc.__all__)
+    cfg = config_from_dict(_raw())
+    ro, tr = ReferenceModelScorer("rollout", prefill_tokens=5), ReferenceModelScorer("training")
+    store, runner = cc.ArtifactStore(tmp_path), cc.PairedRunner(cc.ArtifactStore(tmp_path), timeout_seconds=20.0)
+    with pytest.raises(ValueError):
+        cc.PairedRunner(store, timeout_seconds=0.0)
+    mats, tools = reference_materializers(), RuntimeTools()
+    batch = CanonicalScoringBatch.from_identity(cfg.definition.identity)
+    case = build_execution_plan(cfg).entries[0].case
+    m = tools.materialize(case, mats)
+    r = runner.run("exp", case, m, batch, ro, tr, materializers=mats, bitwise=True)
+    assert not r.resumed and r.alignment.passed and r.summary["mismatch_count"] == 0 and r.summary["active_token_count"] == 24
+    rec = store.validate_completed_attempt(r.attempt_dir)
+    assert set(rec["artifacts"]) == {"request.json", "rollout.json", "training.json", "tensors.pt", "result.json"}
+    bundle = store.load_tensor_bundle(r.attempt_dir / "tensors.pt")
+    assert torch.equal(bundle["tensors"]["rollout_logprobs"], bundle["tensors"]["training_logprobs"])
+    again = runner.run("exp", case, m, batch, ro, tr, materializers=mats, bitwise=True)
+    assert again.resumed and again.attempt_dir == r.attempt_dir and again.summary == r.summary
+    fresh = runner.run("exp", case, m, batch, ro, tr, materializers=mats, bitwise=True, resume=False)
+    assert not fresh.resumed and fresh.attempt_dir.name == "1"
+    other = runner.run("exp", case, m, batch, ro, tr, materializers=mats, bitwise=False)                  # another request: a new attempt
+    assert not other.resumed and other.attempt_dir.name == "2"
+    with pytest.raises(ex.PairedRunnerError, match="not executable|is for case"):
+        runner.run("exp", build_execution_plan(cfg).entries[1].case, m, batch, ro, tr)
+    assert runner.active_child_pids == ()
